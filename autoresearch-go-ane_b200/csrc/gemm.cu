@@ -1,0 +1,274 @@
+// GEMM launchers: tcgen05 bf16 path (gemm_tc.cuh) and the fp32 SIMT path.
+#include "gemm.h"
+
+#include <cuda.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <map>
+#include <mutex>
+#include <string>
+#include <tuple>
+
+#include "gemm_tc.cuh"
+
+namespace ane {
+
+static thread_local std::string g_gemm_err;
+const char* gemm_last_error() { return g_gemm_err.c_str(); }
+
+int gemm_num_sms() {
+  static int sms[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (sms[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    sms[dev] = n;
+  }
+  return sms[dev];
+}
+
+// ------------------------------------------------------------------------------------------
+// Tensor maps
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor [outer, inner] with row pitch ld (elements); box = [box_outer, box_inner].
+static bool make_tmap(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer) {
+  typedef std::tuple<int, const void*, uint64_t, uint64_t, uint64_t, uint32_t, uint32_t> Key;
+  static std::map<Key, CUtensorMap> cache;
+  static std::mutex mu;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  Key key(dev, ptr, inner, outer, ld, box_inner, box_outer);
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return true;
+  }
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    g_gemm_err = "cuTensorMapEncodeTiled entry point not available";
+    return false;
+  }
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ld * 2) % 16 != 0) {
+    g_gemm_err = "TMA operand must be 16-byte aligned with a 16-byte multiple row pitch";
+    return false;
+  }
+  cuuint64_t gdim[2] = {inner, outer};
+  cuuint64_t gstride[1] = {ld * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap tm;
+  CUresult r = fn(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[160];
+    snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed (%d) inner=%llu outer=%llu ld=%llu", (int)r,
+             (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)ld);
+    g_gemm_err = buf;
+    return false;
+  }
+  cache[key] = tm;
+  *out = tm;
+  return true;
+}
+
+template <int BN, bool A_MN, bool B_MN, class Epi>
+static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const Epi& epi, const GemmDesc& d,
+                     int split_k, int* d_status, cudaStream_t stream) {
+  auto kern = gemm_tc_kernel<BN, A_MN, B_MN, Epi>;
+  static bool attr_set = false;  // per template instantiation
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)GemmCfg<BN>::SMEM_BYTES);
+    if (e != cudaSuccess) {
+      g_gemm_err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e);
+      return -3;
+    }
+    attr_set = true;
+  }
+  const int tiles = ((d.M + GEMM_BM - 1) / GEMM_BM) * ((d.N + BN - 1) / BN) * split_k;
+  int grid = tiles < gemm_num_sms() ? tiles : gemm_num_sms();
+  if (grid < 1) grid = 1;
+  kern<<<grid, GEMM_THREADS, GemmCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, epi, d.M, d.N, d.K, split_k, d_status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    g_gemm_err = std::string("gemm_tc launch: ") + cudaGetErrorString(e);
+    return -4;
+  }
+  return 0;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int dispatch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const GemmDesc& d, int split_k,
+                        int* d_status, cudaStream_t stream) {
+  if (d.out == GEMM_OUT_BF16) {
+    EpiStore<bf16> epi{reinterpret_cast<bf16*>(d.C), d.ldc, d.alpha, d.res1, d.s1, d.res2, d.s2, d.ldres};
+    return launch_tc<BN, A_MN, B_MN>(ta, tb, epi, d, 1, d_status, stream);
+  } else if (d.out == GEMM_OUT_F32) {
+    EpiStore<float> epi{reinterpret_cast<float*>(d.C), d.ldc, d.alpha, d.res1, d.s1, d.res2, d.s2, d.ldres};
+    return launch_tc<BN, A_MN, B_MN>(ta, tb, epi, d, 1, d_status, stream);
+  } else {
+    EpiAtomicAdd epi{reinterpret_cast<float*>(d.C), d.ldc, d.alpha};
+    return launch_tc<BN, A_MN, B_MN>(ta, tb, epi, d, split_k, d_status, stream);
+  }
+}
+
+template <int BN>
+static int dispatch_layout(const GemmDesc& d, int split_k, int* d_status, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  bool ok;
+  if (!d.a_mn) ok = make_tmap(&ta, d.A, d.K, d.M, d.lda, GEMM_BK, GEMM_BM);
+  else         ok = make_tmap(&ta, d.A, d.M, d.K, d.lda, 64, GEMM_BK);
+  if (!ok) return -2;
+  if (!d.b_mn) ok = make_tmap(&tb, d.B, d.K, d.N, d.ldb, GEMM_BK, BN);
+  else         ok = make_tmap(&tb, d.B, d.N, d.K, d.ldb, 64, GEMM_BK);
+  if (!ok) return -2;
+  if (!d.a_mn && !d.b_mn) return dispatch_epi<BN, false, false>(ta, tb, d, split_k, d_status, stream);
+  if (!d.a_mn && d.b_mn) return dispatch_epi<BN, false, true>(ta, tb, d, split_k, d_status, stream);
+  if (d.a_mn && d.b_mn) return dispatch_epi<BN, true, true>(ta, tb, d, split_k, d_status, stream);
+  return dispatch_epi<BN, true, false>(ta, tb, d, split_k, d_status, stream);
+}
+
+int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream) {
+  if (d.M <= 0 || d.N <= 0 || d.K <= 0) return 0;
+  if (d.out == GEMM_OUT_BF16 && (d.ldc % 4) != 0) {
+    g_gemm_err = "bf16 output needs ldc % 4 == 0";
+    return -2;
+  }
+  if (d.out == GEMM_OUT_F32 && ((d.ldc % 4) != 0 || (d.res1 && d.ldres % 4 != 0))) {
+    g_gemm_err = "fp32 output needs ldc % 4 == 0";
+    return -2;
+  }
+  const bool wide = d.N > 768;
+  const int bn = wide ? 256 : 128;
+  int split_k = 1;
+  if (d.out == GEMM_OUT_ACCUM) {
+    split_k = d.split_k;
+    if (split_k <= 0) {
+      const int tiles = ((d.M + GEMM_BM - 1) / GEMM_BM) * ((d.N + bn - 1) / bn);
+      const int kblocks = (d.K + GEMM_BK - 1) / GEMM_BK;
+      split_k = (gemm_num_sms() + tiles - 1) / tiles;
+      int max_split = kblocks / 4;
+      if (max_split < 1) max_split = 1;
+      if (split_k > max_split) split_k = max_split;
+      if (split_k < 1) split_k = 1;
+    }
+  }
+  return wide ? dispatch_layout<256>(d, split_k, d_status, stream)
+              : dispatch_layout<128>(d, split_k, d_status, stream);
+}
+
+// ------------------------------------------------------------------------------------------
+// fp32 SIMT GEMM (parity mode).  64x64x16 tiles, 256 threads, 4x4 micro-tiles.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M, int N,
+                int K, int lda, int ldb, int ldc, int a_mn, int b_mn, int out, float alpha,
+                const float* __restrict__ res1, const float* __restrict__ s1, const float* __restrict__ res2,
+                const float* __restrict__ s2, int ldres) {
+  __shared__ float As[16][65];
+  __shared__ float Bs[16][65];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int idx = threadIdx.x; idx < 64 * 16; idx += 256) {
+      int kk, mm;
+      if (a_mn) { mm = idx & 63; kk = idx >> 6; } else { kk = idx & 15; mm = idx >> 4; }
+      const int gm = m0 + mm, gk = k0 + kk;
+      float v = 0.f;
+      if (gm < M && gk < K) v = a_mn ? A[(size_t)gk * lda + gm] : A[(size_t)gm * lda + gk];
+      As[kk][mm] = v;
+      int nn;
+      if (b_mn) { nn = idx & 63; kk = idx >> 6; } else { kk = idx & 15; nn = idx >> 4; }
+      const int gn = n0 + nn;
+      const int gk2 = k0 + kk;
+      v = 0.f;
+      if (gn < N && gk2 < K) v = b_mn ? B[(size_t)gk2 * ldb + gn] : B[(size_t)gn * ldb + gk2];
+      Bs[kk][nn] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  float a1 = 0.f, a2 = 0.f;
+  if (res1) a1 = s1 ? *s1 : 1.f;
+  if (res2) a2 = s2 ? *s2 : 1.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      float v = alpha * acc[i][j];
+      if (out == GEMM_OUT_ACCUM) {
+        C[(size_t)m * ldc + n] += v;
+      } else {
+        if (res1) v += a1 * res1[(size_t)m * ldres + n];
+        if (res2) v += a2 * res2[(size_t)m * ldres + n];
+        C[(size_t)m * ldc + n] = v;
+      }
+    }
+  }
+}
+
+int gemm_f32(const GemmDesc& d, cudaStream_t stream) {
+  if (d.M <= 0 || d.N <= 0 || d.K <= 0) return 0;
+  if (d.out == GEMM_OUT_BF16) {
+    g_gemm_err = "fp32 GEMM cannot write bf16";
+    return -2;
+  }
+  dim3 grid((d.N + 63) / 64, (d.M + 63) / 64);
+  gemm_f32_kernel<<<grid, 256, 0, stream>>>(
+      reinterpret_cast<const float*>(d.A), reinterpret_cast<const float*>(d.B), reinterpret_cast<float*>(d.C),
+      d.M, d.N, d.K, d.lda, d.ldb, d.ldc, d.a_mn ? 1 : 0, d.b_mn ? 1 : 0, d.out, d.alpha, d.res1, d.s1, d.res2,
+      d.s2, d.ldres);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    g_gemm_err = std::string("gemm_f32 launch: ") + cudaGetErrorString(e);
+    return -4;
+  }
+  return 0;
+}
+
+}  // namespace ane

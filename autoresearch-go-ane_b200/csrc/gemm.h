@@ -1,0 +1,48 @@
+// Host-side GEMM dispatch used by the engine.
+//
+// One descriptor covers every dense contraction of the training step:
+//   C[M,N] (op)= alpha * A*B (+ s1*res1 + s2*res2)
+// with A stored [M,K] (a_mn=false) or [K,M] (a_mn=true) and B stored [N,K]
+// (b_mn=false) or [K,N] (b_mn=true).  Shapes follow the reference's call sites:
+// linearCF (ane/common.go:91), linearBackwardDXCF (ane/train_full.go:242),
+// accumLinearGradCF (ane/train_full.go:213) and the three classifier GEMMs
+// (ane/stories/cpu.go:303-385).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ane {
+
+enum GemmOut : int {
+  GEMM_OUT_BF16 = 0,    // store bf16 (bf16 path only)
+  GEMM_OUT_F32 = 1,     // store fp32, optional residual blend
+  GEMM_OUT_ACCUM = 2,   // C += alpha*A*B in fp32 (beta = 1)
+};
+
+struct GemmDesc {
+  const void* A = nullptr;
+  const void* B = nullptr;
+  void* C = nullptr;
+  int M = 0, N = 0, K = 0;
+  int lda = 0, ldb = 0, ldc = 0;
+  bool a_mn = false, b_mn = false;
+  int out = GEMM_OUT_F32;
+  float alpha = 1.f;
+  const float* res1 = nullptr;
+  const float* s1 = nullptr;  // device scalar, nullptr => 1
+  const float* res2 = nullptr;
+  const float* s2 = nullptr;
+  int ldres = 0;
+  int split_k = 0;  // 0 => choose
+};
+
+// bf16 operands, tcgen05 tensor cores.  Returns 0 or a negative error code.
+int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream);
+// fp32 operands, SIMT FMA (the fp32 parity mode).
+int gemm_f32(const GemmDesc& d, cudaStream_t stream);
+
+int gemm_num_sms();
+const char* gemm_last_error();
+
+}  // namespace ane

@@ -1,0 +1,147 @@
+// C-ABI entry points for device buffers and single kernels ("ops").
+//
+// These are the seams the parity tests and per-kernel roofline measurements call
+// through: every argument is a plain pointer or integer, pointers named d_* are
+// device pointers obtained from ane_dev_malloc. All ops run on the legacy default
+// stream of the current device.
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+
+#include "../../include/ane_b200.h"
+#include "common.cuh"
+#include "gemm.h"
+#include "kernels.h"
+
+using namespace ane;
+
+static thread_local std::string g_ops_err;
+static int* g_ops_status = nullptr;  // device status word shared by the op entry points
+
+static int set_err(int code, const std::string& msg) {
+  g_ops_err = msg;
+  return code;
+}
+static int cuda_fail(cudaError_t e, const char* what) {
+  return set_err(ANE_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+#define CK(call)                                    \
+  do {                                              \
+    cudaError_t _e = (call);                        \
+    if (_e != cudaSuccess) return cuda_fail(_e, #call); \
+  } while (0)
+
+static int ensure_status() {
+  if (g_ops_status) return 0;
+  CK(cudaMalloc(&g_ops_status, sizeof(int)));
+  CK(cudaMemset(g_ops_status, 0, sizeof(int)));
+  return 0;
+}
+
+extern "C" {
+
+const char* ane_ops_last_error(void) { return g_ops_err.c_str(); }
+
+int32_t ane_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) return 0;
+  return n;
+}
+
+int32_t ane_dev_set(int32_t device) {
+  CK(cudaSetDevice(device));
+  return 0;
+}
+
+void* ane_dev_malloc(uint64_t bytes) {
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes ? bytes : 1);
+  if (e != cudaSuccess) {
+    cuda_fail(e, "cudaMalloc");
+    return nullptr;
+  }
+  return p;
+}
+int32_t ane_dev_free(void* d_ptr) {
+  CK(cudaFree(d_ptr));
+  return 0;
+}
+int32_t ane_dev_h2d(void* d_dst, const void* h_src, uint64_t bytes) {
+  CK(cudaMemcpy(d_dst, h_src, bytes, cudaMemcpyHostToDevice));
+  return 0;
+}
+int32_t ane_dev_d2h(void* h_dst, const void* d_src, uint64_t bytes) {
+  CK(cudaMemcpy(h_dst, d_src, bytes, cudaMemcpyDeviceToHost));
+  return 0;
+}
+int32_t ane_dev_memset(void* d_ptr, int32_t value, uint64_t bytes) {
+  CK(cudaMemset(d_ptr, value, bytes));
+  return 0;
+}
+int32_t ane_dev_sync(void) {
+  CK(cudaDeviceSynchronize());
+  return 0;
+}
+
+// Reads and clears the device status word the op kernels report into
+// (0 = ok; 101..103 = a bounded pipeline wait gave up).
+int32_t ane_ops_device_status(int32_t* out_status) {
+  if (ensure_status()) return ANE_ERR_CUDA;
+  int v = 0;
+  CK(cudaMemcpy(&v, g_ops_status, sizeof(int), cudaMemcpyDeviceToHost));
+  CK(cudaMemset(g_ops_status, 0, sizeof(int)));
+  if (out_status) *out_status = v;
+  return 0;
+}
+
+// Times `fn`-style regions: begin/end record CUDA events on the default stream.
+static cudaEvent_t g_ev0 = nullptr, g_ev1 = nullptr;
+int32_t ane_timer_begin(void) {
+  if (!g_ev0) {
+    CK(cudaEventCreate(&g_ev0));
+    CK(cudaEventCreate(&g_ev1));
+  }
+  CK(cudaEventRecord(g_ev0, 0));
+  return 0;
+}
+int32_t ane_timer_end(float* out_ms) {
+  if (!g_ev0) return set_err(ANE_ERR_ARG, "ane_timer_end without ane_timer_begin");
+  CK(cudaEventRecord(g_ev1, 0));
+  CK(cudaEventSynchronize(g_ev1));
+  float ms = 0.f;
+  CK(cudaEventElapsedTime(&ms, g_ev0, g_ev1));
+  if (out_ms) *out_ms = ms;
+  return 0;
+}
+
+int32_t ane_op_cast_f32_to_bf16(const float* d_src, void* d_dst, uint64_t n) {
+  cast_f32_to_bf16(d_src, reinterpret_cast<bf16*>(d_dst), n, 0);
+  CK(cudaGetLastError());
+  return 0;
+}
+int32_t ane_op_cast_bf16_to_f32(const void* d_src, float* d_dst, uint64_t n) {
+  cast_bf16_to_f32(reinterpret_cast<const bf16*>(d_src), d_dst, n, 0);
+  CK(cudaGetLastError());
+  return 0;
+}
+
+int32_t ane_op_gemm(const ane_gemm_args* a) {
+  if (!a || a->struct_size != sizeof(ane_gemm_args)) return set_err(ANE_ERR_ARG, "ane_op_gemm: bad struct_size");
+  if (ensure_status()) return ANE_ERR_CUDA;
+  GemmDesc d;
+  d.A = a->d_a; d.B = a->d_b; d.C = a->d_c;
+  d.M = a->m; d.N = a->n; d.K = a->k;
+  d.lda = a->lda; d.ldb = a->ldb; d.ldc = a->ldc;
+  d.a_mn = a->a_mn != 0; d.b_mn = a->b_mn != 0;
+  d.out = a->out_mode;
+  d.alpha = a->alpha;
+  d.res1 = a->d_res1; d.s1 = a->d_s1; d.res2 = a->d_res2; d.s2 = a->d_s2;
+  d.ldres = a->ldres;
+  d.split_k = a->split_k;
+  int rc = (a->dtype == ANE_DTYPE_F32) ? gemm_f32(d, 0) : gemm_bf16(d, g_ops_status, 0);
+  if (rc != 0) return set_err(ANE_ERR_KERNEL, gemm_last_error());
+  return 0;
+}
+
+}  // extern "C"
