@@ -128,6 +128,10 @@ int32_t ane_op_cast_bf16_to_f32(const void* d_src, float* d_dst, uint64_t n) {
 
 int32_t ane_op_gemm(const ane_gemm_args* a) {
   if (!a || a->struct_size != sizeof(ane_gemm_args)) return set_err(ANE_ERR_ARG, "ane_op_gemm: bad struct_size");
+  if (!a->d_a || !a->d_b || !a->d_c) return set_err(ANE_ERR_ARG, "ane_op_gemm: null operand pointer");
+  if (a->m < 0 || a->n < 0 || a->k < 0 || a->lda <= 0 || a->ldb <= 0 || a->ldc <= 0)
+    return set_err(ANE_ERR_ARG, "ane_op_gemm: bad dimensions");
+  if ((a->d_res1 || a->d_res2) && a->ldres <= 0) return set_err(ANE_ERR_ARG, "ane_op_gemm: ldres missing");
   if (ensure_status()) return ANE_ERR_CUDA;
   GemmDesc d;
   d.A = a->d_a; d.B = a->d_b; d.C = a->d_c;
