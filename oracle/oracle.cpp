@@ -270,7 +270,9 @@ void qknorm_one(float* q, int heads, int head_dim, int seq) {
 }
 
 // ane/common.go:229-270 qkNormBackwardCF (one tensor at a time).
-void qknorm_bwd_one(float* dq, const float* q_pre, int heads, int head_dim, int seq) {
+// The reference scales the projection term by qkScale^2 (:247,:263); the exact gradient of
+// y = qkScale*x*rrms has a single qkScale there.  reference_coeff selects which.
+void qknorm_bwd_one(float* dq, const float* q_pre, int heads, int head_dim, int seq, bool reference_coeff) {
   const double qk_scale = 1.2;
   const double inv_hd = 1.0 / (double)head_dim;
   PAR_ALL
@@ -286,7 +288,8 @@ void qknorm_bwd_one(float* dq, const float* q_pre, int heads, int head_dim, int 
       double dot = 0.0;
       for (int i = 0; i < head_dim; ++i)
         dot += (double)dq[(size_t)(base + i) * seq + t] * (double)q_pre[(size_t)(base + i) * seq + t];
-      double coeff = dot * rrms * rrms * rrms * inv_hd * qk_scale * qk_scale;
+      double coeff = dot * rrms * rrms * rrms * inv_hd * qk_scale;
+      if (reference_coeff) coeff = dot * rrms * rrms * rrms * inv_hd * qk_scale * qk_scale;
       for (int i = 0; i < head_dim; ++i) {
         size_t idx = (size_t)(base + i) * seq + t;
         dq[idx] = (float)((double)dq[idx] * rrms * qk_scale - coeff * (double)q_pre[idx]);
@@ -873,8 +876,8 @@ void backward_accumulate(orc_model& m, const uint16_t* input) {
     attention_bwd_cf(m.grad_q.data(), m.grad_k.data(), m.grad_v.data(), m.grad_att.data(), cache.q.data(),
                      cache.k.data(), cache.v.data(), c.heads, c.kv_heads, m.hd, seq, att_bwd_scale);
     if (m.is_n) {
-      qknorm_bwd_one(m.grad_q.data(), cache.q_pre.data(), c.heads, m.hd, seq);
-      qknorm_bwd_one(m.grad_k.data(), cache.k_pre.data(), c.kv_heads, m.hd, seq);
+      qknorm_bwd_one(m.grad_q.data(), cache.q_pre.data(), c.heads, m.hd, seq, m.quirks);
+      qknorm_bwd_one(m.grad_k.data(), cache.k_pre.data(), c.kv_heads, m.hd, seq, m.quirks);
     }
     if (!(m.is_n && m.quirks)) {  // exact backward of the rotation; absent from the reference
       rope_cf(m.grad_q.data(), c.heads, m.hd, seq, m.rope_cos.data(), m.rope_sin.data(), true);
