@@ -1,4 +1,5 @@
-// Element-wise kernels: dtype casts.
+// Element-wise kernels: dtype casts, RoPE + QK-norm, FFN activations, and the small
+// reference-architecture ops (smear, value embeddings, lambda reductions).
 #include "common.cuh"
 #include "kernels.h"
 
@@ -29,6 +30,489 @@ void cast_f32_to_bf16(const float* src, bf16* dst, uint64_t n, cudaStream_t s) {
 void cast_bf16_to_f32(const bf16* src, float* dst, uint64_t n, cudaStream_t s) {
   if (!n) return;
   cast_bf16_to_f32_kernel<<<grid_for(n, 256), 256, 0, s>>>(src, dst, n);
+}
+
+
+// ------------------------------------------------------------------------------------------
+// RoPE tables (ane/train_util.go:183-202): cos/sin of pos / theta^(2i/hd), computed in double.
+// ------------------------------------------------------------------------------------------
+__global__ void rope_table_kernel(float* cosb, float* sinb, int seq, int half, int hd, double theta) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= seq * half) return;
+  const int pos = idx / half, i = idx - pos * half;
+  const double freq = (double)pos / pow(theta, (double)(2 * i) / (double)hd);
+  cosb[idx] = (float)cos(freq);
+  sinb[idx] = (float)sin(freq);
+}
+void build_rope_tables(float* cosb, float* sinb, int seq, int hd, double theta, cudaStream_t s) {
+  const int half = hd / 2, n = seq * half;
+  if (n <= 0) return;
+  rope_table_kernel<<<(n + 255) / 256, 256, 0, s>>>(cosb, sinb, seq, half, hd, theta);
+}
+
+// ------------------------------------------------------------------------------------------
+// RoPE (+ QK-norm) forward / backward: one warp per (token, head) over the q and k heads of a
+// packed [M, (H+2KV)*hd] buffer.  Pairs (2i, 2i+1) rotate together (ane/train_util.go:204-224).
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_qknorm_forward_kernel(T* __restrict__ qkv, T* __restrict__ qk_pre,
+                                           const float* __restrict__ cosb, const float* __restrict__ sinb, int M,
+                                           int seq, int H, int KV, int hd, int qk_norm) {
+  const int heads = H + KV;
+  const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)M * heads) return;
+  const int m = (int)(wid / heads), head = (int)(wid - (long long)m * heads);
+  const int t = m % seq;
+  const int half = hd >> 1;
+  const int ld = (H + 2 * KV) * hd;
+  T* p = qkv + (size_t)m * ld + (size_t)head * hd;  // q heads then k heads are contiguous
+  float ss = 0.f;
+  float e_[2], o_[2];  // up to hd = 128
+  int cnt = 0;
+  for (int i = lane; i < half; i += 32, ++cnt) {
+    const float c = cosb[t * half + i], s = sinb[t * half + i];
+    const float e = to_f<T>(p[2 * i]), o = to_f<T>(p[2 * i + 1]);
+    const float e2 = e * c - o * s, o2 = o * c + e * s;
+    e_[cnt] = e2;
+    o_[cnt] = o2;
+    ss += e2 * e2 + o2 * o2;
+  }
+  if (qk_norm) {
+    ss = warp_sum(ss);
+    const float scale = 1.2f / sqrtf(ss / (float)hd + 1e-5f);
+    T* pre = qk_pre ? qk_pre + (size_t)m * (heads * hd) + (size_t)head * hd : nullptr;
+    cnt = 0;
+    for (int i = lane; i < half; i += 32, ++cnt) {
+      if (pre) {
+        pre[2 * i] = from_f<T>(e_[cnt]);
+        pre[2 * i + 1] = from_f<T>(o_[cnt]);
+      }
+      // Normalise the value that was saved (rounded to T), as the reference normalises its saved copy.
+      const float e2 = pre ? to_f<T>(pre[2 * i]) : e_[cnt];
+      const float o2 = pre ? to_f<T>(pre[2 * i + 1]) : o_[cnt];
+      p[2 * i] = from_f<T>(e2 * scale);
+      p[2 * i + 1] = from_f<T>(o2 * scale);
+    }
+  } else {
+    cnt = 0;
+    for (int i = lane; i < half; i += 32, ++cnt) {
+      p[2 * i] = from_f<T>(e_[cnt]);
+      p[2 * i + 1] = from_f<T>(o_[cnt]);
+    }
+  }
+}
+
+template <typename T>
+void rope_qknorm_forward(T* qkv, T* qk_pre, const float* cosb, const float* sinb, int M, int seq, int H, int KV,
+                         int hd, bool qk_norm, cudaStream_t s) {
+  const long long warps = (long long)M * (H + KV);
+  if (warps <= 0) return;
+  const int wpb = 8;
+  rope_qknorm_forward_kernel<T><<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, s>>>(qkv, qk_pre, cosb, sinb, M,
+                                                                                          seq, H, KV, hd, qk_norm);
+}
+template void rope_qknorm_forward<float>(float*, float*, const float*, const float*, int, int, int, int, int, bool,
+                                         cudaStream_t);
+template void rope_qknorm_forward<bf16>(bf16*, bf16*, const float*, const float*, int, int, int, int, int, bool,
+                                        cudaStream_t);
+
+template <typename T>
+__global__ void rope_qknorm_backward_kernel(T* __restrict__ dqkv, const T* __restrict__ qk_pre,
+                                            const float* __restrict__ cosb, const float* __restrict__ sinb, int M,
+                                            int seq, int H, int KV, int hd, int qk_norm, int reference_coeff,
+                                            int skip_rope) {
+  const int heads = H + KV;
+  const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)M * heads) return;
+  const int m = (int)(wid / heads), head = (int)(wid - (long long)m * heads);
+  const int t = m % seq;
+  const int half = hd >> 1;
+  const int ld = (H + 2 * KV) * hd;
+  T* p = dqkv + (size_t)m * ld + (size_t)head * hd;
+  float ge[2], go[2];
+  int cnt = 0;
+  for (int i = lane; i < half; i += 32, ++cnt) {
+    ge[cnt] = to_f<T>(p[2 * i]);
+    go[cnt] = to_f<T>(p[2 * i + 1]);
+  }
+  if (qk_norm) {
+    const T* pre = qk_pre + (size_t)m * (heads * hd) + (size_t)head * hd;
+    float xe[2], xo[2];
+    float ss = 0.f, dot = 0.f;
+    cnt = 0;
+    for (int i = lane; i < half; i += 32, ++cnt) {
+      xe[cnt] = to_f<T>(pre[2 * i]);
+      xo[cnt] = to_f<T>(pre[2 * i + 1]);
+      ss += xe[cnt] * xe[cnt] + xo[cnt] * xo[cnt];
+      dot += ge[cnt] * xe[cnt] + go[cnt] * xo[cnt];
+    }
+    ss = warp_sum(ss);
+    dot = warp_sum(dot);
+    const float qs = 1.2f;
+    const float r = 1.0f / sqrtf(ss / (float)hd + 1e-5f);
+    float coeff = dot * r * r * r / (float)hd * qs;
+    if (reference_coeff) coeff *= qs;
+    cnt = 0;
+    for (int i = lane; i < half; i += 32, ++cnt) {
+      ge[cnt] = ge[cnt] * r * qs - coeff * xe[cnt];
+      go[cnt] = go[cnt] * r * qs - coeff * xo[cnt];
+    }
+  }
+  cnt = 0;
+  for (int i = lane; i < half; i += 32, ++cnt) {
+    float e = ge[cnt], o = go[cnt];
+    if (!skip_rope) {
+      const float c = cosb[t * half + i], s = sinb[t * half + i];
+      const float e2 = e * c + o * s, o2 = o * c - e * s;
+      e = e2;
+      o = o2;
+    }
+    p[2 * i] = from_f<T>(e);
+    p[2 * i + 1] = from_f<T>(o);
+  }
+}
+
+template <typename T>
+void rope_qknorm_backward(T* dqkv, const T* qk_pre, const float* cosb, const float* sinb, int M, int seq, int H,
+                          int KV, int hd, bool qk_norm, bool reference_coeff, bool skip_rope, cudaStream_t s) {
+  const long long warps = (long long)M * (H + KV);
+  if (warps <= 0) return;
+  const int wpb = 8;
+  rope_qknorm_backward_kernel<T><<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, s>>>(
+      dqkv, qk_pre, cosb, sinb, M, seq, H, KV, hd, qk_norm, reference_coeff, skip_rope);
+}
+template void rope_qknorm_backward<float>(float*, const float*, const float*, const float*, int, int, int, int, int,
+                                          bool, bool, bool, cudaStream_t);
+template void rope_qknorm_backward<bf16>(bf16*, const bf16*, const float*, const float*, int, int, int, int, int, bool,
+                                         bool, bool, cudaStream_t);
+
+// ------------------------------------------------------------------------------------------
+// FFN activations
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void relu2_forward_kernel(const T* __restrict__ h1, T* __restrict__ gate, uint64_t n) {
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    const float h = to_f<T>(h1[i]);
+    gate[i] = from_f<T>(h <= 0.f ? 0.f : h * h);
+  }
+}
+template <typename T>
+__global__ void relu2_backward_kernel(const T* __restrict__ dgate, const T* __restrict__ h1, T* __restrict__ dh1,
+                                      uint64_t n) {
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    float r = to_f<T>(h1[i]);
+    if (r < 0.f) r = 0.f;
+    dh1[i] = from_f<T>(to_f<T>(dgate[i]) * 2.f * r);
+  }
+}
+template <typename T>
+__global__ void swiglu_forward_kernel(const T* __restrict__ h13, T* __restrict__ gate, int M, int Hd) {
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t n = (uint64_t)M * Hd, stride = (uint64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    const uint64_t m = i / Hd, j = i - m * Hd;
+    const float h1 = to_f<T>(h13[m * 2 * Hd + j]), h3 = to_f<T>(h13[m * 2 * Hd + Hd + j]);
+    const float sg = 1.f / (1.f + expf(-h1));
+    gate[i] = from_f<T>(h1 * sg * h3);
+  }
+}
+template <typename T>
+__global__ void swiglu_backward_kernel(const T* __restrict__ dgate, const T* __restrict__ h13, T* __restrict__ dh13,
+                                       int M, int Hd) {
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t n = (uint64_t)M * Hd, stride = (uint64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    const uint64_t m = i / Hd, j = i - m * Hd;
+    const float h1 = to_f<T>(h13[m * 2 * Hd + j]), h3 = to_f<T>(h13[m * 2 * Hd + Hd + j]);
+    const float dg = to_f<T>(dgate[i]);
+    const float sg = 1.f / (1.f + expf(-h1));
+    const float silu = h1 * sg;
+    const float dsilu = sg * (1.f + h1 * (1.f - sg));
+    dh13[m * 2 * Hd + j] = from_f<T>(dg * h3 * dsilu);
+    dh13[m * 2 * Hd + Hd + j] = from_f<T>(dg * silu);
+  }
+}
+
+template <typename T>
+void relu2_forward(const T* h1, T* gate, uint64_t n, cudaStream_t s) {
+  if (!n) return;
+  relu2_forward_kernel<T><<<grid_for(n, 256), 256, 0, s>>>(h1, gate, n);
+}
+template <typename T>
+void relu2_backward(const T* dgate, const T* h1, T* dh1, uint64_t n, cudaStream_t s) {
+  if (!n) return;
+  relu2_backward_kernel<T><<<grid_for(n, 256), 256, 0, s>>>(dgate, h1, dh1, n);
+}
+template <typename T>
+void swiglu_forward(const T* h13, T* gate, int M, int Hd, cudaStream_t s) {
+  const uint64_t n = (uint64_t)M * Hd;
+  if (!n) return;
+  swiglu_forward_kernel<T><<<grid_for(n, 256), 256, 0, s>>>(h13, gate, M, Hd);
+}
+template <typename T>
+void swiglu_backward(const T* dgate, const T* h13, T* dh13, int M, int Hd, cudaStream_t s) {
+  const uint64_t n = (uint64_t)M * Hd;
+  if (!n) return;
+  swiglu_backward_kernel<T><<<grid_for(n, 256), 256, 0, s>>>(dgate, h13, dh13, M, Hd);
+}
+template void relu2_forward<float>(const float*, float*, uint64_t, cudaStream_t);
+template void relu2_forward<bf16>(const bf16*, bf16*, uint64_t, cudaStream_t);
+template void relu2_backward<float>(const float*, const float*, float*, uint64_t, cudaStream_t);
+template void relu2_backward<bf16>(const bf16*, const bf16*, bf16*, uint64_t, cudaStream_t);
+template void swiglu_forward<float>(const float*, float*, int, int, cudaStream_t);
+template void swiglu_forward<bf16>(const bf16*, bf16*, int, int, cudaStream_t);
+template void swiglu_backward<float>(const float*, const float*, float*, int, int, cudaStream_t);
+template void swiglu_backward<bf16>(const bf16*, const bf16*, bf16*, int, int, cudaStream_t);
+
+// ------------------------------------------------------------------------------------------
+// Smear (ane/common.go:324-382), element-wise parts.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+__global__ void smear_forward_kernel(const float* __restrict__ x_pre, const float* __restrict__ gate_pre,
+                                     const float* __restrict__ lambda, float* __restrict__ x, int M, int seq, int D) {
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t n = (uint64_t)M * D, stride = (uint64_t)gridDim.x * blockDim.x;
+  const float lam = *lambda;
+  for (; i < n; i += stride) {
+    const int m = (int)(i / D);
+    const int t = m % seq;
+    const float shifted = t == 0 ? 0.f : x_pre[i - D];
+    x[i] = x_pre[i] + lam * sigmoidf_(gate_pre[i]) * shifted;
+  }
+}
+void smear_forward(const float* x_pre, const float* gate_pre, const float* lambda, float* x, int M, int seq, int D,
+                   cudaStream_t s) {
+  const uint64_t n = (uint64_t)M * D;
+  if (!n) return;
+  smear_forward_kernel<<<grid_for(n, 256), 256, 0, s>>>(x_pre, gate_pre, lambda, x, M, seq, D);
+}
+
+__global__ void smear_backward_kernel(const float* __restrict__ d_out, const float* __restrict__ x_pre,
+                                      const float* __restrict__ gate_pre, const float* __restrict__ lambda,
+                                      float* __restrict__ d_gate_pre, float* __restrict__ dx,
+                                      float* __restrict__ g_lambda, int M, int seq, int D) {
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t n = (uint64_t)M * D, stride = (uint64_t)gridDim.x * blockDim.x;
+  const float lam = *lambda;
+  double local = 0.0;
+  for (; i < n; i += stride) {
+    const int m = (int)(i / D);
+    const int t = m % seq;
+    const float g = sigmoidf_(gate_pre[i]);
+    const float sh = t == 0 ? 0.f : x_pre[i - D];
+    const float dy = d_out[i];
+    local += (double)(dy * g * sh);
+    d_gate_pre[i] = dy * lam * sh * g * (1.f - g);
+    float v = dy;
+    if (t + 1 < seq) v += d_out[i + D] * lam * sigmoidf_(gate_pre[i + D]);
+    dx[i] = v;
+  }
+  local = warp_sum_d(local);
+  __shared__ double s_part[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) s_part[warp] = local;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double tot = 0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += s_part[w];
+    atomicAdd(g_lambda, (float)tot);
+  }
+}
+void smear_backward(const float* d_out, const float* x_pre, const float* gate_pre, const float* lambda,
+                    float* d_gate_pre, float* dx, float* g_lambda, int M, int seq, int D, cudaStream_t s) {
+  const uint64_t n = (uint64_t)M * D;
+  if (!n) return;
+  smear_backward_kernel<<<grid_for(n, 256), 256, 0, s>>>(d_out, x_pre, gate_pre, lambda, d_gate_pre, dx, g_lambda, M,
+                                                         seq, D);
+}
+
+// ------------------------------------------------------------------------------------------
+// Small reductions / vector ops
+// ------------------------------------------------------------------------------------------
+__global__ void dot_accumulate_kernel(const float* __restrict__ a, const float* __restrict__ b, uint64_t n,
+                                      float alpha, float* __restrict__ out) {
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  double local = 0.0;
+  for (; i < n; i += stride) local += (double)(a[i] * b[i]);
+  local = warp_sum_d(local);
+  __shared__ double s_part[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) s_part[warp] = local;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double tot = 0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += s_part[w];
+    atomicAdd(out, alpha * (float)tot);
+  }
+}
+void dot_accumulate(const float* a, const float* b, uint64_t n, float alpha, float* out, cudaStream_t s) {
+  if (!n) return;
+  int grid = grid_for(n, 256);
+  if (grid > 296) grid = 296;
+  dot_accumulate_kernel<<<grid, 256, 0, s>>>(a, b, n, alpha, out);
+}
+
+__global__ void axpy_dev_kernel(float* __restrict__ y, const float* __restrict__ x, const float* __restrict__ alpha,
+                                float sign, uint64_t n, int assign) {
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  const float a = sign * (alpha ? *alpha : 1.f);
+  for (; i < n; i += stride) y[i] = assign ? a * x[i] : y[i] + a * x[i];
+}
+void axpy_dev(float* y, const float* x, const float* alpha, float sign, uint64_t n, bool assign, cudaStream_t s) {
+  if (!n) return;
+  axpy_dev_kernel<<<grid_for(n, 256), 256, 0, s>>>(y, x, alpha, sign, n, assign ? 1 : 0);
+}
+void add_inplace(float* y, const float* x, uint64_t n, cudaStream_t s) { axpy_dev(y, x, nullptr, 1.f, n, false, s); }
+
+// ------------------------------------------------------------------------------------------
+// Value embeddings (ane/train_full.go:1035-1086): one warp per (token, head).
+// ------------------------------------------------------------------------------------------
+static constexpr int kVEGateChannels = 12;  // ane/stories/weights.go:28
+
+template <typename T>
+__global__ void ve_forward_kernel(T* __restrict__ qkv, const float* __restrict__ x, const uint16_t* __restrict__ tok,
+                                  const float* __restrict__ ve_embed, const float* __restrict__ ve_gate,
+                                  float* __restrict__ gate_act, int M, int D, int H, int KV, int hd, int vocab) {
+  const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)M * H) return;
+  const int m = (int)(wid / H), h = (int)(wid - (long long)m * H);
+  float gp = 0.f;
+  for (int c = 0; c < kVEGateChannels; ++c) gp += ve_gate[h * kVEGateChannels + c] * x[(size_t)m * D + c];
+  const float act = 1.0f / (1.0f + expf(-gp));
+  if (lane == 0) gate_act[(size_t)m * H + h] = act;
+  const float gate = 3.0f * act;
+  const int t = tok[m];
+  if (t >= vocab) return;
+  const int ld = (H + 2 * KV) * hd;
+  T* v = qkv + (size_t)m * ld + (size_t)(H + KV) * hd + (size_t)h * hd;
+  const float* ve = ve_embed + (size_t)t * D + (size_t)h * hd;
+  for (int d = lane; d < hd; d += 32) v[d] = from_f<T>(to_f<T>(v[d]) + gate * ve[d]);
+}
+template <typename T>
+void ve_forward(T* qkv, const float* x, const uint16_t* tok, const float* ve_embed, const float* ve_gate,
+                float* gate_act, int M, int D, int H, int KV, int hd, int vocab, cudaStream_t s) {
+  const long long warps = (long long)M * H;
+  if (warps <= 0) return;
+  ve_forward_kernel<T><<<(unsigned)((warps + 7) / 8), 256, 0, s>>>(qkv, x, tok, ve_embed, ve_gate, gate_act, M, D, H,
+                                                                    KV, hd, vocab);
+}
+template void ve_forward<float>(float*, const float*, const uint16_t*, const float*, const float*, float*, int, int,
+                                int, int, int, int, cudaStream_t);
+template void ve_forward<bf16>(bf16*, const float*, const uint16_t*, const float*, const float*, float*, int, int, int,
+                               int, int, int, cudaStream_t);
+
+template <typename T>
+__global__ void ve_backward_kernel(const T* __restrict__ dqkv, const float* __restrict__ x,
+                                   const uint16_t* __restrict__ tok, const float* __restrict__ ve_embed,
+                                   const float* __restrict__ ve_gate, const float* __restrict__ gate_act,
+                                   float* __restrict__ g_ve_embed, float* __restrict__ g_ve_gate,
+                                   float* __restrict__ d_prev, int M, int D, int H, int KV, int hd, int vocab) {
+  const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)M * H) return;
+  const int m = (int)(wid / H), h = (int)(wid - (long long)m * H);
+  const int t = tok[m];
+  if (t >= vocab) return;
+  const float act = gate_act[(size_t)m * H + h];
+  const float gate = 3.0f * act;
+  const int ld = (H + 2 * KV) * hd;
+  const T* dv = dqkv + (size_t)m * ld + (size_t)(H + KV) * hd + (size_t)h * hd;
+  const float* ve = ve_embed + (size_t)t * D + (size_t)h * hd;
+  float* gve = g_ve_embed + (size_t)t * D + (size_t)h * hd;
+  float d_gate = 0.f;
+  for (int d = lane; d < hd; d += 32) {
+    const float g = to_f<T>(dv[d]);
+    atomicAdd(gve + d, g * gate);
+    d_gate += g * ve[d];
+  }
+  d_gate = warp_sum(d_gate);
+  const float d_gate_pre = d_gate * 3.0f * act * (1.f - act);
+  if (lane < kVEGateChannels) {
+    atomicAdd(g_ve_gate + h * kVEGateChannels + lane, d_gate_pre * x[(size_t)m * D + lane]);
+    atomicAdd(d_prev + (size_t)m * D + lane, d_gate_pre * ve_gate[h * kVEGateChannels + lane]);
+  }
+}
+template <typename T>
+void ve_backward(const T* dqkv, const float* x, const uint16_t* tok, const float* ve_embed, const float* ve_gate,
+                 const float* gate_act, float* g_ve_embed, float* g_ve_gate, float* d_prev, int M, int D, int H,
+                 int KV, int hd, int vocab, cudaStream_t s) {
+  const long long warps = (long long)M * H;
+  if (warps <= 0) return;
+  ve_backward_kernel<T><<<(unsigned)((warps + 7) / 8), 256, 0, s>>>(dqkv, x, tok, ve_embed, ve_gate, gate_act,
+                                                                     g_ve_embed, g_ve_gate, d_prev, M, D, H, KV, hd,
+                                                                     vocab);
+}
+template void ve_backward<float>(const float*, const float*, const uint16_t*, const float*, const float*,
+                                 const float*, float*, float*, float*, int, int, int, int, int, int, cudaStream_t);
+template void ve_backward<bf16>(const bf16*, const float*, const uint16_t*, const float*, const float*, const float*,
+                                float*, float*, float*, int, int, int, int, int, int, cudaStream_t);
+
+// ------------------------------------------------------------------------------------------
+// Transpose and argmax
+// ------------------------------------------------------------------------------------------
+__global__ void transpose_f32_kernel(const float* __restrict__ in, float* __restrict__ out, int rows, int cols) {
+  __shared__ float tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int r = r0 + j, c = c0 + threadIdx.x;
+    if (r < rows && c < cols) tile[j][threadIdx.x] = in[(size_t)r * cols + c];
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int c = c0 + j, r = r0 + threadIdx.x;
+    if (r < rows && c < cols) out[(size_t)c * rows + r] = tile[threadIdx.x][j];
+  }
+}
+void transpose_f32(const float* in, float* out, int rows, int cols, cudaStream_t s) {
+  if (rows <= 0 || cols <= 0) return;
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
+  transpose_f32_kernel<<<grid, block, 0, s>>>(in, out, rows, cols);
+}
+
+__global__ void argmax_rows_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int rows, int V) {
+  const int row = blockIdx.x;
+  if (row >= rows) return;
+  const float* p = logits + (size_t)row * V;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = p[i];
+    if (v > best || (v == best && i < best_i)) {
+      best = v;
+      best_i = i;
+    }
+  }
+  __shared__ float s_v[256];
+  __shared__ int s_i[256];
+  s_v[threadIdx.x] = best;
+  s_i[threadIdx.x] = best_i;
+  __syncthreads();
+  for (int o = blockDim.x >> 1; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o) {
+      const float v = s_v[threadIdx.x + o];
+      const int i = s_i[threadIdx.x + o];
+      if (v > s_v[threadIdx.x] || (v == s_v[threadIdx.x] && i < s_i[threadIdx.x])) {
+        s_v[threadIdx.x] = v;
+        s_i[threadIdx.x] = i;
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) out[row] = s_i[0] == 0x7fffffff ? 0 : s_i[0];
+}
+void argmax_rows(const float* logits, int32_t* out, int rows, int V, cudaStream_t s) {
+  if (rows <= 0) return;
+  argmax_rows_kernel<<<rows, 256, 0, s>>>(logits, out, rows, V);
 }
 
 }  // namespace ane

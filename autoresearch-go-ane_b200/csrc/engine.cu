@@ -1,0 +1,1218 @@
+// Training-step engine: device-resident model state plus the orchestration of one
+// Step / EvalLogits / EvalLoss, mirroring ane.Engine (ane/engine.go) over CUDA kernels.
+//
+// Data layout in HBM
+//   parameters   one flat fp32 buffer P (master), with same-shaped G (accumulated gradients),
+//                Adam m and v; a bf16 shadow of the GEMM operands (matrices + embedding) that the
+//                optimizer kernel rewrites, so no separate weight-refresh pass exists
+//                (the reference restages weights after every update, ane/runtime.go:25-94).
+//   activations  token-major [M = batch*seq, C]; residual stream fp32, GEMM operands in T
+//                (bf16 on the tensor-core path, float in fp32 parity mode).
+//   per layer    Wqkv [(H+2KV)*hd, D] (Wq|Wk|Wv rows), Wo [D, H*hd], W13 [Hd or 2Hd, D] (W1|W3), W2 [D, Hd].
+#include "engine.h"
+
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <chrono>
+
+#include "common.cuh"
+#include "dp.h"
+#include "gemm.h"
+#include "kernels.h"
+
+namespace ane {
+
+namespace {
+
+inline int64_t now_ns() {
+  return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch())
+      .count();
+}
+
+// drand48 of the reference sampler (ane/engine.go:873-880).
+constexpr uint64_t kDrandMul = 0x5DEECE66Dull, kDrandAdd = 0xBull, kDrandMask = (1ull << 48) - 1;
+
+template <typename T>
+struct Act {  // saved activations of one layer (ane/train_full.go:12-37)
+  float* x2 = nullptr;
+  T* xn = nullptr;
+  T* qkv = nullptr;
+  T* qkpre = nullptr;
+  T* att = nullptr;
+  T* x2n = nullptr;
+  T* h13 = nullptr;
+  T* gate = nullptr;
+  float* rstd1 = nullptr;
+  float* rstd2 = nullptr;
+  float* lse = nullptr;
+  float* ve_act = nullptr;
+  // debug gradient taps (fp32), only with debug_taps
+  float* t_dout = nullptr;
+  float* t_dx2 = nullptr;
+  float* t_dqkv = nullptr;
+  float* t_dh13 = nullptr;
+};
+
+__global__ void gather_windows_kernel(const uint16_t* __restrict__ tokens, const uint64_t* __restrict__ pos,
+                                      uint16_t* __restrict__ in, uint16_t* __restrict__ tgt, int B, int seq) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= B * seq) return;
+  const int b = i / seq, t = i - b * seq;
+  const uint64_t p = pos[b] + (uint64_t)t;
+  in[i] = tokens[p];
+  tgt[i] = tokens[p + 1];
+}
+
+// out[(b*ncols + c)*seq + t] = src[(b*seq+t)*ld + col0 + c]   (token-major -> the reference's [C][seq])
+template <typename TS>
+__global__ void export_tap_kernel(const TS* __restrict__ src, int ld, int col0, int ncols, int M, int seq,
+                                  float* __restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)M * ncols) return;
+  const int m = (int)(i / ncols), c = (int)(i - (long long)m * ncols);
+  const int b = m / seq, t = m - b * seq;
+  out[((size_t)b * ncols + c) * seq + t] = to_f<TS>(src[(size_t)m * ld + col0 + c]);
+}
+
+// next-token targets inside each window for the evaluation loss: tgt[b,t] = tok[b,t+1], last = invalid.
+__global__ void shift_targets_kernel(const uint16_t* __restrict__ tok, uint16_t* __restrict__ tgt, int B, int seq) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= B * seq) return;
+  const int t = i % seq;
+  tgt[i] = (t + 1 < seq) ? tok[i + 1] : (uint16_t)0xFFFF;
+}
+
+template <typename TS>
+__global__ void to_f32_kernel(const TS* __restrict__ src, float* __restrict__ dst, uint64_t n) {
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) dst[i] = to_f<TS>(src[i]);
+}
+template <typename TD>
+__global__ void from_f32_kernel(const float* __restrict__ src, TD* __restrict__ dst, uint64_t n) {
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) dst[i] = from_f<TD>(src[i]);
+}
+inline unsigned ew_grid(uint64_t n) {
+  uint64_t g = (n + 255) / 256;
+  if (g > 148ull * 16) g = 148ull * 16;
+  return (unsigned)(g < 1 ? 1 : g);
+}
+
+struct Slot {
+  size_t off = 0, n = 0;
+};
+
+template <typename T>
+class EngineT final : public EngineBase {
+ public:
+  ~EngineT() override { destroy(); }
+
+  int open(const ane_options& o, const uint16_t* tokens, uint64_t n_tokens, const uint8_t* dp_id) override;
+  int step(const uint16_t* input, const uint16_t* target, uint32_t n_seq, ane_step_result* out) override;
+  int flush(double* refresh_ms) override;
+  int eval_logits(const uint16_t* tokens, uint32_t n_seq, float* out, uint64_t cap, uint32_t layout) override;
+  int eval_loss(const uint16_t* tokens, uint32_t n_seq, double* loss_sum, uint64_t* n_pos) override;
+  int set_lr(float lr) override;
+  float get_lr() override { return lr_; }
+  int get_state(ane_state* s) override;
+  int set_state(const ane_state* s) override;
+  int64_t tensor_size(uint32_t id, uint32_t layer) override;
+  int import_tensor(uint32_t id, uint32_t layer, uint32_t which, const float* buf, uint64_t n) override;
+  int export_tensor(uint32_t id, uint32_t layer, uint32_t which, float* buf, uint64_t n) override;
+  int64_t get_tap(uint32_t tap, uint32_t layer, float* buf, uint64_t cap) override;
+
+ private:
+  static constexpr bool kIsF32 = sizeof(T) == 4;
+
+  int fail(int code, const std::string& msg) {
+    err_ = msg;
+    return code;
+  }
+  int cuda_check(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return 0;
+    return fail(ANE_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+  }
+  template <typename U>
+  int dalloc(U** p, size_t count) {
+    void* q = nullptr;
+    cudaError_t e = cudaMalloc(&q, std::max<size_t>(count, 1) * sizeof(U));
+    if (e != cudaSuccess) return cuda_check(e, "cudaMalloc");
+    allocs_.push_back(q);
+    *p = reinterpret_cast<U*>(q);
+    return 0;
+  }
+  void destroy();
+  bool is_ve_layer(int i) const { return isN_ && (i % 2 == (L_ - 1) % 2); }  // ane/stories/weights.go:22
+  const T* wop(size_t off) const {
+    if constexpr (kIsF32) return P_ + off;
+    else return Sh_ + off;
+  }
+  int gemm(const GemmDesc& d) {
+    int rc;
+    if constexpr (kIsF32) rc = gemm_f32(d, stream_);
+    else rc = gemm_bf16(d, d_status_, stream_);
+    if (rc != 0) return fail(ANE_ERR_KERNEL, gemm_last_error());
+    return 0;
+  }
+  // T-typed view of an fp32 buffer: in fp32 mode the buffer itself, else a separately written copy.
+  T* tview(float* f32buf, T* tbuf) const {
+    if constexpr (kIsF32) return f32buf;
+    else return tbuf;
+  }
+  T* tcopy_arg(T* tbuf) const {  // what to pass as "also write a T copy" output
+    if constexpr (kIsF32) return nullptr;
+    else return tbuf;
+  }
+  void cast_to_t(const float* src, T* dst, uint64_t n) {
+    if constexpr (!kIsF32) {
+      count_launch();
+      from_f32_kernel<T><<<ew_grid(n), 256, 0, stream_>>>(src, dst, n);
+    }
+  }
+  int layout_params();
+  int alloc_buffers();
+  int refresh_shadow();
+  int forward(const uint16_t* d_tok, int B, bool training);
+  int head_and_backward(int B);
+  int head_eval_loss(int B, double* loss_sum, uint64_t* n_pos);
+  int backward_layers(int B);
+  int do_flush();
+  int check_device_status(int* out_status);
+  Slot slot_of(uint32_t id, uint32_t layer, bool* ok) const;
+
+  // ---- configuration
+  ane_options o_{};
+  int D_ = 0, Hd_ = 0, L_ = 0, H_ = 0, KV_ = 0, hd_ = 0, V_ = 0, S_ = 0, B_ = 0, M_ = 0;
+  int QD_ = 0, KVD_ = 0, QKVD_ = 0, N13_ = 0;
+  bool isN_ = false, quirks_ = false;
+  float lr_ = 0, embed_lr_ = 0, scalar_lr_ = 0, lambda_lr_ = 0;
+  int ce_rows_ = 0;
+  // ---- parameters
+  std::vector<Slot> s_qkv_, s_wo_, s_w13_, s_w2_, s_ve_embed_, s_ve_gate_, s_rms_att_, s_rms_ffn_;
+  Slot s_embed_, s_rms_final_, s_resid_, s_x0l_, s_smear_gate_, s_smear_l_, s_backout_l_;
+  size_t n_params_ = 0, shadow_n_ = 0;
+  size_t r_mat0_ = 0, r_mat1_ = 0, r_ve0_ = 0, r_ve1_ = 0, r_veg0_ = 0, r_veg1_ = 0, r_rms0_ = 0, r_rms1_ = 0,
+         r_lam0_ = 0, r_lam1_ = 0;
+  float *P_ = nullptr, *G_ = nullptr, *Mo_ = nullptr, *Vo_ = nullptr;
+  bf16* Sh_ = nullptr;
+  float* d_one_ = nullptr;   // device constant 1.0f
+  float* d_zero_ = nullptr;  // device constant 0.0f
+  // ---- activations / work buffers
+  std::vector<float*> xs_;
+  std::vector<Act<T>> acts_;
+  float *x0_ = nullptr, *xraw_ = nullptr, *gate_pre_ = nullptr, *gx0_ = nullptr, *gmid_ = nullptr, *dgp_ = nullptr,
+        *dxs_ = nullptr, *dxs2_ = nullptr;
+  T *x0_t_ = nullptr, *dgp_t_ = nullptr;
+  float *dcur_[2] = {nullptr, nullptr}, *dxn_ = nullptr, *dy_ = nullptr, *dx2_ = nullptr, *dqkv_f32_ = nullptr;
+  T *dcur_t_[2] = {nullptr, nullptr}, *dx2_t_ = nullptr, *dgate_ = nullptr, *dh13_ = nullptr, *datt_ = nullptr,
+    *dqkv_ = nullptr, *xnf_ = nullptr;
+  float *rstdf_ = nullptr, *logits_ = nullptr, *loss_rows_ = nullptr, *inv_valid_ = nullptr, *d_loss_ = nullptr;
+  T* dlogits_ = nullptr;
+  float *rope_cos_ = nullptr, *rope_sin_ = nullptr;
+  double* d_acc_ = nullptr;
+  float *d_scales_ = nullptr, *d_norm_ = nullptr;
+  int* d_status_ = nullptr;
+  float* tap_tmp_ = nullptr;
+  size_t tap_tmp_n_ = 0;
+  // ---- tokens / sampler
+  uint16_t *d_tokens_ = nullptr, *d_in_ = nullptr, *d_tgt_ = nullptr;
+  uint16_t *h_in_ = nullptr, *h_tgt_ = nullptr;  // pinned
+  uint64_t *d_pos_ = nullptr, *h_pos_ = nullptr;
+  float* h_loss_ = nullptr;  // pinned
+  uint64_t n_tokens_ = 0, rng_ = 0;
+  // ---- state
+  ane_state st_{};
+  uint32_t pending_seqs_ = 0, micro_steps_ = 0;
+  int64_t t_open_ns_ = 0;
+  int last_B_ = 0;
+  cudaStream_t stream_ = nullptr;
+  cudaEvent_t ev0_ = nullptr, ev1_ = nullptr, ev_adam0_ = nullptr, ev_adam1_ = nullptr;
+  DataParallel dp_;
+  std::vector<void*> allocs_;
+};
+
+template <typename T>
+void EngineT<T>::destroy() {
+  if (stream_) cudaStreamSynchronize(stream_);
+  dp_.shutdown();
+  for (void* p : allocs_) cudaFree(p);
+  allocs_.clear();
+  if (h_in_) cudaFreeHost(h_in_);
+  if (h_tgt_) cudaFreeHost(h_tgt_);
+  if (h_pos_) cudaFreeHost(h_pos_);
+  if (h_loss_) cudaFreeHost(h_loss_);
+  h_in_ = h_tgt_ = nullptr;
+  h_pos_ = nullptr;
+  h_loss_ = nullptr;
+  for (cudaEvent_t* e : {&ev0_, &ev1_, &ev_adam0_, &ev_adam1_})
+    if (*e) {
+      cudaEventDestroy(*e);
+      *e = nullptr;
+    }
+  if (stream_) {
+    cudaStreamDestroy(stream_);
+    stream_ = nullptr;
+  }
+}
+
+// Parameter layout: groups are contiguous so the optimizer needs one launch per group and the
+// gradient all-reduce sees one flat buffer.
+template <typename T>
+int EngineT<T>::layout_params() {
+  size_t off = 0;
+  auto take = [&](size_t n) {
+    Slot s;
+    s.off = off;
+    s.n = n;
+    off += (n + 127) / 128 * 128;
+    return s;
+  };
+  s_qkv_.resize(L_); s_wo_.resize(L_); s_w13_.resize(L_); s_w2_.resize(L_);
+  s_ve_embed_.assign(L_, Slot()); s_ve_gate_.assign(L_, Slot());
+  s_rms_att_.assign(L_, Slot()); s_rms_ffn_.assign(L_, Slot());
+  r_mat0_ = off;
+  for (int l = 0; l < L_; ++l) {
+    s_qkv_[l] = take((size_t)QKVD_ * D_);
+    s_wo_[l] = take((size_t)D_ * QD_);
+    s_w13_[l] = take((size_t)N13_ * D_);
+    s_w2_[l] = take((size_t)D_ * Hd_);
+  }
+  r_mat1_ = off;
+  if (isN_) s_smear_gate_ = take((size_t)D_ * D_);
+  s_embed_ = take((size_t)V_ * D_);
+  shadow_n_ = off;  // bf16 shadow covers matrices, smear gate and the embedding
+  r_ve0_ = off;
+  for (int l = 0; l < L_; ++l)
+    if (is_ve_layer(l)) s_ve_embed_[l] = take((size_t)V_ * D_);
+  r_ve1_ = off;
+  r_veg0_ = off;
+  for (int l = 0; l < L_; ++l)
+    if (is_ve_layer(l)) s_ve_gate_[l] = take((size_t)H_ * 12);
+  r_veg1_ = off;
+  r_rms0_ = off;
+  if (!isN_) {
+    for (int l = 0; l < L_; ++l) {
+      s_rms_att_[l] = take(D_);
+      s_rms_ffn_[l] = take(D_);
+    }
+    s_rms_final_ = take(D_);
+  }
+  r_rms1_ = off;
+  if (isN_) {
+    s_smear_l_ = take(1);
+    s_backout_l_ = take(1);
+    r_lam0_ = off;
+    s_resid_ = take(L_);
+    s_x0l_ = take(L_);
+    r_lam1_ = off;
+  }
+  n_params_ = off;
+  return 0;
+}
+
+template <typename T>
+Slot EngineT<T>::slot_of(uint32_t id, uint32_t layer, bool* ok) const {
+  *ok = true;
+  Slot s;
+  const bool per_layer = (id >= ANE_T_WQ && id <= ANE_T_RMS_FFN) || id == ANE_T_VE_EMBED || id == ANE_T_VE_GATE;
+  if (per_layer && layer >= (uint32_t)L_) {
+    *ok = false;
+    return s;
+  }
+  switch (id) {
+    case ANE_T_EMBED: return s_embed_;
+    case ANE_T_WQ: s.off = s_qkv_[layer].off; s.n = (size_t)QD_ * D_; return s;
+    case ANE_T_WK: s.off = s_qkv_[layer].off + (size_t)QD_ * D_; s.n = (size_t)KVD_ * D_; return s;
+    case ANE_T_WV: s.off = s_qkv_[layer].off + (size_t)(QD_ + KVD_) * D_; s.n = (size_t)KVD_ * D_; return s;
+    case ANE_T_WO: return s_wo_[layer];
+    case ANE_T_W1: s.off = s_w13_[layer].off; s.n = (size_t)Hd_ * D_; return s;
+    case ANE_T_W3:
+      if (isN_) return s;
+      s.off = s_w13_[layer].off + (size_t)Hd_ * D_; s.n = (size_t)Hd_ * D_; return s;
+    case ANE_T_W2: return s_w2_[layer];
+    case ANE_T_RMS_ATT: return s_rms_att_[layer];
+    case ANE_T_RMS_FFN: return s_rms_ffn_[layer];
+    case ANE_T_RMS_FINAL: return s_rms_final_;
+    case ANE_T_VE_EMBED: return s_ve_embed_[layer];
+    case ANE_T_VE_GATE: return s_ve_gate_[layer];
+    case ANE_T_RESID_LAMBDAS: return s_resid_;
+    case ANE_T_X0_LAMBDAS: return s_x0l_;
+    case ANE_T_SMEAR_GATE: return s_smear_gate_;
+    case ANE_T_SMEAR_LAMBDA: return s_smear_l_;
+    case ANE_T_BACKOUT_LAMBDA: return s_backout_l_;
+    default: *ok = false; return s;
+  }
+}
+
+template <typename T>
+int EngineT<T>::alloc_buffers() {
+  const size_t MD = (size_t)M_ * D_;
+  int rc = 0;
+#define A(ptr, n)                        \
+  do {                                   \
+    if ((rc = dalloc(&(ptr), (n))) != 0) return rc; \
+  } while (0)
+  A(P_, n_params_); A(G_, n_params_); A(Mo_, n_params_); A(Vo_, n_params_);
+  if (!kIsF32) A(Sh_, shadow_n_);
+  A(d_one_, 1); A(d_zero_, 1);
+  xs_.assign(L_ + 1, nullptr);
+  for (int l = 0; l <= L_; ++l) A(xs_[l], MD);
+  acts_.assign(L_, Act<T>());
+  for (int l = 0; l < L_; ++l) {
+    Act<T>& a = acts_[l];
+    A(a.x2, MD); A(a.xn, MD); A(a.qkv, (size_t)M_ * QKVD_); A(a.att, (size_t)M_ * QD_); A(a.x2n, MD);
+    A(a.h13, (size_t)M_ * N13_); A(a.gate, (size_t)M_ * Hd_);
+    A(a.rstd1, M_); A(a.rstd2, M_); A(a.lse, (size_t)B_ * H_ * S_);
+    if (isN_) A(a.qkpre, (size_t)M_ * (QD_ + KVD_));
+    if (is_ve_layer(l)) A(a.ve_act, (size_t)M_ * H_);
+    if (o_.debug_taps) {
+      A(a.t_dout, MD); A(a.t_dx2, MD); A(a.t_dqkv, (size_t)M_ * QKVD_); A(a.t_dh13, (size_t)M_ * N13_);
+    }
+  }
+  if (isN_) {
+    A(x0_, MD); A(xraw_, MD); A(gate_pre_, MD); A(gx0_, MD); A(gmid_, MD); A(dgp_, MD); A(dxs_, MD); A(dxs2_, MD);
+    if (!kIsF32) { A(x0_t_, MD); A(dgp_t_, MD); }
+  }
+  A(dcur_[0], MD); A(dcur_[1], MD); A(dxn_, MD); A(dy_, MD); A(dx2_, MD);
+  A(dqkv_f32_, (size_t)M_ * QKVD_);
+  if (!kIsF32) {
+    A(dcur_t_[0], MD); A(dcur_t_[1], MD); A(dx2_t_, MD); A(dqkv_, (size_t)M_ * QKVD_);
+  }
+  A(dgate_, (size_t)M_ * Hd_); A(dh13_, (size_t)M_ * N13_); A(datt_, (size_t)M_ * QD_);
+  A(xnf_, MD); A(rstdf_, M_);
+  A(logits_, (size_t)ce_rows_ * V_); A(dlogits_, (size_t)ce_rows_ * V_);
+  A(loss_rows_, M_); A(inv_valid_, B_); A(d_loss_, 4);
+  A(rope_cos_, (size_t)S_ * (hd_ / 2)); A(rope_sin_, (size_t)S_ * (hd_ / 2));
+  A(d_acc_, 2); A(d_scales_, 4); A(d_norm_, 2); A(d_status_, 1);
+  A(d_in_, M_); A(d_tgt_, M_); A(d_pos_, B_);
+  tap_tmp_n_ = std::max((size_t)M_ * std::max({QKVD_, N13_, D_}), (size_t)V_ * S_);
+  A(tap_tmp_, tap_tmp_n_);
+#undef A
+  return 0;
+}
+
+template <typename T>
+int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n_tokens, const uint8_t* dp_id) {
+  o_ = opts;
+  // ---- defaults (ane/engine.go:188-239, ane/stories/config.go:3-18)
+  if (o_.dim <= 0) o_.dim = 768;
+  if (o_.hidden <= 0) o_.hidden = 2048;
+  if (o_.n_layers <= 0) o_.n_layers = 12;
+  if (o_.n_heads <= 0) o_.n_heads = 12;
+  if (o_.n_kv_heads <= 0) o_.n_kv_heads = o_.n_heads;
+  if (o_.vocab <= 0) o_.vocab = 32000;
+  if (o_.seq <= 0) o_.seq = 256;
+  if (o_.batch <= 0) o_.batch = 1;
+  if (o_.lr <= 0) o_.lr = 3e-4f;
+  if (o_.accum_steps <= 0) o_.accum_steps = 1;
+  if (o_.seed == 0) o_.seed = 42;
+  if (o_.adam_beta1 <= 0) o_.adam_beta1 = 0.9f;
+  if (o_.adam_beta2 <= 0) o_.adam_beta2 = 0.999f;
+  if (o_.adam_eps <= 0) o_.adam_eps = 1e-8f;
+  if (o_.grad_clip < 0) o_.grad_clip = 0;
+  if (o_.loss_scale < 0) o_.loss_scale = 0;
+  if (o_.loss_scale == 0) o_.loss_scale = 256;
+  if (o_.embed_lr_mult <= 0) o_.embed_lr_mult = 1.0f;
+  if (o_.scalar_lr_mult <= 0) o_.scalar_lr_mult = 1.0f;
+  if (o_.lambda_lr_mult <= 0) o_.lambda_lr_mult = 0.01f;
+  if (o_.lambda_beta1 <= 0) o_.lambda_beta1 = o_.adam_beta1;
+  if (o_.lambda_beta2 <= 0) o_.lambda_beta2 = o_.adam_beta2;
+  if (o_.world_size <= 0) o_.world_size = 1;
+  isN_ = o_.arch == ANE_ARCH_REFERENCE;
+  quirks_ = isN_ && o_.quirks != 0;
+  if (o_.rope_theta <= 0) o_.rope_theta = isN_ ? 100000.f : 10000.f;
+  D_ = o_.dim; Hd_ = o_.hidden; L_ = o_.n_layers; H_ = o_.n_heads; KV_ = o_.n_kv_heads; V_ = o_.vocab; S_ = o_.seq;
+  B_ = o_.batch;
+  if (D_ % H_ != 0) return fail(ANE_ERR_ARG, "storiesane open: dim must be a multiple of n_heads");
+  hd_ = D_ / H_;
+  if (H_ % KV_ != 0) return fail(ANE_ERR_ARG, "storiesane open: n_heads must be a multiple of n_kv_heads");
+  if (isN_ && KV_ != H_) return fail(ANE_ERR_ARG, "storiesane open: the reference architecture has no shared KV heads");
+  if ((hd_ & 1) || hd_ > 128) return fail(ANE_ERR_ARG, "storiesane open: head_dim must be even and <= 128");
+  if (D_ % 8 || Hd_ % 8 || (hd_ % 8)) return fail(ANE_ERR_ARG, "storiesane open: dim, hidden and head_dim must be multiples of 8");
+  if (V_ > 65535) return fail(ANE_ERR_ARG, "storiesane open: vocab must fit uint16 token ids");
+  if (V_ % 8) return fail(ANE_ERR_ARG, "storiesane open: vocab must be a multiple of 8");
+  if (isN_ && D_ < 12) return fail(ANE_ERR_ARG, "storiesane open: dim too small for the value-embedding gate");
+  if (n_tokens > 0 && n_tokens < (uint64_t)S_ + 1)
+    return fail(ANE_ERR_ARG, "storiesane open: not enough tokens for seq");  // ane/engine.go:192-194
+  M_ = B_ * S_;
+  QD_ = H_ * hd_; KVD_ = KV_ * hd_; QKVD_ = QD_ + 2 * KVD_;
+  N13_ = isN_ ? Hd_ : 2 * Hd_;
+  ce_rows_ = o_.ce_chunk_rows > 0 ? o_.ce_chunk_rows : 1024;
+  if (ce_rows_ > M_) ce_rows_ = M_;
+  ce_rows_ = std::max(ce_rows_, std::min(M_, S_));  // eval logits uses one sequence per chunk
+  lr_ = o_.lr;
+  set_lr(lr_);
+
+  int rc;
+  if ((rc = cuda_check(cudaSetDevice(o_.device), "cudaSetDevice")) != 0) return rc;
+  if ((rc = cuda_check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate")) != 0) return rc;
+  for (cudaEvent_t* e : {&ev0_, &ev1_, &ev_adam0_, &ev_adam1_})
+    if ((rc = cuda_check(cudaEventCreate(e), "cudaEventCreate")) != 0) return rc;
+  layout_params();
+  if ((rc = alloc_buffers()) != 0) return rc;
+  if ((rc = cuda_check(cudaMallocHost(&h_in_, sizeof(uint16_t) * M_), "cudaMallocHost")) != 0) return rc;
+  if ((rc = cuda_check(cudaMallocHost(&h_tgt_, sizeof(uint16_t) * M_), "cudaMallocHost")) != 0) return rc;
+  if ((rc = cuda_check(cudaMallocHost(&h_pos_, sizeof(uint64_t) * B_), "cudaMallocHost")) != 0) return rc;
+  if ((rc = cuda_check(cudaMallocHost(&h_loss_, sizeof(float) * 4), "cudaMallocHost")) != 0) return rc;
+  for (float* p : {P_, G_, Mo_, Vo_})
+    if ((rc = cuda_check(cudaMemsetAsync(p, 0, sizeof(float) * n_params_, stream_), "memset")) != 0) return rc;
+  cudaMemsetAsync(d_status_, 0, sizeof(int), stream_);
+  const float one = 1.f, zero = 0.f;
+  cudaMemcpyAsync(d_one_, &one, sizeof(float), cudaMemcpyHostToDevice, stream_);
+  cudaMemcpyAsync(d_zero_, &zero, sizeof(float), cudaMemcpyHostToDevice, stream_);
+  // defaults: residual lambdas and norm weights start at 1 (ane/stories/weights.go:155-162)
+  {
+    std::vector<float> ones((size_t)std::max(D_, L_), 1.0f);
+    if (isN_) cudaMemcpyAsync(P_ + s_resid_.off, ones.data(), sizeof(float) * L_, cudaMemcpyHostToDevice, stream_);
+    else {
+      for (int l = 0; l < L_; ++l) {
+        cudaMemcpyAsync(P_ + s_rms_att_[l].off, ones.data(), sizeof(float) * D_, cudaMemcpyHostToDevice, stream_);
+        cudaMemcpyAsync(P_ + s_rms_ffn_[l].off, ones.data(), sizeof(float) * D_, cudaMemcpyHostToDevice, stream_);
+      }
+      cudaMemcpyAsync(P_ + s_rms_final_.off, ones.data(), sizeof(float) * D_, cudaMemcpyHostToDevice, stream_);
+    }
+    cudaStreamSynchronize(stream_);
+  }
+  count_launch();
+  build_rope_tables(rope_cos_, rope_sin_, S_, hd_, (double)o_.rope_theta, stream_);
+  if ((rc = refresh_shadow()) != 0) return rc;
+  if (n_tokens > 0 && tokens) {
+    n_tokens_ = n_tokens;
+    if ((rc = dalloc(&d_tokens_, n_tokens)) != 0) return rc;
+    if ((rc = cuda_check(cudaMemcpyAsync(d_tokens_, tokens, sizeof(uint16_t) * n_tokens, cudaMemcpyHostToDevice, stream_),
+                         "token upload")) != 0)
+      return rc;
+  }
+  rng_ = (((uint64_t)o_.seed & 0xffffffffull) << 16) | 0x330Eull;  // ane/engine.go:873
+  if (o_.world_size > 1) {
+    if (!dp_id) return fail(ANE_ERR_ARG, "storiesane open: world_size > 1 needs a bootstrap id");
+    if ((rc = dp_.init(o_.rank, o_.world_size, dp_id, o_.device)) != 0) return fail(ANE_ERR_NCCL, dp_.last_error());
+  }
+  if ((rc = cuda_check(cudaStreamSynchronize(stream_), "open sync")) != 0) return rc;
+  t_open_ns_ = now_ns();
+  st_.struct_size = sizeof(ane_state);
+  return 0;
+}
+
+template <typename T>
+int EngineT<T>::refresh_shadow() {
+  if constexpr (!kIsF32) {
+    count_launch();
+    cast_f32_to_bf16(P_, Sh_, shadow_n_, stream_);
+  }
+  return 0;
+}
+
+template <typename T>
+int EngineT<T>::set_lr(float lr) {  // ane/engine.go:366-378
+  if (lr <= 0) return fail(ANE_ERR_ARG, "storiesane set lr: lr must be > 0");
+  lr_ = lr;
+  embed_lr_ = lr * o_.embed_lr_mult;
+  scalar_lr_ = lr * o_.scalar_lr_mult;
+  lambda_lr_ = lr * o_.scalar_lr_mult * o_.lambda_lr_mult;
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Forward (ane/train_full.go:383-453; eval path ane/engine.go:954-1038 performs the same arithmetic)
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+int EngineT<T>::forward(const uint16_t* d_tok, int B, bool training) {
+  (void)training;
+  const int M = B * S_;
+  int rc;
+  const float att_scale = (float)(1.0 / sqrt((double)hd_));
+  if (isN_) {
+    count_launch();
+    embed_forward(d_tok, P_ + s_embed_.off, x0_, xraw_, M, D_, V_, true, stream_);
+    cast_to_t(x0_, x0_t_, (uint64_t)M * D_);
+    GemmDesc g;
+    g.A = tview(x0_, x0_t_); g.B = wop(s_smear_gate_.off); g.C = gate_pre_;
+    g.M = M; g.N = D_; g.K = D_; g.lda = D_; g.ldb = D_; g.ldc = D_; g.out = GEMM_OUT_F32;
+    count_launch();
+    if ((rc = gemm(g)) != 0) return rc;
+    count_launch();
+    smear_forward(x0_, gate_pre_, P_ + s_smear_l_.off, xs_[0], M, S_, D_, stream_);
+  } else {
+    count_launch();
+    embed_forward(d_tok, P_ + s_embed_.off, xs_[0], nullptr, M, D_, V_, false, stream_);
+  }
+  for (int l = 0; l < L_; ++l) {
+    Act<T>& a = acts_[l];
+    const float* w_att = isN_ ? nullptr : P_ + s_rms_att_[l].off;
+    const float* w_ffn = isN_ ? nullptr : P_ + s_rms_ffn_[l].off;
+    const float* rl = isN_ ? P_ + s_resid_.off + l : d_one_;
+    const float* xl = isN_ ? P_ + s_x0l_.off + l : nullptr;
+    count_launch();
+    rmsnorm_forward<T>(xs_[l], w_att, a.xn, a.rstd1, M, D_, stream_);
+    {
+      GemmDesc g;
+      g.A = a.xn; g.B = wop(s_qkv_[l].off); g.C = a.qkv;
+      g.M = M; g.N = QKVD_; g.K = D_; g.lda = D_; g.ldb = D_; g.ldc = QKVD_;
+      g.out = kIsF32 ? GEMM_OUT_F32 : GEMM_OUT_BF16;
+      count_launch();
+      if ((rc = gemm(g)) != 0) return rc;
+    }
+    count_launch();
+    rope_qknorm_forward<T>(a.qkv, a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_, stream_);
+    if (is_ve_layer(l)) {
+      count_launch();
+      ve_forward<T>(a.qkv, xs_[l], d_tok, P_ + s_ve_embed_[l].off, P_ + s_ve_gate_[l].off, a.ve_act, M, D_, H_, KV_, hd_,
+                    V_, stream_);
+    }
+    count_launch();
+    attention_forward_simt<T>(a.qkv, a.att, a.lse, B, S_, H_, KV_, hd_, att_scale, stream_);
+    {
+      GemmDesc g;  // x2 = rl*x + Wo*att (+ xl*x0)   ane/train_full.go:414-426
+      g.A = a.att; g.B = wop(s_wo_[l].off); g.C = a.x2;
+      g.M = M; g.N = D_; g.K = QD_; g.lda = QD_; g.ldb = QD_; g.ldc = D_; g.out = GEMM_OUT_F32;
+      g.res1 = xs_[l]; g.s1 = rl; g.ldres = D_;
+      if (isN_) { g.res2 = x0_; g.s2 = xl; }
+      count_launch();
+      if ((rc = gemm(g)) != 0) return rc;
+    }
+    count_launch();
+    rmsnorm_forward<T>(a.x2, w_ffn, a.x2n, a.rstd2, M, D_, stream_);
+    {
+      GemmDesc g;
+      g.A = a.x2n; g.B = wop(s_w13_[l].off); g.C = a.h13;
+      g.M = M; g.N = N13_; g.K = D_; g.lda = D_; g.ldb = D_; g.ldc = N13_;
+      g.out = kIsF32 ? GEMM_OUT_F32 : GEMM_OUT_BF16;
+      count_launch();
+      if ((rc = gemm(g)) != 0) return rc;
+    }
+    count_launch();
+    if (isN_) relu2_forward<T>(a.h13, a.gate, (uint64_t)M * Hd_, stream_);
+    else swiglu_forward<T>(a.h13, a.gate, M, Hd_, stream_);
+    {
+      GemmDesc g;  // out = rl*x2 + W2*gate (+ xl*x0)   ane/train_full.go:434-445
+      g.A = a.gate; g.B = wop(s_w2_[l].off); g.C = xs_[l + 1];
+      g.M = M; g.N = D_; g.K = Hd_; g.lda = Hd_; g.ldb = Hd_; g.ldc = D_; g.out = GEMM_OUT_F32;
+      g.res1 = a.x2; g.s1 = rl; g.ldres = D_;
+      if (isN_) { g.res2 = x0_; g.s2 = xl; }
+      count_launch();
+      if ((rc = gemm(g)) != 0) return rc;
+    }
+  }
+  if (isN_) {  // backout: final -= lambda_b * x_mid   ane/common.go:385-389
+    count_launch();
+    axpy_dev(xs_[L_], xs_[L_ / 2], P_ + s_backout_l_.off, -1.f, (uint64_t)M * D_, false, stream_);
+  }
+  const float* w_final = isN_ ? nullptr : P_ + s_rms_final_.off;
+  count_launch();
+  rmsnorm_forward<T>(xs_[L_], w_final, xnf_, rstdf_, M, D_, stream_);
+  last_B_ = B;
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Final head (ane/train_full.go:480-558): classifier GEMM + softcap + cross-entropy in token chunks,
+// so only ce_rows x vocab logits exist at any time; then dy and the classifier weight gradient.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+int EngineT<T>::head_and_backward(int B) {
+  const int M = B * S_;
+  int rc;
+  count_launch();
+  count_valid_targets(d_tgt_, inv_valid_, B, S_, V_, stream_);
+  for (int r0 = 0; r0 < M; r0 += ce_rows_) {
+    const int rows = std::min(ce_rows_, M - r0);
+    GemmDesc g;
+    g.A = xnf_ + (size_t)r0 * D_; g.B = wop(s_embed_.off); g.C = logits_;
+    g.M = rows; g.N = V_; g.K = D_; g.lda = D_; g.ldb = D_; g.ldc = V_; g.out = GEMM_OUT_F32;
+    count_launch();
+    if ((rc = gemm(g)) != 0) return rc;
+    count_launch();
+    cross_entropy_rows<T>(logits_, d_tgt_, inv_valid_, dlogits_, loss_rows_, rows, r0, S_, V_, isN_, o_.loss_scale,
+                          stream_);
+    GemmDesc gx;  // dy = dlogits * Embed   (ane/stories/cpu.go:333-360)
+    gx.A = dlogits_; gx.B = wop(s_embed_.off); gx.C = dy_ + (size_t)r0 * D_;
+    gx.M = rows; gx.N = D_; gx.K = V_; gx.lda = V_; gx.ldb = D_; gx.ldc = D_; gx.b_mn = true; gx.out = GEMM_OUT_F32;
+    count_launch();
+    if ((rc = gemm(gx)) != 0) return rc;
+    GemmDesc gw;  // gEmbed += dlogits^T * xn   (ane/stories/cpu.go:366-385)
+    gw.A = dlogits_; gw.B = xnf_ + (size_t)r0 * D_; gw.C = G_ + s_embed_.off;
+    gw.M = V_; gw.N = D_; gw.K = rows; gw.lda = V_; gw.ldb = D_; gw.ldc = D_; gw.a_mn = true; gw.b_mn = true;
+    gw.out = GEMM_OUT_ACCUM;
+    count_launch();
+    if ((rc = gemm(gw)) != 0) return rc;
+  }
+  count_launch();
+  reduce_loss(loss_rows_, inv_valid_, d_loss_, B, S_, stream_);
+  const float* w_final = isN_ ? nullptr : P_ + s_rms_final_.off;
+  count_launch();
+  rmsnorm_backward<T>(dy_, xs_[L_], w_final, rstdf_, nullptr, nullptr, dcur_[0], tcopy_arg(dcur_t_[0]),
+                      isN_ ? nullptr : G_ + s_rms_final_.off, M, D_, stream_);
+  return backward_layers(B);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Layer backward (ane/train_full.go:691-820 with the CPU layer functions :592-601, :644-675).
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+int EngineT<T>::backward_layers(int B) {
+  const int M = B * S_;
+  const uint64_t MD = (uint64_t)M * D_;
+  int rc;
+  int cur = 0;
+  const float att_scale_bwd = quirks_ ? 1.0f : (float)(1.0 / sqrt((double)hd_));
+  if (isN_) {
+    // backout backward (ane/common.go:393-403): d lambda_b = -sum(dOut * xMid); stash -lambda_b * dOut
+    count_launch();
+    dot_accumulate(dcur_[cur], xs_[L_ / 2], MD, -1.f, G_ + s_backout_l_.off, stream_);
+    count_launch();
+    axpy_dev(gmid_, dcur_[cur], P_ + s_backout_l_.off, -1.f, MD, true, stream_);
+    cudaMemsetAsync(gx0_, 0, sizeof(float) * MD, stream_);
+  }
+  for (int l = L_ - 1; l >= 0; --l) {
+    Act<T>& a = acts_[l];
+    const float* w_att = isN_ ? nullptr : P_ + s_rms_att_[l].off;
+    const float* w_ffn = isN_ ? nullptr : P_ + s_rms_ffn_[l].off;
+    const float* rl = isN_ ? P_ + s_resid_.off + l : d_one_;
+    const float* xl = isN_ ? P_ + s_x0l_.off + l : nullptr;
+    float* dcur = dcur_[cur];
+    T* dcur_t = tview(dcur_[cur], dcur_t_[cur]);
+    float* dprev = dcur_[cur ^ 1];
+    T* dprev_t = tview(dcur_[cur ^ 1], dcur_t_[cur ^ 1]);
+    T* dx2_t = tview(dx2_, dx2_t_);
+    if (o_.debug_taps) cudaMemcpyAsync(a.t_dout, dcur, sizeof(float) * MD, cudaMemcpyDeviceToDevice, stream_);
+    // ---- FFN backward
+    {
+      GemmDesc g;  // dgate = dOut * W2
+      g.A = dcur_t; g.B = wop(s_w2_[l].off); g.C = dgate_;
+      g.M = M; g.N = Hd_; g.K = D_; g.lda = D_; g.ldb = Hd_; g.ldc = Hd_; g.b_mn = true;
+      g.out = kIsF32 ? GEMM_OUT_F32 : GEMM_OUT_BF16;
+      count_launch();
+      if ((rc = gemm(g)) != 0) return rc;
+    }
+    count_launch();
+    if (isN_) relu2_backward<T>(dgate_, a.h13, dh13_, (uint64_t)M * Hd_, stream_);
+    else swiglu_backward<T>(dgate_, a.h13, dh13_, M, Hd_, stream_);
+    if (o_.debug_taps) {
+      count_launch();
+      to_f32_kernel<T><<<ew_grid((uint64_t)M * N13_), 256, 0, stream_>>>(dh13_, a.t_dh13, (uint64_t)M * N13_);
+    }
+    {
+      GemmDesc g;  // dx2n = dh13 * W13
+      g.A = dh13_; g.B = wop(s_w13_[l].off); g.C = dxn_;
+      g.M = M; g.N = D_; g.K = N13_; g.lda = N13_; g.ldb = D_; g.ldc = D_; g.b_mn = true; g.out = GEMM_OUT_F32;
+      count_launch();
+      if ((rc = gemm(g)) != 0) return rc;
+    }
+    // dx2 = rl*dOut + rms_bwd(dx2n; x2)
+    count_launch();
+    rmsnorm_backward<T>(dxn_, a.x2, w_ffn, a.rstd2, dcur, rl, dx2_, tcopy_arg(dx2_t_),
+                        isN_ ? nullptr : G_ + s_rms_ffn_[l].off, M, D_, stream_);
+    if (o_.debug_taps) cudaMemcpyAsync(a.t_dx2, dx2_, sizeof(float) * MD, cudaMemcpyDeviceToDevice, stream_);
+    {
+      GemmDesc g;  // dW2 += dOut^T * gate
+      g.A = dcur_t; g.B = a.gate; g.C = G_ + s_w2_[l].off;
+      g.M = D_; g.N = Hd_; g.K = M; g.lda = D_; g.ldb = Hd_; g.ldc = Hd_; g.a_mn = true; g.b_mn = true;
+      g.out = GEMM_OUT_ACCUM;
+      count_launch();
+      if ((rc = gemm(g)) != 0) return rc;
+      GemmDesc g2;  // dW13 += dh13^T * x2n
+      g2.A = dh13_; g2.B = a.x2n; g2.C = G_ + s_w13_[l].off;
+      g2.M = N13_; g2.N = D_; g2.K = M; g2.lda = N13_; g2.ldb = D_; g2.ldc = D_; g2.a_mn = true; g2.b_mn = true;
+      g2.out = GEMM_OUT_ACCUM;
+      count_launch();
+      if ((rc = gemm(g2)) != 0) return rc;
+    }
+    if (isN_) {  // lambda gradients, FFN residual (ane/train_full.go:732-748)
+      count_launch(3);
+      dot_accumulate(dcur, a.x2, MD, 1.f, G_ + s_resid_.off + l, stream_);
+      dot_accumulate(dcur, x0_, MD, 1.f, G_ + s_x0l_.off + l, stream_);
+      axpy_dev(gx0_, dcur, xl, 1.f, MD, false, stream_);
+    }
+    // ---- attention backward
+    {
+      GemmDesc g;  // datt = dx2 * Wo
+      g.A = dx2_t; g.B = wop(s_wo_[l].off); g.C = datt_;
+      g.M = M; g.N = QD_; g.K = D_; g.lda = D_; g.ldb = QD_; g.ldc = QD_; g.b_mn = true;
+      g.out = kIsF32 ? GEMM_OUT_F32 : GEMM_OUT_BF16;
+      count_launch();
+      if ((rc = gemm(g)) != 0) return rc;
+    }
+    cudaMemsetAsync(dqkv_f32_, 0, sizeof(float) * (size_t)M * QKVD_, stream_);
+    count_launch();
+    attention_backward_simt<T>(a.qkv, datt_, dqkv_f32_, B, S_, H_, KV_, hd_, att_scale_bwd, stream_);
+    T* dqkv = tview(dqkv_f32_, dqkv_);
+    cast_to_t(dqkv_f32_, dqkv_, (uint64_t)M * QKVD_);
+    count_launch();
+    rope_qknorm_backward<T>(dqkv, a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_, quirks_, quirks_, stream_);
+    if (o_.debug_taps) {
+      count_launch();
+      to_f32_kernel<T><<<ew_grid((uint64_t)M * QKVD_), 256, 0, stream_>>>(dqkv, a.t_dqkv, (uint64_t)M * QKVD_);
+    }
+    {
+      GemmDesc g;  // dxn = dq*Wq + dk*Wk + dv*Wv   (ane/train_full.go:650-665)
+      g.A = dqkv; g.B = wop(s_qkv_[l].off); g.C = dxn_;
+      g.M = M; g.N = D_; g.K = QKVD_; g.lda = QKVD_; g.ldb = D_; g.ldc = D_; g.b_mn = true; g.out = GEMM_OUT_F32;
+      count_launch();
+      if ((rc = gemm(g)) != 0) return rc;
+    }
+    // dprev = rms_bwd(dxn; x) + rl*dx2  (+ value-embedding gate path, + mid-layer backout gradient)
+    const bool post_fix = is_ve_layer(l) || (isN_ && l == L_ / 2);
+    count_launch();
+    rmsnorm_backward<T>(dxn_, xs_[l], w_att, a.rstd1, dx2_, rl, dprev, post_fix ? nullptr : tcopy_arg(dcur_t_[cur ^ 1]),
+                        isN_ ? nullptr : G_ + s_rms_att_[l].off, M, D_, stream_);
+    if (is_ve_layer(l)) {
+      count_launch();
+      ve_backward<T>(dqkv, xs_[l], d_in_, P_ + s_ve_embed_[l].off, P_ + s_ve_gate_[l].off, a.ve_act,
+                     G_ + s_ve_embed_[l].off, G_ + s_ve_gate_[l].off, dprev, M, D_, H_, KV_, hd_, V_, stream_);
+    }
+    {
+      GemmDesc g;  // dWo += dx2^T * att
+      g.A = dx2_t; g.B = a.att; g.C = G_ + s_wo_[l].off;
+      g.M = D_; g.N = QD_; g.K = M; g.lda = D_; g.ldb = QD_; g.ldc = QD_; g.a_mn = true; g.b_mn = true;
+      g.out = GEMM_OUT_ACCUM;
+      count_launch();
+      if ((rc = gemm(g)) != 0) return rc;
+      GemmDesc g2;  // dWqkv += dqkv^T * xn
+      g2.A = dqkv; g2.B = a.xn; g2.C = G_ + s_qkv_[l].off;
+      g2.M = QKVD_; g2.N = D_; g2.K = M; g2.lda = QKVD_; g2.ldb = D_; g2.ldc = D_; g2.a_mn = true; g2.b_mn = true;
+      g2.out = GEMM_OUT_ACCUM;
+      count_launch();
+      if ((rc = gemm(g2)) != 0) return rc;
+    }
+    if (isN_) {  // lambda gradients, attention residual (ane/train_full.go:770-782)
+      count_launch(3);
+      dot_accumulate(dx2_, xs_[l], MD, 1.f, G_ + s_resid_.off + l, stream_);
+      dot_accumulate(dx2_, x0_, MD, 1.f, G_ + s_x0l_.off + l, stream_);
+      axpy_dev(gx0_, dx2_, xl, 1.f, MD, false, stream_);
+      if (l == L_ / 2) {  // gradient of the backout term joins at the output of layer L/2-1
+        count_launch();
+        add_inplace(dprev, gmid_, MD, stream_);
+      }
+    }
+    if (post_fix) cast_to_t(dprev, dcur_t_[cur ^ 1], MD);
+    (void)dprev_t;
+    cur ^= 1;
+  }
+  float* dcur = dcur_[cur];
+  if (isN_) {
+    if (quirks_) {  // reference order: x0 gradient joins before the smear backward (ane/train_full.go:789-798)
+      count_launch();
+      add_inplace(dcur, gx0_, MD, stream_);
+    }
+    count_launch();
+    smear_backward(dcur, x0_, gate_pre_, P_ + s_smear_l_.off, dgp_, dxs_, G_ + s_smear_l_.off, M, S_, D_, stream_);
+    cast_to_t(dgp_, dgp_t_, MD);
+    T* dgp_t = tview(dgp_, dgp_t_);
+    T* x0_t = tview(x0_, x0_t_);
+    GemmDesc g;  // gSmearGate += dGatePre^T * xPre   (ane/common.go:373)
+    g.A = dgp_t; g.B = x0_t; g.C = G_ + s_smear_gate_.off;
+    g.M = D_; g.N = D_; g.K = M; g.lda = D_; g.ldb = D_; g.ldc = D_; g.a_mn = true; g.b_mn = true; g.out = GEMM_OUT_ACCUM;
+    count_launch();
+    if ((rc = gemm(g)) != 0) return rc;
+    GemmDesc g2;  // dxPre += SmearGate^T * dGatePre   (ane/common.go:377-381)
+    g2.A = dgp_t; g2.B = wop(s_smear_gate_.off); g2.C = dxs2_;
+    g2.M = M; g2.N = D_; g2.K = D_; g2.lda = D_; g2.ldb = D_; g2.ldc = D_; g2.b_mn = true; g2.out = GEMM_OUT_F32;
+    g2.res1 = dxs_; g2.s1 = d_one_; g2.ldres = D_;
+    count_launch();
+    if ((rc = gemm(g2)) != 0) return rc;
+    if (!quirks_) {
+      count_launch();
+      add_inplace(dxs2_, gx0_, MD, stream_);
+    }
+    // embedding-norm backward (ane/train_full.go:800-802)
+    count_launch();
+    rmsnorm_backward<T>(dxs2_, xraw_, nullptr, nullptr, nullptr, nullptr, dxs_, nullptr, nullptr, M, D_, stream_);
+    dcur = dxs_;
+  }
+  count_launch();
+  embed_backward(d_in_, dcur, G_ + s_embed_.off, M, D_, V_, stream_);
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Optimizer update (ane/engine.go:646-682).
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+int EngineT<T>::do_flush() {
+  if (pending_seqs_ == 0) return 0;
+  int rc;
+  uint32_t global_pending = pending_seqs_ * (uint32_t)o_.world_size;
+  if (dp_.active()) {
+    if ((rc = dp_.all_reduce_sum(G_, n_params_, stream_)) != 0) return fail(ANE_ERR_NCCL, dp_.last_error());
+  }
+  cudaEventRecord(ev_adam0_, stream_);
+  float pre_scale = (float)(1.0 / (double)global_pending);
+  if (o_.loss_scale > 0) pre_scale /= o_.loss_scale;
+  cudaMemsetAsync(d_acc_, 0, sizeof(double) * 2, stream_);
+  if (o_.grad_clip > 0) {
+    // layer tensors + embedding (+ value embeddings and gates); the llama arch clips over every parameter.
+    count_launch(2);
+    sumsq_accumulate(G_ + r_mat0_, r_mat1_ - r_mat0_, pre_scale, d_acc_, stream_);
+    sumsq_accumulate(G_ + s_embed_.off, r_veg1_ - s_embed_.off, pre_scale, d_acc_, stream_);
+    if (!isN_) {
+      count_launch();
+      sumsq_accumulate(G_ + r_rms0_, r_rms1_ - r_rms0_, pre_scale, d_acc_, stream_);
+    }
+  }
+  count_launch();
+  finalize_clip(d_acc_, pre_scale, o_.grad_clip, d_scales_, d_norm_, stream_);
+  st_.adam_t++;
+  const int t = (int)st_.adam_t;
+  auto hyper = [&](float lr, float b1, float b2, float wd) {
+    AdamHyper h;
+    h.lr = lr; h.b1 = b1; h.b2 = b2; h.eps = o_.adam_eps; h.wd = wd;
+    const float bc1 = (float)(1.0 - pow((double)b1, (double)t));  // ane/train_full.go:1107-1111
+    const float bc2 = (float)(1.0 - pow((double)b2, (double)t));
+    h.inv_bc1 = 1 / bc1;
+    h.inv_bc2 = 1 / bc2;
+    return h;
+  };
+  const float b1 = o_.adam_beta1, b2 = o_.adam_beta2;
+  const float* clip_s = d_scales_ + 1;
+  const float* pre_s = d_scales_;
+  auto run = [&](size_t off, size_t n, AdamHyper h, const float* gs, bool shadow) {
+    if (!n) return;
+    count_launch();
+    adam_update(P_ + off, G_ + off, Mo_ + off, Vo_ + off, (shadow && !kIsF32) ? Sh_ + off : nullptr, n, h, gs, stream_);
+  };
+  run(r_mat0_, r_mat1_ - r_mat0_, hyper(lr_, b1, b2, o_.weight_decay), clip_s, true);
+  if (isN_) run(s_smear_gate_.off, s_embed_.off - s_smear_gate_.off, hyper(lr_, b1, b2, o_.weight_decay), pre_s, true);
+  run(s_embed_.off, r_ve0_ - s_embed_.off, hyper(embed_lr_, b1, b2, 0.f), clip_s, true);
+  run(r_ve0_, r_ve1_ - r_ve0_, hyper(embed_lr_, b1, b2, 0.f), clip_s, false);
+  run(r_veg0_, r_veg1_ - r_veg0_, hyper(scalar_lr_, b1, b2, 0.f), clip_s, false);
+  run(r_rms0_, r_rms1_ - r_rms0_, hyper(lr_, b1, b2, 0.f), clip_s, false);
+  if (isN_) {
+    run(s_smear_l_.off, r_lam0_ - s_smear_l_.off, hyper(scalar_lr_, b1, b2, 0.f), pre_s, false);
+    run(r_lam0_, r_lam1_ - r_lam0_, hyper(lambda_lr_, o_.lambda_beta1, o_.lambda_beta2, 0.f), pre_s, false);
+  }
+  cudaEventRecord(ev_adam1_, stream_);
+  pending_seqs_ = 0;
+  micro_steps_ = 0;
+  st_.pending_steps = 0;
+  st_.cum_batches++;
+  return 0;
+}
+
+template <typename T>
+int EngineT<T>::flush(double* refresh_ms) {
+  int rc = do_flush();
+  if (rc != 0) return rc;
+  if ((rc = cuda_check(cudaStreamSynchronize(stream_), "flush sync")) != 0) return rc;
+  if (refresh_ms) *refresh_ms = 0.0;
+  return 0;
+}
+
+template <typename T>
+int EngineT<T>::check_device_status(int* out_status) {
+  int v = 0;
+  cudaError_t e = cudaMemcpyAsync(&v, d_status_, sizeof(int), cudaMemcpyDeviceToHost, stream_);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream_);
+  if (e != cudaSuccess) return cuda_check(e, "device status read");
+  if (out_status) *out_status = v;
+  if (v != 0) {
+    cudaMemsetAsync(d_status_, 0, sizeof(int), stream_);
+    char buf[96];
+    snprintf(buf, sizeof buf, "storiesane step: device pipeline wait timed out (status %d)", v);
+    return fail(ANE_ERR_DEVICE, buf);
+  }
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Step (ane/engine.go:381-442)
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+int EngineT<T>::step(const uint16_t* input, const uint16_t* target, uint32_t n_seq, ane_step_result* out) {
+  const int64_t t0 = now_ns();
+  int rc;
+  if ((rc = cuda_check(cudaSetDevice(o_.device), "cudaSetDevice")) != 0) return rc;
+  cudaEventRecord(ev0_, stream_);
+  if (input) {
+    if ((int)n_seq != B_) return fail(ANE_ERR_ARG, "storiesane step: n_seq must equal the engine batch");
+    memcpy(h_in_, input, sizeof(uint16_t) * M_);
+    memcpy(h_tgt_, target, sizeof(uint16_t) * M_);
+    cudaMemcpyAsync(d_in_, h_in_, sizeof(uint16_t) * M_, cudaMemcpyHostToDevice, stream_);
+    cudaMemcpyAsync(d_tgt_, h_tgt_, sizeof(uint16_t) * M_, cudaMemcpyHostToDevice, stream_);
+  } else {
+    if (n_tokens_ < (uint64_t)S_ + 1) return fail(ANE_ERR_STATE, "storiesane step: not enough tokens");
+    // One global drand48 stream; rank r takes draws r, r+world, ... of each step (ane/engine.go:395-404).
+    const uint64_t limit = n_tokens_ - S_ - 1;
+    for (int i = 0; i < B_ * o_.world_size; ++i) {
+      rng_ = (kDrandMul * rng_ + kDrandAdd) & kDrandMask;
+      const double u = (double)rng_ / (double)(1ull << 48);
+      uint64_t pos = 0;
+      if (limit > 0) {
+        pos = (uint64_t)(u * (double)limit);
+        if (pos >= limit) pos = limit - 1;
+      }
+      if (i % o_.world_size == o_.rank) {
+        h_pos_[i / o_.world_size] = pos;
+        st_.token_pos = pos + (uint64_t)S_;
+      }
+    }
+    cudaMemcpyAsync(d_pos_, h_pos_, sizeof(uint64_t) * B_, cudaMemcpyHostToDevice, stream_);
+    count_launch();
+    gather_windows_kernel<<<(M_ + 255) / 256, 256, 0, stream_>>>(d_tokens_, d_pos_, d_in_, d_tgt_, B_, S_);
+  }
+  if ((rc = forward(d_in_, B_, true)) != 0) return rc;
+  if ((rc = head_and_backward(B_)) != 0) return rc;
+  cudaMemcpyAsync(h_loss_, d_loss_, sizeof(float), cudaMemcpyDeviceToHost, stream_);
+  pending_seqs_ += (uint32_t)B_;
+  micro_steps_++;
+  st_.pending_steps = micro_steps_;
+  bool flushed = false;
+  if ((int)micro_steps_ >= o_.accum_steps) {
+    if ((rc = do_flush()) != 0) return rc;
+    flushed = true;
+  }
+  cudaEventRecord(ev1_, stream_);
+  int dev_status = 0;
+  if ((rc = check_device_status(&dev_status)) != 0) {
+    if (out) out->device_status = dev_status;
+    return rc;
+  }
+  if ((rc = cuda_check(cudaGetLastError(), "step")) != 0) return rc;
+  float ms = 0.f, adam_ms = 0.f;
+  cudaEventElapsedTime(&ms, ev0_, ev1_);
+  if (flushed) cudaEventElapsedTime(&adam_ms, ev_adam0_, ev_adam1_);
+  const int64_t dur = now_ns() - t0;
+  st_.last_loss = h_loss_[0];
+  st_.cum_steps++;
+  st_.cum_train_ms += (double)dur / 1e6;
+  st_.cum_wall_ms = (double)(now_ns() - t_open_ns_) / 1e6;
+  if (out) {
+    const uint32_t sz = out->struct_size;
+    memset(out, 0, sizeof(*out));
+    out->struct_size = sz;
+    out->loss = h_loss_[0];
+    out->step_ns = dur;
+    out->device_eval_ns = (int64_t)((double)ms * 1e6);
+    out->cpu_work_ns = std::max<int64_t>(0, dur - out->device_eval_ns);
+    out->adam_ns = (int64_t)((double)adam_ms * 1e6);
+    out->flushed = flushed ? 1 : 0;
+    out->device_status = dev_status;
+  }
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// EvalLogits (ane/engine.go:449-462, :954-1038): one classifier GEMM per sequence straight into the
+// reference's [vocab][seq] order (C[v, t] = Embed[v,:] . xn[t,:]).
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+int EngineT<T>::eval_logits(const uint16_t* tokens, uint32_t n_seq, float* out, uint64_t cap, uint32_t layout) {
+  int rc;
+  if ((rc = cuda_check(cudaSetDevice(o_.device), "cudaSetDevice")) != 0) return rc;
+  const uint64_t per_seq = (uint64_t)V_ * S_;
+  if (cap < per_seq * n_seq) return fail(ANE_ERR_ARG, "storiesane eval logits: output buffer too small");
+  for (uint32_t s0 = 0; s0 < n_seq; s0 += (uint32_t)B_) {
+    const int nb = (int)std::min<uint32_t>((uint32_t)B_, n_seq - s0);
+    const int M = nb * S_;
+    memcpy(h_in_, tokens + (size_t)s0 * S_, sizeof(uint16_t) * M);
+    cudaMemcpyAsync(d_in_, h_in_, sizeof(uint16_t) * M, cudaMemcpyHostToDevice, stream_);
+    if ((rc = forward(d_in_, nb, false)) != 0) return rc;
+    for (int b = 0; b < nb; ++b) {
+      GemmDesc g;
+      if (layout == 0) {  // [V][seq]
+        g.A = wop(s_embed_.off); g.B = xnf_ + (size_t)b * S_ * D_; g.C = logits_;
+        g.M = V_; g.N = S_; g.K = D_; g.lda = D_; g.ldb = D_; g.ldc = S_;
+      } else {  // [seq][V]
+        g.A = xnf_ + (size_t)b * S_ * D_; g.B = wop(s_embed_.off); g.C = logits_;
+        g.M = S_; g.N = V_; g.K = D_; g.lda = D_; g.ldb = D_; g.ldc = V_;
+      }
+      g.out = GEMM_OUT_F32;
+      count_launch();
+      if ((rc = gemm(g)) != 0) return rc;
+      if (isN_) {
+        count_launch();
+        softcap_inplace(logits_, per_seq, stream_);
+      }
+      if ((rc = cuda_check(cudaMemcpyAsync(out + (size_t)(s0 + b) * per_seq, logits_, sizeof(float) * per_seq,
+                                           cudaMemcpyDeviceToHost, stream_),
+                           "logits download")) != 0)
+        return rc;
+    }
+  }
+  return check_device_status(nullptr);
+}
+
+// Fused evaluation loss: classifier chunk + cross-entropy on the device, only the scalar comes back.
+template <typename T>
+int EngineT<T>::eval_loss(const uint16_t* tokens, uint32_t n_seq, double* loss_sum, uint64_t* n_pos) {
+  int rc;
+  if ((rc = cuda_check(cudaSetDevice(o_.device), "cudaSetDevice")) != 0) return rc;
+  double total = 0.0;
+  uint64_t count = 0;
+  for (uint32_t s0 = 0; s0 < n_seq; s0 += (uint32_t)B_) {
+    const int nb = (int)std::min<uint32_t>((uint32_t)B_, n_seq - s0);
+    const int M = nb * S_;
+    memcpy(h_in_, tokens + (size_t)s0 * S_, sizeof(uint16_t) * M);
+    cudaMemcpyAsync(d_in_, h_in_, sizeof(uint16_t) * M, cudaMemcpyHostToDevice, stream_);
+    count_launch();
+    shift_targets_kernel<<<(M + 255) / 256, 256, 0, stream_>>>(d_in_, d_tgt_, nb, S_);
+    if ((rc = forward(d_in_, nb, false)) != 0) return rc;
+    cudaMemsetAsync(loss_rows_, 0, sizeof(float) * M, stream_);
+    for (int r0 = 0; r0 < M; r0 += ce_rows_) {
+      const int rows = std::min(ce_rows_, M - r0);
+      GemmDesc g;
+      g.A = xnf_ + (size_t)r0 * D_; g.B = wop(s_embed_.off); g.C = logits_;
+      g.M = rows; g.N = V_; g.K = D_; g.lda = D_; g.ldb = D_; g.ldc = V_; g.out = GEMM_OUT_F32;
+      count_launch();
+      if ((rc = gemm(g)) != 0) return rc;
+      count_launch();
+      cross_entropy_rows<T>(logits_, d_tgt_, d_one_ - 0, (T*)nullptr, loss_rows_, rows, r0, M + 1, V_, isN_, 0.f, stream_);
+    }
+    std::vector<float> rows_host(M);
+    std::vector<uint16_t> tg(M);
+    if ((rc = cuda_check(cudaMemcpyAsync(rows_host.data(), loss_rows_, sizeof(float) * M, cudaMemcpyDeviceToHost, stream_),
+                         "loss rows")) != 0)
+      return rc;
+    if ((rc = cuda_check(cudaStreamSynchronize(stream_), "eval loss sync")) != 0) return rc;
+    for (int i = 0; i < M; ++i) {
+      const int t = i % S_;
+      if (t + 1 >= S_) continue;
+      if (h_in_[i + 1] >= V_) continue;
+      total += (double)rows_host[i];
+      count++;
+    }
+  }
+  if (loss_sum) *loss_sum = total;
+  if (n_pos) *n_pos = count;
+  return check_device_status(nullptr);
+}
+
+template <typename T>
+int EngineT<T>::get_state(ane_state* s) {
+  if (!s) return fail(ANE_ERR_ARG, "storiesane state: null");
+  const uint32_t sz = s->struct_size;
+  *s = st_;
+  s->struct_size = sz ? sz : (uint32_t)sizeof(ane_state);
+  return 0;
+}
+template <typename T>
+int EngineT<T>::set_state(const ane_state* s) {  // ane/engine.go:506-512
+  if (!s) return fail(ANE_ERR_ARG, "storiesane load state: null");
+  st_ = *s;
+  micro_steps_ = s->pending_steps;
+  pending_seqs_ = s->pending_steps * (uint32_t)B_;
+  return 0;
+}
+
+template <typename T>
+int64_t EngineT<T>::tensor_size(uint32_t id, uint32_t layer) {
+  bool ok;
+  Slot s = slot_of(id, layer, &ok);
+  if (!ok) return -1;
+  return (int64_t)s.n;
+}
+
+template <typename T>
+int EngineT<T>::import_tensor(uint32_t id, uint32_t layer, uint32_t which, const float* buf, uint64_t n) {
+  bool ok;
+  Slot s = slot_of(id, layer, &ok);
+  if (!ok || which > 3) return fail(ANE_ERR_ARG, "storiesane import: unknown tensor");
+  if (s.n == 0) return fail(ANE_ERR_ARG, "storiesane import: tensor not present in this architecture");
+  if (n != s.n) return fail(ANE_ERR_ARG, "storiesane import: element count mismatch");
+  float* base = which == 0 ? P_ : which == 1 ? G_ : which == 2 ? Mo_ : Vo_;
+  int rc = cuda_check(cudaMemcpyAsync(base + s.off, buf, sizeof(float) * n, cudaMemcpyHostToDevice, stream_), "import");
+  if (rc) return rc;
+  if (which == 0 && !kIsF32 && s.off < shadow_n_) {
+    count_launch();
+    cast_f32_to_bf16(P_ + s.off, Sh_ + s.off, s.n, stream_);
+  }
+  return cuda_check(cudaStreamSynchronize(stream_), "import sync");
+}
+
+template <typename T>
+int EngineT<T>::export_tensor(uint32_t id, uint32_t layer, uint32_t which, float* buf, uint64_t n) {
+  bool ok;
+  Slot s = slot_of(id, layer, &ok);
+  if (!ok || which > 3) return fail(ANE_ERR_ARG, "storiesane export: unknown tensor");
+  if (n != s.n) return fail(ANE_ERR_ARG, "storiesane export: element count mismatch");
+  if (n == 0) return 0;
+  const float* base = which == 0 ? P_ : which == 1 ? G_ : which == 2 ? Mo_ : Vo_;
+  int rc = cuda_check(cudaMemcpyAsync(buf, base + s.off, sizeof(float) * n, cudaMemcpyDeviceToHost, stream_), "export");
+  if (rc) return rc;
+  return cuda_check(cudaStreamSynchronize(stream_), "export sync");
+}
+
+template <typename T>
+int64_t EngineT<T>::get_tap(uint32_t tap, uint32_t layer, float* buf, uint64_t cap) {
+  const int B = last_B_;
+  if (B <= 0) {
+    fail(ANE_ERR_STATE, "storiesane tap: no step has run");
+    return -1;
+  }
+  const int M = B * S_;
+  const void* src = nullptr;
+  bool src_f32 = true;
+  int ld = 0, col0 = 0, ncols = 0;
+  if (tap < 32 && layer >= (uint32_t)L_) {
+    fail(ANE_ERR_ARG, "storiesane tap: bad layer");
+    return -1;
+  }
+  const bool tf = kIsF32;
+  if (tap < 32) {
+    Act<T>& a = acts_[layer];
+    switch (tap) {
+      case ANE_TAP_X: src = xs_[layer]; ld = D_; ncols = D_; break;
+      case ANE_TAP_XNORM: src = a.xn; src_f32 = tf; ld = D_; ncols = D_; break;
+      case ANE_TAP_Q: src = a.qkv; src_f32 = tf; ld = QKVD_; ncols = QD_; break;
+      case ANE_TAP_K: src = a.qkv; src_f32 = tf; ld = QKVD_; col0 = QD_; ncols = KVD_; break;
+      case ANE_TAP_V: src = a.qkv; src_f32 = tf; ld = QKVD_; col0 = QD_ + KVD_; ncols = KVD_; break;
+      case ANE_TAP_ATT: src = a.att; src_f32 = tf; ld = QD_; ncols = QD_; break;
+      case ANE_TAP_X2: src = a.x2; ld = D_; ncols = D_; break;
+      case ANE_TAP_X2NORM: src = a.x2n; src_f32 = tf; ld = D_; ncols = D_; break;
+      case ANE_TAP_H1: src = a.h13; src_f32 = tf; ld = N13_; ncols = Hd_; break;
+      case ANE_TAP_H3: if (!isN_) { src = a.h13; src_f32 = tf; ld = N13_; col0 = Hd_; ncols = Hd_; } break;
+      case ANE_TAP_GATE: src = a.gate; src_f32 = tf; ld = Hd_; ncols = Hd_; break;
+      case ANE_TAP_QPRE: if (isN_) { src = a.qkpre; src_f32 = tf; ld = QD_ + KVD_; ncols = QD_; } break;
+      case ANE_TAP_KPRE: if (isN_) { src = a.qkpre; src_f32 = tf; ld = QD_ + KVD_; col0 = QD_; ncols = KVD_; } break;
+      case ANE_TAP_DOUT: src = a.t_dout; ld = D_; ncols = D_; break;
+      case ANE_TAP_DX2: src = a.t_dx2; ld = D_; ncols = D_; break;
+      case ANE_TAP_DH1: src = a.t_dh13; ld = N13_; ncols = Hd_; break;
+      case ANE_TAP_DH3: if (!isN_) { src = a.t_dh13; ld = N13_; col0 = Hd_; ncols = Hd_; } break;
+      case ANE_TAP_DQ: src = a.t_dqkv; ld = QKVD_; ncols = QD_; break;
+      case ANE_TAP_DK: src = a.t_dqkv; ld = QKVD_; col0 = QD_; ncols = KVD_; break;
+      case ANE_TAP_DV: src = a.t_dqkv; ld = QKVD_; col0 = QD_ + KVD_; ncols = KVD_; break;
+      default: break;
+    }
+  } else {
+    switch (tap) {
+      case ANE_TAP_X0: if (isN_) { src = x0_; ld = D_; ncols = D_; } break;
+      case ANE_TAP_XMID: if (isN_) { src = xs_[L_ / 2]; ld = D_; ncols = D_; } break;
+      case ANE_TAP_FINAL: src = xs_[L_]; ld = D_; ncols = D_; break;
+      case ANE_TAP_FINAL_NORM: src = xnf_; src_f32 = tf; ld = D_; ncols = D_; break;
+      default: break;
+    }
+  }
+  if (!src || ncols == 0) return 0;
+  const uint64_t n = (uint64_t)M * ncols;
+  if (cap < n) {
+    fail(ANE_ERR_ARG, "storiesane tap: buffer too small");
+    return -1;
+  }
+  if (n > tap_tmp_n_) {
+    fail(ANE_ERR_ARG, "storiesane tap: internal buffer too small");
+    return -1;
+  }
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  count_launch();
+  if (src_f32)
+    export_tap_kernel<float><<<grid, 256, 0, stream_>>>(reinterpret_cast<const float*>(src), ld, col0, ncols, M, S_, tap_tmp_);
+  else
+    export_tap_kernel<T><<<grid, 256, 0, stream_>>>(reinterpret_cast<const T*>(src), ld, col0, ncols, M, S_, tap_tmp_);
+  if (cuda_check(cudaMemcpyAsync(buf, tap_tmp_, sizeof(float) * n, cudaMemcpyDeviceToHost, stream_), "tap") != 0) return -1;
+  if (cuda_check(cudaStreamSynchronize(stream_), "tap sync") != 0) return -1;
+  return (int64_t)n;
+}
+
+}  // namespace
+
+EngineBase* create_engine(int compute_dtype) {
+  if (compute_dtype == ANE_DTYPE_F32) return new EngineT<float>();
+  return new EngineT<bf16>();
+}
+
+}  // namespace ane

@@ -1,0 +1,42 @@
+// Engine interface behind the C ABI (one implementation per compute dtype).
+#pragma once
+
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/ane_b200.h"
+
+namespace ane {
+
+class EngineBase {
+ public:
+  virtual ~EngineBase() {}
+  virtual int open(const ane_options& o, const uint16_t* tokens, uint64_t n_tokens, const uint8_t* dp_id) = 0;
+  // input == nullptr: sample windows with the engine's drand48 sampler.
+  virtual int step(const uint16_t* input, const uint16_t* target, uint32_t n_seq, ane_step_result* out) = 0;
+  virtual int flush(double* refresh_ms) = 0;
+  virtual int eval_logits(const uint16_t* tokens, uint32_t n_seq, float* out, uint64_t cap, uint32_t layout) = 0;
+  virtual int eval_loss(const uint16_t* tokens, uint32_t n_seq, double* loss_sum, uint64_t* n_pos) = 0;
+  virtual int set_lr(float lr) = 0;
+  virtual float get_lr() = 0;
+  virtual int get_state(ane_state* s) = 0;
+  virtual int set_state(const ane_state* s) = 0;
+  virtual int64_t tensor_size(uint32_t id, uint32_t layer) = 0;
+  virtual int import_tensor(uint32_t id, uint32_t layer, uint32_t which, const float* buf, uint64_t n) = 0;
+  virtual int export_tensor(uint32_t id, uint32_t layer, uint32_t which, float* buf, uint64_t n) = 0;
+  virtual int64_t get_tap(uint32_t tap, uint32_t layer, float* buf, uint64_t cap) = 0;
+
+  const std::string& last_error() const { return err_; }
+  uint64_t launches() const { return launches_; }
+
+ protected:
+  void count_launch(int n = 1) { launches_ += (uint64_t)n; }
+  std::string err_;
+  uint64_t launches_ = 0;
+};
+
+EngineBase* create_engine(int compute_dtype);
+
+}  // namespace ane

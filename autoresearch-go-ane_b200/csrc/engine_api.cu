@@ -1,0 +1,146 @@
+// extern "C" surface of the engine (see include/ane_b200.h for the reference citations).
+#include <string.h>
+
+#include <string>
+
+#include "dp.h"
+#include "engine.h"
+
+struct ane_engine {
+  ane::EngineBase* impl = nullptr;
+};
+
+static thread_local std::string g_api_err;
+
+extern "C" {
+
+uint32_t ane_version(void) { return 100; }
+
+const char* ane_last_error(ane_engine* e) {
+  if (e && e->impl) return e->impl->last_error().c_str();
+  return g_api_err.c_str();
+}
+
+int32_t ane_dp_unique_id(uint8_t out_id[128]) {
+  if (!out_id) return ANE_ERR_ARG;
+  std::string err;
+  if (ane::DataParallel::unique_id(out_id, &err) != 0) {
+    g_api_err = err;
+    return ANE_ERR_NCCL;
+  }
+  return 0;
+}
+
+int32_t ane_open(const ane_options* opts, const uint16_t* tokens, uint64_t n_tokens, const uint8_t* dp_id,
+                 ane_engine** out) {
+  if (!opts || !out) {
+    g_api_err = "storiesane open: null argument";
+    return ANE_ERR_ARG;
+  }
+  if (opts->struct_size != sizeof(ane_options)) {
+    g_api_err = "storiesane open: ane_options.struct_size mismatch";
+    return ANE_ERR_ARG;
+  }
+  *out = nullptr;
+  ane::EngineBase* impl = ane::create_engine(opts->compute_dtype);
+  int rc = impl->open(*opts, tokens, n_tokens, dp_id);
+  if (rc != 0) {
+    g_api_err = impl->last_error();
+    delete impl;
+    return rc;
+  }
+  ane_engine* e = new ane_engine();
+  e->impl = impl;
+  *out = e;
+  return 0;
+}
+
+int32_t ane_close(ane_engine* e) {
+  if (!e) return 0;
+  delete e->impl;
+  e->impl = nullptr;
+  delete e;
+  return 0;
+}
+
+#define ENGINE_OR_FAIL(e, what)                                \
+  if (!(e) || !(e)->impl) {                                    \
+    g_api_err = "storiesane " what ": engine is closed";       \
+    return ANE_ERR_ARG;                                        \
+  }
+
+int32_t ane_step(ane_engine* e, ane_step_result* out) {
+  ENGINE_OR_FAIL(e, "step");
+  return e->impl->step(nullptr, nullptr, 0, out);
+}
+int32_t ane_step_tokens(ane_engine* e, const uint16_t* input, const uint16_t* target, uint32_t n_seq,
+                        ane_step_result* out) {
+  ENGINE_OR_FAIL(e, "step");
+  if (!input || !target) {
+    g_api_err = "storiesane step: null token buffers";
+    return ANE_ERR_ARG;
+  }
+  return e->impl->step(input, target, n_seq, out);
+}
+int32_t ane_flush(ane_engine* e, double* refresh_ms) {
+  ENGINE_OR_FAIL(e, "flush");
+  return e->impl->flush(refresh_ms);
+}
+int32_t ane_eval_logits(ane_engine* e, const uint16_t* tokens, uint32_t n_seq, float* out, uint64_t out_cap,
+                        uint32_t layout) {
+  ENGINE_OR_FAIL(e, "eval logits");
+  if (!tokens || !out) {
+    g_api_err = "storiesane eval logits: null buffer";
+    return ANE_ERR_ARG;
+  }
+  return e->impl->eval_logits(tokens, n_seq, out, out_cap, layout);
+}
+int32_t ane_eval_loss(ane_engine* e, const uint16_t* tokens, uint32_t n_seq, double* loss_sum, uint64_t* n_positions) {
+  ENGINE_OR_FAIL(e, "eval loss");
+  if (!tokens) {
+    g_api_err = "storiesane eval loss: null buffer";
+    return ANE_ERR_ARG;
+  }
+  return e->impl->eval_loss(tokens, n_seq, loss_sum, n_positions);
+}
+int32_t ane_set_lr(ane_engine* e, float lr) {
+  ENGINE_OR_FAIL(e, "set lr");
+  return e->impl->set_lr(lr);
+}
+float ane_get_lr(ane_engine* e) {
+  if (!e || !e->impl) return 0.f;
+  return e->impl->get_lr();
+}
+int32_t ane_get_state(ane_engine* e, ane_state* out) {
+  ENGINE_OR_FAIL(e, "state");
+  return e->impl->get_state(out);
+}
+int32_t ane_set_state(ane_engine* e, const ane_state* in) {
+  ENGINE_OR_FAIL(e, "load state");
+  return e->impl->set_state(in);
+}
+int64_t ane_tensor_size(ane_engine* e, uint32_t tensor_id, uint32_t layer) {
+  if (!e || !e->impl) return -1;
+  return e->impl->tensor_size(tensor_id, layer);
+}
+int32_t ane_import_tensor(ane_engine* e, uint32_t tensor_id, uint32_t layer, uint32_t which, const float* buf,
+                          uint64_t n) {
+  ENGINE_OR_FAIL(e, "import");
+  if (!buf) return ANE_ERR_ARG;
+  return e->impl->import_tensor(tensor_id, layer, which, buf, n);
+}
+int32_t ane_export_tensor(ane_engine* e, uint32_t tensor_id, uint32_t layer, uint32_t which, float* buf, uint64_t n) {
+  ENGINE_OR_FAIL(e, "export");
+  if (!buf && n) return ANE_ERR_ARG;
+  return e->impl->export_tensor(tensor_id, layer, which, buf, n);
+}
+int64_t ane_get_tap(ane_engine* e, uint32_t tap_id, uint32_t layer, float* buf, uint64_t cap) {
+  if (!e || !e->impl || !buf) return -1;
+  return e->impl->get_tap(tap_id, layer, buf, cap);
+}
+uint64_t ane_launch_count(ane_engine* e) {
+  if (!e || !e->impl) return 0;
+  return e->impl->launches();
+}
+
+}  // extern "C"

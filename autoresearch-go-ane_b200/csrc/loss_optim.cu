@@ -1,0 +1,261 @@
+// Cross-entropy over logit rows, gradient-norm reduction and the fused AdamW update.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace ane {
+
+// ------------------------------------------------------------------------------------------
+// Cross entropy (ane/stories/cpu.go:212-292) with the soft cap (ane/common.go:272-287) folded in.
+// One block per token row of fp32 logits [rows, V]; two passes (online max/sum, then gradient).
+// ------------------------------------------------------------------------------------------
+static constexpr int kCEThreads = 256;
+
+__device__ __forceinline__ float softcap_f(float x) { return 15.0f * tanhf(x * (1.0f / 15.0f)); }
+
+template <typename TO>
+__global__ void __launch_bounds__(kCEThreads)
+cross_entropy_rows_kernel(const float* __restrict__ logits, const uint16_t* __restrict__ targets,
+                          const float* __restrict__ inv_valid, TO* __restrict__ dlogits,
+                          float* __restrict__ loss_rows, int rows, int row0, int seq, int V, int softcap,
+                          float grad_scale) {
+  const int r = blockIdx.x;
+  if (r >= rows) return;
+  const int grow = row0 + r;  // global token row
+  const float* x = logits + (size_t)r * V;
+  TO* dl = dlogits ? dlogits + (size_t)r * V : nullptr;
+  const int tgt = targets[grow];
+  __shared__ float s_m[kCEThreads / 32], s_l[kCEThreads / 32];
+  __shared__ float s_bm, s_bl;
+  if (tgt >= V) {  // invalid target: zero gradient row, not counted (cpu.go:253-258)
+    if (dl)
+      for (int i = threadIdx.x; i < V; i += kCEThreads) dl[i] = from_f<TO>(0.f);
+    if (threadIdx.x == 0 && loss_rows) loss_rows[grow] = 0.f;
+    return;
+  }
+  float m = -INFINITY, l = 0.f;
+  for (int i = threadIdx.x; i < V; i += kCEThreads) {
+    float z = x[i];
+    if (softcap) z = softcap_f(z);
+    if (z > m) {
+      l = l * __expf(m - z) + 1.f;
+      m = z;
+    } else {
+      l += __expf(z - m);
+    }
+  }
+  // warp then block combine of (m, l)
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o), l2 = __shfl_xor_sync(0xffffffffu, l, o);
+    const float mn = fmaxf(m, m2);
+    l = (m == -INFINITY ? 0.f : l * __expf(m - mn)) + (m2 == -INFINITY ? 0.f : l2 * __expf(m2 - mn));
+    m = mn;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    s_m[warp] = m;
+    s_l[warp] = l;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float bm = s_m[0], bl = s_l[0];
+    for (int w = 1; w < kCEThreads / 32; ++w) {
+      const float mn = fmaxf(bm, s_m[w]);
+      bl = (bm == -INFINITY ? 0.f : bl * __expf(bm - mn)) + (s_m[w] == -INFINITY ? 0.f : s_l[w] * __expf(s_m[w] - mn));
+      bm = mn;
+    }
+    s_bm = bm;
+    s_bl = bl;
+  }
+  __syncthreads();
+  const float bm = s_bm;
+  const float inv_sum = 1.0f / s_bl;
+  const float gs = grad_scale * inv_valid[grow / seq];
+  for (int i = threadIdx.x; i < V; i += kCEThreads) {
+    const float raw = x[i];
+    float z = raw, dcap = 1.f;
+    if (softcap) {
+      const float th = tanhf(raw * (1.0f / 15.0f));
+      z = 15.0f * th;
+      dcap = 1.f - th * th;
+    }
+    const float p = expf(z - bm) * inv_sum;
+    if (i == tgt && loss_rows) loss_rows[grow] = -logf(fmaxf(p, 1e-10f));
+    if (dl) dl[i] = from_f<TO>(gs * (p - (i == tgt ? 1.f : 0.f)) * dcap);
+  }
+}
+
+template <typename TO>
+void cross_entropy_rows(const float* logits, const uint16_t* targets, const float* inv_valid, TO* dlogits,
+                        float* loss_rows, int rows, int row0, int seq, int V, bool softcap, float grad_scale,
+                        cudaStream_t s) {
+  if (rows <= 0) return;
+  cross_entropy_rows_kernel<TO><<<rows, kCEThreads, 0, s>>>(logits, targets, inv_valid, dlogits, loss_rows, rows, row0,
+                                                            seq, V, softcap ? 1 : 0, grad_scale);
+}
+template void cross_entropy_rows<float>(const float*, const uint16_t*, const float*, float*, float*, int, int, int,
+                                        int, bool, float, cudaStream_t);
+template void cross_entropy_rows<bf16>(const float*, const uint16_t*, const float*, bf16*, float*, int, int, int, int,
+                                       bool, float, cudaStream_t);
+
+__global__ void softcap_inplace_kernel(float* __restrict__ logits, uint64_t n) {
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) logits[i] = softcap_f(logits[i]);
+}
+void softcap_inplace(float* logits, uint64_t n, cudaStream_t s) {
+  if (!n) return;
+  uint64_t g = (n + 255) / 256;
+  if (g > 148ull * 16) g = 148ull * 16;
+  softcap_inplace_kernel<<<(unsigned)g, 256, 0, s>>>(logits, n);
+}
+
+__global__ void count_valid_targets_kernel(const uint16_t* __restrict__ targets, float* __restrict__ inv_valid, int B,
+                                           int seq, int V) {
+  const int b = blockIdx.x;
+  if (b >= B) return;
+  int c = 0;
+  for (int t = threadIdx.x; t < seq; t += blockDim.x) c += targets[(size_t)b * seq + t] < V ? 1 : 0;
+  __shared__ int s_c[32];
+  for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+  if ((threadIdx.x & 31) == 0) s_c[threadIdx.x >> 5] = c;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tot = 0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += s_c[w];
+    inv_valid[b] = tot > 0 ? (float)(1.0 / (double)tot) : 0.f;
+  }
+}
+void count_valid_targets(const uint16_t* targets, float* inv_valid, int B, int seq, int V, cudaStream_t s) {
+  if (B <= 0) return;
+  count_valid_targets_kernel<<<B, 128, 0, s>>>(targets, inv_valid, B, seq, V);
+}
+
+// loss_out[0] = (1/B) * sum_b inv_valid[b] * sum_t loss_rows[b,t]   (single block, double accumulation)
+__global__ void reduce_loss_kernel(const float* __restrict__ loss_rows, const float* __restrict__ inv_valid,
+                                   float* __restrict__ loss_out, int B, int seq) {
+  double local = 0.0;
+  const int n = B * seq;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) local += (double)loss_rows[i] * (double)inv_valid[i / seq];
+  local = warp_sum_d(local);
+  __shared__ double s_p[32];
+  if ((threadIdx.x & 31) == 0) s_p[threadIdx.x >> 5] = local;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double tot = 0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += s_p[w];
+    loss_out[0] = (float)(tot / (double)B);
+  }
+}
+void reduce_loss(const float* loss_rows, const float* inv_valid, float* loss_out, int B, int seq, cudaStream_t s) {
+  if (B <= 0) return;
+  reduce_loss_kernel<<<1, 1024, 0, s>>>(loss_rows, inv_valid, loss_out, B, seq);
+}
+
+// ------------------------------------------------------------------------------------------
+// Gradient norm (ane/train_full.go:167-196): sum of squares in double.
+// ------------------------------------------------------------------------------------------
+__global__ void sumsq_kernel(const float* __restrict__ g, uint64_t n, float pre_scale, double* __restrict__ acc) {
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  double local = 0.0;
+  for (; i < n; i += stride) {
+    const float v = g[i] * pre_scale;
+    local += (double)v * (double)v;
+  }
+  local = warp_sum_d(local);
+  __shared__ double s_p[8];
+  if ((threadIdx.x & 31) == 0) s_p[threadIdx.x >> 5] = local;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double tot = 0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += s_p[w];
+    atomicAdd(acc, tot);
+  }
+}
+void sumsq_accumulate(const float* g, uint64_t n, float pre_scale, double* acc, cudaStream_t s) {
+  if (!n) return;
+  uint64_t grid = (n + 255) / 256;
+  if (grid > 148ull * 8) grid = 148ull * 8;
+  sumsq_kernel<<<(unsigned)grid, 256, 0, s>>>(g, n, pre_scale, acc);
+}
+
+__global__ void finalize_clip_kernel(const double* __restrict__ acc, float pre_scale, float clip,
+                                     float* __restrict__ scales, float* __restrict__ norm_out) {
+  const double norm2 = acc[0];
+  float s = 1.f;
+  const float norm = (float)sqrt(norm2);
+  if (clip > 0.f && norm2 > 0.0 && norm > clip) s = clip / norm;
+  scales[0] = pre_scale;
+  scales[1] = pre_scale * s;
+  if (norm_out) norm_out[0] = norm;
+}
+void finalize_clip(const double* acc, float pre_scale, float clip, float* scales, float* norm_out, cudaStream_t s) {
+  finalize_clip_kernel<<<1, 1, 0, s>>>(acc, pre_scale, clip, scales, norm_out);
+}
+
+// ------------------------------------------------------------------------------------------
+// AdamW (ane/train_full.go:1113-1150).  28 B/param of fp32 state traffic + 2 B bf16 shadow.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void adam_one(float& w, float g, float& m, float& v, const AdamHyper& h) {
+  m = h.b1 * m + (1.f - h.b1) * g;
+  v = h.b2 * v + (1.f - h.b2) * g * g;
+  const float mh = m * h.inv_bc1;
+  const float vh = v * h.inv_bc2;
+  float update = mh / (sqrtf(vh) + h.eps);
+  if (h.wd != 0.f) update += h.wd * w;
+  w -= h.lr * update;
+}
+
+__global__ void __launch_bounds__(256)
+adam_kernel(float* __restrict__ w, float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+            bf16* __restrict__ shadow, uint64_t n, AdamHyper h, const float* __restrict__ gscale, int vec_ok) {
+  const float gs = gscale ? *gscale : 1.f;
+  const uint64_t n4 = vec_ok ? (n >> 2) : 0;
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  float4* w4 = reinterpret_cast<float4*>(w);
+  float4* g4 = reinterpret_cast<float4*>(g);
+  float4* m4 = reinterpret_cast<float4*>(m);
+  float4* v4 = reinterpret_cast<float4*>(v);
+  for (uint64_t k = i; k < n4; k += stride) {
+    float4 ww = w4[k], gg = g4[k], mm = m4[k], vv = v4[k];
+    adam_one(ww.x, gg.x * gs, mm.x, vv.x, h);
+    adam_one(ww.y, gg.y * gs, mm.y, vv.y, h);
+    adam_one(ww.z, gg.z * gs, mm.z, vv.z, h);
+    adam_one(ww.w, gg.w * gs, mm.w, vv.w, h);
+    w4[k] = ww;
+    m4[k] = mm;
+    v4[k] = vv;
+    g4[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (shadow) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(ww.x, ww.y), hi = __floats2bfloat162_rn(ww.z, ww.w);
+      uint2 u;
+      u.x = *reinterpret_cast<uint32_t*>(&lo);
+      u.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(shadow)[k] = u;
+    }
+  }
+  for (uint64_t k = (n4 << 2) + i; k < n; k += stride) {
+    float ww = w[k], mm = m[k], vv = v[k];
+    adam_one(ww, g[k] * gs, mm, vv, h);
+    w[k] = ww;
+    m[k] = mm;
+    v[k] = vv;
+    g[k] = 0.f;
+    if (shadow) shadow[k] = __float2bfloat16_rn(ww);
+  }
+}
+
+void adam_update(float* w, float* g, float* m, float* v, bf16* shadow, uint64_t n, AdamHyper h, const float* gscale,
+                 cudaStream_t s) {
+  if (!n) return;
+  uint64_t grid = ((n >> 2) + 255) / 256;
+  if (grid > 148ull * 8) grid = 148ull * 8;
+  if (grid < 1) grid = 1;
+  auto al = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
+  const int vec_ok = al(w, 16) && al(g, 16) && al(m, 16) && al(v, 16) && (!shadow || al(shadow, 8));
+  adam_kernel<<<(unsigned)grid, 256, 0, s>>>(w, g, m, v, shadow, n, h, gscale, vec_ok);
+}
+
+}  // namespace ane

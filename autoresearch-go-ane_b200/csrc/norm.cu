@@ -1,0 +1,213 @@
+// Embedding gather/scatter and RMSNorm forward/backward (HBM-bound kernels).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace ane {
+
+static constexpr int kWarpsPerBlock = 8;
+
+// ------------------------------------------------------------------------------------------
+// Embedding (ane/stories/cpu.go:41-95) with the optional parameterless embed-norm
+// (ane/train_full.go:384-388).  One warp per token row.
+// ------------------------------------------------------------------------------------------
+__global__ void embed_forward_kernel(const uint16_t* __restrict__ tok, const float* __restrict__ embed,
+                                     float* __restrict__ x, float* __restrict__ x_raw, int M, int D, int vocab,
+                                     int embed_norm) {
+  const int row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const int t = tok[row];
+  const bool valid = t < vocab;
+  const float* src = embed + (size_t)(valid ? t : 0) * D;
+  float* dst = x + (size_t)row * D;
+  float ss = 0.f;
+  for (int i = lane; i < D; i += 32) {
+    float v = valid ? src[i] : 0.f;
+    if (x_raw) x_raw[(size_t)row * D + i] = v;
+    ss += v * v;
+    if (!embed_norm) dst[i] = v;
+  }
+  if (embed_norm) {
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)D + 1e-5f);
+    for (int i = lane; i < D; i += 32) {
+      float v = valid ? src[i] : 0.f;
+      dst[i] = v * r;
+    }
+  }
+}
+
+void embed_forward(const uint16_t* tok, const float* embed, float* x, float* x_raw, int M, int D, int vocab,
+                   bool embed_norm, cudaStream_t s) {
+  if (M <= 0) return;
+  const int blocks = (M + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  embed_forward_kernel<<<blocks, kWarpsPerBlock * 32, 0, s>>>(tok, embed, x, x_raw, M, D, vocab, embed_norm ? 1 : 0);
+}
+
+__global__ void embed_backward_kernel(const uint16_t* __restrict__ tok, const float* __restrict__ dx,
+                                      float* __restrict__ g_embed, int M, int D, int vocab) {
+  const int row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const int t = tok[row];
+  if (t >= vocab) return;
+  float* dst = g_embed + (size_t)t * D;
+  const float* src = dx + (size_t)row * D;
+  for (int i = lane; i < D; i += 32) atomicAdd(dst + i, src[i]);
+}
+
+void embed_backward(const uint16_t* tok, const float* dx, float* g_embed, int M, int D, int vocab, cudaStream_t s) {
+  if (M <= 0) return;
+  const int blocks = (M + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  embed_backward_kernel<<<blocks, kWarpsPerBlock * 32, 0, s>>>(tok, dx, g_embed, M, D, vocab);
+}
+
+// ------------------------------------------------------------------------------------------
+// RMSNorm forward: one warp per row, float4 loads, fp32 statistics.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <>
+__device__ __forceinline__ void store4<bf16>(bf16* p, float a, float b, float c, float d) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&lo);
+  u.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename T>
+__global__ void rmsnorm_forward_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
+                                       float* __restrict__ rstd, int M, int D) {
+  const int row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * D);
+  const float4* wr = reinterpret_cast<const float4*>(w);
+  const int n4 = D >> 2;
+  float ss = 0.f;
+  for (int i = lane; i < n4; i += 32) {
+    float4 v = xr[i];
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = warp_sum(ss);
+  const float r = 1.0f / sqrtf(ss / (float)D + 1e-5f);
+  if (lane == 0 && rstd) rstd[row] = r;
+  T* yr = y + (size_t)row * D;
+  for (int i = lane; i < n4; i += 32) {
+    float4 v = xr[i];
+    float4 ww = w ? wr[i] : make_float4(1.f, 1.f, 1.f, 1.f);
+    store4<T>(yr + 4 * i, v.x * r * ww.x, v.y * r * ww.y, v.z * r * ww.z, v.w * r * ww.w);
+  }
+}
+
+template <typename T>
+void rmsnorm_forward(const float* x, const float* w, T* y, float* rstd, int M, int D, cudaStream_t s) {
+  if (M <= 0) return;
+  const int blocks = (M + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  rmsnorm_forward_kernel<T><<<blocks, kWarpsPerBlock * 32, 0, s>>>(x, w, y, rstd, M, D);
+}
+template void rmsnorm_forward<float>(const float*, const float*, float*, float*, int, int, cudaStream_t);
+template void rmsnorm_forward<bf16>(const float*, const float*, bf16*, float*, int, int, cudaStream_t);
+
+// ------------------------------------------------------------------------------------------
+// RMSNorm backward (+ residual blend, + optional weight gradient).
+//   g = dy*w;  dot = sum(g*x);  dx = g*r - x*dot*r^3/D + res_scale*res
+//   dw[i] += sum_rows dy*x*r    (block-local shared accumulation, then global atomics)
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rmsnorm_backward_kernel(const float* __restrict__ dy, const float* __restrict__ x,
+                                        const float* __restrict__ w, const float* __restrict__ rstd,
+                                        const float* __restrict__ res, const float* __restrict__ res_scale,
+                                        float* __restrict__ dx_f32, T* __restrict__ dx_t, float* __restrict__ dw,
+                                        int M, int D) {
+  extern __shared__ float s_dw[];  // [D] when dw != nullptr
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  if (dw) {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) s_dw[i] = 0.f;
+    __syncthreads();
+  }
+  const float rs = res ? (res_scale ? *res_scale : 1.f) : 0.f;
+  const int n4 = D >> 2;
+  const float inv_d = 1.0f / (float)D;
+  for (int row = blockIdx.x * kWarpsPerBlock + warp; row < M; row += gridDim.x * kWarpsPerBlock) {
+    const float4* dyr = reinterpret_cast<const float4*>(dy + (size_t)row * D);
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * D);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    float r;
+    if (rstd) {
+      r = rstd[row];
+    } else {
+      float ss = 0.f;
+      for (int i = lane; i < n4; i += 32) {
+        float4 v = xr[i];
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+      ss = warp_sum(ss);
+      r = 1.0f / sqrtf(ss * inv_d + 1e-5f);
+    }
+    float dot = 0.f;
+    for (int i = lane; i < n4; i += 32) {
+      float4 g = dyr[i], v = xr[i];
+      if (w) {
+        float4 ww = wr[i];
+        g.x *= ww.x; g.y *= ww.y; g.z *= ww.z; g.w *= ww.w;
+      }
+      dot += g.x * v.x + g.y * v.y + g.z * v.z + g.w * v.w;
+    }
+    dot = warp_sum(dot);
+    const float coeff = dot * r * r * r * inv_d;
+    const float4* rr = res ? reinterpret_cast<const float4*>(res + (size_t)row * D) : nullptr;
+    for (int i = lane; i < n4; i += 32) {
+      float4 g = dyr[i], v = xr[i];
+      if (dw) {
+        atomicAdd(&s_dw[4 * i + 0], g.x * v.x * r);
+        atomicAdd(&s_dw[4 * i + 1], g.y * v.y * r);
+        atomicAdd(&s_dw[4 * i + 2], g.z * v.z * r);
+        atomicAdd(&s_dw[4 * i + 3], g.w * v.w * r);
+      }
+      if (w) {
+        float4 ww = wr[i];
+        g.x *= ww.x; g.y *= ww.y; g.z *= ww.z; g.w *= ww.w;
+      }
+      float4 o;
+      o.x = g.x * r - coeff * v.x;
+      o.y = g.y * r - coeff * v.y;
+      o.z = g.z * r - coeff * v.z;
+      o.w = g.w * r - coeff * v.w;
+      if (rr) {
+        float4 q = rr[i];
+        o.x += rs * q.x; o.y += rs * q.y; o.z += rs * q.z; o.w += rs * q.w;
+      }
+      if (dx_f32) *reinterpret_cast<float4*>(dx_f32 + (size_t)row * D + 4 * i) = o;
+      if (dx_t) store4<T>(dx_t + (size_t)row * D + 4 * i, o.x, o.y, o.z, o.w);
+    }
+  }
+  if (dw) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < D; i += blockDim.x) atomicAdd(dw + i, s_dw[i]);
+  }
+}
+
+template <typename T>
+void rmsnorm_backward(const float* dy, const float* x, const float* w, const float* rstd, const float* res,
+                      const float* res_scale, float* dx_f32, T* dx_t, float* dw, int M, int D, cudaStream_t s) {
+  if (M <= 0) return;
+  int blocks = (M + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  if (dw && blocks > 148 * 2) blocks = 148 * 2;  // bound the number of global atomic passes
+  const size_t smem = dw ? sizeof(float) * (size_t)D : 0;
+  // dx_t may alias dx_f32 only when T == float; callers pass nullptr instead.
+  rmsnorm_backward_kernel<T><<<blocks, kWarpsPerBlock * 32, smem, s>>>(dy, x, w, rstd, res, res_scale, dx_f32, dx_t,
+                                                                         dw, M, D);
+}
+template void rmsnorm_backward<float>(const float*, const float*, const float*, const float*, const float*,
+                                      const float*, float*, float*, float*, int, int, cudaStream_t);
+template void rmsnorm_backward<bf16>(const float*, const float*, const float*, const float*, const float*,
+                                     const float*, float*, bf16*, float*, int, int, cudaStream_t);
+
+}  // namespace ane

@@ -78,6 +78,127 @@ typedef struct ane_gemm_args {
 } ane_gemm_args;
 int32_t ane_op_gemm(const ane_gemm_args* args);
 
+
+/* ============================================================================
+ * Engine: the drop-in surface behind ane.Engine (ane/engine.go).
+ * ========================================================================== */
+
+#define ANE_ARCH_REFERENCE 0 /* the network ane/train_full.go:383-453 trains           */
+#define ANE_ARCH_LLAMA 1     /* weighted RMSNorm, SwiGLU (W1/W3/W2), optional GQA        */
+
+/* Mirrors ane.Options (ane/engine.go:14-40); zero / negative values take the defaults
+ * of ane.Open (ane/engine.go:188-239).  Model dimensions are runtime fields here (the
+ * reference fixes them in ane/stories/config.go:3-18); zero means the reference value. */
+typedef struct ane_options {
+  uint32_t struct_size;
+  int32_t dim, hidden, n_layers, n_heads, n_kv_heads, vocab; /* 768, 2048, 12, 12, =n_heads, 32000 */
+  int32_t seq;                                                /* 256 */
+  int32_t batch;          /* sequences per ane_step call (reference: 1) */
+  int32_t arch;           /* ANE_ARCH_*                                  */
+  int32_t quirks;         /* 1: reproduce the reference's backward exactly (ANE_ARCH_REFERENCE only) */
+  int32_t compute_dtype;  /* ANE_DTYPE_BF16 (tensor cores) or ANE_DTYPE_F32 (parity mode) */
+  float rope_theta;       /* 0: 100000 (reference arch) / 10000 (llama arch) */
+  int32_t accum_steps;    /* ane_step calls per optimizer update */
+  float lr;
+  int64_t seed;
+  float adam_beta1, adam_beta2, adam_eps, weight_decay, grad_clip, loss_scale;
+  float embed_lr_mult, scalar_lr_mult, lambda_lr_mult, lambda_beta1, lambda_beta2;
+  int32_t use_ane;         /* accepted and ignored: the GPU path is always on */
+  int32_t hybrid_backward; /* accepted and ignored */
+  int32_t device;          /* CUDA device ordinal */
+  int32_t rank, world_size;/* data-parallel rank / size (world_size <= 1: single GPU) */
+  int32_t debug_taps;      /* 1: keep per-layer gradient taps for ane_get_tap */
+  int32_t ce_chunk_rows;   /* token rows per classifier/cross-entropy chunk (0: library chooses) */
+  int32_t reserved[6];
+} ane_options;
+
+/* Mirrors ane.StepResult (ane/engine.go:55-69); durations in nanoseconds. */
+typedef struct ane_step_result {
+  uint32_t struct_size;
+  float loss;
+  int64_t step_ns;
+  int64_t compile_ns;          /* always 0: nothing is compiled at run time */
+  int64_t startup_compile_ns;  /* always 0 */
+  int64_t device_eval_ns;      /* GPU time of the step (the reference's ANEEvalDuration slot) */
+  int64_t cpu_work_ns;         /* host time not overlapped with the device */
+  int64_t weight_refresh_ns;   /* always 0: the bf16 shadow weights are written by the optimizer kernel */
+  int64_t final_head_ns, embed_grad_ns, rms_dw_ns, dw_gemm_ns, dw_wait_ns, adam_ns;
+  int32_t flushed;             /* 1 if this call ran the optimizer update */
+  int32_t device_status;       /* 0, or the code a kernel's bounded wait reported */
+} ane_step_result;
+
+/* Mirrors ane.State (ane/engine.go:43-52). */
+typedef struct ane_state {
+  uint32_t struct_size;
+  uint32_t cum_steps, cum_batches, adam_t, pending_steps;
+  uint64_t token_pos;
+  float last_loss;
+  float pad_;
+  double cum_train_ms, cum_wall_ms;
+} ane_state;
+
+typedef struct ane_engine ane_engine;
+
+/* 128-byte NCCL bootstrap id: rank 0 calls ane_dp_unique_id and shares the bytes with the
+ * other ranks (any out-of-band channel) before every rank calls ane_open with it. */
+int32_t ane_dp_unique_id(uint8_t out_id[128]);
+
+/* ane.Open (ane/engine.go:184).  tokens may be NULL/0 for an evaluation-only engine.
+ * dp_id is NULL unless opts->world_size > 1.  Weights start at zero (norm weights and
+ * residual lambdas at 1); load them with ane_import_tensor. */
+int32_t ane_open(const ane_options* opts, const uint16_t* tokens, uint64_t n_tokens, const uint8_t* dp_id,
+                 ane_engine** out);
+int32_t ane_close(ane_engine* e);              /* ane/engine.go:567 */
+const char* ane_last_error(ane_engine* e);     /* message for the last non-zero status (e may be NULL) */
+uint32_t ane_version(void);
+
+/* Engine.Step (ane/engine.go:381): samples `batch` windows with the drand48 sampler
+ * (ane/engine.go:395-404, :873-880), runs forward, head, backward; every accum_steps calls it
+ * applies the optimizer update (ane/engine.go:646-682). */
+int32_t ane_step(ane_engine* e, ane_step_result* out);
+/* Same step on caller-provided windows: input/target are [n_seq][seq] host arrays, n_seq == batch. */
+int32_t ane_step_tokens(ane_engine* e, const uint16_t* input, const uint16_t* target, uint32_t n_seq,
+                        ane_step_result* out);
+/* Engine.Flush (ane/engine.go:484): apply pending accumulated gradients now. */
+int32_t ane_flush(ane_engine* e, double* refresh_ms);
+/* Engine.EvalLogits (ane/engine.go:449).  tokens: [n_seq][seq].  layout 0 = the reference's
+ * [n_seq][vocab][seq] (logits[v*seq+t]); layout 1 = [n_seq*seq][vocab].  out_cap in floats. */
+int32_t ane_eval_logits(ane_engine* e, const uint16_t* tokens, uint32_t n_seq, float* out, uint64_t out_cap,
+                        uint32_t layout);
+/* Fused evaluation loss (no logits leave the device): per window, sum over t < seq-1 of
+ * -log softmax(logits[:,t])[tokens[t+1]], the loop of harness.go:46-89 with correct indexing. */
+int32_t ane_eval_loss(ane_engine* e, const uint16_t* tokens, uint32_t n_seq, double* loss_sum, uint64_t* n_positions);
+int32_t ane_set_lr(ane_engine* e, float lr);   /* ane/engine.go:366 */
+float ane_get_lr(ane_engine* e);               /* ane/engine.go:358 */
+int32_t ane_get_state(ane_engine* e, ane_state* out);       /* ane/engine.go:498 */
+int32_t ane_set_state(ane_engine* e, const ane_state* in);  /* ane/engine.go:506 */
+
+/* Weights / gradients / optimizer moments by tensor id, as row-major fp32 in the reference's
+ * shapes (ane/stories/weights.go:13-42), so a host can read and write checkpoints
+ * (ane/stories/ckpt.go:77-269).  which: 0 weight, 1 accumulated gradient, 2 Adam m, 3 Adam v. */
+enum {
+  ANE_T_EMBED = 0, ANE_T_WQ = 1, ANE_T_WK = 2, ANE_T_WV = 3, ANE_T_WO = 4, ANE_T_W1 = 5, ANE_T_W2 = 6, ANE_T_W3 = 7,
+  ANE_T_RMS_ATT = 8, ANE_T_RMS_FFN = 9, ANE_T_RMS_FINAL = 10, ANE_T_VE_EMBED = 11, ANE_T_VE_GATE = 12,
+  ANE_T_RESID_LAMBDAS = 13, ANE_T_X0_LAMBDAS = 14, ANE_T_SMEAR_GATE = 15, ANE_T_SMEAR_LAMBDA = 16,
+  ANE_T_BACKOUT_LAMBDA = 17, ANE_T_COUNT = 18
+};
+int64_t ane_tensor_size(ane_engine* e, uint32_t tensor_id, uint32_t layer); /* elements; 0 if absent; <0 error */
+int32_t ane_import_tensor(ane_engine* e, uint32_t tensor_id, uint32_t layer, uint32_t which, const float* buf,
+                          uint64_t n);
+int32_t ane_export_tensor(ane_engine* e, uint32_t tensor_id, uint32_t layer, uint32_t which, float* buf, uint64_t n);
+
+/* Activation taps of the last step, reference layout [n_seq][channels][seq] (ane/train_full.go:12-37). */
+enum {
+  ANE_TAP_X = 0, ANE_TAP_XNORM, ANE_TAP_Q, ANE_TAP_K, ANE_TAP_V, ANE_TAP_ATT, ANE_TAP_X2, ANE_TAP_X2NORM,
+  ANE_TAP_H1, ANE_TAP_GATE, ANE_TAP_FFN_OUT, ANE_TAP_QPRE, ANE_TAP_KPRE, ANE_TAP_H3,
+  ANE_TAP_DOUT, ANE_TAP_DH1, ANE_TAP_DX2, ANE_TAP_DQ, ANE_TAP_DK, ANE_TAP_DV, ANE_TAP_DH3,
+  ANE_TAP_X0 = 32, ANE_TAP_XMID, ANE_TAP_FINAL, ANE_TAP_FINAL_NORM
+};
+int64_t ane_get_tap(ane_engine* e, uint32_t tap_id, uint32_t layer, float* buf, uint64_t cap); /* returns floats written */
+
+/* Kernel launches issued by this library since the engine was opened (for measurement reports). */
+uint64_t ane_launch_count(ane_engine* e);
+
 #ifdef __cplusplus
 }
 #endif
