@@ -100,6 +100,10 @@ SIGNATURES = {
     "ane_export_tensor": (c_int32, [c_void_p, c_uint32, c_uint32, c_uint32, POINTER(c_float), c_uint64]),
     "ane_get_tap": (c_int64, [c_void_p, c_uint32, c_uint32, POINTER(c_float), c_uint64]),
     "ane_launch_count": (c_uint64, [c_void_p]),
+    "ane_engine_timer_begin": (c_int32, [c_void_p]),
+    "ane_engine_timer_end": (c_int32, [c_void_p, POINTER(c_float)]),
+    "ane_profile_gemm": (c_int32, [c_void_p, c_int32]),
+    "ane_profile_read": (c_int32, [c_void_p, POINTER(c_double), POINTER(c_double), POINTER(c_uint64)]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

@@ -264,6 +264,22 @@ class Engine:
             return None
         return buf[:n].reshape(-1, self.seq)
 
+    def timer_begin(self):
+        self._check(lib.ane_engine_timer_begin(self._h))
+
+    def timer_end(self) -> float:
+        ms = c_float(0)
+        self._check(lib.ane_engine_timer_end(self._h, byref(ms)))
+        return float(ms.value)
+
+    def profile_gemm(self, enable: bool):
+        self._check(lib.ane_profile_gemm(self._h, int(enable)))
+
+    def profile_read(self) -> tuple[float, float, int]:
+        ms, fl, n = c_double(0), c_double(0), c_uint64(0)
+        self._check(lib.ane_profile_read(self._h, byref(ms), byref(fl), byref(n)))
+        return ms.value, fl.value, int(n.value)
+
     def launch_count(self) -> int:
         return int(lib.ane_launch_count(self._h))
 

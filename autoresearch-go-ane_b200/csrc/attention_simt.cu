@@ -13,8 +13,8 @@ static constexpr int kAttWarps = 4;
 static constexpr int kMaxHdPerLane = 4;  // head_dim <= 128
 
 // One warp per query row (b, h, t).  Dynamic smem: kAttWarps * hd floats (query vectors).
-template <typename T>
-__global__ void attention_forward_simt_kernel(const T* __restrict__ qkv, T* __restrict__ out,
+template <typename T, typename TO>
+__global__ void attention_forward_simt_kernel(const T* __restrict__ qkv, TO* __restrict__ out,
                                               float* __restrict__ lse, int B, int seq, int H, int KV, int hd,
                                               float scale) {
   extern __shared__ float s_q[];
@@ -64,32 +64,35 @@ __global__ void attention_forward_simt_kernel(const T* __restrict__ qkv, T* __re
     m_run = m_new;
   }
   const float inv = 1.0f / l_run;
-  T* op = out + (row0 + t) * (size_t)(H * hd) + (size_t)h * hd;
+  TO* op = out + (row0 + t) * (size_t)(H * hd) + (size_t)h * hd;
 #pragma unroll
   for (int c = 0; c < kMaxHdPerLane; ++c) {
     const int d = lane + 32 * c;
-    if (d < hd) op[d] = from_f<T>(acc[c] * inv);
+    if (d < hd) op[d] = from_f<TO>(acc[c] * inv);
   }
   if (lane == 0 && lse) lse[((size_t)b * H + h) * seq + t] = m_run + logf(l_run);
 }
 
-template <typename T>
-void attention_forward_simt(const T* qkv, T* out, float* lse, int B, int seq, int H, int KV, int hd, float scale,
+template <typename T, typename TO>
+void attention_forward_simt(const T* qkv, TO* out, float* lse, int B, int seq, int H, int KV, int hd, float scale,
                             cudaStream_t s) {
   const long long total = (long long)B * H * seq;
   if (total <= 0) return;
   const unsigned blocks = (unsigned)((total + kAttWarps - 1) / kAttWarps);
-  attention_forward_simt_kernel<T><<<blocks, kAttWarps * 32, kAttWarps * hd * sizeof(float), s>>>(qkv, out, lse, B, seq,
+  attention_forward_simt_kernel<T, TO><<<blocks, kAttWarps * 32, kAttWarps * hd * sizeof(float), s>>>(qkv, out, lse, B, seq,
                                                                                                    H, KV, hd, scale);
 }
-template void attention_forward_simt<float>(const float*, float*, float*, int, int, int, int, int, float,
-                                            cudaStream_t);
-template void attention_forward_simt<bf16>(const bf16*, bf16*, float*, int, int, int, int, int, float, cudaStream_t);
+template void attention_forward_simt<float, float>(const float*, float*, float*, int, int, int, int, int, float,
+                                                   cudaStream_t);
+template void attention_forward_simt<bf16, bf16>(const bf16*, bf16*, float*, int, int, int, int, int, float,
+                                                 cudaStream_t);
+template void attention_forward_simt<float, bf16>(const float*, bf16*, float*, int, int, int, int, int, float,
+                                                  cudaStream_t);
 
 // Backward: one warp per query row.  Dynamic smem per warp: 2*hd (q, dO) + 2*seq (scores, dP) floats.
 // dq/dk/dv accumulate into a zero-initialised fp32 [M, (H+2KV)*hd] buffer with atomics.
-template <typename T>
-__global__ void attention_backward_simt_kernel(const T* __restrict__ qkv, const T* __restrict__ d_out,
+template <typename T, typename TD>
+__global__ void attention_backward_simt_kernel(const T* __restrict__ qkv, const TD* __restrict__ d_out,
                                                float* __restrict__ dqkv, int B, int seq, int H, int KV, int hd,
                                                float scale) {
   extern __shared__ float s_mem[];
@@ -109,10 +112,10 @@ __global__ void attention_backward_simt_kernel(const T* __restrict__ qkv, const 
   float* sc = base + 2 * hd;
   float* dP = sc + seq;
   const T* qp = qkv + (row0 + t) * ld + (size_t)h * hd;
-  const T* dop = d_out + (row0 + t) * (size_t)(H * hd) + (size_t)h * hd;
+  const TD* dop = d_out + (row0 + t) * (size_t)(H * hd) + (size_t)h * hd;
   for (int d = lane; d < hd; d += 32) {
     q[d] = to_f<T>(qp[d]);
-    dO[d] = to_f<T>(dop[d]);
+    dO[d] = to_f<TD>(dop[d]);
   }
   __syncwarp();
   const T* kbase = qkv + row0 * ld + (size_t)(H + kvh) * hd;
@@ -172,25 +175,27 @@ __global__ void attention_backward_simt_kernel(const T* __restrict__ qkv, const 
   }
 }
 
-template <typename T>
-void attention_backward_simt(const T* qkv, const T* d_out, float* dqkv_f32, int B, int seq, int H, int KV, int hd,
+template <typename T, typename TD>
+void attention_backward_simt(const T* qkv, const TD* d_out, float* dqkv_f32, int B, int seq, int H, int KV, int hd,
                              float scale, cudaStream_t s) {
   const long long total = (long long)B * H * seq;
   if (total <= 0) return;
   const unsigned blocks = (unsigned)((total + kAttWarps - 1) / kAttWarps);
   const size_t smem = sizeof(float) * (size_t)kAttWarps * (2 * hd + 2 * seq);
-  static bool attr_done[2] = {false, false};
-  const int ti = sizeof(T) == 4 ? 0 : 1;
-  if (!attr_done[ti] && smem > 48 * 1024) {
-    cudaFuncSetAttribute(attention_backward_simt_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    attr_done[ti] = true;
+  static bool attr_done = false;  // one flag per template instantiation
+  if (!attr_done && smem > 48 * 1024) {
+    cudaFuncSetAttribute(attention_backward_simt_kernel<T, TD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         200 * 1024);
+    attr_done = true;
   }
-  attention_backward_simt_kernel<T><<<blocks, kAttWarps * 32, smem, s>>>(qkv, d_out, dqkv_f32, B, seq, H, KV, hd,
+  attention_backward_simt_kernel<T, TD><<<blocks, kAttWarps * 32, smem, s>>>(qkv, d_out, dqkv_f32, B, seq, H, KV, hd,
                                                                          scale);
 }
-template void attention_backward_simt<float>(const float*, const float*, float*, int, int, int, int, int, float,
-                                             cudaStream_t);
-template void attention_backward_simt<bf16>(const bf16*, const bf16*, float*, int, int, int, int, int, float,
-                                            cudaStream_t);
+template void attention_backward_simt<float, float>(const float*, const float*, float*, int, int, int, int, int, float,
+                                                    cudaStream_t);
+template void attention_backward_simt<bf16, bf16>(const bf16*, const bf16*, float*, int, int, int, int, int, float,
+                                                  cudaStream_t);
+template void attention_backward_simt<float, bf16>(const float*, const bf16*, float*, int, int, int, int, int, float,
+                                                   cudaStream_t);
 
 }  // namespace ane

@@ -23,8 +23,8 @@ enum DeviceStatus : int {
   DEV_BAD_INDEX = 110,
 };
 
-// ~2 s at 2 GHz. A healthy pipeline stage completes in microseconds.
-static constexpr long long kWaitBudgetCycles = 4000000000LL;
+// ~0.5 s at 2 GHz. A healthy pipeline stage completes in microseconds.
+static constexpr long long kWaitBudgetCycles = 1000000000LL;
 
 #if defined(__CUDACC__)
 

@@ -39,8 +39,8 @@ template <typename T>
 struct Act {  // saved activations of one layer (ane/train_full.go:12-37)
   float* x2 = nullptr;
   T* xn = nullptr;
-  T* qkv = nullptr;
-  T* qkpre = nullptr;
+  void* qkv = nullptr;    // packed q|k|v: fp32 when the engine keeps attention operands in fp32, else T
+  void* qkpre = nullptr;  // rotated pre-norm q|k (reference architecture), same type as qkv
   T* att = nullptr;
   T* x2n = nullptr;
   T* h13 = nullptr;
@@ -125,6 +125,10 @@ class EngineT final : public EngineBase {
   int import_tensor(uint32_t id, uint32_t layer, uint32_t which, const float* buf, uint64_t n) override;
   int export_tensor(uint32_t id, uint32_t layer, uint32_t which, float* buf, uint64_t n) override;
   int64_t get_tap(uint32_t tap, uint32_t layer, float* buf, uint64_t cap) override;
+  int profile_gemm(int enable) override;
+  int profile_read(double* gemm_ms, double* gemm_flops, uint64_t* gemm_launches) override;
+  int timer_begin() override;
+  int timer_end(float* ms) override;
 
  private:
   static constexpr bool kIsF32 = sizeof(T) == 4;
@@ -154,8 +158,19 @@ class EngineT final : public EngineBase {
   }
   int gemm(const GemmDesc& d) {
     int rc;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (profiling_) {
+      cudaEventCreate(&e0);
+      cudaEventCreate(&e1);
+      cudaEventRecord(e0, stream_);
+    }
     if constexpr (kIsF32) rc = gemm_f32(d, stream_);
     else rc = gemm_bf16(d, d_status_, stream_);
+    if (profiling_) {
+      cudaEventRecord(e1, stream_);
+      prof_events_.push_back({e0, e1});
+      prof_flops_ += 2.0 * (double)d.M * (double)d.N * (double)d.K;
+    }
     if (rc != 0) return fail(ANE_ERR_KERNEL, gemm_last_error());
     return 0;
   }
@@ -190,6 +205,9 @@ class EngineT final : public EngineBase {
   int D_ = 0, Hd_ = 0, L_ = 0, H_ = 0, KV_ = 0, hd_ = 0, V_ = 0, S_ = 0, B_ = 0, M_ = 0;
   int QD_ = 0, KVD_ = 0, QKVD_ = 0, N13_ = 0;
   bool isN_ = false, quirks_ = false;
+  // The reference architecture's backward recomputes attention with unscaled scores
+  // (ane/train_full.go:268-269), which amplifies operand rounding; its q/k/v stay in fp32.
+  bool qkv_f32_ = false;
   float lr_ = 0, embed_lr_ = 0, scalar_lr_ = 0, lambda_lr_ = 0;
   int ce_rows_ = 0;
   // ---- parameters
@@ -234,6 +252,10 @@ class EngineT final : public EngineBase {
   cudaEvent_t ev0_ = nullptr, ev1_ = nullptr, ev_adam0_ = nullptr, ev_adam1_ = nullptr;
   DataParallel dp_;
   std::vector<void*> allocs_;
+  bool profiling_ = false;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_events_;
+  double prof_flops_ = 0.0;
+  cudaEvent_t ev_t0_ = nullptr, ev_t1_ = nullptr;
 };
 
 template <typename T>
@@ -249,7 +271,8 @@ void EngineT<T>::destroy() {
   h_in_ = h_tgt_ = nullptr;
   h_pos_ = nullptr;
   h_loss_ = nullptr;
-  for (cudaEvent_t* e : {&ev0_, &ev1_, &ev_adam0_, &ev_adam1_})
+  profile_gemm(0);
+  for (cudaEvent_t* e : {&ev0_, &ev1_, &ev_adam0_, &ev_adam1_, &ev_t0_, &ev_t1_})
     if (*e) {
       cudaEventDestroy(*e);
       *e = nullptr;
@@ -365,10 +388,19 @@ int EngineT<T>::alloc_buffers() {
   acts_.assign(L_, Act<T>());
   for (int l = 0; l < L_; ++l) {
     Act<T>& a = acts_[l];
-    A(a.x2, MD); A(a.xn, MD); A(a.qkv, (size_t)M_ * QKVD_); A(a.att, (size_t)M_ * QD_); A(a.x2n, MD);
+    A(a.x2, MD); A(a.xn, MD); A(a.att, (size_t)M_ * QD_); A(a.x2n, MD);
+    {
+      uint8_t* raw = nullptr;
+      A(raw, (size_t)M_ * QKVD_ * (qkv_f32_ ? 4 : sizeof(T)));
+      a.qkv = raw;
+    }
     A(a.h13, (size_t)M_ * N13_); A(a.gate, (size_t)M_ * Hd_);
     A(a.rstd1, M_); A(a.rstd2, M_); A(a.lse, (size_t)B_ * H_ * S_);
-    if (isN_) A(a.qkpre, (size_t)M_ * (QD_ + KVD_));
+    if (isN_) {
+      uint8_t* raw = nullptr;
+      A(raw, (size_t)M_ * (QD_ + KVD_) * (qkv_f32_ ? 4 : sizeof(T)));
+      a.qkpre = raw;
+    }
     if (is_ve_layer(l)) A(a.ve_act, (size_t)M_ * H_);
     if (o_.debug_taps) {
       A(a.t_dout, MD); A(a.t_dx2, MD); A(a.t_dqkv, (size_t)M_ * QKVD_); A(a.t_dh13, (size_t)M_ * N13_);
@@ -425,6 +457,7 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
   if (o_.world_size <= 0) o_.world_size = 1;
   isN_ = o_.arch == ANE_ARCH_REFERENCE;
   quirks_ = isN_ && o_.quirks != 0;
+  qkv_f32_ = kIsF32 || isN_;
   if (o_.rope_theta <= 0) o_.rope_theta = isN_ ? 100000.f : 10000.f;
   D_ = o_.dim; Hd_ = o_.hidden; L_ = o_.n_layers; H_ = o_.n_heads; KV_ = o_.n_kv_heads; V_ = o_.vocab; S_ = o_.seq;
   B_ = o_.batch;
@@ -554,19 +587,25 @@ int EngineT<T>::forward(const uint16_t* d_tok, int B, bool training) {
       GemmDesc g;
       g.A = a.xn; g.B = wop(s_qkv_[l].off); g.C = a.qkv;
       g.M = M; g.N = QKVD_; g.K = D_; g.lda = D_; g.ldb = D_; g.ldc = QKVD_;
-      g.out = kIsF32 ? GEMM_OUT_F32 : GEMM_OUT_BF16;
+      g.out = qkv_f32_ ? GEMM_OUT_F32 : GEMM_OUT_BF16;
       count_launch();
       if ((rc = gemm(g)) != 0) return rc;
     }
     count_launch();
-    rope_qknorm_forward<T>(a.qkv, a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_, stream_);
-    if (is_ve_layer(l)) {
+    if (qkv_f32_)
+      rope_qknorm_forward<float>((float*)a.qkv, (float*)a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_, stream_);
+    else
+      rope_qknorm_forward<T>((T*)a.qkv, (T*)a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_, stream_);
+    if (is_ve_layer(l)) {  // reference architecture only, so qkv is fp32 here
       count_launch();
-      ve_forward<T>(a.qkv, xs_[l], d_tok, P_ + s_ve_embed_[l].off, P_ + s_ve_gate_[l].off, a.ve_act, M, D_, H_, KV_, hd_,
-                    V_, stream_);
+      ve_forward<float>((float*)a.qkv, xs_[l], d_tok, P_ + s_ve_embed_[l].off, P_ + s_ve_gate_[l].off, a.ve_act, M, D_,
+                        H_, KV_, hd_, V_, stream_);
     }
     count_launch();
-    attention_forward_simt<T>(a.qkv, a.att, a.lse, B, S_, H_, KV_, hd_, att_scale, stream_);
+    if (qkv_f32_)
+      attention_forward_simt<float, T>((const float*)a.qkv, a.att, a.lse, B, S_, H_, KV_, hd_, att_scale, stream_);
+    else
+      attention_forward_simt<T, T>((const T*)a.qkv, a.att, a.lse, B, S_, H_, KV_, hd_, att_scale, stream_);
     {
       GemmDesc g;  // x2 = rl*x + Wo*att (+ xl*x0)   ane/train_full.go:414-426
       g.A = a.att; g.B = wop(s_wo_[l].off); g.C = a.x2;
@@ -740,15 +779,18 @@ int EngineT<T>::backward_layers(int B) {
     }
     cudaMemsetAsync(dqkv_f32_, 0, sizeof(float) * (size_t)M * QKVD_, stream_);
     count_launch();
-    attention_backward_simt<T>(a.qkv, datt_, dqkv_f32_, B, S_, H_, KV_, hd_, att_scale_bwd, stream_);
+    if (qkv_f32_)
+      attention_backward_simt<float, T>((const float*)a.qkv, datt_, dqkv_f32_, B, S_, H_, KV_, hd_, att_scale_bwd, stream_);
+    else
+      attention_backward_simt<T, T>((const T*)a.qkv, datt_, dqkv_f32_, B, S_, H_, KV_, hd_, att_scale_bwd, stream_);
+    // QK-norm / rotation backward in fp32, then one rounding to the GEMM operand type.
+    count_launch();
+    rope_qknorm_backward<float>(dqkv_f32_, (const float*)a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_,
+                                quirks_, quirks_, stream_);
     T* dqkv = tview(dqkv_f32_, dqkv_);
     cast_to_t(dqkv_f32_, dqkv_, (uint64_t)M * QKVD_);
-    count_launch();
-    rope_qknorm_backward<T>(dqkv, a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_, quirks_, quirks_, stream_);
-    if (o_.debug_taps) {
-      count_launch();
-      to_f32_kernel<T><<<ew_grid((uint64_t)M * QKVD_), 256, 0, stream_>>>(dqkv, a.t_dqkv, (uint64_t)M * QKVD_);
-    }
+    if (o_.debug_taps)
+      cudaMemcpyAsync(a.t_dqkv, dqkv_f32_, sizeof(float) * (size_t)M * QKVD_, cudaMemcpyDeviceToDevice, stream_);
     {
       GemmDesc g;  // dxn = dq*Wq + dk*Wk + dv*Wv   (ane/train_full.go:650-665)
       g.A = dqkv; g.B = wop(s_qkv_[l].off); g.C = dxn_;
@@ -763,8 +805,8 @@ int EngineT<T>::backward_layers(int B) {
                         isN_ ? nullptr : G_ + s_rms_att_[l].off, M, D_, stream_);
     if (is_ve_layer(l)) {
       count_launch();
-      ve_backward<T>(dqkv, xs_[l], d_in_, P_ + s_ve_embed_[l].off, P_ + s_ve_gate_[l].off, a.ve_act,
-                     G_ + s_ve_embed_[l].off, G_ + s_ve_gate_[l].off, dprev, M, D_, H_, KV_, hd_, V_, stream_);
+      ve_backward<float>(dqkv_f32_, xs_[l], d_in_, P_ + s_ve_embed_[l].off, P_ + s_ve_gate_[l].off, a.ve_act,
+                         G_ + s_ve_embed_[l].off, G_ + s_ve_gate_[l].off, dprev, M, D_, H_, KV_, hd_, V_, stream_);
     }
     {
       GemmDesc g;  // dWo += dx2^T * att
@@ -1158,17 +1200,17 @@ int64_t EngineT<T>::get_tap(uint32_t tap, uint32_t layer, float* buf, uint64_t c
     switch (tap) {
       case ANE_TAP_X: src = xs_[layer]; ld = D_; ncols = D_; break;
       case ANE_TAP_XNORM: src = a.xn; src_f32 = tf; ld = D_; ncols = D_; break;
-      case ANE_TAP_Q: src = a.qkv; src_f32 = tf; ld = QKVD_; ncols = QD_; break;
-      case ANE_TAP_K: src = a.qkv; src_f32 = tf; ld = QKVD_; col0 = QD_; ncols = KVD_; break;
-      case ANE_TAP_V: src = a.qkv; src_f32 = tf; ld = QKVD_; col0 = QD_ + KVD_; ncols = KVD_; break;
+      case ANE_TAP_Q: src = a.qkv; src_f32 = qkv_f32_; ld = QKVD_; ncols = QD_; break;
+      case ANE_TAP_K: src = a.qkv; src_f32 = qkv_f32_; ld = QKVD_; col0 = QD_; ncols = KVD_; break;
+      case ANE_TAP_V: src = a.qkv; src_f32 = qkv_f32_; ld = QKVD_; col0 = QD_ + KVD_; ncols = KVD_; break;
       case ANE_TAP_ATT: src = a.att; src_f32 = tf; ld = QD_; ncols = QD_; break;
       case ANE_TAP_X2: src = a.x2; ld = D_; ncols = D_; break;
       case ANE_TAP_X2NORM: src = a.x2n; src_f32 = tf; ld = D_; ncols = D_; break;
       case ANE_TAP_H1: src = a.h13; src_f32 = tf; ld = N13_; ncols = Hd_; break;
       case ANE_TAP_H3: if (!isN_) { src = a.h13; src_f32 = tf; ld = N13_; col0 = Hd_; ncols = Hd_; } break;
       case ANE_TAP_GATE: src = a.gate; src_f32 = tf; ld = Hd_; ncols = Hd_; break;
-      case ANE_TAP_QPRE: if (isN_) { src = a.qkpre; src_f32 = tf; ld = QD_ + KVD_; ncols = QD_; } break;
-      case ANE_TAP_KPRE: if (isN_) { src = a.qkpre; src_f32 = tf; ld = QD_ + KVD_; col0 = QD_; ncols = KVD_; } break;
+      case ANE_TAP_QPRE: if (isN_) { src = a.qkpre; src_f32 = qkv_f32_; ld = QD_ + KVD_; ncols = QD_; } break;
+      case ANE_TAP_KPRE: if (isN_) { src = a.qkpre; src_f32 = qkv_f32_; ld = QD_ + KVD_; col0 = QD_; ncols = KVD_; } break;
       case ANE_TAP_DOUT: src = a.t_dout; ld = D_; ncols = D_; break;
       case ANE_TAP_DX2: src = a.t_dx2; ld = D_; ncols = D_; break;
       case ANE_TAP_DH1: src = a.t_dh13; ld = N13_; ncols = Hd_; break;
@@ -1206,6 +1248,56 @@ int64_t EngineT<T>::get_tap(uint32_t tap, uint32_t layer, float* buf, uint64_t c
   if (cuda_check(cudaMemcpyAsync(buf, tap_tmp_, sizeof(float) * n, cudaMemcpyDeviceToHost, stream_), "tap") != 0) return -1;
   if (cuda_check(cudaStreamSynchronize(stream_), "tap sync") != 0) return -1;
   return (int64_t)n;
+}
+
+template <typename T>
+int EngineT<T>::profile_gemm(int enable) {
+  cudaStreamSynchronize(stream_);
+  for (auto& pr : prof_events_) {
+    cudaEventDestroy(pr.first);
+    cudaEventDestroy(pr.second);
+  }
+  prof_events_.clear();
+  prof_flops_ = 0.0;
+  profiling_ = enable != 0;
+  return 0;
+}
+
+template <typename T>
+int EngineT<T>::profile_read(double* gemm_ms, double* gemm_flops, uint64_t* gemm_launches) {
+  int rc = cuda_check(cudaStreamSynchronize(stream_), "profile sync");
+  if (rc) return rc;
+  double total = 0.0;
+  for (auto& pr : prof_events_) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, pr.first, pr.second) == cudaSuccess) total += ms;
+  }
+  if (gemm_ms) *gemm_ms = total;
+  if (gemm_flops) *gemm_flops = prof_flops_;
+  if (gemm_launches) *gemm_launches = prof_events_.size();
+  return 0;
+}
+
+template <typename T>
+int EngineT<T>::timer_begin() {
+  if (!ev_t0_) {
+    int rc = cuda_check(cudaEventCreate(&ev_t0_), "cudaEventCreate");
+    if (rc) return rc;
+    if ((rc = cuda_check(cudaEventCreate(&ev_t1_), "cudaEventCreate")) != 0) return rc;
+  }
+  return cuda_check(cudaEventRecord(ev_t0_, stream_), "timer begin");
+}
+
+template <typename T>
+int EngineT<T>::timer_end(float* ms) {
+  if (!ev_t0_) return fail(ANE_ERR_STATE, "storiesane timer: end without begin");
+  int rc = cuda_check(cudaEventRecord(ev_t1_, stream_), "timer end");
+  if (rc) return rc;
+  if ((rc = cuda_check(cudaEventSynchronize(ev_t1_), "timer sync")) != 0) return rc;
+  float v = 0.f;
+  if ((rc = cuda_check(cudaEventElapsedTime(&v, ev_t0_, ev_t1_), "timer elapsed")) != 0) return rc;
+  if (ms) *ms = v;
+  return 0;
 }
 
 }  // namespace

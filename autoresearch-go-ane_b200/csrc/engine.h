@@ -27,6 +27,12 @@ class EngineBase {
   virtual int import_tensor(uint32_t id, uint32_t layer, uint32_t which, const float* buf, uint64_t n) = 0;
   virtual int export_tensor(uint32_t id, uint32_t layer, uint32_t which, float* buf, uint64_t n) = 0;
   virtual int64_t get_tap(uint32_t tap, uint32_t layer, float* buf, uint64_t cap) = 0;
+  // Per-GEMM device timing (CUDA events around every GEMM launch) for roofline reports.
+  virtual int profile_gemm(int enable) = 0;
+  virtual int profile_read(double* gemm_ms, double* gemm_flops, uint64_t* gemm_launches) = 0;
+  // CUDA-event timer on the engine's own stream.
+  virtual int timer_begin() = 0;
+  virtual int timer_end(float* ms) = 0;
 
   const std::string& last_error() const { return err_; }
   uint64_t launches() const { return launches_; }

@@ -10,6 +10,11 @@ struct ane_engine {
   ane::EngineBase* impl = nullptr;
 };
 
+// The Go and Python bindings mirror these layouts field by field.
+static_assert(sizeof(ane_options) == 168, "ane_options layout changed: update the bindings");
+static_assert(sizeof(ane_step_result) == 112, "ane_step_result layout changed: update the bindings");
+static_assert(sizeof(ane_state) == 56, "ane_state layout changed: update the bindings");
+
 static thread_local std::string g_api_err;
 
 extern "C" {
@@ -137,6 +142,22 @@ int32_t ane_export_tensor(ane_engine* e, uint32_t tensor_id, uint32_t layer, uin
 int64_t ane_get_tap(ane_engine* e, uint32_t tap_id, uint32_t layer, float* buf, uint64_t cap) {
   if (!e || !e->impl || !buf) return -1;
   return e->impl->get_tap(tap_id, layer, buf, cap);
+}
+int32_t ane_profile_gemm(ane_engine* e, int32_t enable) {
+  ENGINE_OR_FAIL(e, "profile");
+  return e->impl->profile_gemm(enable);
+}
+int32_t ane_profile_read(ane_engine* e, double* gemm_ms, double* gemm_flops, uint64_t* gemm_launches) {
+  ENGINE_OR_FAIL(e, "profile");
+  return e->impl->profile_read(gemm_ms, gemm_flops, gemm_launches);
+}
+int32_t ane_engine_timer_begin(ane_engine* e) {
+  ENGINE_OR_FAIL(e, "timer");
+  return e->impl->timer_begin();
+}
+int32_t ane_engine_timer_end(ane_engine* e, float* out_ms) {
+  ENGINE_OR_FAIL(e, "timer");
+  return e->impl->timer_end(out_ms);
 }
 uint64_t ane_launch_count(ane_engine* e) {
   if (!e || !e->impl) return 0;

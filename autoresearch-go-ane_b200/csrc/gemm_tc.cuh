@@ -144,6 +144,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  // A pipeline wait that gave up earlier in this stream poisons the status word: later launches
+  // return at once instead of each running into its own time-out.
+  if (status != nullptr && *reinterpret_cast<volatile int*>(status) != DEV_OK) return;
+
   const int tiles_m = (M + BM - 1) / BM;
   const int tiles_n = (N + BN - 1) / BN;
   const int kblocks = (K + BK - 1) / BK;

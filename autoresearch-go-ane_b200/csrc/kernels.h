@@ -62,12 +62,12 @@ void swiglu_backward(const T* dgate, const T* h13, T* dh13, int M, int Hd, cudaS
 //   q,k,v live in one packed buffer [M, ld] at column offsets 0, H*hd, (H+KV)*hd.
 //   out [M, H*hd]; lse [B*H*seq] = log-sum-exp of the scaled scores.
 // Forward: ane/common.go:61-89.  Backward: ane/train_full.go:261-316 with `scale` explicit.
-template <typename T>
-void attention_forward_simt(const T* qkv, T* out, float* lse, int B, int seq, int H, int KV, int hd, float scale,
+template <typename T, typename TO>
+void attention_forward_simt(const T* qkv, TO* out, float* lse, int B, int seq, int H, int KV, int hd, float scale,
                             cudaStream_t s);
 // dq,dk,dv accumulate into fp32 [M, (H+2KV)*hd] (must be zeroed by the caller).
-template <typename T>
-void attention_backward_simt(const T* qkv, const T* d_out, float* dqkv_f32, int B, int seq, int H, int KV, int hd,
+template <typename T, typename TD>
+void attention_backward_simt(const T* qkv, const TD* d_out, float* dqkv_f32, int B, int seq, int H, int KV, int hd,
                              float scale, cudaStream_t s);
 
 // Cross-entropy over token-major logits [rows, V] (fp32), ane/stories/cpu.go:212-292 with the

@@ -1,0 +1,299 @@
+#!/usr/bin/env python
+"""Benchmark of the training-step hot path.
+
+  python bench.py --gpus N --steps K --warmup W [--impl ours|reference]
+
+One "step" = forward + backward + AdamW over one micro-batch of the 110M Llama2-style config
+(dim 768, 12 layers, 12 heads, SwiGLU hidden 2048, vocab 32000, seq 256, micro-batch 32 per GPU,
+bf16 GEMM operands, fp32 master weights and optimizer).  Synthetic data: seeded Zipf(1.1) token
+stream and N(0, 0.02) weights stand in for TinyStories and the stories110M checkpoint.
+
+`value` is tokens/s with the token stream resident in HBM (Engine.Step samples windows on the
+device); `e2e` is the same metric through ane_step_tokens with host batches copied H2D and the
+loss read back every step.  `--impl reference` times the CPU restatement of the reference's Go
+step (the reference itself cannot be built here) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "autoresearch-go-ane_b200"))
+
+import numpy as np  # noqa: E402
+
+WORKLOAD = dict(dim=768, hidden=2048, n_layers=12, n_heads=12, n_kv_heads=12, vocab=32000, seq=256)
+MICRO_BATCH = 32
+N_STREAM_TOKENS = 1 << 22
+# Algorithmic FLOPs per trained token: 6*N_mm + 3.5*(2*L*T*D), N_mm = matmul parameters incl. classifier.
+N_MM = 12 * (4 * 768 * 768 + 3 * 768 * 2048) + 32000 * 768
+TRAIN_FLOPS_PER_TOKEN = 6 * N_MM + 3.5 * (2 * 12 * 256 * 768)
+
+
+def zipf_tokens(n, vocab, seed, s=1.1):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    p = np.arange(1, vocab + 1, dtype=np.float64) ** (-s)
+    cdf = np.cumsum(p / p.sum())
+    return np.minimum(np.searchsorted(cdf, rng.random(n), side="right"), vocab - 1).astype(np.uint16)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), d.get("bf16_tflops_sustained", 1400.0), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, device: int):
+        self.device = device
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def init_weights(engine, ane, seed):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    L, D, Hd, V = WORKLOAD["n_layers"], WORKLOAD["dim"], WORKLOAD["hidden"], WORKLOAD["vocab"]
+    engine.import_tensor(ane.T_EMBED, 0, (0.02 * rng.standard_normal(V * D)).astype(np.float32))
+    for layer in range(L):
+        for tid, n in ((ane.T_WQ, D * D), (ane.T_WK, D * D), (ane.T_WV, D * D), (ane.T_WO, D * D), (ane.T_W1, Hd * D),
+                       (ane.T_W2, D * Hd), (ane.T_W3, Hd * D)):
+            engine.import_tensor(tid, layer, (0.02 * rng.standard_normal(n)).astype(np.float32))
+
+
+def run_ours(args):
+    import ane
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    dp_id = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
+        obj = [ane.dp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(obj, src=0)
+        dp_id = obj[0]
+
+    def barrier():
+        if dist is not None:
+            import torch
+            dist.barrier()
+            torch.cuda.synchronize()
+        ane._ffi.lib.ane_dev_sync()
+
+    def max_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        import torch
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    tokens = zipf_tokens(N_STREAM_TOKENS, WORKLOAD["vocab"], seed=0)
+    opts = ane.Options(tokens=tokens, batch=MICRO_BATCH, arch=ane.ARCH_LLAMA, quirks=0, compute_dtype=ane.DTYPE_BF16,
+                       accum_steps=1, lr=3e-4, adam_beta1=0.9, adam_beta2=0.95, weight_decay=0.1, grad_clip=1.0,
+                       seed=42, device=local_rank, rank=rank, world_size=world, dp_id=dp_id, **WORKLOAD)
+    e = ane.open(opts)
+    init_weights(e, ane, seed=1234)
+    T = WORKLOAD["seq"]
+    tokens_per_step = MICRO_BATCH * T * world
+
+    # ---- device-resident leg ("value")
+    for _ in range(args.warmup):
+        r = e.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = e.launch_count()
+    e.timer_begin()
+    t0 = time.perf_counter()
+    last = None
+    for _ in range(args.steps):
+        last = e.step()
+    ms = e.timer_end()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    barrier()
+    launches = e.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    ms = max_over_ranks(ms)
+    ms_per_step = ms / args.steps
+    value = tokens_per_step / (ms_per_step * 1e-3)
+
+    # ---- end-to-end leg: host batches in, loss out, every step
+    rng = np.random.default_rng(7 + rank)
+    pos = rng.integers(0, tokens.size - T - 1, size=(args.steps + 1, MICRO_BATCH))
+    batches = []
+    for s in range(args.steps + 1):
+        inp = np.stack([tokens[p:p + T] for p in pos[s]])
+        tgt = np.stack([tokens[p + 1:p + 1 + T] for p in pos[s]])
+        batches.append((inp, tgt))
+    e.step_tokens(*batches[-1])
+    barrier()
+    t0 = time.perf_counter()
+    for s in range(args.steps):
+        e.step_tokens(*batches[s])
+    ane._ffi.lib.ane_dev_sync()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+    e2e_value = tokens_per_step * args.steps / e2e_s
+    h2d = 2 * MICRO_BATCH * T * 2
+    d2h = 8
+
+    # ---- dominant-kernel roofline: every GEMM launch timed with CUDA events over one profiled step
+    e.profile_gemm(True)
+    e.step()
+    gemm_ms, gemm_flops, gemm_launches = e.profile_read()
+    e.profile_gemm(False)
+    hbm, tf_burst, tf_sust, src = measured_peaks()
+    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    roofline = {"bound": "tensor", "achieved": round(achieved, 1), "peak": tf_sust, "unit": "TFLOP/s",
+                "frac": round(achieved / tf_sust, 4), "traffic": None, "peak_source": f"bf16_tflops_sustained ({src})",
+                "kernel": "gemm_tc_kernel (tcgen05 GEMM, all shapes of one step)", "gemm_launches_per_step": gemm_launches,
+                "gemm_ms_per_step": round(gemm_ms, 3),
+                "step_frac_of_burst_peak": round(TRAIN_FLOPS_PER_TOKEN * tokens_per_step / world / (ms_per_step * 1e-3) / 1e12 / tf_burst, 4)}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_baseline = cpu_reference_leg(steps=1, warmup=0)
+    e.close()
+    if rank == 0:
+        line = {
+            "metric": "train tok/s (110M, seq 256)", "value": round(value, 1), "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "110M Llama2-style train step: dim 768, 12 layers, 12 heads, SwiGLU 2048, vocab 32000, "
+                                   "seq 256, micro-batch 32 per GPU; Zipf(1.1) tokens, N(0,0.02) weights",
+                       "global_batch": MICRO_BATCH * world, "seq_len": T, "parallelism": f"dp{world}",
+                       "l2_policy": "inputs larger than L2 (2.7 GB of activations per step)"},
+            "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "loss": round(float(last.loss), 4),
+            "wall_ms_per_step": round(wall_ms / args.steps, 4),
+        }
+        if cpu_baseline is not None:
+            line["cpu_baseline"] = cpu_baseline
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def cpu_reference_leg(steps: int, warmup: int):
+    """Times the CPU restatement of the reference step (oracle port) on the host cores: one sequence
+    of 256 tokens through forward + backward + gradient accumulation per sample."""
+    from oracle import oracle as O
+
+    m = O.Model(dim=768, hidden=2048, heads=12, kv_heads=12, layers=12, vocab=32000, seq=256, arch=O.ARCH_L, quirks=0,
+                accum_steps=1 << 30, lr=3e-4, beta1=0.9, beta2=0.95, weight_decay=0.1, grad_clip=1.0)
+    O.init_weights(m, 1234)
+    toks = zipf_tokens(4096, 32000, seed=0)
+    for _ in range(warmup):
+        m.accumulate(toks[:256].copy(), toks[1:257].copy())
+    t0 = time.perf_counter()
+    for s in range(steps):
+        o = 257 * (s % 8)
+        m.accumulate(toks[o:o + 256].copy(), toks[o + 1:o + 257].copy())
+    dt = time.perf_counter() - t0
+    cores = int(O.lib().orc_num_threads())
+    m.close()
+    return {"value": round(256 * steps / dt, 2), "unit": "tok/s", "cores": cores, "kind": "port",
+            "sample": f"{steps} sequence(s) of 256 tokens (1/32 of one GPU micro-batch), fwd+bwd+grad accumulation, "
+                      f"{dt:.1f} s of CPU work"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 4))
+    base = cpu_reference_leg(steps=steps, warmup=1 if args.warmup > 0 else 0)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    line = {
+        "impl": "reference", "metric": "train tok/s (110M, seq 256)", "value": base["value"], "unit": "tok/s",
+        "n_gpus": world, "steps": steps, "warmup": 1 if args.warmup > 0 else 0,
+        "ms_per_step": round(256 / base["value"] * 1e3, 2), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "110M Llama2-style train step on host cores (CPU restatement of the reference's Go step; "
+                               "each step = 1 sequence of 256 tokens)", "global_batch": 1, "seq_len": 256,
+                   "parallelism": "cpu"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -196,6 +196,14 @@ enum {
 };
 int64_t ane_get_tap(ane_engine* e, uint32_t tap_id, uint32_t layer, float* buf, uint64_t cap); /* returns floats written */
 
+/* Measurement seams (no counterpart in the reference, whose StepResult timers are host clocks,
+ * ane/metrics.go:13-43): CUDA-event timer on the engine's stream, and per-GEMM device time /
+ * algorithmic FLOPs accumulated while profiling is enabled. */
+int32_t ane_engine_timer_begin(ane_engine* e);
+int32_t ane_engine_timer_end(ane_engine* e, float* out_ms);
+int32_t ane_profile_gemm(ane_engine* e, int32_t enable);
+int32_t ane_profile_read(ane_engine* e, double* gemm_ms, double* gemm_flops, uint64_t* gemm_launches);
+
 /* Kernel launches issued by this library since the engine was opened (for measurement reports). */
 uint64_t ane_launch_count(ane_engine* e);
 

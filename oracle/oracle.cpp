@@ -23,13 +23,14 @@ namespace {
 typedef std::vector<float> vecf;
 
 int g_ref_threading = 0;
+int g_threads = 1;  // set by orc_set_num_threads; 1 until the host side picks a count
 
 // Loops the reference itself spreads over cores (parallelFor / parallelForCF /
 // compileParallel) are always parallel; the others only when not imitating the
 // reference's threading.
-#define PAR_REF _Pragma("omp parallel for schedule(static)")
-#define PAR_ALL _Pragma("omp parallel for schedule(static) if (!g_ref_threading)")
-#define PAR_DW _Pragma("omp parallel for schedule(static) num_threads(g_ref_threading ? std::min(4, omp_get_max_threads()) : omp_get_max_threads())")
+#define PAR_REF _Pragma("omp parallel for schedule(static) num_threads(g_threads)")
+#define PAR_ALL _Pragma("omp parallel for schedule(static) num_threads(g_ref_threading ? 1 : g_threads)")
+#define PAR_DW _Pragma("omp parallel for schedule(static) num_threads(g_ref_threading ? std::min(4, g_threads) : g_threads)")
 
 // ---------------------------------------------------------------------------------------------
 // Primitives
@@ -1306,6 +1307,7 @@ int32_t orc_argmax(const float* v, int32_t n) {
 }
 
 void orc_set_reference_threading(int32_t on) { g_ref_threading = on ? 1 : 0; }
-int32_t orc_num_threads(void) { return omp_get_max_threads(); }
+int32_t orc_num_threads(void) { return g_threads; }
+void orc_set_num_threads(int32_t n) { g_threads = n < 1 ? 1 : n; }
 
 }  // extern "C"

@@ -121,6 +121,7 @@ int32_t orc_argmax(const float* v, int32_t n);
  * arithmetic is independent across iterations. Arithmetic is identical either way. */
 void orc_set_reference_threading(int32_t on);
 int32_t orc_num_threads(void);
+void orc_set_num_threads(int32_t n);
 
 #ifdef __cplusplus
 }

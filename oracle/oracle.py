@@ -63,11 +63,40 @@ def build(force: bool = False) -> str:
 _lib = None
 
 
+def usable_cpus() -> int:
+    """CPUs this process may really use: the affinity mask capped by the cgroup CPU quota.  OpenMP
+    sizing from the raw core count oversubscribes a quota-limited container badly."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except Exception:
+        n = os.cpu_count() or 1
+    for path in ("/sys/fs/cgroup/cpu.max", "/sys/fs/cgroup/cpu/cpu.cfs_quota_us"):
+        try:
+            with open(path) as f:
+                parts = f.read().split()
+            if path.endswith("cpu.max"):
+                if parts[0] != "max":
+                    n = min(n, max(1, int(float(parts[0]) / float(parts[1]))))
+            else:
+                q = int(parts[0])
+                if q > 0:
+                    with open("/sys/fs/cgroup/cpu/cpu.cfs_period_us") as g:
+                        n = min(n, max(1, q // int(g.read().split()[0])))
+            break
+        except Exception:
+            continue
+    env = os.environ.get("ANE_ORACLE_THREADS")
+    if env:
+        n = max(1, int(env))
+    return max(1, min(n, 64))
+
+
 def lib():
     global _lib
     if _lib is not None:
         return _lib
     build()
+    os.environ.setdefault("OMP_WAIT_POLICY", "PASSIVE")
     L = ctypes.CDLL(_LIB_PATH)
     fp = POINTER(c_float)
     u16p = POINTER(c_uint16)
@@ -116,6 +145,8 @@ def lib():
     L.orc_argmax.argtypes = [fp, c_int32]
     L.orc_set_reference_threading.argtypes = [c_int32]
     L.orc_num_threads.restype = c_int32
+    L.orc_set_num_threads.argtypes = [c_int32]
+    L.orc_set_num_threads(usable_cpus())
     _lib = L
     return L
 

@@ -1,0 +1,113 @@
+"""tcgen05 GEMM (and the fp32 SIMT GEMM) against the oracle's naive loops, through the C ABI.
+Shapes cover the step's three operand layouts, ragged edges and split-K accumulation."""
+import ctypes
+
+import numpy as np
+import pytest
+
+import ane
+from ane import _ffi
+from oracle import oracle as O
+from parity_utils import rel_l2
+
+pytestmark = pytest.mark.gpu
+lib = _ffi.lib
+
+
+def _ck(rc):
+    assert rc == 0, lib.ane_ops_last_error().decode()
+
+
+def _up(a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    p = lib.ane_dev_malloc(a.nbytes)
+    _ck(lib.ane_dev_h2d(p, a.ctypes.data, a.nbytes))
+    return p
+
+
+def _up_bf16(a):
+    p = _up(a)
+    q = lib.ane_dev_malloc(a.size * 2)
+    _ck(lib.ane_op_cast_f32_to_bf16(p, q, a.size))
+    lib.ane_dev_free(p)
+    return q
+
+
+def _down(p, shape):
+    a = np.empty(shape, dtype=np.float32)
+    _ck(lib.ane_dev_d2h(a.ctypes.data, p, a.nbytes))
+    return a
+
+
+def _bf16_round(a):
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    return r.astype(np.uint32).view(np.float32).reshape(a.shape)
+
+
+def _fp(a):
+    return a.ctypes.data_as(ctypes.POINTER(ctypes.c_float))
+
+
+def _gemm(dtype, A_store, B_store, C_init, M, N, K, a_mn, b_mn, out_mode, split_k=0):
+    upf = _up_bf16 if dtype == ane.DTYPE_BF16 else _up
+    dA, dB, dC = upf(A_store), upf(B_store), _up(C_init)
+    g = _ffi.GemmArgs()
+    g.struct_size = ctypes.sizeof(_ffi.GemmArgs)
+    g.dtype = dtype
+    g.d_a, g.d_b, g.d_c = dA, dB, dC
+    g.m, g.n, g.k = M, N, K
+    g.lda, g.ldb, g.ldc = A_store.shape[1], B_store.shape[1], N
+    g.a_mn, g.b_mn, g.out_mode, g.alpha, g.split_k = a_mn, b_mn, out_mode, 1.0, split_k
+    _ck(lib.ane_op_gemm(ctypes.byref(g)))
+    _ck(lib.ane_dev_sync())
+    st = ctypes.c_int32(0)
+    _ck(lib.ane_ops_device_status(ctypes.byref(st)))
+    assert st.value == 0
+    out = _down(dC, (M, N))
+    for p in (dA, dB, dC):
+        lib.ane_dev_free(p)
+    return out
+
+
+@pytest.mark.parametrize("dtype", [ane.DTYPE_BF16, ane.DTYPE_F32])
+@pytest.mark.parametrize("oc,ic,seq", [(96, 64, 40), (256, 136, 300), (768, 256, 128)])
+def test_linear_forward_dx_dw_match_oracle(dtype, oc, ic, seq):
+    """linearCF / linearBackwardDXCF / accumLinearGradCF (ane/common.go:91, ane/train_full.go:213,242)."""
+    rng = np.random.default_rng(oc + seq)
+    rnd = _bf16_round if dtype == ane.DTYPE_BF16 else (lambda a: a)
+    W = rnd(rng.standard_normal((oc, ic)).astype(np.float32) * 0.1)
+    x_cf = rnd(rng.standard_normal((ic, seq)).astype(np.float32))          # reference layout [C][seq]
+    dy_cf = rnd(rng.standard_normal((oc, seq)).astype(np.float32))
+    tol = 2e-5
+    # forward: y[t,o] = x[t,:] . W[o,:]
+    want = np.empty((oc, seq), np.float32)
+    O.lib().orc_linear(_fp(want), _fp(W), _fp(x_cf), oc, ic, seq)
+    got = _gemm(dtype, np.ascontiguousarray(x_cf.T), W, np.zeros((seq, oc), np.float32), seq, oc, ic, 0, 0, 1)
+    assert rel_l2(got.T, want) < tol
+    # dx[t,i] = dy[t,:] . W[:,i]   (B stored [K=oc, N=ic])
+    want = np.empty((ic, seq), np.float32)
+    O.lib().orc_linear_dx(_fp(want), _fp(W), _fp(dy_cf), oc, ic, seq)
+    got = _gemm(dtype, np.ascontiguousarray(dy_cf.T), W, np.zeros((seq, ic), np.float32), seq, ic, oc, 0, 1, 1)
+    assert rel_l2(got.T, want) < tol
+    # dW[o,i] += sum_t dy[t,o] x[t,i]   (both operands stored [K=seq, .]); beta = 1
+    dw0 = rng.standard_normal((oc, ic)).astype(np.float32)
+    want = dw0.copy()
+    O.lib().orc_linear_dw(_fp(want), _fp(dy_cf), _fp(x_cf), oc, ic, seq)
+    for split in (1, 2):
+        got = _gemm(dtype, np.ascontiguousarray(dy_cf.T), np.ascontiguousarray(x_cf.T), dw0, oc, ic, seq, 1, 1, 2, split)
+        assert rel_l2(got, want) < tol
+
+
+def test_gemm_rejects_misaligned_pitch():
+    A = np.zeros((16, 20), np.float32)  # 20 bf16 = 40 bytes per row: not a 16-byte multiple
+    dA, dB, dC = _up_bf16(A), _up_bf16(A), _up(np.zeros((16, 16), np.float32))
+    g = _ffi.GemmArgs()
+    g.struct_size = ctypes.sizeof(_ffi.GemmArgs)
+    g.dtype = ane.DTYPE_BF16
+    g.d_a, g.d_b, g.d_c = dA, dB, dC
+    g.m, g.n, g.k, g.lda, g.ldb, g.ldc, g.out_mode, g.alpha = 16, 16, 20, 20, 20, 16, 1, 1.0
+    assert lib.ane_op_gemm(ctypes.byref(g)) != 0
+    assert b"16-byte" in lib.ane_ops_last_error()
+    for p in (dA, dB, dC):
+        lib.ane_dev_free(p)
