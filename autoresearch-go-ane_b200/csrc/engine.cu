@@ -208,6 +208,8 @@ class EngineT final : public EngineBase {
   // The reference architecture's backward recomputes attention with unscaled scores
   // (ane/train_full.go:268-269), which amplifies operand rounding; its q/k/v stay in fp32.
   bool qkv_f32_ = false;
+  bool att_tc_ = false;  // tensor-core attention kernels (bf16 operands, head_dim 64)
+  float* att_delta_ = nullptr;
   float lr_ = 0, embed_lr_ = 0, scalar_lr_ = 0, lambda_lr_ = 0;
   int ce_rows_ = 0;
   // ---- parameters
@@ -416,7 +418,7 @@ int EngineT<T>::alloc_buffers() {
     A(dcur_t_[0], MD); A(dcur_t_[1], MD); A(dx2_t_, MD); A(dqkv_, (size_t)M_ * QKVD_);
   }
   A(dgate_, (size_t)M_ * Hd_); A(dh13_, (size_t)M_ * N13_); A(datt_, (size_t)M_ * QD_);
-  A(xnf_, MD); A(rstdf_, M_);
+  A(xnf_, MD); A(rstdf_, M_); A(att_delta_, (size_t)B_ * H_ * S_);
   A(logits_, (size_t)ce_rows_ * V_); A(dlogits_, (size_t)ce_rows_ * V_);
   A(loss_rows_, M_); A(inv_valid_, B_); A(d_loss_, 4);
   A(rope_cos_, (size_t)S_ * (hd_ / 2)); A(rope_sin_, (size_t)S_ * (hd_ / 2));
@@ -475,6 +477,7 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
   M_ = B_ * S_;
   QD_ = H_ * hd_; KVD_ = KV_ * hd_; QKVD_ = QD_ + 2 * KVD_;
   N13_ = isN_ ? Hd_ : 2 * Hd_;
+  att_tc_ = !qkv_f32_ && attention_tc_supported(hd_);
   ce_rows_ = o_.ce_chunk_rows > 0 ? o_.ce_chunk_rows : 1024;
   if (ce_rows_ > M_) ce_rows_ = M_;
   ce_rows_ = std::max(ce_rows_, std::min(M_, S_));  // eval logits uses one sequence per chunk
@@ -602,10 +605,14 @@ int EngineT<T>::forward(const uint16_t* d_tok, int B, bool training) {
                         H_, KV_, hd_, V_, stream_);
     }
     count_launch();
-    if (qkv_f32_)
+    if (qkv_f32_) {
       attention_forward_simt<float, T>((const float*)a.qkv, a.att, a.lse, B, S_, H_, KV_, hd_, att_scale, stream_);
-    else
-      attention_forward_simt<T, T>((const T*)a.qkv, a.att, a.lse, B, S_, H_, KV_, hd_, att_scale, stream_);
+    } else if constexpr (!kIsF32) {
+      if (att_tc_)
+        attention_forward_tc((const bf16*)a.qkv, a.att, a.lse, B, S_, H_, KV_, att_scale, stream_);
+      else
+        attention_forward_simt<T, T>((const T*)a.qkv, a.att, a.lse, B, S_, H_, KV_, hd_, att_scale, stream_);
+    }
     {
       GemmDesc g;  // x2 = rl*x + Wo*att (+ xl*x0)   ane/train_full.go:414-426
       g.A = a.att; g.B = wop(s_wo_[l].off); g.C = a.x2;
@@ -777,12 +784,21 @@ int EngineT<T>::backward_layers(int B) {
       count_launch();
       if ((rc = gemm(g)) != 0) return rc;
     }
-    cudaMemsetAsync(dqkv_f32_, 0, sizeof(float) * (size_t)M * QKVD_, stream_);
-    count_launch();
-    if (qkv_f32_)
+    if (qkv_f32_) {
+      cudaMemsetAsync(dqkv_f32_, 0, sizeof(float) * (size_t)M * QKVD_, stream_);
+      count_launch();
       attention_backward_simt<float, T>((const float*)a.qkv, datt_, dqkv_f32_, B, S_, H_, KV_, hd_, att_scale_bwd, stream_);
-    else
-      attention_backward_simt<T, T>((const T*)a.qkv, datt_, dqkv_f32_, B, S_, H_, KV_, hd_, att_scale_bwd, stream_);
+    } else if constexpr (!kIsF32) {
+      if (att_tc_) {
+        count_launch(3);
+        attention_backward_tc((const bf16*)a.qkv, a.att, datt_, a.lse, att_delta_, dqkv_f32_, B, S_, H_, KV_,
+                              att_scale_bwd, stream_);
+      } else {
+        cudaMemsetAsync(dqkv_f32_, 0, sizeof(float) * (size_t)M * QKVD_, stream_);
+        count_launch();
+        attention_backward_simt<T, T>((const T*)a.qkv, datt_, dqkv_f32_, B, S_, H_, KV_, hd_, att_scale_bwd, stream_);
+      }
+    }
     // QK-norm / rotation backward in fp32, then one rounding to the GEMM operand type.
     count_launch();
     rope_qknorm_backward<float>(dqkv_f32_, (const float*)a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_,

@@ -70,6 +70,14 @@ template <typename T, typename TD>
 void attention_backward_simt(const T* qkv, const TD* d_out, float* dqkv_f32, int B, int seq, int H, int KV, int hd,
                              float scale, cudaStream_t s);
 
+// Tensor-core causal attention (bf16 operands, head_dim 64 only; see attention_tc.cu).
+bool attention_tc_supported(int hd);
+void attention_forward_tc(const bf16* qkv, bf16* out, float* lse, int B, int seq, int H, int KV, float scale,
+                          cudaStream_t s);
+// Writes every element of dq|dk|dv (fp32, packed like qkv); `delta` is scratch [B*H*seq].
+void attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* d_out, const float* lse, float* delta,
+                           float* dqkv_f32, int B, int seq, int H, int KV, float scale, cudaStream_t s);
+
 // Cross-entropy over token-major logits [rows, V] (fp32), ane/stories/cpu.go:212-292 with the
 // soft cap of ane/common.go:272-287 folded in:
 //   z = softcap ? 15*tanh(x/15) : x;  p = softmax(z);  loss_row = -log(max(p[tgt],1e-10))
