@@ -86,6 +86,8 @@ SIGNATURES = {
     "ane_close": (c_int32, [c_void_p]),
     "ane_last_error": (c_char_p, [c_void_p]),
     "ane_version": (c_uint32, []),
+    "ane_sampler_seed": (c_uint64, [c_int64]),
+    "ane_sample_windows": (c_int32, [POINTER(c_uint64), c_uint64, c_uint32, c_uint32, c_uint32, c_uint32, POINTER(c_uint64)]),
     "ane_step": (c_int32, [c_void_p, POINTER(StepResult)]),
     "ane_step_tokens": (c_int32, [c_void_p, POINTER(c_uint16), POINTER(c_uint16), c_uint32, POINTER(StepResult)]),
     "ane_flush": (c_int32, [c_void_p, POINTER(c_double)]),

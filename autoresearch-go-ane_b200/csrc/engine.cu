@@ -25,6 +25,26 @@
 
 namespace ane {
 
+// Window sampler of Engine.Step (ane/engine.go:395-404) over the drand48 generator
+// (ane/engine.go:873-880), extended to data parallelism: every rank advances the one global
+// stream by batch*world draws per step and keeps draws rank, rank+world, ...  Host-only.
+void sample_windows(uint64_t* rng, uint64_t n_tokens, uint32_t seq, uint32_t batch, uint32_t rank, uint32_t world,
+                    uint64_t* out_pos) {
+  constexpr uint64_t kMul = 0x5DEECE66Dull, kAdd = 0xBull, kMask = (1ull << 48) - 1;
+  if (world == 0) world = 1;
+  const uint64_t limit = n_tokens > (uint64_t)seq + 1 ? n_tokens - seq - 1 : 0;
+  for (uint32_t i = 0; i < batch * world; ++i) {
+    *rng = (kMul * (*rng) + kAdd) & kMask;
+    const double u = (double)(*rng) / (double)(1ull << 48);
+    uint64_t pos = 0;
+    if (limit > 0) {
+      pos = (uint64_t)(u * (double)limit);
+      if (pos >= limit) pos = limit - 1;
+    }
+    if (i % world == rank) out_pos[i / world] = pos;
+  }
+}
+
 namespace {
 
 inline int64_t now_ns() {
@@ -32,8 +52,6 @@ inline int64_t now_ns() {
       .count();
 }
 
-// drand48 of the reference sampler (ane/engine.go:873-880).
-constexpr uint64_t kDrandMul = 0x5DEECE66Dull, kDrandAdd = 0xBull, kDrandMask = (1ull << 48) - 1;
 
 template <typename T>
 struct Act {  // saved activations of one layer (ane/train_full.go:12-37)
@@ -995,20 +1013,8 @@ int EngineT<T>::step(const uint16_t* input, const uint16_t* target, uint32_t n_s
   } else {
     if (n_tokens_ < (uint64_t)S_ + 1) return fail(ANE_ERR_STATE, "storiesane step: not enough tokens");
     // One global drand48 stream; rank r takes draws r, r+world, ... of each step (ane/engine.go:395-404).
-    const uint64_t limit = n_tokens_ - S_ - 1;
-    for (int i = 0; i < B_ * o_.world_size; ++i) {
-      rng_ = (kDrandMul * rng_ + kDrandAdd) & kDrandMask;
-      const double u = (double)rng_ / (double)(1ull << 48);
-      uint64_t pos = 0;
-      if (limit > 0) {
-        pos = (uint64_t)(u * (double)limit);
-        if (pos >= limit) pos = limit - 1;
-      }
-      if (i % o_.world_size == o_.rank) {
-        h_pos_[i / o_.world_size] = pos;
-        st_.token_pos = pos + (uint64_t)S_;
-      }
-    }
+    sample_windows(&rng_, n_tokens_, (uint32_t)S_, (uint32_t)B_, (uint32_t)o_.rank, (uint32_t)o_.world_size, h_pos_);
+    st_.token_pos = h_pos_[B_ - 1] + (uint64_t)S_;
     cudaMemcpyAsync(d_pos_, h_pos_, sizeof(uint64_t) * B_, cudaMemcpyHostToDevice, stream_);
     count_launch();
     gather_windows_kernel<<<(M_ + 255) / 256, 256, 0, stream_>>>(d_tokens_, d_pos_, d_in_, d_tgt_, B_, S_);

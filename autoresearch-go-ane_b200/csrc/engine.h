@@ -45,4 +45,7 @@ class EngineBase {
 
 EngineBase* create_engine(int compute_dtype);
 
+void sample_windows(uint64_t* rng, uint64_t n_tokens, uint32_t seq, uint32_t batch, uint32_t rank, uint32_t world,
+                    uint64_t* out_pos);
+
 }  // namespace ane

@@ -21,6 +21,15 @@ extern "C" {
 
 uint32_t ane_version(void) { return 100; }
 
+uint64_t ane_sampler_seed(int64_t seed) { return (((uint64_t)seed & 0xffffffffull) << 16) | 0x330Eull; }
+
+int32_t ane_sample_windows(uint64_t* rng_state, uint64_t n_tokens, uint32_t seq, uint32_t batch, uint32_t rank,
+                           uint32_t world, uint64_t* out_pos) {
+  if (!rng_state || !out_pos || batch == 0 || rank >= (world ? world : 1)) return ANE_ERR_ARG;
+  ane::sample_windows(rng_state, n_tokens, seq, batch, rank, world, out_pos);
+  return 0;
+}
+
 const char* ane_last_error(ane_engine* e) {
   if (e && e->impl) return e->impl->last_error().c_str();
   return g_api_err.c_str();

@@ -152,6 +152,14 @@ int32_t ane_close(ane_engine* e);              /* ane/engine.go:567 */
 const char* ane_last_error(ane_engine* e);     /* message for the last non-zero status (e may be NULL) */
 uint32_t ane_version(void);
 
+/* The window sampler Engine.Step uses, exposed for hosts and tests (pure host code, no GPU):
+ * ane_sampler_seed = drand48Seed (ane/engine.go:873); ane_sample_windows advances the generator by
+ * batch*world draws (ane/engine.go:877-880, :395-404) and returns this rank's `batch` window starts
+ * (draws rank, rank+world, ...), so all ranks together consume one reference sample stream. */
+uint64_t ane_sampler_seed(int64_t seed);
+int32_t ane_sample_windows(uint64_t* rng_state, uint64_t n_tokens, uint32_t seq, uint32_t batch, uint32_t rank,
+                           uint32_t world, uint64_t* out_pos);
+
 /* Engine.Step (ane/engine.go:381): samples `batch` windows with the drand48 sampler
  * (ane/engine.go:395-404, :873-880), runs forward, head, backward; every accum_steps calls it
  * applies the optimizer update (ane/engine.go:646-682). */

@@ -671,7 +671,10 @@ void ve_forward(orc_model& m, int layer, LayerCache& cache, const uint16_t* inpu
   const vecf& ve_gate = m.T(ORC_W, ORC_T_VE_GATE, layer);
   for (int t = 0; t < seq; ++t) {
     int tok = input[t];
-    for (int d = 0; d < dim; ++d) cache.ve[(size_t)d * seq + t] = ve_embed[(size_t)tok * dim + d];
+    // The reference indexes veEmbed[tok*dim+d] unchecked (a Go index panic for tok >= vocab); here an
+    // out-of-range token reads a zero row, matching EmbedLookup's treatment (ane/stories/cpu.go:60-65).
+    const bool tok_ok = tok < m.c.vocab;
+    for (int d = 0; d < dim; ++d) cache.ve[(size_t)d * seq + t] = tok_ok ? ve_embed[(size_t)tok * dim + d] : 0.f;
     for (int h = 0; h < heads; ++h) {
       float gate_pre = 0.f;
       for (int cidx = 0; cidx < gc; ++cidx) gate_pre += ve_gate[h * gc + cidx] * cache.x[(size_t)cidx * seq + t];
@@ -697,7 +700,7 @@ void ve_backward(orc_model& m, int layer, LayerCache& cache, float* d_prev, cons
       float d_gate = 0.f;
       for (int d = h * hd; d < (h + 1) * hd; ++d) {
         float dvdt = dv[(size_t)d * seq + t];
-        d_ve_embed[(size_t)tok * dim + d] += dvdt * gate;
+        if (tok < m.c.vocab) d_ve_embed[(size_t)tok * dim + d] += dvdt * gate;
         d_gate += dvdt * cache.ve[(size_t)d * seq + t];
       }
       float d_gate_pre = d_gate * 3.0f * act * (1 - act);
