@@ -16,6 +16,13 @@ __global__ void cast_bf16_to_f32_kernel(const bf16* __restrict__ src, float* __r
   for (; i < n; i += stride) dst[i] = __bfloat162float(src[i]);
 }
 
+// 16-byte vectors of T: 8 bf16 or 4 floats.
+template <typename T>
+struct Vec16 {
+  static constexpr int N = 16 / sizeof(T);
+  T v[N];
+};
+
 static inline int grid_for(uint64_t n, int block) {
   uint64_t g = (n + block - 1) / block;
   if (g > 148ull * 16) g = 148ull * 16;
@@ -103,9 +110,45 @@ __global__ void rope_qknorm_forward_kernel(T* __restrict__ qkv, T* __restrict__ 
   }
 }
 
+// Rotation only (no QK-norm): element-wise over the q|k columns, 16 bytes per thread.
+template <typename T>
+__global__ void rope_only_forward_kernel(T* __restrict__ qkv, const float* __restrict__ cosb,
+                                         const float* __restrict__ sinb, int M, int seq, int H, int KV, int hd) {
+  constexpr int VN = Vec16<T>::N;
+  const int qk_cols = (H + KV) * hd;
+  const int vec_per_row = qk_cols / VN;
+  const int ld = (H + 2 * KV) * hd;
+  const int half = hd >> 1;
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t n = (uint64_t)M * vec_per_row, stride = (uint64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    const int m = (int)(i / vec_per_row);
+    const int col = (int)(i - (uint64_t)m * vec_per_row) * VN;
+    const int t = m % seq;
+    const int pair0 = (col % hd) >> 1;
+    T* p = qkv + (size_t)m * ld + col;
+    uint4 u = *reinterpret_cast<const uint4*>(p);
+    T* e = reinterpret_cast<T*>(&u);
+#pragma unroll
+    for (int q = 0; q < VN / 2; ++q) {
+      const float c = cosb[t * half + pair0 + q], sn = sinb[t * half + pair0 + q];
+      const float a = to_f<T>(e[2 * q]), b = to_f<T>(e[2 * q + 1]);
+      e[2 * q] = from_f<T>(a * c - b * sn);
+      e[2 * q + 1] = from_f<T>(b * c + a * sn);
+    }
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+}
+
 template <typename T>
 void rope_qknorm_forward(T* qkv, T* qk_pre, const float* cosb, const float* sinb, int M, int seq, int H, int KV,
                          int hd, bool qk_norm, cudaStream_t s) {
+  if (!qk_norm) {
+    const uint64_t n = (uint64_t)M * (H + KV) * hd / Vec16<T>::N;
+    if (!n) return;
+    rope_only_forward_kernel<T><<<grid_for(n, 256), 256, 0, s>>>(qkv, cosb, sinb, M, seq, H, KV, hd);
+    return;
+  }
   const long long warps = (long long)M * (H + KV);
   if (warps <= 0) return;
   const int wpb = 8;
@@ -117,16 +160,22 @@ template void rope_qknorm_forward<float>(float*, float*, const float*, const flo
 template void rope_qknorm_forward<bf16>(bf16*, bf16*, const float*, const float*, int, int, int, int, int, bool,
                                         cudaStream_t);
 
-template <typename T>
+template <typename T, typename TO>
 __global__ void rope_qknorm_backward_kernel(T* __restrict__ dqkv, const T* __restrict__ qk_pre,
                                             const float* __restrict__ cosb, const float* __restrict__ sinb, int M,
                                             int seq, int H, int KV, int hd, int qk_norm, int reference_coeff,
-                                            int skip_rope) {
+                                            int skip_rope, TO* __restrict__ out_t, int write_back) {
   const int heads = H + KV;
+  const int slots = out_t ? H + 2 * KV : heads;  // with a typed copy, the v heads are converted too
   const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  if (wid >= (long long)M * heads) return;
-  const int m = (int)(wid / heads), head = (int)(wid - (long long)m * heads);
+  if (wid >= (long long)M * slots) return;
+  const int m = (int)(wid / slots), head = (int)(wid - (long long)m * slots);
+  if (head >= heads) {  // v head: conversion only
+    const size_t off = (size_t)m * ((H + 2 * KV) * hd) + (size_t)head * hd;
+    for (int i = lane; i < hd; i += 32) out_t[off + i] = from_f<TO>(to_f<T>(dqkv[off + i]));
+    return;
+  }
   const int t = m % seq;
   const int half = hd >> 1;
   const int ld = (H + 2 * KV) * hd;
@@ -169,24 +218,32 @@ __global__ void rope_qknorm_backward_kernel(T* __restrict__ dqkv, const T* __res
       e = e2;
       o = o2;
     }
-    p[2 * i] = from_f<T>(e);
-    p[2 * i + 1] = from_f<T>(o);
+    if (write_back) {
+      p[2 * i] = from_f<T>(e);
+      p[2 * i + 1] = from_f<T>(o);
+    }
+    if (out_t) {
+      TO* po = out_t + (size_t)m * ld + (size_t)head * hd;
+      po[2 * i] = from_f<TO>(e);
+      po[2 * i + 1] = from_f<TO>(o);
+    }
   }
 }
 
-template <typename T>
+template <typename T, typename TO>
 void rope_qknorm_backward(T* dqkv, const T* qk_pre, const float* cosb, const float* sinb, int M, int seq, int H,
-                          int KV, int hd, bool qk_norm, bool reference_coeff, bool skip_rope, cudaStream_t s) {
-  const long long warps = (long long)M * (H + KV);
+                          int KV, int hd, bool qk_norm, bool reference_coeff, bool skip_rope, TO* out_t,
+                          bool write_back, cudaStream_t s) {
+  const long long warps = (long long)M * (out_t ? H + 2 * KV : H + KV);
   if (warps <= 0) return;
   const int wpb = 8;
-  rope_qknorm_backward_kernel<T><<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, s>>>(
-      dqkv, qk_pre, cosb, sinb, M, seq, H, KV, hd, qk_norm, reference_coeff, skip_rope);
+  rope_qknorm_backward_kernel<T, TO><<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, s>>>(
+      dqkv, qk_pre, cosb, sinb, M, seq, H, KV, hd, qk_norm, reference_coeff, skip_rope, out_t, write_back ? 1 : 0);
 }
-template void rope_qknorm_backward<float>(float*, const float*, const float*, const float*, int, int, int, int, int,
-                                          bool, bool, bool, cudaStream_t);
-template void rope_qknorm_backward<bf16>(bf16*, const bf16*, const float*, const float*, int, int, int, int, int, bool,
-                                         bool, bool, cudaStream_t);
+template void rope_qknorm_backward<float, float>(float*, const float*, const float*, const float*, int, int, int, int,
+                                                 int, bool, bool, bool, float*, bool, cudaStream_t);
+template void rope_qknorm_backward<float, bf16>(float*, const float*, const float*, const float*, int, int, int, int,
+                                                int, bool, bool, bool, bf16*, bool, cudaStream_t);
 
 // ------------------------------------------------------------------------------------------
 // FFN activations
@@ -213,29 +270,57 @@ __global__ void relu2_backward_kernel(const T* __restrict__ dgate, const T* __re
 }
 template <typename T>
 __global__ void swiglu_forward_kernel(const T* __restrict__ h13, T* __restrict__ gate, int M, int Hd) {
+  constexpr int VN = Vec16<T>::N;
+  const int vec_per_row = Hd / VN;
   uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const uint64_t n = (uint64_t)M * Hd, stride = (uint64_t)gridDim.x * blockDim.x;
+  const uint64_t n = (uint64_t)M * vec_per_row, stride = (uint64_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) {
-    const uint64_t m = i / Hd, j = i - m * Hd;
-    const float h1 = to_f<T>(h13[m * 2 * Hd + j]), h3 = to_f<T>(h13[m * 2 * Hd + Hd + j]);
-    const float sg = 1.f / (1.f + expf(-h1));
-    gate[i] = from_f<T>(h1 * sg * h3);
+    const uint64_t m = i / vec_per_row, j = (i - m * vec_per_row) * VN;
+    const uint4 a = *reinterpret_cast<const uint4*>(h13 + m * 2 * Hd + j);
+    const uint4 b = *reinterpret_cast<const uint4*>(h13 + m * 2 * Hd + Hd + j);
+    const T* h1 = reinterpret_cast<const T*>(&a);
+    const T* h3 = reinterpret_cast<const T*>(&b);
+    uint4 o;
+    T* g = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int q = 0; q < VN; ++q) {
+      const float x = to_f<T>(h1[q]);
+      const float sg = 1.f / (1.f + __expf(-x));
+      g[q] = from_f<T>(x * sg * to_f<T>(h3[q]));
+    }
+    *reinterpret_cast<uint4*>(gate + m * Hd + j) = o;
   }
 }
 template <typename T>
 __global__ void swiglu_backward_kernel(const T* __restrict__ dgate, const T* __restrict__ h13, T* __restrict__ dh13,
                                        int M, int Hd) {
+  constexpr int VN = Vec16<T>::N;
+  const int vec_per_row = Hd / VN;
   uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const uint64_t n = (uint64_t)M * Hd, stride = (uint64_t)gridDim.x * blockDim.x;
+  const uint64_t n = (uint64_t)M * vec_per_row, stride = (uint64_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) {
-    const uint64_t m = i / Hd, j = i - m * Hd;
-    const float h1 = to_f<T>(h13[m * 2 * Hd + j]), h3 = to_f<T>(h13[m * 2 * Hd + Hd + j]);
-    const float dg = to_f<T>(dgate[i]);
-    const float sg = 1.f / (1.f + expf(-h1));
-    const float silu = h1 * sg;
-    const float dsilu = sg * (1.f + h1 * (1.f - sg));
-    dh13[m * 2 * Hd + j] = from_f<T>(dg * h3 * dsilu);
-    dh13[m * 2 * Hd + Hd + j] = from_f<T>(dg * silu);
+    const uint64_t m = i / vec_per_row, j = (i - m * vec_per_row) * VN;
+    const uint4 a = *reinterpret_cast<const uint4*>(h13 + m * 2 * Hd + j);
+    const uint4 b = *reinterpret_cast<const uint4*>(h13 + m * 2 * Hd + Hd + j);
+    const uint4 c = *reinterpret_cast<const uint4*>(dgate + m * Hd + j);
+    const T* h1 = reinterpret_cast<const T*>(&a);
+    const T* h3 = reinterpret_cast<const T*>(&b);
+    const T* dgv = reinterpret_cast<const T*>(&c);
+    uint4 o1, o3;
+    T* d1 = reinterpret_cast<T*>(&o1);
+    T* d3 = reinterpret_cast<T*>(&o3);
+#pragma unroll
+    for (int q = 0; q < VN; ++q) {
+      const float x = to_f<T>(h1[q]);
+      const float dg = to_f<T>(dgv[q]);
+      const float sg = 1.f / (1.f + __expf(-x));
+      const float silu = x * sg;
+      const float dsilu = sg * (1.f + x * (1.f - sg));
+      d1[q] = from_f<T>(dg * to_f<T>(h3[q]) * dsilu);
+      d3[q] = from_f<T>(dg * silu);
+    }
+    *reinterpret_cast<uint4*>(dh13 + m * 2 * Hd + j) = o1;
+    *reinterpret_cast<uint4*>(dh13 + m * 2 * Hd + Hd + j) = o3;
   }
 }
 
@@ -251,13 +336,13 @@ void relu2_backward(const T* dgate, const T* h1, T* dh1, uint64_t n, cudaStream_
 }
 template <typename T>
 void swiglu_forward(const T* h13, T* gate, int M, int Hd, cudaStream_t s) {
-  const uint64_t n = (uint64_t)M * Hd;
+  const uint64_t n = (uint64_t)M * Hd / Vec16<T>::N;
   if (!n) return;
   swiglu_forward_kernel<T><<<grid_for(n, 256), 256, 0, s>>>(h13, gate, M, Hd);
 }
 template <typename T>
 void swiglu_backward(const T* dgate, const T* h13, T* dh13, int M, int Hd, cudaStream_t s) {
-  const uint64_t n = (uint64_t)M * Hd;
+  const uint64_t n = (uint64_t)M * Hd / Vec16<T>::N;
   if (!n) return;
   swiglu_backward_kernel<T><<<grid_for(n, 256), 256, 0, s>>>(dgate, h13, dh13, M, Hd);
 }

@@ -817,12 +817,13 @@ int EngineT<T>::backward_layers(int B) {
         attention_backward_simt<T, T>((const T*)a.qkv, datt_, dqkv_f32_, B, S_, H_, KV_, hd_, att_scale_bwd, stream_);
       }
     }
-    // QK-norm / rotation backward in fp32, then one rounding to the GEMM operand type.
+    // QK-norm / rotation backward in fp32 and, fused, the one rounding to the GEMM operand type.
+    // The fp32 result is kept when something still reads it (value-embedding backward, taps).
+    const bool keep_f32 = kIsF32 || is_ve_layer(l) || o_.debug_taps;
     count_launch();
-    rope_qknorm_backward<float>(dqkv_f32_, (const float*)a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_,
-                                quirks_, quirks_, stream_);
+    rope_qknorm_backward<float, T>(dqkv_f32_, (const float*)a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_,
+                                   quirks_, quirks_, tcopy_arg(dqkv_), keep_f32, stream_);
     T* dqkv = tview(dqkv_f32_, dqkv_);
-    cast_to_t(dqkv_f32_, dqkv_, (uint64_t)M * QKVD_);
     if (o_.debug_taps)
       cudaMemcpyAsync(a.t_dqkv, dqkv_f32_, sizeof(float) * (size_t)M * QKVD_, cudaMemcpyDeviceToDevice, stream_);
     {

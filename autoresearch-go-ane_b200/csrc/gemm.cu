@@ -51,15 +51,16 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D bf16 tensor [outer, inner] with row pitch ld (elements); box = [box_outer, box_inner].
+// 2-D tensor [outer, inner] with row pitch ld (elements); box = [box_outer, box_inner]; 128B swizzle.
 static bool make_tmap(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
-                      uint32_t box_inner, uint32_t box_outer) {
-  typedef std::tuple<int, const void*, uint64_t, uint64_t, uint64_t, uint32_t, uint32_t> Key;
+                      uint32_t box_inner, uint32_t box_outer, bool is_f32 = false) {
+  typedef std::tuple<int, const void*, uint64_t, uint64_t, uint64_t, uint32_t, uint32_t, bool> Key;
   static std::map<Key, CUtensorMap> cache;
   static std::mutex mu;
   int dev = 0;
   cudaGetDevice(&dev);
-  Key key(dev, ptr, inner, outer, ld, box_inner, box_outer);
+  Key key(dev, ptr, inner, outer, ld, box_inner, box_outer, is_f32);
+  const uint64_t esz = is_f32 ? 4 : 2;
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
@@ -71,16 +72,16 @@ static bool make_tmap(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_
     g_gemm_err = "cuTensorMapEncodeTiled entry point not available";
     return false;
   }
-  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ld * 2) % 16 != 0) {
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ld * esz) % 16 != 0) {
     g_gemm_err = "TMA operand must be 16-byte aligned with a 16-byte multiple row pitch";
     return false;
   }
   cuuint64_t gdim[2] = {inner, outer};
-  cuuint64_t gstride[1] = {ld * 2};
+  cuuint64_t gstride[1] = {ld * esz};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMap tm;
-  CUresult r = fn(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+  CUresult r = fn(&tm, is_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -95,10 +96,10 @@ static bool make_tmap(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_
   return true;
 }
 
-template <int BN, bool A_MN, bool B_MN, class Epi>
-static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const Epi& epi, const GemmDesc& d,
-                     int split_k, int* d_status, cudaStream_t stream) {
-  auto kern = gemm_tc_kernel<BN, A_MN, B_MN, Epi>;
+template <int BN, bool A_MN, bool B_MN, int EPI>
+static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const EpiParams& epi,
+                     const GemmDesc& d, int split_k, int* d_status, cudaStream_t stream) {
+  auto kern = gemm_tc_kernel<BN, A_MN, B_MN, EPI>;
   static bool attr_set = false;  // per template instantiation
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -112,7 +113,7 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const Epi& ep
   const int tiles = ((d.M + GEMM_BM - 1) / GEMM_BM) * ((d.N + BN - 1) / BN) * split_k;
   int grid = tiles < gemm_num_sms() ? tiles : gemm_num_sms();
   if (grid < 1) grid = 1;
-  kern<<<grid, GEMM_THREADS, GemmCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, epi, d.M, d.N, d.K, split_k, d_status);
+  kern<<<grid, GEMM_THREADS, GemmCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, tc, epi, d.M, d.N, d.K, split_k, d_status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     g_gemm_err = std::string("gemm_tc launch: ") + cudaGetErrorString(e);
@@ -124,16 +125,15 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const Epi& ep
 template <int BN, bool A_MN, bool B_MN>
 static int dispatch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const GemmDesc& d, int split_k,
                         int* d_status, cudaStream_t stream) {
+  EpiParams epi{d.alpha, d.res1, d.s1, d.res2, d.s2, d.ldres};
+  CUtensorMap tc;
   if (d.out == GEMM_OUT_BF16) {
-    EpiStore<bf16> epi{reinterpret_cast<bf16*>(d.C), d.ldc, d.alpha, d.res1, d.s1, d.res2, d.s2, d.ldres};
-    return launch_tc<BN, A_MN, B_MN>(ta, tb, epi, d, 1, d_status, stream);
-  } else if (d.out == GEMM_OUT_F32) {
-    EpiStore<float> epi{reinterpret_cast<float*>(d.C), d.ldc, d.alpha, d.res1, d.s1, d.res2, d.s2, d.ldres};
-    return launch_tc<BN, A_MN, B_MN>(ta, tb, epi, d, 1, d_status, stream);
-  } else {
-    EpiAtomicAdd epi{reinterpret_cast<float*>(d.C), d.ldc, d.alpha};
-    return launch_tc<BN, A_MN, B_MN>(ta, tb, epi, d, split_k, d_status, stream);
+    if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 64, 32, false)) return -2;
+    return launch_tc<BN, A_MN, B_MN, EPI_STORE_BF16>(ta, tb, tc, epi, d, 1, d_status, stream);
   }
+  if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 32, 32, true)) return -2;
+  if (d.out == GEMM_OUT_F32) return launch_tc<BN, A_MN, B_MN, EPI_STORE_F32>(ta, tb, tc, epi, d, 1, d_status, stream);
+  return launch_tc<BN, A_MN, B_MN, EPI_REDUCE_F32>(ta, tb, tc, epi, d, split_k, d_status, stream);
 }
 
 template <int BN>
@@ -154,31 +154,45 @@ static int dispatch_layout(const GemmDesc& d, int split_k, int* d_status, cudaSt
 
 int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream) {
   if (d.M <= 0 || d.N <= 0 || d.K <= 0) return 0;
-  if (d.out == GEMM_OUT_BF16 && (d.ldc % 4) != 0) {
-    g_gemm_err = "bf16 output needs ldc % 4 == 0";
+  if (d.out == GEMM_OUT_F32 && (d.res1 || d.res2) && (d.ldres % 4 != 0 ||
+      (reinterpret_cast<uintptr_t>(d.res1) & 15) != 0 || (reinterpret_cast<uintptr_t>(d.res2) & 15) != 0)) {
+    g_gemm_err = "fp32 residual operands must be 16-byte aligned with ldres % 4 == 0";
     return -2;
   }
-  if (d.out == GEMM_OUT_F32 && ((d.ldc % 4) != 0 || (d.res1 && d.ldres % 4 != 0))) {
-    g_gemm_err = "fp32 output needs ldc % 4 == 0";
-    return -2;
-  }
-  const bool wide = d.N > 768;
-  const int bn = wide ? 256 : 128;
-  int split_k = 1;
-  if (d.out == GEMM_OUT_ACCUM) {
-    split_k = d.split_k;
-    if (split_k <= 0) {
-      const int tiles = ((d.M + GEMM_BM - 1) / GEMM_BM) * ((d.N + bn - 1) / bn);
-      const int kblocks = (d.K + GEMM_BK - 1) / GEMM_BK;
-      split_k = (gemm_num_sms() + tiles - 1) / tiles;
-      int max_split = kblocks / 4;
-      if (max_split < 1) max_split = 1;
-      if (split_k > max_split) split_k = max_split;
-      if (split_k < 1) split_k = 1;
+  // Tile width: 128x128 tiles need ~128 B/clk of shared-memory fill per SM and stall on it, so wider
+  // tiles win unless they leave the last wave mostly empty.  Cost model: waves x tile width.
+  const int sms = gemm_num_sms();
+  const int tiles_m = (d.M + GEMM_BM - 1) / GEMM_BM;
+  const int kblocks = (d.K + GEMM_BK - 1) / GEMM_BK;
+  int best_bn = 128, best_split = 1;
+  long best_cost = -1;
+  for (int bn : {256, 192, 128}) {
+    const int tiles = tiles_m * ((d.N + bn - 1) / bn);
+    int split_k = 1;
+    if (d.out == GEMM_OUT_ACCUM) {
+      split_k = d.split_k;
+      if (split_k <= 0) {
+        split_k = sms / tiles;  // fill one wave without exceeding it
+        int max_split = kblocks / 4;
+        if (max_split < 1) max_split = 1;
+        if (split_k > max_split) split_k = max_split;
+        if (split_k < 1) split_k = 1;
+      }
+    }
+    const long waves = ((long)tiles * split_k + sms - 1) / sms;
+    const long kb = (kblocks + split_k - 1) / split_k;
+    long cost = waves * kb * bn;
+    if (bn == 128) cost += cost / 3;   // fill-rate penalty of the narrow tile
+    if (bn == 192) cost += cost / 10;  // a narrower tile must win clearly
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best_bn = bn;
+      best_split = split_k;
     }
   }
-  return wide ? dispatch_layout<256>(d, split_k, d_status, stream)
-              : dispatch_layout<128>(d, split_k, d_status, stream);
+  if (best_bn == 256) return dispatch_layout<256>(d, best_split, d_status, stream);
+  if (best_bn == 192) return dispatch_layout<192>(d, best_split, d_status, stream);
+  return dispatch_layout<128>(d, best_split, d_status, stream);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -29,14 +29,20 @@ static constexpr int GEMM_THREADS = 192;
 
 template <int BN>
 struct GemmCfg {
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = (BN == 128) ? 6 : 4;
   static constexpr uint32_t A_BYTES = GEMM_BM * GEMM_BK * 2;
   static constexpr uint32_t B_BYTES = BN * GEMM_BK * 2;
-  static constexpr uint32_t SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + 1024;  // +1024: manual alignment
+  static constexpr uint32_t STAGING_BYTES = 4 * 2 * 4096;  // 4 epilogue warps x 2 buffers x (32 rows x 128 B)
+  static constexpr uint32_t SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + STAGING_BYTES + 1024;  // +1024: alignment
   static constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
 };
 
 // 64-bit shared-memory matrix descriptor (sm_100 format, version field = 1).
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);            // start address, bits [0,14)
@@ -47,85 +53,29 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
   return d;
 }
 
-// Plain store / blend epilogue:  C = alpha*acc + s1*res1 + s2*res2
-template <typename OutT>
-struct EpiStore {
-  OutT* C;
-  int ldc;
+// Epilogue kinds.  Every kind stages 32-row x 128-byte pieces of the accumulator in 128B-swizzled
+// shared memory and hands them to TMA, so global writes are full lines and edge tiles are clipped by
+// the tensor map instead of by per-thread bounds checks.
+enum EpiKind : int {
+  EPI_STORE_BF16 = 0,   // C(bf16) = alpha*acc
+  EPI_STORE_F32 = 1,    // C(fp32) = alpha*acc + s1*res1 + s2*res2
+  EPI_REDUCE_F32 = 2,   // C(fp32) += alpha*acc  (TMA reduce-add; split-K safe)
+};
+
+struct EpiParams {
   float alpha;
   const float* res1;  // optional fp32 [M, ldres]
   const float* s1;    // optional device scalar (nullptr => 1)
   const float* res2;
   const float* s2;
   int ldres;
-  struct State {};
-  __device__ __forceinline__ void tile_begin(State&, int, int) const {}
-  __device__ __forceinline__ void tile_end(State&, int, int, int, int) const {}
-  __device__ __forceinline__ void chunk(State&, int m, int n0, float* acc, int M, int N) const {
-    if (m >= M) return;
-    float a1 = 0.f, a2 = 0.f;
-    if (res1) a1 = s1 ? *s1 : 1.f;
-    if (res2) a2 = s2 ? *s2 : 1.f;
-    OutT* crow = C + (size_t)m * ldc + n0;
-    const float* r1 = res1 ? res1 + (size_t)m * ldres + n0 : nullptr;
-    const float* r2 = res2 ? res2 + (size_t)m * ldres + n0 : nullptr;
-    if (n0 + 32 <= N) {
-#pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        float v[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) v[q] = alpha * acc[j + q];
-        if (r1) {
-          float4 t = *reinterpret_cast<const float4*>(r1 + j);
-          v[0] += a1 * t.x; v[1] += a1 * t.y; v[2] += a1 * t.z; v[3] += a1 * t.w;
-        }
-        if (r2) {
-          float4 t = *reinterpret_cast<const float4*>(r2 + j);
-          v[0] += a2 * t.x; v[1] += a2 * t.y; v[2] += a2 * t.z; v[3] += a2 * t.w;
-        }
-        if constexpr (sizeof(OutT) == 4) {
-          *reinterpret_cast<float4*>(crow + j) = make_float4(v[0], v[1], v[2], v[3]);
-        } else {
-          __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]);
-          __nv_bfloat162 p1 = __floats2bfloat162_rn(v[2], v[3]);
-          uint2 u;
-          u.x = *reinterpret_cast<uint32_t*>(&p0);
-          u.y = *reinterpret_cast<uint32_t*>(&p1);
-          *reinterpret_cast<uint2*>(crow + j) = u;
-        }
-      }
-    } else {
-      for (int j = 0; j < 32 && n0 + j < N; ++j) {
-        float v = alpha * acc[j];
-        if (r1) v += a1 * r1[j];
-        if (r2) v += a2 * r2[j];
-        crow[j] = from_f<OutT>(v);
-      }
-    }
-  }
 };
 
-// Accumulating epilogue (beta = 1): C += alpha*acc, via fp32 reductions so that
-// split-K work items may target the same output tile.
-struct EpiAtomicAdd {
-  float* C;
-  int ldc;
-  float alpha;
-  struct State {};
-  __device__ __forceinline__ void tile_begin(State&, int, int) const {}
-  __device__ __forceinline__ void tile_end(State&, int, int, int, int) const {}
-  __device__ __forceinline__ void chunk(State&, int m, int n0, float* acc, int M, int N) const {
-    if (m >= M) return;
-    float* crow = C + (size_t)m * ldc + n0;
-    int lim = N - n0 < 32 ? N - n0 : 32;
-    for (int j = 0; j < lim; ++j) atomicAdd(crow + j, alpha * acc[j]);
-  }
-};
-
-template <int BN, bool A_MN, bool B_MN, class Epi>
+template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               Epi epi, int M, int N, int K, int split_k, int* status) {
+               const __grid_constant__ CUtensorMap tmC, EpiParams epi, int M, int N, int K, int split_k,
+               int* status) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int BM = GEMM_BM, BK = GEMM_BK;
@@ -140,6 +90,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smem_a0 = smem_base;
   const uint32_t smem_b0 = smem_base + STAGES * Cfg::A_BYTES;
+  const uint32_t smem_stage0 = smem_b0 + STAGES * Cfg::B_BYTES;  // epilogue staging, 1024-B aligned
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -166,6 +117,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&tmem_slot), Cfg::TMEM_COLS);
@@ -266,8 +218,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else {
     // ------------------------------ epilogue warps ------------------------------
     const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, 32*lane_group+32)
+    // Columns per staged piece: 128 bytes of output per row.
+    constexpr int CW = (EPI == EPI_STORE_BF16) ? 64 : 32;
+    const uint32_t stage_base = smem_stage0 + (uint32_t)(warp - 2) * 8192u;
+    uint8_t* stage_ptr = smem_raw + (stage_base - smem_u32(smem_raw));
     int local = 0;
+    int sbuf = 0;
     bool ok = true;
+    float a1 = 0.f, a2 = 0.f;
+    if constexpr (EPI == EPI_STORE_F32) {
+      if (epi.res1) a1 = epi.s1 ? *epi.s1 : 1.f;
+      if (epi.res2) a2 = epi.s2 ? *epi.s2 : 1.f;
+    }
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
       const int split = w / (tiles_m * tiles_n);
       const int rem = w - split * (tiles_m * tiles_n);
@@ -282,25 +244,85 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         break;
       }
       tc_fence_after();
-      const int m = tm * BM + lane_group * 32 + lane;
+      const int m_warp = tm * BM + lane_group * 32;
+      const int m = m_warp + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * BN);
-      typename Epi::State st;
-      epi.tile_begin(st, m, tn * BN);
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        if (tn * BN + c >= N) break;  // warp-uniform
-        float acc[32];
+      for (int c = 0; c < BN; c += CW) {
+        const int n0 = tn * BN + c;
+        if (n0 >= N || m_warp >= M) break;  // warp-uniform
+        float acc[CW];
         __syncwarp();
         tmem_ld_32x32(taddr + (uint32_t)c, acc);
+        if constexpr (CW == 64) tmem_ld_32x32(taddr + (uint32_t)c + 32u, acc + 32);
         tmem_ld_wait();
-        epi.chunk(st, m, tn * BN + c, acc, M, N);
+        // The piece staged two iterations ago must have been read by its TMA store before its
+        // buffer is rewritten.
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint8_t* row_ptr = stage_ptr + sbuf * 4096 + lane * 128;
+        if constexpr (EPI == EPI_STORE_BF16) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {  // 8 chunks of 8 bf16
+            uint4 u;
+            u.x = pack2_bf16(epi.alpha * acc[8 * q + 0], epi.alpha * acc[8 * q + 1]);
+            u.y = pack2_bf16(epi.alpha * acc[8 * q + 2], epi.alpha * acc[8 * q + 3]);
+            u.z = pack2_bf16(epi.alpha * acc[8 * q + 4], epi.alpha * acc[8 * q + 5]);
+            u.w = pack2_bf16(epi.alpha * acc[8 * q + 6], epi.alpha * acc[8 * q + 7]);
+            *reinterpret_cast<uint4*>(row_ptr + ((q ^ (lane & 7)) << 4)) = u;
+          }
+        } else {
+          const bool in_rows = m < M;
+          const float* r1 = (EPI == EPI_STORE_F32 && epi.res1 && in_rows) ? epi.res1 + (size_t)m * epi.ldres + n0 : nullptr;
+          const float* r2 = (EPI == EPI_STORE_F32 && epi.res2 && in_rows) ? epi.res2 + (size_t)m * epi.ldres + n0 : nullptr;
+          const bool full = n0 + 32 <= N;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {  // 8 chunks of 4 fp32
+            float4 v = make_float4(epi.alpha * acc[4 * q], epi.alpha * acc[4 * q + 1], epi.alpha * acc[4 * q + 2],
+                                   epi.alpha * acc[4 * q + 3]);
+            if constexpr (EPI == EPI_STORE_F32) {
+              if (r1) {
+                if (full) {
+                  const float4 t = *reinterpret_cast<const float4*>(r1 + 4 * q);
+                  v.x += a1 * t.x; v.y += a1 * t.y; v.z += a1 * t.z; v.w += a1 * t.w;
+                } else {
+                  if (n0 + 4 * q + 0 < N) v.x += a1 * r1[4 * q + 0];
+                  if (n0 + 4 * q + 1 < N) v.y += a1 * r1[4 * q + 1];
+                  if (n0 + 4 * q + 2 < N) v.z += a1 * r1[4 * q + 2];
+                  if (n0 + 4 * q + 3 < N) v.w += a1 * r1[4 * q + 3];
+                }
+              }
+              if (r2) {
+                if (full) {
+                  const float4 t = *reinterpret_cast<const float4*>(r2 + 4 * q);
+                  v.x += a2 * t.x; v.y += a2 * t.y; v.z += a2 * t.z; v.w += a2 * t.w;
+                } else {
+                  if (n0 + 4 * q + 0 < N) v.x += a2 * r2[4 * q + 0];
+                  if (n0 + 4 * q + 1 < N) v.y += a2 * r2[4 * q + 1];
+                  if (n0 + 4 * q + 2 < N) v.z += a2 * r2[4 * q + 2];
+                  if (n0 + 4 * q + 3 < N) v.w += a2 * r2[4 * q + 3];
+                }
+              }
+            }
+            *reinterpret_cast<float4*>(row_ptr + ((q ^ (lane & 7)) << 4)) = v;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t src = stage_base + (uint32_t)sbuf * 4096u;
+          if constexpr (EPI == EPI_REDUCE_F32) tma_reduce_add_2d(&tmC, src, n0, m_warp);
+          else tma_store_2d(&tmC, src, n0, m_warp);
+          tma_store_commit();
+        }
+        sbuf ^= 1;
       }
-      epi.tile_end(st, m, tn, M, N);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[buf]));
       ++local;
     }
+    if (lane == 0) tma_store_wait<0>();
   }
 
   tc_fence_before();

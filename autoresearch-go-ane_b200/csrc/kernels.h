@@ -43,9 +43,12 @@ void rope_qknorm_forward(T* qkv, T* qk_pre, const float* cosb, const float* sinb
                          int hd, bool qk_norm, cudaStream_t s);
 // Backward of the above on dq|dk in a packed dqkv buffer: QK-norm backward (ane/common.go:229-270;
 // reference_coeff reproduces its qkScale^2 factor) then inverse rotation unless skip_rope.
-template <typename T>
+// out_t (optional) receives the whole packed dq|dk|dv row converted to TO (the v columns pass through);
+// write_back = also store the transformed dq|dk in place.
+template <typename T, typename TO>
 void rope_qknorm_backward(T* dqkv, const T* qk_pre, const float* cosb, const float* sinb, int M, int seq, int H,
-                          int KV, int hd, bool qk_norm, bool reference_coeff, bool skip_rope, cudaStream_t s);
+                          int KV, int hd, bool qk_norm, bool reference_coeff, bool skip_rope, TO* out_t,
+                          bool write_back, cudaStream_t s);
 void build_rope_tables(float* cosb, float* sinb, int seq, int hd, double theta, cudaStream_t s);
 
 // FFN activations.  relu2: g = max(h,0)^2 (ane/common.go:146).  swiglu: g = silu(h1)*h3 with h13 = [M, 2*Hd].
