@@ -81,6 +81,9 @@ SIGNATURES = {
     "ane_op_cast_f32_to_bf16": (c_int32, [c_void_p, c_void_p, c_uint64]),
     "ane_op_cast_bf16_to_f32": (c_int32, [c_void_p, c_void_p, c_uint64]),
     "ane_op_gemm": (c_int32, [POINTER(GemmArgs)]),
+    "ane_op_sumsq": (c_int32, [c_void_p, c_uint64, c_float, c_void_p]),
+    "ane_op_sumsq_noalloc": (c_int32, [c_void_p, c_uint64, c_float, c_void_p]),
+    "ane_op_sumsq_noalloc_last_error": (c_char_p, []),
     "ane_dp_unique_id": (c_int32, [POINTER(c_uint8)]),
     "ane_open": (c_int32, [POINTER(Options), POINTER(c_uint16), c_uint64, POINTER(c_uint8), POINTER(c_void_p)]),
     "ane_close": (c_int32, [c_void_p]),

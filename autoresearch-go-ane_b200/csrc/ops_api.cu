@@ -126,6 +126,22 @@ int32_t ane_op_cast_bf16_to_f32(const void* d_src, float* d_dst, uint64_t n) {
   return 0;
 }
 
+// Squared norm of a gradient buffer: *d_out = sum (g*pre_scale)^2 in double
+// (ane/train_full.go:167-196 with ane/accel_stub.go:88-95).  The accumulator the kernel reduces
+// into is device scratch allocated here for the duration of the call.
+int32_t ane_op_sumsq(const float* d_g, uint64_t n, float pre_scale, double* d_out) {
+  if (!d_g || !d_out) return set_err(ANE_ERR_ARG, "ane_op_sumsq: null pointer");
+  double* acc = nullptr;
+  CK(cudaMalloc(&acc, sizeof(double)));
+  CK(cudaMemsetAsync(acc, 0, sizeof(double), 0));
+  sumsq_accumulate(d_g, n, pre_scale, acc, 0);
+  CK(cudaGetLastError());
+  CK(cudaMemcpyAsync(d_out, acc, sizeof(double), cudaMemcpyDeviceToDevice, 0));
+  CK(cudaStreamSynchronize(0));
+  CK(cudaFree(acc));
+  return 0;
+}
+
 int32_t ane_op_gemm(const ane_gemm_args* a) {
   if (!a || a->struct_size != sizeof(ane_gemm_args)) return set_err(ANE_ERR_ARG, "ane_op_gemm: bad struct_size");
   if (!a->d_a || !a->d_b || !a->d_c) return set_err(ANE_ERR_ARG, "ane_op_gemm: null operand pointer");

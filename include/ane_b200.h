@@ -49,6 +49,18 @@ int32_t ane_ops_device_status(int32_t* out_status);
 int32_t ane_op_cast_f32_to_bf16(const float* d_src, void* d_dst, uint64_t n);
 int32_t ane_op_cast_bf16_to_f32(const void* d_src, float* d_dst, uint64_t n);
 
+/* Squared gradient norm, *d_out = sum (g*pre_scale)^2 accumulated in double: the first half of
+ * clipLayerGradients (ane/train_full.go:167-196; sumSquaresGrad, ane/accel_stub.go:88-95).
+ * d_g and d_out are device pointers.  Allocates a device accumulator for the call. */
+int32_t ane_op_sumsq(const float* d_g, uint64_t n, float pre_scale, double* d_out);
+/* Same result without allocating anything: the working storage is a fixed 32 KiB array inside the
+ * library, so n is limited to 2^28 elements (larger n returns ANE_ERR_ARG).  For hosts that own all
+ * device memory themselves or must not trigger an allocation in a latency-critical loop.  No
+ * counterpart in the reference.  The first call on a device resolves the array's address (do it
+ * before any stream capture); calls share the array, so overlapping calls race. */
+int32_t ane_op_sumsq_noalloc(const float* d_g, uint64_t n, float pre_scale, double* d_out);
+const char* ane_op_sumsq_noalloc_last_error(void);
+
 /*
  * Dense contraction C[M,N] (op)= alpha*A*B (+ s1*res1 + s2*res2).
  * Replaces cblas_sgemm at ane/accel_darwin.go:74,94,124-138,163-175,207 and
