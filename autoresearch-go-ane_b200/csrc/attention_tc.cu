@@ -1,11 +1,14 @@
 // Causal flash-style attention on tensor cores (bf16 operands, fp32 softmax and accumulation),
 // head_dim 64, GQA-aware.  Probabilities are never written to memory: the forward keeps a running
-// (max, sum) per query row, the backward recomputes each 64x64 score tile from Q, K and the saved
-// log-sum-exp.
+// (max, sum) per query row, the backward recomputes each score tile from Q, K and the saved
+// log-sum-exp.  Key/value (forward, dQ) or query/dO (dK/dV) tiles stream through a two-stage
+// cp.async ring so loads overlap the MMAs.
 //
 // Forward restates ane/common.go:61-89; backward restates ane/train_full.go:261-316 (with the
-// score scale of the forward).  The reference's ANE graphs materialise [heads, seq, seq]
-// probabilities (ane/mil_stories.go:383-432); these kernels replace them.
+// score scale of the forward) and, fused into its epilogue, the inverse of the rotation of
+// ane/train_util.go:204-224, so dq|dk|dv leave the kernel as bf16 GEMM operands.  The reference's
+// ANE graphs materialise [heads, seq, seq] probabilities (ane/mil_stories.go:383-432); these
+// kernels replace them.
 //
 // Layout: q|k|v packed token-major [M, (H+2KV)*64]; out [M, H*64]; lse, delta [B, H, seq].
 #include "common.cuh"
@@ -16,9 +19,10 @@ namespace ane {
 namespace {
 
 constexpr int HD = 64;
-constexpr int BT = 64;          // query / key tile
-constexpr int LDS = HD + 8;     // padded smem row (144 B: 16-B aligned rows, conflict-free ldmatrix)
-constexpr int ATT_THREADS = 128;
+constexpr int KT = 64;           // streamed tile (keys in fwd/dQ, queries in dK/dV)
+constexpr int BR = 128;          // resident tile rows per block (8 warps x 16 rows)
+constexpr int LDS = HD + 8;      // padded smem row (144 B: 16-B aligned rows, conflict-free ldmatrix)
+constexpr int ATT_THREADS = 256;
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const bf16* p) {
@@ -43,18 +47,28 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+__device__ __forceinline__ void cp_async_16(bf16* dst, const bf16* src, bool valid) {
+  const uint32_t d = smem_u32(dst);
+  const int bytes = valid ? 16 : 0;  // 0 => the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
-// Copies a [64 x 64] bf16 tile (rows row0.., row pitch ld) into padded smem; rows >= rows_valid are zero.
-__device__ __forceinline__ void load_tile(bf16* dst, const bf16* src, int ld, int rows_valid) {
-  for (int i = threadIdx.x; i < BT * (HD / 8); i += ATT_THREADS) {
+// Asynchronously copies an [nrows x 64] bf16 tile (row pitch ld) into padded smem; rows >= rows_valid
+// are zero-filled.  rows_valid >= 1.
+__device__ __forceinline__ void load_tile_async(bf16* dst, const bf16* src, int ld, int nrows, int rows_valid) {
+  for (int i = threadIdx.x; i < nrows * (HD / 8); i += ATT_THREADS) {
     const int r = i >> 3, c = (i & 7) * 8;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (r < rows_valid) v = *reinterpret_cast<const uint4*>(src + (size_t)r * ld + c);
-    *reinterpret_cast<uint4*>(dst + r * LDS + c) = v;
+    const bool ok = r < rows_valid;
+    cp_async_16(dst + r * LDS + c, src + (size_t)(ok ? r : 0) * ld + c, ok);
   }
 }
 
-// acc[nt][.] (16 x 64) += A(16 rows of `a_tile` starting at a_row0; K = HD) * B^T, with B stored [n][k] in b_tile.
+// acc (16 x 64) += A(16 rows of a_tile from a_row0; K = HD) * B^T, with B stored [n][k] in b_tile (64 rows).
 __device__ __forceinline__ void gemm_a_smem_b_nk(float (&acc)[8][4], const bf16* a_tile, int a_row0, const bf16* b_tile,
                                                  int lane) {
 #pragma unroll
@@ -71,11 +85,11 @@ __device__ __forceinline__ void gemm_a_smem_b_nk(float (&acc)[8][4], const bf16*
   }
 }
 
-// acc (16 x 64) += P (16 x 64 in registers, accumulator layout `p`, converted to bf16) * B, with B stored [k][n].
+// acc (16 x 64) += P (16 x 64 in registers, accumulator layout, rounded to bf16) * B, with B stored [k][n] (64 rows).
 __device__ __forceinline__ void gemm_a_regs_b_kn(float (&acc)[8][4], const float (&p)[8][4], const bf16* b_tile,
                                                  int lane) {
 #pragma unroll
-  for (int kk = 0; kk < BT / 16; ++kk) {
+  for (int kk = 0; kk < KT / 16; ++kk) {
     uint32_t a[4];
     a[0] = pack_bf16(p[2 * kk][0], p[2 * kk][1]);
     a[1] = pack_bf16(p[2 * kk][2], p[2 * kk][3]);
@@ -99,93 +113,136 @@ __device__ __forceinline__ float quad_sum(float v) {
   v += __shfl_xor_sync(0xffffffffu, v, 1);
   return v + __shfl_xor_sync(0xffffffffu, v, 2);
 }
+__device__ __forceinline__ void zero_acc(float (&a)[8][4]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) a[i][e] = 0.f;
+}
+
+// Writes one accumulator (16 rows x 64 cols per warp) as bf16 into a packed gradient row, optionally
+// undoing the pair rotation first (each thread holds whole (even, odd) pairs).
+__device__ __forceinline__ void store_grad_bf16(bf16* base, int ld, int row_lo, int T, size_t row0,
+                                                const float (&acc)[8][4], const float* cosb, const float* sinb,
+                                                int g, int t4) {
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = row_lo + g + r * 8;
+    if (row >= T) continue;
+    bf16* p = base + (row0 + row) * ld;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      float e = acc[nt][2 * r], o = acc[nt][2 * r + 1];
+      if (cosb) {
+        const int pair = nt * 4 + t4;
+        const float c = cosb[row * (HD / 2) + pair], s = sinb[row * (HD / 2) + pair];
+        const float e2 = e * c + o * s, o2 = o * c - e * s;
+        e = e2;
+        o = o2;
+      }
+      *reinterpret_cast<__nv_bfloat162*>(p + nt * 8 + 2 * t4) = __floats2bfloat162_rn(e, o);
+    }
+  }
+}
 
 // ------------------------------------------------------------------------------------------------
-// Forward: grid (q tiles, B*H); 4 warps x 16 query rows.
+// Forward: grid (query tiles of 128, B*H); 8 warps x 16 query rows; key/value tiles of 64 streamed.
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(ATT_THREADS)
 attention_fwd_tc_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, float* __restrict__ lse, int T, int H,
                         int KV, float scale) {
-  __shared__ __align__(16) bf16 Qs[BT * LDS];
-  __shared__ __align__(16) bf16 Ks[BT * LDS];
-  __shared__ __align__(16) bf16 Vs[BT * LDS];
+  extern __shared__ __align__(16) uint8_t att_smem[];
+  bf16* Qs = reinterpret_cast<bf16*>(att_smem);   // [BR][LDS]
+  bf16* Ks = Qs + BR * LDS;                       // [2][KT][LDS]
+  bf16* Vs = Ks + 2 * KT * LDS;                   // [2][KT][LDS]
   const int qt = blockIdx.x, bh = blockIdx.y;
   const int b = bh / H, h = bh - b * H, kvh = h / (H / KV);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
   const int ld = (H + 2 * KV) * HD;
   const size_t row0 = (size_t)b * T;
-  const int q0 = qt * BT;
-  load_tile(Qs, qkv + (row0 + q0) * ld + (size_t)h * HD, ld, min(BT, T - q0));
+  const int q0 = qt * BR;
+  const int q_last = min(q0 + BR, T) - 1;
+  const int n_kv = q_last / KT + 1;
+  const bf16* kbase = qkv + row0 * ld + (size_t)(H + kvh) * HD;
+  const bf16* vbase = qkv + row0 * ld + (size_t)(H + KV + kvh) * HD;
+  load_tile_async(Qs, qkv + (row0 + q0) * ld + (size_t)h * HD, ld, BR, min(BR, T - q0));
+  load_tile_async(Ks, kbase, ld, KT, min(KT, T));
+  load_tile_async(Vs, vbase, ld, KT, min(KT, T));
+  cp_async_commit();
   float o[8][4];
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
+  zero_acc(o);
   float m_i[2] = {-INFINITY, -INFINITY}, l_i[2] = {0.f, 0.f};
   const float sl2 = scale * kLog2e;
-  for (int j = 0; j <= qt; ++j) {
-    __syncthreads();
-    const int k0 = j * BT;
-    load_tile(Ks, qkv + (row0 + k0) * ld + (size_t)(H + kvh) * HD, ld, min(BT, T - k0));
-    load_tile(Vs, qkv + (row0 + k0) * ld + (size_t)(H + KV + kvh) * HD, ld, min(BT, T - k0));
-    __syncthreads();
-    float s[8][4];
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) s[i][e] = 0.f;
-    gemm_a_smem_b_nk(s, Qs, warp * 16, Ks, lane);
-    float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int row = q0 + warp * 16 + g + (e >> 1) * 8;
-        const int col = k0 + nt * 8 + 2 * t4 + (e & 1);
-        float v = s[nt][e] * sl2;
-        if (col > row || col >= T) v = -INFINITY;
-        s[nt][e] = v;
-        mx[e >> 1] = fmaxf(mx[e >> 1], v);
-      }
-    float corr[2], m_new[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      mx[r] = quad_max(mx[r]);
-      m_new[r] = fmaxf(m_i[r], mx[r]);
-      const float m_use = (m_new[r] == -INFINITY) ? 0.f : m_new[r];  // rows past the sequence end
-      corr[r] = exp2f(m_i[r] - m_use);
-      m_i[r] = m_new[r];
-      m_new[r] = m_use;
+  const int r_lo = q0 + warp * 16;
+  for (int j = 0; j < n_kv; ++j) {
+    const int k0 = j * KT;
+    if (j + 1 < n_kv) {
+      const int kn = k0 + KT;
+      load_tile_async(Ks + ((j + 1) & 1) * KT * LDS, kbase + (size_t)kn * ld, ld, KT, min(KT, T - kn));
+      load_tile_async(Vs + ((j + 1) & 1) * KT * LDS, vbase + (size_t)kn * ld, ld, KT, min(KT, T - kn));
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
-    float rs[2] = {0.f, 0.f};
+    __syncthreads();
+    if (k0 <= r_lo + 15 && r_lo < T) {  // warp-uniform: skip tiles entirely above the diagonal
+      const bf16* Kc = Ks + (j & 1) * KT * LDS;
+      const bf16* Vc = Vs + (j & 1) * KT * LDS;
+      float s[8][4];
+      zero_acc(s);
+      gemm_a_smem_b_nk(s, Qs, warp * 16, Kc, lane);
+      float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
+      for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float p = exp2f(s[nt][e] - m_new[e >> 1]);
-        s[nt][e] = p;
-        rs[e >> 1] += p;
+        for (int e = 0; e < 4; ++e) {
+          const int row = r_lo + g + (e >> 1) * 8;
+          const int col = k0 + nt * 8 + 2 * t4 + (e & 1);
+          float v = s[nt][e] * sl2;
+          if (col > row || col >= T) v = -INFINITY;
+          s[nt][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      float corr[2], m_use[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = quad_max(mx[r]);
+        const float m_new = fmaxf(m_i[r], mx[r]);
+        m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;  // rows with nothing visible yet
+        corr[r] = exp2f(m_i[r] - m_use[r]);
+        m_i[r] = m_new;
       }
+      float rs[2] = {0.f, 0.f};
 #pragma unroll
-    for (int r = 0; r < 2; ++r) l_i[r] = l_i[r] * corr[r] + rs[r];
+      for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
+        for (int e = 0; e < 4; ++e) {
+          const float p = exp2f(s[nt][e] - m_use[e >> 1]);
+          s[nt][e] = p;
+          rs[e >> 1] += p;
+        }
 #pragma unroll
-      for (int e = 0; e < 4; ++e) o[nt][e] *= corr[e >> 1];
-    gemm_a_regs_b_kn(o, s, Vs, lane);
+      for (int r = 0; r < 2; ++r) l_i[r] = l_i[r] * corr[r] + rs[r];
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[nt][e] *= corr[e >> 1];
+      gemm_a_regs_b_kn(o, s, Vc, lane);
+    }
+    __syncthreads();
   }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     l_i[r] = quad_sum(l_i[r]);
-    const int row = q0 + warp * 16 + g + r * 8;
+    const int row = r_lo + g + r * 8;
     if (row < T) {
       const float inv = 1.0f / l_i[r];
       bf16* op = out + (row0 + row) * (size_t)(H * HD) + (size_t)h * HD;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        __nv_bfloat162 v = __floats2bfloat162_rn(o[nt][2 * r] * inv, o[nt][2 * r + 1] * inv);
-        *reinterpret_cast<__nv_bfloat162*>(op + nt * 8 + 2 * t4) = v;
-      }
+      for (int nt = 0; nt < 8; ++nt)
+        *reinterpret_cast<__nv_bfloat162*>(op + nt * 8 + 2 * t4) =
+            __floats2bfloat162_rn(o[nt][2 * r] * inv, o[nt][2 * r + 1] * inv);
       if (t4 == 0) lse[((size_t)b * H + h) * T + row] = m_i[r] / kLog2e + logf(l_i[r]);
     }
   }
@@ -209,165 +266,191 @@ __global__ void attention_delta_kernel(const bf16* __restrict__ d_out, const bf1
 }
 
 // ------------------------------------------------------------------------------------------------
-// Backward, dQ: grid (q tiles, B*H); 4 warps x 16 query rows; loops over key tiles <= q tile.
+// Backward, dQ: grid (query tiles of 128, B*H); key/value tiles streamed.
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(ATT_THREADS)
 attention_bwd_dq_tc_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ d_out, const float* __restrict__ lse,
-                           const float* __restrict__ delta, float* __restrict__ dqkv, int T, int H, int KV,
-                           float scale) {
-  __shared__ __align__(16) bf16 Qs[BT * LDS];
-  __shared__ __align__(16) bf16 dOs[BT * LDS];
-  __shared__ __align__(16) bf16 Ks[BT * LDS];
-  __shared__ __align__(16) bf16 Vs[BT * LDS];
+                           const float* __restrict__ delta, bf16* __restrict__ dqkv, const float* __restrict__ cosb,
+                           const float* __restrict__ sinb, int T, int H, int KV, float scale) {
+  extern __shared__ __align__(16) uint8_t att_smem[];
+  bf16* Qs = reinterpret_cast<bf16*>(att_smem);   // [BR][LDS]
+  bf16* dOs = Qs + BR * LDS;                      // [BR][LDS]
+  bf16* Ks = dOs + BR * LDS;                      // [2][KT][LDS]
+  bf16* Vs = Ks + 2 * KT * LDS;                   // [2][KT][LDS]
   const int qt = blockIdx.x, bh = blockIdx.y;
   const int b = bh / H, h = bh - b * H, kvh = h / (H / KV);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
   const int ld = (H + 2 * KV) * HD;
   const size_t row0 = (size_t)b * T;
-  const int q0 = qt * BT;
-  const int q_valid = min(BT, T - q0);
-  load_tile(Qs, qkv + (row0 + q0) * ld + (size_t)h * HD, ld, q_valid);
-  load_tile(dOs, d_out + (row0 + q0) * (size_t)(H * HD) + (size_t)h * HD, H * HD, q_valid);
+  const int q0 = qt * BR;
+  const int q_valid = min(BR, T - q0);
+  const int n_kv = (q0 + q_valid - 1) / KT + 1;
+  const bf16* kbase = qkv + row0 * ld + (size_t)(H + kvh) * HD;
+  const bf16* vbase = qkv + row0 * ld + (size_t)(H + KV + kvh) * HD;
+  load_tile_async(Qs, qkv + (row0 + q0) * ld + (size_t)h * HD, ld, BR, q_valid);
+  load_tile_async(dOs, d_out + (row0 + q0) * (size_t)(H * HD) + (size_t)h * HD, H * HD, BR, q_valid);
+  load_tile_async(Ks, kbase, ld, KT, min(KT, T));
+  load_tile_async(Vs, vbase, ld, KT, min(KT, T));
+  cp_async_commit();
+  const int r_lo = q0 + warp * 16;
   float lse_r[2], del_r[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
-    const int row = q0 + warp * 16 + g + r * 8;
+    const int row = r_lo + g + r * 8;
     const bool ok = row < T;
     lse_r[r] = ok ? lse[((size_t)b * H + h) * T + row] * kLog2e : 0.f;
     del_r[r] = ok ? delta[((size_t)b * H + h) * T + row] : 0.f;
   }
   float dq[8][4];
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) dq[i][e] = 0.f;
+  zero_acc(dq);
   const float sl2 = scale * kLog2e;
-  for (int j = 0; j <= qt; ++j) {
+  for (int j = 0; j < n_kv; ++j) {
+    const int k0 = j * KT;
+    if (j + 1 < n_kv) {
+      const int kn = k0 + KT;
+      load_tile_async(Ks + ((j + 1) & 1) * KT * LDS, kbase + (size_t)kn * ld, ld, KT, min(KT, T - kn));
+      load_tile_async(Vs + ((j + 1) & 1) * KT * LDS, vbase + (size_t)kn * ld, ld, KT, min(KT, T - kn));
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
     __syncthreads();
-    const int k0 = j * BT;
-    load_tile(Ks, qkv + (row0 + k0) * ld + (size_t)(H + kvh) * HD, ld, min(BT, T - k0));
-    load_tile(Vs, qkv + (row0 + k0) * ld + (size_t)(H + KV + kvh) * HD, ld, min(BT, T - k0));
-    __syncthreads();
-    float s[8][4], dp[8][4];
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        s[i][e] = 0.f;
-        dp[i][e] = 0.f;
-      }
-    gemm_a_smem_b_nk(s, Qs, warp * 16, Ks, lane);
-    gemm_a_smem_b_nk(dp, dOs, warp * 16, Vs, lane);
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int row = q0 + warp * 16 + g + (e >> 1) * 8;
-        const int col = k0 + nt * 8 + 2 * t4 + (e & 1);
-        float p = 0.f;
-        if (col <= row && row < T) p = exp2f(s[nt][e] * sl2 - lse_r[e >> 1]);
-        s[nt][e] = p * (dp[nt][e] - del_r[e >> 1]) * scale;  // dS
-      }
-    gemm_a_regs_b_kn(dq, s, Ks, lane);
-  }
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int row = q0 + warp * 16 + g + r * 8;
-    if (row < T) {
-      float* p = dqkv + (row0 + row) * ld + (size_t)h * HD;
+    if (k0 <= r_lo + 15 && r_lo < T) {
+      const bf16* Kc = Ks + (j & 1) * KT * LDS;
+      const bf16* Vc = Vs + (j & 1) * KT * LDS;
+      float s[8][4], dp[8][4];
+      zero_acc(s);
+      zero_acc(dp);
+      gemm_a_smem_b_nk(s, Qs, warp * 16, Kc, lane);
+      gemm_a_smem_b_nk(dp, dOs, warp * 16, Vc, lane);
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt)
-        *reinterpret_cast<float2*>(p + nt * 8 + 2 * t4) = make_float2(dq[nt][2 * r], dq[nt][2 * r + 1]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int row = r_lo + g + (e >> 1) * 8;
+          const int col = k0 + nt * 8 + 2 * t4 + (e & 1);
+          float p = 0.f;
+          if (col <= row && row < T) p = exp2f(s[nt][e] * sl2 - lse_r[e >> 1]);
+          s[nt][e] = p * (dp[nt][e] - del_r[e >> 1]) * scale;  // dS
+        }
+      gemm_a_regs_b_kn(dq, s, Kc, lane);
     }
+    __syncthreads();
   }
+  store_grad_bf16(dqkv + (size_t)h * HD, ld, r_lo, T, row0, dq, cosb, sinb, g, t4);
 }
 
 // ------------------------------------------------------------------------------------------------
-// Backward, dK/dV: grid (key tiles, B*KV); 4 warps x 16 key rows; loops over the query heads that
-// share this KV head and over query tiles >= key tile, so no atomics are needed.
+// Backward, dK/dV: grid (key tiles of 128, B*KV); 8 warps x 16 key rows; streams the query/dO tiles
+// of every query head that shares this KV head, so no atomics are needed.
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(ATT_THREADS)
 attention_bwd_dkv_tc_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ d_out,
-                            const float* __restrict__ lse, const float* __restrict__ delta, float* __restrict__ dqkv,
-                            int T, int H, int KV, float scale) {
-  __shared__ __align__(16) bf16 Qs[BT * LDS];
-  __shared__ __align__(16) bf16 dOs[BT * LDS];
-  __shared__ __align__(16) bf16 Ks[BT * LDS];
-  __shared__ __align__(16) bf16 Vs[BT * LDS];
-  __shared__ float lse_s[BT], del_s[BT];
+                            const float* __restrict__ lse, const float* __restrict__ delta, bf16* __restrict__ dqkv,
+                            const float* __restrict__ cosb, const float* __restrict__ sinb, int T, int H, int KV,
+                            float scale) {
+  extern __shared__ __align__(16) uint8_t att_smem[];
+  bf16* Ks = reinterpret_cast<bf16*>(att_smem);   // [BR][LDS]
+  bf16* Vs = Ks + BR * LDS;                       // [BR][LDS]
+  bf16* Qs = Vs + BR * LDS;                       // [2][KT][LDS]
+  bf16* dOs = Qs + 2 * KT * LDS;                  // [2][KT][LDS]
+  float* lse_s = reinterpret_cast<float*>(dOs + 2 * KT * LDS);  // [2][KT]
+  float* del_s = lse_s + 2 * KT;                                // [2][KT]
   const int kt = blockIdx.x, bk = blockIdx.y;
   const int b = bk / KV, kvh = bk - b * KV;
   const int group = H / KV;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
   const int ld = (H + 2 * KV) * HD;
   const size_t row0 = (size_t)b * T;
-  const int k0 = kt * BT;
-  load_tile(Ks, qkv + (row0 + k0) * ld + (size_t)(H + kvh) * HD, ld, min(BT, T - k0));
-  load_tile(Vs, qkv + (row0 + k0) * ld + (size_t)(H + KV + kvh) * HD, ld, min(BT, T - k0));
-  float dk[8][4], dv[8][4];
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      dk[i][e] = 0.f;
-      dv[i][e] = 0.f;
+  const int k0 = kt * BR;
+  const int k_valid = min(BR, T - k0);
+  const int n_qt = (T + KT - 1) / KT;
+  const int i0 = k0 / KT;                 // first query tile that can see these keys
+  const int per_head = n_qt - i0;
+  const int n_it = group * per_head;
+  auto issue = [&](int it) {
+    const int hq = kvh * group + it / per_head;
+    const int q0 = (i0 + it % per_head) * KT;
+    const int q_valid = min(KT, T - q0);
+    const int bufi = it & 1;
+    load_tile_async(Qs + bufi * KT * LDS, qkv + (row0 + q0) * ld + (size_t)hq * HD, ld, KT, q_valid);
+    load_tile_async(dOs + bufi * KT * LDS, d_out + (row0 + q0) * (size_t)(H * HD) + (size_t)hq * HD, H * HD, KT,
+                    q_valid);
+    if (threadIdx.x < KT) {
+      const int row = q0 + threadIdx.x;
+      const bool ok = row < T;
+      lse_s[bufi * KT + threadIdx.x] = ok ? lse[((size_t)b * H + hq) * T + row] * kLog2e : 0.f;
+      del_s[bufi * KT + threadIdx.x] = ok ? delta[((size_t)b * H + hq) * T + row] : 0.f;
     }
+  };
+  load_tile_async(Ks, qkv + (row0 + k0) * ld + (size_t)(H + kvh) * HD, ld, BR, k_valid);
+  load_tile_async(Vs, qkv + (row0 + k0) * ld + (size_t)(H + KV + kvh) * HD, ld, BR, k_valid);
+  issue(0);
+  cp_async_commit();
+  float dk[8][4], dv[8][4];
+  zero_acc(dk);
+  zero_acc(dv);
   const float sl2 = scale * kLog2e;
-  const int n_qt = (T + BT - 1) / BT;
-  for (int hq = kvh * group; hq < (kvh + 1) * group; ++hq) {
-    for (int i = kt; i < n_qt; ++i) {
-      __syncthreads();
-      const int q0 = i * BT;
-      const int q_valid = min(BT, T - q0);
-      load_tile(Qs, qkv + (row0 + q0) * ld + (size_t)hq * HD, ld, q_valid);
-      load_tile(dOs, d_out + (row0 + q0) * (size_t)(H * HD) + (size_t)hq * HD, H * HD, q_valid);
-      if (threadIdx.x < BT) {
-        const int row = q0 + threadIdx.x;
-        const bool ok = row < T;
-        lse_s[threadIdx.x] = ok ? lse[((size_t)b * H + hq) * T + row] * kLog2e : 0.f;
-        del_s[threadIdx.x] = ok ? delta[((size_t)b * H + hq) * T + row] : 0.f;
-      }
-      __syncthreads();
+  const int kr_lo = k0 + warp * 16;
+  for (int it = 0; it < n_it; ++it) {
+    if (it + 1 < n_it) {
+      issue(it + 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int q0 = (i0 + it % per_head) * KT;
+    if (q0 + KT - 1 >= kr_lo && kr_lo < T) {  // warp-uniform: some query of this tile sees some key of this warp
+      const bf16* Qc = Qs + (it & 1) * KT * LDS;
+      const bf16* dOc = dOs + (it & 1) * KT * LDS;
+      const float* lse_c = lse_s + (it & 1) * KT;
+      const float* del_c = del_s + (it & 1) * KT;
       float st[8][4], dpt[8][4];
-#pragma unroll
-      for (int a = 0; a < 8; ++a)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          st[a][e] = 0.f;
-          dpt[a][e] = 0.f;
-        }
-      gemm_a_smem_b_nk(st, Ks, warp * 16, Qs, lane);     // S^T  = K  Q^T
-      gemm_a_smem_b_nk(dpt, Vs, warp * 16, dOs, lane);   // dP^T = V dO^T
+      zero_acc(st);
+      zero_acc(dpt);
+      gemm_a_smem_b_nk(st, Ks, warp * 16, Qc, lane);     // S^T  = K  Q^T
+      gemm_a_smem_b_nk(dpt, Vs, warp * 16, dOc, lane);   // dP^T = V dO^T
       float pt[8][4];
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int krow = k0 + warp * 16 + g + (e >> 1) * 8;   // key index
-          const int qc = nt * 8 + 2 * t4 + (e & 1);              // query index inside the tile
+          const int krow = kr_lo + g + (e >> 1) * 8;          // key index
+          const int qc = nt * 8 + 2 * t4 + (e & 1);            // query index inside the tile
           const int qrow = q0 + qc;
           float p = 0.f;
-          if (krow <= qrow && qrow < T) p = exp2f(st[nt][e] * sl2 - lse_s[qc]);
+          if (krow <= qrow && qrow < T) p = exp2f(st[nt][e] * sl2 - lse_c[qc]);
           pt[nt][e] = p;
-          st[nt][e] = p * (dpt[nt][e] - del_s[qc]) * scale;     // dS^T
+          st[nt][e] = p * (dpt[nt][e] - del_c[qc]) * scale;   // dS^T
         }
-      gemm_a_regs_b_kn(dv, pt, dOs, lane);   // dV += P^T dO
-      gemm_a_regs_b_kn(dk, st, Qs, lane);    // dK += dS^T Q
+      gemm_a_regs_b_kn(dv, pt, dOc, lane);   // dV += P^T dO
+      gemm_a_regs_b_kn(dk, st, Qc, lane);    // dK += dS^T Q
     }
+    __syncthreads();
   }
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int row = k0 + warp * 16 + g + r * 8;
-    if (row < T) {
-      float* pk = dqkv + (row0 + row) * ld + (size_t)(H + kvh) * HD;
-      float* pv = dqkv + (row0 + row) * ld + (size_t)(H + KV + kvh) * HD;
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        *reinterpret_cast<float2*>(pk + nt * 8 + 2 * t4) = make_float2(dk[nt][2 * r], dk[nt][2 * r + 1]);
-        *reinterpret_cast<float2*>(pv + nt * 8 + 2 * t4) = make_float2(dv[nt][2 * r], dv[nt][2 * r + 1]);
-      }
-    }
-  }
+  store_grad_bf16(dqkv + (size_t)(H + kvh) * HD, ld, kr_lo, T, row0, dk, cosb, sinb, g, t4);
+  store_grad_bf16(dqkv + (size_t)(H + KV + kvh) * HD, ld, kr_lo, T, row0, dv, nullptr, nullptr, g, t4);
+}
+
+constexpr size_t kFwdSmem = (size_t)(BR + 4 * KT) * LDS * sizeof(bf16);
+constexpr size_t kDqSmem = (size_t)(2 * BR + 4 * KT) * LDS * sizeof(bf16);
+constexpr size_t kDkvSmem = (size_t)(2 * BR + 4 * KT) * LDS * sizeof(bf16) + 4 * KT * sizeof(float);
+
+bool g_attr_done = false;
+bool ensure_attrs() {
+  if (g_attr_done) return true;
+  if (cudaFuncSetAttribute(attention_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwdSmem) !=
+          cudaSuccess ||
+      cudaFuncSetAttribute(attention_bwd_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDqSmem) !=
+          cudaSuccess ||
+      cudaFuncSetAttribute(attention_bwd_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDkvSmem) !=
+          cudaSuccess)
+    return false;
+  g_attr_done = true;
+  return true;
 }
 
 }  // namespace
@@ -376,20 +459,23 @@ bool attention_tc_supported(int hd) { return hd == HD; }
 
 void attention_forward_tc(const bf16* qkv, bf16* out, float* lse, int B, int seq, int H, int KV, float scale,
                           cudaStream_t s) {
-  if (B <= 0 || seq <= 0) return;
-  dim3 grid((seq + BT - 1) / BT, B * H);
-  attention_fwd_tc_kernel<<<grid, ATT_THREADS, 0, s>>>(qkv, out, lse, seq, H, KV, scale);
+  if (B <= 0 || seq <= 0 || !ensure_attrs()) return;
+  dim3 grid((seq + BR - 1) / BR, B * H);
+  attention_fwd_tc_kernel<<<grid, ATT_THREADS, kFwdSmem, s>>>(qkv, out, lse, seq, H, KV, scale);
 }
 
 void attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* d_out, const float* lse, float* delta,
-                           float* dqkv_f32, int B, int seq, int H, int KV, float scale, cudaStream_t s) {
-  if (B <= 0 || seq <= 0) return;
+                           bf16* dqkv, const float* cosb, const float* sinb, int B, int seq, int H, int KV,
+                           float scale, cudaStream_t s) {
+  if (B <= 0 || seq <= 0 || !ensure_attrs()) return;
   const long long warps = (long long)B * seq * H;
   attention_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>(d_out, out, delta, B, seq, H);
-  dim3 gq((seq + BT - 1) / BT, B * H);
-  attention_bwd_dq_tc_kernel<<<gq, ATT_THREADS, 0, s>>>(qkv, d_out, lse, delta, dqkv_f32, seq, H, KV, scale);
-  dim3 gk((seq + BT - 1) / BT, B * KV);
-  attention_bwd_dkv_tc_kernel<<<gk, ATT_THREADS, 0, s>>>(qkv, d_out, lse, delta, dqkv_f32, seq, H, KV, scale);
+  dim3 gq((seq + BR - 1) / BR, B * H);
+  attention_bwd_dq_tc_kernel<<<gq, ATT_THREADS, kDqSmem, s>>>(qkv, d_out, lse, delta, dqkv, cosb, sinb, seq, H, KV,
+                                                               scale);
+  dim3 gk((seq + BR - 1) / BR, B * KV);
+  attention_bwd_dkv_tc_kernel<<<gk, ATT_THREADS, kDkvSmem, s>>>(qkv, d_out, lse, delta, dqkv, cosb, sinb, seq, H, KV,
+                                                                 scale);
 }
 
 }  // namespace ane

@@ -496,7 +496,7 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
   QD_ = H_ * hd_; KVD_ = KV_ * hd_; QKVD_ = QD_ + 2 * KVD_;
   N13_ = isN_ ? Hd_ : 2 * Hd_;
   att_tc_ = !qkv_f32_ && attention_tc_supported(hd_);
-  ce_rows_ = o_.ce_chunk_rows > 0 ? o_.ce_chunk_rows : 1024;
+  ce_rows_ = o_.ce_chunk_rows > 0 ? o_.ce_chunk_rows : 4096;
   if (ce_rows_ > M_) ce_rows_ = M_;
   ce_rows_ = std::max(ce_rows_, std::min(M_, S_));  // eval logits uses one sequence per chunk
   lr_ = o_.lr;
@@ -802,30 +802,39 @@ int EngineT<T>::backward_layers(int B) {
       count_launch();
       if ((rc = gemm(g)) != 0) return rc;
     }
+    T* dqkv = tview(dqkv_f32_, dqkv_);
+    bool dqkv_ready = false;  // true once dqkv holds the final GEMM operand
     if (qkv_f32_) {
       cudaMemsetAsync(dqkv_f32_, 0, sizeof(float) * (size_t)M * QKVD_, stream_);
       count_launch();
       attention_backward_simt<float, T>((const float*)a.qkv, datt_, dqkv_f32_, B, S_, H_, KV_, hd_, att_scale_bwd, stream_);
     } else if constexpr (!kIsF32) {
       if (att_tc_) {
+        // Tensor-core path: the kernels undo the rotation and emit bf16 operands directly.
         count_launch(3);
-        attention_backward_tc((const bf16*)a.qkv, a.att, datt_, a.lse, att_delta_, dqkv_f32_, B, S_, H_, KV_,
-                              att_scale_bwd, stream_);
+        attention_backward_tc((const bf16*)a.qkv, a.att, datt_, a.lse, att_delta_, dqkv_, rope_cos_, rope_sin_, B, S_,
+                              H_, KV_, att_scale_bwd, stream_);
+        dqkv_ready = true;
+        if (o_.debug_taps) {
+          count_launch();
+          to_f32_kernel<T><<<ew_grid((uint64_t)M * QKVD_), 256, 0, stream_>>>(dqkv_, a.t_dqkv, (uint64_t)M * QKVD_);
+        }
       } else {
         cudaMemsetAsync(dqkv_f32_, 0, sizeof(float) * (size_t)M * QKVD_, stream_);
         count_launch();
         attention_backward_simt<T, T>((const T*)a.qkv, datt_, dqkv_f32_, B, S_, H_, KV_, hd_, att_scale_bwd, stream_);
       }
     }
-    // QK-norm / rotation backward in fp32 and, fused, the one rounding to the GEMM operand type.
-    // The fp32 result is kept when something still reads it (value-embedding backward, taps).
-    const bool keep_f32 = kIsF32 || is_ve_layer(l) || o_.debug_taps;
-    count_launch();
-    rope_qknorm_backward<float, T>(dqkv_f32_, (const float*)a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_,
-                                   quirks_, quirks_, tcopy_arg(dqkv_), keep_f32, stream_);
-    T* dqkv = tview(dqkv_f32_, dqkv_);
-    if (o_.debug_taps)
-      cudaMemcpyAsync(a.t_dqkv, dqkv_f32_, sizeof(float) * (size_t)M * QKVD_, cudaMemcpyDeviceToDevice, stream_);
+    if (!dqkv_ready) {
+      // QK-norm / rotation backward in fp32 and, fused, the one rounding to the GEMM operand type.
+      // The fp32 result is kept when something still reads it (value-embedding backward, taps).
+      const bool keep_f32 = kIsF32 || is_ve_layer(l) || o_.debug_taps;
+      count_launch();
+      rope_qknorm_backward<float, T>(dqkv_f32_, (const float*)a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_,
+                                     quirks_, quirks_, tcopy_arg(dqkv_), keep_f32, stream_);
+      if (o_.debug_taps)
+        cudaMemcpyAsync(a.t_dqkv, dqkv_f32_, sizeof(float) * (size_t)M * QKVD_, cudaMemcpyDeviceToDevice, stream_);
+    }
     {
       GemmDesc g;  // dxn = dq*Wq + dk*Wk + dv*Wv   (ane/train_full.go:650-665)
       g.A = dqkv; g.B = wop(s_qkv_[l].off); g.C = dxn_;

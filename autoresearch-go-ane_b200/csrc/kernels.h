@@ -77,9 +77,11 @@ void attention_backward_simt(const T* qkv, const TD* d_out, float* dqkv_f32, int
 bool attention_tc_supported(int hd);
 void attention_forward_tc(const bf16* qkv, bf16* out, float* lse, int B, int seq, int H, int KV, float scale,
                           cudaStream_t s);
-// Writes every element of dq|dk|dv (fp32, packed like qkv); `delta` is scratch [B*H*seq].
+// Writes every element of dq|dk|dv (bf16, packed like qkv); with cos/sin tables the rotation of q and k
+// is undone in the epilogue (pass nullptr to skip).  `delta` is scratch [B*H*seq].
 void attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* d_out, const float* lse, float* delta,
-                           float* dqkv_f32, int B, int seq, int H, int KV, float scale, cudaStream_t s);
+                           bf16* dqkv, const float* cosb, const float* sinb, int B, int seq, int H, int KV,
+                           float scale, cudaStream_t s);
 
 // Cross-entropy over token-major logits [rows, V] (fp32), ane/stories/cpu.go:212-292 with the
 // soft cap of ane/common.go:272-287 folded in:

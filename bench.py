@@ -150,7 +150,8 @@ def run_ours(args):
     tokens = zipf_tokens(N_STREAM_TOKENS, WORKLOAD["vocab"], seed=0)
     opts = ane.Options(tokens=tokens, batch=MICRO_BATCH, arch=ane.ARCH_LLAMA, quirks=0, compute_dtype=ane.DTYPE_BF16,
                        accum_steps=1, lr=3e-4, adam_beta1=0.9, adam_beta2=0.95, weight_decay=0.1, grad_clip=1.0,
-                       seed=42, device=local_rank, rank=rank, world_size=world, dp_id=dp_id, **WORKLOAD)
+                       seed=42, device=local_rank, rank=rank, world_size=world, dp_id=dp_id, ce_chunk_rows=args.ce_chunk,
+                       **WORKLOAD)
     e = ane.open(opts)
     init_weights(e, ane, seed=1234)
     T = WORKLOAD["seq"]
@@ -286,6 +287,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ce-chunk", type=int, default=0, help="token rows per classifier/CE chunk (0 = library default)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
