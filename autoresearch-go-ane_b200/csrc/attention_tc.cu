@@ -345,7 +345,7 @@ attention_bwd_dq_tc_kernel(const bf16* __restrict__ qkv, const bf16* __restrict_
 // Backward, dK/dV: grid (key tiles of 128, B*KV); 8 warps x 16 key rows; streams the query/dO tiles
 // of every query head that shares this KV head, so no atomics are needed.
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(ATT_THREADS)
+__global__ void __launch_bounds__(ATT_THREADS, 2)
 attention_bwd_dkv_tc_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ d_out,
                             const float* __restrict__ lse, const float* __restrict__ delta, bf16* __restrict__ dqkv,
                             const float* __restrict__ cosb, const float* __restrict__ sinb, int T, int H, int KV,
@@ -413,7 +413,7 @@ attention_bwd_dkv_tc_kernel(const bf16* __restrict__ qkv, const bf16* __restrict
       zero_acc(dpt);
       gemm_a_smem_b_nk(st, Ks, warp * 16, Qc, lane);     // S^T  = K  Q^T
       gemm_a_smem_b_nk(dpt, Vs, warp * 16, dOc, lane);   // dP^T = V dO^T
-      float pt[8][4];
+      // st becomes P^T in place; after dV it becomes dS^T in place, so only two 16x64 temporaries live.
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
@@ -423,10 +423,16 @@ attention_bwd_dkv_tc_kernel(const bf16* __restrict__ qkv, const bf16* __restrict
           const int qrow = q0 + qc;
           float p = 0.f;
           if (krow <= qrow && qrow < T) p = exp2f(st[nt][e] * sl2 - lse_c[qc]);
-          pt[nt][e] = p;
-          st[nt][e] = p * (dpt[nt][e] - del_c[qc]) * scale;   // dS^T
+          st[nt][e] = p;
         }
-      gemm_a_regs_b_kn(dv, pt, dOc, lane);   // dV += P^T dO
+      gemm_a_regs_b_kn(dv, st, dOc, lane);   // dV += P^T dO
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int qc = nt * 8 + 2 * t4 + (e & 1);
+          st[nt][e] = st[nt][e] * (dpt[nt][e] - del_c[qc]) * scale;   // dS^T
+        }
       gemm_a_regs_b_kn(dk, st, Qc, lane);    // dK += dS^T Q
     }
     __syncthreads();

@@ -33,15 +33,21 @@ cross_entropy_rows_kernel(const float* __restrict__ logits, const uint16_t* __re
     return;
   }
   float m = -INFINITY, l = 0.f;
-  for (int i = threadIdx.x; i < V; i += kCEThreads) {
-    float z = x[i];
-    if (softcap) z = softcap_f(z);
-    if (z > m) {
-      l = l * __expf(m - z) + 1.f;
-      m = z;
-    } else {
-      l += __expf(z - m);
+  const int V4 = V >> 2;  // V is a multiple of 4 (checked when the engine opens)
+  const float4* x4 = reinterpret_cast<const float4*>(x);
+  for (int i = threadIdx.x; i < V4; i += kCEThreads) {
+    const float4 q = x4[i];
+    float z[4] = {q.x, q.y, q.z, q.w};
+    if (softcap) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) z[k] = softcap_f(z[k]);
     }
+    const float zm = fmaxf(fmaxf(z[0], z[1]), fmaxf(z[2], z[3]));
+    if (zm > m) {
+      l *= __expf(m - zm);
+      m = zm;
+    }
+    l += __expf(z[0] - m) + __expf(z[1] - m) + __expf(z[2] - m) + __expf(z[3] - m);
   }
   // warp then block combine of (m, l)
 #pragma unroll
@@ -71,17 +77,34 @@ cross_entropy_rows_kernel(const float* __restrict__ logits, const uint16_t* __re
   const float bm = s_bm;
   const float inv_sum = 1.0f / s_bl;
   const float gs = grad_scale * inv_valid[grow / seq];
-  for (int i = threadIdx.x; i < V; i += kCEThreads) {
-    const float raw = x[i];
-    float z = raw, dcap = 1.f;
-    if (softcap) {
-      const float th = tanhf(raw * (1.0f / 15.0f));
-      z = 15.0f * th;
-      dcap = 1.f - th * th;
+  for (int i = threadIdx.x; i < V4; i += kCEThreads) {
+    const float4 q = x4[i];
+    const float raw[4] = {q.x, q.y, q.z, q.w};
+    float outv[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float z = raw[k], dcap = 1.f;
+      if (softcap) {
+        const float th = tanhf(raw[k] * (1.0f / 15.0f));
+        z = 15.0f * th;
+        dcap = 1.f - th * th;
+      }
+      const float p = __expf(z - bm) * inv_sum;
+      const int idx = 4 * i + k;
+      if (idx == tgt && loss_rows) loss_rows[grow] = -logf(fmaxf(expf(z - bm) * inv_sum, 1e-10f));
+      outv[k] = gs * (p - (idx == tgt ? 1.f : 0.f)) * dcap;
     }
-    const float p = expf(z - bm) * inv_sum;
-    if (i == tgt && loss_rows) loss_rows[grow] = -logf(fmaxf(p, 1e-10f));
-    if (dl) dl[i] = from_f<TO>(gs * (p - (i == tgt ? 1.f : 0.f)) * dcap);
+    if (dl) {
+      if constexpr (sizeof(TO) == 4) {
+        *reinterpret_cast<float4*>(dl + 4 * i) = make_float4(outv[0], outv[1], outv[2], outv[3]);
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(outv[0], outv[1]), hi = __floats2bfloat162_rn(outv[2], outv[3]);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&lo);
+        u.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(dl + 4 * i) = u;
+      }
+    }
   }
 }
 

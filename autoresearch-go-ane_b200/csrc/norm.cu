@@ -1,4 +1,6 @@
 // Embedding gather/scatter and RMSNorm forward/backward (HBM-bound kernels).
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -194,11 +196,117 @@ __global__ void rmsnorm_backward_kernel(const float* __restrict__ dy, const floa
   }
 }
 
+// Register-resident variant for D = 128*NV (NV float4 per lane): each row is read once.
+template <typename T, int NV>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+rmsnorm_backward_reg_kernel(const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ w,
+                            const float* __restrict__ rstd, const float* __restrict__ res,
+                            const float* __restrict__ res_scale, float* __restrict__ dx_f32, T* __restrict__ dx_t,
+                            float* __restrict__ dw, int M) {
+  constexpr int D = 128 * NV;
+  __shared__ float s_dw[kWarpsPerBlock][D > 1024 ? 1 : D];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const float rs = res ? (res_scale ? *res_scale : 1.f) : 0.f;
+  const float inv_d = 1.0f / (float)D;
+  float4 wv[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+    wv[k] = w ? reinterpret_cast<const float4*>(w)[lane + 32 * k] : make_float4(1.f, 1.f, 1.f, 1.f);
+  float4 dwacc[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) dwacc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int row = blockIdx.x * kWarpsPerBlock + warp; row < M; row += gridDim.x * kWarpsPerBlock) {
+    const float4* dyr = reinterpret_cast<const float4*>(dy + (size_t)row * D);
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * D);
+    float4 g[NV], v[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      g[k] = dyr[lane + 32 * k];
+      v[k] = xr[lane + 32 * k];
+    }
+    float r;
+    if (rstd) {
+      r = rstd[row];
+    } else {
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+      ss = warp_sum(ss);
+      r = 1.0f / sqrtf(ss * inv_d + 1e-5f);
+    }
+    if (dw) {
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        dwacc[k].x += g[k].x * v[k].x * r;
+        dwacc[k].y += g[k].y * v[k].y * r;
+        dwacc[k].z += g[k].z * v[k].z * r;
+        dwacc[k].w += g[k].w * v[k].w * r;
+      }
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      g[k].x *= wv[k].x; g[k].y *= wv[k].y; g[k].z *= wv[k].z; g[k].w *= wv[k].w;
+      dot += g[k].x * v[k].x + g[k].y * v[k].y + g[k].z * v[k].z + g[k].w * v[k].w;
+    }
+    dot = warp_sum(dot);
+    const float coeff = dot * r * r * r * inv_d;
+    const float4* rr = res ? reinterpret_cast<const float4*>(res + (size_t)row * D) : nullptr;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      float4 o;
+      o.x = g[k].x * r - coeff * v[k].x;
+      o.y = g[k].y * r - coeff * v[k].y;
+      o.z = g[k].z * r - coeff * v[k].z;
+      o.w = g[k].w * r - coeff * v[k].w;
+      if (rr) {
+        const float4 q = rr[lane + 32 * k];
+        o.x += rs * q.x; o.y += rs * q.y; o.z += rs * q.z; o.w += rs * q.w;
+      }
+      if (dx_f32) reinterpret_cast<float4*>(dx_f32 + (size_t)row * D)[lane + 32 * k] = o;
+      if (dx_t) store4<T>(dx_t + (size_t)row * D + 4 * (lane + 32 * k), o.x, o.y, o.z, o.w);
+    }
+  }
+  if (dw) {
+    if constexpr (D <= 1024) {
+#pragma unroll
+      for (int k = 0; k < NV; ++k) reinterpret_cast<float4*>(&s_dw[warp][0])[lane + 32 * k] = dwacc[k];
+      __syncthreads();
+      for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float t = 0.f;
+#pragma unroll
+        for (int wq = 0; wq < kWarpsPerBlock; ++wq) t += s_dw[wq][i];
+        atomicAdd(dw + i, t);
+      }
+    }
+  }
+}
+
 template <typename T>
 void rmsnorm_backward(const float* dy, const float* x, const float* w, const float* rstd, const float* res,
                       const float* res_scale, float* dx_f32, T* dx_t, float* dw, int M, int D, cudaStream_t s) {
   if (M <= 0) return;
   int blocks = (M + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  if (D % 128 == 0 && D <= 1024) {
+    const int rb = std::min(blocks, 148 * 4);
+#define ANE_RMS_BWD_CASE(NV)                                                                                      \
+  case NV:                                                                                                         \
+    rmsnorm_backward_reg_kernel<T, NV><<<rb, kWarpsPerBlock * 32, 0, s>>>(dy, x, w, rstd, res, res_scale, dx_f32, \
+                                                                           dx_t, dw, M);                          \
+    return;
+    switch (D / 128) {
+      ANE_RMS_BWD_CASE(1)
+      ANE_RMS_BWD_CASE(2)
+      ANE_RMS_BWD_CASE(3)
+      ANE_RMS_BWD_CASE(4)
+      ANE_RMS_BWD_CASE(5)
+      ANE_RMS_BWD_CASE(6)
+      ANE_RMS_BWD_CASE(7)
+      ANE_RMS_BWD_CASE(8)
+    }
+#undef ANE_RMS_BWD_CASE
+  }
   if (dw && blocks > 148 * 2) blocks = 148 * 2;  // bound the number of global atomic passes
   const size_t smem = dw ? sizeof(float) * (size_t)D : 0;
   // dx_t may alias dx_f32 only when T == float; callers pass nullptr instead.

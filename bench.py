@@ -280,6 +280,55 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+KERNEL_CASES = {
+    # name: (M, N, K, a_mn, b_mn, out_mode)  -- shapes of the 110M step at micro-batch 32
+    "classifier_fwd": (8192, 32000, 768, 0, 0, 0),   # logits = x_norm . Embed^T, bf16 out (524 MB written)
+    "qkv_fwd": (8192, 2304, 768, 0, 0, 0),
+    "w2_dx": (8192, 768, 4096, 0, 1, 1),
+    "w13_dw": (4096, 768, 8192, 1, 1, 2),
+}
+
+
+def run_kernel_case(args):
+    """One GEMM shape of the step in isolation (device-resident zero operands), for ncu captures and
+    per-shape roofline numbers:  python bench.py --kernel-case classifier_fwd --steps 3 --warmup 2"""
+    import ctypes
+
+    import ane
+    from ane import _ffi
+
+    lib = _ffi.lib
+    M, N, K, a_mn, b_mn, out_mode = KERNEL_CASES[args.kernel_case]
+    c_bytes = M * N * (2 if out_mode == 0 else 4)
+    dA, dB, dC = lib.ane_dev_malloc(M * K * 2), lib.ane_dev_malloc(N * K * 2), lib.ane_dev_malloc(c_bytes)
+    for p, n in ((dA, M * K * 2), (dB, N * K * 2), (dC, c_bytes)):
+        lib.ane_dev_memset(p, 0, n)
+    g = _ffi.GemmArgs()
+    g.struct_size = ctypes.sizeof(_ffi.GemmArgs)
+    g.dtype = ane.DTYPE_BF16
+    g.d_a, g.d_b, g.d_c = dA, dB, dC
+    g.m, g.n, g.k = M, N, K
+    g.lda = M if a_mn else K
+    g.ldb = N if b_mn else K
+    g.ldc = N
+    g.a_mn, g.b_mn, g.out_mode, g.alpha = a_mn, b_mn, out_mode, 1.0
+    for _ in range(args.warmup):
+        assert lib.ane_op_gemm(ctypes.byref(g)) == 0, lib.ane_ops_last_error()
+    lib.ane_dev_sync()
+    lib.ane_timer_begin()
+    for _ in range(args.steps):
+        assert lib.ane_op_gemm(ctypes.byref(g)) == 0, lib.ane_ops_last_error()
+    ms = ctypes.c_float(0)
+    lib.ane_timer_end(ctypes.byref(ms))
+    per = ms.value / args.steps
+    _, tf_burst, _, src = measured_peaks()
+    tflops = 2.0 * M * N * K / (per * 1e-3) / 1e12
+    alg_bytes = (M * K + N * K) * 2 + c_bytes * (2 if out_mode == 2 else 1)
+    print(json.dumps({"kernel_case": args.kernel_case, "shape": [M, N, K], "us_per_launch": round(per * 1e3, 2),
+                      "achieved_tflops": round(tflops, 1), "frac_of_burst_peak": round(tflops / tf_burst, 4),
+                      "peak_source": src, "algorithmic_bytes": alg_bytes}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -288,7 +337,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ce-chunk", type=int, default=0, help="token rows per classifier/CE chunk (0 = library default)")
+    ap.add_argument("--kernel-case", choices=sorted(KERNEL_CASES), default=None)
     args = ap.parse_args()
+    if args.kernel_case:
+        run_kernel_case(args)
+        return
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":
