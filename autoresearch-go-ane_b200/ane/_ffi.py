@@ -96,6 +96,7 @@ SIGNATURES = {
     "ane_flush": (c_int32, [c_void_p, POINTER(c_double)]),
     "ane_eval_logits": (c_int32, [c_void_p, POINTER(c_uint16), c_uint32, POINTER(c_float), c_uint64, c_uint32]),
     "ane_eval_loss": (c_int32, [c_void_p, POINTER(c_uint16), c_uint32, POINTER(c_double), POINTER(c_uint64)]),
+    "ane_decode_greedy": (c_int32, [c_void_p, POINTER(c_uint16), c_uint32, c_uint32, c_uint32, POINTER(c_uint16)]),
     "ane_set_lr": (c_int32, [c_void_p, c_float]),
     "ane_get_lr": (c_float, [c_void_p]),
     "ane_get_state": (c_int32, [c_void_p, POINTER(State)]),

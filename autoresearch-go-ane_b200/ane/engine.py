@@ -211,6 +211,15 @@ class Engine:
         self._check(lib.ane_eval_loss(self._h, _u16p(tokens), n_seq, byref(s), byref(n)))
         return s.value, int(n.value)
 
+    def decode_greedy(self, prompts: np.ndarray, n_new: int) -> np.ndarray:
+        """prompts [n_seq, prompt_len] -> generated tokens [n_seq, n_new] (KV-cached greedy decoding)."""
+        self._alive("decode")
+        prompts = np.ascontiguousarray(prompts, dtype=np.uint16)
+        n_seq, plen = prompts.shape
+        out = np.empty((n_seq, n_new), dtype=np.uint16)
+        self._check(lib.ane_decode_greedy(self._h, _u16p(prompts), n_seq, plen, n_new, _u16p(out)))
+        return out
+
     def lr(self) -> float:  # ane/engine.go:358
         return float(lib.ane_get_lr(self._h)) if self._h else 0.0
 

@@ -198,4 +198,113 @@ template void attention_backward_simt<bf16, bf16>(const bf16*, const bf16*, floa
 template void attention_backward_simt<float, bf16>(const float*, const bf16*, float*, int, int, int, int, int, float,
                                                    cudaStream_t);
 
+
+// ------------------------------------------------------------------------------------------------
+// KV cache for decoding: caches are [B, max_seq, KV*hd].
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void kv_cache_copy_kernel(const T* __restrict__ qkv, T* __restrict__ kcache, T* __restrict__ vcache, int B,
+                                     int seq, int max_seq, int pos0, int H, int KV, int hd) {
+  const int kvd = KV * hd;
+  const int ld = (H + 2 * KV) * hd;
+  const long long n = (long long)B * seq * kvd;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % kvd);
+    const long long m = i / kvd;
+    const int b = (int)(m / seq), t = (int)(m - (long long)b * seq);
+    const size_t dst = ((size_t)b * max_seq + pos0 + t) * kvd + c;
+    kcache[dst] = qkv[(size_t)m * ld + (size_t)H * hd + c];
+    vcache[dst] = qkv[(size_t)m * ld + (size_t)(H + KV) * hd + c];
+  }
+}
+template <typename T>
+void kv_cache_fill(const T* qkv, T* kcache, T* vcache, int B, int seq, int max_seq, int H, int KV, int hd,
+                   cudaStream_t s) {
+  const long long n = (long long)B * seq * KV * hd;
+  if (n <= 0) return;
+  long long g = (n + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  kv_cache_copy_kernel<T><<<(unsigned)g, 256, 0, s>>>(qkv, kcache, vcache, B, seq, max_seq, 0, H, KV, hd);
+}
+template <typename T>
+void kv_cache_append(const T* qkv, T* kcache, T* vcache, int B, int max_seq, int pos, int H, int KV, int hd,
+                     cudaStream_t s) {
+  const long long n = (long long)B * KV * hd;
+  if (n <= 0) return;
+  kv_cache_copy_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(qkv, kcache, vcache, B, 1, max_seq, pos, H, KV, hd);
+}
+template void kv_cache_fill<float>(const float*, float*, float*, int, int, int, int, int, int, cudaStream_t);
+template void kv_cache_fill<bf16>(const bf16*, bf16*, bf16*, int, int, int, int, int, int, cudaStream_t);
+template void kv_cache_append<float>(const float*, float*, float*, int, int, int, int, int, int, cudaStream_t);
+template void kv_cache_append<bf16>(const bf16*, bf16*, bf16*, int, int, int, int, int, int, cudaStream_t);
+
+// One warp per (sequence, head): the single query row attends to cache positions 0..pos.
+template <typename T>
+__global__ void attention_decode_simt_kernel(const T* __restrict__ qkv, const T* __restrict__ kcache,
+                                             const T* __restrict__ vcache, T* __restrict__ out, int B, int max_seq,
+                                             int pos, int H, int KV, int hd, float scale) {
+  extern __shared__ float s_q[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wid = blockIdx.x * kAttWarps + warp;
+  if (wid >= B * H) return;
+  const int b = wid / H, h = wid - b * H;
+  const int kvh = h / (H / KV);
+  const int kvd = KV * hd;
+  const int ld = (H + 2 * KV) * hd;
+  float* q = s_q + warp * hd;
+  const T* qp = qkv + (size_t)b * ld + (size_t)h * hd;
+  for (int d = lane; d < hd; d += 32) q[d] = to_f<T>(qp[d]);
+  __syncwarp();
+  const T* kbase = kcache + (size_t)b * max_seq * kvd + (size_t)kvh * hd;
+  const T* vbase = vcache + (size_t)b * max_seq * kvd + (size_t)kvh * hd;
+  float m_run = -INFINITY, l_run = 0.f;
+  float acc[kMaxHdPerLane] = {0.f, 0.f, 0.f, 0.f};
+  for (int j0 = 0; j0 <= pos; j0 += 32) {
+    const int j = j0 + lane;
+    float sc = -INFINITY;
+    if (j <= pos) {
+      const T* kp = kbase + (size_t)j * kvd;
+      float dot = 0.f;
+      for (int d = 0; d < hd; ++d) dot += q[d] * to_f<T>(kp[d]);
+      sc = dot * scale;
+    }
+    const float m_new = fmaxf(m_run, warp_max(sc));
+    const float corr = __expf(m_run - m_new);
+    const float p = (j <= pos) ? __expf(sc - m_new) : 0.f;
+    l_run = l_run * corr + warp_sum(p);
+#pragma unroll
+    for (int c = 0; c < kMaxHdPerLane; ++c) acc[c] *= corr;
+    const int lim = min(32, pos - j0 + 1);
+    for (int jj = 0; jj < lim; ++jj) {
+      const float pj = __shfl_sync(0xffffffffu, p, jj);
+      const T* vp = vbase + (size_t)(j0 + jj) * kvd;
+#pragma unroll
+      for (int c = 0; c < kMaxHdPerLane; ++c) {
+        const int d = lane + 32 * c;
+        if (d < hd) acc[c] += pj * to_f<T>(vp[d]);
+      }
+    }
+    m_run = m_new;
+  }
+  const float inv = 1.0f / l_run;
+  T* op = out + (size_t)b * (H * hd) + (size_t)h * hd;
+#pragma unroll
+  for (int c = 0; c < kMaxHdPerLane; ++c) {
+    const int d = lane + 32 * c;
+    if (d < hd) op[d] = from_f<T>(acc[c] * inv);
+  }
+}
+template <typename T>
+void attention_decode_simt(const T* qkv, const T* kcache, const T* vcache, T* out, int B, int max_seq, int pos, int H,
+                           int KV, int hd, float scale, cudaStream_t s) {
+  const int total = B * H;
+  if (total <= 0) return;
+  attention_decode_simt_kernel<T><<<(total + kAttWarps - 1) / kAttWarps, kAttWarps * 32, kAttWarps * hd * sizeof(float), s>>>(
+      qkv, kcache, vcache, out, B, max_seq, pos, H, KV, hd, scale);
+}
+template void attention_decode_simt<float>(const float*, const float*, const float*, float*, int, int, int, int, int,
+                                           int, float, cudaStream_t);
+template void attention_decode_simt<bf16>(const bf16*, const bf16*, const bf16*, bf16*, int, int, int, int, int, int,
+                                          float, cudaStream_t);
+
 }  // namespace ane

@@ -64,13 +64,13 @@ void build_rope_tables(float* cosb, float* sinb, int seq, int hd, double theta, 
 template <typename T>
 __global__ void rope_qknorm_forward_kernel(T* __restrict__ qkv, T* __restrict__ qk_pre,
                                            const float* __restrict__ cosb, const float* __restrict__ sinb, int M,
-                                           int seq, int H, int KV, int hd, int qk_norm) {
+                                           int seq, int H, int KV, int hd, int qk_norm, int pos0) {
   const int heads = H + KV;
   const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (wid >= (long long)M * heads) return;
   const int m = (int)(wid / heads), head = (int)(wid - (long long)m * heads);
-  const int t = m % seq;
+  const int t = pos0 + m % seq;
   const int half = hd >> 1;
   const int ld = (H + 2 * KV) * hd;
   T* p = qkv + (size_t)m * ld + (size_t)head * hd;  // q heads then k heads are contiguous
@@ -113,7 +113,7 @@ __global__ void rope_qknorm_forward_kernel(T* __restrict__ qkv, T* __restrict__ 
 // Rotation only (no QK-norm): element-wise over the q|k columns, 16 bytes per thread.
 template <typename T>
 __global__ void rope_only_forward_kernel(T* __restrict__ qkv, const float* __restrict__ cosb,
-                                         const float* __restrict__ sinb, int M, int seq, int H, int KV, int hd) {
+                                         const float* __restrict__ sinb, int M, int seq, int H, int KV, int hd, int pos0) {
   constexpr int VN = Vec16<T>::N;
   const int qk_cols = (H + KV) * hd;
   const int vec_per_row = qk_cols / VN;
@@ -124,7 +124,7 @@ __global__ void rope_only_forward_kernel(T* __restrict__ qkv, const float* __res
   for (; i < n; i += stride) {
     const int m = (int)(i / vec_per_row);
     const int col = (int)(i - (uint64_t)m * vec_per_row) * VN;
-    const int t = m % seq;
+    const int t = pos0 + m % seq;
     const int pair0 = (col % hd) >> 1;
     T* p = qkv + (size_t)m * ld + col;
     uint4 u = *reinterpret_cast<const uint4*>(p);
@@ -142,22 +142,22 @@ __global__ void rope_only_forward_kernel(T* __restrict__ qkv, const float* __res
 
 template <typename T>
 void rope_qknorm_forward(T* qkv, T* qk_pre, const float* cosb, const float* sinb, int M, int seq, int H, int KV,
-                         int hd, bool qk_norm, cudaStream_t s) {
+                         int hd, bool qk_norm, int pos0, cudaStream_t s) {
   if (!qk_norm) {
     const uint64_t n = (uint64_t)M * (H + KV) * hd / Vec16<T>::N;
     if (!n) return;
-    rope_only_forward_kernel<T><<<grid_for(n, 256), 256, 0, s>>>(qkv, cosb, sinb, M, seq, H, KV, hd);
+    rope_only_forward_kernel<T><<<grid_for(n, 256), 256, 0, s>>>(qkv, cosb, sinb, M, seq, H, KV, hd, pos0);
     return;
   }
   const long long warps = (long long)M * (H + KV);
   if (warps <= 0) return;
   const int wpb = 8;
-  rope_qknorm_forward_kernel<T><<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, s>>>(qkv, qk_pre, cosb, sinb, M,
-                                                                                          seq, H, KV, hd, qk_norm);
+  rope_qknorm_forward_kernel<T><<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, s>>>(
+      qkv, qk_pre, cosb, sinb, M, seq, H, KV, hd, qk_norm, pos0);
 }
-template void rope_qknorm_forward<float>(float*, float*, const float*, const float*, int, int, int, int, int, bool,
+template void rope_qknorm_forward<float>(float*, float*, const float*, const float*, int, int, int, int, int, bool, int,
                                          cudaStream_t);
-template void rope_qknorm_forward<bf16>(bf16*, bf16*, const float*, const float*, int, int, int, int, int, bool,
+template void rope_qknorm_forward<bf16>(bf16*, bf16*, const float*, const float*, int, int, int, int, int, bool, int,
                                         cudaStream_t);
 
 template <typename T, typename TO>

@@ -135,6 +135,7 @@ class EngineT final : public EngineBase {
   int flush(double* refresh_ms) override;
   int eval_logits(const uint16_t* tokens, uint32_t n_seq, float* out, uint64_t cap, uint32_t layout) override;
   int eval_loss(const uint16_t* tokens, uint32_t n_seq, double* loss_sum, uint64_t* n_pos) override;
+  int decode_greedy(const uint16_t* prompts, uint32_t n_seq, uint32_t prompt_len, uint32_t n_new, uint16_t* out) override;
   int set_lr(float lr) override;
   float get_lr() override { return lr_; }
   int get_state(ane_state* s) override;
@@ -210,7 +211,7 @@ class EngineT final : public EngineBase {
   int layout_params();
   int alloc_buffers();
   int refresh_shadow();
-  int forward(const uint16_t* d_tok, int B, bool training);
+  int forward(const uint16_t* d_tok, int B, int Tl, int pos0);
   int head_and_backward(int B);
   int head_eval_loss(int B, double* loss_sum, uint64_t* n_pos);
   int backward_layers(int B);
@@ -227,6 +228,11 @@ class EngineT final : public EngineBase {
   // (ane/train_full.go:268-269), which amplifies operand rounding; its q/k/v stay in fp32.
   bool qkv_f32_ = false;
   bool att_tc_ = false;  // tensor-core attention kernels (bf16 operands, head_dim 64)
+  bool decoding_ = false;  // forward() runs one KV-cached decode step
+  std::vector<T*> kcache_, vcache_;  // [B, S_, KV*hd] per layer, allocated by the first decode
+  int32_t* d_argmax_ = nullptr;
+  uint16_t *d_dec_tok_ = nullptr, *d_dec_out_ = nullptr;
+  float* h_logits_ = nullptr;  // pinned staging for EvalLogits downloads
   float* att_delta_ = nullptr;
   float lr_ = 0, embed_lr_ = 0, scalar_lr_ = 0, lambda_lr_ = 0;
   int ce_rows_ = 0;
@@ -271,6 +277,10 @@ class EngineT final : public EngineBase {
   cudaStream_t stream_ = nullptr;
   cudaEvent_t ev0_ = nullptr, ev1_ = nullptr, ev_adam0_ = nullptr, ev_adam1_ = nullptr;
   DataParallel dp_;
+  cudaStream_t comm_stream_ = nullptr;   // gradient all-reduce, overlapped with backward
+  cudaEvent_t ev_bucket_ = nullptr, ev_comm_done_ = nullptr;
+  bool overlap_reduce_ = false;           // this micro-step is the last before the optimizer update
+  size_t reduced_lo_ = 0;                 // G_[reduced_lo_, r_mat1_) has already been handed to the all-reduce
   std::vector<void*> allocs_;
   bool profiling_ = false;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_events_;
@@ -288,6 +298,8 @@ void EngineT<T>::destroy() {
   if (h_tgt_) cudaFreeHost(h_tgt_);
   if (h_pos_) cudaFreeHost(h_pos_);
   if (h_loss_) cudaFreeHost(h_loss_);
+  if (h_logits_) cudaFreeHost(h_logits_);
+  h_logits_ = nullptr;
   h_in_ = h_tgt_ = nullptr;
   h_pos_ = nullptr;
   h_loss_ = nullptr;
@@ -297,6 +309,15 @@ void EngineT<T>::destroy() {
       cudaEventDestroy(*e);
       *e = nullptr;
     }
+  for (cudaEvent_t* e : {&ev_bucket_, &ev_comm_done_})
+    if (*e) {
+      cudaEventDestroy(*e);
+      *e = nullptr;
+    }
+  if (comm_stream_) {
+    cudaStreamDestroy(comm_stream_);
+    comm_stream_ = nullptr;
+  }
   if (stream_) {
     cudaStreamDestroy(stream_);
     stream_ = nullptr;
@@ -513,6 +534,7 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
   if ((rc = cuda_check(cudaMallocHost(&h_tgt_, sizeof(uint16_t) * M_), "cudaMallocHost")) != 0) return rc;
   if ((rc = cuda_check(cudaMallocHost(&h_pos_, sizeof(uint64_t) * B_), "cudaMallocHost")) != 0) return rc;
   if ((rc = cuda_check(cudaMallocHost(&h_loss_, sizeof(float) * 4), "cudaMallocHost")) != 0) return rc;
+  if ((rc = cuda_check(cudaMallocHost(&h_logits_, sizeof(float) * (size_t)V_ * S_), "cudaMallocHost")) != 0) return rc;
   for (float* p : {P_, G_, Mo_, Vo_})
     if ((rc = cuda_check(cudaMemsetAsync(p, 0, sizeof(float) * n_params_, stream_), "memset")) != 0) return rc;
   cudaMemsetAsync(d_status_, 0, sizeof(int), stream_);
@@ -546,6 +568,12 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
   if (o_.world_size > 1) {
     if (!dp_id) return fail(ANE_ERR_ARG, "storiesane open: world_size > 1 needs a bootstrap id");
     if ((rc = dp_.init(o_.rank, o_.world_size, dp_id, o_.device)) != 0) return fail(ANE_ERR_NCCL, dp_.last_error());
+    int lo_prio = 0, hi_prio = 0;
+    cudaDeviceGetStreamPriorityRange(&lo_prio, &hi_prio);
+    if ((rc = cuda_check(cudaStreamCreateWithPriority(&comm_stream_, cudaStreamNonBlocking, hi_prio), "comm stream")) != 0)
+      return rc;
+    if ((rc = cuda_check(cudaEventCreateWithFlags(&ev_bucket_, cudaEventDisableTiming), "event")) != 0) return rc;
+    if ((rc = cuda_check(cudaEventCreateWithFlags(&ev_comm_done_, cudaEventDisableTiming), "event")) != 0) return rc;
   }
   if ((rc = cuda_check(cudaStreamSynchronize(stream_), "open sync")) != 0) return rc;
   t_open_ns_ = now_ns();
@@ -576,9 +604,10 @@ int EngineT<T>::set_lr(float lr) {  // ane/engine.go:366-378
 // Forward (ane/train_full.go:383-453; eval path ane/engine.go:954-1038 performs the same arithmetic)
 // ------------------------------------------------------------------------------------------------
 template <typename T>
-int EngineT<T>::forward(const uint16_t* d_tok, int B, bool training) {
-  (void)training;
-  const int M = B * S_;
+int EngineT<T>::forward(const uint16_t* d_tok, int B, int Tl, int pos0) {
+  // Tl = tokens per sequence in this pass (S_ for training/eval, the prompt length for prefill, 1 for a
+  // decode step); pos0 = position of the first token (non-zero only while decoding).
+  const int M = B * Tl;
   int rc;
   const float att_scale = (float)(1.0 / sqrt((double)hd_));
   if (isN_) {
@@ -591,7 +620,7 @@ int EngineT<T>::forward(const uint16_t* d_tok, int B, bool training) {
     count_launch();
     if ((rc = gemm(g)) != 0) return rc;
     count_launch();
-    smear_forward(x0_, gate_pre_, P_ + s_smear_l_.off, xs_[0], M, S_, D_, stream_);
+    smear_forward(x0_, gate_pre_, P_ + s_smear_l_.off, xs_[0], M, Tl, D_, stream_);
   } else {
     count_launch();
     embed_forward(d_tok, P_ + s_embed_.off, xs_[0], nullptr, M, D_, V_, false, stream_);
@@ -614,22 +643,28 @@ int EngineT<T>::forward(const uint16_t* d_tok, int B, bool training) {
     }
     count_launch();
     if (qkv_f32_)
-      rope_qknorm_forward<float>((float*)a.qkv, (float*)a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_, stream_);
+      rope_qknorm_forward<float>((float*)a.qkv, (float*)a.qkpre, rope_cos_, rope_sin_, M, Tl, H_, KV_, hd_, isN_, pos0, stream_);
     else
-      rope_qknorm_forward<T>((T*)a.qkv, (T*)a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_, stream_);
+      rope_qknorm_forward<T>((T*)a.qkv, (T*)a.qkpre, rope_cos_, rope_sin_, M, Tl, H_, KV_, hd_, isN_, pos0, stream_);
     if (is_ve_layer(l)) {  // reference architecture only, so qkv is fp32 here
       count_launch();
       ve_forward<float>((float*)a.qkv, xs_[l], d_tok, P_ + s_ve_embed_[l].off, P_ + s_ve_gate_[l].off, a.ve_act, M, D_,
                         H_, KV_, hd_, V_, stream_);
     }
     count_launch();
-    if (qkv_f32_) {
-      attention_forward_simt<float, T>((const float*)a.qkv, a.att, a.lse, B, S_, H_, KV_, hd_, att_scale, stream_);
+    if (decoding_) {
+      // one new token per sequence: append its k|v to the cache and attend over positions 0..pos0
+      kv_cache_append<T>((const T*)a.qkv, kcache_[l], vcache_[l], B, S_, pos0, H_, KV_, hd_, stream_);
+      count_launch();
+      attention_decode_simt<T>((const T*)a.qkv, kcache_[l], vcache_[l], a.att, B, S_, pos0, H_, KV_, hd_, att_scale,
+                               stream_);
+    } else if (qkv_f32_) {
+      attention_forward_simt<float, T>((const float*)a.qkv, a.att, a.lse, B, Tl, H_, KV_, hd_, att_scale, stream_);
     } else if constexpr (!kIsF32) {
       if (att_tc_)
-        attention_forward_tc((const bf16*)a.qkv, a.att, a.lse, B, S_, H_, KV_, att_scale, stream_);
+        attention_forward_tc((const bf16*)a.qkv, a.att, a.lse, B, Tl, H_, KV_, att_scale, stream_);
       else
-        attention_forward_simt<T, T>((const T*)a.qkv, a.att, a.lse, B, S_, H_, KV_, hd_, att_scale, stream_);
+        attention_forward_simt<T, T>((const T*)a.qkv, a.att, a.lse, B, Tl, H_, KV_, hd_, att_scale, stream_);
     }
     {
       GemmDesc g;  // x2 = rl*x + Wo*att (+ xl*x0)   ane/train_full.go:414-426
@@ -878,6 +913,15 @@ int EngineT<T>::backward_layers(int B) {
     }
     if (post_fix) cast_to_t(dprev, dcur_t_[cur ^ 1], MD);
     (void)dprev_t;
+    if (overlap_reduce_) {
+      // Layer l's matrix gradients are final: hand them to the all-reduce on the communication stream
+      // while the layers below are still being differentiated.
+      const size_t lo = s_qkv_[l].off, hi = reduced_lo_;
+      cudaEventRecord(ev_bucket_, stream_);
+      cudaStreamWaitEvent(comm_stream_, ev_bucket_, 0);
+      if (dp_.all_reduce_sum(G_ + lo, hi - lo, comm_stream_) != 0) return fail(ANE_ERR_NCCL, dp_.last_error());
+      reduced_lo_ = lo;
+    }
     cur ^= 1;
   }
   float* dcur = dcur_[cur];
@@ -925,7 +969,20 @@ int EngineT<T>::do_flush() {
   int rc;
   uint32_t global_pending = pending_seqs_ * (uint32_t)o_.world_size;
   if (dp_.active()) {
-    if ((rc = dp_.all_reduce_sum(G_, n_params_, stream_)) != 0) return fail(ANE_ERR_NCCL, dp_.last_error());
+    if (overlap_reduce_) {
+      // matrices were reduced bucket by bucket during backward; the rest (embedding, norms, ...) follows
+      cudaEventRecord(ev_bucket_, stream_);
+      cudaStreamWaitEvent(comm_stream_, ev_bucket_, 0);
+      if (reduced_lo_ > r_mat0_ && dp_.all_reduce_sum(G_ + r_mat0_, reduced_lo_ - r_mat0_, comm_stream_) != 0)
+        return fail(ANE_ERR_NCCL, dp_.last_error());
+      if (dp_.all_reduce_sum(G_ + r_mat1_, n_params_ - r_mat1_, comm_stream_) != 0)
+        return fail(ANE_ERR_NCCL, dp_.last_error());
+      cudaEventRecord(ev_comm_done_, comm_stream_);
+      cudaStreamWaitEvent(stream_, ev_comm_done_, 0);
+      overlap_reduce_ = false;
+    } else if ((rc = dp_.all_reduce_sum(G_, n_params_, stream_)) != 0) {
+      return fail(ANE_ERR_NCCL, dp_.last_error());
+    }
   }
   cudaEventRecord(ev_adam0_, stream_);
   float pre_scale = (float)(1.0 / (double)global_pending);
@@ -1029,7 +1086,9 @@ int EngineT<T>::step(const uint16_t* input, const uint16_t* target, uint32_t n_s
     count_launch();
     gather_windows_kernel<<<(M_ + 255) / 256, 256, 0, stream_>>>(d_tokens_, d_pos_, d_in_, d_tgt_, B_, S_);
   }
-  if ((rc = forward(d_in_, B_, true)) != 0) return rc;
+  overlap_reduce_ = dp_.active() && (int)micro_steps_ + 1 >= o_.accum_steps;
+  reduced_lo_ = r_mat1_;
+  if ((rc = forward(d_in_, B_, S_, 0)) != 0) return rc;
   if ((rc = head_and_backward(B_)) != 0) return rc;
   cudaMemcpyAsync(h_loss_, d_loss_, sizeof(float), cudaMemcpyDeviceToHost, stream_);
   pending_seqs_ += (uint32_t)B_;
@@ -1085,7 +1144,7 @@ int EngineT<T>::eval_logits(const uint16_t* tokens, uint32_t n_seq, float* out, 
     const int M = nb * S_;
     memcpy(h_in_, tokens + (size_t)s0 * S_, sizeof(uint16_t) * M);
     cudaMemcpyAsync(d_in_, h_in_, sizeof(uint16_t) * M, cudaMemcpyHostToDevice, stream_);
-    if ((rc = forward(d_in_, nb, false)) != 0) return rc;
+    if ((rc = forward(d_in_, nb, S_, 0)) != 0) return rc;
     for (int b = 0; b < nb; ++b) {
       GemmDesc g;
       if (layout == 0) {  // [V][seq]
@@ -1102,10 +1161,12 @@ int EngineT<T>::eval_logits(const uint16_t* tokens, uint32_t n_seq, float* out, 
         count_launch();
         softcap_inplace(logits_, per_seq, stream_);
       }
-      if ((rc = cuda_check(cudaMemcpyAsync(out + (size_t)(s0 + b) * per_seq, logits_, sizeof(float) * per_seq,
-                                           cudaMemcpyDeviceToHost, stream_),
+      // device -> pinned staging (full PCIe rate) -> caller's buffer
+      if ((rc = cuda_check(cudaMemcpyAsync(h_logits_, logits_, sizeof(float) * per_seq, cudaMemcpyDeviceToHost, stream_),
                            "logits download")) != 0)
         return rc;
+      if ((rc = cuda_check(cudaStreamSynchronize(stream_), "logits sync")) != 0) return rc;
+      memcpy(out + (size_t)(s0 + b) * per_seq, h_logits_, sizeof(float) * per_seq);
     }
   }
   return check_device_status(nullptr);
@@ -1125,7 +1186,7 @@ int EngineT<T>::eval_loss(const uint16_t* tokens, uint32_t n_seq, double* loss_s
     cudaMemcpyAsync(d_in_, h_in_, sizeof(uint16_t) * M, cudaMemcpyHostToDevice, stream_);
     count_launch();
     shift_targets_kernel<<<(M + 255) / 256, 256, 0, stream_>>>(d_in_, d_tgt_, nb, S_);
-    if ((rc = forward(d_in_, nb, false)) != 0) return rc;
+    if ((rc = forward(d_in_, nb, S_, 0)) != 0) return rc;
     cudaMemsetAsync(loss_rows_, 0, sizeof(float) * M, stream_);
     for (int r0 = 0; r0 < M; r0 += ce_rows_) {
       const int rows = std::min(ce_rows_, M - r0);
@@ -1153,6 +1214,86 @@ int EngineT<T>::eval_loss(const uint16_t* tokens, uint32_t n_seq, double* loss_s
   }
   if (loss_sum) *loss_sum = total;
   if (n_pos) *n_pos = count;
+  return check_device_status(nullptr);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Greedy decoding with a KV cache (llama-style architecture).  Prefill runs the ordinary forward over the
+// prompt, k|v of every layer are copied into the cache, then each step runs the layer stack on one
+// token per sequence.  Tokens stay on the device until the end; argmax follows ane/train_full.go:344-354
+// (lowest index wins ties).  The reference has no KV cache (its Llama2Config.NKVHeads is parsed and
+// ignored, ane/stories/config.go:20-28); the check is the full-recompute forward.
+// ------------------------------------------------------------------------------------------------
+__global__ void store_tokens_kernel(const int32_t* __restrict__ arg, uint16_t* __restrict__ next_tok,
+                                    uint16_t* __restrict__ out, int B, int n_new, int step) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const uint16_t t = (uint16_t)arg[b];
+  next_tok[b] = t;
+  out[(size_t)b * n_new + step] = t;
+}
+
+template <typename T>
+int EngineT<T>::decode_greedy(const uint16_t* prompts, uint32_t n_seq, uint32_t prompt_len, uint32_t n_new,
+                              uint16_t* out) {
+  int rc;
+  if (isN_) return fail(ANE_ERR_STATE, "storiesane decode: KV-cache decoding is built for the llama-style architecture");
+  if (n_seq == 0 || (int)n_seq > B_) return fail(ANE_ERR_ARG, "storiesane decode: n_seq must be in [1, batch]");
+  if (prompt_len == 0 || n_new == 0 || (int)(prompt_len + n_new) > S_)
+    return fail(ANE_ERR_ARG, "storiesane decode: prompt_len + n_new must fit the engine's seq");
+  if ((rc = cuda_check(cudaSetDevice(o_.device), "cudaSetDevice")) != 0) return rc;
+  const int B = (int)n_seq, P = (int)prompt_len;
+  if (kcache_.empty()) {
+    kcache_.assign(L_, nullptr);
+    vcache_.assign(L_, nullptr);
+    for (int l = 0; l < L_; ++l) {
+      if ((rc = dalloc(&kcache_[l], (size_t)B_ * S_ * KVD_)) != 0) return rc;
+      if ((rc = dalloc(&vcache_[l], (size_t)B_ * S_ * KVD_)) != 0) return rc;
+    }
+    if ((rc = dalloc(&d_argmax_, B_)) != 0) return rc;
+    if ((rc = dalloc(&d_dec_tok_, B_)) != 0) return rc;
+    if ((rc = dalloc(&d_dec_out_, (size_t)B_ * S_)) != 0) return rc;
+  }
+  // The prompt does not fit the pinned window buffer in general (B*P <= B_*S_ does hold).
+  memcpy(h_in_, prompts, sizeof(uint16_t) * (size_t)B * P);
+  cudaMemcpyAsync(d_in_, h_in_, sizeof(uint16_t) * (size_t)B * P, cudaMemcpyHostToDevice, stream_);
+  decoding_ = false;
+  if ((rc = forward(d_in_, B, P, 0)) != 0) return rc;
+  for (int l = 0; l < L_; ++l) {
+    count_launch();
+    kv_cache_fill<T>((const T*)acts_[l].qkv, kcache_[l], vcache_[l], B, P, S_, H_, KV_, hd_, stream_);
+  }
+  auto next_token = [&](int rows_per_seq, int step) -> int {
+    // logits of the last position of every sequence -> argmax -> token
+    GemmDesc g;
+    g.A = xnf_ + (size_t)(rows_per_seq - 1) * D_; g.B = wop(s_embed_.off); g.C = logits_;
+    g.M = B; g.N = V_; g.K = D_; g.lda = rows_per_seq * D_; g.ldb = D_; g.ldc = V_; g.out = GEMM_OUT_F32;
+    count_launch();
+    int r = gemm(g);
+    if (r != 0) return r;
+    count_launch(2);
+    argmax_rows(logits_, d_argmax_, B, V_, stream_);
+    store_tokens_kernel<<<(B + 127) / 128, 128, 0, stream_>>>(d_argmax_, d_dec_tok_, d_dec_out_, B, (int)n_new, step);
+    return 0;
+  };
+  if ((rc = next_token(P, 0)) != 0) return rc;
+  decoding_ = true;
+  for (int step = 1; step < (int)n_new; ++step) {
+    const int pos = P + step - 1;  // position of the token generated in the previous step
+    if ((rc = forward(d_dec_tok_, B, 1, pos)) != 0) {
+      decoding_ = false;
+      return rc;
+    }
+    if ((rc = next_token(1, step)) != 0) {
+      decoding_ = false;
+      return rc;
+    }
+  }
+  decoding_ = false;
+  if ((rc = cuda_check(cudaMemcpyAsync(out, d_dec_out_, sizeof(uint16_t) * (size_t)B * n_new, cudaMemcpyDeviceToHost,
+                                       stream_),
+                       "decode download")) != 0)
+    return rc;
   return check_device_status(nullptr);
 }
 

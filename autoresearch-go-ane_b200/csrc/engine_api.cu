@@ -117,6 +117,15 @@ int32_t ane_eval_loss(ane_engine* e, const uint16_t* tokens, uint32_t n_seq, dou
   }
   return e->impl->eval_loss(tokens, n_seq, loss_sum, n_positions);
 }
+int32_t ane_decode_greedy(ane_engine* e, const uint16_t* prompts, uint32_t n_seq, uint32_t prompt_len, uint32_t n_new,
+                          uint16_t* out) {
+  ENGINE_OR_FAIL(e, "decode");
+  if (!prompts || !out) {
+    g_api_err = "storiesane decode: null buffer";
+    return ANE_ERR_ARG;
+  }
+  return e->impl->decode_greedy(prompts, n_seq, prompt_len, n_new, out);
+}
 int32_t ane_set_lr(ane_engine* e, float lr) {
   ENGINE_OR_FAIL(e, "set lr");
   return e->impl->set_lr(lr);

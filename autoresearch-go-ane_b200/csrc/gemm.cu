@@ -110,8 +110,17 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     }
     attr_set = true;
   }
-  const int tiles = ((d.M + GEMM_BM - 1) / GEMM_BM) * ((d.N + BN - 1) / BN) * split_k;
-  int grid = tiles < gemm_num_sms() ? tiles : gemm_num_sms();
+  const int base_tiles = ((d.M + GEMM_BM - 1) / GEMM_BM) * ((d.N + BN - 1) / BN);
+  int grid;
+  if (split_k > 0) {
+    const int tiles = base_tiles * split_k;
+    grid = tiles < gemm_num_sms() ? tiles : gemm_num_sms();
+  } else {  // stream-K: equal shares of the tile x k-block units, at least 8 k-blocks per CTA
+    const long long units = (long long)base_tiles * ((d.K + GEMM_BK - 1) / GEMM_BK);
+    long long g = units / 8;
+    if (g > gemm_num_sms()) g = gemm_num_sms();
+    grid = (int)g;
+  }
   if (grid < 1) grid = 1;
   kern<<<grid, GEMM_THREADS, GemmCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, tc, epi, d.M, d.N, d.K, split_k, d_status);
   cudaError_t e = cudaGetLastError();
@@ -159,26 +168,43 @@ int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream) {
     g_gemm_err = "fp32 residual operands must be 16-byte aligned with ldres % 4 == 0";
     return -2;
   }
-  // Tile width: 128x128 tiles need ~128 B/clk of shared-memory fill per SM and stall on it, so wider
-  // tiles win unless they leave the last wave mostly empty.  Cost model: waves x tile width.
   const int sms = gemm_num_sms();
   const int tiles_m = (d.M + GEMM_BM - 1) / GEMM_BM;
   const int kblocks = (d.K + GEMM_BK - 1) / GEMM_BK;
+  if (d.out == GEMM_OUT_ACCUM && d.split_k <= 0) {
+    // Accumulating GEMMs (weight gradients) end in reduce-adds anyway.  Tile width = the one that pads N
+    // least (ties: wider); schedule = classic split-K when it fills whole waves, else stream-K (equal
+    // shares of the tile x k-block units per CTA, at the price of about two extra partial epilogues).
+    int best_bn = 256;
+    long best_pad = -1;
+    for (int bn : {256, 192, 128}) {
+      const long pad = (long)((d.N + bn - 1) / bn) * bn;
+      if (best_pad < 0 || pad < best_pad) {
+        best_pad = pad;
+        best_bn = bn;
+      }
+    }
+    const int tiles = tiles_m * ((d.N + best_bn - 1) / best_bn);
+    int split = sms / tiles;
+    int max_split = kblocks / 4;
+    if (max_split < 1) max_split = 1;
+    if (split > max_split) split = max_split;
+    if (split < 1) split = 1;
+    const long waves = ((long)tiles * split + sms - 1) / sms;
+    const long classic_cost = waves * ((kblocks + split - 1) / split);
+    const long streamk_cost = ((long)tiles * kblocks + sms - 1) / sms + 8;
+    const int sched = (streamk_cost < classic_cost) ? 0 : split;  // 0 selects stream-K in the kernel
+    if (best_bn == 256) return dispatch_layout<256>(d, sched, d_status, stream);
+    if (best_bn == 192) return dispatch_layout<192>(d, sched, d_status, stream);
+    return dispatch_layout<128>(d, sched, d_status, stream);
+  }
+  // Tile width: 128x128 tiles need ~128 B/clk of shared-memory fill per SM and stall on it, so wider
+  // tiles win unless they leave the last wave mostly empty.  Cost model: waves x tile width.
   int best_bn = 128, best_split = 1;
   long best_cost = -1;
   for (int bn : {256, 192, 128}) {
     const int tiles = tiles_m * ((d.N + bn - 1) / bn);
-    int split_k = 1;
-    if (d.out == GEMM_OUT_ACCUM) {
-      split_k = d.split_k;
-      if (split_k <= 0) {
-        split_k = sms / tiles;  // fill one wave without exceeding it
-        int max_split = kblocks / 4;
-        if (max_split < 1) max_split = 1;
-        if (split_k > max_split) split_k = max_split;
-        if (split_k < 1) split_k = 1;
-      }
-    }
+    const int split_k = (d.out == GEMM_OUT_ACCUM) ? d.split_k : 1;
     const long waves = ((long)tiles * split_k + sms - 1) / sms;
     const long kb = (kblocks + split_k - 1) / split_k;
     long cost = waves * kb * bn;

@@ -71,6 +71,58 @@ struct EpiParams {
   int ldres;
 };
 
+// Work scheduler shared by the three warp roles (each role walks the same sequence).
+//   split_k > 0 : classic persistent schedule, work item = (k split, tile), stride gridDim.x.
+//   split_k == 0: stream-K.  The tiles x k-blocks units are dealt out in equal contiguous ranges, one per
+//                 CTA; a range is cut into segments at tile boundaries and every segment ends in a
+//                 reduce-add, so it needs an accumulating epilogue.  Removes the partial last wave.
+struct GemmSched {
+  int tiles_m, tiles, kblocks, split_k, kb_per_split, total_work, w;
+  long long u, u1;
+  __device__ __forceinline__ void init(int M, int N, int K, int BN, int split) {
+    tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
+    const int tiles_n = (N + BN - 1) / BN;
+    tiles = tiles_m * tiles_n;
+    kblocks = (K + GEMM_BK - 1) / GEMM_BK;
+    split_k = split;
+    if (split_k > 0) {
+      kb_per_split = (kblocks + split_k - 1) / split_k;
+      total_work = tiles * split_k;
+      w = blockIdx.x;
+    } else {
+      const long long units = (long long)tiles * kblocks;
+      u = units * blockIdx.x / gridDim.x;
+      u1 = units * (blockIdx.x + 1) / gridDim.x;
+    }
+  }
+  // Next non-empty segment: tile (tm, tn) and k-block range [kb0, kb1).
+  __device__ __forceinline__ bool next(int& tm, int& tn, int& kb0, int& kb1) {
+    if (split_k > 0) {
+      while (w < total_work) {
+        const int split = w / tiles;
+        const int rem = w - split * tiles;
+        w += gridDim.x;
+        kb0 = split * kb_per_split;
+        kb1 = min(kb0 + kb_per_split, kblocks);
+        if (kb1 <= kb0) continue;
+        tn = rem / tiles_m;
+        tm = rem - tn * tiles_m;
+        return true;
+      }
+      return false;
+    }
+    if (u >= u1) return false;
+    const int tile = (int)(u / kblocks);
+    kb0 = (int)(u - (long long)tile * kblocks);
+    const long long left = u1 - u;
+    kb1 = (left < (long long)(kblocks - kb0)) ? kb0 + (int)left : kblocks;
+    u += kb1 - kb0;
+    tn = tile / tiles_m;
+    tm = tile - tn * tiles_m;
+    return true;
+  }
+};
+
 template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -99,11 +151,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // return at once instead of each running into its own time-out.
   if (status != nullptr && *reinterpret_cast<volatile int*>(status) != DEV_OK) return;
 
-  const int tiles_m = (M + BM - 1) / BM;
-  const int tiles_n = (N + BN - 1) / BN;
-  const int kblocks = (K + BK - 1) / BK;
-  const int kb_per_split = (kblocks + split_k - 1) / split_k;
-  const int total_work = tiles_m * tiles_n * split_k;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -134,12 +181,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const int split = w / (tiles_m * tiles_n);
-        const int rem = w - split * (tiles_m * tiles_n);
-        const int tn = rem / tiles_m, tm = rem - tn * tiles_m;
-        const int kb0 = split * kb_per_split;
-        const int kb1 = min(kb0 + kb_per_split, kblocks);
+      GemmSched sched;
+      sched.init(M, N, K, BN, split_k);
+      int tm, tn, kb0, kb1;
+      while (ok && sched.next(tm, tn, kb0, kb1)) {
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, status, DEV_MBAR_TIMEOUT_PRODUCER)) {
             ok = false;
@@ -177,11 +222,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const int split = w / (tiles_m * tiles_n);
-        const int kb0 = split * kb_per_split;
-        const int kb1 = min(kb0 + kb_per_split, kblocks);
-        if (kb1 <= kb0) continue;
+      GemmSched sched;
+      sched.init(M, N, K, BN, split_k);
+      int tm, tn, kb0, kb1;
+      while (ok && sched.next(tm, tn, kb0, kb1)) {
         const int buf = local & 1;
         const uint32_t tphase = (uint32_t)(local >> 1) & 1u;
         if (!mbar_wait(smem_u32(&bar_tempty[buf]), tphase ^ 1u, status, DEV_MBAR_TIMEOUT_MMA)) {
@@ -230,22 +274,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (epi.res1) a1 = epi.s1 ? *epi.s1 : 1.f;
       if (epi.res2) a2 = epi.s2 ? *epi.s2 : 1.f;
     }
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-      const int split = w / (tiles_m * tiles_n);
-      const int rem = w - split * (tiles_m * tiles_n);
-      const int tn = rem / tiles_m, tm = rem - tn * tiles_m;
-      const int kb0 = split * kb_per_split;
-      const int kb1 = min(kb0 + kb_per_split, kblocks);
-      if (kb1 <= kb0) continue;
+    GemmSched sched;
+    sched.init(M, N, K, BN, split_k);
+    int tm, tn, kb0, kb1;
+    while (ok && sched.next(tm, tn, kb0, kb1)) {
       const int buf = local & 1;
       const uint32_t tphase = (uint32_t)(local >> 1) & 1u;
+      const int m_warp = tm * BM + lane_group * 32;
+      const int m = m_warp + lane;
+      // Residual rows are fetched one 32-column piece ahead (the first piece while the MMAs of this
+      // tile are still running), so their latency is off the epilogue's critical path.
+      float4 pre[8];
+      bool pre_ok = false;
+      if constexpr (EPI == EPI_STORE_F32) {
+        if (epi.res1 && m < M && tn * BN + 32 <= N) {
+          const float4* rp = reinterpret_cast<const float4*>(epi.res1 + (size_t)m * epi.ldres + tn * BN);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) pre[q] = rp[q];
+          pre_ok = true;
+        }
+      }
       if (!mbar_wait(smem_u32(&bar_tfull[buf]), tphase, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const int m_warp = tm * BM + lane_group * 32;
-      const int m = m_warp + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * BN);
 #pragma unroll 1
       for (int c = 0; c < BN; c += CW) {
@@ -255,6 +308,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         __syncwarp();
         tmem_ld_32x32(taddr + (uint32_t)c, acc);
         if constexpr (CW == 64) tmem_ld_32x32(taddr + (uint32_t)c + 32u, acc + 32);
+        float4 cur[8];
+        bool cur_ok = false;
+        if constexpr (EPI == EPI_STORE_F32) {
+          cur_ok = pre_ok;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) cur[q] = pre[q];
+          pre_ok = false;
+          const int nn = n0 + CW;
+          if (epi.res1 && m < M && c + CW < BN && nn + 32 <= N) {
+            const float4* rp = reinterpret_cast<const float4*>(epi.res1 + (size_t)m * epi.ldres + nn);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) pre[q] = rp[q];
+            pre_ok = true;
+          }
+        }
         tmem_ld_wait();
         // The piece staged two iterations ago must have been read by its TMA store before its
         // buffer is rewritten.
@@ -282,7 +350,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                    epi.alpha * acc[4 * q + 3]);
             if constexpr (EPI == EPI_STORE_F32) {
               if (r1) {
-                if (full) {
+                if (cur_ok) {
+                  const float4 t = cur[q];
+                  v.x += a1 * t.x; v.y += a1 * t.y; v.z += a1 * t.z; v.w += a1 * t.w;
+                } else if (full) {
                   const float4 t = *reinterpret_cast<const float4*>(r1 + 4 * q);
                   v.x += a1 * t.x; v.y += a1 * t.y; v.z += a1 * t.z; v.w += a1 * t.w;
                 } else {

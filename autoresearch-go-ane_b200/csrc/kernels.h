@@ -38,9 +38,10 @@ void rmsnorm_backward(const float* dy, const float* x, const float* w, const flo
 // In-place interleaved-pair RoPE (ane/train_util.go:204-224) on the q and k column blocks of a packed
 // [M, (H+2KV)*hd] buffer, followed (qk_norm) by the per-head 1.2*rms norm (ane/common.go:199-227);
 // qk_pre, if given, receives the rotated pre-norm q|k ([M, (H+KV)*hd]).
+// Row m holds position pos0 + (m % seq).
 template <typename T>
 void rope_qknorm_forward(T* qkv, T* qk_pre, const float* cosb, const float* sinb, int M, int seq, int H, int KV,
-                         int hd, bool qk_norm, cudaStream_t s);
+                         int hd, bool qk_norm, int pos0, cudaStream_t s);
 // Backward of the above on dq|dk in a packed dqkv buffer: QK-norm backward (ane/common.go:229-270;
 // reference_coeff reproduces its qkScale^2 factor) then inverse rotation unless skip_rope.
 // out_t (optional) receives the whole packed dq|dk|dv row converted to TO (the v columns pass through);
@@ -72,6 +73,18 @@ void attention_forward_simt(const T* qkv, TO* out, float* lse, int B, int seq, i
 template <typename T, typename TD>
 void attention_backward_simt(const T* qkv, const TD* d_out, float* dqkv_f32, int B, int seq, int H, int KV, int hd,
                              float scale, cudaStream_t s);
+
+// KV cache (decode): caches are [B, max_seq, KV*hd]; qkv rows are packed q|k|v as above.
+template <typename T>
+void kv_cache_fill(const T* qkv, T* kcache, T* vcache, int B, int seq, int max_seq, int H, int KV, int hd,
+                   cudaStream_t s);
+template <typename T>
+void kv_cache_append(const T* qkv, T* kcache, T* vcache, int B, int max_seq, int pos, int H, int KV, int hd,
+                     cudaStream_t s);
+// One query row per sequence (qkv [B, ld]) against cache positions 0..pos.
+template <typename T>
+void attention_decode_simt(const T* qkv, const T* kcache, const T* vcache, T* out, int B, int max_seq, int pos, int H,
+                           int KV, int hd, float scale, cudaStream_t s);
 
 // Tensor-core causal attention (bf16 operands, head_dim 64 only; see attention_tc.cu).
 bool attention_tc_supported(int hd);

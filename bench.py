@@ -29,12 +29,39 @@ sys.path.insert(0, os.path.join(ROOT, "autoresearch-go-ane_b200"))
 
 import numpy as np  # noqa: E402
 
-WORKLOAD = dict(dim=768, hidden=2048, n_layers=12, n_heads=12, n_kv_heads=12, vocab=32000, seq=256)
-MICRO_BATCH = 32
+WORKLOADS = {
+    # the configuration the headline metric is quoted on
+    "110m": dict(cfg=dict(dim=768, hidden=2048, n_layers=12, n_heads=12, n_kv_heads=12, vocab=32000, seq=256),
+                 batch=32, arch="llama",
+                 name="110M Llama2-style train step: dim 768, 12 layers, 12 heads, SwiGLU 2048, vocab 32000, seq 256, "
+                      "micro-batch 32 per GPU; Zipf(1.1) tokens, N(0,0.02) weights"),
+    # GQA long-context variant (12 query heads / 4 KV heads, seq 1024, micro-batch 8)
+    "gqa1024": dict(cfg=dict(dim=768, hidden=2048, n_layers=12, n_heads=12, n_kv_heads=4, vocab=32000, seq=1024),
+                    batch=8, arch="llama",
+                    name="GQA variant: dim 768, 12 layers, 12 query / 4 KV heads, SwiGLU 2048, vocab 32000, seq 1024, "
+                         "micro-batch 8 per GPU"),
+    # the network the reference itself trains, at the benchmark's micro-batch
+    "reference": dict(cfg=dict(dim=768, hidden=2048, n_layers=12, n_heads=12, n_kv_heads=12, vocab=32000, seq=256),
+                      batch=32, arch="reference",
+                      name="reference architecture (ReLU^2 FFN, QK-norm, value embeddings, smear, backout, softcap): "
+                           "dim 768, 12 layers, seq 256, micro-batch 32 per GPU"),
+}
+WORKLOAD = WORKLOADS["110m"]["cfg"]
+MICRO_BATCH = WORKLOADS["110m"]["batch"]
 N_STREAM_TOKENS = 1 << 22
-# Algorithmic FLOPs per trained token: 6*N_mm + 3.5*(2*L*T*D), N_mm = matmul parameters incl. classifier.
-N_MM = 12 * (4 * 768 * 768 + 3 * 768 * 2048) + 32000 * 768
-TRAIN_FLOPS_PER_TOKEN = 6 * N_MM + 3.5 * (2 * 12 * 256 * 768)
+
+
+def train_flops_per_token(cfg, arch):
+    """Algorithmic FLOPs per trained token: 6*N_mm + 3.5*(2*L*T*D), N_mm = matmul parameters incl. classifier."""
+    D, Hd, L, H, KV, V, T = (cfg[k] for k in ("dim", "hidden", "n_layers", "n_heads", "n_kv_heads", "vocab", "seq"))
+    hd = D // H
+    n_mm = L * (2 * D * D + 2 * D * KV * hd + (3 if arch == "llama" else 2) * D * Hd) + V * D
+    if arch == "reference":
+        n_mm += D * D  # smear gate
+    return 6 * n_mm + 3.5 * (2 * L * T * D)
+
+
+TRAIN_FLOPS_PER_TOKEN = train_flops_per_token(WORKLOAD, "llama")
 
 
 def zipf_tokens(n, vocab, seed, s=1.1):
@@ -103,14 +130,27 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def init_weights(engine, ane, seed):
+def init_weights(engine, ane, seed, cfg):
+    """N(0, 0.02) for every matrix / embedding the architecture has; scalars keep the library defaults,
+    except the reference architecture's lambdas which take their RandomInit values
+    (ane/stories/weights.go:190-202)."""
     rng = np.random.Generator(np.random.PCG64(seed))
-    L, D, Hd, V = WORKLOAD["n_layers"], WORKLOAD["dim"], WORKLOAD["hidden"], WORKLOAD["vocab"]
-    engine.import_tensor(ane.T_EMBED, 0, (0.02 * rng.standard_normal(V * D)).astype(np.float32))
-    for layer in range(L):
-        for tid, n in ((ane.T_WQ, D * D), (ane.T_WK, D * D), (ane.T_WV, D * D), (ane.T_WO, D * D), (ane.T_W1, Hd * D),
-                       (ane.T_W2, D * Hd), (ane.T_W3, Hd * D)):
-            engine.import_tensor(tid, layer, (0.02 * rng.standard_normal(n)).astype(np.float32))
+    for layer in range(cfg["n_layers"]):
+        for tid in (ane.T_WQ, ane.T_WK, ane.T_WV, ane.T_WO, ane.T_W1, ane.T_W2, ane.T_W3, ane.T_VE_EMBED):
+            n = engine.tensor_size(tid, layer)
+            if n > 0:
+                engine.import_tensor(tid, layer, (0.02 * rng.standard_normal(n)).astype(np.float32))
+        n = engine.tensor_size(ane.T_VE_GATE, layer)
+        if n > 0:
+            engine.import_tensor(ane.T_VE_GATE, layer, (0.02 * rng.random(n)).astype(np.float32))
+    for tid in (ane.T_EMBED, ane.T_SMEAR_GATE):
+        n = engine.tensor_size(tid, 0)
+        if n > 0:
+            engine.import_tensor(tid, 0, (0.02 * rng.standard_normal(n)).astype(np.float32))
+    for tid, val in ((ane.T_X0_LAMBDAS, 0.1), (ane.T_SMEAR_LAMBDA, 0.01), (ane.T_BACKOUT_LAMBDA, 0.01)):
+        n = engine.tensor_size(tid, 0)
+        if n > 0:
+            engine.import_tensor(tid, 0, np.full(n, val, dtype=np.float32))
 
 
 def run_ours(args):
@@ -147,13 +187,18 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    wl = WORKLOADS[args.workload]
+    WORKLOAD, MICRO_BATCH = wl["cfg"], wl["batch"]
+    is_ref_arch = wl["arch"] == "reference"
+    flops_per_token = train_flops_per_token(WORKLOAD, wl["arch"])
     tokens = zipf_tokens(N_STREAM_TOKENS, WORKLOAD["vocab"], seed=0)
-    opts = ane.Options(tokens=tokens, batch=MICRO_BATCH, arch=ane.ARCH_LLAMA, quirks=0, compute_dtype=ane.DTYPE_BF16,
+    opts = ane.Options(tokens=tokens, batch=MICRO_BATCH, arch=ane.ARCH_REFERENCE if is_ref_arch else ane.ARCH_LLAMA,
+                       quirks=1 if is_ref_arch else 0, compute_dtype=ane.DTYPE_BF16,
                        accum_steps=1, lr=3e-4, adam_beta1=0.9, adam_beta2=0.95, weight_decay=0.1, grad_clip=1.0,
                        seed=42, device=local_rank, rank=rank, world_size=world, dp_id=dp_id, ce_chunk_rows=args.ce_chunk,
                        **WORKLOAD)
     e = ane.open(opts)
-    init_weights(e, ane, seed=1234)
+    init_weights(e, ane, seed=1234, cfg=WORKLOAD)
     T = WORKLOAD["seq"]
     tokens_per_step = MICRO_BATCH * T * world
 
@@ -210,10 +255,28 @@ def run_ours(args):
                 "frac": round(achieved / tf_sust, 4), "traffic": None, "peak_source": f"bf16_tflops_sustained ({src})",
                 "kernel": "gemm_tc_kernel (tcgen05 GEMM, all shapes of one step)", "gemm_launches_per_step": gemm_launches,
                 "gemm_ms_per_step": round(gemm_ms, 3),
-                "step_frac_of_burst_peak": round(TRAIN_FLOPS_PER_TOKEN * tokens_per_step / world / (ms_per_step * 1e-3) / 1e12 / tf_burst, 4)}
+                "step_frac_of_burst_peak": round(flops_per_token * tokens_per_step / world / (ms_per_step * 1e-3) / 1e12 / tf_burst, 4)}
+
+    # ---- EvalLogits latency (the second half of the headline metric): one 256-token window per call,
+    # full 32000 x 256 fp32 logits returned to the host in the reference's [vocab][seq] order.
+    window = np.ascontiguousarray(tokens[:T])
+    for _ in range(3):
+        e.eval_logits(window)
+    n_eval = 10
+    t0 = time.perf_counter()
+    for _ in range(n_eval):
+        e.eval_logits(window)
+    eval_ns = (time.perf_counter() - t0) / n_eval * 1e9
+    t0 = time.perf_counter()
+    for _ in range(n_eval):
+        e.eval_loss(window)
+    eval_loss_ns = (time.perf_counter() - t0) / n_eval * 1e9
+    eval_logits = {"ns_per_op": round(eval_ns), "eval_loss_ns_per_op": round(eval_loss_ns),
+                   "d2h_bytes_per_op": WORKLOAD["vocab"] * T * 4,
+                   "note": "host-visible latency of one EvalLogits call (batch 1); EvalLoss keeps logits on the device"}
 
     cpu_baseline = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload == "110m":
         cpu_baseline = cpu_reference_leg(steps=1, warmup=0)
     e.close()
     if rank == 0:
@@ -221,13 +284,12 @@ def run_ours(args):
             "metric": "train tok/s (110M, seq 256)", "value": round(value, 1), "unit": "tok/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "110M Llama2-style train step: dim 768, 12 layers, 12 heads, SwiGLU 2048, vocab 32000, "
-                                   "seq 256, micro-batch 32 per GPU; Zipf(1.1) tokens, N(0,0.02) weights",
+            "config": {"workload": wl["name"],
                        "global_batch": MICRO_BATCH * world, "seq_len": T, "parallelism": f"dp{world}",
-                       "l2_policy": "inputs larger than L2 (2.7 GB of activations per step)"},
+                       "l2_policy": "inputs larger than L2 (GBs of activations per step)"},
             "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "loss": round(float(last.loss), 4),
-            "wall_ms_per_step": round(wall_ms / args.steps, 4),
+            "wall_ms_per_step": round(wall_ms / args.steps, 4), "eval_logits": eval_logits,
         }
         if cpu_baseline is not None:
             line["cpu_baseline"] = cpu_baseline
@@ -337,6 +399,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ce-chunk", type=int, default=0, help="token rows per classifier/CE chunk (0 = library default)")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="110m")
     ap.add_argument("--kernel-case", choices=sorted(KERNEL_CASES), default=None)
     args = ap.parse_args()
     if args.kernel_case:

@@ -188,6 +188,11 @@ int32_t ane_eval_logits(ane_engine* e, const uint16_t* tokens, uint32_t n_seq, f
 /* Fused evaluation loss (no logits leave the device): per window, sum over t < seq-1 of
  * -log softmax(logits[:,t])[tokens[t+1]], the loop of harness.go:46-89 with correct indexing. */
 int32_t ane_eval_loss(ane_engine* e, const uint16_t* tokens, uint32_t n_seq, double* loss_sum, uint64_t* n_positions);
+/* Greedy generation with a KV cache (llama-style architecture): prompts [n_seq][prompt_len] ->
+ * out [n_seq][n_new]; prompt_len + n_new <= seq, n_seq <= batch.  Token choice is the reference's argmax
+ * (ane/train_full.go:344-354: first index of the maximum).  The reference itself has no KV cache. */
+int32_t ane_decode_greedy(ane_engine* e, const uint16_t* prompts, uint32_t n_seq, uint32_t prompt_len, uint32_t n_new,
+                          uint16_t* out);
 int32_t ane_set_lr(ane_engine* e, float lr);   /* ane/engine.go:366 */
 float ane_get_lr(ane_engine* e);               /* ane/engine.go:358 */
 int32_t ane_get_state(ane_engine* e, ane_state* out);       /* ane/engine.go:498 */
