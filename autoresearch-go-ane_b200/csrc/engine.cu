@@ -13,6 +13,7 @@
 
 #include <math.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -175,18 +176,19 @@ class EngineT final : public EngineBase {
     if constexpr (kIsF32) return P_ + off;
     else return Sh_ + off;
   }
-  int gemm(const GemmDesc& d) {
+  int gemm(const GemmDesc& d, cudaStream_t on = nullptr) {
     int rc;
+    cudaStream_t st = on ? on : stream_;
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     if (profiling_) {
       cudaEventCreate(&e0);
       cudaEventCreate(&e1);
-      cudaEventRecord(e0, stream_);
+      cudaEventRecord(e0, st);
     }
-    if constexpr (kIsF32) rc = gemm_f32(d, stream_);
-    else rc = gemm_bf16(d, d_status_, stream_);
+    if constexpr (kIsF32) rc = gemm_f32(d, st);
+    else rc = gemm_bf16(d, d_status_, st);
     if (profiling_) {
-      cudaEventRecord(e1, stream_);
+      cudaEventRecord(e1, st);
       prof_events_.push_back({e0, e1});
       prof_flops_ += 2.0 * (double)d.M * (double)d.N * (double)d.K;
     }
@@ -252,9 +254,17 @@ class EngineT final : public EngineBase {
   float *x0_ = nullptr, *xraw_ = nullptr, *gate_pre_ = nullptr, *gx0_ = nullptr, *gmid_ = nullptr, *dgp_ = nullptr,
         *dxs_ = nullptr, *dxs2_ = nullptr;
   T *x0_t_ = nullptr, *dgp_t_ = nullptr;
-  float *dcur_[2] = {nullptr, nullptr}, *dxn_ = nullptr, *dy_ = nullptr, *dx2_ = nullptr, *dqkv_f32_ = nullptr;
-  T *dcur_t_[2] = {nullptr, nullptr}, *dx2_t_ = nullptr, *dgate_ = nullptr, *dh13_ = nullptr, *datt_ = nullptr,
-    *dqkv_ = nullptr, *xnf_ = nullptr;
+  // Backward operands that the weight-gradient GEMMs read are double-buffered by layer parity, so those
+  // GEMMs can trail the main chain on their own stream by up to two layers.
+  float *dcur_[2] = {nullptr, nullptr}, *dxn_ = nullptr, *dy_ = nullptr, *dx2_[2] = {nullptr, nullptr},
+        *dqkv_f32_[2] = {nullptr, nullptr};
+  T *dcur_t_[2] = {nullptr, nullptr}, *dx2_t_[2] = {nullptr, nullptr}, *dgate_ = nullptr, *dh13_[2] = {nullptr, nullptr},
+    *datt_ = nullptr, *dqkv_[2] = {nullptr, nullptr}, *xnf_ = nullptr;
+  cudaStream_t dw_stream_ = nullptr;       // weight-gradient GEMMs (the reference's async dW workers,
+                                           // ane/train_full.go:969-992, become a second stream)
+  std::vector<cudaEvent_t> ev_dw_done_;    // per layer: its four dW GEMMs have finished
+  cudaEvent_t ev_dw_in_ = nullptr;
+  bool dw_overlap_ = true;
   float *rstdf_ = nullptr, *logits_ = nullptr, *loss_rows_ = nullptr, *inv_valid_ = nullptr, *d_loss_ = nullptr;
   T* dlogits_ = nullptr;
   float *rope_cos_ = nullptr, *rope_sin_ = nullptr;
@@ -309,7 +319,15 @@ void EngineT<T>::destroy() {
       cudaEventDestroy(*e);
       *e = nullptr;
     }
-  for (cudaEvent_t* e : {&ev_bucket_, &ev_comm_done_})
+  for (auto& ev : ev_dw_done_)
+    if (ev) cudaEventDestroy(ev);
+  ev_dw_done_.clear();
+  if (dw_stream_) {
+    cudaStreamSynchronize(dw_stream_);
+    cudaStreamDestroy(dw_stream_);
+    dw_stream_ = nullptr;
+  }
+  for (cudaEvent_t* e : {&ev_bucket_, &ev_comm_done_, &ev_dw_in_})
     if (*e) {
       cudaEventDestroy(*e);
       *e = nullptr;
@@ -451,12 +469,13 @@ int EngineT<T>::alloc_buffers() {
     A(x0_, MD); A(xraw_, MD); A(gate_pre_, MD); A(gx0_, MD); A(gmid_, MD); A(dgp_, MD); A(dxs_, MD); A(dxs2_, MD);
     if (!kIsF32) { A(x0_t_, MD); A(dgp_t_, MD); }
   }
-  A(dcur_[0], MD); A(dcur_[1], MD); A(dxn_, MD); A(dy_, MD); A(dx2_, MD);
-  A(dqkv_f32_, (size_t)M_ * QKVD_);
+  A(dcur_[0], MD); A(dcur_[1], MD); A(dxn_, MD); A(dy_, MD); A(dx2_[0], MD); A(dx2_[1], MD);
+  A(dqkv_f32_[0], (size_t)M_ * QKVD_); A(dqkv_f32_[1], (size_t)M_ * QKVD_);
   if (!kIsF32) {
-    A(dcur_t_[0], MD); A(dcur_t_[1], MD); A(dx2_t_, MD); A(dqkv_, (size_t)M_ * QKVD_);
+    A(dcur_t_[0], MD); A(dcur_t_[1], MD); A(dx2_t_[0], MD); A(dx2_t_[1], MD);
+    A(dqkv_[0], (size_t)M_ * QKVD_); A(dqkv_[1], (size_t)M_ * QKVD_);
   }
-  A(dgate_, (size_t)M_ * Hd_); A(dh13_, (size_t)M_ * N13_); A(datt_, (size_t)M_ * QD_);
+  A(dgate_, (size_t)M_ * Hd_); A(dh13_[0], (size_t)M_ * N13_); A(dh13_[1], (size_t)M_ * N13_); A(datt_, (size_t)M_ * QD_);
   A(xnf_, MD); A(rstdf_, M_); A(att_delta_, (size_t)B_ * H_ * S_);
   A(logits_, (size_t)ce_rows_ * V_); A(dlogits_, (size_t)ce_rows_ * V_);
   A(loss_rows_, M_); A(inv_valid_, B_); A(d_loss_, 4);
@@ -528,6 +547,15 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
   if ((rc = cuda_check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate")) != 0) return rc;
   for (cudaEvent_t* e : {&ev0_, &ev1_, &ev_adam0_, &ev_adam1_})
     if ((rc = cuda_check(cudaEventCreate(e), "cudaEventCreate")) != 0) return rc;
+  if ((rc = cuda_check(cudaStreamCreateWithFlags(&dw_stream_, cudaStreamNonBlocking), "cudaStreamCreate")) != 0) return rc;
+  if ((rc = cuda_check(cudaEventCreateWithFlags(&ev_dw_in_, cudaEventDisableTiming), "cudaEventCreate")) != 0) return rc;
+  ev_dw_done_.assign(o_.n_layers, nullptr);
+  for (auto& ev : ev_dw_done_)
+    if ((rc = cuda_check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate")) != 0) return rc;
+  {
+    const char* env = getenv("ANE_B200_DW_OVERLAP");
+    dw_overlap_ = !(env && env[0] == '0');
+  }
   layout_params();
   if ((rc = alloc_buffers()) != 0) return rc;
   if ((rc = cuda_check(cudaMallocHost(&h_in_, sizeof(uint16_t) * M_), "cudaMallocHost")) != 0) return rc;
@@ -778,7 +806,16 @@ int EngineT<T>::backward_layers(int B) {
     T* dcur_t = tview(dcur_[cur], dcur_t_[cur]);
     float* dprev = dcur_[cur ^ 1];
     T* dprev_t = tview(dcur_[cur ^ 1], dcur_t_[cur ^ 1]);
-    T* dx2_t = tview(dx2_, dx2_t_);
+    const int pb = l & 1;  // buffer parity of this layer
+    float* dx2 = dx2_[pb];
+    T* dx2_t = tview(dx2_[pb], dx2_t_[pb]);
+    T* dh13 = dh13_[pb];
+    float* dqkv_f32 = dqkv_f32_[pb];
+    // Side stream for this layer's weight-gradient GEMMs (main stream when overlap is off or while
+    // per-GEMM profiling wants a serial timeline).
+    cudaStream_t dws = (dw_overlap_ && !profiling_) ? dw_stream_ : stream_;
+    // The parity buffers were last read by the dW GEMMs of layer l+2.
+    if (dws != stream_ && l + 2 < L_) cudaStreamWaitEvent(stream_, ev_dw_done_[l + 2], 0);
     if (o_.debug_taps) cudaMemcpyAsync(a.t_dout, dcur, sizeof(float) * MD, cudaMemcpyDeviceToDevice, stream_);
     // ---- FFN backward
     {
@@ -790,37 +827,41 @@ int EngineT<T>::backward_layers(int B) {
       if ((rc = gemm(g)) != 0) return rc;
     }
     count_launch();
-    if (isN_) relu2_backward<T>(dgate_, a.h13, dh13_, (uint64_t)M * Hd_, stream_);
-    else swiglu_backward<T>(dgate_, a.h13, dh13_, M, Hd_, stream_);
+    if (isN_) relu2_backward<T>(dgate_, a.h13, dh13, (uint64_t)M * Hd_, stream_);
+    else swiglu_backward<T>(dgate_, a.h13, dh13, M, Hd_, stream_);
     if (o_.debug_taps) {
       count_launch();
-      to_f32_kernel<T><<<ew_grid((uint64_t)M * N13_), 256, 0, stream_>>>(dh13_, a.t_dh13, (uint64_t)M * N13_);
+      to_f32_kernel<T><<<ew_grid((uint64_t)M * N13_), 256, 0, stream_>>>(dh13, a.t_dh13, (uint64_t)M * N13_);
     }
     {
       GemmDesc g;  // dx2n = dh13 * W13
-      g.A = dh13_; g.B = wop(s_w13_[l].off); g.C = dxn_;
+      g.A = dh13; g.B = wop(s_w13_[l].off); g.C = dxn_;
       g.M = M; g.N = D_; g.K = N13_; g.lda = N13_; g.ldb = D_; g.ldc = D_; g.b_mn = true; g.out = GEMM_OUT_F32;
       count_launch();
       if ((rc = gemm(g)) != 0) return rc;
     }
     // dx2 = rl*dOut + rms_bwd(dx2n; x2)
     count_launch();
-    rmsnorm_backward<T>(dxn_, a.x2, w_ffn, a.rstd2, dcur, rl, dx2_, tcopy_arg(dx2_t_),
+    rmsnorm_backward<T>(dxn_, a.x2, w_ffn, a.rstd2, dcur, rl, dx2, tcopy_arg(dx2_t_[pb]),
                         isN_ ? nullptr : G_ + s_rms_ffn_[l].off, M, D_, stream_);
-    if (o_.debug_taps) cudaMemcpyAsync(a.t_dx2, dx2_, sizeof(float) * MD, cudaMemcpyDeviceToDevice, stream_);
+    if (o_.debug_taps) cudaMemcpyAsync(a.t_dx2, dx2, sizeof(float) * MD, cudaMemcpyDeviceToDevice, stream_);
     {
       GemmDesc g;  // dW2 += dOut^T * gate
       g.A = dcur_t; g.B = a.gate; g.C = G_ + s_w2_[l].off;
       g.M = D_; g.N = Hd_; g.K = M; g.lda = D_; g.ldb = Hd_; g.ldc = Hd_; g.a_mn = true; g.b_mn = true;
       g.out = GEMM_OUT_ACCUM;
+      if (dws != stream_) {  // operands (dOut copy, gate, dh13, x2n) are ready at this point of the main stream
+        cudaEventRecord(ev_dw_in_, stream_);
+        cudaStreamWaitEvent(dws, ev_dw_in_, 0);
+      }
       count_launch();
-      if ((rc = gemm(g)) != 0) return rc;
+      if ((rc = gemm(g, dws)) != 0) return rc;
       GemmDesc g2;  // dW13 += dh13^T * x2n
-      g2.A = dh13_; g2.B = a.x2n; g2.C = G_ + s_w13_[l].off;
+      g2.A = dh13; g2.B = a.x2n; g2.C = G_ + s_w13_[l].off;
       g2.M = N13_; g2.N = D_; g2.K = M; g2.lda = N13_; g2.ldb = D_; g2.ldc = D_; g2.a_mn = true; g2.b_mn = true;
       g2.out = GEMM_OUT_ACCUM;
       count_launch();
-      if ((rc = gemm(g2)) != 0) return rc;
+      if ((rc = gemm(g2, dws)) != 0) return rc;
     }
     if (isN_) {  // lambda gradients, FFN residual (ane/train_full.go:732-748)
       count_launch(3);
@@ -837,27 +878,27 @@ int EngineT<T>::backward_layers(int B) {
       count_launch();
       if ((rc = gemm(g)) != 0) return rc;
     }
-    T* dqkv = tview(dqkv_f32_, dqkv_);
+    T* dqkv = tview(dqkv_f32, dqkv_[pb]);
     bool dqkv_ready = false;  // true once dqkv holds the final GEMM operand
     if (qkv_f32_) {
-      cudaMemsetAsync(dqkv_f32_, 0, sizeof(float) * (size_t)M * QKVD_, stream_);
+      cudaMemsetAsync(dqkv_f32, 0, sizeof(float) * (size_t)M * QKVD_, stream_);
       count_launch();
-      attention_backward_simt<float, T>((const float*)a.qkv, datt_, dqkv_f32_, B, S_, H_, KV_, hd_, att_scale_bwd, stream_);
+      attention_backward_simt<float, T>((const float*)a.qkv, datt_, dqkv_f32, B, S_, H_, KV_, hd_, att_scale_bwd, stream_);
     } else if constexpr (!kIsF32) {
       if (att_tc_) {
         // Tensor-core path: the kernels undo the rotation and emit bf16 operands directly.
         count_launch(3);
-        attention_backward_tc((const bf16*)a.qkv, a.att, datt_, a.lse, att_delta_, dqkv_, rope_cos_, rope_sin_, B, S_,
+        attention_backward_tc((const bf16*)a.qkv, a.att, datt_, a.lse, att_delta_, dqkv_[pb], rope_cos_, rope_sin_, B, S_,
                               H_, KV_, att_scale_bwd, stream_);
         dqkv_ready = true;
         if (o_.debug_taps) {
           count_launch();
-          to_f32_kernel<T><<<ew_grid((uint64_t)M * QKVD_), 256, 0, stream_>>>(dqkv_, a.t_dqkv, (uint64_t)M * QKVD_);
+          to_f32_kernel<T><<<ew_grid((uint64_t)M * QKVD_), 256, 0, stream_>>>(dqkv_[pb], a.t_dqkv, (uint64_t)M * QKVD_);
         }
       } else {
-        cudaMemsetAsync(dqkv_f32_, 0, sizeof(float) * (size_t)M * QKVD_, stream_);
+        cudaMemsetAsync(dqkv_f32, 0, sizeof(float) * (size_t)M * QKVD_, stream_);
         count_launch();
-        attention_backward_simt<T, T>((const T*)a.qkv, datt_, dqkv_f32_, B, S_, H_, KV_, hd_, att_scale_bwd, stream_);
+        attention_backward_simt<T, T>((const T*)a.qkv, datt_, dqkv_f32, B, S_, H_, KV_, hd_, att_scale_bwd, stream_);
       }
     }
     if (!dqkv_ready) {
@@ -865,10 +906,10 @@ int EngineT<T>::backward_layers(int B) {
       // The fp32 result is kept when something still reads it (value-embedding backward, taps).
       const bool keep_f32 = kIsF32 || is_ve_layer(l) || o_.debug_taps;
       count_launch();
-      rope_qknorm_backward<float, T>(dqkv_f32_, (const float*)a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_,
-                                     quirks_, quirks_, tcopy_arg(dqkv_), keep_f32, stream_);
+      rope_qknorm_backward<float, T>(dqkv_f32, (const float*)a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_,
+                                     quirks_, quirks_, tcopy_arg(dqkv_[pb]), keep_f32, stream_);
       if (o_.debug_taps)
-        cudaMemcpyAsync(a.t_dqkv, dqkv_f32_, sizeof(float) * (size_t)M * QKVD_, cudaMemcpyDeviceToDevice, stream_);
+        cudaMemcpyAsync(a.t_dqkv, dqkv_f32, sizeof(float) * (size_t)M * QKVD_, cudaMemcpyDeviceToDevice, stream_);
     }
     {
       GemmDesc g;  // dxn = dq*Wq + dk*Wk + dv*Wv   (ane/train_full.go:650-665)
@@ -879,12 +920,14 @@ int EngineT<T>::backward_layers(int B) {
     }
     // dprev = rms_bwd(dxn; x) + rl*dx2  (+ value-embedding gate path, + mid-layer backout gradient)
     const bool post_fix = is_ve_layer(l) || (isN_ && l == L_ / 2);
+    // dprev's buffers were read (as that layer's dOut) by the dW2 GEMM of layer l+1.
+    if (dws != stream_ && l + 1 < L_) cudaStreamWaitEvent(stream_, ev_dw_done_[l + 1], 0);
     count_launch();
-    rmsnorm_backward<T>(dxn_, xs_[l], w_att, a.rstd1, dx2_, rl, dprev, post_fix ? nullptr : tcopy_arg(dcur_t_[cur ^ 1]),
+    rmsnorm_backward<T>(dxn_, xs_[l], w_att, a.rstd1, dx2, rl, dprev, post_fix ? nullptr : tcopy_arg(dcur_t_[cur ^ 1]),
                         isN_ ? nullptr : G_ + s_rms_att_[l].off, M, D_, stream_);
     if (is_ve_layer(l)) {
       count_launch();
-      ve_backward<float>(dqkv_f32_, xs_[l], d_in_, P_ + s_ve_embed_[l].off, P_ + s_ve_gate_[l].off, a.ve_act,
+      ve_backward<float>(dqkv_f32, xs_[l], d_in_, P_ + s_ve_embed_[l].off, P_ + s_ve_gate_[l].off, a.ve_act,
                          G_ + s_ve_embed_[l].off, G_ + s_ve_gate_[l].off, dprev, M, D_, H_, KV_, hd_, V_, stream_);
     }
     {
@@ -892,20 +935,25 @@ int EngineT<T>::backward_layers(int B) {
       g.A = dx2_t; g.B = a.att; g.C = G_ + s_wo_[l].off;
       g.M = D_; g.N = QD_; g.K = M; g.lda = D_; g.ldb = QD_; g.ldc = QD_; g.a_mn = true; g.b_mn = true;
       g.out = GEMM_OUT_ACCUM;
+      if (dws != stream_) {
+        cudaEventRecord(ev_dw_in_, stream_);
+        cudaStreamWaitEvent(dws, ev_dw_in_, 0);
+      }
       count_launch();
-      if ((rc = gemm(g)) != 0) return rc;
+      if ((rc = gemm(g, dws)) != 0) return rc;
       GemmDesc g2;  // dWqkv += dqkv^T * xn
       g2.A = dqkv; g2.B = a.xn; g2.C = G_ + s_qkv_[l].off;
       g2.M = QKVD_; g2.N = D_; g2.K = M; g2.lda = QKVD_; g2.ldb = D_; g2.ldc = D_; g2.a_mn = true; g2.b_mn = true;
       g2.out = GEMM_OUT_ACCUM;
       count_launch();
-      if ((rc = gemm(g2)) != 0) return rc;
+      if ((rc = gemm(g2, dws)) != 0) return rc;
+      if (dws != stream_) cudaEventRecord(ev_dw_done_[l], dws);
     }
     if (isN_) {  // lambda gradients, attention residual (ane/train_full.go:770-782)
       count_launch(3);
-      dot_accumulate(dx2_, xs_[l], MD, 1.f, G_ + s_resid_.off + l, stream_);
-      dot_accumulate(dx2_, x0_, MD, 1.f, G_ + s_x0l_.off + l, stream_);
-      axpy_dev(gx0_, dx2_, xl, 1.f, MD, false, stream_);
+      dot_accumulate(dx2, xs_[l], MD, 1.f, G_ + s_resid_.off + l, stream_);
+      dot_accumulate(dx2, x0_, MD, 1.f, G_ + s_x0l_.off + l, stream_);
+      axpy_dev(gx0_, dx2, xl, 1.f, MD, false, stream_);
       if (l == L_ / 2) {  // gradient of the backout term joins at the output of layer L/2-1
         count_launch();
         add_inplace(dprev, gmid_, MD, stream_);
@@ -919,11 +967,13 @@ int EngineT<T>::backward_layers(int B) {
       const size_t lo = s_qkv_[l].off, hi = reduced_lo_;
       cudaEventRecord(ev_bucket_, stream_);
       cudaStreamWaitEvent(comm_stream_, ev_bucket_, 0);
+      if (dws != stream_) cudaStreamWaitEvent(comm_stream_, ev_dw_done_[l], 0);
       if (dp_.all_reduce_sum(G_ + lo, hi - lo, comm_stream_) != 0) return fail(ANE_ERR_NCCL, dp_.last_error());
       reduced_lo_ = lo;
     }
     cur ^= 1;
   }
+  if (dw_overlap_ && !profiling_) cudaStreamWaitEvent(stream_, ev_dw_done_[0], 0);  // joins every dW GEMM (in-order stream)
   float* dcur = dcur_[cur];
   if (isN_) {
     if (quirks_) {  // reference order: x0 gradient joins before the smear backward (ane/train_full.go:789-798)
