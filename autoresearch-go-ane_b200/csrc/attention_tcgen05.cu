@@ -1,0 +1,627 @@
+// Causal attention on the tcgen05 tensor cores (bf16 operands, fp32 accumulation in tensor memory),
+// head_dim 64, sequence length a multiple of 128, GQA-aware.
+//
+// All three kernels share one shape: a RESIDENT pair of 128-row tiles (R1, R2) stays in shared memory
+// for the life of the CTA, a STREAMED pair of 64-row tiles (X1, X2) arrives through a two-stage TMA
+// ring, and every iteration is
+//
+//     MMA 1 :  S' = R1 X1^T   (and dP' = R2 X2^T in the backward)      128 x 64, K = head_dim
+//     SIMT  :  one thread per row of S' reads it from tensor memory, applies mask / softmax algebra
+//              and writes bf16 operand tiles (128B-swizzled, K-major) back to shared memory
+//     MMA 2 :  accumulators (+)= operand tile * X          128 x 64, K = 64 streamed rows
+//
+//   forward :  R1 = Q_i            X = (K_j, V_j)    O_i  = sum_j P_ij V_j         (online softmax)
+//   dK/dV   :  R  = (K_j, V_j)     X = (Q_i, dO_i)   dV_j += P^T dO_i,  dK_j += dS^T Q_i
+//   dQ      :  R  = (Q_i, dO_i)    X = (K_j, V_j)    dQ_i += dS K_j
+//
+// Probabilities never reach global memory; the backward recomputes them from the saved log-sum-exp.
+// The rotation of q and k is undone in the dQ / dK epilogues, so dq|dk|dv leave as bf16 GEMM operands.
+// Every mbarrier wait is bounded and reports through the status word (see common.cuh).
+//
+// Forward restates ane/common.go:61-89, backward ane/train_full.go:261-316 (score scale explicit),
+// the inverse rotation ane/train_util.go:204-224.
+#include "common.cuh"
+#include "gemm.h"
+#include "gemm_tc.cuh"
+#include "kernels.h"
+
+namespace ane {
+
+namespace {
+
+constexpr int A5_THREADS = 320;              // warp 0: TMA, warp 1: MMA, warps 2-9: two threads per tile row
+constexpr int A5_COMPUTE = 256;              // (each takes 32 of the 64 columns of its row)
+constexpr uint32_t kTileR = 128 * 128;       // resident tile: 128 rows x 128 B
+constexpr uint32_t kTileX = 64 * 128;        // streamed tile:  64 rows x 128 B
+constexpr float kLog2e = 1.4426950408889634f;
+
+enum Attn5Mode : int { A5_DKV = 1, A5_DQ = 2 };
+
+struct Attn5Params {
+  const float* lse;    // [B, H, T] natural-log sum-exp of the scaled scores
+  const float* delta;  // [B, H, T] rowsum(dO * O)
+  bf16* dqkv;          // packed like qkv
+  const float* cosb;   // [T, 32] rotation tables or nullptr
+  const float* sinb;
+  int T, H, KV;
+  float scale;
+  int* status;
+};
+
+// Instruction descriptor: bf16 x bf16 -> fp32, M = 128, N = 64; operand majors selectable.
+__host__ __device__ constexpr uint32_t a5_idesc(bool a_mn, bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+__device__ __forceinline__ float fast_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// Stores 8 consecutive values of a row as one 16-byte chunk of a 128B-swizzled K-major operand tile.
+__device__ __forceinline__ void st_chunk(uint8_t* tile, int row, int chunk, const float* v) {
+  uint4 u;
+  u.x = pack2_bf16(v[0], v[1]);
+  u.y = pack2_bf16(v[2], v[3]);
+  u.z = pack2_bf16(v[4], v[5]);
+  u.w = pack2_bf16(v[6], v[7]);
+  *reinterpret_cast<uint4*>(tile + row * 128 + ((chunk ^ (row & 7)) << 4)) = u;
+}
+
+// Writes 32 accumulator columns [32*half, 32*half+32) of a 64-wide row as bf16, optionally undoing the pair
+// rotation (position `pos`); dst points at column 0 of the row.
+__device__ __forceinline__ void store_half_row_bf16(bf16* dst, const float* a, int half, const float* cosb,
+                                                    const float* sinb, int pos) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = a[8 * q + e];
+    if (cosb) {
+      const float4 c = *reinterpret_cast<const float4*>(cosb + (size_t)pos * 32 + half * 16 + q * 4);
+      const float4 s = *reinterpret_cast<const float4*>(sinb + (size_t)pos * 32 + half * 16 + q * 4);
+      const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float ev = v[2 * e], ov = v[2 * e + 1];
+        v[2 * e] = ev * cc[e] + ov * ss[e];
+        v[2 * e + 1] = ov * cc[e] - ev * ss[e];
+      }
+    }
+    uint4 u;
+    u.x = pack2_bf16(v[0], v[1]);
+    u.y = pack2_bf16(v[2], v[3]);
+    u.z = pack2_bf16(v[4], v[5]);
+    u.w = pack2_bf16(v[6], v[7]);
+    *reinterpret_cast<uint4*>(dst + half * 32 + q * 8) = u;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Backward.  MODE A5_DKV: grid (key tiles of 128, B*KV), streams the (Q, dO) 64-row tiles of every
+// query head sharing the KV head (no atomics).  MODE A5_DQ: grid (query tiles of 128, B*H), streams
+// the (K, V) 64-row tiles up to the diagonal.  Two CTAs per SM: 256 TMEM columns and < 100 KB each.
+// ------------------------------------------------------------------------------------------------
+template <int MODE>
+__global__ void __launch_bounds__(A5_THREADS, 2)
+attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_constant__ CUtensorMap tm_qkv_x,
+                 const __grid_constant__ CUtensorMap tm_do_r, const __grid_constant__ CUtensorMap tm_do_x,
+                 Attn5Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[2];
+  __shared__ __align__(8) uint64_t bar_empty[2];
+  __shared__ __align__(8) uint64_t bar_r, bar_s, bar_p, bar_acc;
+  __shared__ uint32_t tmem_slot;
+  __shared__ __align__(16) float ld_s[2][128];  // dK/dV: per streamed query [0,64) lse*log2e, [64,128) delta
+
+  int* status = p.status;
+  if (status != nullptr && *reinterpret_cast<volatile int*>(status) != DEV_OK) return;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sR1 = smem_base, sR2 = sR1 + kTileR;
+  const uint32_t sX1 = sR2 + kTileR;           // [2 stages]
+  const uint32_t sX2 = sX1 + 2 * kTileX;       // [2 stages]
+  const uint32_t sDS = sX2 + 2 * kTileX;       // dS' operand tile
+  const uint32_t sP = sDS + kTileR;            // P' operand tile (dK/dV only)
+  uint8_t* pDS = smem_al + (sDS - smem_base);
+  uint8_t* pP = smem_al + (sP - smem_base);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int T = p.T, H = p.H, KV = p.KV, group = H / KV;
+  const int nT = T / 128;
+  int rt, b, h = 0, kvh, n_per = 0, n_it;
+  if constexpr (MODE == A5_DKV) {
+    rt = blockIdx.x;  // heaviest key tiles (most visible queries) first
+    b = blockIdx.y / KV;
+    kvh = blockIdx.y - b * KV;
+    n_per = T / 64 - 2 * rt;
+    n_it = group * n_per;
+  } else {
+    rt = nT - 1 - blockIdx.x;  // heaviest query tiles first
+    b = blockIdx.y / H;
+    h = blockIdx.y - b * H;
+    kvh = h / group;
+    n_it = 2 * rt + 2;
+  }
+  const int row0 = b * T;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&bar_r), 1);
+    mbar_init(smem_u32(&bar_s), 1);
+    mbar_init(smem_u32(&bar_p), 8);
+    mbar_init(smem_u32(&bar_acc), 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_qkv_r);
+    tma_prefetch_desc(&tm_qkv_x);
+    if constexpr (MODE == A5_DKV) tma_prefetch_desc(&tm_do_x);
+    else tma_prefetch_desc(&tm_do_r);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_slot), 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 64, tA1 = tmem_base + 128, tA2 = tmem_base + 192;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      const uint32_t rbar = smem_u32(&bar_r);
+      mbar_expect_tx(rbar, 2 * kTileR);
+      if constexpr (MODE == A5_DKV) {
+        tma_load_2d(sR1, &tm_qkv_r, rbar, (H + kvh) * 64, row0 + rt * 128);
+        tma_load_2d(sR2, &tm_qkv_r, rbar, (H + KV + kvh) * 64, row0 + rt * 128);
+      } else {
+        tma_load_2d(sR1, &tm_qkv_r, rbar, h * 64, row0 + rt * 128);
+        tma_load_2d(sR2, &tm_do_r, rbar, h * 64, row0 + rt * 128);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it & 1;
+        const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, status, DEV_MBAR_TIMEOUT_PRODUCER)) break;
+        const uint32_t full = smem_u32(&bar_full[s]);
+        mbar_expect_tx(full, 2 * kTileX);
+        if constexpr (MODE == A5_DKV) {
+          const int g = it / n_per;
+          const int qh = 2 * rt + (it - g * n_per);
+          const int hq = kvh * group + g;
+          tma_load_2d(sX1 + s * kTileX, &tm_qkv_x, full, hq * 64, row0 + qh * 64);
+          tma_load_2d(sX2 + s * kTileX, &tm_do_x, full, hq * 64, row0 + qh * 64);
+        } else {
+          tma_load_2d(sX1 + s * kTileX, &tm_qkv_x, full, (H + kvh) * 64, row0 + it * 64);
+          tma_load_2d(sX2 + s * kTileX, &tm_qkv_x, full, (H + KV + kvh) * 64, row0 + it * 64);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ---------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_kk = a5_idesc(false, false);  // both operands K-major
+      constexpr uint32_t idesc_kn = a5_idesc(false, true);   // B stored [k][n]
+      bool ok = mbar_wait(smem_u32(&bar_r), 0, status, DEV_MBAR_TIMEOUT_MMA);
+      for (int it = 0; ok && it < n_it; ++it) {
+        const int s = it & 1;
+        const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&bar_full[s]), ph, status, DEV_MBAR_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t x1 = sX1 + s * kTileX, x2 = sX2 + s * kTileX;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_bf16(tS, make_smem_desc(sR1 + k * 32, 16, 1024), make_smem_desc(x1 + k * 32, 16, 1024), idesc_kk,
+                      k > 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_bf16(tDP, make_smem_desc(sR2 + k * 32, 16, 1024), make_smem_desc(x2 + k * 32, 16, 1024), idesc_kk,
+                      k > 0 ? 1u : 0u);
+        tc_commit(smem_u32(&bar_s));
+        if (!mbar_wait(smem_u32(&bar_p), (uint32_t)it & 1u, status, DEV_MBAR_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        if constexpr (MODE == A5_DKV) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // dV += P^T dO
+            tc_mma_bf16(tA1, make_smem_desc(sP + k * 32, 16, 1024), make_smem_desc(x2 + k * 2048, 8192, 1024),
+                        idesc_kn, (it > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // dK += dS^T Q
+            tc_mma_bf16(tA2, make_smem_desc(sDS + k * 32, 16, 1024), make_smem_desc(x1 + k * 2048, 8192, 1024),
+                        idesc_kn, (it > 0 || k > 0) ? 1u : 0u);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // dQ += dS K
+            tc_mma_bf16(tA1, make_smem_desc(sDS + k * 32, 16, 1024), make_smem_desc(x1 + k * 2048, 8192, 1024),
+                        idesc_kn, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&bar_empty[s]));
+        if (it == n_it - 1) tc_commit(smem_u32(&bar_acc));
+      }
+    }
+  } else {
+    // ------------------------------ two threads per tile row ------------------------------
+    const int lane_group = warp & 3;                 // TMEM lanes this warp may read
+    const int half = (warp - 2) >> 2;                // which 32 of the 64 columns
+    const int r = lane_group * 32 + lane;            // row of the resident tile = TMEM lane
+    const int ct = threadIdx.x - 64;                 // 0..255 within the compute group
+    const uint32_t lane_off = ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(half * 32);
+    const float sl2 = p.scale * kLog2e;
+    const int rpos = rt * 128 + r;                   // position of this row inside its sequence
+    float lse_r = 0.f, del_r = 0.f;
+    if constexpr (MODE == A5_DQ) {
+      lse_r = p.lse[((size_t)b * H + h) * T + rpos] * kLog2e;
+      del_r = p.delta[((size_t)b * H + h) * T + rpos];
+    }
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int s = it & 1;
+      int xpos0;  // sequence position of the first streamed row
+      if constexpr (MODE == A5_DKV) {
+        const int g = it / n_per;
+        const int qh = 2 * rt + (it - g * n_per);
+        const int hq = kvh * group + g;
+        xpos0 = qh * 64;
+        const size_t base = ((size_t)b * H + hq) * T + xpos0;
+        if (ct < 128) ld_s[s][ct] = (ct < 64) ? p.lse[base + ct] * kLog2e : p.delta[base + ct - 64];
+        named_bar_sync(1, A5_COMPUTE);
+      } else {
+        xpos0 = it * 64;
+      }
+      if (!mbar_wait(smem_u32(&bar_s), (uint32_t)it & 1u, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      float sv[32], dv[32];
+      tmem_ld_32x32(tS + lane_off, sv);
+      tmem_ld_32x32(tDP + lane_off, dv);
+      tmem_ld_wait();
+      // Mask only where the tile touches the diagonal (warp-uniform test).
+      bool diag;
+      if constexpr (MODE == A5_DKV) diag = xpos0 < rt * 128 + 127;
+      else diag = xpos0 + 63 > rt * 128;
+      const int c0 = xpos0 + half * 32;  // sequence position of this thread's first column
+      if constexpr (MODE == A5_DKV) {
+        const float4* l4 = reinterpret_cast<const float4*>(&ld_s[s][half * 32]);
+        const float4* d4 = reinterpret_cast<const float4*>(&ld_s[s][64 + half * 32]);
+#pragma unroll
+        for (int e4 = 0; e4 < 8; ++e4) {
+          const float4 l = l4[e4], d = d4[e4];
+          const float lv[4] = {l.x, l.y, l.z, l.w}, dl[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int e = e4 * 4 + k;
+            float pr = fast_ex2(sv[e] * sl2 - lv[k]);
+            if (diag && rpos > c0 + e) pr = 0.f;  // key after query
+            sv[e] = pr;
+            dv[e] = pr * (dv[e] - dl[k]) * p.scale;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float pr = fast_ex2(sv[e] * sl2 - lse_r);
+          if (diag && c0 + e > rpos) pr = 0.f;
+          sv[e] = pr;
+          dv[e] = pr * (dv[e] - del_r) * p.scale;
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if constexpr (MODE == A5_DKV) st_chunk(pP, r, half * 4 + q, sv + 8 * q);
+        st_chunk(pDS, r, half * 4 + q, dv + 8 * q);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_p));
+    }
+    if (ok && mbar_wait(smem_u32(&bar_acc), 0, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
+      tc_fence_after();
+      const int ld = (H + 2 * KV) * 64;
+      bf16* row_ptr = p.dqkv + (size_t)(row0 + rpos) * ld;
+      float a[32];
+      tmem_ld_32x32(tA1 + lane_off, a);
+      tmem_ld_wait();
+      if constexpr (MODE == A5_DKV) {
+        store_half_row_bf16(row_ptr + (size_t)(H + KV + kvh) * 64, a, half, nullptr, nullptr, rpos);  // dV
+        tmem_ld_32x32(tA2 + lane_off, a);
+        tmem_ld_wait();
+        store_half_row_bf16(row_ptr + (size_t)(H + kvh) * 64, a, half, p.cosb, p.sinb, rpos);         // dK
+      } else {
+        store_half_row_bf16(row_ptr + (size_t)h * 64, a, half, p.cosb, p.sinb, rpos);                 // dQ
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// Forward: grid (query tiles of 128, B*H).  Score tiles are double-buffered in tensor memory so the
+// MMA of key block j+1 overlaps the softmax of block j; each P V product lands in its own TMEM
+// buffer and is folded into the register-resident output row (with the running-max correction)
+// one iteration later, off the critical path.
+// ------------------------------------------------------------------------------------------------
+struct Attn5FwdParams {
+  bf16* out;    // [M, H*64]
+  float* lse;   // [B, H, T]
+  int T, H, KV;
+  float scale;
+  int* status;
+};
+
+__global__ void __launch_bounds__(A5_THREADS, 2)
+attn5_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_constant__ CUtensorMap tm_qkv_x,
+                 Attn5FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[2];
+  __shared__ __align__(8) uint64_t bar_empty[2];
+  __shared__ __align__(8) uint64_t bar_s[2];
+  __shared__ __align__(8) uint64_t bar_p[2];
+  __shared__ __align__(8) uint64_t bar_o[2];
+  __shared__ __align__(8) uint64_t bar_r;
+  __shared__ uint32_t tmem_slot;
+  __shared__ float xmax[2][2][128];  // [block parity][column half][row] partial row maxima
+
+  int* status = p.status;
+  if (status != nullptr && *reinterpret_cast<volatile int*>(status) != DEV_OK) return;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sR1 = smem_base;
+  const uint32_t sX1 = sR1 + kTileR;           // K blocks [2 stages]
+  const uint32_t sX2 = sX1 + 2 * kTileX;       // V blocks [2 stages]
+  const uint32_t sP = sX2 + 2 * kTileX;        // P operand tiles [2]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int T = p.T, H = p.H, KV = p.KV, group = H / KV;
+  const int rt = T / 128 - 1 - blockIdx.x;     // heaviest query tiles first
+  const int b = blockIdx.y / H, h = blockIdx.y - b * H, kvh = h / group;
+  const int n_it = 2 * rt + 2;
+  const int row0 = b * T;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+      mbar_init(smem_u32(&bar_s[s]), 1);
+      mbar_init(smem_u32(&bar_p[s]), 8);
+      mbar_init(smem_u32(&bar_o[s]), 1);
+    }
+    mbar_init(smem_u32(&bar_r), 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_qkv_r);
+    tma_prefetch_desc(&tm_qkv_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_slot), 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;  // S[0] S[1] O[0] O[1], 64 columns each
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t rbar = smem_u32(&bar_r);
+      mbar_expect_tx(rbar, kTileR);
+      tma_load_2d(sR1, &tm_qkv_r, rbar, h * 64, row0 + rt * 128);
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it & 1;
+        const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, status, DEV_MBAR_TIMEOUT_PRODUCER)) break;
+        const uint32_t full = smem_u32(&bar_full[s]);
+        mbar_expect_tx(full, 2 * kTileX);
+        tma_load_2d(sX1 + s * kTileX, &tm_qkv_x, full, (H + kvh) * 64, row0 + it * 64);
+        tma_load_2d(sX2 + s * kTileX, &tm_qkv_x, full, (H + KV + kvh) * 64, row0 + it * 64);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_kk = a5_idesc(false, false);
+      constexpr uint32_t idesc_kn = a5_idesc(false, true);
+      auto issue_scores = [&](int it) -> bool {
+        const int s = it & 1;
+        if (!mbar_wait(smem_u32(&bar_full[s]), (uint32_t)(it >> 1) & 1u, status, DEV_MBAR_TIMEOUT_MMA)) return false;
+        tc_fence_after();
+        const uint32_t x1 = sX1 + s * kTileX;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_bf16(tmem_base + (uint32_t)(s * 64), make_smem_desc(sR1 + k * 32, 16, 1024),
+                      make_smem_desc(x1 + k * 32, 16, 1024), idesc_kk, k > 0 ? 1u : 0u);
+        tc_commit(smem_u32(&bar_s[s]));
+        return true;
+      };
+      bool ok = mbar_wait(smem_u32(&bar_r), 0, status, DEV_MBAR_TIMEOUT_MMA);
+      ok = ok && issue_scores(0);
+      for (int it = 0; ok && it < n_it; ++it) {
+        const int s = it & 1;
+        if (it + 1 < n_it && !issue_scores(it + 1)) break;
+        if (!mbar_wait(smem_u32(&bar_p[s]), (uint32_t)(it >> 1) & 1u, status, DEV_MBAR_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t x2 = sX2 + s * kTileX, pt = sP + s * kTileR;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)  // O_part = P V
+          tc_mma_bf16(tmem_base + 128u + (uint32_t)(s * 64), make_smem_desc(pt + k * 32, 16, 1024),
+                      make_smem_desc(x2 + k * 2048, 8192, 1024), idesc_kn, k > 0 ? 1u : 0u);
+        tc_commit(smem_u32(&bar_o[s]));
+        tc_commit(smem_u32(&bar_empty[s]));
+      }
+    }
+  } else {
+    // Two threads per query row: each owns 32 of the 64 key columns of a block and 32 of the 64
+    // output columns.  Partial row maxima are exchanged through shared memory; row sums stay partial
+    // (same running maximum on both sides) and are combined once at the end.
+    const int lane_group = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int r = lane_group * 32 + lane;
+    const uint32_t lane_off = ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(half * 32);
+    const float sl2 = p.scale * kLog2e;
+    const int rpos = rt * 128 + r;
+    float o[32];
+#pragma unroll
+    for (int e = 0; e < 32; ++e) o[e] = 0.f;
+    float m_run = -INFINITY, l_part = 0.f, corr_pending = 0.f;
+    bool ok = true;
+    // o = o * corr + O_part(it), read from tensor memory once its MMA has retired.
+    auto fold = [&](int it, float corr) -> bool {
+      const int s = it & 1;
+      if (!mbar_wait(smem_u32(&bar_o[s]), (uint32_t)(it >> 1) & 1u, status, DEV_MBAR_TIMEOUT_EPILOGUE)) return false;
+      tc_fence_after();
+      float part[32];
+      tmem_ld_32x32(tmem_base + 128u + (uint32_t)(s * 64) + lane_off, part);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) o[e] = o[e] * corr + part[e];
+      return true;
+    };
+    for (int it = 0; it < n_it; ++it) {
+      const int s = it & 1;
+      const int c0 = it * 64 + half * 32;  // sequence position of this thread's first key
+      if (!mbar_wait(smem_u32(&bar_s[s]), (uint32_t)(it >> 1) & 1u, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      float sv[32];
+      tmem_ld_32x32(tmem_base + (uint32_t)(s * 64) + lane_off, sv);
+      tmem_ld_wait();
+      const bool diag = it * 64 + 63 > rt * 128;  // warp-uniform
+      float mx = -INFINITY;
+      if (diag) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          sv[e] = (c0 + e <= rpos) ? sv[e] * sl2 : -INFINITY;
+          mx = fmaxf(mx, sv[e]);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          sv[e] *= sl2;
+          mx = fmaxf(mx, sv[e]);
+        }
+      }
+      xmax[s][half][r] = mx;
+      named_bar_sync(1, A5_COMPUTE);
+      mx = fmaxf(mx, xmax[s][half ^ 1][r]);
+      const float m_new = fmaxf(m_run, mx);  // finite: key 0 is visible to every query
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float corr = fast_ex2(m_run - m_use);
+      float rs = 0.f;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        sv[e] = fast_ex2(sv[e] - m_use);
+        rs += sv[e];
+      }
+      uint8_t* pP = smem_al + (sP - smem_base) + s * kTileR;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) st_chunk(pP, r, half * 4 + q, sv + 8 * q);
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_p[s]));
+      l_part = l_part * corr + rs;
+      m_run = m_new;
+      // Fold the previous block's P V (its MMA ran while this block's softmax did).
+      if (it > 0 && !fold(it - 1, corr_pending)) {
+        ok = false;
+        break;
+      }
+      corr_pending = corr;
+    }
+    if (ok && fold(n_it - 1, corr_pending)) {
+      xmax[0][half][r] = l_part;  // last use of xmax[0] as maxima was two barriers ago at least
+      named_bar_sync(1, A5_COMPUTE);
+      const float l_run = l_part + xmax[0][half ^ 1][r];
+      const float inv = 1.0f / l_run;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) o[e] *= inv;
+      store_half_row_bf16(p.out + (size_t)(row0 + rpos) * (H * 64) + (size_t)h * 64, o, half, nullptr, nullptr, 0);
+      if (half == 0) p.lse[((size_t)b * H + h) * T + rpos] = m_run / kLog2e + logf(l_run);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+constexpr size_t kFwdSmem5 = kTileR + 4 * kTileX + 2 * kTileR + 1024;
+constexpr size_t kDkvSmem5 = 2 * kTileR + 4 * kTileX + 2 * kTileR + 1024;
+constexpr size_t kDqSmem5 = 2 * kTileR + 4 * kTileX + 1 * kTileR + 1024;
+
+bool g_attr5_done = false;
+bool ensure_attrs5() {
+  if (g_attr5_done) return true;
+  if (cudaFuncSetAttribute(attn5_bwd_kernel<A5_DKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDkvSmem5) !=
+          cudaSuccess ||
+      cudaFuncSetAttribute(attn5_bwd_kernel<A5_DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDqSmem5) !=
+          cudaSuccess ||
+      cudaFuncSetAttribute(attn5_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwdSmem5) != cudaSuccess)
+    return false;
+  g_attr5_done = true;
+  return true;
+}
+
+}  // namespace
+
+bool attention_tcgen05_supported(int hd, int seq) { return hd == 64 && seq > 0 && seq % 128 == 0; }
+
+int attention_forward_tcgen05(const bf16* qkv, bf16* out, float* lse, int B, int seq, int H, int KV, float scale,
+                              int* d_status, cudaStream_t s) {
+  if (B <= 0) return 0;
+  if (!attention_tcgen05_supported(64, seq) || H % KV != 0 || !ensure_attrs5()) return -1;
+  const uint64_t M = (uint64_t)B * seq;
+  const uint64_t ld = (uint64_t)(H + 2 * KV) * 64;
+  CUtensorMap tm_qkv_r, tm_qkv_x;
+  if (!make_tmap_2d(&tm_qkv_r, qkv, ld, M, ld, 64, 128, false) || !make_tmap_2d(&tm_qkv_x, qkv, ld, M, ld, 64, 64, false))
+    return -2;
+  Attn5FwdParams p{out, lse, seq, H, KV, scale, d_status};
+  dim3 grid(seq / 128, B * H);
+  attn5_fwd_kernel<<<grid, A5_THREADS, kFwdSmem5, s>>>(tm_qkv_r, tm_qkv_x, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+int attention_backward_tcgen05(const bf16* qkv, const bf16* d_out, const float* lse, const float* delta, bf16* dqkv,
+                               const float* cosb, const float* sinb, int B, int seq, int H, int KV, float scale,
+                               int* d_status, cudaStream_t s) {
+  if (B <= 0) return 0;
+  if (!attention_tcgen05_supported(64, seq) || H % KV != 0 || !ensure_attrs5()) return -1;
+  const uint64_t M = (uint64_t)B * seq;
+  const uint64_t ld = (uint64_t)(H + 2 * KV) * 64;
+  CUtensorMap tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x;
+  if (!make_tmap_2d(&tm_qkv_r, qkv, ld, M, ld, 64, 128, false) || !make_tmap_2d(&tm_qkv_x, qkv, ld, M, ld, 64, 64, false) ||
+      !make_tmap_2d(&tm_do_r, d_out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 128, false) ||
+      !make_tmap_2d(&tm_do_x, d_out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 64, false))
+    return -2;
+  Attn5Params p{lse, delta, dqkv, cosb, sinb, seq, H, KV, scale, d_status};
+  dim3 gk(seq / 128, B * KV);
+  attn5_bwd_kernel<A5_DKV><<<gk, A5_THREADS, kDkvSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, p);
+  dim3 gq(seq / 128, B * H);
+  attn5_bwd_kernel<A5_DQ><<<gq, A5_THREADS, kDqSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace ane

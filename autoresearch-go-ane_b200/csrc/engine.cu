@@ -190,6 +190,7 @@ class EngineT final : public EngineBase {
     if (profiling_) {
       cudaEventRecord(e1, st);
       prof_events_.push_back({e0, e1});
+      prof_shapes_.push_back({d.M, d.N, d.K, (d.a_mn ? 1 : 0) | (d.b_mn ? 2 : 0) | (d.out << 2) | (d.res1 ? 16 : 0)});
       prof_flops_ += 2.0 * (double)d.M * (double)d.N * (double)d.K;
     }
     if (rc != 0) return fail(ANE_ERR_KERNEL, gemm_last_error());
@@ -294,6 +295,8 @@ class EngineT final : public EngineBase {
   std::vector<void*> allocs_;
   bool profiling_ = false;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_events_;
+  struct ProfShape { int M, N, K, flags; };
+  std::vector<ProfShape> prof_shapes_;
   double prof_flops_ = 0.0;
   cudaEvent_t ev_t0_ = nullptr, ev_t1_ = nullptr;
 };
@@ -690,7 +693,7 @@ int EngineT<T>::forward(const uint16_t* d_tok, int B, int Tl, int pos0) {
       attention_forward_simt<float, T>((const float*)a.qkv, a.att, a.lse, B, Tl, H_, KV_, hd_, att_scale, stream_);
     } else if constexpr (!kIsF32) {
       if (att_tc_)
-        attention_forward_tc((const bf16*)a.qkv, a.att, a.lse, B, Tl, H_, KV_, att_scale, stream_);
+        attention_forward_tc((const bf16*)a.qkv, a.att, a.lse, B, Tl, H_, KV_, att_scale, d_status_, stream_);
       else
         attention_forward_simt<T, T>((const T*)a.qkv, a.att, a.lse, B, Tl, H_, KV_, hd_, att_scale, stream_);
     }
@@ -889,7 +892,7 @@ int EngineT<T>::backward_layers(int B) {
         // Tensor-core path: the kernels undo the rotation and emit bf16 operands directly.
         count_launch(3);
         attention_backward_tc((const bf16*)a.qkv, a.att, datt_, a.lse, att_delta_, dqkv_[pb], rope_cos_, rope_sin_, B, S_,
-                              H_, KV_, att_scale_bwd, stream_);
+                              H_, KV_, att_scale_bwd, d_status_, stream_);
         dqkv_ready = true;
         if (o_.debug_taps) {
           count_launch();
@@ -1481,6 +1484,7 @@ int EngineT<T>::profile_gemm(int enable) {
     cudaEventDestroy(pr.second);
   }
   prof_events_.clear();
+  prof_shapes_.clear();
   prof_flops_ = 0.0;
   profiling_ = enable != 0;
   return 0;
@@ -1491,9 +1495,31 @@ int EngineT<T>::profile_read(double* gemm_ms, double* gemm_flops, uint64_t* gemm
   int rc = cuda_check(cudaStreamSynchronize(stream_), "profile sync");
   if (rc) return rc;
   double total = 0.0;
-  for (auto& pr : prof_events_) {
+  // ANE_B200_GEMM_TABLE=1 prints one line per distinct GEMM shape to stderr (launches, time, TFLOP/s).
+  const bool table = getenv("ANE_B200_GEMM_TABLE") != nullptr;
+  struct Row { ProfShape s; int n; double ms; };
+  std::vector<Row> rows;
+  for (size_t i = 0; i < prof_events_.size(); ++i) {
     float ms = 0.f;
-    if (cudaEventElapsedTime(&ms, pr.first, pr.second) == cudaSuccess) total += ms;
+    if (cudaEventElapsedTime(&ms, prof_events_[i].first, prof_events_[i].second) != cudaSuccess) continue;
+    total += ms;
+    if (!table) continue;
+    const ProfShape& s = prof_shapes_[i];
+    bool found = false;
+    for (auto& r : rows)
+      if (r.s.M == s.M && r.s.N == s.N && r.s.K == s.K && r.s.flags == s.flags) {
+        r.n++;
+        r.ms += ms;
+        found = true;
+        break;
+      }
+    if (!found) rows.push_back({s, 1, (double)ms});
+  }
+  for (auto& r : rows) {
+    const double fl = 2.0 * r.s.M * r.s.N * r.s.K * r.n;
+    fprintf(stderr, "gemm M=%d N=%d K=%d a_mn=%d b_mn=%d out=%d res=%d  n=%d  %.1f us/launch  %.0f TFLOP/s\n", r.s.M, r.s.N,
+            r.s.K, r.s.flags & 1, (r.s.flags >> 1) & 1, (r.s.flags >> 2) & 3, (r.s.flags >> 4) & 1, r.n,
+            1e3 * r.ms / r.n, fl / (r.ms * 1e-3) / 1e12);
   }
   if (gemm_ms) *gemm_ms = total;
   if (gemm_flops) *gemm_flops = prof_flops_;

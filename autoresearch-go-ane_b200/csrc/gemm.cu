@@ -96,6 +96,11 @@ static bool make_tmap(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_
   return true;
 }
 
+bool make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
+                  uint32_t box_outer, bool is_f32) {
+  return make_tmap(out, ptr, inner, outer, ld, box_inner, box_outer, is_f32);
+}
+
 template <int BN, bool A_MN, bool B_MN, int EPI>
 static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const EpiParams& epi,
                      const GemmDesc& d, int split_k, int* d_status, cudaStream_t stream) {

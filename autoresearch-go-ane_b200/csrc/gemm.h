@@ -9,6 +9,7 @@
 // (ane/stories/cpu.go:303-385).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -43,6 +44,10 @@ int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream);
 int gemm_f32(const GemmDesc& d, cudaStream_t stream);
 
 int gemm_num_sms();
+// 2-D tensor map over a row-major [outer, inner] buffer (row pitch ld elements) of bf16 (or fp32) with a
+// 128B-swizzled [box_outer, box_inner] box; cached per (device, arguments).  False + gemm_last_error() on failure.
+bool make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
+                  uint32_t box_outer, bool is_f32);
 const char* gemm_last_error();
 
 }  // namespace ane

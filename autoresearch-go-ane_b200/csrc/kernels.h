@@ -89,12 +89,21 @@ void attention_decode_simt(const T* qkv, const T* kcache, const T* vcache, T* ou
 // Tensor-core causal attention (bf16 operands, head_dim 64 only; see attention_tc.cu).
 bool attention_tc_supported(int hd);
 void attention_forward_tc(const bf16* qkv, bf16* out, float* lse, int B, int seq, int H, int KV, float scale,
-                          cudaStream_t s);
+                          int* d_status, cudaStream_t s);
+int attention_forward_tcgen05(const bf16* qkv, bf16* out, float* lse, int B, int seq, int H, int KV, float scale,
+                              int* d_status, cudaStream_t s);
 // Writes every element of dq|dk|dv (bf16, packed like qkv); with cos/sin tables the rotation of q and k
 // is undone in the epilogue (pass nullptr to skip).  `delta` is scratch [B*H*seq].
+// With head_dim 64 and seq % 128 == 0 the tcgen05 kernels (attention_tcgen05.cu) run, else mma.sync ones;
+// `d_status` is the device status word their bounded waits report through.
 void attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* d_out, const float* lse, float* delta,
                            bf16* dqkv, const float* cosb, const float* sinb, int B, int seq, int H, int KV,
-                           float scale, cudaStream_t s);
+                           float scale, int* d_status, cudaStream_t s);
+bool attention_tcgen05_supported(int hd, int seq);
+// Needs delta = rowsum(dO * O) precomputed.  Returns 0 or a negative error code.
+int attention_backward_tcgen05(const bf16* qkv, const bf16* d_out, const float* lse, const float* delta, bf16* dqkv,
+                               const float* cosb, const float* sinb, int B, int seq, int H, int KV, float scale,
+                               int* d_status, cudaStream_t s);
 
 // Cross-entropy over token-major logits [rows, V] (fp32), ane/stories/cpu.go:212-292 with the
 // soft cap of ane/common.go:272-287 folded in:

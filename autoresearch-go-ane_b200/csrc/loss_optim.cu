@@ -178,12 +178,31 @@ void reduce_loss(const float* loss_rows, const float* inv_valid, float* loss_out
 // ------------------------------------------------------------------------------------------
 // Gradient norm (ane/train_full.go:167-196): sum of squares in double.
 // ------------------------------------------------------------------------------------------
-__global__ void sumsq_kernel(const float* __restrict__ g, uint64_t n, float pre_scale, double* __restrict__ acc) {
-  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+__global__ void __launch_bounds__(256)
+sumsq_kernel(const float* __restrict__ g, uint64_t n, float pre_scale, double* __restrict__ acc) {
+  const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
   double local = 0.0;
-  for (; i < n; i += stride) {
-    const float v = g[i] * pre_scale;
+  // 16-byte loads, two in flight per thread, when the buffer is aligned; scalar head/tail otherwise.
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(g) & 15) == 0;
+  const uint64_t n4 = vec_ok ? n / 4 : 0;
+  const float4* g4 = reinterpret_cast<const float4*>(g);
+  uint64_t i = tid;
+  for (; i + stride < n4; i += 2 * stride) {
+    const float4 a = __ldg(g4 + i);
+    const float4 b = __ldg(g4 + i + stride);
+    const float a0 = a.x * pre_scale, a1 = a.y * pre_scale, a2 = a.z * pre_scale, a3 = a.w * pre_scale;
+    const float b0 = b.x * pre_scale, b1 = b.y * pre_scale, b2 = b.z * pre_scale, b3 = b.w * pre_scale;
+    local += (double)a0 * a0 + (double)a1 * a1 + (double)a2 * a2 + (double)a3 * a3;
+    local += (double)b0 * b0 + (double)b1 * b1 + (double)b2 * b2 + (double)b3 * b3;
+  }
+  for (; i < n4; i += stride) {
+    const float4 a = __ldg(g4 + i);
+    const float a0 = a.x * pre_scale, a1 = a.y * pre_scale, a2 = a.z * pre_scale, a3 = a.w * pre_scale;
+    local += (double)a0 * a0 + (double)a1 * a1 + (double)a2 * a2 + (double)a3 * a3;
+  }
+  for (uint64_t j = n4 * 4 + tid; j < n; j += stride) {
+    const float v = g[j] * pre_scale;
     local += (double)v * (double)v;
   }
   local = warp_sum_d(local);

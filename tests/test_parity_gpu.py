@@ -104,6 +104,30 @@ def test_bf16_step_matches_oracle(arch, quirks, extra):
     e.close()
 
 
+@pytest.mark.parametrize("kv_heads,seq", [(1, 256), (2, 384)])
+def test_bf16_attention_multi_tile_sequences(kv_heads, seq):
+    """head_dim 64 with seq a multiple of 128 runs the tcgen05 attention kernels; two and three
+    128-row tiles exercise the off-diagonal iterations, both ring stages and the GQA head loop.
+    Attention gradients (after the inverse rotation) are compared tap by tap."""
+    cfg = dict(dim=128, hidden=256, heads=2, kv_heads=kv_heads, layers=2, vocab=512, seq=seq)
+    hyper = dict(lr=3e-4, accum_steps=1000)
+    m, e = make_pair(ane, cfg, arch=O.ARCH_L, quirks=0, dtype=ane.DTYPE_BF16, batch=2, hyper=hyper, std=0.08)
+    inp, tgt = batch_tokens(cfg, 2, 11, invalid=False)
+    losses = oracle_batch_accumulate(m, inp, tgt, cfg["seq"])
+    r = e.step_tokens(inp, tgt)
+    assert r.device_status == 0
+    assert abs(r.loss - float(np.mean(losses))) < LOSS_TOL
+    errs = tap_errors(m, e, cfg, 2, FWD_TAPS)
+    # wider weights (std 0.08) than the other bf16 cases, so that attention is far from uniform:
+    # the product taps (gate = silu(h1)*h3) then sit slightly above 1e-2
+    assert max(errs.values()) < 1.5e-2, max(errs.items(), key=lambda kv: kv[1])
+    errs = tap_errors(m, e, cfg, 2, [O.TAP_DQ, O.TAP_DK, O.TAP_DV])
+    assert max(errs.values()) < 2e-2, sorted(errs.items(), key=lambda kv: -kv[1])[:4]
+    rep = []
+    assert compare_grads(m, e, rep) < 2e-2, sorted(rep, key=lambda x: -x[2])[:5]
+    e.close()
+
+
 def test_loss_trajectory_20_steps_bf16_reference_arch():
     """20 optimizer steps (accumulation + AdamW included): loss within 1e-3 nats of the oracle each step."""
     cfg = dict(dim=128, hidden=256, heads=4, layers=4, vocab=1024, seq=64)
