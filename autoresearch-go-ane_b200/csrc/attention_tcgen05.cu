@@ -74,35 +74,6 @@ __device__ __forceinline__ void st_chunk(uint8_t* tile, int row, int chunk, cons
   *reinterpret_cast<uint4*>(tile + row * 128 + ((chunk ^ (row & 7)) << 4)) = u;
 }
 
-// Writes 32 accumulator columns [32*half, 32*half+32) of a 64-wide row as bf16, optionally undoing the pair
-// rotation (position `pos`); dst points at column 0 of the row.
-__device__ __forceinline__ void store_half_row_bf16(bf16* dst, const float* a, int half, const float* cosb,
-                                                    const float* sinb, int pos) {
-#pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    float v[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] = a[8 * q + e];
-    if (cosb) {
-      const float4 c = *reinterpret_cast<const float4*>(cosb + (size_t)pos * 32 + half * 16 + q * 4);
-      const float4 s = *reinterpret_cast<const float4*>(sinb + (size_t)pos * 32 + half * 16 + q * 4);
-      const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {s.x, s.y, s.z, s.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float ev = v[2 * e], ov = v[2 * e + 1];
-        v[2 * e] = ev * cc[e] + ov * ss[e];
-        v[2 * e + 1] = ov * cc[e] - ev * ss[e];
-      }
-    }
-    uint4 u;
-    u.x = pack2_bf16(v[0], v[1]);
-    u.y = pack2_bf16(v[2], v[3]);
-    u.z = pack2_bf16(v[4], v[5]);
-    u.w = pack2_bf16(v[6], v[7]);
-    *reinterpret_cast<uint4*>(dst + half * 32 + q * 8) = u;
-  }
-}
-
 // ------------------------------------------------------------------------------------------------
 // Backward.  MODE A5_DKV: grid (key tiles of 128, B*KV), streams the (Q, dO) 64-row tiles of every
 // query head sharing the KV head (no atomics).  MODE A5_DQ: grid (query tiles of 128, B*H), streams
@@ -112,11 +83,12 @@ template <int MODE>
 __global__ void __launch_bounds__(A5_THREADS, 2)
 attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_constant__ CUtensorMap tm_qkv_x,
                  const __grid_constant__ CUtensorMap tm_do_r, const __grid_constant__ CUtensorMap tm_do_x,
-                 Attn5Params p) {
+                 const __grid_constant__ CUtensorMap tm_dqkv, const __grid_constant__ CUtensorMap tm_cos,
+                 const __grid_constant__ CUtensorMap tm_sin, Attn5Params p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[2];
   __shared__ __align__(8) uint64_t bar_empty[2];
-  __shared__ __align__(8) uint64_t bar_r, bar_s, bar_p, bar_acc;
+  __shared__ __align__(8) uint64_t bar_r, bar_s, bar_p, bar_acc, bar_cs;
   __shared__ uint32_t tmem_slot;
   __shared__ __align__(16) float ld_s[2][128];  // dK/dV: per streamed query [0,64) lse*log2e, [64,128) delta
 
@@ -130,13 +102,15 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
   const uint32_t sX2 = sX1 + 2 * kTileX;       // [2 stages]
   const uint32_t sDS = sX2 + 2 * kTileX;       // dS' operand tile
   const uint32_t sP = sDS + kTileR;            // P' operand tile (dK/dV only)
+  uint8_t* pR1 = smem_al;
+  uint8_t* pR2 = smem_al + kTileR;
   uint8_t* pDS = smem_al + (sDS - smem_base);
   uint8_t* pP = smem_al + (sP - smem_base);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int T = p.T, H = p.H, KV = p.KV, group = H / KV;
   const int nT = T / 128;
-  int rt, b, h = 0, kvh, n_per = 0, n_it;
+  int rt, b, h = 0, kvh, n_per = 1, n_it;
   if constexpr (MODE == A5_DKV) {
     rt = blockIdx.x;  // heaviest key tiles (most visible queries) first
     b = blockIdx.y / KV;
@@ -151,6 +125,24 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
     n_it = 2 * rt + 2;
   }
   const int row0 = b * T;
+  const bool rope = p.cosb != nullptr;
+
+  // Streamed tiles of iteration `it` into ring stage it & 1 (the caller has made sure the stage is free).
+  auto issue_x = [&](int it) {
+    const int s = it & 1;
+    const uint32_t full = smem_u32(&bar_full[s]);
+    mbar_expect_tx(full, 2 * kTileX);
+    if constexpr (MODE == A5_DKV) {
+      const int g = it / n_per;
+      const int qh = 2 * rt + (it - g * n_per);
+      const int hq = kvh * group + g;
+      tma_load_2d(sX1 + s * kTileX, &tm_qkv_x, full, hq * 64, row0 + qh * 64);
+      tma_load_2d(sX2 + s * kTileX, &tm_do_x, full, hq * 64, row0 + qh * 64);
+    } else {
+      tma_load_2d(sX1 + s * kTileX, &tm_qkv_x, full, (H + kvh) * 64, row0 + it * 64);
+      tma_load_2d(sX2 + s * kTileX, &tm_qkv_x, full, (H + KV + kvh) * 64, row0 + it * 64);
+    }
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
@@ -161,11 +153,20 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
     mbar_init(smem_u32(&bar_s), 1);
     mbar_init(smem_u32(&bar_p), 8);
     mbar_init(smem_u32(&bar_acc), 1);
+    mbar_init(smem_u32(&bar_cs), 1);
     fence_mbar_init();
-    tma_prefetch_desc(&tm_qkv_r);
-    tma_prefetch_desc(&tm_qkv_x);
-    if constexpr (MODE == A5_DKV) tma_prefetch_desc(&tm_do_x);
-    else tma_prefetch_desc(&tm_do_r);
+    // The first loads leave before the CTA-wide set-up barrier: their latency overlaps the TMEM allocation.
+    const uint32_t rbar = smem_u32(&bar_r);
+    mbar_expect_tx(rbar, 2 * kTileR);
+    if constexpr (MODE == A5_DKV) {
+      tma_load_2d(sR1, &tm_qkv_r, rbar, (H + kvh) * 64, row0 + rt * 128);
+      tma_load_2d(sR2, &tm_qkv_r, rbar, (H + KV + kvh) * 64, row0 + rt * 128);
+    } else {
+      tma_load_2d(sR1, &tm_qkv_r, rbar, h * 64, row0 + rt * 128);
+      tma_load_2d(sR2, &tm_do_r, rbar, h * 64, row0 + rt * 128);
+    }
+    issue_x(0);
+    issue_x(1);  // n_it >= 2 always
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&tmem_slot), 256);
@@ -180,31 +181,11 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
-      const uint32_t rbar = smem_u32(&bar_r);
-      mbar_expect_tx(rbar, 2 * kTileR);
-      if constexpr (MODE == A5_DKV) {
-        tma_load_2d(sR1, &tm_qkv_r, rbar, (H + kvh) * 64, row0 + rt * 128);
-        tma_load_2d(sR2, &tm_qkv_r, rbar, (H + KV + kvh) * 64, row0 + rt * 128);
-      } else {
-        tma_load_2d(sR1, &tm_qkv_r, rbar, h * 64, row0 + rt * 128);
-        tma_load_2d(sR2, &tm_do_r, rbar, h * 64, row0 + rt * 128);
-      }
-      for (int it = 0; it < n_it; ++it) {
+      for (int it = 2; it < n_it; ++it) {
         const int s = it & 1;
         const uint32_t ph = (uint32_t)(it >> 1) & 1u;
         if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, status, DEV_MBAR_TIMEOUT_PRODUCER)) break;
-        const uint32_t full = smem_u32(&bar_full[s]);
-        mbar_expect_tx(full, 2 * kTileX);
-        if constexpr (MODE == A5_DKV) {
-          const int g = it / n_per;
-          const int qh = 2 * rt + (it - g * n_per);
-          const int hq = kvh * group + g;
-          tma_load_2d(sX1 + s * kTileX, &tm_qkv_x, full, hq * 64, row0 + qh * 64);
-          tma_load_2d(sX2 + s * kTileX, &tm_do_x, full, hq * 64, row0 + qh * 64);
-        } else {
-          tma_load_2d(sX1 + s * kTileX, &tm_qkv_x, full, (H + kvh) * 64, row0 + it * 64);
-          tma_load_2d(sX2 + s * kTileX, &tm_qkv_x, full, (H + KV + kvh) * 64, row0 + it * 64);
-        }
+        issue_x(it);
       }
     }
   } else if (warp == 1) {
@@ -230,6 +211,14 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
         tc_commit(smem_u32(&bar_s));
         if (!mbar_wait(smem_u32(&bar_p), (uint32_t)it & 1u, status, DEV_MBAR_TIMEOUT_MMA)) break;
         tc_fence_after();
+        if (it == n_it - 1 && rope) {
+          // The resident tiles have been read for the last time (the row threads saw this iteration's
+          // S' before arriving): their space takes the rotation tables of these 128 positions.
+          const uint32_t cbar = smem_u32(&bar_cs);
+          mbar_expect_tx(cbar, 2 * kTileR);
+          tma_load_2d(sR1, &tm_cos, cbar, 0, rt * 128);
+          tma_load_2d(sR2, &tm_sin, cbar, 0, rt * 128);
+        }
         if constexpr (MODE == A5_DKV) {
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // dV += P^T dO
@@ -327,21 +316,53 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_p));
     }
-    if (ok && mbar_wait(smem_u32(&bar_acc), 0, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
+    // Epilogue: accumulators -> bf16 tiles in the (now idle) operand buffers -> TMA stores.  The inverse
+    // rotation reads its cos/sin rows from the swizzled tiles the MMA thread fetched over R1 / R2.
+    ok = ok && mbar_wait(smem_u32(&bar_acc), 0, status, DEV_MBAR_TIMEOUT_EPILOGUE);
+    if (ok && rope) ok = mbar_wait(smem_u32(&bar_cs), 0, status, DEV_MBAR_TIMEOUT_EPILOGUE);
+    if (ok) {
       tc_fence_after();
-      const int ld = (H + 2 * KV) * 64;
-      bf16* row_ptr = p.dqkv + (size_t)(row0 + rpos) * ld;
       float a[32];
+      auto unrotate = [&]() {
+        if (!rope) return;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int off = r * 128 + (((half * 4 + q) ^ (r & 7)) << 4);
+          const float4 c = *reinterpret_cast<const float4*>(pR1 + off);
+          const float4 s = *reinterpret_cast<const float4*>(pR2 + off);
+          const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float ev = a[8 * q + 2 * e], ov = a[8 * q + 2 * e + 1];
+            a[8 * q + 2 * e] = ev * cc[e] + ov * ss[e];
+            a[8 * q + 2 * e + 1] = ov * cc[e] - ev * ss[e];
+          }
+        }
+      };
       tmem_ld_32x32(tA1 + lane_off, a);
       tmem_ld_wait();
+      if constexpr (MODE == A5_DQ) unrotate();
+#pragma unroll
+      for (int q = 0; q < 4; ++q) st_chunk(MODE == A5_DKV ? pP : pDS, r, half * 4 + q, a + 8 * q);  // dV | dQ
       if constexpr (MODE == A5_DKV) {
-        store_half_row_bf16(row_ptr + (size_t)(H + KV + kvh) * 64, a, half, nullptr, nullptr, rpos);  // dV
         tmem_ld_32x32(tA2 + lane_off, a);
         tmem_ld_wait();
-        store_half_row_bf16(row_ptr + (size_t)(H + kvh) * 64, a, half, p.cosb, p.sinb, rpos);         // dK
-      } else {
-        store_half_row_bf16(row_ptr + (size_t)h * 64, a, half, p.cosb, p.sinb, rpos);                 // dQ
+        unrotate();
+#pragma unroll
+        for (int q = 0; q < 4; ++q) st_chunk(pDS, r, half * 4 + q, a + 8 * q);  // dK
       }
+      fence_proxy_async_smem();
+    }
+    named_bar_sync(1, A5_COMPUTE);
+    if (ok && ct == 0) {
+      if constexpr (MODE == A5_DKV) {
+        tma_store_2d(&tm_dqkv, sP, (H + KV + kvh) * 64, row0 + rt * 128);
+        tma_store_2d(&tm_dqkv, sDS, (H + kvh) * 64, row0 + rt * 128);
+      } else {
+        tma_store_2d(&tm_dqkv, sDS, h * 64, row0 + rt * 128);
+      }
+      tma_store_commit();
+      tma_store_wait_read<0>();
     }
   }
 
@@ -370,7 +391,7 @@ struct Attn5FwdParams {
 
 __global__ void __launch_bounds__(A5_THREADS, 2)
 attn5_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_constant__ CUtensorMap tm_qkv_x,
-                 Attn5FwdParams p) {
+                 const __grid_constant__ CUtensorMap tm_out, Attn5FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[2];
   __shared__ __align__(8) uint64_t bar_empty[2];
@@ -398,6 +419,15 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
   const int n_it = 2 * rt + 2;
   const int row0 = b * T;
 
+  // K and V blocks of iteration `it` into ring stage it & 1 (the caller has made sure the stage is free).
+  auto issue_x = [&](int it) {
+    const int s = it & 1;
+    const uint32_t full = smem_u32(&bar_full[s]);
+    mbar_expect_tx(full, 2 * kTileX);
+    tma_load_2d(sX1 + s * kTileX, &tm_qkv_x, full, (H + kvh) * 64, row0 + it * 64);
+    tma_load_2d(sX2 + s * kTileX, &tm_qkv_x, full, (H + KV + kvh) * 64, row0 + it * 64);
+  };
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
@@ -408,8 +438,12 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
     }
     mbar_init(smem_u32(&bar_r), 1);
     fence_mbar_init();
-    tma_prefetch_desc(&tm_qkv_r);
-    tma_prefetch_desc(&tm_qkv_x);
+    // The first loads leave before the CTA-wide set-up barrier: their latency overlaps the TMEM allocation.
+    const uint32_t rbar = smem_u32(&bar_r);
+    mbar_expect_tx(rbar, kTileR);
+    tma_load_2d(sR1, &tm_qkv_r, rbar, h * 64, row0 + rt * 128);
+    issue_x(0);
+    issue_x(1);  // n_it >= 2 always
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&tmem_slot), 256);
@@ -422,17 +456,11 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
 
   if (warp == 0) {
     if (lane == 0) {
-      const uint32_t rbar = smem_u32(&bar_r);
-      mbar_expect_tx(rbar, kTileR);
-      tma_load_2d(sR1, &tm_qkv_r, rbar, h * 64, row0 + rt * 128);
-      for (int it = 0; it < n_it; ++it) {
+      for (int it = 2; it < n_it; ++it) {
         const int s = it & 1;
         const uint32_t ph = (uint32_t)(it >> 1) & 1u;
         if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, status, DEV_MBAR_TIMEOUT_PRODUCER)) break;
-        const uint32_t full = smem_u32(&bar_full[s]);
-        mbar_expect_tx(full, 2 * kTileX);
-        tma_load_2d(sX1 + s * kTileX, &tm_qkv_x, full, (H + kvh) * 64, row0 + it * 64);
-        tma_load_2d(sX2 + s * kTileX, &tm_qkv_x, full, (H + KV + kvh) * 64, row0 + it * 64);
+        issue_x(it);
       }
     }
   } else if (warp == 1) {
@@ -548,15 +576,28 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
       }
       corr_pending = corr;
     }
-    if (ok && fold(n_it - 1, corr_pending)) {
-      xmax[0][half][r] = l_part;  // last use of xmax[0] as maxima was two barriers ago at least
-      named_bar_sync(1, A5_COMPUTE);
-      const float l_run = l_part + xmax[0][half ^ 1][r];
+    ok = ok && fold(n_it - 1, corr_pending);
+    float l_run = 1.f;
+    if (ok) xmax[0][half][r] = l_part;  // xmax[0] last held maxima at least two barriers ago
+    named_bar_sync(1, A5_COMPUTE);
+    if (ok) {
+      l_run = l_part + xmax[0][half ^ 1][r];
       const float inv = 1.0f / l_run;
 #pragma unroll
       for (int e = 0; e < 32; ++e) o[e] *= inv;
-      store_half_row_bf16(p.out + (size_t)(row0 + rpos) * (H * 64) + (size_t)h * 64, o, half, nullptr, nullptr, 0);
+      // The output tile is staged in the P buffer that the last P V product did not use (n_it is even,
+      // so that is buffer 0; its last reader retired before the previous fold) and leaves by TMA.
+      uint8_t* pO = smem_al + (sP - smem_base);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) st_chunk(pO, r, half * 4 + q, o + 8 * q);
+      fence_proxy_async_smem();
       if (half == 0) p.lse[((size_t)b * H + h) * T + rpos] = m_run / kLog2e + logf(l_run);
+    }
+    named_bar_sync(1, A5_COMPUTE);
+    if (ok && threadIdx.x == 64) {
+      tma_store_2d(&tm_out, sP, h * 64, row0 + rt * 128);
+      tma_store_commit();
+      tma_store_wait_read<0>();
     }
   }
 
@@ -595,12 +636,13 @@ int attention_forward_tcgen05(const bf16* qkv, bf16* out, float* lse, int B, int
   if (!attention_tcgen05_supported(64, seq) || H % KV != 0 || !ensure_attrs5()) return -1;
   const uint64_t M = (uint64_t)B * seq;
   const uint64_t ld = (uint64_t)(H + 2 * KV) * 64;
-  CUtensorMap tm_qkv_r, tm_qkv_x;
-  if (!make_tmap_2d(&tm_qkv_r, qkv, ld, M, ld, 64, 128, false) || !make_tmap_2d(&tm_qkv_x, qkv, ld, M, ld, 64, 64, false))
+  CUtensorMap tm_qkv_r, tm_qkv_x, tm_out;
+  if (!make_tmap_2d(&tm_qkv_r, qkv, ld, M, ld, 64, 128, false) || !make_tmap_2d(&tm_qkv_x, qkv, ld, M, ld, 64, 64, false) ||
+      !make_tmap_2d(&tm_out, out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 128, false))
     return -2;
   Attn5FwdParams p{out, lse, seq, H, KV, scale, d_status};
   dim3 grid(seq / 128, B * H);
-  attn5_fwd_kernel<<<grid, A5_THREADS, kFwdSmem5, s>>>(tm_qkv_r, tm_qkv_x, p);
+  attn5_fwd_kernel<<<grid, A5_THREADS, kFwdSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_out, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -611,16 +653,25 @@ int attention_backward_tcgen05(const bf16* qkv, const bf16* d_out, const float* 
   if (!attention_tcgen05_supported(64, seq) || H % KV != 0 || !ensure_attrs5()) return -1;
   const uint64_t M = (uint64_t)B * seq;
   const uint64_t ld = (uint64_t)(H + 2 * KV) * 64;
-  CUtensorMap tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x;
+  CUtensorMap tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_dqkv, tm_cos, tm_sin;
   if (!make_tmap_2d(&tm_qkv_r, qkv, ld, M, ld, 64, 128, false) || !make_tmap_2d(&tm_qkv_x, qkv, ld, M, ld, 64, 64, false) ||
       !make_tmap_2d(&tm_do_r, d_out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 128, false) ||
-      !make_tmap_2d(&tm_do_x, d_out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 64, false))
+      !make_tmap_2d(&tm_do_x, d_out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 64, false) ||
+      !make_tmap_2d(&tm_dqkv, dqkv, ld, M, ld, 64, 128, false))
     return -2;
+  if (cosb != nullptr && sinb != nullptr) {  // [seq, 32] fp32 tables, one 128-byte row per position
+    if (!make_tmap_2d(&tm_cos, cosb, 32, (uint64_t)seq, 32, 32, 128, true) ||
+        !make_tmap_2d(&tm_sin, sinb, 32, (uint64_t)seq, 32, 32, 128, true))
+      return -2;
+  } else {
+    cosb = sinb = nullptr;
+    tm_cos = tm_sin = tm_dqkv;  // never dereferenced
+  }
   Attn5Params p{lse, delta, dqkv, cosb, sinb, seq, H, KV, scale, d_status};
   dim3 gk(seq / 128, B * KV);
-  attn5_bwd_kernel<A5_DKV><<<gk, A5_THREADS, kDkvSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, p);
+  attn5_bwd_kernel<A5_DKV><<<gk, A5_THREADS, kDkvSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_dqkv, tm_cos, tm_sin, p);
   dim3 gq(seq / 128, B * H);
-  attn5_bwd_kernel<A5_DQ><<<gq, A5_THREADS, kDqSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, p);
+  attn5_bwd_kernel<A5_DQ><<<gq, A5_THREADS, kDqSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_dqkv, tm_cos, tm_sin, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

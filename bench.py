@@ -352,6 +352,9 @@ KERNEL_CASES = {
     "qkv_fwd": (8192, 2304, 768, 0, 0, 0),
     "w2_dx": (8192, 768, 4096, 0, 1, 1),
     "w13_dw": (4096, 768, 8192, 1, 1, 2),
+    "wo_fwd": (8192, 768, 768, 0, 0, 1, 1),          # fp32 out + fp32 residual (x2 = x + att . Wo^T)
+    "w2_fwd": (8192, 768, 2048, 0, 0, 1, 1),
+    "wo_dx": (8192, 768, 768, 0, 1, 0),
 }
 
 
@@ -364,7 +367,8 @@ def run_kernel_case(args):
     from ane import _ffi
 
     lib = _ffi.lib
-    M, N, K, a_mn, b_mn, out_mode = KERNEL_CASES[args.kernel_case]
+    M, N, K, a_mn, b_mn, out_mode = KERNEL_CASES[args.kernel_case][:6]
+    with_res = len(KERNEL_CASES[args.kernel_case]) > 6
     c_bytes = M * N * (2 if out_mode == 0 else 4)
     dA, dB, dC = lib.ane_dev_malloc(M * K * 2), lib.ane_dev_malloc(N * K * 2), lib.ane_dev_malloc(c_bytes)
     for p, n in ((dA, M * K * 2), (dB, N * K * 2), (dC, c_bytes)):
@@ -378,6 +382,10 @@ def run_kernel_case(args):
     g.ldb = N if b_mn else K
     g.ldc = N
     g.a_mn, g.b_mn, g.out_mode, g.alpha = a_mn, b_mn, out_mode, 1.0
+    if with_res:
+        dR = lib.ane_dev_malloc(c_bytes)
+        lib.ane_dev_memset(dR, 0, c_bytes)
+        g.d_res1, g.ldres = dR, N
     for _ in range(args.warmup):
         assert lib.ane_op_gemm(ctypes.byref(g)) == 0, lib.ane_ops_last_error()
     lib.ane_dev_sync()
@@ -389,7 +397,7 @@ def run_kernel_case(args):
     per = ms.value / args.steps
     _, tf_burst, _, src = measured_peaks()
     tflops = 2.0 * M * N * K / (per * 1e-3) / 1e12
-    alg_bytes = (M * K + N * K) * 2 + c_bytes * (2 if out_mode == 2 else 1)
+    alg_bytes = (M * K + N * K) * 2 + c_bytes * (2 if (out_mode == 2 or with_res) else 1)
     print(json.dumps({"kernel_case": args.kernel_case, "shape": [M, N, K], "us_per_launch": round(per * 1e3, 2),
                       "achieved_tflops": round(tflops, 1), "frac_of_burst_peak": round(tflops / tf_burst, 4),
                       "peak_source": src, "algorithmic_bytes": alg_bytes}), flush=True)
