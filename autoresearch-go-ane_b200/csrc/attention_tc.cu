@@ -480,13 +480,13 @@ void attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* d_out, 
                            bf16* dqkv, const float* cosb, const float* sinb, int B, int seq, int H, int KV,
                            float scale, int* d_status, cudaStream_t s) {
   if (B <= 0 || seq <= 0 || !ensure_attrs()) return;
-  const long long warps = (long long)B * seq * H;
-  attention_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>(d_out, out, delta, B, seq, H);
   // ANE_B200_ATT_LEGACY=1 keeps the mma.sync kernels (A/B measurements).
   static const bool legacy = getenv("ANE_B200_ATT_LEGACY") != nullptr;
   if (!legacy && attention_tcgen05_supported(HD, seq) &&
-      attention_backward_tcgen05(qkv, d_out, lse, delta, dqkv, cosb, sinb, B, seq, H, KV, scale, d_status, s) == 0)
+      attention_backward_tcgen05(qkv, out, d_out, lse, delta, dqkv, cosb, sinb, B, seq, H, KV, scale, d_status, s) == 0)
     return;
+  const long long warps = (long long)B * seq * H;
+  attention_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>(d_out, out, delta, B, seq, H);
   dim3 gq((seq + BR - 1) / BR, B * H);
   attention_bwd_dq_tc_kernel<<<gq, ATT_THREADS, kDqSmem, s>>>(qkv, d_out, lse, delta, dqkv, cosb, sinb, seq, H, KV,
                                                                scale);

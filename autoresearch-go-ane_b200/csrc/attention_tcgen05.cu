@@ -39,7 +39,7 @@ enum Attn5Mode : int { A5_DKV = 1, A5_DQ = 2 };
 
 struct Attn5Params {
   const float* lse;    // [B, H, T] natural-log sum-exp of the scaled scores
-  const float* delta;  // [B, H, T] rowsum(dO * O)
+  float* delta;        // [B, H, T] rowsum(dO * O): written by the dQ kernel, read by the dK/dV kernel
   bf16* dqkv;          // packed like qkv
   const float* cosb;   // [T, 32] rotation tables or nullptr
   const float* sinb;
@@ -83,14 +83,15 @@ template <int MODE>
 __global__ void __launch_bounds__(A5_THREADS, 2)
 attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_constant__ CUtensorMap tm_qkv_x,
                  const __grid_constant__ CUtensorMap tm_do_r, const __grid_constant__ CUtensorMap tm_do_x,
-                 const __grid_constant__ CUtensorMap tm_dqkv, const __grid_constant__ CUtensorMap tm_cos,
-                 const __grid_constant__ CUtensorMap tm_sin, Attn5Params p) {
+                 const __grid_constant__ CUtensorMap tm_o_r, const __grid_constant__ CUtensorMap tm_dqkv,
+                 const __grid_constant__ CUtensorMap tm_cos, const __grid_constant__ CUtensorMap tm_sin, Attn5Params p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[2];
   __shared__ __align__(8) uint64_t bar_empty[2];
   __shared__ __align__(8) uint64_t bar_r, bar_s, bar_p, bar_acc, bar_cs;
   __shared__ uint32_t tmem_slot;
   __shared__ __align__(16) float ld_s[2][128];  // dK/dV: per streamed query [0,64) lse*log2e, [64,128) delta
+  __shared__ float xd[2][128];                  // dQ: partial rowsum(dO * O) per column half
 
   int* status = p.status;
   if (status != nullptr && *reinterpret_cast<volatile int*>(status) != DEV_OK) return;
@@ -157,13 +158,15 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
     fence_mbar_init();
     // The first loads leave before the CTA-wide set-up barrier: their latency overlaps the TMEM allocation.
     const uint32_t rbar = smem_u32(&bar_r);
-    mbar_expect_tx(rbar, 2 * kTileR);
+    mbar_expect_tx(rbar, (MODE == A5_DKV ? 2 : 3) * kTileR);
     if constexpr (MODE == A5_DKV) {
       tma_load_2d(sR1, &tm_qkv_r, rbar, (H + kvh) * 64, row0 + rt * 128);
       tma_load_2d(sR2, &tm_qkv_r, rbar, (H + KV + kvh) * 64, row0 + rt * 128);
     } else {
+      // The attention output tile O_i rides along (into the still idle dS' buffer) for delta = rowsum(dO * O).
       tma_load_2d(sR1, &tm_qkv_r, rbar, h * 64, row0 + rt * 128);
       tma_load_2d(sR2, &tm_do_r, rbar, h * 64, row0 + rt * 128);
+      tma_load_2d(sDS, &tm_o_r, rbar, h * 64, row0 + rt * 128);
     }
     issue_x(0);
     issue_x(1);  // n_it >= 2 always
@@ -248,12 +251,34 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
     const float sl2 = p.scale * kLog2e;
     const int rpos = rt * 128 + r;                   // position of this row inside its sequence
     float lse_r = 0.f, del_r = 0.f;
+    bool ok = true;
     if constexpr (MODE == A5_DQ) {
       lse_r = p.lse[((size_t)b * H + h) * T + rpos] * kLog2e;
-      del_r = p.delta[((size_t)b * H + h) * T + rpos];
+      // delta for these 128 queries, from the dO and O tiles in shared memory; the dK/dV kernel that
+      // follows in the stream reads it from global memory.
+      ok = mbar_wait(smem_u32(&bar_r), 0, status, DEV_MBAR_TIMEOUT_EPILOGUE);
+      float part = 0.f;
+      if (ok) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int off = r * 128 + (((half * 4 + q) ^ (r & 7)) << 4);
+          const uint4 a = *reinterpret_cast<const uint4*>(pR2 + off);
+          const uint4 c = *reinterpret_cast<const uint4*>(pDS + off);
+          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+          const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&c);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 af = __bfloat1622float2(a2[e]), cf = __bfloat1622float2(c2[e]);
+            part += af.x * cf.x + af.y * cf.y;
+          }
+        }
+      }
+      xd[half][r] = part;
+      named_bar_sync(1, A5_COMPUTE);  // also: every read of O is done before dS' is written over it
+      del_r = part + xd[half ^ 1][r];
+      if (half == 0) p.delta[((size_t)b * H + h) * T + rpos] = del_r;
     }
-    bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
+    for (int it = 0; ok && it < n_it; ++it) {
       const int s = it & 1;
       int xpos0;  // sequence position of the first streamed row
       if constexpr (MODE == A5_DKV) {
@@ -646,17 +671,19 @@ int attention_forward_tcgen05(const bf16* qkv, bf16* out, float* lse, int B, int
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-int attention_backward_tcgen05(const bf16* qkv, const bf16* d_out, const float* lse, const float* delta, bf16* dqkv,
+int attention_backward_tcgen05(const bf16* qkv, const bf16* out, const bf16* d_out, const float* lse, float* delta,
+                               bf16* dqkv,
                                const float* cosb, const float* sinb, int B, int seq, int H, int KV, float scale,
                                int* d_status, cudaStream_t s) {
   if (B <= 0) return 0;
   if (!attention_tcgen05_supported(64, seq) || H % KV != 0 || !ensure_attrs5()) return -1;
   const uint64_t M = (uint64_t)B * seq;
   const uint64_t ld = (uint64_t)(H + 2 * KV) * 64;
-  CUtensorMap tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_dqkv, tm_cos, tm_sin;
+  CUtensorMap tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_o_r, tm_dqkv, tm_cos, tm_sin;
   if (!make_tmap_2d(&tm_qkv_r, qkv, ld, M, ld, 64, 128, false) || !make_tmap_2d(&tm_qkv_x, qkv, ld, M, ld, 64, 64, false) ||
       !make_tmap_2d(&tm_do_r, d_out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 128, false) ||
       !make_tmap_2d(&tm_do_x, d_out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 64, false) ||
+      !make_tmap_2d(&tm_o_r, out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 128, false) ||
       !make_tmap_2d(&tm_dqkv, dqkv, ld, M, ld, 64, 128, false))
     return -2;
   if (cosb != nullptr && sinb != nullptr) {  // [seq, 32] fp32 tables, one 128-byte row per position
@@ -668,10 +695,13 @@ int attention_backward_tcgen05(const bf16* qkv, const bf16* d_out, const float* 
     tm_cos = tm_sin = tm_dqkv;  // never dereferenced
   }
   Attn5Params p{lse, delta, dqkv, cosb, sinb, seq, H, KV, scale, d_status};
-  dim3 gk(seq / 128, B * KV);
-  attn5_bwd_kernel<A5_DKV><<<gk, A5_THREADS, kDkvSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_dqkv, tm_cos, tm_sin, p);
+  // dQ first: it also produces delta, which the dK/dV kernel consumes.
   dim3 gq(seq / 128, B * H);
-  attn5_bwd_kernel<A5_DQ><<<gq, A5_THREADS, kDqSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_dqkv, tm_cos, tm_sin, p);
+  attn5_bwd_kernel<A5_DQ><<<gq, A5_THREADS, kDqSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_o_r, tm_dqkv, tm_cos,
+                                                           tm_sin, p);
+  dim3 gk(seq / 128, B * KV);
+  attn5_bwd_kernel<A5_DKV><<<gk, A5_THREADS, kDkvSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_o_r, tm_dqkv, tm_cos,
+                                                             tm_sin, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

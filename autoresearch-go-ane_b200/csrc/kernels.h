@@ -100,8 +100,9 @@ void attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* d_out, 
                            bf16* dqkv, const float* cosb, const float* sinb, int B, int seq, int H, int KV,
                            float scale, int* d_status, cudaStream_t s);
 bool attention_tcgen05_supported(int hd, int seq);
-// Needs delta = rowsum(dO * O) precomputed.  Returns 0 or a negative error code.
-int attention_backward_tcgen05(const bf16* qkv, const bf16* d_out, const float* lse, const float* delta, bf16* dqkv,
+// `delta` is scratch [B*H*seq] (rowsum(dO * O), produced by the dQ kernel).  Returns 0 or a negative error code.
+int attention_backward_tcgen05(const bf16* qkv, const bf16* out, const bf16* d_out, const float* lse, float* delta,
+                               bf16* dqkv,
                                const float* cosb, const float* sinb, int B, int seq, int H, int KV, float scale,
                                int* d_status, cudaStream_t s);
 

@@ -189,6 +189,9 @@ def run_ours(args):
 
     wl = WORKLOADS[args.workload]
     WORKLOAD, MICRO_BATCH = wl["cfg"], wl["batch"]
+    if args.batch > 0:  # another micro-batch than the workload's own (the workload name then says so)
+        wl = dict(wl, name=wl["name"].replace(f"micro-batch {MICRO_BATCH} per GPU", f"micro-batch {args.batch} per GPU"))
+        MICRO_BATCH = args.batch
     is_ref_arch = wl["arch"] == "reference"
     flops_per_token = train_flops_per_token(WORKLOAD, wl["arch"])
     tokens = zipf_tokens(N_STREAM_TOKENS, WORKLOAD["vocab"], seed=0)
@@ -412,6 +415,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ce-chunk", type=int, default=0, help="token rows per classifier/CE chunk (0 = library default)")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="110m")
+    ap.add_argument("--batch", type=int, default=0, help="sequences per GPU per step (0 = the workload's own)")
     ap.add_argument("--kernel-case", choices=sorted(KERNEL_CASES), default=None)
     args = ap.parse_args()
     if args.kernel_case:
