@@ -75,8 +75,8 @@ __device__ __forceinline__ void st_chunk(uint8_t* tile, int row, int chunk, cons
 }
 
 // ------------------------------------------------------------------------------------------------
-// Backward.  MODE A5_DKV: grid (key tiles of 128, B*KV), streams the (Q, dO) 64-row tiles of every
-// query head sharing the KV head (no atomics).  MODE A5_DQ: grid (query tiles of 128, B*H), streams
+// Backward.  MODE A5_DKV: grid (B*KV, key tiles of 128), streams the (Q, dO) 64-row tiles of every
+// query head sharing the KV head (no atomics).  MODE A5_DQ: grid (B*H, query tiles of 128), streams
 // the (K, V) 64-row tiles up to the diagonal.  Two CTAs per SM: 256 TMEM columns and < 100 KB each.
 // ------------------------------------------------------------------------------------------------
 template <int MODE>
@@ -88,7 +88,7 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[2];
   __shared__ __align__(8) uint64_t bar_empty[2];
-  __shared__ __align__(8) uint64_t bar_r, bar_s, bar_p, bar_acc, bar_cs;
+  __shared__ __align__(8) uint64_t bar_r, bar_s1, bar_s2, bar_p1, bar_p2, bar_acc, bar_cs;
   __shared__ uint32_t tmem_slot;
   __shared__ __align__(16) float ld_s[2][128];  // dK/dV: per streamed query [0,64) lse*log2e, [64,128) delta
   __shared__ float xd[2][128];                  // dQ: partial rowsum(dO * O) per column half
@@ -113,15 +113,15 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
   const int nT = T / 128;
   int rt, b, h = 0, kvh, n_per = 1, n_it;
   if constexpr (MODE == A5_DKV) {
-    rt = blockIdx.x;  // heaviest key tiles (most visible queries) first
-    b = blockIdx.y / KV;
-    kvh = blockIdx.y - b * KV;
+    rt = blockIdx.y;  // grid (B*KV, tiles): every heaviest key tile (most visible queries) is scheduled first
+    b = blockIdx.x / KV;
+    kvh = blockIdx.x - b * KV;
     n_per = T / 64 - 2 * rt;
     n_it = group * n_per;
   } else {
-    rt = nT - 1 - blockIdx.x;  // heaviest query tiles first
-    b = blockIdx.y / H;
-    h = blockIdx.y - b * H;
+    rt = nT - 1 - blockIdx.y;  // grid (B*H, tiles): heaviest query tiles first
+    b = blockIdx.x / H;
+    h = blockIdx.x - b * H;
     kvh = h / group;
     n_it = 2 * rt + 2;
   }
@@ -151,8 +151,10 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
     mbar_init(smem_u32(&bar_r), 1);
-    mbar_init(smem_u32(&bar_s), 1);
-    mbar_init(smem_u32(&bar_p), 8);
+    mbar_init(smem_u32(&bar_s1), 1);
+    mbar_init(smem_u32(&bar_s2), 1);
+    mbar_init(smem_u32(&bar_p1), 8);
+    mbar_init(smem_u32(&bar_p2), 8);
     mbar_init(smem_u32(&bar_acc), 1);
     mbar_init(smem_u32(&bar_cs), 1);
     fence_mbar_init();
@@ -207,36 +209,35 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
         for (int k = 0; k < 4; ++k)
           tc_mma_bf16(tS, make_smem_desc(sR1 + k * 32, 16, 1024), make_smem_desc(x1 + k * 32, 16, 1024), idesc_kk,
                       k > 0 ? 1u : 0u);
+        tc_commit(smem_u32(&bar_s1));  // the row threads turn S' into P' while dP' is still being computed
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           tc_mma_bf16(tDP, make_smem_desc(sR2 + k * 32, 16, 1024), make_smem_desc(x2 + k * 32, 16, 1024), idesc_kk,
                       k > 0 ? 1u : 0u);
-        tc_commit(smem_u32(&bar_s));
-        if (!mbar_wait(smem_u32(&bar_p), (uint32_t)it & 1u, status, DEV_MBAR_TIMEOUT_MMA)) break;
+        tc_commit(smem_u32(&bar_s2));
+        const uint32_t par = (uint32_t)it & 1u;
+        if constexpr (MODE == A5_DKV) {
+          if (!mbar_wait(smem_u32(&bar_p1), par, status, DEV_MBAR_TIMEOUT_MMA)) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // dV += P^T dO, while the row threads still work on dS'
+            tc_mma_bf16(tA1, make_smem_desc(sP + k * 32, 16, 1024), make_smem_desc(x2 + k * 2048, 8192, 1024),
+                        idesc_kn, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        if (!mbar_wait(smem_u32(&bar_p2), par, status, DEV_MBAR_TIMEOUT_MMA)) break;
         tc_fence_after();
         if (it == n_it - 1 && rope) {
           // The resident tiles have been read for the last time (the row threads saw this iteration's
-          // S' before arriving): their space takes the rotation tables of these 128 positions.
+          // S' and dP' before arriving): their space takes the rotation tables of these 128 positions.
           const uint32_t cbar = smem_u32(&bar_cs);
           mbar_expect_tx(cbar, 2 * kTileR);
           tma_load_2d(sR1, &tm_cos, cbar, 0, rt * 128);
           tma_load_2d(sR2, &tm_sin, cbar, 0, rt * 128);
         }
-        if constexpr (MODE == A5_DKV) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k)  // dV += P^T dO
-            tc_mma_bf16(tA1, make_smem_desc(sP + k * 32, 16, 1024), make_smem_desc(x2 + k * 2048, 8192, 1024),
-                        idesc_kn, (it > 0 || k > 0) ? 1u : 0u);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)  // dK += dS^T Q
-            tc_mma_bf16(tA2, make_smem_desc(sDS + k * 32, 16, 1024), make_smem_desc(x1 + k * 2048, 8192, 1024),
-                        idesc_kn, (it > 0 || k > 0) ? 1u : 0u);
-        } else {
-#pragma unroll
-          for (int k = 0; k < 4; ++k)  // dQ += dS K
-            tc_mma_bf16(tA1, make_smem_desc(sDS + k * 32, 16, 1024), make_smem_desc(x1 + k * 2048, 8192, 1024),
-                        idesc_kn, (it > 0 || k > 0) ? 1u : 0u);
-        }
+        for (int k = 0; k < 4; ++k)  // dK += dS^T Q   |   dQ += dS K
+          tc_mma_bf16(MODE == A5_DKV ? tA2 : tA1, make_smem_desc(sDS + k * 32, 16, 1024),
+                      make_smem_desc(x1 + k * 2048, 8192, 1024), idesc_kn, (it > 0 || k > 0) ? 1u : 0u);
         tc_commit(smem_u32(&bar_empty[s]));
         if (it == n_it - 1) tc_commit(smem_u32(&bar_acc));
       }
@@ -292,14 +293,14 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
       } else {
         xpos0 = it * 64;
       }
-      if (!mbar_wait(smem_u32(&bar_s), (uint32_t)it & 1u, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
+      const uint32_t par = (uint32_t)it & 1u;
+      if (!mbar_wait(smem_u32(&bar_s1), par, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      float sv[32], dv[32];
+      float sv[32];
       tmem_ld_32x32(tS + lane_off, sv);
-      tmem_ld_32x32(tDP + lane_off, dv);
       tmem_ld_wait();
       // Mask only where the tile touches the diagonal (warp-uniform test).
       bool diag;
@@ -308,38 +309,61 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
       const int c0 = xpos0 + half * 32;  // sequence position of this thread's first column
       if constexpr (MODE == A5_DKV) {
         const float4* l4 = reinterpret_cast<const float4*>(&ld_s[s][half * 32]);
-        const float4* d4 = reinterpret_cast<const float4*>(&ld_s[s][64 + half * 32]);
 #pragma unroll
         for (int e4 = 0; e4 < 8; ++e4) {
-          const float4 l = l4[e4], d = d4[e4];
-          const float lv[4] = {l.x, l.y, l.z, l.w}, dl[4] = {d.x, d.y, d.z, d.w};
+          const float4 l = l4[e4];
+          const float lv[4] = {l.x, l.y, l.z, l.w};
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const int e = e4 * 4 + k;
             float pr = fast_ex2(sv[e] * sl2 - lv[k]);
             if (diag && rpos > c0 + e) pr = 0.f;  // key after query
             sv[e] = pr;
-            dv[e] = pr * (dv[e] - dl[k]) * p.scale;
           }
         }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) st_chunk(pP, r, half * 4 + q, sv + 8 * q);
+        tc_fence_before();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_p1));
       } else {
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
           float pr = fast_ex2(sv[e] * sl2 - lse_r);
           if (diag && c0 + e > rpos) pr = 0.f;
           sv[e] = pr;
-          dv[e] = pr * (dv[e] - del_r) * p.scale;
         }
       }
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        if constexpr (MODE == A5_DKV) st_chunk(pP, r, half * 4 + q, sv + 8 * q);
-        st_chunk(pDS, r, half * 4 + q, dv + 8 * q);
+      if (!mbar_wait(smem_u32(&bar_s2), par, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
+        ok = false;
+        break;
       }
+      tc_fence_after();
+      float dv[32];
+      tmem_ld_32x32(tDP + lane_off, dv);
+      tmem_ld_wait();
+      // dS' without the score scale: the accumulators fed by dS' are scaled once in the epilogue.
+      if constexpr (MODE == A5_DKV) {
+        const float4* d4 = reinterpret_cast<const float4*>(&ld_s[s][64 + half * 32]);
+#pragma unroll
+        for (int e4 = 0; e4 < 8; ++e4) {
+          const float4 d = d4[e4];
+          dv[e4 * 4 + 0] = sv[e4 * 4 + 0] * (dv[e4 * 4 + 0] - d.x);
+          dv[e4 * 4 + 1] = sv[e4 * 4 + 1] * (dv[e4 * 4 + 1] - d.y);
+          dv[e4 * 4 + 2] = sv[e4 * 4 + 2] * (dv[e4 * 4 + 2] - d.z);
+          dv[e4 * 4 + 3] = sv[e4 * 4 + 3] * (dv[e4 * 4 + 3] - d.w);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) dv[e] = sv[e] * (dv[e] - del_r);
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) st_chunk(pDS, r, half * 4 + q, dv + 8 * q);
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_p));
+      if (lane == 0) mbar_arrive(smem_u32(&bar_p2));
     }
     // Epilogue: accumulators -> bf16 tiles in the (now idle) operand buffers -> TMA stores.  The inverse
     // rotation reads its cos/sin rows from the swizzled tiles the MMA thread fetched over R1 / R2.
@@ -366,12 +390,18 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
       };
       tmem_ld_32x32(tA1 + lane_off, a);
       tmem_ld_wait();
-      if constexpr (MODE == A5_DQ) unrotate();
+      if constexpr (MODE == A5_DQ) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) a[e] *= p.scale;
+        unrotate();
+      }
 #pragma unroll
       for (int q = 0; q < 4; ++q) st_chunk(MODE == A5_DKV ? pP : pDS, r, half * 4 + q, a + 8 * q);  // dV | dQ
       if constexpr (MODE == A5_DKV) {
         tmem_ld_32x32(tA2 + lane_off, a);
         tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) a[e] *= p.scale;
         unrotate();
 #pragma unroll
         for (int q = 0; q < 4; ++q) st_chunk(pDS, r, half * 4 + q, a + 8 * q);  // dK
@@ -401,7 +431,7 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
 
 
 // ------------------------------------------------------------------------------------------------
-// Forward: grid (query tiles of 128, B*H).  Score tiles are double-buffered in tensor memory so the
+// Forward: grid (B*H, query tiles of 128).  Score tiles are double-buffered in tensor memory so the
 // MMA of key block j+1 overlaps the softmax of block j; each P V product lands in its own TMEM
 // buffer and is folded into the register-resident output row (with the running-max correction)
 // one iteration later, off the critical path.
@@ -439,8 +469,8 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int T = p.T, H = p.H, KV = p.KV, group = H / KV;
-  const int rt = T / 128 - 1 - blockIdx.x;     // heaviest query tiles first
-  const int b = blockIdx.y / H, h = blockIdx.y - b * H, kvh = h / group;
+  const int rt = T / 128 - 1 - blockIdx.y;     // grid (B*H, tiles): heaviest query tiles first
+  const int b = blockIdx.x / H, h = blockIdx.x - b * H, kvh = h / group;
   const int n_it = 2 * rt + 2;
   const int row0 = b * T;
 
@@ -666,7 +696,7 @@ int attention_forward_tcgen05(const bf16* qkv, bf16* out, float* lse, int B, int
       !make_tmap_2d(&tm_out, out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 128, false))
     return -2;
   Attn5FwdParams p{out, lse, seq, H, KV, scale, d_status};
-  dim3 grid(seq / 128, B * H);
+  dim3 grid(B * H, seq / 128);
   attn5_fwd_kernel<<<grid, A5_THREADS, kFwdSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_out, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -696,10 +726,10 @@ int attention_backward_tcgen05(const bf16* qkv, const bf16* out, const bf16* d_o
   }
   Attn5Params p{lse, delta, dqkv, cosb, sinb, seq, H, KV, scale, d_status};
   // dQ first: it also produces delta, which the dK/dV kernel consumes.
-  dim3 gq(seq / 128, B * H);
+  dim3 gq(B * H, seq / 128);
   attn5_bwd_kernel<A5_DQ><<<gq, A5_THREADS, kDqSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_o_r, tm_dqkv, tm_cos,
                                                            tm_sin, p);
-  dim3 gk(seq / 128, B * KV);
+  dim3 gk(B * KV, seq / 128);
   attn5_bwd_kernel<A5_DKV><<<gk, A5_THREADS, kDkvSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_o_r, tm_dqkv, tm_cos,
                                                              tm_sin, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

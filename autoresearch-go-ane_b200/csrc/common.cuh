@@ -25,6 +25,9 @@ enum DeviceStatus : int {
 
 // ~0.5 s at 2 GHz. A healthy pipeline stage completes in microseconds.
 static constexpr long long kWaitBudgetCycles = 1000000000LL;
+// How long one try_wait may keep the thread suspended (it resumes at once when the phase completes);
+// a waiting warp that sleeps leaves its issue slots to the warps that have work.
+static constexpr unsigned kTryWaitHintNs = 20000u;
 
 #if defined(__CUDACC__)
 
@@ -70,11 +73,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     asm volatile(
         "{\n\t"
         ".reg .pred P;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, P;\n\t"
         "}\n"
         : "=r"(done)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kTryWaitHintNs)
         : "memory");
     if (done) return true;
     if (!timing) {
