@@ -158,6 +158,7 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
     mbar_init(smem_u32(&bar_acc), 1);
     mbar_init(smem_u32(&bar_cs), 1);
     fence_mbar_init();
+    pdl_wait();  // everything read below was written by earlier kernels
     // The first loads leave before the CTA-wide set-up barrier: their latency overlaps the TMEM allocation.
     const uint32_t rbar = smem_u32(&bar_r);
     mbar_expect_tx(rbar, (MODE == A5_DKV ? 2 : 3) * kTileR);
@@ -177,9 +178,11 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
     tmem_alloc(smem_u32(&tmem_slot), 256);
     tmem_relinquish();
   }
+  pdl_trigger();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();
   const uint32_t tmem_base = tmem_slot;
   const uint32_t tS = tmem_base, tDP = tmem_base + 64, tA1 = tmem_base + 128, tA2 = tmem_base + 192;
 
@@ -493,6 +496,7 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
     }
     mbar_init(smem_u32(&bar_r), 1);
     fence_mbar_init();
+    pdl_wait();  // q|k|v were written by earlier kernels
     // The first loads leave before the CTA-wide set-up barrier: their latency overlaps the TMEM allocation.
     const uint32_t rbar = smem_u32(&bar_r);
     mbar_expect_tx(rbar, kTileR);
@@ -504,9 +508,11 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
     tmem_alloc(smem_u32(&tmem_slot), 256);
     tmem_relinquish();
   }
+  pdl_trigger();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();
   const uint32_t tmem_base = tmem_slot;  // S[0] S[1] O[0] O[1], 64 columns each
 
   if (warp == 0) {
@@ -697,8 +703,7 @@ int attention_forward_tcgen05(const bf16* qkv, bf16* out, float* lse, int B, int
     return -2;
   Attn5FwdParams p{out, lse, seq, H, KV, scale, d_status};
   dim3 grid(B * H, seq / 128);
-  attn5_fwd_kernel<<<grid, A5_THREADS, kFwdSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_out, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return launch_pdl(attn5_fwd_kernel, grid, dim3(A5_THREADS), kFwdSmem5, s, tm_qkv_r, tm_qkv_x, tm_out, p) == cudaSuccess ? 0 : -4;
 }
 
 int attention_backward_tcgen05(const bf16* qkv, const bf16* out, const bf16* d_out, const float* lse, float* delta,
@@ -727,11 +732,13 @@ int attention_backward_tcgen05(const bf16* qkv, const bf16* out, const bf16* d_o
   Attn5Params p{lse, delta, dqkv, cosb, sinb, seq, H, KV, scale, d_status};
   // dQ first: it also produces delta, which the dK/dV kernel consumes.
   dim3 gq(B * H, seq / 128);
-  attn5_bwd_kernel<A5_DQ><<<gq, A5_THREADS, kDqSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_o_r, tm_dqkv, tm_cos,
-                                                           tm_sin, p);
+  if (launch_pdl(attn5_bwd_kernel<A5_DQ>, gq, dim3(A5_THREADS), kDqSmem5, s, tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_o_r,
+                 tm_dqkv, tm_cos, tm_sin, p) != cudaSuccess)
+    return -4;
   dim3 gk(B * KV, seq / 128);
-  attn5_bwd_kernel<A5_DKV><<<gk, A5_THREADS, kDkvSmem5, s>>>(tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_o_r, tm_dqkv, tm_cos,
-                                                             tm_sin, p);
+  if (launch_pdl(attn5_bwd_kernel<A5_DKV>, gk, dim3(A5_THREADS), kDkvSmem5, s, tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_o_r,
+                 tm_dqkv, tm_cos, tm_sin, p) != cudaSuccess)
+    return -4;
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -114,6 +114,8 @@ __global__ void rope_qknorm_forward_kernel(T* __restrict__ qkv, T* __restrict__ 
 template <typename T>
 __global__ void rope_only_forward_kernel(T* __restrict__ qkv, const float* __restrict__ cosb,
                                          const float* __restrict__ sinb, int M, int seq, int H, int KV, int hd, int pos0) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int VN = Vec16<T>::N;
   const int qk_cols = (H + KV) * hd;
   const int vec_per_row = qk_cols / VN;
@@ -146,7 +148,7 @@ void rope_qknorm_forward(T* qkv, T* qk_pre, const float* cosb, const float* sinb
   if (!qk_norm) {
     const uint64_t n = (uint64_t)M * (H + KV) * hd / Vec16<T>::N;
     if (!n) return;
-    rope_only_forward_kernel<T><<<grid_for(n, 256), 256, 0, s>>>(qkv, cosb, sinb, M, seq, H, KV, hd, pos0);
+    launch_pdl(rope_only_forward_kernel<T>, dim3(grid_for(n, 256)), dim3(256), 0, s, qkv, cosb, sinb, M, seq, H, KV, hd, pos0);
     return;
   }
   const long long warps = (long long)M * (H + KV);
@@ -270,6 +272,8 @@ __global__ void relu2_backward_kernel(const T* __restrict__ dgate, const T* __re
 }
 template <typename T>
 __global__ void swiglu_forward_kernel(const T* __restrict__ h13, T* __restrict__ gate, int M, int Hd) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int VN = Vec16<T>::N;
   const int vec_per_row = Hd / VN;
   uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -294,6 +298,8 @@ __global__ void swiglu_forward_kernel(const T* __restrict__ h13, T* __restrict__
 template <typename T>
 __global__ void swiglu_backward_kernel(const T* __restrict__ dgate, const T* __restrict__ h13, T* __restrict__ dh13,
                                        int M, int Hd) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int VN = Vec16<T>::N;
   const int vec_per_row = Hd / VN;
   uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -338,13 +344,13 @@ template <typename T>
 void swiglu_forward(const T* h13, T* gate, int M, int Hd, cudaStream_t s) {
   const uint64_t n = (uint64_t)M * Hd / Vec16<T>::N;
   if (!n) return;
-  swiglu_forward_kernel<T><<<grid_for(n, 256), 256, 0, s>>>(h13, gate, M, Hd);
+  launch_pdl(swiglu_forward_kernel<T>, dim3(grid_for(n, 256)), dim3(256), 0, s, h13, gate, M, Hd);
 }
 template <typename T>
 void swiglu_backward(const T* dgate, const T* h13, T* dh13, int M, int Hd, cudaStream_t s) {
   const uint64_t n = (uint64_t)M * Hd / Vec16<T>::N;
   if (!n) return;
-  swiglu_backward_kernel<T><<<grid_for(n, 256), 256, 0, s>>>(dgate, h13, dh13, M, Hd);
+  launch_pdl(swiglu_backward_kernel<T>, dim3(grid_for(n, 256)), dim3(256), 0, s, dgate, h13, dh13, M, Hd);
 }
 template void relu2_forward<float>(const float*, float*, uint64_t, cudaStream_t);
 template void relu2_forward<bf16>(const bf16*, bf16*, uint64_t, cudaStream_t);

@@ -3,6 +3,7 @@
 
 #include <cuda.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <map>
@@ -16,6 +17,14 @@ namespace ane {
 
 static thread_local std::string g_gemm_err;
 const char* gemm_last_error() { return g_gemm_err.c_str(); }
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("ANE_B200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
 
 int gemm_num_sms() {
   static int sms[64] = {0};
@@ -127,8 +136,8 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     grid = (int)g;
   }
   if (grid < 1) grid = 1;
-  kern<<<grid, GEMM_THREADS, GemmCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, tc, epi, d.M, d.N, d.K, split_k, d_status);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), GemmCfg<BN>::SMEM_BYTES, stream, ta, tb, tc, epi, d.M, d.N,
+                             d.K, split_k, d_status);
   if (e != cudaSuccess) {
     g_gemm_err = std::string("gemm_tc launch: ") + cudaGetErrorString(e);
     return -4;

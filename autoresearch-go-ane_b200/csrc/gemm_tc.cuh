@@ -170,10 +170,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tmem_alloc(smem_u32(&tmem_slot), Cfg::TMEM_COLS);
     tmem_relinquish();
   }
+  pdl_trigger();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  pdl_wait();  // operands, residuals and C belong to earlier kernels: nothing above touched them
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------

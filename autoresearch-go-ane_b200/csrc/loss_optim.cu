@@ -18,6 +18,8 @@ cross_entropy_rows_kernel(const float* __restrict__ logits, const uint16_t* __re
                           const float* __restrict__ inv_valid, TO* __restrict__ dlogits,
                           float* __restrict__ loss_rows, int rows, int row0, int seq, int V, int softcap,
                           float grad_scale) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   if (r >= rows) return;
   const int grow = row0 + r;  // global token row
@@ -113,8 +115,8 @@ void cross_entropy_rows(const float* logits, const uint16_t* targets, const floa
                         float* loss_rows, int rows, int row0, int seq, int V, bool softcap, float grad_scale,
                         cudaStream_t s) {
   if (rows <= 0) return;
-  cross_entropy_rows_kernel<TO><<<rows, kCEThreads, 0, s>>>(logits, targets, inv_valid, dlogits, loss_rows, rows, row0,
-                                                            seq, V, softcap ? 1 : 0, grad_scale);
+  launch_pdl(cross_entropy_rows_kernel<TO>, dim3(rows), dim3(kCEThreads), 0, s, logits, targets, inv_valid, dlogits, loss_rows,
+             rows, row0, seq, V, softcap ? 1 : 0, grad_scale);
 }
 template void cross_entropy_rows<float>(const float*, const uint16_t*, const float*, float*, float*, int, int, int,
                                         int, bool, float, cudaStream_t);

@@ -85,6 +85,8 @@ __device__ __forceinline__ void store4<bf16>(bf16* p, float a, float b, float c,
 template <typename T>
 __global__ void rmsnorm_forward_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
                                        float* __restrict__ rstd, int M, int D) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= M) return;
@@ -111,7 +113,7 @@ template <typename T>
 void rmsnorm_forward(const float* x, const float* w, T* y, float* rstd, int M, int D, cudaStream_t s) {
   if (M <= 0) return;
   const int blocks = (M + kWarpsPerBlock - 1) / kWarpsPerBlock;
-  rmsnorm_forward_kernel<T><<<blocks, kWarpsPerBlock * 32, 0, s>>>(x, w, y, rstd, M, D);
+  launch_pdl(rmsnorm_forward_kernel<T>, dim3(blocks), dim3(kWarpsPerBlock * 32), 0, s, x, w, y, rstd, M, D);
 }
 template void rmsnorm_forward<float>(const float*, const float*, float*, float*, int, int, cudaStream_t);
 template void rmsnorm_forward<bf16>(const float*, const float*, bf16*, float*, int, int, cudaStream_t);
@@ -203,6 +205,8 @@ rmsnorm_backward_reg_kernel(const float* __restrict__ dy, const float* __restric
                             const float* __restrict__ rstd, const float* __restrict__ res,
                             const float* __restrict__ res_scale, float* __restrict__ dx_f32, T* __restrict__ dx_t,
                             float* __restrict__ dw, int M) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int D = 128 * NV;
   __shared__ float s_dw[kWarpsPerBlock][D > 1024 ? 1 : D];
   const int lane = threadIdx.x & 31;
@@ -292,8 +296,8 @@ void rmsnorm_backward(const float* dy, const float* x, const float* w, const flo
     const int rb = std::min(blocks, 148 * 4);
 #define ANE_RMS_BWD_CASE(NV)                                                                                      \
   case NV:                                                                                                         \
-    rmsnorm_backward_reg_kernel<T, NV><<<rb, kWarpsPerBlock * 32, 0, s>>>(dy, x, w, rstd, res, res_scale, dx_f32, \
-                                                                           dx_t, dw, M);                          \
+    launch_pdl(rmsnorm_backward_reg_kernel<T, NV>, dim3(rb), dim3(kWarpsPerBlock * 32), 0, s, dy, x, w, rstd, res,  \
+               res_scale, dx_f32, dx_t, dw, M);                                                                    \
     return;
     switch (D / 128) {
       ANE_RMS_BWD_CASE(1)
