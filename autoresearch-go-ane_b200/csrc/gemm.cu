@@ -110,21 +110,22 @@ bool make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t ou
   return make_tmap(out, ptr, inner, outer, ld, box_inner, box_outer, is_f32);
 }
 
-template <int BN, bool A_MN, bool B_MN, int EPI>
+template <int BN, int MT, bool A_MN, bool B_MN, int EPI>
 static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const EpiParams& epi,
                      const GemmDesc& d, int split_k, int* d_status, cudaStream_t stream) {
-  auto kern = gemm_tc_kernel<BN, A_MN, B_MN, EPI>;
+  auto kern = gemm_tc_kernel<BN, MT, A_MN, B_MN, EPI>;
   static bool attr_set = false;  // per template instantiation
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)GemmCfg<BN>::SMEM_BYTES);
+                                         (int)GemmCfg<BN, MT>::SMEM_BYTES);
     if (e != cudaSuccess) {
       g_gemm_err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e);
       return -3;
     }
     attr_set = true;
   }
-  const int base_tiles = ((d.M + GEMM_BM - 1) / GEMM_BM) * ((d.N + BN - 1) / BN);
+  constexpr int BM_TILE = GEMM_BM * MT;
+  const int base_tiles = ((d.M + BM_TILE - 1) / BM_TILE) * ((d.N + BN - 1) / BN);
   int grid;
   if (split_k > 0) {
     const int tiles = base_tiles * split_k;
@@ -136,7 +137,7 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     grid = (int)g;
   }
   if (grid < 1) grid = 1;
-  cudaError_t e = launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), GemmCfg<BN>::SMEM_BYTES, stream, ta, tb, tc, epi, d.M, d.N,
+  cudaError_t e = launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), GemmCfg<BN, MT>::SMEM_BYTES, stream, ta, tb, tc, epi, d.M, d.N,
                              d.K, split_k, d_status);
   if (e != cudaSuccess) {
     g_gemm_err = std::string("gemm_tc launch: ") + cudaGetErrorString(e);
@@ -145,21 +146,22 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
   return 0;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, int MT, bool A_MN, bool B_MN>
 static int dispatch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const GemmDesc& d, int split_k,
                         int* d_status, cudaStream_t stream) {
   EpiParams epi{d.alpha, d.res1, d.s1, d.res2, d.s2, d.ldres};
   CUtensorMap tc;
   if (d.out == GEMM_OUT_BF16) {
     if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 64, 32, false)) return -2;
-    return launch_tc<BN, A_MN, B_MN, EPI_STORE_BF16>(ta, tb, tc, epi, d, 1, d_status, stream);
+    return launch_tc<BN, MT, A_MN, B_MN, EPI_STORE_BF16>(ta, tb, tc, epi, d, 1, d_status, stream);
   }
   if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 32, 32, true)) return -2;
-  if (d.out == GEMM_OUT_F32) return launch_tc<BN, A_MN, B_MN, EPI_STORE_F32>(ta, tb, tc, epi, d, 1, d_status, stream);
-  return launch_tc<BN, A_MN, B_MN, EPI_REDUCE_F32>(ta, tb, tc, epi, d, split_k, d_status, stream);
+  if (d.out == GEMM_OUT_F32)
+    return launch_tc<BN, MT, A_MN, B_MN, EPI_STORE_F32>(ta, tb, tc, epi, d, 1, d_status, stream);
+  return launch_tc<BN, MT, A_MN, B_MN, EPI_REDUCE_F32>(ta, tb, tc, epi, d, split_k, d_status, stream);
 }
 
-template <int BN>
+template <int BN, int MT>
 static int dispatch_layout(const GemmDesc& d, int split_k, int* d_status, cudaStream_t stream) {
   CUtensorMap ta, tb;
   bool ok;
@@ -169,26 +171,86 @@ static int dispatch_layout(const GemmDesc& d, int split_k, int* d_status, cudaSt
   if (!d.b_mn) ok = make_tmap(&tb, d.B, d.K, d.N, d.ldb, GEMM_BK, BN);
   else         ok = make_tmap(&tb, d.B, d.N, d.K, d.ldb, 64, GEMM_BK);
   if (!ok) return -2;
-  if (!d.a_mn && !d.b_mn) return dispatch_epi<BN, false, false>(ta, tb, d, split_k, d_status, stream);
-  if (!d.a_mn && d.b_mn) return dispatch_epi<BN, false, true>(ta, tb, d, split_k, d_status, stream);
-  if (d.a_mn && d.b_mn) return dispatch_epi<BN, true, true>(ta, tb, d, split_k, d_status, stream);
-  return dispatch_epi<BN, true, false>(ta, tb, d, split_k, d_status, stream);
+  if (!d.a_mn && !d.b_mn) return dispatch_epi<BN, MT, false, false>(ta, tb, d, split_k, d_status, stream);
+  if (!d.a_mn && d.b_mn) return dispatch_epi<BN, MT, false, true>(ta, tb, d, split_k, d_status, stream);
+  if (d.a_mn && d.b_mn) return dispatch_epi<BN, MT, true, true>(ta, tb, d, split_k, d_status, stream);
+  return dispatch_epi<BN, MT, true, false>(ta, tb, d, split_k, d_status, stream);
 }
 
-int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream) {
-  if (d.M <= 0 || d.N <= 0 || d.K <= 0) return 0;
-  if (d.out == GEMM_OUT_F32 && (d.res1 || d.res2) && (d.ldres % 4 != 0 ||
-      (reinterpret_cast<uintptr_t>(d.res1) & 15) != 0 || (reinterpret_cast<uintptr_t>(d.res2) & 15) != 0)) {
-    g_gemm_err = "fp32 residual operands must be 16-byte aligned with ldres % 4 == 0";
-    return -2;
-  }
-  const int sms = gemm_num_sms();
-  const int tiles_m = (d.M + GEMM_BM - 1) / GEMM_BM;
+// ------------------------------------------------------------------------------------------
+// Tile / schedule selection.
+//   128-row tiles: width by a waves x width cost (wider tiles win unless they leave the last wave
+//   mostly empty; 128-wide tiles stall on shared-memory fill); accumulating GEMMs take the width that
+//   pads N least and classic split-K when it fills whole waves, else stream-K.
+//   256-row tiles (two A sub-tiles share each B tile: a third less shared-memory fill per FLOP, but
+//   no second TMEM accumulator set, so the epilogue is not hidden): measured faster by 5-15 % when
+//   the main loop is long (K >= 2048), the 256-row tiles still cover most SMs and the epilogue is
+//   short (no residual; M >= 2048 for weight gradients); slower otherwise.
+// ------------------------------------------------------------------------------------------
+struct GemmPlan {
+  int bn = 256, mt = 1, sched = 1;  // sched > 0: classic persistent with that split-K; 0: stream-K
+};
+
+static GemmPlan plan_gemm(const GemmDesc& d, int sms) {
   const int kblocks = (d.K + GEMM_BK - 1) / GEMM_BK;
-  if (d.out == GEMM_OUT_ACCUM && d.split_k <= 0) {
-    // Accumulating GEMMs (weight gradients) end in reduce-adds anyway.  Tile width = the one that pads N
-    // least (ties: wider); schedule = classic split-K when it fills whole waves, else stream-K (equal
-    // shares of the tile x k-block units per CTA, at the price of about two extra partial epilogues).
+  static const int force_mt = [] {
+    const char* e = getenv("ANE_B200_GEMM_MT");  // 1 or 2 pins the tile height (measurements)
+    return e ? atoi(e) : 0;
+  }();
+  GemmPlan p;
+  const bool accum = d.out == GEMM_OUT_ACCUM;
+  // ---- 256-row tiles
+  if (force_mt != 1 && d.M > 128 && (kblocks >= 32 || force_mt == 2)) {
+    const int tiles_m2 = (d.M + 255) / 256;
+    int bn2 = 256;
+    long pad_best = -1;
+    for (int bn : {256, 192}) {  // least padding of N, ties to the wider tile
+      const long pad = (long)((d.N + bn - 1) / bn) * bn;
+      if (pad_best < 0 || pad < pad_best) {
+        pad_best = pad;
+        bn2 = bn;
+      }
+    }
+    const long tiles2 = (long)tiles_m2 * ((d.N + bn2 - 1) / bn2);
+    if (accum && d.split_k <= 0 && (d.M >= 2048 || force_mt == 2)) {
+      p.mt = 2;
+      p.bn = bn2;
+      int split = (int)(sms / tiles2);
+      int max_split = kblocks / 4;
+      if (max_split < 1) max_split = 1;
+      if (split > max_split) split = max_split;
+      if (split < 1) split = 1;
+      const long waves = (tiles2 * split + sms - 1) / sms;
+      const long classic_cost = waves * ((kblocks + split - 1) / split);
+      const long streamk_cost = (tiles2 * kblocks + sms - 1) / sms + 8;
+      p.sched = (streamk_cost < classic_cost && tiles2 * kblocks >= 8L * sms) ? 0 : split;
+      return p;
+    }
+    if (!accum && ((d.res1 == nullptr && d.res2 == nullptr) || force_mt == 2)) {
+      // whole waves only: a last wave that is mostly empty costs more than the fill saves; and no
+      // residual epilogue, which is long and would no longer hide behind the next tile
+      double best_eff = 0.0;
+      int best_bn = 256;
+      for (int bn : {256, 192}) {
+        const long t = (long)tiles_m2 * ((d.N + bn - 1) / bn);
+        const long waves = (t + sms - 1) / sms;
+        const double eff = (double)t / (double)(waves * sms) * ((double)d.N / (double)(((d.N + bn - 1) / bn) * bn));
+        if (eff > best_eff + 1e-9) {
+          best_eff = eff;
+          best_bn = bn;
+        }
+      }
+      if (force_mt == 2 || best_eff >= 0.8) {
+        p.mt = 2;
+        p.bn = best_bn;
+        p.sched = 1;
+        return p;
+      }
+    }
+  }
+  // ---- 128-row tiles
+  const int tiles_m = (d.M + GEMM_BM - 1) / GEMM_BM;
+  if (accum && d.split_k <= 0) {
     int best_bn = 256;
     long best_pad = -1;
     for (int bn : {256, 192, 128}) {
@@ -207,18 +269,14 @@ int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream) {
     const long waves = ((long)tiles * split + sms - 1) / sms;
     const long classic_cost = waves * ((kblocks + split - 1) / split);
     const long streamk_cost = ((long)tiles * kblocks + sms - 1) / sms + 8;
-    const int sched = (streamk_cost < classic_cost) ? 0 : split;  // 0 selects stream-K in the kernel
-    if (best_bn == 256) return dispatch_layout<256>(d, sched, d_status, stream);
-    if (best_bn == 192) return dispatch_layout<192>(d, sched, d_status, stream);
-    return dispatch_layout<128>(d, sched, d_status, stream);
+    p.bn = best_bn;
+    p.sched = (streamk_cost < classic_cost) ? 0 : split;
+    return p;
   }
-  // Tile width: 128x128 tiles need ~128 B/clk of shared-memory fill per SM and stall on it, so wider
-  // tiles win unless they leave the last wave mostly empty.  Cost model: waves x tile width.
-  int best_bn = 128, best_split = 1;
   long best_cost = -1;
   for (int bn : {256, 192, 128}) {
     const int tiles = tiles_m * ((d.N + bn - 1) / bn);
-    const int split_k = (d.out == GEMM_OUT_ACCUM) ? d.split_k : 1;
+    const int split_k = accum ? d.split_k : 1;
     const long waves = ((long)tiles * split_k + sms - 1) / sms;
     const long kb = (kblocks + split_k - 1) / split_k;
     long cost = waves * kb * bn;
@@ -226,13 +284,28 @@ int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream) {
     if (bn == 192) cost += cost / 10;  // a narrower tile must win clearly
     if (best_cost < 0 || cost < best_cost) {
       best_cost = cost;
-      best_bn = bn;
-      best_split = split_k;
+      p.bn = bn;
+      p.sched = split_k;
     }
   }
-  if (best_bn == 256) return dispatch_layout<256>(d, best_split, d_status, stream);
-  if (best_bn == 192) return dispatch_layout<192>(d, best_split, d_status, stream);
-  return dispatch_layout<128>(d, best_split, d_status, stream);
+  return p;
+}
+
+int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream) {
+  if (d.M <= 0 || d.N <= 0 || d.K <= 0) return 0;
+  if (d.out == GEMM_OUT_F32 && (d.res1 || d.res2) && (d.ldres % 4 != 0 ||
+      (reinterpret_cast<uintptr_t>(d.res1) & 15) != 0 || (reinterpret_cast<uintptr_t>(d.res2) & 15) != 0)) {
+    g_gemm_err = "fp32 residual operands must be 16-byte aligned with ldres % 4 == 0";
+    return -2;
+  }
+  const GemmPlan p = plan_gemm(d, gemm_num_sms());
+  if (p.mt == 2) {
+    if (p.bn == 256) return dispatch_layout<256, 2>(d, p.sched, d_status, stream);
+    return dispatch_layout<192, 2>(d, p.sched, d_status, stream);
+  }
+  if (p.bn == 256) return dispatch_layout<256, 1>(d, p.sched, d_status, stream);
+  if (p.bn == 192) return dispatch_layout<192, 1>(d, p.sched, d_status, stream);
+  return dispatch_layout<128, 1>(d, p.sched, d_status, stream);
 }
 
 // ------------------------------------------------------------------------------------------

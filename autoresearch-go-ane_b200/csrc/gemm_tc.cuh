@@ -27,14 +27,22 @@ static constexpr int GEMM_BM = 128;
 static constexpr int GEMM_BK = 64;
 static constexpr int GEMM_THREADS = 192;
 
-template <int BN>
+// MT = number of 128-row A sub-tiles per output tile.  MT = 2 (256 x BN tiles) shares every B tile between
+// two MMAs, so the shared-memory fill per FLOP drops by a third; its MT*BN accumulator columns leave no
+// room for a second TMEM buffer when BN > 128, so the epilogue of a tile then does not overlap the next
+// tile's main loop -- it pays for long K, not for short K.
+template <int BN, int MT>
 struct GemmCfg {
-  static constexpr int STAGES = (BN == 128) ? 6 : 4;
-  static constexpr uint32_t A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int BM_TILE = GEMM_BM * MT;
+  static constexpr uint32_t A_BYTES = BM_TILE * GEMM_BK * 2;
   static constexpr uint32_t B_BYTES = BN * GEMM_BK * 2;
   static constexpr uint32_t STAGING_BYTES = 4 * 2 * 4096;  // 4 epilogue warps x 2 buffers x (32 rows x 128 B)
+  static constexpr int STAGES_FIT = (int)((232448u - 1024u - STAGING_BYTES) / (A_BYTES + B_BYTES));
+  static constexpr int STAGES = STAGES_FIT > 6 ? 6 : STAGES_FIT;
   static constexpr uint32_t SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + STAGING_BYTES + 1024;  // +1024: alignment
-  static constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+  static constexpr int ACC_COLS = MT * BN;                       // one accumulator set
+  static constexpr int NBUF = (2 * ACC_COLS <= 512) ? 2 : 1;     // TMEM accumulator sets
+  static constexpr uint32_t TMEM_COLS = (NBUF * ACC_COLS <= 256) ? 256 : 512;
 };
 
 // 64-bit shared-memory matrix descriptor (sm_100 format, version field = 1).
@@ -79,8 +87,8 @@ struct EpiParams {
 struct GemmSched {
   int tiles_m, tiles, kblocks, split_k, kb_per_split, total_work, w;
   long long u, u1;
-  __device__ __forceinline__ void init(int M, int N, int K, int BN, int split) {
-    tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
+  __device__ __forceinline__ void init(int M, int N, int K, int BM_TILE, int BN, int split) {
+    tiles_m = (M + BM_TILE - 1) / BM_TILE;
     const int tiles_n = (N + BN - 1) / BN;
     tiles = tiles_m * tiles_n;
     kblocks = (K + GEMM_BK - 1) / GEMM_BK;
@@ -123,20 +131,21 @@ struct GemmSched {
   }
 };
 
-template <int BN, bool A_MN, bool B_MN, int EPI>
+template <int BN, int MT, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, EpiParams epi, int M, int N, int K, int split_k,
                int* status) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, MT>;
   constexpr int STAGES = Cfg::STAGES;
-  constexpr int BM = GEMM_BM, BK = GEMM_BK;
+  constexpr int BM = Cfg::BM_TILE, BK = GEMM_BK;
+  constexpr int NBUF = Cfg::NBUF;
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[STAGES];
   __shared__ __align__(8) uint64_t bar_empty[STAGES];
-  __shared__ __align__(8) uint64_t bar_tfull[2];
-  __shared__ __align__(8) uint64_t bar_tempty[2];
+  __shared__ __align__(8) uint64_t bar_tfull[NBUF];
+  __shared__ __align__(8) uint64_t bar_tempty[NBUF];
   __shared__ uint32_t tmem_slot;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -157,7 +166,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < NBUF; ++b) {
       mbar_init(smem_u32(&bar_tfull[b]), 1);
       mbar_init(smem_u32(&bar_tempty[b]), 4);
     }
@@ -184,7 +193,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t phase = 0;
       bool ok = true;
       GemmSched sched;
-      sched.init(M, N, K, BN, split_k);
+      sched.init(M, N, K, BM, BN, split_k);
       int tm, tn, kb0, kb1;
       while (ok && sched.next(tm, tn, kb0, kb1)) {
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -197,7 +206,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t sa = smem_a0 + stage * Cfg::A_BYTES;
           const uint32_t sb = smem_b0 + stage * Cfg::B_BYTES;
           if constexpr (!A_MN) {
-            tma_load_2d(sa, &tmA, full, kb * BK, tm * BM);
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+              tma_load_2d(sa + i * (GEMM_BM * BK * 2), &tmA, full, kb * BK, tm * BM + i * GEMM_BM);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
@@ -219,23 +230,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) |
                                  ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
-                                 ((uint32_t)(BM >> 4) << 24);
+                                 ((uint32_t)(GEMM_BM >> 4) << 24);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
       GemmSched sched;
-      sched.init(M, N, K, BN, split_k);
+      sched.init(M, N, K, BM, BN, split_k);
       int tm, tn, kb0, kb1;
       while (ok && sched.next(tm, tn, kb0, kb1)) {
-        const int buf = local & 1;
-        const uint32_t tphase = (uint32_t)(local >> 1) & 1u;
+        const int buf = local % NBUF;
+        const uint32_t tphase = (uint32_t)(local / NBUF) & 1u;
         if (!mbar_wait(smem_u32(&bar_tempty[buf]), tphase ^ 1u, status, DEV_MBAR_TIMEOUT_MMA)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * Cfg::ACC_COLS);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&bar_full[stage]), phase, status, DEV_MBAR_TIMEOUT_MMA)) {
             ok = false;
@@ -246,12 +257,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t sb = smem_b0 + stage * Cfg::B_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            uint64_t adesc, bdesc;
-            if constexpr (!A_MN) adesc = make_smem_desc(sa + k * 32, 16, 1024);
-            else                 adesc = make_smem_desc(sa + k * 2048, 64 * BK * 2, 1024);
+            uint64_t bdesc;
             if constexpr (!B_MN) bdesc = make_smem_desc(sb + k * 32, 16, 1024);
             else                 bdesc = make_smem_desc(sb + k * 2048, 64 * BK * 2, 1024);
-            tc_mma_bf16(tmem_d, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {  // the A sub-tiles share this B tile
+              uint64_t adesc;
+              const uint32_t sai = sa + i * (GEMM_BM * BK * 2);
+              if constexpr (!A_MN) adesc = make_smem_desc(sai + k * 32, 16, 1024);
+              else                 adesc = make_smem_desc(sai + k * 2048, 64 * BK * 2, 1024);
+              tc_mma_bf16(tmem_d + (uint32_t)(i * BN), adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            }
           }
           tc_commit(smem_u32(&bar_empty[stage]));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -277,31 +293,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (epi.res2) a2 = epi.s2 ? *epi.s2 : 1.f;
     }
     GemmSched sched;
-    sched.init(M, N, K, BN, split_k);
+    sched.init(M, N, K, BM, BN, split_k);
     int tm, tn, kb0, kb1;
     while (ok && sched.next(tm, tn, kb0, kb1)) {
-      const int buf = local & 1;
-      const uint32_t tphase = (uint32_t)(local >> 1) & 1u;
-      const int m_warp = tm * BM + lane_group * 32;
-      const int m = m_warp + lane;
+      const int buf = local % NBUF;
+      const uint32_t tphase = (uint32_t)(local / NBUF) & 1u;
       // Residual rows are fetched one 32-column piece ahead (the first piece while the MMAs of this
       // tile are still running), so their latency is off the epilogue's critical path.
       float4 pre[8];
       bool pre_ok = false;
-      if constexpr (EPI == EPI_STORE_F32) {
-        if (epi.res1 && m < M && tn * BN + 32 <= N) {
-          const float4* rp = reinterpret_cast<const float4*>(epi.res1 + (size_t)m * epi.ldres + tn * BN);
+      auto prefetch_first = [&](int m) {
+        if constexpr (EPI == EPI_STORE_F32) {
+          pre_ok = false;
+          if (epi.res1 && m < M && tn * BN + 32 <= N) {
+            const float4* rp = reinterpret_cast<const float4*>(epi.res1 + (size_t)m * epi.ldres + tn * BN);
 #pragma unroll
-          for (int q = 0; q < 8; ++q) pre[q] = rp[q];
-          pre_ok = true;
+            for (int q = 0; q < 8; ++q) pre[q] = rp[q];
+            pre_ok = true;
+          }
         }
-      }
+      };
+      prefetch_first(tm * BM + lane_group * 32 + lane);
       if (!mbar_wait(smem_u32(&bar_tfull[buf]), tphase, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * BN);
+#pragma unroll 1
+      for (int sub = 0; sub < MT; ++sub) {
+      const int m_warp = tm * BM + sub * GEMM_BM + lane_group * 32;
+      const int m = m_warp + lane;
+      if (sub > 0) prefetch_first(m);
+      const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) +
+                             (uint32_t)(buf * Cfg::ACC_COLS + sub * BN);
 #pragma unroll 1
       for (int c = 0; c < BN; c += CW) {
         const int n0 = tn * BN + c;
@@ -390,6 +414,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         sbuf ^= 1;
       }
+      }  // sub
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[buf]));
