@@ -34,6 +34,9 @@ int gemm_num_sms() {
   if (sms[dev] == 0) {
     int n = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    // ANE_B200_GEMM_SMS caps the persistent grids (e.g. to leave SMs to a communication kernel).
+    const char* e = getenv("ANE_B200_GEMM_SMS");
+    if (e && atoi(e) > 0 && atoi(e) < n) n = atoi(e);
     sms[dev] = n;
   }
   return sms[dev];
