@@ -7,8 +7,12 @@ namespace ane {
 // ------------------------------------------------------------------------------------------
 // Cross entropy (ane/stories/cpu.go:212-292) with the soft cap (ane/common.go:272-287) folded in.
 // One block per token row of fp32 logits [rows, V]; two passes (online max/sum, then gradient).
+// The launch asks for enough (unused) dynamic shared memory to hold residency at three blocks per SM:
+// the rows in flight (3 x 148 x V x 4 B = 57 MB at V = 32000) then fit the 126 MB L2 and the second
+// pass is served from there instead of from HBM.
 // ------------------------------------------------------------------------------------------
-static constexpr int kCEThreads = 256;
+static constexpr int kCEThreads = 512;
+static constexpr int kCEResidencySmem = 64 * 1024;
 
 __device__ __forceinline__ float softcap_f(float x) { return 15.0f * tanhf(x * (1.0f / 15.0f)); }
 
@@ -37,6 +41,7 @@ cross_entropy_rows_kernel(const float* __restrict__ logits, const uint16_t* __re
   float m = -INFINITY, l = 0.f;
   const int V4 = V >> 2;  // V is a multiple of 4 (checked when the engine opens)
   const float4* x4 = reinterpret_cast<const float4*>(x);
+#pragma unroll 2
   for (int i = threadIdx.x; i < V4; i += kCEThreads) {
     const float4 q = x4[i];
     float z[4] = {q.x, q.y, q.z, q.w};
@@ -115,7 +120,14 @@ void cross_entropy_rows(const float* logits, const uint16_t* targets, const floa
                         float* loss_rows, int rows, int row0, int seq, int V, bool softcap, float grad_scale,
                         cudaStream_t s) {
   if (rows <= 0) return;
-  launch_pdl(cross_entropy_rows_kernel<TO>, dim3(rows), dim3(kCEThreads), 0, s, logits, targets, inv_valid, dlogits, loss_rows,
+  static bool attr_done = false;  // per instantiation (TO)
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(cross_entropy_rows_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kCEResidencySmem) != cudaSuccess)
+      return;
+    attr_done = true;
+  }
+  launch_pdl(cross_entropy_rows_kernel<TO>, dim3(rows), dim3(kCEThreads), kCEResidencySmem, s, logits, targets, inv_valid, dlogits, loss_rows,
              rows, row0, seq, V, softcap ? 1 : 0, grad_scale);
 }
 template void cross_entropy_rows<float>(const float*, const uint16_t*, const float*, float*, float*, int, int, int,
