@@ -270,6 +270,11 @@ __global__ void relu2_backward_kernel(const T* __restrict__ dgate, const T* __re
     dh1[i] = from_f<T>(to_f<T>(dgate[i]) * 2.f * r);
   }
 }
+// SwiGLU on the interleaved FFN layout: h13 [M, 2*Hd] holds, per 64 columns, 32 columns of h1 = x W1^T
+// followed by the matching 32 columns of h3 = x W3^T (the rows of W1 and W3 are interleaved the same way
+// in the fused W13 matrix), so that one GEMM tile carries both factors of gate = silu(h1) * h3.
+__host__ __device__ __forceinline__ uint64_t h1_col(uint64_t j) { return ((j >> 5) << 6) + (j & 31); }
+
 template <typename T>
 __global__ void swiglu_forward_kernel(const T* __restrict__ h13, T* __restrict__ gate, int M, int Hd) {
   pdl_trigger();
@@ -280,8 +285,8 @@ __global__ void swiglu_forward_kernel(const T* __restrict__ h13, T* __restrict__
   const uint64_t n = (uint64_t)M * vec_per_row, stride = (uint64_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) {
     const uint64_t m = i / vec_per_row, j = (i - m * vec_per_row) * VN;
-    const uint4 a = *reinterpret_cast<const uint4*>(h13 + m * 2 * Hd + j);
-    const uint4 b = *reinterpret_cast<const uint4*>(h13 + m * 2 * Hd + Hd + j);
+    const uint4 a = *reinterpret_cast<const uint4*>(h13 + m * 2 * Hd + h1_col(j));
+    const uint4 b = *reinterpret_cast<const uint4*>(h13 + m * 2 * Hd + h1_col(j) + 32);
     const T* h1 = reinterpret_cast<const T*>(&a);
     const T* h3 = reinterpret_cast<const T*>(&b);
     uint4 o;
@@ -306,8 +311,8 @@ __global__ void swiglu_backward_kernel(const T* __restrict__ dgate, const T* __r
   const uint64_t n = (uint64_t)M * vec_per_row, stride = (uint64_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) {
     const uint64_t m = i / vec_per_row, j = (i - m * vec_per_row) * VN;
-    const uint4 a = *reinterpret_cast<const uint4*>(h13 + m * 2 * Hd + j);
-    const uint4 b = *reinterpret_cast<const uint4*>(h13 + m * 2 * Hd + Hd + j);
+    const uint4 a = *reinterpret_cast<const uint4*>(h13 + m * 2 * Hd + h1_col(j));
+    const uint4 b = *reinterpret_cast<const uint4*>(h13 + m * 2 * Hd + h1_col(j) + 32);
     const uint4 c = *reinterpret_cast<const uint4*>(dgate + m * Hd + j);
     const T* h1 = reinterpret_cast<const T*>(&a);
     const T* h3 = reinterpret_cast<const T*>(&b);
@@ -325,8 +330,8 @@ __global__ void swiglu_backward_kernel(const T* __restrict__ dgate, const T* __r
       d1[q] = from_f<T>(dg * to_f<T>(h3[q]) * dsilu);
       d3[q] = from_f<T>(dg * silu);
     }
-    *reinterpret_cast<uint4*>(dh13 + m * 2 * Hd + j) = o1;
-    *reinterpret_cast<uint4*>(dh13 + m * 2 * Hd + Hd + j) = o3;
+    *reinterpret_cast<uint4*>(dh13 + m * 2 * Hd + h1_col(j)) = o1;
+    *reinterpret_cast<uint4*>(dh13 + m * 2 * Hd + h1_col(j) + 32) = o3;
   }
 }
 

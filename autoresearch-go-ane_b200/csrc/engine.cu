@@ -86,14 +86,16 @@ __global__ void gather_windows_kernel(const uint16_t* __restrict__ tokens, const
 }
 
 // out[(b*ncols + c)*seq + t] = src[(b*seq+t)*ld + col0 + c]   (token-major -> the reference's [C][seq])
+// il != 0: tap column c lives at source column (c/32)*64 + c%32 + col0 (the interleaved h1 | h3 layout).
 template <typename TS>
-__global__ void export_tap_kernel(const TS* __restrict__ src, int ld, int col0, int ncols, int M, int seq,
+__global__ void export_tap_kernel(const TS* __restrict__ src, int ld, int col0, int ncols, int M, int seq, int il,
                                   float* __restrict__ out) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)M * ncols) return;
   const int m = (int)(i / ncols), c = (int)(i - (long long)m * ncols);
   const int b = m / seq, t = m - b * seq;
-  out[((size_t)b * ncols + c) * seq + t] = to_f<TS>(src[(size_t)m * ld + col0 + c]);
+  const int sc = il ? ((c >> 5) << 6) + (c & 31) + col0 : col0 + c;
+  out[((size_t)b * ncols + c) * seq + t] = to_f<TS>(src[(size_t)m * ld + sc]);
 }
 
 // next-token targets inside each window for the evaluation loss: tgt[b,t] = tok[b,t+1], last = invalid.
@@ -268,6 +270,9 @@ class EngineT final : public EngineBase {
   bool dw_overlap_ = true;
   float *rstdf_ = nullptr, *logits_ = nullptr, *loss_rows_ = nullptr, *inv_valid_ = nullptr, *d_loss_ = nullptr;
   T* dlogits_ = nullptr;
+  T* dlogits2_ = nullptr;                  // second chunk buffer: the classifier dW GEMM of chunk c runs on the
+  cudaEvent_t ev_cls_ce_[2] = {nullptr, nullptr};  // side stream while chunk c+1 is computed
+  cudaEvent_t ev_cls_dw_[2] = {nullptr, nullptr};
   float *rope_cos_ = nullptr, *rope_sin_ = nullptr;
   double* d_acc_ = nullptr;
   float *d_scales_ = nullptr, *d_norm_ = nullptr;
@@ -330,7 +335,7 @@ void EngineT<T>::destroy() {
     cudaStreamDestroy(dw_stream_);
     dw_stream_ = nullptr;
   }
-  for (cudaEvent_t* e : {&ev_bucket_, &ev_comm_done_, &ev_dw_in_})
+  for (cudaEvent_t* e : {&ev_bucket_, &ev_comm_done_, &ev_dw_in_, &ev_cls_ce_[0], &ev_cls_ce_[1], &ev_cls_dw_[0], &ev_cls_dw_[1]})
     if (*e) {
       cudaEventDestroy(*e);
       *e = nullptr;
@@ -480,7 +485,7 @@ int EngineT<T>::alloc_buffers() {
   }
   A(dgate_, (size_t)M_ * Hd_); A(dh13_[0], (size_t)M_ * N13_); A(dh13_[1], (size_t)M_ * N13_); A(datt_, (size_t)M_ * QD_);
   A(xnf_, MD); A(rstdf_, M_); A(att_delta_, (size_t)B_ * H_ * S_);
-  A(logits_, (size_t)ce_rows_ * V_); A(dlogits_, (size_t)ce_rows_ * V_);
+  A(logits_, (size_t)ce_rows_ * V_); A(dlogits_, (size_t)ce_rows_ * V_); A(dlogits2_, (size_t)ce_rows_ * V_);
   A(loss_rows_, M_); A(inv_valid_, B_); A(d_loss_, 4);
   A(rope_cos_, (size_t)S_ * (hd_ / 2)); A(rope_sin_, (size_t)S_ * (hd_ / 2));
   A(d_acc_, 2); A(d_scales_, 4); A(d_norm_, 2); A(d_status_, 1);
@@ -530,6 +535,7 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
   if (isN_ && KV_ != H_) return fail(ANE_ERR_ARG, "storiesane open: the reference architecture has no shared KV heads");
   if ((hd_ & 1) || hd_ > 128) return fail(ANE_ERR_ARG, "storiesane open: head_dim must be even and <= 128");
   if (D_ % 8 || Hd_ % 8 || (hd_ % 8)) return fail(ANE_ERR_ARG, "storiesane open: dim, hidden and head_dim must be multiples of 8");
+  if (!isN_ && Hd_ % 32) return fail(ANE_ERR_ARG, "storiesane open: hidden must be a multiple of 32 (SwiGLU layout)");
   if (V_ > 65535) return fail(ANE_ERR_ARG, "storiesane open: vocab must fit uint16 token ids");
   if (V_ % 8) return fail(ANE_ERR_ARG, "storiesane open: vocab must be a multiple of 8");
   if (isN_ && D_ < 12) return fail(ANE_ERR_ARG, "storiesane open: dim too small for the value-embedding gate");
@@ -552,6 +558,8 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
     if ((rc = cuda_check(cudaEventCreate(e), "cudaEventCreate")) != 0) return rc;
   if ((rc = cuda_check(cudaStreamCreateWithFlags(&dw_stream_, cudaStreamNonBlocking), "cudaStreamCreate")) != 0) return rc;
   if ((rc = cuda_check(cudaEventCreateWithFlags(&ev_dw_in_, cudaEventDisableTiming), "cudaEventCreate")) != 0) return rc;
+  for (cudaEvent_t* e : {&ev_cls_ce_[0], &ev_cls_ce_[1], &ev_cls_dw_[0], &ev_cls_dw_[1]})
+    if ((rc = cuda_check(cudaEventCreateWithFlags(e, cudaEventDisableTiming), "cudaEventCreate")) != 0) return rc;
   ev_dw_done_.assign(o_.n_layers, nullptr);
   for (auto& ev : ev_dw_done_)
     if ((rc = cuda_check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate")) != 0) return rc;
@@ -664,19 +672,32 @@ int EngineT<T>::forward(const uint16_t* d_tok, int B, int Tl, int pos0) {
     const float* xl = isN_ ? P_ + s_x0l_.off + l : nullptr;
     count_launch();
     rmsnorm_forward<T>(xs_[l], w_att, a.xn, a.rstd1, M, D_, stream_);
+    // llama arch, bf16, head_dim 64: the rotation of q and k happens on the fp32 accumulators in the epilogue
+    static const bool no_fuse_rope = getenv("ANE_B200_NO_FUSE_ROPE") != nullptr;  // A/B measurements
+    const bool fused_rope = !kIsF32 && !qkv_f32_ && !isN_ && hd_ == 64 && !no_fuse_rope;
     {
       GemmDesc g;
       g.A = a.xn; g.B = wop(s_qkv_[l].off); g.C = a.qkv;
       g.M = M; g.N = QKVD_; g.K = D_; g.lda = D_; g.ldb = D_; g.ldc = QKVD_;
       g.out = qkv_f32_ ? GEMM_OUT_F32 : GEMM_OUT_BF16;
+      if (fused_rope) {
+        g.out = GEMM_OUT_BF16_ROPE;
+        g.rope_cos = rope_cos_;
+        g.rope_sin = rope_sin_;
+        g.rope_seq = Tl;
+        g.rope_pos0 = pos0;
+        g.rope_cols = (H_ + KV_) * hd_;
+      }
       count_launch();
       if ((rc = gemm(g)) != 0) return rc;
     }
-    count_launch();
-    if (qkv_f32_)
-      rope_qknorm_forward<float>((float*)a.qkv, (float*)a.qkpre, rope_cos_, rope_sin_, M, Tl, H_, KV_, hd_, isN_, pos0, stream_);
-    else
-      rope_qknorm_forward<T>((T*)a.qkv, (T*)a.qkpre, rope_cos_, rope_sin_, M, Tl, H_, KV_, hd_, isN_, pos0, stream_);
+    if (!fused_rope) {
+      count_launch();
+      if (qkv_f32_)
+        rope_qknorm_forward<float>((float*)a.qkv, (float*)a.qkpre, rope_cos_, rope_sin_, M, Tl, H_, KV_, hd_, isN_, pos0, stream_);
+      else
+        rope_qknorm_forward<T>((T*)a.qkv, (T*)a.qkpre, rope_cos_, rope_sin_, M, Tl, H_, KV_, hd_, isN_, pos0, stream_);
+    }
     if (is_ve_layer(l)) {  // reference architecture only, so qkv is fp32 here
       count_launch();
       ve_forward<float>((float*)a.qkv, xs_[l], d_tok, P_ + s_ve_embed_[l].off, P_ + s_ve_gate_[l].off, a.ve_act, M, D_,
@@ -713,12 +734,23 @@ int EngineT<T>::forward(const uint16_t* d_tok, int B, int Tl, int pos0) {
       g.A = a.x2n; g.B = wop(s_w13_[l].off); g.C = a.h13;
       g.M = M; g.N = N13_; g.K = D_; g.lda = D_; g.ldb = D_; g.ldc = N13_;
       g.out = kIsF32 ? GEMM_OUT_F32 : GEMM_OUT_BF16;
+      // llama arch, bf16: the GEMM epilogue also writes gate = silu(h1) * h3 (W1 | W3 rows are interleaved in
+      // 32-row blocks, so every 64-column piece of h13 holds matching h1 and h3 columns).
+      static const bool no_fuse_gate = getenv("ANE_B200_NO_FUSE_SWIGLU") != nullptr;  // A/B measurements
+      const bool fused_gate = !kIsF32 && !isN_ && !no_fuse_gate && Hd_ % 64 == 0;
+      if (fused_gate) {
+        g.out = GEMM_OUT_BF16_SWIGLU;
+        g.aux = a.gate;
+        g.ldaux = Hd_;
+      }
       count_launch();
       if ((rc = gemm(g)) != 0) return rc;
+      if (!fused_gate) {
+        count_launch();
+        if (isN_) relu2_forward<T>(a.h13, a.gate, (uint64_t)M * Hd_, stream_);
+        else swiglu_forward<T>(a.h13, a.gate, M, Hd_, stream_);
+      }
     }
-    count_launch();
-    if (isN_) relu2_forward<T>(a.h13, a.gate, (uint64_t)M * Hd_, stream_);
-    else swiglu_forward<T>(a.h13, a.gate, M, Hd_, stream_);
     {
       GemmDesc g;  // out = rl*x2 + W2*gate (+ xl*x0)   ane/train_full.go:434-445
       g.A = a.gate; g.B = wop(s_w2_[l].off); g.C = xs_[l + 1];
@@ -750,27 +782,39 @@ int EngineT<T>::head_and_backward(int B) {
   int rc;
   count_launch();
   count_valid_targets(d_tgt_, inv_valid_, B, S_, V_, stream_);
-  for (int r0 = 0; r0 < M; r0 += ce_rows_) {
+  // The dEmbed GEMM of a chunk runs on the side stream (it only feeds the optimizer); the two dlogits
+  // buffers alternate so that the next chunk's cross-entropy does not overwrite its operand.
+  cudaStream_t dws = (dw_overlap_ && !profiling_) ? dw_stream_ : stream_;
+  int chunk = 0;
+  for (int r0 = 0; r0 < M; r0 += ce_rows_, ++chunk) {
     const int rows = std::min(ce_rows_, M - r0);
+    const int cb = chunk & 1;
+    T* dlogits = cb ? dlogits2_ : dlogits_;
+    if (dws != stream_ && chunk >= 2) cudaStreamWaitEvent(stream_, ev_cls_dw_[cb], 0);
     GemmDesc g;
     g.A = xnf_ + (size_t)r0 * D_; g.B = wop(s_embed_.off); g.C = logits_;
     g.M = rows; g.N = V_; g.K = D_; g.lda = D_; g.ldb = D_; g.ldc = V_; g.out = GEMM_OUT_F32;
     count_launch();
     if ((rc = gemm(g)) != 0) return rc;
     count_launch();
-    cross_entropy_rows<T>(logits_, d_tgt_, inv_valid_, dlogits_, loss_rows_, rows, r0, S_, V_, isN_, o_.loss_scale,
+    cross_entropy_rows<T>(logits_, d_tgt_, inv_valid_, dlogits, loss_rows_, rows, r0, S_, V_, isN_, o_.loss_scale,
                           stream_);
+    if (dws != stream_) {
+      cudaEventRecord(ev_cls_ce_[cb], stream_);
+      cudaStreamWaitEvent(dws, ev_cls_ce_[cb], 0);
+    }
     GemmDesc gx;  // dy = dlogits * Embed   (ane/stories/cpu.go:333-360)
-    gx.A = dlogits_; gx.B = wop(s_embed_.off); gx.C = dy_ + (size_t)r0 * D_;
+    gx.A = dlogits; gx.B = wop(s_embed_.off); gx.C = dy_ + (size_t)r0 * D_;
     gx.M = rows; gx.N = D_; gx.K = V_; gx.lda = V_; gx.ldb = D_; gx.ldc = D_; gx.b_mn = true; gx.out = GEMM_OUT_F32;
     count_launch();
     if ((rc = gemm(gx)) != 0) return rc;
     GemmDesc gw;  // gEmbed += dlogits^T * xn   (ane/stories/cpu.go:366-385)
-    gw.A = dlogits_; gw.B = xnf_ + (size_t)r0 * D_; gw.C = G_ + s_embed_.off;
+    gw.A = dlogits; gw.B = xnf_ + (size_t)r0 * D_; gw.C = G_ + s_embed_.off;
     gw.M = V_; gw.N = D_; gw.K = rows; gw.lda = V_; gw.ldb = D_; gw.ldc = D_; gw.a_mn = true; gw.b_mn = true;
     gw.out = GEMM_OUT_ACCUM;
     count_launch();
-    if ((rc = gemm(gw)) != 0) return rc;
+    if ((rc = gemm(gw, dws)) != 0) return rc;
+    if (dws != stream_) cudaEventRecord(ev_cls_dw_[cb], dws);
   }
   count_launch();
   reduce_loss(loss_rows_, inv_valid_, d_loss_, B, S_, stream_);
@@ -1383,7 +1427,20 @@ int EngineT<T>::import_tensor(uint32_t id, uint32_t layer, uint32_t which, const
   if (s.n == 0) return fail(ANE_ERR_ARG, "storiesane import: tensor not present in this architecture");
   if (n != s.n) return fail(ANE_ERR_ARG, "storiesane import: element count mismatch");
   float* base = which == 0 ? P_ : which == 1 ? G_ : which == 2 ? Mo_ : Vo_;
-  int rc = cuda_check(cudaMemcpyAsync(base + s.off, buf, sizeof(float) * n, cudaMemcpyHostToDevice, stream_), "import");
+  int rc;
+  if (!isN_ && (id == ANE_T_W1 || id == ANE_T_W3)) {
+    // W1 and W3 share the fused W13 matrix in blocks of 32 rows: [W1 rows 0..31 | W3 rows 0..31 | W1 rows 32..63 | ...]
+    const size_t blk = (size_t)32 * D_ * sizeof(float);
+    float* dst = base + s_w13_[layer].off + (id == ANE_T_W3 ? (size_t)32 * D_ : 0);
+    rc = cuda_check(cudaMemcpy2DAsync(dst, 2 * blk, buf, blk, blk, (size_t)Hd_ / 32, cudaMemcpyHostToDevice, stream_), "import");
+    if (rc) return rc;
+    if (which == 0 && !kIsF32) {
+      count_launch();
+      cast_f32_to_bf16(P_ + s_w13_[layer].off, Sh_ + s_w13_[layer].off, s_w13_[layer].n, stream_);
+    }
+    return cuda_check(cudaStreamSynchronize(stream_), "import sync");
+  }
+  rc = cuda_check(cudaMemcpyAsync(base + s.off, buf, sizeof(float) * n, cudaMemcpyHostToDevice, stream_), "import");
   if (rc) return rc;
   if (which == 0 && !kIsF32 && s.off < shadow_n_) {
     count_launch();
@@ -1400,7 +1457,14 @@ int EngineT<T>::export_tensor(uint32_t id, uint32_t layer, uint32_t which, float
   if (n != s.n) return fail(ANE_ERR_ARG, "storiesane export: element count mismatch");
   if (n == 0) return 0;
   const float* base = which == 0 ? P_ : which == 1 ? G_ : which == 2 ? Mo_ : Vo_;
-  int rc = cuda_check(cudaMemcpyAsync(buf, base + s.off, sizeof(float) * n, cudaMemcpyDeviceToHost, stream_), "export");
+  int rc;
+  if (!isN_ && (id == ANE_T_W1 || id == ANE_T_W3)) {  // de-interleave the 32-row blocks (see import_tensor)
+    const size_t blk = (size_t)32 * D_ * sizeof(float);
+    const float* src = base + s_w13_[layer].off + (id == ANE_T_W3 ? (size_t)32 * D_ : 0);
+    rc = cuda_check(cudaMemcpy2DAsync(buf, blk, src, 2 * blk, blk, (size_t)Hd_ / 32, cudaMemcpyDeviceToHost, stream_), "export");
+  } else {
+    rc = cuda_check(cudaMemcpyAsync(buf, base + s.off, sizeof(float) * n, cudaMemcpyDeviceToHost, stream_), "export");
+  }
   if (rc) return rc;
   return cuda_check(cudaStreamSynchronize(stream_), "export sync");
 }
@@ -1415,7 +1479,7 @@ int64_t EngineT<T>::get_tap(uint32_t tap, uint32_t layer, float* buf, uint64_t c
   const int M = B * S_;
   const void* src = nullptr;
   bool src_f32 = true;
-  int ld = 0, col0 = 0, ncols = 0;
+  int ld = 0, col0 = 0, ncols = 0, il = 0;
   if (tap < 32 && layer >= (uint32_t)L_) {
     fail(ANE_ERR_ARG, "storiesane tap: bad layer");
     return -1;
@@ -1432,15 +1496,15 @@ int64_t EngineT<T>::get_tap(uint32_t tap, uint32_t layer, float* buf, uint64_t c
       case ANE_TAP_ATT: src = a.att; src_f32 = tf; ld = QD_; ncols = QD_; break;
       case ANE_TAP_X2: src = a.x2; ld = D_; ncols = D_; break;
       case ANE_TAP_X2NORM: src = a.x2n; src_f32 = tf; ld = D_; ncols = D_; break;
-      case ANE_TAP_H1: src = a.h13; src_f32 = tf; ld = N13_; ncols = Hd_; break;
-      case ANE_TAP_H3: if (!isN_) { src = a.h13; src_f32 = tf; ld = N13_; col0 = Hd_; ncols = Hd_; } break;
+      case ANE_TAP_H1: src = a.h13; src_f32 = tf; ld = N13_; ncols = Hd_; il = !isN_; break;
+      case ANE_TAP_H3: if (!isN_) { src = a.h13; src_f32 = tf; ld = N13_; col0 = 32; ncols = Hd_; il = 1; } break;
       case ANE_TAP_GATE: src = a.gate; src_f32 = tf; ld = Hd_; ncols = Hd_; break;
       case ANE_TAP_QPRE: if (isN_) { src = a.qkpre; src_f32 = qkv_f32_; ld = QD_ + KVD_; ncols = QD_; } break;
       case ANE_TAP_KPRE: if (isN_) { src = a.qkpre; src_f32 = qkv_f32_; ld = QD_ + KVD_; col0 = QD_; ncols = KVD_; } break;
       case ANE_TAP_DOUT: src = a.t_dout; ld = D_; ncols = D_; break;
       case ANE_TAP_DX2: src = a.t_dx2; ld = D_; ncols = D_; break;
-      case ANE_TAP_DH1: src = a.t_dh13; ld = N13_; ncols = Hd_; break;
-      case ANE_TAP_DH3: if (!isN_) { src = a.t_dh13; ld = N13_; col0 = Hd_; ncols = Hd_; } break;
+      case ANE_TAP_DH1: src = a.t_dh13; ld = N13_; ncols = Hd_; il = !isN_; break;
+      case ANE_TAP_DH3: if (!isN_) { src = a.t_dh13; ld = N13_; col0 = 32; ncols = Hd_; il = 1; } break;
       case ANE_TAP_DQ: src = a.t_dqkv; ld = QKVD_; ncols = QD_; break;
       case ANE_TAP_DK: src = a.t_dqkv; ld = QKVD_; col0 = QD_; ncols = KVD_; break;
       case ANE_TAP_DV: src = a.t_dqkv; ld = QKVD_; col0 = QD_ + KVD_; ncols = KVD_; break;
@@ -1468,9 +1532,9 @@ int64_t EngineT<T>::get_tap(uint32_t tap, uint32_t layer, float* buf, uint64_t c
   const unsigned grid = (unsigned)((n + 255) / 256);
   count_launch();
   if (src_f32)
-    export_tap_kernel<float><<<grid, 256, 0, stream_>>>(reinterpret_cast<const float*>(src), ld, col0, ncols, M, S_, tap_tmp_);
+    export_tap_kernel<float><<<grid, 256, 0, stream_>>>(reinterpret_cast<const float*>(src), ld, col0, ncols, M, S_, il, tap_tmp_);
   else
-    export_tap_kernel<T><<<grid, 256, 0, stream_>>>(reinterpret_cast<const T*>(src), ld, col0, ncols, M, S_, tap_tmp_);
+    export_tap_kernel<T><<<grid, 256, 0, stream_>>>(reinterpret_cast<const T*>(src), ld, col0, ncols, M, S_, il, tap_tmp_);
   if (cuda_check(cudaMemcpyAsync(buf, tap_tmp_, sizeof(float) * n, cudaMemcpyDeviceToHost, stream_), "tap") != 0) return -1;
   if (cuda_check(cudaStreamSynchronize(stream_), "tap sync") != 0) return -1;
   return (int64_t)n;

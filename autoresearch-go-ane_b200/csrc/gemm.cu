@@ -114,7 +114,8 @@ bool make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t ou
 }
 
 template <int BN, int MT, bool A_MN, bool B_MN, int EPI>
-static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const EpiParams& epi,
+static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& td,
+                     const EpiParams& epi,
                      const GemmDesc& d, int split_k, int* d_status, cudaStream_t stream) {
   auto kern = gemm_tc_kernel<BN, MT, A_MN, B_MN, EPI>;
   static bool attr_set = false;  // per template instantiation
@@ -140,7 +141,7 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     grid = (int)g;
   }
   if (grid < 1) grid = 1;
-  cudaError_t e = launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), GemmCfg<BN, MT>::SMEM_BYTES, stream, ta, tb, tc, epi, d.M, d.N,
+  cudaError_t e = launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), GemmCfg<BN, MT>::SMEM_BYTES, stream, ta, tb, tc, td, epi, d.M, d.N,
                              d.K, split_k, d_status);
   if (e != cudaSuccess) {
     g_gemm_err = std::string("gemm_tc launch: ") + cudaGetErrorString(e);
@@ -152,16 +153,38 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
 template <int BN, int MT, bool A_MN, bool B_MN>
 static int dispatch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const GemmDesc& d, int split_k,
                         int* d_status, cudaStream_t stream) {
-  EpiParams epi{d.alpha, d.res1, d.s1, d.res2, d.s2, d.ldres};
+  EpiParams epi{d.alpha, d.res1, d.s1, d.res2, d.s2, d.ldres, reinterpret_cast<bf16*>(d.aux), d.ldaux,
+                d.rope_cos, d.rope_sin, d.rope_seq, d.rope_pos0, d.rope_cols};
   CUtensorMap tc;
   if (d.out == GEMM_OUT_BF16) {
     if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 64, 32, false)) return -2;
-    return launch_tc<BN, MT, A_MN, B_MN, EPI_STORE_BF16>(ta, tb, tc, epi, d, 1, d_status, stream);
+    return launch_tc<BN, MT, A_MN, B_MN, EPI_STORE_BF16>(ta, tb, tc, tc, epi, d, 1, d_status, stream);
+  }
+  if (d.out == GEMM_OUT_BF16_ROPE) {
+    if constexpr (!A_MN && !B_MN) {
+      if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 64, 32, false)) return -2;
+      return launch_tc<BN, MT, A_MN, B_MN, EPI_STORE_BF16_ROPE>(ta, tb, tc, tc, epi, d, 1, d_status, stream);
+    } else {
+      g_gemm_err = "the rotary epilogue takes K-major operands only";
+      return -2;
+    }
+  }
+  if (d.out == GEMM_OUT_BF16_SWIGLU) {
+    if constexpr (!A_MN && !B_MN) {
+      CUtensorMap td;  // gate [M, N/2]: pieces of 32 rows x 64 columns
+      if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 64, 32, false) ||
+          !make_tmap(&td, d.aux, d.N / 2, d.M, d.ldaux, 64, 32, false))
+        return -2;
+      return launch_tc<BN, MT, A_MN, B_MN, EPI_STORE_BF16_SWIGLU>(ta, tb, tc, td, epi, d, 1, d_status, stream);
+    } else {
+      g_gemm_err = "the SwiGLU epilogue takes K-major operands only";
+      return -2;
+    }
   }
   if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 32, 32, true)) return -2;
   if (d.out == GEMM_OUT_F32)
-    return launch_tc<BN, MT, A_MN, B_MN, EPI_STORE_F32>(ta, tb, tc, epi, d, 1, d_status, stream);
-  return launch_tc<BN, MT, A_MN, B_MN, EPI_REDUCE_F32>(ta, tb, tc, epi, d, split_k, d_status, stream);
+    return launch_tc<BN, MT, A_MN, B_MN, EPI_STORE_F32>(ta, tb, tc, tc, epi, d, 1, d_status, stream);
+  return launch_tc<BN, MT, A_MN, B_MN, EPI_REDUCE_F32>(ta, tb, tc, tc, epi, d, split_k, d_status, stream);
 }
 
 template <int BN, int MT>
@@ -301,7 +324,19 @@ int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream) {
     g_gemm_err = "fp32 residual operands must be 16-byte aligned with ldres % 4 == 0";
     return -2;
   }
-  const GemmPlan p = plan_gemm(d, gemm_num_sms());
+  if (d.out == GEMM_OUT_BF16_SWIGLU && (d.aux == nullptr || d.N % 128 != 0 || d.ldaux % 8 != 0 ||
+                                        (reinterpret_cast<uintptr_t>(d.aux) & 15) != 0)) {
+    g_gemm_err = "SwiGLU epilogue: N must be a multiple of 128 and the gate buffer 16-byte aligned with ldaux % 8 == 0";
+    return -2;
+  }
+  if (d.out == GEMM_OUT_BF16_ROPE &&
+      (d.rope_cos == nullptr || d.rope_sin == nullptr || d.rope_seq <= 0 || d.rope_cols % 64 != 0 || d.alpha != 1.f ||
+       (reinterpret_cast<uintptr_t>(d.rope_cos) & 15) != 0 || (reinterpret_cast<uintptr_t>(d.rope_sin) & 15) != 0)) {
+    g_gemm_err = "rotary epilogue: needs 16-byte aligned cos/sin tables, rope_seq > 0, rope_cols % 64 == 0 and alpha == 1";
+    return -2;
+  }
+  GemmPlan p = plan_gemm(d, gemm_num_sms());
+  if (d.out == GEMM_OUT_BF16_SWIGLU && p.bn == 192) p.bn = 256;  // gate rows pair up two 64-column pieces
   if (p.mt == 2) {
     if (p.bn == 256) return dispatch_layout<256, 2>(d, p.sched, d_status, stream);
     return dispatch_layout<192, 2>(d, p.sched, d_status, stream);

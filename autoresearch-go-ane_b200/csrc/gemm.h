@@ -19,6 +19,13 @@ enum GemmOut : int {
   GEMM_OUT_BF16 = 0,    // store bf16 (bf16 path only)
   GEMM_OUT_F32 = 1,     // store fp32, optional residual blend
   GEMM_OUT_ACCUM = 2,   // C += alpha*A*B in fp32 (beta = 1)
+  // store bf16 and, for C = [h1 | h3] interleaved in 32-column blocks, also gate = silu(h1) * h3 into
+  // `aux` [M, N/2] (bf16, row pitch ldaux); K-major operands only, N % 64 == 0
+  GEMM_OUT_BF16_SWIGLU = 3,
+  // store bf16 after rotating the (even, odd) column pairs of every 64-column head below column
+  // `rope_cols` by the angle of the row's position (rope_pos0 + row % rope_seq): the q|k part of a packed
+  // q|k|v projection with head_dim 64.  cos/sin tables are [positions, 32] fp32.  K-major operands only.
+  GEMM_OUT_BF16_ROPE = 4,
 };
 
 struct GemmDesc {
@@ -35,6 +42,11 @@ struct GemmDesc {
   const float* res2 = nullptr;
   const float* s2 = nullptr;
   int ldres = 0;
+  void* aux = nullptr;  // GEMM_OUT_BF16_SWIGLU: gate output
+  int ldaux = 0;
+  const float* rope_cos = nullptr;  // GEMM_OUT_BF16_ROPE
+  const float* rope_sin = nullptr;
+  int rope_seq = 0, rope_pos0 = 0, rope_cols = 0;
   int split_k = 0;  // 0 => choose
 };
 

@@ -68,6 +68,12 @@ enum EpiKind : int {
   EPI_STORE_BF16 = 0,   // C(bf16) = alpha*acc
   EPI_STORE_F32 = 1,    // C(fp32) = alpha*acc + s1*res1 + s2*res2
   EPI_REDUCE_F32 = 2,   // C(fp32) += alpha*acc  (TMA reduce-add; split-K safe)
+  // EPI_STORE_BF16 plus gate = silu(h1) * h3 from the fp32 accumulators: every 64-column piece holds 32
+  // columns of h1 and the matching 32 of h3; the gate piece goes straight to global memory.
+  EPI_STORE_BF16_SWIGLU = 3,
+  // EPI_STORE_BF16 with the rotary embedding applied to the fp32 accumulators of the q|k heads (one
+  // 64-column piece = one head); each epilogue thread keeps the cos/sin row of its token in registers.
+  EPI_STORE_BF16_ROPE = 4,
 };
 
 struct EpiParams {
@@ -77,6 +83,11 @@ struct EpiParams {
   const float* res2;
   const float* s2;
   int ldres;
+  bf16* aux;   // EPI_STORE_BF16_SWIGLU: gate [M, N/2]
+  int ldaux;
+  const float* rope_cos;  // EPI_STORE_BF16_ROPE: [positions, 32]
+  const float* rope_sin;
+  int rope_seq, rope_pos0, rope_cols;
 };
 
 // Work scheduler shared by the three warp roles (each role walks the same sequence).
@@ -134,8 +145,8 @@ struct GemmSched {
 template <int BN, int MT, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmC, EpiParams epi, int M, int N, int K, int split_k,
-               int* status) {
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD, EpiParams epi, int M,
+               int N, int K, int split_k, int* status) {
   using Cfg = GemmCfg<BN, MT>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr int BM = Cfg::BM_TILE, BK = GEMM_BK;
@@ -281,7 +292,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ------------------------------ epilogue warps ------------------------------
     const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, 32*lane_group+32)
     // Columns per staged piece: 128 bytes of output per row.
-    constexpr int CW = (EPI == EPI_STORE_BF16) ? 64 : 32;
+    constexpr bool kBf16Out = (EPI == EPI_STORE_BF16 || EPI == EPI_STORE_BF16_SWIGLU || EPI == EPI_STORE_BF16_ROPE);
+    constexpr int CW = kBf16Out ? 64 : 32;
     const uint32_t stage_base = smem_stage0 + (uint32_t)(warp - 2) * 8192u;
     uint8_t* stage_ptr = smem_raw + (stage_base - smem_u32(smem_raw));
     int local = 0;
@@ -324,6 +336,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int m_warp = tm * BM + sub * GEMM_BM + lane_group * 32;
       const int m = m_warp + lane;
       if (sub > 0) prefetch_first(m);
+      uint32_t gate_even[16];  // EPI_STORE_BF16_SWIGLU: the even piece's half of a gate row
+      float4 rc4[8], rs4[8];   // EPI_STORE_BF16_ROPE: cos / sin of this thread's token, 32 pairs
+      if constexpr (EPI == EPI_STORE_BF16_ROPE) {
+        if (tn * BN < epi.rope_cols && m < M) {
+          const size_t pos = (size_t)(epi.rope_pos0 + m % epi.rope_seq) * 32;
+          const float4* cp = reinterpret_cast<const float4*>(epi.rope_cos + pos);
+          const float4* sp = reinterpret_cast<const float4*>(epi.rope_sin + pos);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            rc4[q] = cp[q];
+            rs4[q] = sp[q];
+          }
+        }
+      }
       const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) +
                              (uint32_t)(buf * Cfg::ACC_COLS + sub * BN);
 #pragma unroll 1
@@ -355,7 +381,56 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) tma_store_wait_read<1>();
         __syncwarp();
         uint8_t* row_ptr = stage_ptr + sbuf * 4096 + lane * 128;
-        if constexpr (EPI == EPI_STORE_BF16) {
+        if constexpr (kBf16Out) {
+          if constexpr (EPI == EPI_STORE_BF16_ROPE) {
+            if (n0 < epi.rope_cols && m < M) {  // pairs (2p, 2p+1) of this head
+              const float* rc = reinterpret_cast<const float*>(rc4);
+              const float* rs = reinterpret_cast<const float*>(rs4);
+#pragma unroll
+              for (int pr = 0; pr < 32; ++pr) {
+                const float a = acc[2 * pr], b = acc[2 * pr + 1];
+                acc[2 * pr] = a * rc[pr] - b * rs[pr];
+                acc[2 * pr + 1] = b * rc[pr] + a * rs[pr];
+              }
+            }
+          }
+          if constexpr (EPI == EPI_STORE_BF16_SWIGLU) {
+            // gate = silu(h1) * h3 for the 32 gate columns of this piece.  Two consecutive pieces make one
+            // 128-byte gate row: the even piece parks its half in registers, the odd piece stages the row
+            // as one more piece of the two-buffer rotation (it takes this buffer, h13 takes the other).
+            uint32_t gcur[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              // silu(x) * h = x * h / (1 + 2^(-x log2 e)): one ex2 and one fast reciprocal per element (the
+              // epilogue has four warps per SM, so instruction count matters here)
+              const float x0 = epi.alpha * acc[2 * e], x1 = epi.alpha * acc[2 * e + 1];
+              const float h0 = epi.alpha * acc[32 + 2 * e], h1 = epi.alpha * acc[32 + 2 * e + 1];
+              const float d0 = 1.f + exp2f(-1.4426950408889634f * x0), d1 = 1.f + exp2f(-1.4426950408889634f * x1);
+              gcur[e] = pack2_bf16(__fdividef(x0 * h0, d0), __fdividef(x1 * h1, d1));
+            }
+            if (((c / CW) & 1) == 0) {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) gate_even[e] = gcur[e];
+            } else {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                *reinterpret_cast<uint4*>(row_ptr + ((q ^ (lane & 7)) << 4)) =
+                    make_uint4(gate_even[4 * q], gate_even[4 * q + 1], gate_even[4 * q + 2], gate_even[4 * q + 3]);
+                *reinterpret_cast<uint4*>(row_ptr + (((q + 4) ^ (lane & 7)) << 4)) =
+                    make_uint4(gcur[4 * q], gcur[4 * q + 1], gcur[4 * q + 2], gcur[4 * q + 3]);
+              }
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&tmD, stage_base + (uint32_t)sbuf * 4096u, (n0 - CW) >> 1, m_warp);
+                tma_store_commit();
+                tma_store_wait_read<1>();  // the other buffer (the piece before this one) is free again
+              }
+              sbuf ^= 1;
+              __syncwarp();
+              row_ptr = stage_ptr + sbuf * 4096 + lane * 128;
+            }
+          }
 #pragma unroll
           for (int q = 0; q < 8; ++q) {  // 8 chunks of 8 bf16
             uint4 u;

@@ -282,6 +282,36 @@ def run_ours(args):
                    "d2h_bytes_per_op": WORKLOAD["vocab"] * T * 4,
                    "note": "host-visible latency of one EvalLogits call (batch 1); EvalLoss keeps logits on the device"}
 
+    # ---- optional extra legs (one GPU): batched evaluation and KV-cached greedy decoding
+    extras = None
+    if args.extras and world == 1:
+        extras = {}
+        nb = 64
+        batch_tokens = np.ascontiguousarray(tokens[:nb * T])
+        e.eval_loss(batch_tokens)
+        t0 = time.perf_counter()
+        for _ in range(5):
+            e.eval_loss(batch_tokens)
+        dt = (time.perf_counter() - t0) / 5
+        extras["eval_loss_batch64"] = {"ms_per_op": round(dt * 1e3, 3), "tok_per_s": round(nb * T / dt, 1)}
+        e.eval_logits(batch_tokens, layout=1)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            e.eval_logits(batch_tokens, layout=1)
+        dt = (time.perf_counter() - t0) / 3
+        extras["eval_logits_batch64"] = {"ms_per_op": round(dt * 1e3, 3), "tok_per_s": round(nb * T / dt, 1),
+                                         "d2h_bytes_per_op": nb * T * WORKLOAD["vocab"] * 4,
+                                         "note": "host-visible, fp32 logits for 64 x seq tokens copied to the host"}
+        if T >= 768:  # prompt 512 + 256 generated tokens must fit the KV cache (= seq)
+            prompts = np.ascontiguousarray(tokens[:32 * 512].reshape(32, 512))
+            e.decode_greedy(prompts[:, :64], 4)
+            t0 = time.perf_counter()
+            out = e.decode_greedy(prompts, 256)
+            dt = time.perf_counter() - t0
+            extras["decode_greedy"] = {"batch": 32, "prompt": 512, "new_tokens": 256, "seconds": round(dt, 4),
+                                       "generated_tok_per_s": round(32 * 256 / dt, 1),
+                                       "note": "prefill + 256 KV-cached greedy steps, host-visible"}
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload == "110m":
         cpu_baseline = cpu_reference_leg(steps=1, warmup=0)
@@ -300,6 +330,8 @@ def run_ours(args):
         }
         if cpu_baseline is not None:
             line["cpu_baseline"] = cpu_baseline
+        if extras is not None:
+            line["extras"] = extras
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -415,6 +447,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ce-chunk", type=int, default=0, help="token rows per classifier/CE chunk (0 = library default)")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="110m")
+    ap.add_argument("--extras", action="store_true", help="also time batch-64 evaluation and (seq >= 768) greedy decoding")
     ap.add_argument("--batch", type=int, default=0, help="sequences per GPU per step (0 = the workload's own)")
     ap.add_argument("--kernel-case", choices=sorted(KERNEL_CASES), default=None)
     args = ap.parse_args()
