@@ -109,9 +109,70 @@ __global__ void rmsnorm_forward_kernel(const float* __restrict__ x, const float*
   }
 }
 
+// Register-resident variant for D = 128*NV: a few resident blocks per SM deal the rows round-robin and
+// each warp requests its next row before it reduces the current one.
+static constexpr int kRmsFwdWarps = 16;
+template <typename T, int NV>
+__global__ void __launch_bounds__(kRmsFwdWarps * 32)
+rmsnorm_forward_reg_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
+                           float* __restrict__ rstd, int M) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int D = 128 * NV;
+  const int lane = threadIdx.x & 31;
+  const int stride = gridDim.x * kRmsFwdWarps;
+  int row = blockIdx.x * kRmsFwdWarps + (threadIdx.x >> 5);
+  if (row >= M) return;
+  float4 wv[NV], nxt[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    wv[k] = w ? reinterpret_cast<const float4*>(w)[lane + 32 * k] : make_float4(1.f, 1.f, 1.f, 1.f);
+    nxt[k] = reinterpret_cast<const float4*>(x + (size_t)row * D)[lane + 32 * k];
+  }
+  for (; row < M; row += stride) {
+    float4 v[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) v[k] = nxt[k];
+    if (row + stride < M) {
+      const float4* xn = reinterpret_cast<const float4*>(x + (size_t)(row + stride) * D);
+#pragma unroll
+      for (int k = 0; k < NV; ++k) nxt[k] = xn[lane + 32 * k];
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)D + 1e-5f);
+    if (lane == 0 && rstd) rstd[row] = r;
+    T* yr = y + (size_t)row * D;
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+      store4<T>(yr + 4 * (lane + 32 * k), v[k].x * r * wv[k].x, v[k].y * r * wv[k].y, v[k].z * r * wv[k].z,
+                v[k].w * r * wv[k].w);
+  }
+}
+
 template <typename T>
 void rmsnorm_forward(const float* x, const float* w, T* y, float* rstd, int M, int D, cudaStream_t s) {
   if (M <= 0) return;
+  if (D % 128 == 0 && D <= 1024) {
+    const int rb = std::min((M + kRmsFwdWarps - 1) / kRmsFwdWarps, 148 * 2);
+#define ANE_RMS_FWD_CASE(NV)                                                                                     \
+  case NV:                                                                                                        \
+    launch_pdl(rmsnorm_forward_reg_kernel<T, NV>, dim3(rb), dim3(kRmsFwdWarps * 32), 0, s, x, w, y, rstd, M);    \
+    return;
+    switch (D / 128) {
+      ANE_RMS_FWD_CASE(1)
+      ANE_RMS_FWD_CASE(2)
+      ANE_RMS_FWD_CASE(3)
+      ANE_RMS_FWD_CASE(4)
+      ANE_RMS_FWD_CASE(5)
+      ANE_RMS_FWD_CASE(6)
+      ANE_RMS_FWD_CASE(7)
+      ANE_RMS_FWD_CASE(8)
+    }
+#undef ANE_RMS_FWD_CASE
+  }
   const int blocks = (M + kWarpsPerBlock - 1) / kWarpsPerBlock;
   launch_pdl(rmsnorm_forward_kernel<T>, dim3(blocks), dim3(kWarpsPerBlock * 32), 0, s, x, w, y, rstd, M, D);
 }
@@ -198,9 +259,12 @@ __global__ void rmsnorm_backward_kernel(const float* __restrict__ dy, const floa
   }
 }
 
-// Register-resident variant for D = 128*NV (NV float4 per lane): each row is read once.
+// Register-resident variant for D = 128*NV (NV float4 per lane): each row is read once, and all three
+// inputs of a row (dy, x, residual) are requested before anything is computed, so a row costs one memory
+// round trip.  One block of twelve warps per SM, rows dealt round-robin.
+static constexpr int kRmsBwdWarps = 12;
 template <typename T, int NV>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+__global__ void __launch_bounds__(kRmsBwdWarps * 32)
 rmsnorm_backward_reg_kernel(const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ w,
                             const float* __restrict__ rstd, const float* __restrict__ res,
                             const float* __restrict__ res_scale, float* __restrict__ dx_f32, T* __restrict__ dx_t,
@@ -208,7 +272,7 @@ rmsnorm_backward_reg_kernel(const float* __restrict__ dy, const float* __restric
   pdl_trigger();
   pdl_wait();
   constexpr int D = 128 * NV;
-  __shared__ float s_dw[kWarpsPerBlock][D > 1024 ? 1 : D];
+  __shared__ float s_dw[kRmsBwdWarps][D > 1024 ? 1 : D];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const float rs = res ? (res_scale ? *res_scale : 1.f) : 0.f;
@@ -220,14 +284,16 @@ rmsnorm_backward_reg_kernel(const float* __restrict__ dy, const float* __restric
   float4 dwacc[NV];
 #pragma unroll
   for (int k = 0; k < NV; ++k) dwacc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int row = blockIdx.x * kWarpsPerBlock + warp; row < M; row += gridDim.x * kWarpsPerBlock) {
+  for (int row = blockIdx.x * kRmsBwdWarps + warp; row < M; row += gridDim.x * kRmsBwdWarps) {
     const float4* dyr = reinterpret_cast<const float4*>(dy + (size_t)row * D);
     const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row * D);
-    float4 g[NV], v[NV];
+    const float4* rr = res ? reinterpret_cast<const float4*>(res + (size_t)row * D) : nullptr;
+    float4 g[NV], v[NV], q[NV];
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       g[k] = dyr[lane + 32 * k];
       v[k] = xr[lane + 32 * k];
+      q[k] = rr ? rr[lane + 32 * k] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     float r;
     if (rstd) {
@@ -256,7 +322,6 @@ rmsnorm_backward_reg_kernel(const float* __restrict__ dy, const float* __restric
     }
     dot = warp_sum(dot);
     const float coeff = dot * r * r * r * inv_d;
-    const float4* rr = res ? reinterpret_cast<const float4*>(res + (size_t)row * D) : nullptr;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       float4 o;
@@ -264,10 +329,7 @@ rmsnorm_backward_reg_kernel(const float* __restrict__ dy, const float* __restric
       o.y = g[k].y * r - coeff * v[k].y;
       o.z = g[k].z * r - coeff * v[k].z;
       o.w = g[k].w * r - coeff * v[k].w;
-      if (rr) {
-        const float4 q = rr[lane + 32 * k];
-        o.x += rs * q.x; o.y += rs * q.y; o.z += rs * q.z; o.w += rs * q.w;
-      }
+      o.x += rs * q[k].x; o.y += rs * q[k].y; o.z += rs * q[k].z; o.w += rs * q[k].w;
       if (dx_f32) reinterpret_cast<float4*>(dx_f32 + (size_t)row * D)[lane + 32 * k] = o;
       if (dx_t) store4<T>(dx_t + (size_t)row * D + 4 * (lane + 32 * k), o.x, o.y, o.z, o.w);
     }
@@ -280,7 +342,7 @@ rmsnorm_backward_reg_kernel(const float* __restrict__ dy, const float* __restric
       for (int i = threadIdx.x; i < D; i += blockDim.x) {
         float t = 0.f;
 #pragma unroll
-        for (int wq = 0; wq < kWarpsPerBlock; ++wq) t += s_dw[wq][i];
+        for (int wq = 0; wq < kRmsBwdWarps; ++wq) t += s_dw[wq][i];
         atomicAdd(dw + i, t);
       }
     }
@@ -293,10 +355,10 @@ void rmsnorm_backward(const float* dy, const float* x, const float* w, const flo
   if (M <= 0) return;
   int blocks = (M + kWarpsPerBlock - 1) / kWarpsPerBlock;
   if (D % 128 == 0 && D <= 1024) {
-    const int rb = std::min(blocks, 148 * 4);
+    const int rb = std::min((M + kRmsBwdWarps - 1) / kRmsBwdWarps, 148);
 #define ANE_RMS_BWD_CASE(NV)                                                                                      \
   case NV:                                                                                                         \
-    launch_pdl(rmsnorm_backward_reg_kernel<T, NV>, dim3(rb), dim3(kWarpsPerBlock * 32), 0, s, dy, x, w, rstd, res,  \
+    launch_pdl(rmsnorm_backward_reg_kernel<T, NV>, dim3(rb), dim3(kRmsBwdWarps * 32), 0, s, dy, x, w, rstd, res,    \
                res_scale, dx_f32, dx_t, dw, M);                                                                    \
     return;
     switch (D / 128) {
