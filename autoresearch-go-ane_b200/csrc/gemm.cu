@@ -118,10 +118,10 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
                      const EpiParams& epi,
                      const GemmDesc& d, int split_k, int* d_status, cudaStream_t stream) {
   auto kern = gemm_tc_kernel<BN, MT, A_MN, B_MN, EPI>;
+  constexpr uint32_t smem_bytes = GemmCfg<BN, MT>::SMEM_BYTES + (EPI == EPI_STORE_F32_TMARES ? GEMM_TMARES_BYTES : 0u);
   static bool attr_set = false;  // per template instantiation
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)GemmCfg<BN, MT>::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
     if (e != cudaSuccess) {
       g_gemm_err = std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e);
       return -3;
@@ -141,7 +141,7 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     grid = (int)g;
   }
   if (grid < 1) grid = 1;
-  cudaError_t e = launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), GemmCfg<BN, MT>::SMEM_BYTES, stream, ta, tb, tc, td, epi, d.M, d.N,
+  cudaError_t e = launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), smem_bytes, stream, ta, tb, tc, td, epi, d.M, d.N,
                              d.K, split_k, d_status);
   if (e != cudaSuccess) {
     g_gemm_err = std::string("gemm_tc launch: ") + cudaGetErrorString(e);
@@ -182,8 +182,18 @@ static int dispatch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
     }
   }
   if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 32, 32, true)) return -2;
-  if (d.out == GEMM_OUT_F32)
+  if (d.out == GEMM_OUT_F32) {
+    // One residual, K-major operands and room for the residual buffers: let TMA fetch the residual pieces.
+    if constexpr (!A_MN && !B_MN && GemmCfg<BN, MT>::SMEM_BYTES + GEMM_TMARES_BYTES <= 232448u) {
+      static const bool no_tma_res = getenv("ANE_B200_NO_TMA_RES") != nullptr;  // A/B measurements
+      if (d.res1 != nullptr && d.res2 == nullptr && !no_tma_res) {
+        CUtensorMap td;
+        if (!make_tmap(&td, d.res1, d.N, d.M, d.ldres, 32, 32, true)) return -2;
+        return launch_tc<BN, MT, A_MN, B_MN, EPI_STORE_F32_TMARES>(ta, tb, tc, td, epi, d, 1, d_status, stream);
+      }
+    }
     return launch_tc<BN, MT, A_MN, B_MN, EPI_STORE_F32>(ta, tb, tc, tc, epi, d, 1, d_status, stream);
+  }
   return launch_tc<BN, MT, A_MN, B_MN, EPI_REDUCE_F32>(ta, tb, tc, tc, epi, d, split_k, d_status, stream);
 }
 

@@ -74,7 +74,12 @@ enum EpiKind : int {
   // EPI_STORE_BF16 with the rotary embedding applied to the fp32 accumulators of the q|k heads (one
   // 64-column piece = one head); each epilogue thread keeps the cos/sin row of its token in registers.
   EPI_STORE_BF16_ROPE = 4,
+  // C(fp32) = alpha*acc + s1*res1 with the residual pieces fetched by TMA (two 32-row x 128-byte buffers
+  // per epilogue warp, two pieces ahead) instead of by per-thread row loads: the residual read then costs
+  // one bulk copy per piece.  Needs 32 KB of shared memory beyond GemmCfg::SMEM_BYTES.
+  EPI_STORE_F32_TMARES = 5,
 };
+static constexpr uint32_t GEMM_TMARES_BYTES = 4 * 2 * 4096;
 
 struct EpiParams {
   float alpha;
@@ -158,6 +163,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __shared__ __align__(8) uint64_t bar_tfull[NBUF];
   __shared__ __align__(8) uint64_t bar_tempty[NBUF];
   __shared__ uint32_t tmem_slot;
+  __shared__ __align__(8) uint64_t bar_res[4][2];  // EPI_STORE_F32_TMARES: residual piece landed
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smem_a0 = smem_base;
@@ -176,6 +182,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    if constexpr (EPI == EPI_STORE_F32_TMARES) {
+      for (int w = 0; w < 4; ++w)
+        for (int b = 0; b < 2; ++b) mbar_init(smem_u32(&bar_res[w][b]), 1);
+      tma_prefetch_desc(&tmD);
     }
     for (int b = 0; b < NBUF; ++b) {
       mbar_init(smem_u32(&bar_tfull[b]), 1);
@@ -300,10 +311,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int sbuf = 0;
     bool ok = true;
     float a1 = 0.f, a2 = 0.f;
-    if constexpr (EPI == EPI_STORE_F32) {
+    if constexpr (EPI == EPI_STORE_F32 || EPI == EPI_STORE_F32_TMARES) {
       if (epi.res1) a1 = epi.s1 ? *epi.s1 : 1.f;
       if (epi.res2) a2 = epi.s2 ? *epi.s2 : 1.f;
     }
+    // EPI_STORE_F32_TMARES: this warp's two residual buffers, behind the store staging of all four warps
+    const uint32_t res_base = smem_stage0 + Cfg::STAGING_BYTES + (uint32_t)(warp - 2) * 8192u;
+    const uint8_t* res_ptr = smem_raw + (res_base - smem_u32(smem_raw));
+    uint32_t res_uses = 0;  // pieces consumed so far (buffer = uses & 1, phase = (uses >> 1) & 1)
     GemmSched sched;
     sched.init(M, N, K, BM, BN, split_k);
     int tm, tn, kb0, kb1;
@@ -326,6 +341,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       };
       prefetch_first(tm * BM + lane_group * 32 + lane);
+      // Residual piece `piece` (counted over the whole kernel) of the current (tile, sub): same validity test as
+      // the consuming loop, so every issued piece is consumed.
+      uint32_t res_issued = res_uses;
+      auto issue_res = [&](int m_w, int n0r) {
+        if constexpr (EPI == EPI_STORE_F32_TMARES) {
+          if (n0r < N && n0r < (tn + 1) * BN && m_w < M) {
+            if (lane == 0) {
+              const uint32_t b = res_issued & 1u;
+              const uint32_t bar = smem_u32(&bar_res[warp - 2][b]);
+              mbar_expect_tx(bar, 4096);
+              tma_load_2d(res_base + b * 4096u, &tmD, bar, n0r, m_w);
+            }
+            ++res_issued;
+          }
+        }
+      };
+      if constexpr (EPI == EPI_STORE_F32_TMARES) {  // first two pieces of sub-tile 0, while the MMAs still run
+        issue_res(tm * BM + lane_group * 32, tn * BN);
+        issue_res(tm * BM + lane_group * 32, tn * BN + CW);
+      }
       if (!mbar_wait(smem_u32(&bar_tfull[buf]), tphase, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
         ok = false;
         break;
@@ -335,7 +370,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int sub = 0; sub < MT; ++sub) {
       const int m_warp = tm * BM + sub * GEMM_BM + lane_group * 32;
       const int m = m_warp + lane;
-      if (sub > 0) prefetch_first(m);
+      if (sub > 0) {
+        prefetch_first(m);
+        if constexpr (EPI == EPI_STORE_F32_TMARES) {
+          issue_res(m_warp, tn * BN);
+          issue_res(m_warp, tn * BN + CW);
+        }
+      }
       uint32_t gate_even[16];  // EPI_STORE_BF16_SWIGLU: the even piece's half of a gate row
       float4 rc4[8], rs4[8];   // EPI_STORE_BF16_ROPE: cos / sin of this thread's token, 32 pairs
       if constexpr (EPI == EPI_STORE_BF16_ROPE) {
@@ -445,10 +486,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const float* r1 = (EPI == EPI_STORE_F32 && epi.res1 && in_rows) ? epi.res1 + (size_t)m * epi.ldres + n0 : nullptr;
           const float* r2 = (EPI == EPI_STORE_F32 && epi.res2 && in_rows) ? epi.res2 + (size_t)m * epi.ldres + n0 : nullptr;
           const bool full = n0 + 32 <= N;
+          const uint8_t* res_row = nullptr;
+          if constexpr (EPI == EPI_STORE_F32_TMARES) {
+            const uint32_t b = res_uses & 1u;
+            if (!mbar_wait(smem_u32(&bar_res[warp - 2][b]), (res_uses >> 1) & 1u, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
+              ok = false;
+              break;
+            }
+            res_row = res_ptr + b * 4096u + lane * 128;
+          }
 #pragma unroll
           for (int q = 0; q < 8; ++q) {  // 8 chunks of 4 fp32
             float4 v = make_float4(epi.alpha * acc[4 * q], epi.alpha * acc[4 * q + 1], epi.alpha * acc[4 * q + 2],
                                    epi.alpha * acc[4 * q + 3]);
+            if constexpr (EPI == EPI_STORE_F32_TMARES) {  // rows / columns outside the tensor arrive as zeros
+              const float4 t = *reinterpret_cast<const float4*>(res_row + ((q ^ (lane & 7)) << 4));
+              v.x += a1 * t.x; v.y += a1 * t.y; v.z += a1 * t.z; v.w += a1 * t.w;
+            }
             if constexpr (EPI == EPI_STORE_F32) {
               if (r1) {
                 if (cur_ok) {
@@ -481,6 +535,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         fence_proxy_async_smem();
         __syncwarp();
+        if constexpr (EPI == EPI_STORE_F32_TMARES) {  // this residual buffer is free: fetch the piece after next
+          ++res_uses;
+          issue_res(m_warp, n0 + 2 * CW);
+        }
         if (lane == 0) {
           const uint32_t src = stage_base + (uint32_t)sbuf * 4096u;
           if constexpr (EPI == EPI_REDUCE_F32) tma_reduce_add_2d(&tmC, src, n0, m_warp);

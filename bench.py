@@ -303,10 +303,15 @@ def run_ours(args):
                                          "d2h_bytes_per_op": nb * T * WORKLOAD["vocab"] * 4,
                                          "note": "host-visible, fp32 logits for 64 x seq tokens copied to the host"}
         if T >= 768:  # prompt 512 + 256 generated tokens must fit the KV cache (= seq)
+            # decoding runs 32 sequences at once, whatever the training micro-batch: a second engine
+            e.close()
+            e = ane.open(ane.Options(tokens=tokens, batch=32, arch=ane.ARCH_LLAMA, quirks=0, compute_dtype=ane.DTYPE_BF16,
+                                     accum_steps=1, seed=42, device=local_rank, **WORKLOAD))
+            init_weights(e, ane, seed=1234, cfg=WORKLOAD)
             prompts = np.ascontiguousarray(tokens[:32 * 512].reshape(32, 512))
             e.decode_greedy(prompts[:, :64], 4)
             t0 = time.perf_counter()
-            out = e.decode_greedy(prompts, 256)
+            e.decode_greedy(prompts, 256)
             dt = time.perf_counter() - t0
             extras["decode_greedy"] = {"batch": 32, "prompt": 512, "new_tokens": 256, "seconds": round(dt, 4),
                                        "generated_tok_per_s": round(32 * 256 / dt, 1),
