@@ -319,7 +319,7 @@ def run_ours(args):
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload == "110m":
-        cpu_baseline = cpu_reference_leg(steps=1, warmup=0)
+        cpu_baseline = cpu_reference_leg(steps=8, warmup=1)
     e.close()
     if rank == 0:
         line = {
