@@ -269,6 +269,7 @@ class EngineT final : public EngineBase {
   cudaEvent_t ev_dw_in_ = nullptr;
   bool dw_overlap_ = true;
   float *rstdf_ = nullptr, *logits_ = nullptr, *loss_rows_ = nullptr, *inv_valid_ = nullptr, *d_loss_ = nullptr;
+  float* tgt_logit_ = nullptr;             // fp32 logit of every row's target (bf16-logits cross-entropy)
   T* dlogits_ = nullptr;
   T* dlogits2_ = nullptr;                  // second chunk buffer: the classifier dW GEMM of chunk c runs on the
   cudaEvent_t ev_cls_ce_[2] = {nullptr, nullptr};  // side stream while chunk c+1 is computed
@@ -486,7 +487,7 @@ int EngineT<T>::alloc_buffers() {
   A(dgate_, (size_t)M_ * Hd_); A(dh13_[0], (size_t)M_ * N13_); A(dh13_[1], (size_t)M_ * N13_); A(datt_, (size_t)M_ * QD_);
   A(xnf_, MD); A(rstdf_, M_); A(att_delta_, (size_t)B_ * H_ * S_);
   A(logits_, (size_t)ce_rows_ * V_); A(dlogits_, (size_t)ce_rows_ * V_); A(dlogits2_, (size_t)ce_rows_ * V_);
-  A(loss_rows_, M_); A(inv_valid_, B_); A(d_loss_, 4);
+  A(loss_rows_, M_); A(inv_valid_, B_); A(d_loss_, 4); A(tgt_logit_, M_);
   A(rope_cos_, (size_t)S_ * (hd_ / 2)); A(rope_sin_, (size_t)S_ * (hd_ / 2));
   A(d_acc_, 2); A(d_scales_, 4); A(d_norm_, 2); A(d_status_, 1);
   A(d_in_, M_); A(d_tgt_, M_); A(d_pos_, B_);
@@ -794,11 +795,23 @@ int EngineT<T>::head_and_backward(int B) {
     GemmDesc g;
     g.A = xnf_ + (size_t)r0 * D_; g.B = wop(s_embed_.off); g.C = logits_;
     g.M = rows; g.N = V_; g.K = D_; g.lda = D_; g.ldb = D_; g.ldc = V_; g.out = GEMM_OUT_F32;
+    if constexpr (!kIsF32) {
+      // bf16 logits (half the traffic of the chunk) plus the target logit of every row in fp32; the buffer is
+      // the fp32 one, half used
+      g.out = GEMM_OUT_BF16_TGT;
+      g.tgt = d_tgt_;
+      g.tgt_out = tgt_logit_;
+      g.tgt_row0 = r0;
+    }
     count_launch();
     if ((rc = gemm(g)) != 0) return rc;
     count_launch();
-    cross_entropy_rows<T>(logits_, d_tgt_, inv_valid_, dlogits, loss_rows_, rows, r0, S_, V_, isN_, o_.loss_scale,
-                          stream_);
+    if constexpr (!kIsF32)
+      cross_entropy_rows_bf16(reinterpret_cast<const bf16*>(logits_), d_tgt_, inv_valid_, tgt_logit_, dlogits, loss_rows_,
+                              rows, r0, S_, V_, isN_, o_.loss_scale, stream_);
+    else
+      cross_entropy_rows<T>(logits_, d_tgt_, inv_valid_, dlogits, loss_rows_, rows, r0, S_, V_, isN_, o_.loss_scale,
+                            stream_);
     if (dws != stream_) {
       cudaEventRecord(ev_cls_ce_[cb], stream_);
       cudaStreamWaitEvent(dws, ev_cls_ce_[cb], 0);

@@ -154,11 +154,24 @@ template <int BN, int MT, bool A_MN, bool B_MN>
 static int dispatch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const GemmDesc& d, int split_k,
                         int* d_status, cudaStream_t stream) {
   EpiParams epi{d.alpha, d.res1, d.s1, d.res2, d.s2, d.ldres, reinterpret_cast<bf16*>(d.aux), d.ldaux,
-                d.rope_cos, d.rope_sin, d.rope_seq, d.rope_pos0, d.rope_cols};
+                d.rope_cos, d.rope_sin, d.rope_seq, d.rope_pos0, d.rope_cols, d.tgt, d.tgt_out, d.tgt_row0};
   CUtensorMap tc;
   if (d.out == GEMM_OUT_BF16) {
     if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 64, 32, false)) return -2;
     return launch_tc<BN, MT, A_MN, B_MN, EPI_STORE_BF16>(ta, tb, tc, tc, epi, d, 1, d_status, stream);
+  }
+  if (d.out == GEMM_OUT_BF16_TGT) {
+    if constexpr (!A_MN && !B_MN) {
+      if (d.tgt == nullptr || d.tgt_out == nullptr) {
+        g_gemm_err = "target-logit epilogue: missing target pointers";
+        return -2;
+      }
+      if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 64, 32, false)) return -2;
+      return launch_tc<BN, MT, A_MN, B_MN, EPI_STORE_BF16_TGT>(ta, tb, tc, tc, epi, d, 1, d_status, stream);
+    } else {
+      g_gemm_err = "the target-logit epilogue takes K-major operands only";
+      return -2;
+    }
   }
   if (d.out == GEMM_OUT_BF16_ROPE) {
     if constexpr (!A_MN && !B_MN) {

@@ -26,6 +26,10 @@ enum GemmOut : int {
   // `rope_cols` by the angle of the row's position (rope_pos0 + row % rope_seq): the q|k part of a packed
   // q|k|v projection with head_dim 64.  cos/sin tables are [positions, 32] fp32.  K-major operands only.
   GEMM_OUT_BF16_ROPE = 4,
+  // store bf16 and, for every row whose target column (tgt[tgt_row0 + row]) falls inside the matrix, also
+  // that one element in fp32 into tgt_out[tgt_row0 + row]: classifier logits for the cross-entropy, which
+  // then reads bf16 logits but takes the target logit at full precision.  K-major operands only.
+  GEMM_OUT_BF16_TGT = 5,
 };
 
 struct GemmDesc {
@@ -47,6 +51,9 @@ struct GemmDesc {
   const float* rope_cos = nullptr;  // GEMM_OUT_BF16_ROPE
   const float* rope_sin = nullptr;
   int rope_seq = 0, rope_pos0 = 0, rope_cols = 0;
+  const uint16_t* tgt = nullptr;  // GEMM_OUT_BF16_TGT
+  float* tgt_out = nullptr;
+  int tgt_row0 = 0;
   int split_k = 0;  // 0 => choose
 };
 

@@ -78,6 +78,8 @@ enum EpiKind : int {
   // per epilogue warp, two pieces ahead) instead of by per-thread row loads: the residual read then costs
   // one bulk copy per piece.  Needs 32 KB of shared memory beyond GemmCfg::SMEM_BYTES.
   EPI_STORE_F32_TMARES = 5,
+  // EPI_STORE_BF16 that also writes the accumulator of each row's target column in fp32.
+  EPI_STORE_BF16_TGT = 6,
 };
 static constexpr uint32_t GEMM_TMARES_BYTES = 4 * 2 * 4096;
 
@@ -93,6 +95,9 @@ struct EpiParams {
   const float* rope_cos;  // EPI_STORE_BF16_ROPE: [positions, 32]
   const float* rope_sin;
   int rope_seq, rope_pos0, rope_cols;
+  const uint16_t* tgt;  // EPI_STORE_BF16_TGT
+  float* tgt_out;
+  int tgt_row0;
 };
 
 // Work scheduler shared by the three warp roles (each role walks the same sequence).
@@ -303,7 +308,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ------------------------------ epilogue warps ------------------------------
     const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, 32*lane_group+32)
     // Columns per staged piece: 128 bytes of output per row.
-    constexpr bool kBf16Out = (EPI == EPI_STORE_BF16 || EPI == EPI_STORE_BF16_SWIGLU || EPI == EPI_STORE_BF16_ROPE);
+    constexpr bool kBf16Out = (EPI == EPI_STORE_BF16 || EPI == EPI_STORE_BF16_SWIGLU || EPI == EPI_STORE_BF16_ROPE ||
+                               EPI == EPI_STORE_BF16_TGT);
     constexpr int CW = kBf16Out ? 64 : 32;
     const uint32_t stage_base = smem_stage0 + (uint32_t)(warp - 2) * 8192u;
     uint8_t* stage_ptr = smem_raw + (stage_base - smem_u32(smem_raw));
@@ -377,6 +383,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           issue_res(m_warp, tn * BN + CW);
         }
       }
+      int tgt_col = -1;        // EPI_STORE_BF16_TGT: this row's target column
+      if constexpr (EPI == EPI_STORE_BF16_TGT) {
+        if (m < M) tgt_col = (int)epi.tgt[epi.tgt_row0 + m];
+      }
       uint32_t gate_even[16];  // EPI_STORE_BF16_SWIGLU: the even piece's half of a gate row
       float4 rc4[8], rs4[8];   // EPI_STORE_BF16_ROPE: cos / sin of this thread's token, 32 pairs
       if constexpr (EPI == EPI_STORE_BF16_ROPE) {
@@ -423,6 +433,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         __syncwarp();
         uint8_t* row_ptr = stage_ptr + sbuf * 4096 + lane * 128;
         if constexpr (kBf16Out) {
+          if constexpr (EPI == EPI_STORE_BF16_TGT) {
+            const int t = tgt_col - n0;
+            if (t >= 0 && t < CW) {  // one piece per row at most
+              float v = 0.f;
+#pragma unroll
+              for (int e = 0; e < CW; ++e) v = (e == t) ? acc[e] : v;
+              epi.tgt_out[epi.tgt_row0 + m] = epi.alpha * v;
+            }
+          }
           if constexpr (EPI == EPI_STORE_BF16_ROPE) {
             if (n0 < epi.rope_cols && m < M) {  // pairs (2p, 2p+1) of this head
               const float* rc = reinterpret_cast<const float*>(rc4);

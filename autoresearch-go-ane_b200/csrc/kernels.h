@@ -115,6 +115,10 @@ template <typename TO>
 void cross_entropy_rows(const float* logits, const uint16_t* targets, const float* inv_valid, TO* dlogits,
                         float* loss_rows, int rows, int row0, int seq, int V, bool softcap, float grad_scale,
                         cudaStream_t s);
+// The same from bf16 logits, with the (raw) target logit of every row supplied in fp32.
+void cross_entropy_rows_bf16(const bf16* logits, const uint16_t* targets, const float* inv_valid, const float* tgt_logit,
+                             bf16* dlogits, float* loss_rows, int rows, int row0, int seq, int V, bool softcap,
+                             float grad_scale, cudaStream_t s);
 void softcap_inplace(float* logits, uint64_t n, cudaStream_t s);
 // inv_valid[b] = 1/count(targets[b,:] < V) (0 when none); ane/stories/cpu.go:276-279.
 void count_valid_targets(const uint16_t* targets, float* inv_valid, int B, int seq, int V, cudaStream_t s);

@@ -115,6 +115,129 @@ cross_entropy_rows_kernel(const float* __restrict__ logits, const uint16_t* __re
   }
 }
 
+// Same loss and gradient from bf16 logits (16-byte loads of 8), with the target logit supplied in fp32
+// (tgt_logit[row], written by the classifier GEMM epilogue): the log-sum-exp of rounded logits errs by a
+// probability-weighted mean of zero-mean rounding errors, while the target term, which would carry its
+// rounding error into the loss one to one, stays exact.
+__global__ void __launch_bounds__(kCEThreads)
+cross_entropy_rows_bf16_kernel(const bf16* __restrict__ logits, const uint16_t* __restrict__ targets,
+                               const float* __restrict__ inv_valid, const float* __restrict__ tgt_logit,
+                               bf16* __restrict__ dlogits, float* __restrict__ loss_rows, int rows, int row0, int seq,
+                               int V, int softcap, float grad_scale) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  if (r >= rows) return;
+  const int grow = row0 + r;
+  const uint4* x8 = reinterpret_cast<const uint4*>(logits + (size_t)r * V);
+  uint4* d8 = dlogits ? reinterpret_cast<uint4*>(dlogits + (size_t)r * V) : nullptr;
+  const int tgt = targets[grow];
+  const int V8 = V >> 3;  // V is a multiple of 8 (checked when the engine opens)
+  __shared__ float s_m[kCEThreads / 32], s_l[kCEThreads / 32];
+  __shared__ float s_bm, s_bl;
+  if (tgt >= V) {  // invalid target: zero gradient row, not counted (cpu.go:253-258)
+    if (d8)
+      for (int i = threadIdx.x; i < V8; i += kCEThreads) d8[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (threadIdx.x == 0 && loss_rows) loss_rows[grow] = 0.f;
+    return;
+  }
+  float m = -INFINITY, l = 0.f;
+#pragma unroll 2
+  for (int i = threadIdx.x; i < V8; i += kCEThreads) {
+    const uint4 q = x8[i];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+    float z[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]);
+      z[2 * k] = softcap ? softcap_f(f.x) : f.x;
+      z[2 * k + 1] = softcap ? softcap_f(f.y) : f.y;
+    }
+    float zm = z[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) zm = fmaxf(zm, z[k]);
+    if (zm > m) {
+      l *= __expf(m - zm);
+      m = zm;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) l += __expf(z[k] - m);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o), l2 = __shfl_xor_sync(0xffffffffu, l, o);
+    const float mn = fmaxf(m, m2);
+    l = (m == -INFINITY ? 0.f : l * __expf(m - mn)) + (m2 == -INFINITY ? 0.f : l2 * __expf(m2 - mn));
+    m = mn;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    s_m[warp] = m;
+    s_l[warp] = l;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float bm = s_m[0], bl = s_l[0];
+    for (int w = 1; w < kCEThreads / 32; ++w) {
+      const float mn = fmaxf(bm, s_m[w]);
+      bl = (bm == -INFINITY ? 0.f : bl * __expf(bm - mn)) + (s_m[w] == -INFINITY ? 0.f : s_l[w] * __expf(s_m[w] - mn));
+      bm = mn;
+    }
+    s_bm = bm;
+    s_bl = bl;
+    if (loss_rows) {
+      float zt = tgt_logit[grow];
+      if (softcap) zt = softcap_f(zt);
+      loss_rows[grow] = -logf(fmaxf(expf(zt - bm) / bl, 1e-10f));
+    }
+  }
+  __syncthreads();
+  if (!d8) return;
+  const float bm = s_bm;
+  const float inv_sum = 1.0f / s_bl;
+  const float gs = grad_scale * inv_valid[grow / seq];
+  for (int i = threadIdx.x; i < V8; i += kCEThreads) {
+    const uint4 q = x8[i];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+    float outv[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float2 f = __bfloat1622float2(h[k >> 1]);
+      const float raw = (k & 1) ? f.y : f.x;
+      float z = raw, dcap = 1.f;
+      if (softcap) {
+        const float th = tanhf(raw * (1.0f / 15.0f));
+        z = 15.0f * th;
+        dcap = 1.f - th * th;
+      }
+      const float p = __expf(z - bm) * inv_sum;
+      outv[k] = gs * (p - ((8 * i + k) == tgt ? 1.f : 0.f)) * dcap;
+    }
+    uint4 u;
+    __nv_bfloat162 t;
+    t = __floats2bfloat162_rn(outv[0], outv[1]); u.x = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(outv[2], outv[3]); u.y = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(outv[4], outv[5]); u.z = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(outv[6], outv[7]); u.w = *reinterpret_cast<uint32_t*>(&t);
+    d8[i] = u;
+  }
+}
+
+void cross_entropy_rows_bf16(const bf16* logits, const uint16_t* targets, const float* inv_valid, const float* tgt_logit,
+                             bf16* dlogits, float* loss_rows, int rows, int row0, int seq, int V, bool softcap,
+                             float grad_scale, cudaStream_t s) {
+  if (rows <= 0) return;
+  static bool attr_done = false;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(cross_entropy_rows_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kCEResidencySmem) != cudaSuccess)
+      return;
+    attr_done = true;
+  }
+  launch_pdl(cross_entropy_rows_bf16_kernel, dim3(rows), dim3(kCEThreads), kCEResidencySmem, s, logits, targets, inv_valid,
+             tgt_logit, dlogits, loss_rows, rows, row0, seq, V, softcap ? 1 : 0, grad_scale);
+}
+
 template <typename TO>
 void cross_entropy_rows(const float* logits, const uint16_t* targets, const float* inv_valid, TO* dlogits,
                         float* loss_rows, int rows, int row0, int seq, int V, bool softcap, float grad_scale,
@@ -149,6 +272,8 @@ void softcap_inplace(float* logits, uint64_t n, cudaStream_t s) {
 
 __global__ void count_valid_targets_kernel(const uint16_t* __restrict__ targets, float* __restrict__ inv_valid, int B,
                                            int seq, int V) {
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x;
   if (b >= B) return;
   int c = 0;
@@ -165,12 +290,14 @@ __global__ void count_valid_targets_kernel(const uint16_t* __restrict__ targets,
 }
 void count_valid_targets(const uint16_t* targets, float* inv_valid, int B, int seq, int V, cudaStream_t s) {
   if (B <= 0) return;
-  count_valid_targets_kernel<<<B, 128, 0, s>>>(targets, inv_valid, B, seq, V);
+  launch_pdl(count_valid_targets_kernel, dim3(B), dim3(128), 0, s, targets, inv_valid, B, seq, V);
 }
 
 // loss_out[0] = (1/B) * sum_b inv_valid[b] * sum_t loss_rows[b,t]   (single block, double accumulation)
 __global__ void reduce_loss_kernel(const float* __restrict__ loss_rows, const float* __restrict__ inv_valid,
                                    float* __restrict__ loss_out, int B, int seq) {
+  pdl_trigger();
+  pdl_wait();
   double local = 0.0;
   const int n = B * seq;
   for (int i = threadIdx.x; i < n; i += blockDim.x) local += (double)loss_rows[i] * (double)inv_valid[i / seq];
@@ -186,7 +313,7 @@ __global__ void reduce_loss_kernel(const float* __restrict__ loss_rows, const fl
 }
 void reduce_loss(const float* loss_rows, const float* inv_valid, float* loss_out, int B, int seq, cudaStream_t s) {
   if (B <= 0) return;
-  reduce_loss_kernel<<<1, 1024, 0, s>>>(loss_rows, inv_valid, loss_out, B, seq);
+  launch_pdl(reduce_loss_kernel, dim3(1), dim3(1024), 0, s, loss_rows, inv_valid, loss_out, B, seq);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -194,6 +321,8 @@ void reduce_loss(const float* loss_rows, const float* inv_valid, float* loss_out
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 sumsq_kernel(const float* __restrict__ g, uint64_t n, float pre_scale, double* __restrict__ acc) {
+  pdl_trigger();
+  pdl_wait();
   const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
   double local = 0.0;
@@ -233,11 +362,13 @@ void sumsq_accumulate(const float* g, uint64_t n, float pre_scale, double* acc, 
   if (!n) return;
   uint64_t grid = (n + 255) / 256;
   if (grid > 148ull * 8) grid = 148ull * 8;
-  sumsq_kernel<<<(unsigned)grid, 256, 0, s>>>(g, n, pre_scale, acc);
+  launch_pdl(sumsq_kernel, dim3((unsigned)grid), dim3(256), 0, s, g, n, pre_scale, acc);
 }
 
 __global__ void finalize_clip_kernel(const double* __restrict__ acc, float pre_scale, float clip,
                                      float* __restrict__ scales, float* __restrict__ norm_out) {
+  pdl_trigger();
+  pdl_wait();
   const double norm2 = acc[0];
   float s = 1.f;
   const float norm = (float)sqrt(norm2);
@@ -247,7 +378,7 @@ __global__ void finalize_clip_kernel(const double* __restrict__ acc, float pre_s
   if (norm_out) norm_out[0] = norm;
 }
 void finalize_clip(const double* acc, float pre_scale, float clip, float* scales, float* norm_out, cudaStream_t s) {
-  finalize_clip_kernel<<<1, 1, 0, s>>>(acc, pre_scale, clip, scales, norm_out);
+  launch_pdl(finalize_clip_kernel, dim3(1), dim3(1), 0, s, acc, pre_scale, clip, scales, norm_out);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -266,6 +397,8 @@ __device__ __forceinline__ void adam_one(float& w, float g, float& m, float& v, 
 __global__ void __launch_bounds__(256)
 adam_kernel(float* __restrict__ w, float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
             bf16* __restrict__ shadow, uint64_t n, AdamHyper h, const float* __restrict__ gscale, int vec_ok) {
+  pdl_trigger();
+  pdl_wait();
   const float gs = gscale ? *gscale : 1.f;
   const uint64_t n4 = vec_ok ? (n >> 2) : 0;
   uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -311,7 +444,7 @@ void adam_update(float* w, float* g, float* m, float* v, bf16* shadow, uint64_t 
   if (grid < 1) grid = 1;
   auto al = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
   const int vec_ok = al(w, 16) && al(g, 16) && al(m, 16) && al(v, 16) && (!shadow || al(shadow, 8));
-  adam_kernel<<<(unsigned)grid, 256, 0, s>>>(w, g, m, v, shadow, n, h, gscale, vec_ok);
+  launch_pdl(adam_kernel, dim3((unsigned)grid), dim3(256), 0, s, w, g, m, v, shadow, n, h, gscale, vec_ok);
 }
 
 }  // namespace ane

@@ -15,6 +15,8 @@ static constexpr int kWarpsPerBlock = 8;
 __global__ void embed_forward_kernel(const uint16_t* __restrict__ tok, const float* __restrict__ embed,
                                      float* __restrict__ x, float* __restrict__ x_raw, int M, int D, int vocab,
                                      int embed_norm) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= M) return;
@@ -43,11 +45,13 @@ void embed_forward(const uint16_t* tok, const float* embed, float* x, float* x_r
                    bool embed_norm, cudaStream_t s) {
   if (M <= 0) return;
   const int blocks = (M + kWarpsPerBlock - 1) / kWarpsPerBlock;
-  embed_forward_kernel<<<blocks, kWarpsPerBlock * 32, 0, s>>>(tok, embed, x, x_raw, M, D, vocab, embed_norm ? 1 : 0);
+  launch_pdl(embed_forward_kernel, dim3(blocks), dim3(kWarpsPerBlock * 32), 0, s, tok, embed, x, x_raw, M, D, vocab, embed_norm ? 1 : 0);
 }
 
 __global__ void embed_backward_kernel(const uint16_t* __restrict__ tok, const float* __restrict__ dx,
                                       float* __restrict__ g_embed, int M, int D, int vocab) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= M) return;
@@ -61,7 +65,7 @@ __global__ void embed_backward_kernel(const uint16_t* __restrict__ tok, const fl
 void embed_backward(const uint16_t* tok, const float* dx, float* g_embed, int M, int D, int vocab, cudaStream_t s) {
   if (M <= 0) return;
   const int blocks = (M + kWarpsPerBlock - 1) / kWarpsPerBlock;
-  embed_backward_kernel<<<blocks, kWarpsPerBlock * 32, 0, s>>>(tok, dx, g_embed, M, D, vocab);
+  launch_pdl(embed_backward_kernel, dim3(blocks), dim3(kWarpsPerBlock * 32), 0, s, tok, dx, g_embed, M, D, vocab);
 }
 
 // ------------------------------------------------------------------------------------------
