@@ -546,7 +546,7 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
   QD_ = H_ * hd_; KVD_ = KV_ * hd_; QKVD_ = QD_ + 2 * KVD_;
   N13_ = isN_ ? Hd_ : 2 * Hd_;
   att_tc_ = !qkv_f32_ && attention_tc_supported(hd_);
-  ce_rows_ = o_.ce_chunk_rows > 0 ? o_.ce_chunk_rows : 4096;
+  ce_rows_ = o_.ce_chunk_rows > 0 ? o_.ce_chunk_rows : 8192;  // 8192 x 32000 bf16 logits = 524 MB per chunk
   if (ce_rows_ > M_) ce_rows_ = M_;
   ce_rows_ = std::max(ce_rows_, std::min(M_, S_));  // eval logits uses one sequence per chunk
   lr_ = o_.lr;
