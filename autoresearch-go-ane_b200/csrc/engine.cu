@@ -274,6 +274,7 @@ class EngineT final : public EngineBase {
   T* dlogits2_ = nullptr;                  // second chunk buffer: the classifier dW GEMM of chunk c runs on the
   cudaEvent_t ev_cls_ce_[2] = {nullptr, nullptr};  // side stream while chunk c+1 is computed
   cudaEvent_t ev_cls_dw_[2] = {nullptr, nullptr};
+  cudaEvent_t ev_logits_[8] = {};          // EvalLogits: one per downloaded piece
   float *rope_cos_ = nullptr, *rope_sin_ = nullptr;
   double* d_acc_ = nullptr;
   float *d_scales_ = nullptr, *d_norm_ = nullptr;
@@ -340,6 +341,11 @@ void EngineT<T>::destroy() {
     if (*e) {
       cudaEventDestroy(*e);
       *e = nullptr;
+    }
+  for (auto& e : ev_logits_)
+    if (e) {
+      cudaEventDestroy(e);
+      e = nullptr;
     }
   if (comm_stream_) {
     cudaStreamDestroy(comm_stream_);
@@ -561,6 +567,8 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
   if ((rc = cuda_check(cudaEventCreateWithFlags(&ev_dw_in_, cudaEventDisableTiming), "cudaEventCreate")) != 0) return rc;
   for (cudaEvent_t* e : {&ev_cls_ce_[0], &ev_cls_ce_[1], &ev_cls_dw_[0], &ev_cls_dw_[1]})
     if ((rc = cuda_check(cudaEventCreateWithFlags(e, cudaEventDisableTiming), "cudaEventCreate")) != 0) return rc;
+  for (auto& e : ev_logits_)
+    if ((rc = cuda_check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate")) != 0) return rc;
   ev_dw_done_.assign(o_.n_layers, nullptr);
   for (auto& ev : ev_dw_done_)
     if ((rc = cuda_check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate")) != 0) return rc;
@@ -1271,12 +1279,26 @@ int EngineT<T>::eval_logits(const uint16_t* tokens, uint32_t n_seq, float* out, 
         count_launch();
         softcap_inplace(logits_, per_seq, stream_);
       }
-      // device -> pinned staging (full PCIe rate) -> caller's buffer
-      if ((rc = cuda_check(cudaMemcpyAsync(h_logits_, logits_, sizeof(float) * per_seq, cudaMemcpyDeviceToHost, stream_),
-                           "logits download")) != 0)
-        return rc;
-      if ((rc = cuda_check(cudaStreamSynchronize(stream_), "logits sync")) != 0) return rc;
-      memcpy(out + (size_t)(s0 + b) * per_seq, h_logits_, sizeof(float) * per_seq);
+      // device -> pinned staging (full PCIe rate) -> caller's buffer, in pieces: the host copies piece i
+      // out of the staging buffer while pieces i+1.. are still crossing PCIe
+      constexpr int kPieces = 8;
+      const uint64_t piece = (per_seq + kPieces - 1) / kPieces;
+      for (int pi = 0; pi < kPieces; ++pi) {
+        const uint64_t off = (uint64_t)pi * piece;
+        if (off >= per_seq) break;
+        const uint64_t n = std::min(piece, per_seq - off);
+        if ((rc = cuda_check(cudaMemcpyAsync(h_logits_ + off, logits_ + off, sizeof(float) * n, cudaMemcpyDeviceToHost,
+                                             stream_), "logits download")) != 0)
+          return rc;
+        cudaEventRecord(ev_logits_[pi], stream_);
+      }
+      for (int pi = 0; pi < kPieces; ++pi) {
+        const uint64_t off = (uint64_t)pi * piece;
+        if (off >= per_seq) break;
+        const uint64_t n = std::min(piece, per_seq - off);
+        if ((rc = cuda_check(cudaEventSynchronize(ev_logits_[pi]), "logits sync")) != 0) return rc;
+        memcpy(out + (size_t)(s0 + b) * per_seq + off, h_logits_ + off, sizeof(float) * n);
+      }
     }
   }
   return check_device_status(nullptr);

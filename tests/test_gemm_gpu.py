@@ -49,9 +49,10 @@ def _fp(a):
     return a.ctypes.data_as(ctypes.POINTER(ctypes.c_float))
 
 
-def _gemm(dtype, A_store, B_store, C_init, M, N, K, a_mn, b_mn, out_mode, split_k=0):
+def _gemm(dtype, A_store, B_store, C_init, M, N, K, a_mn, b_mn, out_mode, split_k=0, res=None):
     upf = _up_bf16 if dtype == ane.DTYPE_BF16 else _up
     dA, dB, dC = upf(A_store), upf(B_store), _up(C_init)
+    dR = _up(res) if res is not None else None
     g = _ffi.GemmArgs()
     g.struct_size = ctypes.sizeof(_ffi.GemmArgs)
     g.dtype = dtype
@@ -59,15 +60,48 @@ def _gemm(dtype, A_store, B_store, C_init, M, N, K, a_mn, b_mn, out_mode, split_
     g.m, g.n, g.k = M, N, K
     g.lda, g.ldb, g.ldc = A_store.shape[1], B_store.shape[1], N
     g.a_mn, g.b_mn, g.out_mode, g.alpha, g.split_k = a_mn, b_mn, out_mode, 1.0, split_k
+    if dR is not None:
+        g.d_res1, g.ldres = dR, N
     _ck(lib.ane_op_gemm(ctypes.byref(g)))
     _ck(lib.ane_dev_sync())
     st = ctypes.c_int32(0)
     _ck(lib.ane_ops_device_status(ctypes.byref(st)))
     assert st.value == 0
     out = _down(dC, (M, N))
-    for p in (dA, dB, dC):
+    for p in (dA, dB, dC) + ((dR,) if dR is not None else ()):
         lib.ane_dev_free(p)
     return out
+
+
+def test_step_sized_shapes_take_the_wide_tile_and_tma_residual_paths():
+    """Shapes of the 110M step that select the 256-row tiles (long K, enough tiles), the stream-K weight
+    gradient on 256-row tiles and the TMA-fed residual epilogue; checked against numpy on the same
+    bf16-rounded operands (fp32 accumulation order differs, hence 1e-4)."""
+    rng = np.random.default_rng(3)
+    # dx form: C[M,N] = A[M,K] . B[K,N]
+    M, N, K = 8192, 768, 2304
+    A = _bf16_round(rng.standard_normal((M, K)).astype(np.float32) * 0.1)
+    B = _bf16_round(rng.standard_normal((K, N)).astype(np.float32) * 0.1)
+    got = _gemm(ane.DTYPE_BF16, A, B, np.zeros((M, N), np.float32), M, N, K, 0, 1, 1)
+    assert rel_l2(got, A @ B) < 1e-4
+    # dW form with accumulation: C[M,N] += A^T[M,K] . B[K,N], A stored [K, M]
+    M, N, K = 2304, 768, 8192
+    At = _bf16_round(rng.standard_normal((K, M)).astype(np.float32) * 0.1)
+    B = _bf16_round(rng.standard_normal((K, N)).astype(np.float32) * 0.1)
+    C0 = rng.standard_normal((M, N)).astype(np.float32)
+    got = _gemm(ane.DTYPE_BF16, At, B, C0, M, N, K, 1, 1, 2)
+    assert rel_l2(got, C0 + At.T @ B) < 1e-4
+    # forward form with a residual: C = A . W^T + R
+    M, N, K = 8192, 768, 768
+    A = _bf16_round(rng.standard_normal((M, K)).astype(np.float32) * 0.1)
+    W = _bf16_round(rng.standard_normal((N, K)).astype(np.float32) * 0.1)
+    R = rng.standard_normal((M, N)).astype(np.float32)
+    got = _gemm(ane.DTYPE_BF16, A, W, np.zeros((M, N), np.float32), M, N, K, 0, 0, 1, res=R)
+    assert rel_l2(got, A @ W.T + R) < 1e-4
+    # ragged rows and columns through the same residual path (TMA clips the residual pieces)
+    M, N, K = 8100, 760, 768
+    got = _gemm(ane.DTYPE_BF16, A[:M], W[:N], np.zeros((M, N), np.float32), M, N, K, 0, 0, 1, res=np.ascontiguousarray(R[:M, :N]))
+    assert rel_l2(got, A[:M] @ W[:N].T + R[:M, :N]) < 1e-4
 
 
 @pytest.mark.parametrize("dtype", [ane.DTYPE_BF16, ane.DTYPE_F32])
