@@ -191,14 +191,19 @@ class Engine:
     def vocab(self) -> int:
         return self.opts.vocab if self.opts.vocab > 0 else 32000
 
-    def eval_logits(self, tokens: np.ndarray, layout: int = 0) -> np.ndarray:  # ane/engine.go:449
+    def eval_logits(self, tokens: np.ndarray, layout: int = 0, out: np.ndarray | None = None) -> np.ndarray:
+        """ane/engine.go:449.  Returns a fresh array like the reference does; `out` lets a caller that
+        evaluates many windows reuse one (a fresh 32 MB array costs page faults on every call)."""
         self._alive("eval logits")
         tokens = np.ascontiguousarray(tokens, dtype=np.uint16)
         if tokens.size % self.seq != 0 or tokens.size == 0:
             raise EngineError(-1, f"storiesane eval logits: token len={tokens.size} want={self.seq}")
         n_seq = tokens.size // self.seq
         shape = (n_seq, self.vocab, self.seq) if layout == 0 else (n_seq * self.seq, self.vocab)
-        out = np.empty(shape, dtype=np.float32)
+        if out is None:
+            out = np.empty(shape, dtype=np.float32)
+        elif out.dtype != np.float32 or not out.flags.c_contiguous or out.size != int(np.prod(shape)):
+            raise EngineError(-1, "storiesane eval logits: out must be a C-contiguous float32 array of the result's size")
         self._check(lib.ane_eval_logits(self._h, _u16p(tokens), n_seq, out.ctypes.data_as(POINTER(c_float)), out.size,
                                         layout))
         return out
