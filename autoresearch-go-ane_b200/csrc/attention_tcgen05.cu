@@ -671,6 +671,374 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
 }
 
 constexpr size_t kFwdSmem5 = kTileR + 4 * kTileX + 2 * kTileR + 1024;
+
+// ------------------------------------------------------------------------------------------------
+// Split-precision backward for q|k|v kept in fp32 (the reference architecture).  The reference's
+// backward recomputes its probabilities from UNSCALED scores (ane/train_full.go:268-269), whose
+// magnitude (up to ~1.4 * head_dim) turns the bf16 rounding of q and k into percent-level errors of
+// P.  Here q and k arrive as two bf16 tensors each (hi = bf16(x), lo = bf16(x - hi)) and the score
+// product is issued as three accumulating MMAs, q_hi k_hi + q_hi k_lo + q_lo k_hi, which restores
+// ~16 mantissa bits; every other product (dO V^T, P^T dO, dS^T Q, dS K) is not amplified and uses
+// the hi parts alone.  Because the backward softmax has its own scale, its row statistics come from
+// a statistics pass (MODE A5_STATS: lse and delta = sum_j P dP, accumulated online), not from the
+// forward.  Gradients leave as bf16 without any rotation (the caller's QK-norm / rotation backward
+// follows in fp32).  One CTA per SM (112-128 KB of shared memory).
+// ------------------------------------------------------------------------------------------------
+enum : int { A5_STATS = 3 };
+
+struct Attn5SplitParams {
+  float* lse;      // [B, H, T] log-sum-exp of scale * scores (written by STATS, read by the others)
+  float* delta;    // [B, H, T] sum_j P dP                      (written by STATS, read by the others)
+  int T, H, KV;
+  float scale;
+  int* status;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(A5_THREADS, 1)
+attn5_bwd_split_kernel(const __grid_constant__ CUtensorMap tm_hi_r, const __grid_constant__ CUtensorMap tm_hi_x,
+                       const __grid_constant__ CUtensorMap tm_lo_r, const __grid_constant__ CUtensorMap tm_lo_x,
+                       const __grid_constant__ CUtensorMap tm_do_r, const __grid_constant__ CUtensorMap tm_do_x,
+                       const __grid_constant__ CUtensorMap tm_dqkv, Attn5SplitParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[2];
+  __shared__ __align__(8) uint64_t bar_empty[2];
+  __shared__ __align__(8) uint64_t bar_r, bar_s1, bar_s2, bar_p1, bar_p2, bar_acc;
+  __shared__ uint32_t tmem_slot;
+  __shared__ __align__(16) float ld_s[2][128];  // dK/dV: per streamed query [0,64) lse*log2e, [64,128) delta
+  __shared__ float xs[3][2][128];               // STATS: (m, l, acc) per column half and row
+
+  int* status = p.status;
+  if (status != nullptr && *reinterpret_cast<volatile int*>(status) != DEV_OK) return;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sR1h = smem_base, sR1l = sR1h + kTileR, sR2 = sR1l + kTileR;  // resident: hi, lo, second operand
+  const uint32_t sX = sR2 + kTileR;                                           // [2 stages][X1 hi | X1 lo | X2]
+  const uint32_t sDS = sX + 2 * 3 * kTileX;                                   // dS' operand tile
+  const uint32_t sP = sDS + kTileR;                                           // P' operand tile (dK/dV only)
+  uint8_t* pDS = smem_al + (sDS - smem_base);
+  uint8_t* pP = smem_al + (sP - smem_base);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int T = p.T, H = p.H, KV = p.KV, group = H / KV;
+  const int nT = T / 128;
+  int rt, b, h = 0, kvh, n_per = 1, n_it;
+  if constexpr (MODE == A5_DKV) {
+    rt = blockIdx.y;
+    b = blockIdx.x / KV;
+    kvh = blockIdx.x - b * KV;
+    n_per = T / 64 - 2 * rt;
+    n_it = group * n_per;
+  } else {
+    rt = nT - 1 - blockIdx.y;
+    b = blockIdx.x / H;
+    h = blockIdx.x - b * H;
+    kvh = h / group;
+    n_it = 2 * rt + 2;
+  }
+  const int row0 = b * T;
+
+  auto issue_x = [&](int it) {
+    const int s = it & 1;
+    const uint32_t full = smem_u32(&bar_full[s]);
+    const uint32_t x1h = sX + s * 3 * kTileX, x1l = x1h + kTileX, x2 = x1l + kTileX;
+    mbar_expect_tx(full, 3 * kTileX);
+    if constexpr (MODE == A5_DKV) {
+      const int g = it / n_per;
+      const int qh = 2 * rt + (it - g * n_per);
+      const int hq = kvh * group + g;
+      tma_load_2d(x1h, &tm_hi_x, full, hq * 64, row0 + qh * 64);
+      tma_load_2d(x1l, &tm_lo_x, full, hq * 64, row0 + qh * 64);
+      tma_load_2d(x2, &tm_do_x, full, hq * 64, row0 + qh * 64);
+    } else {
+      tma_load_2d(x1h, &tm_hi_x, full, (H + kvh) * 64, row0 + it * 64);
+      tma_load_2d(x1l, &tm_lo_x, full, (H + kvh) * 64, row0 + it * 64);
+      tma_load_2d(x2, &tm_hi_x, full, (H + KV + kvh) * 64, row0 + it * 64);
+    }
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&bar_r), 1);
+    mbar_init(smem_u32(&bar_s1), 1);
+    mbar_init(smem_u32(&bar_s2), 1);
+    mbar_init(smem_u32(&bar_p1), 8);
+    mbar_init(smem_u32(&bar_p2), 8);
+    mbar_init(smem_u32(&bar_acc), 1);
+    fence_mbar_init();
+    pdl_wait();
+    const uint32_t rbar = smem_u32(&bar_r);
+    mbar_expect_tx(rbar, 3 * kTileR);
+    if constexpr (MODE == A5_DKV) {
+      tma_load_2d(sR1h, &tm_hi_r, rbar, (H + kvh) * 64, row0 + rt * 128);
+      tma_load_2d(sR1l, &tm_lo_r, rbar, (H + kvh) * 64, row0 + rt * 128);
+      tma_load_2d(sR2, &tm_hi_r, rbar, (H + KV + kvh) * 64, row0 + rt * 128);
+    } else {
+      tma_load_2d(sR1h, &tm_hi_r, rbar, h * 64, row0 + rt * 128);
+      tma_load_2d(sR1l, &tm_lo_r, rbar, h * 64, row0 + rt * 128);
+      tma_load_2d(sR2, &tm_do_r, rbar, h * 64, row0 + rt * 128);
+    }
+    issue_x(0);
+    issue_x(1);  // n_it >= 2 always
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_slot), 256);
+    tmem_relinquish();
+  }
+  pdl_trigger();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  pdl_wait();
+  const uint32_t tmem_base = tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 64, tA1 = tmem_base + 128, tA2 = tmem_base + 192;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int it = 2; it < n_it; ++it) {
+        const int s = it & 1;
+        const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, status, DEV_MBAR_TIMEOUT_PRODUCER)) break;
+        issue_x(it);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_kk = a5_idesc(false, false);
+      constexpr uint32_t idesc_kn = a5_idesc(false, true);
+      bool ok = mbar_wait(smem_u32(&bar_r), 0, status, DEV_MBAR_TIMEOUT_MMA);
+      for (int it = 0; ok && it < n_it; ++it) {
+        const int s = it & 1;
+        const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&bar_full[s]), ph, status, DEV_MBAR_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t x1h = sX + s * 3 * kTileX, x1l = x1h + kTileX, x2 = x1l + kTileX;
+        // S' = R1 X1^T at split precision: hi hi + lo hi + hi lo
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_bf16(tS, make_smem_desc(sR1h + k * 32, 16, 1024), make_smem_desc(x1h + k * 32, 16, 1024), idesc_kk,
+                      k > 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_bf16(tS, make_smem_desc(sR1l + k * 32, 16, 1024), make_smem_desc(x1h + k * 32, 16, 1024), idesc_kk, 1u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_bf16(tS, make_smem_desc(sR1h + k * 32, 16, 1024), make_smem_desc(x1l + k * 32, 16, 1024), idesc_kk, 1u);
+        tc_commit(smem_u32(&bar_s1));
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_bf16(tDP, make_smem_desc(sR2 + k * 32, 16, 1024), make_smem_desc(x2 + k * 32, 16, 1024), idesc_kk,
+                      k > 0 ? 1u : 0u);
+        tc_commit(smem_u32(&bar_s2));
+        const uint32_t par = (uint32_t)it & 1u;
+        if constexpr (MODE == A5_DKV) {
+          if (!mbar_wait(smem_u32(&bar_p1), par, status, DEV_MBAR_TIMEOUT_MMA)) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // dV += P^T dO
+            tc_mma_bf16(tA1, make_smem_desc(sP + k * 32, 16, 1024), make_smem_desc(x2 + k * 2048, 8192, 1024),
+                        idesc_kn, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        if (!mbar_wait(smem_u32(&bar_p2), par, status, DEV_MBAR_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        if constexpr (MODE != A5_STATS) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // dK += dS^T Q_hi   |   dQ += dS K_hi
+            tc_mma_bf16(MODE == A5_DKV ? tA2 : tA1, make_smem_desc(sDS + k * 32, 16, 1024),
+                        make_smem_desc(x1h + k * 2048, 8192, 1024), idesc_kn, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&bar_empty[s]));
+        if (it == n_it - 1) tc_commit(smem_u32(&bar_acc));
+      }
+    }
+  } else {
+    const int lane_group = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int r = lane_group * 32 + lane;
+    const int ct = threadIdx.x - 64;
+    const uint32_t lane_off = ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(half * 32);
+    const float sl2 = p.scale * kLog2e;
+    const int rpos = rt * 128 + r;
+    float lse_r = 0.f, del_r = 0.f;
+    if constexpr (MODE == A5_DQ) {
+      lse_r = p.lse[((size_t)b * H + h) * T + rpos] * kLog2e;
+      del_r = p.delta[((size_t)b * H + h) * T + rpos];
+    }
+    float m_run = -INFINITY, l_run = 0.f, a_run = 0.f;  // STATS: online max / sum-exp / sum exp*dP (log2 domain)
+    bool ok = true;
+    for (int it = 0; ok && it < n_it; ++it) {
+      const int s = it & 1;
+      int xpos0;
+      if constexpr (MODE == A5_DKV) {
+        const int g = it / n_per;
+        const int qh = 2 * rt + (it - g * n_per);
+        const int hq = kvh * group + g;
+        xpos0 = qh * 64;
+        const size_t base = ((size_t)b * H + hq) * T + xpos0;
+        if (ct < 128) ld_s[s][ct] = (ct < 64) ? p.lse[base + ct] * kLog2e : p.delta[base + ct - 64];
+        named_bar_sync(1, A5_COMPUTE);
+      } else {
+        xpos0 = it * 64;
+      }
+      const uint32_t par = (uint32_t)it & 1u;
+      if (!mbar_wait(smem_u32(&bar_s1), par, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      float sv[32];
+      tmem_ld_32x32(tS + lane_off, sv);
+      tmem_ld_wait();
+      bool diag;
+      if constexpr (MODE == A5_DKV) diag = xpos0 < rt * 128 + 127;
+      else diag = xpos0 + 63 > rt * 128;
+      const int c0 = xpos0 + half * 32;
+      float m_new = m_run;
+      if constexpr (MODE == A5_DKV) {
+        const float4* l4 = reinterpret_cast<const float4*>(&ld_s[s][half * 32]);
+#pragma unroll
+        for (int e4 = 0; e4 < 8; ++e4) {
+          const float4 l = l4[e4];
+          const float lv[4] = {l.x, l.y, l.z, l.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int e = e4 * 4 + k;
+            float pr = fast_ex2(sv[e] * sl2 - lv[k]);
+            if (diag && rpos > c0 + e) pr = 0.f;
+            sv[e] = pr;
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) st_chunk(pP, r, half * 4 + q, sv + 8 * q);
+        tc_fence_before();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_p1));
+      } else if constexpr (MODE == A5_DQ) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float pr = fast_ex2(sv[e] * sl2 - lse_r);
+          if (diag && c0 + e > rpos) pr = 0.f;
+          sv[e] = pr;
+        }
+      } else {  // STATS: scaled scores in the log2 domain, running maximum
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          sv[e] = (diag && c0 + e > rpos) ? -INFINITY : sv[e] * sl2;
+          m_new = fmaxf(m_new, sv[e]);
+        }
+      }
+      if (!mbar_wait(smem_u32(&bar_s2), par, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      float dv[32];
+      tmem_ld_32x32(tDP + lane_off, dv);
+      tmem_ld_wait();
+      if constexpr (MODE == A5_STATS) {
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float corr = fast_ex2(m_run - m_use);
+        float ls = 0.f, as = 0.f;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const float pr = fast_ex2(sv[e] - m_use);
+          ls += pr;
+          as += pr * dv[e];
+        }
+        l_run = l_run * corr + ls;
+        a_run = a_run * corr + as;
+        m_run = m_new;
+      } else {
+        if constexpr (MODE == A5_DKV) {
+          const float4* d4 = reinterpret_cast<const float4*>(&ld_s[s][64 + half * 32]);
+#pragma unroll
+          for (int e4 = 0; e4 < 8; ++e4) {
+            const float4 d = d4[e4];
+            dv[e4 * 4 + 0] = sv[e4 * 4 + 0] * (dv[e4 * 4 + 0] - d.x);
+            dv[e4 * 4 + 1] = sv[e4 * 4 + 1] * (dv[e4 * 4 + 1] - d.y);
+            dv[e4 * 4 + 2] = sv[e4 * 4 + 2] * (dv[e4 * 4 + 2] - d.z);
+            dv[e4 * 4 + 3] = sv[e4 * 4 + 3] * (dv[e4 * 4 + 3] - d.w);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) dv[e] = sv[e] * (dv[e] - del_r);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) st_chunk(pDS, r, half * 4 + q, dv + 8 * q);
+        fence_proxy_async_smem();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_p2));
+    }
+    ok = ok && mbar_wait(smem_u32(&bar_acc), 0, status, DEV_MBAR_TIMEOUT_EPILOGUE);
+    if constexpr (MODE == A5_STATS) {
+      // merge the two column halves of every row: (m, l, acc) -> lse (natural log), delta = acc / l
+      xs[0][half][r] = m_run;
+      xs[1][half][r] = l_run;
+      xs[2][half][r] = a_run;
+      named_bar_sync(1, A5_COMPUTE);
+      if (ok && half == 0) {
+        const float m2 = xs[0][1][r], l2 = xs[1][1][r], a2 = xs[2][1][r];
+        const float m = fmaxf(m_run, m2);  // finite: key 0 is visible to every query
+        const float c1 = fast_ex2(m_run - m), c2 = fast_ex2(m2 - m);
+        const float l = l_run * c1 + l2 * c2;
+        const float a = a_run * c1 + a2 * c2;
+        const size_t o = ((size_t)b * H + h) * T + rpos;
+        p.lse[o] = (m + log2f(l)) / kLog2e;
+        p.delta[o] = a / l;
+      }
+    } else {
+      if (ok) {
+        tc_fence_after();
+        float a[32];
+        tmem_ld_32x32(tA1 + lane_off, a);
+        tmem_ld_wait();
+        if constexpr (MODE == A5_DQ) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) a[e] *= p.scale;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) st_chunk(MODE == A5_DKV ? pP : pDS, r, half * 4 + q, a + 8 * q);  // dV | dQ
+        if constexpr (MODE == A5_DKV) {
+          tmem_ld_32x32(tA2 + lane_off, a);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) a[e] *= p.scale;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) st_chunk(pDS, r, half * 4 + q, a + 8 * q);  // dK
+        }
+        fence_proxy_async_smem();
+      }
+      named_bar_sync(1, A5_COMPUTE);
+      if (ok && ct == 0) {
+        if constexpr (MODE == A5_DKV) {
+          tma_store_2d(&tm_dqkv, sP, (H + KV + kvh) * 64, row0 + rt * 128);
+          tma_store_2d(&tm_dqkv, sDS, (H + kvh) * 64, row0 + rt * 128);
+        } else {
+          tma_store_2d(&tm_dqkv, sDS, h * 64, row0 + rt * 128);
+        }
+        tma_store_commit();
+        tma_store_wait_read<0>();
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+constexpr size_t kSplitSmem = 3 * kTileR + 6 * kTileX + 2 * kTileR + 1024;
+
 constexpr size_t kDkvSmem5 = 2 * kTileR + 4 * kTileX + 2 * kTileR + 1024;
 constexpr size_t kDqSmem5 = 2 * kTileR + 4 * kTileX + 1 * kTileR + 1024;
 
@@ -681,7 +1049,13 @@ bool ensure_attrs5() {
           cudaSuccess ||
       cudaFuncSetAttribute(attn5_bwd_kernel<A5_DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDqSmem5) !=
           cudaSuccess ||
-      cudaFuncSetAttribute(attn5_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwdSmem5) != cudaSuccess)
+      cudaFuncSetAttribute(attn5_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwdSmem5) != cudaSuccess ||
+      cudaFuncSetAttribute(attn5_bwd_split_kernel<A5_STATS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)kSplitSmem) != cudaSuccess ||
+      cudaFuncSetAttribute(attn5_bwd_split_kernel<A5_DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSplitSmem) !=
+          cudaSuccess ||
+      cudaFuncSetAttribute(attn5_bwd_split_kernel<A5_DKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSplitSmem) !=
+          cudaSuccess)
     return false;
   g_attr5_done = true;
   return true;
@@ -740,6 +1114,32 @@ int attention_backward_tcgen05(const bf16* qkv, const bf16* out, const bf16* d_o
                  tm_dqkv, tm_cos, tm_sin, p) != cudaSuccess)
     return -4;
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+int attention_backward_tcgen05_split(const bf16* qkv_hi, const bf16* qkv_lo, const bf16* d_out, float* lse, float* delta,
+                                     bf16* dqkv, int B, int seq, int H, int KV, float scale, int* d_status,
+                                     cudaStream_t s) {
+  if (B <= 0) return 0;
+  if (!attention_tcgen05_supported(64, seq) || H % KV != 0 || !ensure_attrs5()) return -1;
+  const uint64_t M = (uint64_t)B * seq;
+  const uint64_t ld = (uint64_t)(H + 2 * KV) * 64;
+  CUtensorMap hi_r, hi_x, lo_r, lo_x, do_r, do_x, out_r;
+  if (!make_tmap_2d(&hi_r, qkv_hi, ld, M, ld, 64, 128, false) || !make_tmap_2d(&hi_x, qkv_hi, ld, M, ld, 64, 64, false) ||
+      !make_tmap_2d(&lo_r, qkv_lo, ld, M, ld, 64, 128, false) || !make_tmap_2d(&lo_x, qkv_lo, ld, M, ld, 64, 64, false) ||
+      !make_tmap_2d(&do_r, d_out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 128, false) ||
+      !make_tmap_2d(&do_x, d_out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 64, false) ||
+      !make_tmap_2d(&out_r, dqkv, ld, M, ld, 64, 128, false))
+    return -2;
+  Attn5SplitParams p{lse, delta, seq, H, KV, scale, d_status};
+  dim3 gq(B * H, seq / 128), gk(B * KV, seq / 128);
+  if (launch_pdl(attn5_bwd_split_kernel<A5_STATS>, gq, dim3(A5_THREADS), kSplitSmem, s, hi_r, hi_x, lo_r, lo_x, do_r, do_x,
+                 out_r, p) != cudaSuccess ||
+      launch_pdl(attn5_bwd_split_kernel<A5_DQ>, gq, dim3(A5_THREADS), kSplitSmem, s, hi_r, hi_x, lo_r, lo_x, do_r, do_x,
+                 out_r, p) != cudaSuccess ||
+      launch_pdl(attn5_bwd_split_kernel<A5_DKV>, gk, dim3(A5_THREADS), kSplitSmem, s, hi_r, hi_x, lo_r, lo_x, do_r, do_x,
+                 out_r, p) != cudaSuccess)
+    return -4;
+  return 0;
 }
 
 }  // namespace ane

@@ -30,6 +30,29 @@ static inline int grid_for(uint64_t n, int block) {
   return (int)g;
 }
 
+// hi = bf16(x), lo = bf16(x - hi): two bf16 tensors that together carry ~16 mantissa bits of x.
+__global__ void split_f32_to_bf16x2_kernel(const float* __restrict__ src, bf16* __restrict__ hi, bf16* __restrict__ lo,
+                                           uint64_t n4) {
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (; i < n4; i += stride) {
+    const float4 v = reinterpret_cast<const float4*>(src)[i];
+    const float x[4] = {v.x, v.y, v.z, v.w};
+    bf16 h[4], l[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      h[k] = __float2bfloat16_rn(x[k]);
+      l[k] = __float2bfloat16_rn(x[k] - __bfloat162float(h[k]));
+    }
+    reinterpret_cast<uint2*>(hi)[i] = *reinterpret_cast<const uint2*>(h);
+    reinterpret_cast<uint2*>(lo)[i] = *reinterpret_cast<const uint2*>(l);
+  }
+}
+void split_f32_to_bf16x2(const float* src, bf16* hi, bf16* lo, uint64_t n, cudaStream_t s) {
+  if (!n) return;  // n must be a multiple of 4
+  split_f32_to_bf16x2_kernel<<<grid_for(n / 4, 256), 256, 0, s>>>(src, hi, lo, n / 4);
+}
+
 void cast_f32_to_bf16(const float* src, bf16* dst, uint64_t n, cudaStream_t s) {
   if (!n) return;
   cast_f32_to_bf16_kernel<<<grid_for(n, 256), 256, 0, s>>>(src, dst, n);

@@ -239,6 +239,11 @@ class EngineT final : public EngineBase {
   uint16_t *d_dec_tok_ = nullptr, *d_dec_out_ = nullptr;
   float* h_logits_ = nullptr;  // pinned staging for EvalLogits downloads
   float* att_delta_ = nullptr;
+  // fp32 q|k|v (reference arch) on the tcgen05 attention kernels: bf16 hi / lo copies, the backward's own
+  // log-sum-exp, raw bf16 gradients
+  bool att_split_ = false;
+  bf16 *qkvh_ = nullptr, *qkvl_ = nullptr, *dqkv_raw_ = nullptr;
+  float* att_lse_b_ = nullptr;
   float lr_ = 0, embed_lr_ = 0, scalar_lr_ = 0, lambda_lr_ = 0;
   int ce_rows_ = 0;
   // ---- parameters
@@ -492,6 +497,10 @@ int EngineT<T>::alloc_buffers() {
   }
   A(dgate_, (size_t)M_ * Hd_); A(dh13_[0], (size_t)M_ * N13_); A(dh13_[1], (size_t)M_ * N13_); A(datt_, (size_t)M_ * QD_);
   A(xnf_, MD); A(rstdf_, M_); A(att_delta_, (size_t)B_ * H_ * S_);
+  if (att_split_) {
+    A(qkvh_, (size_t)M_ * QKVD_); A(qkvl_, (size_t)M_ * QKVD_); A(dqkv_raw_, (size_t)M_ * QKVD_);
+    A(att_lse_b_, (size_t)B_ * H_ * S_);
+  }
   A(logits_, (size_t)ce_rows_ * V_); A(dlogits_, (size_t)ce_rows_ * V_); A(dlogits2_, (size_t)ce_rows_ * V_);
   A(loss_rows_, M_); A(inv_valid_, B_); A(d_loss_, 4); A(tgt_logit_, M_);
   A(rope_cos_, (size_t)S_ * (hd_ / 2)); A(rope_sin_, (size_t)S_ * (hd_ / 2));
@@ -552,6 +561,7 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
   QD_ = H_ * hd_; KVD_ = KV_ * hd_; QKVD_ = QD_ + 2 * KVD_;
   N13_ = isN_ ? Hd_ : 2 * Hd_;
   att_tc_ = !qkv_f32_ && attention_tc_supported(hd_);
+  att_split_ = !kIsF32 && qkv_f32_ && attention_tcgen05_supported(hd_, S_) && getenv("ANE_B200_ATT_SIMT") == nullptr;
   ce_rows_ = o_.ce_chunk_rows > 0 ? o_.ce_chunk_rows : 8192;  // 8192 x 32000 bf16 logits = 524 MB per chunk
   if (ce_rows_ > M_) ce_rows_ = M_;
   ce_rows_ = std::max(ce_rows_, std::min(M_, S_));  // eval logits uses one sequence per chunk
@@ -720,7 +730,16 @@ int EngineT<T>::forward(const uint16_t* d_tok, int B, int Tl, int pos0) {
       attention_decode_simt<T>((const T*)a.qkv, kcache_[l], vcache_[l], a.att, B, S_, pos0, H_, KV_, hd_, att_scale,
                                stream_);
     } else if (qkv_f32_) {
-      attention_forward_simt<float, T>((const float*)a.qkv, a.att, a.lse, B, Tl, H_, KV_, hd_, att_scale, stream_);
+      bool done = false;
+      if constexpr (!kIsF32) {
+        if (att_split_ && Tl == S_) {  // scaled scores are not amplified: the bf16 hi part suffices in the forward
+          count_launch();
+          cast_f32_to_bf16((const float*)a.qkv, qkvh_, (uint64_t)M * QKVD_, stream_);
+          done = attention_forward_tcgen05(qkvh_, a.att, a.lse, B, Tl, H_, KV_, att_scale, d_status_, stream_) == 0;
+        }
+      }
+      if (!done)
+        attention_forward_simt<float, T>((const float*)a.qkv, a.att, a.lse, B, Tl, H_, KV_, hd_, att_scale, stream_);
     } else if constexpr (!kIsF32) {
       if (att_tc_)
         attention_forward_tc((const bf16*)a.qkv, a.att, a.lse, B, Tl, H_, KV_, att_scale, d_status_, stream_);
@@ -949,9 +968,22 @@ int EngineT<T>::backward_layers(int B) {
     T* dqkv = tview(dqkv_f32, dqkv_[pb]);
     bool dqkv_ready = false;  // true once dqkv holds the final GEMM operand
     if (qkv_f32_) {
-      cudaMemsetAsync(dqkv_f32, 0, sizeof(float) * (size_t)M * QKVD_, stream_);
-      count_launch();
-      attention_backward_simt<float, T>((const float*)a.qkv, datt_, dqkv_f32, B, S_, H_, KV_, hd_, att_scale_bwd, stream_);
+      bool done = false;
+      if constexpr (!kIsF32) {
+        if (att_split_) {
+          count_launch(5);
+          split_f32_to_bf16x2((const float*)a.qkv, qkvh_, qkvl_, (uint64_t)M * QKVD_, stream_);
+          done = attention_backward_tcgen05_split(qkvh_, qkvl_, datt_, att_lse_b_, att_delta_, dqkv_raw_, B, S_, H_, KV_,
+                                                  att_scale_bwd, d_status_, stream_) == 0;
+          if (done)
+            to_f32_kernel<bf16><<<ew_grid((uint64_t)M * QKVD_), 256, 0, stream_>>>(dqkv_raw_, dqkv_f32, (uint64_t)M * QKVD_);
+        }
+      }
+      if (!done) {
+        cudaMemsetAsync(dqkv_f32, 0, sizeof(float) * (size_t)M * QKVD_, stream_);
+        count_launch();
+        attention_backward_simt<float, T>((const float*)a.qkv, datt_, dqkv_f32, B, S_, H_, KV_, hd_, att_scale_bwd, stream_);
+      }
     } else if constexpr (!kIsF32) {
       if (att_tc_) {
         // Tensor-core path: the kernels undo the rotation and emit bf16 operands directly.

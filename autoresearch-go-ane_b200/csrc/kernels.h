@@ -16,6 +16,8 @@ namespace ane {
 typedef __nv_bfloat16 bf16;
 
 void cast_f32_to_bf16(const float* src, bf16* dst, uint64_t n, cudaStream_t s);
+// hi = bf16(x), lo = bf16(x - hi); n % 4 == 0, 16-byte aligned pointers.
+void split_f32_to_bf16x2(const float* src, bf16* hi, bf16* lo, uint64_t n, cudaStream_t s);
 void cast_bf16_to_f32(const bf16* src, float* dst, uint64_t n, cudaStream_t s);
 
 // x[m,:] = embed[tok[m],:] (zeros for ids >= vocab), ane/stories/cpu.go:41-72.
@@ -100,6 +102,11 @@ void attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* d_out, 
                            bf16* dqkv, const float* cosb, const float* sinb, int B, int seq, int H, int KV,
                            float scale, int* d_status, cudaStream_t s);
 bool attention_tcgen05_supported(int hd, int seq);
+// Backward for q|k|v kept in fp32 and given as bf16 (hi, lo) pairs: scores at split precision, own row
+// statistics for the backward's `scale` (lse, delta: scratch [B*H*seq]), dq|dk|dv out as bf16, no rotation.
+int attention_backward_tcgen05_split(const bf16* qkv_hi, const bf16* qkv_lo, const bf16* d_out, float* lse, float* delta,
+                                     bf16* dqkv, int B, int seq, int H, int KV, float scale, int* d_status,
+                                     cudaStream_t s);
 // `delta` is scratch [B*H*seq] (rowsum(dO * O), produced by the dQ kernel).  Returns 0 or a negative error code.
 int attention_backward_tcgen05(const bf16* qkv, const bf16* out, const bf16* d_out, const float* lse, float* delta,
                                bf16* dqkv,
