@@ -455,12 +455,29 @@ void smear_backward(const float* d_out, const float* x_pre, const float* gate_pr
 // ------------------------------------------------------------------------------------------
 // Small reductions / vector ops
 // ------------------------------------------------------------------------------------------
-__global__ void dot_accumulate_kernel(const float* __restrict__ a, const float* __restrict__ b, uint64_t n,
-                                      float alpha, float* __restrict__ out) {
-  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+__global__ void __launch_bounds__(256)
+dot_accumulate_kernel(const float* __restrict__ a, const float* __restrict__ b, uint64_t n, float alpha,
+                      float* __restrict__ out) {
+  const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
   double local = 0.0;
-  for (; i < n; i += stride) local += (double)(a[i] * b[i]);
+  // 16-byte loads, two per operand in flight, when both buffers are aligned; products are rounded to fp32
+  // before the double sum, as in the reference's loops (ane/train_full.go:733-782)
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0;
+  const uint64_t n4 = vec_ok ? n / 4 : 0;
+  const float4* a4 = reinterpret_cast<const float4*>(a);
+  const float4* b4 = reinterpret_cast<const float4*>(b);
+  uint64_t i = tid;
+  for (; i + stride < n4; i += 2 * stride) {
+    const float4 x0 = a4[i], y0 = b4[i], x1 = a4[i + stride], y1 = b4[i + stride];
+    local += (double)(x0.x * y0.x) + (double)(x0.y * y0.y) + (double)(x0.z * y0.z) + (double)(x0.w * y0.w);
+    local += (double)(x1.x * y1.x) + (double)(x1.y * y1.y) + (double)(x1.z * y1.z) + (double)(x1.w * y1.w);
+  }
+  for (; i < n4; i += stride) {
+    const float4 x0 = a4[i], y0 = b4[i];
+    local += (double)(x0.x * y0.x) + (double)(x0.y * y0.y) + (double)(x0.z * y0.z) + (double)(x0.w * y0.w);
+  }
+  for (uint64_t j = n4 * 4 + tid; j < n; j += stride) local += (double)(a[j] * b[j]);
   local = warp_sum_d(local);
   __shared__ double s_part[8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -474,8 +491,8 @@ __global__ void dot_accumulate_kernel(const float* __restrict__ a, const float* 
 }
 void dot_accumulate(const float* a, const float* b, uint64_t n, float alpha, float* out, cudaStream_t s) {
   if (!n) return;
-  int grid = grid_for(n, 256);
-  if (grid > 296) grid = 296;
+  int grid = grid_for((n + 3) / 4, 256);
+  if (grid > 148 * 8) grid = 148 * 8;
   dot_accumulate_kernel<<<grid, 256, 0, s>>>(a, b, n, alpha, out);
 }
 
