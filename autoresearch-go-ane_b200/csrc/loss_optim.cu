@@ -15,6 +15,9 @@ static constexpr int kCEThreads = 512;
 static constexpr int kCEResidencySmem = 64 * 1024;
 
 __device__ __forceinline__ float softcap_f(float x) { return 15.0f * tanhf(x * (1.0f / 15.0f)); }
+// tanh through one exp and one fast division (absolute error ~1e-7): for the bf16-logits kernel, whose
+// inputs are already rounded to 3 decimal digits.
+__device__ __forceinline__ float fast_tanh(float y) { return 1.0f - __fdividef(2.0f, __expf(2.0f * y) + 1.0f); }
 
 template <typename TO>
 __global__ void __launch_bounds__(kCEThreads)
@@ -150,8 +153,8 @@ cross_entropy_rows_bf16_kernel(const bf16* __restrict__ logits, const uint16_t* 
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const float2 f = __bfloat1622float2(h[k]);
-      z[2 * k] = softcap ? softcap_f(f.x) : f.x;
-      z[2 * k + 1] = softcap ? softcap_f(f.y) : f.y;
+      z[2 * k] = softcap ? 15.0f * fast_tanh(f.x * (1.0f / 15.0f)) : f.x;
+      z[2 * k + 1] = softcap ? 15.0f * fast_tanh(f.y * (1.0f / 15.0f)) : f.y;
     }
     float zm = z[0];
 #pragma unroll
@@ -206,7 +209,7 @@ cross_entropy_rows_bf16_kernel(const bf16* __restrict__ logits, const uint16_t* 
       const float raw = (k & 1) ? f.y : f.x;
       float z = raw, dcap = 1.f;
       if (softcap) {
-        const float th = tanhf(raw * (1.0f / 15.0f));
+        const float th = fast_tanh(raw * (1.0f / 15.0f));
         z = 15.0f * th;
         dcap = 1.f - th * th;
       }
