@@ -1061,9 +1061,15 @@ int EngineT<T>::backward_layers(int B) {
     }
     if (post_fix) cast_to_t(dprev, dcur_t_[cur ^ 1], MD);
     (void)dprev_t;
-    if (overlap_reduce_) {
-      // Layer l's matrix gradients are final: hand them to the all-reduce on the communication stream
-      // while the layers below are still being differentiated.
+    // ANE_B200_DP_LAYERS_PER_BUCKET groups that many layers into one all-reduce (default 1).
+    static const int layers_per_bucket = [] {
+      const char* e = getenv("ANE_B200_DP_LAYERS_PER_BUCKET");
+      const int v = e ? atoi(e) : 1;
+      return v > 0 ? v : 1;
+    }();
+    if (overlap_reduce_ && l % layers_per_bucket == 0) {
+      // The matrix gradients of layers l.. are final: hand them to the all-reduce on the communication
+      // stream while the layers below are still being differentiated.
       const size_t lo = s_qkv_[l].off, hi = reduced_lo_;
       cudaEventRecord(ev_bucket_, stream_);
       cudaStreamWaitEvent(comm_stream_, ev_bucket_, 0);
