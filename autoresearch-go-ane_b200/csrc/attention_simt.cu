@@ -239,36 +239,59 @@ template void kv_cache_append<float>(const float*, float*, float*, int, int, int
 template void kv_cache_append<bf16>(const bf16*, bf16*, bf16*, int, int, int, int, int, int, cudaStream_t);
 
 // One warp per (sequence, head): the single query row attends to cache positions 0..pos.
+// One block per (sequence, query head); its warps split the cached positions (warp w takes the 32-key
+// chunks w, w + kDecWarps, ...), each keeps a running (max, sum, P*V) and the block merges them at the end.
+// Key rows are read with 16-byte loads, value rows as one coalesced 128-byte row per key.
+static constexpr int kDecWarps = 8;
+
 template <typename T>
-__global__ void attention_decode_simt_kernel(const T* __restrict__ qkv, const T* __restrict__ kcache,
-                                             const T* __restrict__ vcache, T* __restrict__ out, int B, int max_seq,
-                                             int pos, int H, int KV, int hd, float scale) {
-  extern __shared__ float s_q[];
+__device__ __forceinline__ float dot_row(const float* q, const T* kp, int hd) {
+  float dot = 0.f;
+  if constexpr (sizeof(T) == 2) {
+    for (int d = 0; d < hd; d += 8) {  // hd % 8 == 0 (checked when the engine opens)
+      const uint4 u = *reinterpret_cast<const uint4*>(kp + d);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h2[e]);
+        dot += q[d + 2 * e] * f.x + q[d + 2 * e + 1] * f.y;
+      }
+    }
+  } else {
+    for (int d = 0; d < hd; d += 4) {
+      const float4 f = *reinterpret_cast<const float4*>(kp + d);
+      dot += q[d] * f.x + q[d + 1] * f.y + q[d + 2] * f.z + q[d + 3] * f.w;
+    }
+  }
+  return dot;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kDecWarps * 32)
+attention_decode_simt_kernel(const T* __restrict__ qkv, const T* __restrict__ kcache, const T* __restrict__ vcache,
+                             T* __restrict__ out, int B, int max_seq, int pos, int H, int KV, int hd, float scale) {
+  extern __shared__ float s_dec[];  // q[hd] | per warp: m, l | per warp: acc[hd]
+  float* q = s_dec;
+  float* s_m = q + hd;
+  float* s_l = s_m + kDecWarps;
+  float* s_acc = s_l + kDecWarps;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int wid = blockIdx.x * kAttWarps + warp;
-  if (wid >= B * H) return;
-  const int b = wid / H, h = wid - b * H;
+  const int b = blockIdx.x / H, h = blockIdx.x - b * H;
   const int kvh = h / (H / KV);
   const int kvd = KV * hd;
   const int ld = (H + 2 * KV) * hd;
-  float* q = s_q + warp * hd;
   const T* qp = qkv + (size_t)b * ld + (size_t)h * hd;
-  for (int d = lane; d < hd; d += 32) q[d] = to_f<T>(qp[d]);
-  __syncwarp();
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) q[d] = to_f<T>(qp[d]);
+  __syncthreads();
   const T* kbase = kcache + (size_t)b * max_seq * kvd + (size_t)kvh * hd;
   const T* vbase = vcache + (size_t)b * max_seq * kvd + (size_t)kvh * hd;
   float m_run = -INFINITY, l_run = 0.f;
   float acc[kMaxHdPerLane] = {0.f, 0.f, 0.f, 0.f};
-  for (int j0 = 0; j0 <= pos; j0 += 32) {
+  for (int j0 = warp * 32; j0 <= pos; j0 += kDecWarps * 32) {
     const int j = j0 + lane;
     float sc = -INFINITY;
-    if (j <= pos) {
-      const T* kp = kbase + (size_t)j * kvd;
-      float dot = 0.f;
-      for (int d = 0; d < hd; ++d) dot += q[d] * to_f<T>(kp[d]);
-      sc = dot * scale;
-    }
-    const float m_new = fmaxf(m_run, warp_max(sc));
+    if (j <= pos) sc = dot_row<T>(q, kbase + (size_t)j * kvd, hd) * scale;
+    const float m_new = fmaxf(m_run, warp_max(sc));  // finite: this chunk has at least key j0
     const float corr = __expf(m_run - m_new);
     const float p = (j <= pos) ? __expf(sc - m_new) : 0.f;
     l_run = l_run * corr + warp_sum(p);
@@ -286,21 +309,137 @@ __global__ void attention_decode_simt_kernel(const T* __restrict__ qkv, const T*
     }
     m_run = m_new;
   }
-  const float inv = 1.0f / l_run;
-  T* op = out + (size_t)b * (H * hd) + (size_t)h * hd;
+  if (lane == 0) {
+    s_m[warp] = m_run;
+    s_l[warp] = l_run;
+  }
 #pragma unroll
   for (int c = 0; c < kMaxHdPerLane; ++c) {
     const int d = lane + 32 * c;
-    if (d < hd) op[d] = from_f<T>(acc[c] * inv);
+    if (d < hd) s_acc[warp * hd + d] = acc[c];
+  }
+  __syncthreads();
+  // merge: warps without any key have m = -inf, l = 0 and drop out
+  float m = -INFINITY;
+  for (int w = 0; w < kDecWarps; ++w) m = fmaxf(m, s_m[w]);
+  float l = 0.f;
+  for (int w = 0; w < kDecWarps; ++w) l += s_l[w] * __expf(s_m[w] - m);
+  T* op = out + (size_t)b * (H * hd) + (size_t)h * hd;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float o = 0.f;
+    for (int w = 0; w < kDecWarps; ++w) o += s_acc[w * hd + d] * __expf(s_m[w] - m);
+    op[d] = from_f<T>(o / l);
   }
 }
+// head_dim 64, bf16 cache: every lane owns whole keys for BOTH products (its key's score, then p * its value
+// row into a private 64-wide accumulator), so a chunk of 32 keys costs sixteen 16-byte loads per lane and
+// no shuffles; the lanes' accumulators are summed once at the end.  The query heads that share a KV head
+// are handled by separate blocks (their K/V rows then come from L2).
+__global__ void __launch_bounds__(kDecWarps * 32, 2)
+attention_decode_hd64_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                             bf16* __restrict__ out, int B, int max_seq, int pos, int H, int KV, float scale) {
+  constexpr int hd = 64;
+  __shared__ float q[hd];
+  __shared__ float s_m[kDecWarps], s_l[kDecWarps];
+  __shared__ float s_acc[kDecWarps][hd];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.x / H, h = blockIdx.x - b * H;
+  const int kvh = h / (H / KV);
+  const int kvd = KV * hd;
+  const int ld = (H + 2 * KV) * hd;
+  if (threadIdx.x < hd) q[threadIdx.x] = __bfloat162float(qkv[(size_t)b * ld + (size_t)h * hd + threadIdx.x]);
+  __syncthreads();
+  const bf16* kbase = kcache + (size_t)b * max_seq * kvd + (size_t)kvh * hd;
+  const bf16* vbase = vcache + (size_t)b * max_seq * kvd + (size_t)kvh * hd;
+  float m_run = -INFINITY, l_lane = 0.f;
+  float acc[hd];
+#pragma unroll
+  for (int d = 0; d < hd; ++d) acc[d] = 0.f;
+  for (int j0 = warp * 32; j0 <= pos; j0 += kDecWarps * 32) {
+    const int j = j0 + lane;
+    const bool valid = j <= pos;
+    float sc = -INFINITY;
+    if (valid) {
+      uint4 kr[8];
+      const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)j * kvd);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) kr[c] = kp[c];
+      float dot = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&kr[c]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h2[e]);
+          dot += q[8 * c + 2 * e] * f.x + q[8 * c + 2 * e + 1] * f.y;
+        }
+      }
+      sc = dot * scale;
+    }
+    const float m_new = fmaxf(m_run, warp_max(sc));  // finite: this chunk has at least key j0
+    const float corr = __expf(m_run - m_new);
+    const float p = valid ? __expf(sc - m_new) : 0.f;
+    l_lane = l_lane * corr + p;
+    if (valid) {
+      uint4 vr[8];
+      const uint4* vp = reinterpret_cast<const uint4*>(vbase + (size_t)j * kvd);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) vr[c] = vp[c];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&vr[c]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h2[e]);
+          acc[8 * c + 2 * e] = acc[8 * c + 2 * e] * corr + p * f.x;
+          acc[8 * c + 2 * e + 1] = acc[8 * c + 2 * e + 1] * corr + p * f.y;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int d = 0; d < hd; ++d) acc[d] *= corr;
+    }
+    m_run = m_new;
+  }
+  // sum the lanes' partial results (they share m_run), then merge the warps
+  const float l_warp = warp_sum(l_lane);
+#pragma unroll
+  for (int d = 0; d < hd; ++d) {
+    const float t = warp_sum(acc[d]);
+    if (lane == (d & 31)) s_acc[warp][d] = t;
+  }
+  if (lane == 0) {
+    s_m[warp] = m_run;
+    s_l[warp] = l_warp;
+  }
+  __syncthreads();
+  if (threadIdx.x < hd) {
+    float m = -INFINITY;
+    for (int w = 0; w < kDecWarps; ++w) m = fmaxf(m, s_m[w]);
+    float l = 0.f, o = 0.f;
+    for (int w = 0; w < kDecWarps; ++w) {
+      const float f = __expf(s_m[w] - m);  // warps without any key: exp(-inf) = 0
+      l += s_l[w] * f;
+      o += s_acc[w][threadIdx.x] * f;
+    }
+    out[(size_t)b * (H * hd) + (size_t)h * hd + threadIdx.x] = __float2bfloat16_rn(o / l);
+  }
+}
+
 template <typename T>
 void attention_decode_simt(const T* qkv, const T* kcache, const T* vcache, T* out, int B, int max_seq, int pos, int H,
                            int KV, int hd, float scale, cudaStream_t s) {
   const int total = B * H;
   if (total <= 0) return;
-  attention_decode_simt_kernel<T><<<(total + kAttWarps - 1) / kAttWarps, kAttWarps * 32, kAttWarps * hd * sizeof(float), s>>>(
-      qkv, kcache, vcache, out, B, max_seq, pos, H, KV, hd, scale);
+  if constexpr (sizeof(T) == 2) {
+    if (hd == 64) {
+      attention_decode_hd64_kernel<<<total, kDecWarps * 32, 0, s>>>(qkv, kcache, vcache, out, B, max_seq, pos, H, KV, scale);
+      return;
+    }
+  }
+  const size_t smem = sizeof(float) * (size_t)(hd + 2 * kDecWarps + kDecWarps * hd);
+  attention_decode_simt_kernel<T><<<total, kDecWarps * 32, smem, s>>>(qkv, kcache, vcache, out, B, max_seq, pos, H, KV, hd,
+                                                                       scale);
 }
 template void attention_decode_simt<float>(const float*, const float*, const float*, float*, int, int, int, int, int,
                                            int, float, cudaStream_t);
