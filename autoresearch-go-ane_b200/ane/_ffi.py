@@ -81,6 +81,7 @@ SIGNATURES = {
     "ane_op_cast_f32_to_bf16": (c_int32, [c_void_p, c_void_p, c_uint64]),
     "ane_op_cast_bf16_to_f32": (c_int32, [c_void_p, c_void_p, c_uint64]),
     "ane_op_gemm": (c_int32, [POINTER(GemmArgs)]),
+    "ane_op_sample_rows": (c_int32, [c_void_p, c_void_p, c_float, c_void_p, c_int32, c_int32]),
     "ane_op_sumsq": (c_int32, [c_void_p, c_uint64, c_float, c_void_p]),
     "ane_op_sumsq_noalloc": (c_int32, [c_void_p, c_uint64, c_float, c_void_p]),
     "ane_op_sumsq_noalloc_last_error": (c_char_p, []),
@@ -97,6 +98,8 @@ SIGNATURES = {
     "ane_eval_logits": (c_int32, [c_void_p, POINTER(c_uint16), c_uint32, POINTER(c_float), c_uint64, c_uint32]),
     "ane_eval_loss": (c_int32, [c_void_p, POINTER(c_uint16), c_uint32, POINTER(c_double), POINTER(c_uint64)]),
     "ane_decode_greedy": (c_int32, [c_void_p, POINTER(c_uint16), c_uint32, c_uint32, c_uint32, POINTER(c_uint16)]),
+    "ane_decode_sample": (c_int32, [c_void_p, POINTER(c_uint16), c_uint32, c_uint32, c_uint32, c_float, POINTER(c_double),
+                                    POINTER(c_uint16)]),
     "ane_set_lr": (c_int32, [c_void_p, c_float]),
     "ane_get_lr": (c_float, [c_void_p]),
     "ane_get_state": (c_int32, [c_void_p, POINTER(State)]),

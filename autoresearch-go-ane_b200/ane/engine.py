@@ -225,6 +225,20 @@ class Engine:
         self._check(lib.ane_decode_greedy(self._h, _u16p(prompts), n_seq, plen, n_new, _u16p(out)))
         return out
 
+    def decode_sample(self, prompts: np.ndarray, n_new: int, temperature: float, uniforms: np.ndarray) -> np.ndarray:
+        """decode_greedy with the reference's temperature sampler (ane/train_full.go:318-342); `uniforms`
+        [n_new, n_seq] holds the caller's draws in [0, 1), one per generated token."""
+        self._alive("decode")
+        prompts = np.ascontiguousarray(prompts, dtype=np.uint16)
+        n_seq, plen = prompts.shape
+        uniforms = np.ascontiguousarray(uniforms, dtype=np.float64)
+        if uniforms.shape != (n_new, n_seq):
+            raise EngineError(-1, f"storiesane decode: uniforms shape={uniforms.shape} want={(n_new, n_seq)}")
+        out = np.empty((n_seq, n_new), dtype=np.uint16)
+        self._check(lib.ane_decode_sample(self._h, _u16p(prompts), n_seq, plen, n_new, temperature,
+                                          uniforms.ctypes.data_as(POINTER(c_double)), _u16p(out)))
+        return out
+
     def lr(self) -> float:  # ane/engine.go:358
         return float(lib.ane_get_lr(self._h)) if self._h else 0.0
 

@@ -651,4 +651,72 @@ void argmax_rows(const float* logits, int32_t* out, int rows, int V, cudaStream_
   argmax_rows_kernel<<<rows, 256, 0, s>>>(logits, out, rows, V);
 }
 
+// Temperature sampling (ane/train_full.go:318-342): total = sum_i exp((l_i - max) / T) in double, target = u * total,
+// result = first i whose running sum reaches target.  One block per row: every thread owns a contiguous chunk and
+// sums it in index order, thread 0 scans the 256 chunk sums in order, and the thread whose chunk straddles the
+// target walks it again.  The running sum therefore groups the additions by chunk; the index can differ from the
+// reference's single serial sum only when target lies within double rounding of a prefix boundary.
+__global__ void __launch_bounds__(256)
+sample_rows_kernel(const float* __restrict__ logits, const double* __restrict__ u, float temperature,
+                   int32_t* __restrict__ out, int rows, int V) {
+  const int row = blockIdx.x;
+  if (row >= rows) return;
+  const float* p = logits + (size_t)row * V;
+  __shared__ float s_max[256];
+  __shared__ double s_sum[256];
+  __shared__ double s_target;
+  __shared__ int s_pick;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, p[i]);
+  s_max[threadIdx.x] = mx;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o) s_max[threadIdx.x] = fmaxf(s_max[threadIdx.x], s_max[threadIdx.x + o]);
+    __syncthreads();
+  }
+  const double maxv = (double)s_max[0];
+  const double inv_temp = (double)(1.0f / temperature);
+  const int per = (V + 255) / 256;
+  const int i0 = min((int)threadIdx.x * per, V), i1 = min(i0 + per, V);
+  double part = 0.0;
+  for (int i = i0; i < i1; ++i) part += exp(((double)p[i] - maxv) * inv_temp);
+  s_sum[threadIdx.x] = part;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double acc = 0.0;
+    for (int t = 0; t < 256; ++t) {  // s_sum[t] becomes the sum of all chunks before t
+      const double v = s_sum[t];
+      s_sum[t] = acc;
+      acc += v;
+    }
+    s_target = u[row] * acc;
+    s_pick = V - 1;  // the reference's answer when the running sum never reaches target
+  }
+  __syncthreads();
+  const double target = s_target;
+  const double before = s_sum[threadIdx.x];
+  const double through = before + part;
+  // exactly one chunk has before < target <= through, except at target == 0 (the first element wins)
+  if (i1 > i0 && through >= target && (before < target || threadIdx.x == 0)) {
+    double acc = before;
+    int pick = i1 - 1;
+    for (int i = i0; i < i1; ++i) {
+      acc += exp(((double)p[i] - maxv) * inv_temp);
+      if (acc >= target) {
+        pick = i;
+        break;
+      }
+    }
+    atomicMin(&s_pick, pick);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) out[row] = s_pick;
+}
+void sample_rows(const float* logits, const double* u, float temperature, int32_t* out, int rows, int V,
+                 cudaStream_t s) {
+  if (rows <= 0) return;
+  if (temperature <= 1e-6f) argmax_rows_kernel<<<rows, 256, 0, s>>>(logits, out, rows, V);
+  else sample_rows_kernel<<<rows, 256, 0, s>>>(logits, u, temperature, out, rows, V);
+}
+
 }  // namespace ane

@@ -138,7 +138,8 @@ class EngineT final : public EngineBase {
   int flush(double* refresh_ms) override;
   int eval_logits(const uint16_t* tokens, uint32_t n_seq, float* out, uint64_t cap, uint32_t layout) override;
   int eval_loss(const uint16_t* tokens, uint32_t n_seq, double* loss_sum, uint64_t* n_pos) override;
-  int decode_greedy(const uint16_t* prompts, uint32_t n_seq, uint32_t prompt_len, uint32_t n_new, uint16_t* out) override;
+  int decode(const uint16_t* prompts, uint32_t n_seq, uint32_t prompt_len, uint32_t n_new, float temperature,
+             const double* uniforms, uint16_t* out) override;
   int set_lr(float lr) override;
   float get_lr() override { return lr_; }
   int get_state(ane_state* s) override;
@@ -236,6 +237,7 @@ class EngineT final : public EngineBase {
   bool decoding_ = false;  // forward() runs one KV-cached decode step
   std::vector<T*> kcache_, vcache_;  // [B, S_, KV*hd] per layer, allocated by the first decode
   int32_t* d_argmax_ = nullptr;
+  double* d_dec_u_ = nullptr;  // uniform draws of a sampling decode, [n_new][n_seq]
   uint16_t *d_dec_tok_ = nullptr, *d_dec_out_ = nullptr;
   float* h_logits_ = nullptr;  // pinned staging for EvalLogits downloads
   float* att_delta_ = nullptr;
@@ -1404,9 +1406,11 @@ __global__ void store_tokens_kernel(const int32_t* __restrict__ arg, uint16_t* _
 }
 
 template <typename T>
-int EngineT<T>::decode_greedy(const uint16_t* prompts, uint32_t n_seq, uint32_t prompt_len, uint32_t n_new,
-                              uint16_t* out) {
+int EngineT<T>::decode(const uint16_t* prompts, uint32_t n_seq, uint32_t prompt_len, uint32_t n_new,
+                       float temperature, const double* uniforms, uint16_t* out) {
   int rc;
+  const bool sampling = temperature > 1e-6f;  // ane/train_full.go:319
+  if (sampling && !uniforms) return fail(ANE_ERR_ARG, "storiesane decode: sampling needs one uniform draw per token");
   if (isN_) return fail(ANE_ERR_STATE, "storiesane decode: KV-cache decoding is built for the llama-style architecture");
   if (n_seq == 0 || (int)n_seq > B_) return fail(ANE_ERR_ARG, "storiesane decode: n_seq must be in [1, batch]");
   if (prompt_len == 0 || n_new == 0 || (int)(prompt_len + n_new) > S_)
@@ -1423,7 +1427,10 @@ int EngineT<T>::decode_greedy(const uint16_t* prompts, uint32_t n_seq, uint32_t 
     if ((rc = dalloc(&d_argmax_, B_)) != 0) return rc;
     if ((rc = dalloc(&d_dec_tok_, B_)) != 0) return rc;
     if ((rc = dalloc(&d_dec_out_, (size_t)B_ * S_)) != 0) return rc;
+    if ((rc = dalloc(&d_dec_u_, (size_t)B_ * S_)) != 0) return rc;
   }
+  if (sampling)  // [n_new][n_seq]: the draws of one step are contiguous
+    cudaMemcpyAsync(d_dec_u_, uniforms, sizeof(double) * (size_t)n_seq * n_new, cudaMemcpyHostToDevice, stream_);
   // The prompt does not fit the pinned window buffer in general (B*P <= B_*S_ does hold).
   memcpy(h_in_, prompts, sizeof(uint16_t) * (size_t)B * P);
   cudaMemcpyAsync(d_in_, h_in_, sizeof(uint16_t) * (size_t)B * P, cudaMemcpyHostToDevice, stream_);
@@ -1434,7 +1441,7 @@ int EngineT<T>::decode_greedy(const uint16_t* prompts, uint32_t n_seq, uint32_t 
     kv_cache_fill<T>((const T*)acts_[l].qkv, kcache_[l], vcache_[l], B, P, S_, H_, KV_, hd_, stream_);
   }
   auto next_token = [&](int rows_per_seq, int step) -> int {
-    // logits of the last position of every sequence -> argmax -> token
+    // logits of the last position of every sequence -> argmax or sampled index -> token
     GemmDesc g;
     g.A = xnf_ + (size_t)(rows_per_seq - 1) * D_; g.B = wop(s_embed_.off); g.C = logits_;
     g.M = B; g.N = V_; g.K = D_; g.lda = rows_per_seq * D_; g.ldb = D_; g.ldc = V_; g.out = GEMM_OUT_F32;
@@ -1442,7 +1449,7 @@ int EngineT<T>::decode_greedy(const uint16_t* prompts, uint32_t n_seq, uint32_t 
     int r = gemm(g);
     if (r != 0) return r;
     count_launch(2);
-    argmax_rows(logits_, d_argmax_, B, V_, stream_);
+    sample_rows(logits_, d_dec_u_ + (size_t)step * B, sampling ? temperature : 0.f, d_argmax_, B, V_, stream_);
     store_tokens_kernel<<<(B + 127) / 128, 128, 0, stream_>>>(d_argmax_, d_dec_tok_, d_dec_out_, B, (int)n_new, step);
     return 0;
   };

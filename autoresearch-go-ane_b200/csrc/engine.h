@@ -19,8 +19,8 @@ class EngineBase {
   virtual int flush(double* refresh_ms) = 0;
   virtual int eval_logits(const uint16_t* tokens, uint32_t n_seq, float* out, uint64_t cap, uint32_t layout) = 0;
   virtual int eval_loss(const uint16_t* tokens, uint32_t n_seq, double* loss_sum, uint64_t* n_pos) = 0;
-  virtual int decode_greedy(const uint16_t* prompts, uint32_t n_seq, uint32_t prompt_len, uint32_t n_new,
-                            uint16_t* out) = 0;
+  virtual int decode(const uint16_t* prompts, uint32_t n_seq, uint32_t prompt_len, uint32_t n_new, float temperature,
+                     const double* uniforms, uint16_t* out) = 0;
   virtual int set_lr(float lr) = 0;
   virtual float get_lr() = 0;
   virtual int get_state(ane_state* s) = 0;

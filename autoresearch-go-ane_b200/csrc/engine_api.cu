@@ -124,7 +124,17 @@ int32_t ane_decode_greedy(ane_engine* e, const uint16_t* prompts, uint32_t n_seq
     g_api_err = "storiesane decode: null buffer";
     return ANE_ERR_ARG;
   }
-  return e->impl->decode_greedy(prompts, n_seq, prompt_len, n_new, out);
+  return e->impl->decode(prompts, n_seq, prompt_len, n_new, 0.f, nullptr, out);
+}
+
+int32_t ane_decode_sample(ane_engine* e, const uint16_t* prompts, uint32_t n_seq, uint32_t prompt_len, uint32_t n_new,
+                          float temperature, const double* uniforms, uint16_t* out) {
+  ENGINE_OR_FAIL(e, "decode");
+  if (!prompts || !out) {
+    g_api_err = "storiesane decode: null buffer";
+    return ANE_ERR_ARG;
+  }
+  return e->impl->decode(prompts, n_seq, prompt_len, n_new, temperature, uniforms, out);
 }
 int32_t ane_set_lr(ane_engine* e, float lr) {
   ENGINE_OR_FAIL(e, "set lr");

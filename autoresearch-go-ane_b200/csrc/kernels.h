@@ -169,5 +169,9 @@ void ve_backward(const T* dqkv, const float* x, const uint16_t* tok, const float
 void transpose_f32(const float* in, float* out, int rows, int cols, cudaStream_t s);
 // Greedy argmax per row, lowest index wins ties (ane/train_full.go:344-354).
 void argmax_rows(const float* logits, int32_t* out, int rows, int V, cudaStream_t s);
+// Temperature sampling per row with one caller-supplied uniform draw u[row] in [0,1) (ane/train_full.go:318-342);
+// temperature <= 1e-6 is the argmax.
+void sample_rows(const float* logits, const double* u, float temperature, int32_t* out, int rows, int V,
+                 cudaStream_t s);
 
 }  // namespace ane

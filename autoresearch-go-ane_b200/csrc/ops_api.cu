@@ -142,6 +142,16 @@ int32_t ane_op_sumsq(const float* d_g, uint64_t n, float pre_scale, double* d_ou
   return 0;
 }
 
+int32_t ane_op_sample_rows(const float* d_logits, const double* d_u, float temperature, int32_t* d_out, int32_t rows,
+                           int32_t vocab) {
+  if (!d_logits || !d_out || (temperature > 1e-6f && !d_u)) return set_err(ANE_ERR_ARG, "ane_op_sample_rows: null pointer");
+  if (rows < 0 || vocab <= 0) return set_err(ANE_ERR_ARG, "ane_op_sample_rows: bad dimensions");
+  sample_rows(d_logits, d_u, temperature, d_out, rows, vocab, 0);
+  CK(cudaGetLastError());
+  CK(cudaStreamSynchronize(0));
+  return 0;
+}
+
 int32_t ane_op_gemm(const ane_gemm_args* a) {
   if (!a || a->struct_size != sizeof(ane_gemm_args)) return set_err(ANE_ERR_ARG, "ane_op_gemm: bad struct_size");
   if (!a->d_a || !a->d_b || !a->d_c) return set_err(ANE_ERR_ARG, "ane_op_gemm: null operand pointer");

@@ -11,6 +11,7 @@ package ane
 
 import (
 	"fmt"
+	"math/rand"
 	"os"
 	"runtime"
 	"sync"
@@ -137,6 +138,7 @@ var (
 	cImport     func(e uintptr, id, layer, which uint32, buf *float32, n uint64) int32
 	cExport     func(e uintptr, id, layer, which uint32, buf *float32, n uint64) int32
 	cTensorSize func(e uintptr, id, layer uint32) int64
+	cDecode     func(e uintptr, prompts *uint16, nSeq, promptLen, nNew uint32, temperature float32, uniforms *float64, out *uint16) int32
 )
 
 func load() error {
@@ -164,6 +166,7 @@ func load() error {
 		purego.RegisterLibFunc(&cImport, lib, "ane_import_tensor")
 		purego.RegisterLibFunc(&cExport, lib, "ane_export_tensor")
 		purego.RegisterLibFunc(&cTensorSize, lib, "ane_tensor_size")
+		purego.RegisterLibFunc(&cDecode, lib, "ane_decode_sample")
 	})
 	return loadErr
 }
@@ -311,6 +314,38 @@ func (e *Engine) EvalLoss(tokens []uint16) (float64, int, error) {
 		return 0, 0, e.err("eval loss", rc)
 	}
 	return sum, int(n), nil
+}
+
+// Generate is additive: KV-cached generation for nSeq prompts of equal length laid out back to back.
+// temperature <= 1e-6 is the reference's argmax (ane/train_full.go:344-354); otherwise its
+// sampleFromLogits (ane/train_full.go:318-342) with rng.Float64() drawn here, one draw per token in
+// step-major order, so a caller that seeds rng like the reference reproduces its choices.
+func (e *Engine) Generate(rng *rand.Rand, prompts []uint16, nSeq, nNew int, temperature float32) ([]uint16, error) {
+	if e == nil || e.h == 0 {
+		return nil, fmt.Errorf("storiesane decode: engine is closed")
+	}
+	if nSeq <= 0 || nNew <= 0 || len(prompts) == 0 || len(prompts)%nSeq != 0 {
+		return nil, fmt.Errorf("storiesane decode: prompts len=%d not a multiple of nSeq=%d", len(prompts), nSeq)
+	}
+	var draws []float64
+	if temperature > 1e-6 {
+		if rng == nil {
+			return nil, fmt.Errorf("storiesane decode: sampling needs a rand source")
+		}
+		draws = make([]float64, nSeq*nNew)
+		for i := range draws {
+			draws[i] = rng.Float64()
+		}
+	}
+	out := make([]uint16, nSeq*nNew)
+	rc := cDecode(e.h, unsafe.SliceData(prompts), uint32(nSeq), uint32(len(prompts)/nSeq), uint32(nNew), temperature,
+		unsafe.SliceData(draws), unsafe.SliceData(out))
+	runtime.KeepAlive(prompts)
+	runtime.KeepAlive(draws)
+	if rc != 0 {
+		return nil, e.err("decode", rc)
+	}
+	return out, nil
 }
 
 // Flush mirrors (*Engine).Flush (ane/engine.go:484).

@@ -48,6 +48,11 @@ int32_t ane_ops_device_status(int32_t* out_status);
 
 int32_t ane_op_cast_f32_to_bf16(const float* d_src, void* d_dst, uint64_t n);
 int32_t ane_op_cast_bf16_to_f32(const void* d_src, float* d_dst, uint64_t n);
+/* sampleFromLogits (ane/train_full.go:318-342) for `rows` rows of `vocab` fp32 logits: d_out[r] = sampled
+ * index of row r for the uniform draw d_u[r]; temperature <= 1e-6 gives argmax (ane/train_full.go:344-354).
+ * All three pointers are device pointers. */
+int32_t ane_op_sample_rows(const float* d_logits, const double* d_u, float temperature, int32_t* d_out, int32_t rows,
+                           int32_t vocab);
 
 /* Squared gradient norm, *d_out = sum (g*pre_scale)^2 accumulated in double: the first half of
  * clipLayerGradients (ane/train_full.go:167-196; sumSquaresGrad, ane/accel_stub.go:88-95).
@@ -193,6 +198,13 @@ int32_t ane_eval_loss(ane_engine* e, const uint16_t* tokens, uint32_t n_seq, dou
  * (ane/train_full.go:344-354: first index of the maximum).  The reference itself has no KV cache. */
 int32_t ane_decode_greedy(ane_engine* e, const uint16_t* prompts, uint32_t n_seq, uint32_t prompt_len, uint32_t n_new,
                           uint16_t* out);
+/* The same generation loop with the reference's temperature sampler in place of the argmax
+ * (sampleFromLogits, ane/train_full.go:318-342: total = sum exp((l - max)/T) in double, first index whose
+ * running sum reaches u*total).  The reference draws u from Go's math/rand, which is not reproduced: the
+ * caller supplies the draws, uniforms[step*n_seq + b] in [0,1), one per generated token.  temperature
+ * <= 1e-6 is the argmax and ignores uniforms. */
+int32_t ane_decode_sample(ane_engine* e, const uint16_t* prompts, uint32_t n_seq, uint32_t prompt_len, uint32_t n_new,
+                          float temperature, const double* uniforms, uint16_t* out);
 int32_t ane_set_lr(ane_engine* e, float lr);   /* ane/engine.go:366 */
 float ane_get_lr(ane_engine* e);               /* ane/engine.go:358 */
 int32_t ane_get_state(ane_engine* e, ane_state* out);       /* ane/engine.go:498 */

@@ -1309,6 +1309,25 @@ int32_t orc_argmax(const float* v, int32_t n) {
   return best;
 }
 
+// ane/train_full.go:318-342 sampleFromLogits, with the uniform draw supplied by the caller (the reference
+// takes it from Go's math/rand, which is not restated).
+int32_t orc_sample(const float* logits, int32_t n, float temperature, double u) {
+  if (temperature <= 1e-6f) return orc_argmax(logits, n);
+  float maxv = logits[0];
+  for (int i = 1; i < n; ++i)
+    if (logits[i] > maxv) maxv = logits[i];
+  const double inv_temp = (double)(1 / temperature);
+  double total = 0.0;
+  for (int i = 0; i < n; ++i) total += exp(((double)logits[i] - (double)maxv) * inv_temp);
+  const double target = u * total;
+  double acc = 0.0;
+  for (int i = 0; i < n; ++i) {
+    acc += exp(((double)logits[i] - (double)maxv) * inv_temp);
+    if (acc >= target) return i;
+  }
+  return n - 1;
+}
+
 void orc_set_reference_threading(int32_t on) { g_ref_threading = on ? 1 : 0; }
 int32_t orc_num_threads(void) { return g_threads; }
 void orc_set_num_threads(int32_t n) { g_threads = n < 1 ? 1 : n; }

@@ -115,6 +115,7 @@ void orc_softcap(float* logits, uint64_t n);
 void orc_adam(float* w, const float* g, float* m, float* v, uint64_t n, int32_t t, float lr, float b1, float b2,
               float eps, float wd);
 int32_t orc_argmax(const float* v, int32_t n);
+int32_t orc_sample(const float* logits, int32_t n, float temperature, double u);
 
 /* Threading: 1 = only the loops the reference runs through parallelFor*
  * (norms, CE, classifier GEMMs, Adam) plus dW jobs; 0 (default) = every loop whose

@@ -143,6 +143,8 @@ def lib():
     L.orc_adam.argtypes = [fp, fp, fp, fp, c_uint64, c_int32, c_float, c_float, c_float, c_float, c_float]
     L.orc_argmax.restype = c_int32
     L.orc_argmax.argtypes = [fp, c_int32]
+    L.orc_sample.restype = c_int32
+    L.orc_sample.argtypes = [fp, c_int32, c_float, c_double]
     L.orc_set_reference_threading.argtypes = [c_int32]
     L.orc_num_threads.restype = c_int32
     L.orc_set_num_threads.argtypes = [c_int32]

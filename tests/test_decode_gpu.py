@@ -62,3 +62,70 @@ def test_decode_rejected_for_reference_arch():
     with pytest.raises(ane.EngineError):
         e.decode_greedy(np.zeros((1, 8), np.uint16), 4)
     e.close()
+
+
+def _upload(lib, a):
+    p = lib.ane_dev_malloc(a.nbytes)
+    assert lib.ane_dev_h2d(p, a.ctypes.data, a.nbytes) == 0
+    return p
+
+
+def test_sampler_rows_match_oracle_serial_walk():
+    """sampleFromLogits (ane/train_full.go:318-342) is an index path: the device's chunked double sums must
+    land on the oracle's index for the same uniform draw (a different index needs the target within double
+    rounding of a prefix boundary, which seeded draws do not hit)."""
+    import ctypes
+    from ane import _ffi
+    lib = _ffi.lib
+    rng = np.random.default_rng(11)
+    rows, vocab = 16, 32000
+    logits = (4.0 * rng.standard_normal((rows, vocab))).astype(np.float32)
+    logits[3, :] = 0.25                       # flat row: every index equally likely
+    logits[4, 100] = 60.0                     # one dominant logit
+    d_logits = _upload(lib, logits)
+    d_out = lib.ane_dev_malloc(4 * rows)
+    fp = ctypes.POINTER(ctypes.c_float)
+    for temp in (0.0, 0.7, 1.0, 1.8):
+        for trial in range(3):
+            u = rng.random(rows)
+            if trial == 0:
+                u[:3] = (0.0, 1.0 - 2.0 ** -53, 0.5)
+            d_u = _upload(lib, u)
+            assert lib.ane_op_sample_rows(d_logits, d_u, temp, d_out, rows, vocab) == 0, lib.ane_ops_last_error()
+            got = np.zeros(rows, dtype=np.int32)
+            assert lib.ane_dev_d2h(got.ctypes.data, d_out, got.nbytes) == 0
+            for r in range(rows):
+                want = O.lib().orc_sample(logits[r].ctypes.data_as(fp), vocab, temp, float(u[r]))
+                assert int(got[r]) == want, (temp, trial, r)
+            lib.ane_dev_free(d_u)
+    lib.ane_dev_free(d_logits)
+    lib.ane_dev_free(d_out)
+
+
+def test_decode_sample_fp32_matches_oracle_full_recompute():
+    import ctypes
+    cfg = dict(dim=64, hidden=96, heads=4, kv_heads=2, layers=3, vocab=256, seq=48)
+    m, e = make_pair(ane, cfg, arch=O.ARCH_L, quirks=0, dtype=ane.DTYPE_F32, batch=3, std=0.3, debug_taps=False)
+    prompts = O.zipf_tokens(3 * 20, cfg["vocab"], 8).reshape(3, 20)
+    n_new, temp = 10, 0.9
+    u = np.random.default_rng(21).random((n_new, 3))
+    got = e.decode_sample(prompts, n_new, temp, u)
+    fp = ctypes.POINTER(ctypes.c_float)
+    for b in range(3):
+        seq = list(prompts[b])
+        for step in range(n_new):
+            padded = np.zeros(cfg["seq"], dtype=np.uint16)
+            padded[:len(seq)] = seq
+            col = np.ascontiguousarray(m.eval_logits(padded)[:, len(seq) - 1])
+            want = O.lib().orc_sample(col.ctypes.data_as(fp), cfg["vocab"], temp, float(u[step, b]))
+            if int(got[b, step]) != want:
+                # fp32 GEMM summation order moves the logits by ~1e-6: accept a neighbour only when the draw sits
+                # on that boundary
+                w = np.exp((col.astype(np.float64) - col.max()) / temp)
+                cum = np.cumsum(w) / w.sum()
+                assert abs(cum[min(want, int(got[b, step]))] - u[step, b]) < 1e-5, (b, step)
+            seq.append(int(got[b, step]))
+    assert (e.decode_sample(prompts, n_new, 0.0, u) == e.decode_greedy(prompts, n_new)).all()
+    with pytest.raises(ane.EngineError):
+        e.decode_sample(prompts, n_new, temp, u[:, :2])
+    e.close()
