@@ -128,8 +128,38 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     }
     attr_set = true;
   }
-  constexpr int BM_TILE = GEMM_BM * MT;
+  constexpr int BM_TILE = GemmCfg<BN, MT>::BM_TILE;
   const int base_tiles = ((d.M + BM_TILE - 1) / BM_TILE) * ((d.N + BN - 1) / BN);
+  if constexpr (GemmCfg<BN, MT>::PAIR) {
+    // one cluster of two CTAs per tile; as many clusters as the device keeps resident at once
+    static int max_pairs = 0;  // per template instantiation
+    if (max_pairs == 0) {
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3(2 * 74);
+      q.blockDim = dim3(GEMM_THREADS);
+      q.dynamicSmemBytes = smem_bytes;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 2;
+      at[0].val.clusterDim.y = 1;
+      at[0].val.clusterDim.z = 1;
+      q.attrs = at;
+      q.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess || n <= 0) n = gemm_num_sms() / 2;
+      if (n > gemm_num_sms() / 2) n = gemm_num_sms() / 2;
+      max_pairs = n;
+    }
+    const int work = base_tiles * (split_k > 0 ? split_k : 1);
+    const int pairs = work < max_pairs ? work : max_pairs;
+    cudaError_t e = launch_pdl_cluster(kern, dim3(2 * (pairs < 1 ? 1 : pairs)), dim3(GEMM_THREADS), smem_bytes, stream, 2u,
+                                       ta, tb, tc, td, epi, d.M, d.N, d.K, split_k > 0 ? split_k : 1, d_status);
+    if (e != cudaSuccess) {
+      g_gemm_err = std::string("gemm_tc pair launch: ") + cudaGetErrorString(e);
+      return -4;
+    }
+    return 0;
+  }
   int grid;
   if (split_k > 0) {
     const int tiles = base_tiles * split_k;
@@ -207,7 +237,12 @@ static int dispatch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
     }
     return launch_tc<BN, MT, A_MN, B_MN, EPI_STORE_F32>(ta, tb, tc, tc, epi, d, 1, d_status, stream);
   }
-  return launch_tc<BN, MT, A_MN, B_MN, EPI_REDUCE_F32>(ta, tb, tc, tc, epi, d, split_k, d_status, stream);
+  if constexpr (GemmCfg<BN, MT>::PAIR) {
+    g_gemm_err = "CTA-pair tiles are built for the non-accumulating epilogues";
+    return -2;
+  } else {
+    return launch_tc<BN, MT, A_MN, B_MN, EPI_REDUCE_F32>(ta, tb, tc, tc, epi, d, split_k, d_status, stream);
+  }
 }
 
 template <int BN, int MT>
@@ -217,13 +252,23 @@ static int dispatch_layout(const GemmDesc& d, int split_k, int* d_status, cudaSt
   if (!d.a_mn) ok = make_tmap(&ta, d.A, d.K, d.M, d.lda, GEMM_BK, GEMM_BM);
   else         ok = make_tmap(&ta, d.A, d.M, d.K, d.lda, 64, GEMM_BK);
   if (!ok) return -2;
-  if (!d.b_mn) ok = make_tmap(&tb, d.B, d.K, d.N, d.ldb, GEMM_BK, BN);
+  // K-major B: one box per CTA and stage (a CTA of a pair loads half of the tile's rows)
+  if (!d.b_mn) ok = make_tmap(&tb, d.B, d.K, d.N, d.ldb, GEMM_BK, GemmCfg<BN, MT>::PAIR ? BN / 2 : BN);
   else         ok = make_tmap(&tb, d.B, d.N, d.K, d.ldb, 64, GEMM_BK);
   if (!ok) return -2;
+  if constexpr (GemmCfg<BN, MT>::PAIR) {  // forward and dX forms only (A K-major)
+    if (!d.a_mn && !d.b_mn) return dispatch_epi<BN, MT, false, false>(ta, tb, d, split_k, d_status, stream);
+    if constexpr (BN % 128 == 0) {
+      if (!d.a_mn && d.b_mn) return dispatch_epi<BN, MT, false, true>(ta, tb, d, split_k, d_status, stream);
+    }
+    g_gemm_err = "CTA-pair tiles: unsupported operand layout";
+    return -2;
+  } else {
   if (!d.a_mn && !d.b_mn) return dispatch_epi<BN, MT, false, false>(ta, tb, d, split_k, d_status, stream);
   if (!d.a_mn && d.b_mn) return dispatch_epi<BN, MT, false, true>(ta, tb, d, split_k, d_status, stream);
   if (d.a_mn && d.b_mn) return dispatch_epi<BN, MT, true, true>(ta, tb, d, split_k, d_status, stream);
   return dispatch_epi<BN, MT, true, false>(ta, tb, d, split_k, d_status, stream);
+  }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -360,6 +405,29 @@ int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream) {
   }
   GemmPlan p = plan_gemm(d, gemm_num_sms());
   if (d.out == GEMM_OUT_BF16_SWIGLU && p.bn == 192) p.bn = 256;  // gate rows pair up two 64-column pieces
+  // CTA-pair tiles (256 x 256 per two SMs, half of the B tile per CTA): measured faster than both single-CTA
+  // forms when K is short (the 256-row single-CTA tile cannot hide its epilogue there) and the tiles fill the
+  // pairs' waves; slower for N = 768 (96 tiles on 74 pairs) and for long K.
+  static const int pair_env = [] {
+    const char* e = getenv("ANE_B200_GEMM_PAIR");  // 0: off; 128 | 192 | 256: that width wherever pairs apply
+    return e ? atoi(e) : -1;
+  }();
+  if (pair_env != 0 && d.out != GEMM_OUT_ACCUM && !d.a_mn && d.M >= 256) {
+    int bn = 0;
+    if (pair_env > 0) {
+      bn = pair_env;
+      if (bn == 192 && (d.b_mn || d.out == GEMM_OUT_BF16_SWIGLU)) bn = 256;
+    } else {
+      const int pairs = gemm_num_sms() / 2;
+      const long tiles = (long)((d.M + 255) / 256) * ((d.N + 255) / 256);
+      const long waves = (tiles + pairs - 1) / pairs;
+      const double eff = (double)tiles / (double)(waves * pairs) * ((double)d.N / (double)(((d.N + 255) / 256) * 256));
+      if ((d.K + GEMM_BK - 1) / GEMM_BK < 32 && eff >= 0.85) bn = 256;
+    }
+    if (bn == 256) return dispatch_layout<256, GEMM_MT_PAIR>(d, 1, d_status, stream);
+    if (bn == 192) return dispatch_layout<192, GEMM_MT_PAIR>(d, 1, d_status, stream);
+    if (bn == 128) return dispatch_layout<128, GEMM_MT_PAIR>(d, 1, d_status, stream);
+  }
   if (p.mt == 2) {
     if (p.bn == 256) return dispatch_layout<256, 2>(d, p.sched, d_status, stream);
     return dispatch_layout<192, 2>(d, p.sched, d_status, stream);

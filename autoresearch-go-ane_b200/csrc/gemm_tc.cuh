@@ -11,7 +11,10 @@
 // Pipeline: warp 0 issues TMA loads (128B-swizzled tiles) into a shared-memory
 // ring; warp 1 issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM
 // accumulators; warps 2..5 drain the other accumulator with tcgen05.ld and run
-// the epilogue functor. No cluster launch, no multicast.
+// the epilogue functor.  MT == GEMM_MT_PAIR runs the same pipeline on a cluster of two CTAs that share one
+// 256 x BN tile through tcgen05.mma.cta_group::2: each CTA loads its 128 rows of A and half of the B tile, so the
+// shared-memory fill per FLOP drops without giving up the second accumulator set.  Every load still writes a
+// single CTA's shared memory.
 //
 // This replaces the nine cblas_sgemm call sites of the reference
 // (ane/accel_darwin.go:74-207, ane/stories/gemm_accel_darwin.go:15-55) and the
@@ -31,16 +34,24 @@ static constexpr int GEMM_THREADS = 192;
 // two MMAs, so the shared-memory fill per FLOP drops by a third; its MT*BN accumulator columns leave no
 // room for a second TMEM buffer when BN > 128, so the epilogue of a tile then does not overlap the next
 // tile's main loop -- it pays for long K, not for short K.
+static constexpr int GEMM_MT_PAIR = 4;  // tag value of MT: one 256-row tile per CTA pair
 template <int BN, int MT>
 struct GemmCfg {
-  static constexpr int BM_TILE = GEMM_BM * MT;
-  static constexpr uint32_t A_BYTES = BM_TILE * GEMM_BK * 2;
-  static constexpr uint32_t B_BYTES = BN * GEMM_BK * 2;
-  static constexpr uint32_t STAGING_BYTES = 4 * 2 * 4096;  // 4 epilogue warps x 2 buffers x (32 rows x 128 B)
+  static constexpr bool PAIR = MT == GEMM_MT_PAIR;
+  static constexpr int SUBS = PAIR ? 1 : MT;                      // 128-row accumulator sub-tiles per CTA
+  static constexpr int BM_TILE = PAIR ? 2 * GEMM_BM : GEMM_BM * MT;  // rows of a scheduled tile
+  static constexpr uint32_t A_BYTES = SUBS * GEMM_BM * GEMM_BK * 2;  // per CTA and stage
+  static constexpr uint32_t B_BYTES = (PAIR ? BN / 2 : BN) * GEMM_BK * 2;
+  // Staged output pieces per epilogue warp (a buffer is reused once its TMA store has read it; four buffers
+  // measured no faster than two and cost a pipeline stage).
+  static constexpr int SBUF = 2;
+  static constexpr uint32_t STAGING_BYTES = 4 * SBUF * 4096;  // 4 epilogue warps x SBUF buffers x (32 rows x 128 B)
   static constexpr int STAGES_FIT = (int)((232448u - 1024u - STAGING_BYTES) / (A_BYTES + B_BYTES));
-  static constexpr int STAGES = STAGES_FIT > 6 ? 6 : STAGES_FIT;
+  // (a pair keeps room for the residual buffers of EPI_STORE_F32_TMARES: five stages)
+  static constexpr int STAGES_RES = (int)((232448u - 1024u - STAGING_BYTES - 4 * 2 * 4096) / (A_BYTES + B_BYTES));
+  static constexpr int STAGES = PAIR ? (STAGES_RES > 6 ? 6 : STAGES_RES) : (STAGES_FIT > 6 ? 6 : STAGES_FIT);
   static constexpr uint32_t SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + STAGING_BYTES + 1024;  // +1024: alignment
-  static constexpr int ACC_COLS = MT * BN;                       // one accumulator set
+  static constexpr int ACC_COLS = SUBS * BN;                     // one accumulator set
   static constexpr int NBUF = (2 * ACC_COLS <= 512) ? 2 : 1;     // TMEM accumulator sets
   static constexpr uint32_t TMEM_COLS = (NBUF * ACC_COLS <= 256) ? 256 : 512;
 };
@@ -108,7 +119,10 @@ struct EpiParams {
 struct GemmSched {
   int tiles_m, tiles, kblocks, split_k, kb_per_split, total_work, w;
   long long u, u1;
-  __device__ __forceinline__ void init(int M, int N, int K, int BM_TILE, int BN, int split) {
+  int bid, nblk;  // this CTA's (or CTA pair's) index and the number of them
+  __device__ __forceinline__ void init(int M, int N, int K, int BM_TILE, int BN, int split, int bid_, int nblk_) {
+    bid = bid_;
+    nblk = nblk_;
     tiles_m = (M + BM_TILE - 1) / BM_TILE;
     const int tiles_n = (N + BN - 1) / BN;
     tiles = tiles_m * tiles_n;
@@ -117,11 +131,11 @@ struct GemmSched {
     if (split_k > 0) {
       kb_per_split = (kblocks + split_k - 1) / split_k;
       total_work = tiles * split_k;
-      w = blockIdx.x;
+      w = bid;
     } else {
       const long long units = (long long)tiles * kblocks;
-      u = units * blockIdx.x / gridDim.x;
-      u1 = units * (blockIdx.x + 1) / gridDim.x;
+      u = units * bid / nblk;
+      u1 = units * (bid + 1) / nblk;
     }
   }
   // Next non-empty segment: tile (tm, tn) and k-block range [kb0, kb1).
@@ -130,7 +144,7 @@ struct GemmSched {
       while (w < total_work) {
         const int split = w / tiles;
         const int rem = w - split * tiles;
-        w += gridDim.x;
+        w += nblk;
         kb0 = split * kb_per_split;
         kb1 = min(kb0 + kb_per_split, kblocks);
         if (kb1 <= kb0) continue;
@@ -161,6 +175,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   constexpr int STAGES = Cfg::STAGES;
   constexpr int BM = Cfg::BM_TILE, BK = GEMM_BK;
   constexpr int NBUF = Cfg::NBUF;
+  constexpr bool PAIR = Cfg::PAIR;
+  constexpr int SUBS = Cfg::SUBS;
+  static_assert(!PAIR || (BN % 32 == 0 && (!B_MN || BN % 128 == 0)), "a CTA of a pair loads whole 64-column chunks");
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[STAGES];
@@ -180,8 +197,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   // A pipeline wait that gave up earlier in this stream poisons the status word: later launches
   // return at once instead of each running into its own time-out.
-  if (status != nullptr && *reinterpret_cast<volatile int*>(status) != DEV_OK) return;
-
+  // (a pair always runs through: its two CTAs must take the same path, and every wait below is bounded)
+  if (!PAIR && status != nullptr && *reinterpret_cast<volatile int*>(status) != DEV_OK) return;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // 0 = the CTA that issues the MMAs
+  const int sched_id = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int sched_n = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int row_off = PAIR ? (int)rank * GEMM_BM : 0;   // this CTA's rows inside the tile
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -195,7 +216,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int b = 0; b < NBUF; ++b) {
       mbar_init(smem_u32(&bar_tfull[b]), 1);
-      mbar_init(smem_u32(&bar_tempty[b]), 4);
+      mbar_init(smem_u32(&bar_tempty[b]), PAIR ? 8 : 4);  // the epilogue warps of both CTAs
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
@@ -203,12 +224,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_slot), Cfg::TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(smem_u32(&tmem_slot), Cfg::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(&tmem_slot), Cfg::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   pdl_trigger();
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
   pdl_wait();  // operands, residuals and C belong to earlier kernels: nothing above touched them
@@ -220,7 +247,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t phase = 0;
       bool ok = true;
       GemmSched sched;
-      sched.init(M, N, K, BM, BN, split_k);
+      sched.init(M, N, K, BM, BN, split_k, sched_id, sched_n);
       int tm, tn, kb0, kb1;
       while (ok && sched.next(tm, tn, kb0, kb1)) {
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -228,13 +255,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             ok = false;
             break;
           }
-          const uint32_t full = smem_u32(&bar_full[stage]);
-          mbar_expect_tx(full, Cfg::A_BYTES + Cfg::B_BYTES);
           const uint32_t sa = smem_a0 + stage * Cfg::A_BYTES;
           const uint32_t sb = smem_b0 + stage * Cfg::B_BYTES;
+          if constexpr (PAIR) {
+            // both CTAs' bytes complete on the leader's barrier, which expects the sum
+            const uint32_t full = map_to_cta(smem_u32(&bar_full[stage]), 0);
+            if (rank == 0) mbar_expect_tx(smem_u32(&bar_full[stage]), 2 * (Cfg::A_BYTES + Cfg::B_BYTES));
+            const int m0 = tm * BM + row_off, n0 = tn * BN + (int)rank * (BN / 2);
+            if constexpr (!A_MN) {
+              tma_load_2d_pair(sa, &tmA, full, kb * BK, m0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < GEMM_BM / 64; ++j)
+                tma_load_2d_pair(sa + j * (64 * BK * 2), &tmA, full, m0 + j * 64, kb * BK);
+            }
+            if constexpr (!B_MN) {
+              tma_load_2d_pair(sb, &tmB, full, kb * BK, n0);  // box of BN/2 rows
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 128; ++j)
+                tma_load_2d_pair(sb + j * (64 * BK * 2), &tmB, full, n0 + j * 64, kb * BK);
+            }
+          } else {
+          const uint32_t full = smem_u32(&bar_full[stage]);
+          mbar_expect_tx(full, Cfg::A_BYTES + Cfg::B_BYTES);
           if constexpr (!A_MN) {
 #pragma unroll
-            for (int i = 0; i < MT; ++i)
+            for (int i = 0; i < SUBS; ++i)
               tma_load_2d(sa + i * (GEMM_BM * BK * 2), &tmA, full, kb * BK, tm * BM + i * GEMM_BM);
           } else {
 #pragma unroll
@@ -248,22 +295,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int j = 0; j < BN / 64; ++j)
               tma_load_2d(sb + j * (64 * BK * 2), &tmB, full, tn * BN + j * 64, kb * BK);
           }
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ---------------------------------
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) |
                                  ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
-                                 ((uint32_t)(GEMM_BM >> 4) << 24);
+                                 ((uint32_t)((PAIR ? 2 * GEMM_BM : GEMM_BM) >> 4) << 24);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
       GemmSched sched;
-      sched.init(M, N, K, BM, BN, split_k);
+      sched.init(M, N, K, BM, BN, split_k, sched_id, sched_n);
       int tm, tn, kb0, kb1;
       while (ok && sched.next(tm, tn, kb0, kb1)) {
         const int buf = local % NBUF;
@@ -288,19 +336,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if constexpr (!B_MN) bdesc = make_smem_desc(sb + k * 32, 16, 1024);
             else                 bdesc = make_smem_desc(sb + k * 2048, 64 * BK * 2, 1024);
 #pragma unroll
-            for (int i = 0; i < MT; ++i) {  // the A sub-tiles share this B tile
+            for (int i = 0; i < SUBS; ++i) {  // the A sub-tiles share this B tile
               uint64_t adesc;
               const uint32_t sai = sa + i * (GEMM_BM * BK * 2);
               if constexpr (!A_MN) adesc = make_smem_desc(sai + k * 32, 16, 1024);
               else                 adesc = make_smem_desc(sai + k * 2048, 64 * BK * 2, 1024);
-              tc_mma_bf16(tmem_d + (uint32_t)(i * BN), adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+              if constexpr (PAIR) tc_mma_bf16_pair(tmem_d, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+              else tc_mma_bf16(tmem_d + (uint32_t)(i * BN), adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
             }
           }
-          tc_commit(smem_u32(&bar_empty[stage]));
+          if constexpr (PAIR) tc_commit_pair(smem_u32(&bar_empty[stage]));  // frees the stage in both CTAs
+          else tc_commit(smem_u32(&bar_empty[stage]));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        tc_commit(smem_u32(&bar_tfull[buf]));
+        if constexpr (PAIR) tc_commit_pair(smem_u32(&bar_tfull[buf]));
+        else tc_commit(smem_u32(&bar_tfull[buf]));
         ++local;
       }
     }
@@ -311,7 +362,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     constexpr bool kBf16Out = (EPI == EPI_STORE_BF16 || EPI == EPI_STORE_BF16_SWIGLU || EPI == EPI_STORE_BF16_ROPE ||
                                EPI == EPI_STORE_BF16_TGT);
     constexpr int CW = kBf16Out ? 64 : 32;
-    const uint32_t stage_base = smem_stage0 + (uint32_t)(warp - 2) * 8192u;
+    constexpr int SBUF = Cfg::SBUF;
+    const uint32_t stage_base = smem_stage0 + (uint32_t)(warp - 2) * (uint32_t)(SBUF * 4096);
     uint8_t* stage_ptr = smem_raw + (stage_base - smem_u32(smem_raw));
     int local = 0;
     int sbuf = 0;
@@ -326,7 +378,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint8_t* res_ptr = smem_raw + (res_base - smem_u32(smem_raw));
     uint32_t res_uses = 0;  // pieces consumed so far (buffer = uses & 1, phase = (uses >> 1) & 1)
     GemmSched sched;
-    sched.init(M, N, K, BM, BN, split_k);
+    sched.init(M, N, K, BM, BN, split_k, sched_id, sched_n);
     int tm, tn, kb0, kb1;
     while (ok && sched.next(tm, tn, kb0, kb1)) {
       const int buf = local % NBUF;
@@ -346,7 +398,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
       };
-      prefetch_first(tm * BM + lane_group * 32 + lane);
+      prefetch_first(tm * BM + row_off + lane_group * 32 + lane);
       // Residual piece `piece` (counted over the whole kernel) of the current (tile, sub): same validity test as
       // the consuming loop, so every issued piece is consumed.
       uint32_t res_issued = res_uses;
@@ -364,8 +416,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       };
       if constexpr (EPI == EPI_STORE_F32_TMARES) {  // first two pieces of sub-tile 0, while the MMAs still run
-        issue_res(tm * BM + lane_group * 32, tn * BN);
-        issue_res(tm * BM + lane_group * 32, tn * BN + CW);
+        issue_res(tm * BM + row_off + lane_group * 32, tn * BN);
+        issue_res(tm * BM + row_off + lane_group * 32, tn * BN + CW);
       }
       if (!mbar_wait(smem_u32(&bar_tfull[buf]), tphase, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
         ok = false;
@@ -373,8 +425,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       tc_fence_after();
 #pragma unroll 1
-      for (int sub = 0; sub < MT; ++sub) {
-      const int m_warp = tm * BM + sub * GEMM_BM + lane_group * 32;
+      for (int sub = 0; sub < SUBS; ++sub) {
+      const int m_warp = tm * BM + row_off + sub * GEMM_BM + lane_group * 32;
       const int m = m_warp + lane;
       if (sub > 0) {
         prefetch_first(m);
@@ -427,9 +479,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
         tmem_ld_wait();
-        // The piece staged two iterations ago must have been read by its TMA store before its
+        // The piece staged SBUF iterations ago must have been read by its TMA store before its
         // buffer is rewritten.
-        if (lane == 0) tma_store_wait_read<1>();
+        if (lane == 0) tma_store_wait_read<SBUF - 1>();
         __syncwarp();
         uint8_t* row_ptr = stage_ptr + sbuf * 4096 + lane * 128;
         if constexpr (kBf16Out) {
@@ -484,9 +536,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               if (lane == 0) {
                 tma_store_2d(&tmD, stage_base + (uint32_t)sbuf * 4096u, (n0 - CW) >> 1, m_warp);
                 tma_store_commit();
-                tma_store_wait_read<1>();  // the other buffer (the piece before this one) is free again
+                tma_store_wait_read<SBUF - 1>();  // the next buffer in the rotation is free again
               }
-              sbuf ^= 1;
+              sbuf = (sbuf + 1) % SBUF;
               __syncwarp();
               row_ptr = stage_ptr + sbuf * 4096 + lane * 128;
             }
@@ -506,6 +558,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const float* r2 = (EPI == EPI_STORE_F32 && epi.res2 && in_rows) ? epi.res2 + (size_t)m * epi.ldres + n0 : nullptr;
           const bool full = n0 + 32 <= N;
           const uint8_t* res_row = nullptr;
+          float4 rres[8];  // the residual piece, read before any staging store (the compiler cannot tell the two apart)
           if constexpr (EPI == EPI_STORE_F32_TMARES) {
             const uint32_t b = res_uses & 1u;
             if (!mbar_wait(smem_u32(&bar_res[warp - 2][b]), (res_uses >> 1) & 1u, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
@@ -513,13 +566,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               break;
             }
             res_row = res_ptr + b * 4096u + lane * 128;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) rres[q] = *reinterpret_cast<const float4*>(res_row + ((q ^ (lane & 7)) << 4));
           }
 #pragma unroll
           for (int q = 0; q < 8; ++q) {  // 8 chunks of 4 fp32
             float4 v = make_float4(epi.alpha * acc[4 * q], epi.alpha * acc[4 * q + 1], epi.alpha * acc[4 * q + 2],
                                    epi.alpha * acc[4 * q + 3]);
             if constexpr (EPI == EPI_STORE_F32_TMARES) {  // rows / columns outside the tensor arrive as zeros
-              const float4 t = *reinterpret_cast<const float4*>(res_row + ((q ^ (lane & 7)) << 4));
+              const float4 t = rres[q];
               v.x += a1 * t.x; v.y += a1 * t.y; v.z += a1 * t.z; v.w += a1 * t.w;
             }
             if constexpr (EPI == EPI_STORE_F32) {
@@ -564,12 +619,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           else tma_store_2d(&tmC, src, n0, m_warp);
           tma_store_commit();
         }
-        sbuf ^= 1;
+        sbuf = (sbuf + 1) % SBUF;
       }
       }  // sub
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[buf]));
+      if (lane == 0) {
+        if (PAIR && rank != 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bar_tempty[buf]), 0));
+        else mbar_arrive(smem_u32(&bar_tempty[buf]));
+      }
       ++local;
     }
     if (lane == 0) tma_store_wait<0>();
@@ -577,9 +635,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // the peer has drained its accumulators and its last loads have landed
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+    else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 

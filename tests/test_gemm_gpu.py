@@ -104,6 +104,25 @@ def test_step_sized_shapes_take_the_wide_tile_and_tma_residual_paths():
     assert rel_l2(got, A[:M] @ W[:N].T + R[:M, :N]) < 1e-4
 
 
+def test_short_k_wide_n_shapes_take_the_cta_pair_tiles():
+    """K = 768 with enough 256 x 256 tiles to fill the CTA pairs: the planner picks the two-CTA kernel
+    (tcgen05.mma.cta_group::2, half of the B tile per CTA).  Both B layouts, a residual, and ragged M and N
+    (the second CTA's rows / B columns then start or end outside the tensors)."""
+    rng = np.random.default_rng(5)
+    for (M, N, K, b_mn, res) in [(8192, 2304, 768, 0, False), (4000, 2300, 768, 1, False), (3900, 2304, 704, 0, True),
+                                 (8192, 2048, 768, 1, False)]:
+        A = _bf16_round(rng.standard_normal((M, K)).astype(np.float32) * 0.1)
+        if b_mn:
+            B = _bf16_round(rng.standard_normal((K, N + (-N) % 8)).astype(np.float32) * 0.1)   # 16-byte row pitch
+            want = A @ B[:, :N]
+        else:
+            B = _bf16_round(rng.standard_normal((N, K)).astype(np.float32) * 0.1)
+            want = A @ B.T
+        R = rng.standard_normal((M, N)).astype(np.float32) if res else None
+        got = _gemm(ane.DTYPE_BF16, A, B, np.zeros((M, N), np.float32), M, N, K, 0, b_mn, 1, res=R)
+        assert rel_l2(got, want + (R if res else 0)) < 1e-4, (M, N, K, b_mn, res)
+
+
 @pytest.mark.parametrize("dtype", [ane.DTYPE_BF16, ane.DTYPE_F32])
 @pytest.mark.parametrize("oc,ic,seq", [(96, 64, 40), (256, 136, 300), (768, 256, 128)])
 def test_linear_forward_dx_dw_match_oracle(dtype, oc, ic, seq):
