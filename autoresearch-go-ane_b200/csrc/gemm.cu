@@ -118,7 +118,8 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
                      const EpiParams& epi,
                      const GemmDesc& d, int split_k, int* d_status, cudaStream_t stream) {
   auto kern = gemm_tc_kernel<BN, MT, A_MN, B_MN, EPI>;
-  constexpr uint32_t smem_bytes = GemmCfg<BN, MT>::SMEM_BYTES + (EPI == EPI_STORE_F32_TMARES ? GEMM_TMARES_BYTES : 0u);
+  constexpr uint32_t smem_bytes = GemmCfg<BN, MT>::smem_bytes(EPI == EPI_STORE_F32_TMARES);
+  static_assert(smem_bytes <= GEMM_SMEM_LIMIT && GemmCfg<BN, MT>::stages(EPI == EPI_STORE_F32_TMARES) >= 3, "pipeline does not fit");
   static bool attr_set = false;  // per template instantiation
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
@@ -227,7 +228,7 @@ static int dispatch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
   if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 32, 32, true)) return -2;
   if (d.out == GEMM_OUT_F32) {
     // One residual, K-major operands and room for the residual buffers: let TMA fetch the residual pieces.
-    if constexpr (!A_MN && !B_MN && GemmCfg<BN, MT>::SMEM_BYTES + GEMM_TMARES_BYTES <= 232448u) {
+    if constexpr (!A_MN && !B_MN && GemmCfg<BN, MT>::smem_bytes(true) <= GEMM_SMEM_LIMIT && GemmCfg<BN, MT>::stages(true) >= 3) {
       static const bool no_tma_res = getenv("ANE_B200_NO_TMA_RES") != nullptr;  // A/B measurements
       if (d.res1 != nullptr && d.res2 == nullptr && !no_tma_res) {
         CUtensorMap td;
@@ -258,9 +259,7 @@ static int dispatch_layout(const GemmDesc& d, int split_k, int* d_status, cudaSt
   if (!ok) return -2;
   if constexpr (GemmCfg<BN, MT>::PAIR) {  // forward and dX forms only (A K-major)
     if (!d.a_mn && !d.b_mn) return dispatch_epi<BN, MT, false, false>(ta, tb, d, split_k, d_status, stream);
-    if constexpr (BN % 128 == 0) {
-      if (!d.a_mn && d.b_mn) return dispatch_epi<BN, MT, false, true>(ta, tb, d, split_k, d_status, stream);
-    }
+    if (!d.a_mn && d.b_mn) return dispatch_epi<BN, MT, false, true>(ta, tb, d, split_k, d_status, stream);
     g_gemm_err = "CTA-pair tiles: unsupported operand layout";
     return -2;
   } else {
@@ -409,21 +408,36 @@ int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream) {
   // forms when K is short (the 256-row single-CTA tile cannot hide its epilogue there) and the tiles fill the
   // pairs' waves; slower for N = 768 (96 tiles on 74 pairs) and for long K.
   static const int pair_env = [] {
-    const char* e = getenv("ANE_B200_GEMM_PAIR");  // 0: off; 128 | 192 | 256: that width wherever pairs apply
+    // 0: off; 128 | 192 | 256: 256-row pair tiles of that width, 512: 512 x 192 pair tiles, wherever pairs apply
+    const char* e = getenv("ANE_B200_GEMM_PAIR");
     return e ? atoi(e) : -1;
   }();
   if (pair_env != 0 && d.out != GEMM_OUT_ACCUM && !d.a_mn && d.M >= 256) {
     int bn = 0;
     if (pair_env > 0) {
       bn = pair_env;
-      if (bn == 192 && (d.b_mn || d.out == GEMM_OUT_BF16_SWIGLU)) bn = 256;
+      if (bn == 192 && d.out == GEMM_OUT_BF16_SWIGLU) bn = 256;
     } else {
       const int pairs = gemm_num_sms() / 2;
       const long tiles = (long)((d.M + 255) / 256) * ((d.N + 255) / 256);
       const long waves = (tiles + pairs - 1) / pairs;
       const double eff = (double)tiles / (double)(waves * pairs) * ((double)d.N / (double)(((d.N + 255) / 256) * 256));
-      if ((d.K + GEMM_BK - 1) / GEMM_BK < 32 && eff >= 0.85) bn = 256;
+      const int kblocks = (d.K + GEMM_BK - 1) / GEMM_BK;
+      if (kblocks < 32 && eff >= 0.85) {
+        bn = 256;
+      } else if (d.out != GEMM_OUT_BF16_SWIGLU) {
+        // 512 x 192 tiles (two sub-tiles per CTA, one accumulator set): the least fill per FLOP.  For the
+        // N = 768 shapes they make one wave of 64 tiles; measured faster than the single-CTA 256-row tile for
+        // K >= 2048 and for the short-K bf16 store, slower for the short-K residual epilogue (which is exposed).
+        const long tiles2 = (long)((d.M + 511) / 512) * ((d.N + 191) / 192);
+        const long waves2 = (tiles2 + pairs - 1) / pairs;
+        const double eff2 =
+            (double)tiles2 / (double)(waves2 * pairs) * ((double)d.N / (double)(((d.N + 191) / 192) * 192));
+        const bool exposed_residual = kblocks < 32 && (d.res1 != nullptr || d.res2 != nullptr);
+        if (eff2 >= 0.85 && !exposed_residual) bn = 512;
+      }
     }
+    if (bn == 512 && d.out != GEMM_OUT_BF16_SWIGLU) return dispatch_layout<192, GEMM_MT_PAIR2>(d, 1, d_status, stream);
     if (bn == 256) return dispatch_layout<256, GEMM_MT_PAIR>(d, 1, d_status, stream);
     if (bn == 192) return dispatch_layout<192, GEMM_MT_PAIR>(d, 1, d_status, stream);
     if (bn == 128) return dispatch_layout<128, GEMM_MT_PAIR>(d, 1, d_status, stream);

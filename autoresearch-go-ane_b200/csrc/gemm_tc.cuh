@@ -34,23 +34,38 @@ static constexpr int GEMM_THREADS = 192;
 // two MMAs, so the shared-memory fill per FLOP drops by a third; its MT*BN accumulator columns leave no
 // room for a second TMEM buffer when BN > 128, so the epilogue of a tile then does not overlap the next
 // tile's main loop -- it pays for long K, not for short K.
-static constexpr int GEMM_MT_PAIR = 4;  // tag value of MT: one 256-row tile per CTA pair
+// MT = GEMM_MT_PAIR / GEMM_MT_PAIR2: a cluster of two CTAs works on one tile through cta_group::2 MMAs
+// (M = 256: 128 rows from each CTA, half of the B tile from each CTA).  PAIR keeps one 128-row sub-tile per
+// CTA and both accumulator sets (short K); PAIR2 gives each CTA two sub-tiles (512 x BN tiles, one
+// accumulator set): the least fill per FLOP, for long K with few columns.
+static constexpr int GEMM_MT_PAIR = 4;
+static constexpr int GEMM_MT_PAIR2 = 5;
+static constexpr uint32_t GEMM_TMARES_BYTES = 4 * 2 * 4096;
+static constexpr uint32_t GEMM_SMEM_LIMIT = 232448u;
 template <int BN, int MT>
 struct GemmCfg {
-  static constexpr bool PAIR = MT == GEMM_MT_PAIR;
-  static constexpr int SUBS = PAIR ? 1 : MT;                      // 128-row accumulator sub-tiles per CTA
-  static constexpr int BM_TILE = PAIR ? 2 * GEMM_BM : GEMM_BM * MT;  // rows of a scheduled tile
-  static constexpr uint32_t A_BYTES = SUBS * GEMM_BM * GEMM_BK * 2;  // per CTA and stage
-  static constexpr uint32_t B_BYTES = (PAIR ? BN / 2 : BN) * GEMM_BK * 2;
+  static constexpr bool PAIR = MT >= GEMM_MT_PAIR;
+  static constexpr int SUBS = MT == GEMM_MT_PAIR ? 1 : (MT == GEMM_MT_PAIR2 ? 2 : MT);  // 128-row sub-tiles per CTA
+  static constexpr int BM_TILE = (PAIR ? 2 : 1) * SUBS * GEMM_BM;       // rows of a scheduled tile
+  static constexpr uint32_t A_BYTES = SUBS * GEMM_BM * GEMM_BK * 2;     // per CTA and stage
+  // a CTA of a pair holds half of the tile's B rows, rounded up to whole 64-column chunks (an MN-major half of
+  // 96 columns is loaded as two chunks, the second half used)
+  static constexpr int B_ROWS = PAIR ? ((BN / 2 + 63) / 64) * 64 : BN;
+  static constexpr uint32_t B_BYTES = B_ROWS * GEMM_BK * 2;
   // Staged output pieces per epilogue warp (a buffer is reused once its TMA store has read it; four buffers
   // measured no faster than two and cost a pipeline stage).
   static constexpr int SBUF = 2;
   static constexpr uint32_t STAGING_BYTES = 4 * SBUF * 4096;  // 4 epilogue warps x SBUF buffers x (32 rows x 128 B)
-  static constexpr int STAGES_FIT = (int)((232448u - 1024u - STAGING_BYTES) / (A_BYTES + B_BYTES));
-  // (a pair keeps room for the residual buffers of EPI_STORE_F32_TMARES: five stages)
-  static constexpr int STAGES_RES = (int)((232448u - 1024u - STAGING_BYTES - 4 * 2 * 4096) / (A_BYTES + B_BYTES));
-  static constexpr int STAGES = PAIR ? (STAGES_RES > 6 ? 6 : STAGES_RES) : (STAGES_FIT > 6 ? 6 : STAGES_FIT);
-  static constexpr uint32_t SMEM_BYTES = STAGES * (A_BYTES + B_BYTES) + STAGING_BYTES + 1024;  // +1024: alignment
+  // Pipeline depth.  Single-CTA kernels take what fits beside the staging buffers and use the TMA-fed residual
+  // epilogue only if its buffers still fit; pair kernels give up stages for them instead.
+  __host__ __device__ static constexpr int stages(bool tma_res) {
+    const uint32_t avail = GEMM_SMEM_LIMIT - 1024u - STAGING_BYTES - ((PAIR && tma_res) ? GEMM_TMARES_BYTES : 0u);
+    const int n = (int)(avail / (A_BYTES + B_BYTES));
+    return n > 6 ? 6 : n;
+  }
+  __host__ __device__ static constexpr uint32_t smem_bytes(bool tma_res) {  // +1024: alignment
+    return stages(tma_res) * (A_BYTES + B_BYTES) + STAGING_BYTES + 1024 + (tma_res ? GEMM_TMARES_BYTES : 0u);
+  }
   static constexpr int ACC_COLS = SUBS * BN;                     // one accumulator set
   static constexpr int NBUF = (2 * ACC_COLS <= 512) ? 2 : 1;     // TMEM accumulator sets
   static constexpr uint32_t TMEM_COLS = (NBUF * ACC_COLS <= 256) ? 256 : 512;
@@ -87,13 +102,11 @@ enum EpiKind : int {
   EPI_STORE_BF16_ROPE = 4,
   // C(fp32) = alpha*acc + s1*res1 with the residual pieces fetched by TMA (two 32-row x 128-byte buffers
   // per epilogue warp, two pieces ahead) instead of by per-thread row loads: the residual read then costs
-  // one bulk copy per piece.  Needs 32 KB of shared memory beyond GemmCfg::SMEM_BYTES.
+  // one bulk copy per piece.  Needs GEMM_TMARES_BYTES of shared memory beside the pipeline stages.
   EPI_STORE_F32_TMARES = 5,
   // EPI_STORE_BF16 that also writes the accumulator of each row's target column in fp32.
   EPI_STORE_BF16_TGT = 6,
 };
-static constexpr uint32_t GEMM_TMARES_BYTES = 4 * 2 * 4096;
-
 struct EpiParams {
   float alpha;
   const float* res1;  // optional fp32 [M, ldres]
@@ -172,12 +185,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD, EpiParams epi, int M,
                int N, int K, int split_k, int* status) {
   using Cfg = GemmCfg<BN, MT>;
-  constexpr int STAGES = Cfg::STAGES;
+  constexpr int STAGES = Cfg::stages(EPI == EPI_STORE_F32_TMARES);
   constexpr int BM = Cfg::BM_TILE, BK = GEMM_BK;
   constexpr int NBUF = Cfg::NBUF;
   constexpr bool PAIR = Cfg::PAIR;
   constexpr int SUBS = Cfg::SUBS;
-  static_assert(!PAIR || (BN % 32 == 0 && (!B_MN || BN % 128 == 0)), "a CTA of a pair loads whole 64-column chunks");
+  static_assert(!PAIR || BN % 32 == 0, "each CTA of a pair supplies BN/2 columns of B");
+  // bytes one CTA's loads of a stage deliver
+  constexpr uint32_t STAGE_TX = Cfg::A_BYTES + (PAIR ? (B_MN ? Cfg::B_BYTES : (uint32_t)(BN / 2) * BK * 2) : Cfg::B_BYTES);
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[STAGES];
@@ -202,7 +217,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // 0 = the CTA that issues the MMAs
   const int sched_id = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int sched_n = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
-  const int row_off = PAIR ? (int)rank * GEMM_BM : 0;   // this CTA's rows inside the tile
+  // rows of this CTA's sub-tile i inside the tile: a pair's MMA i covers 256 consecutive rows, 128 per CTA
+  auto sub_row = [&](int i) { return PAIR ? i * 2 * GEMM_BM + (int)rank * GEMM_BM : i * GEMM_BM; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -260,25 +276,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if constexpr (PAIR) {
             // both CTAs' bytes complete on the leader's barrier, which expects the sum
             const uint32_t full = map_to_cta(smem_u32(&bar_full[stage]), 0);
-            if (rank == 0) mbar_expect_tx(smem_u32(&bar_full[stage]), 2 * (Cfg::A_BYTES + Cfg::B_BYTES));
-            const int m0 = tm * BM + row_off, n0 = tn * BN + (int)rank * (BN / 2);
-            if constexpr (!A_MN) {
-              tma_load_2d_pair(sa, &tmA, full, kb * BK, m0);
-            } else {
+            if (rank == 0) mbar_expect_tx(smem_u32(&bar_full[stage]), 2 * STAGE_TX);
+            const int n0 = tn * BN + (int)rank * (BN / 2);
 #pragma unroll
-              for (int j = 0; j < GEMM_BM / 64; ++j)
-                tma_load_2d_pair(sa + j * (64 * BK * 2), &tmA, full, m0 + j * 64, kb * BK);
+            for (int i = 0; i < SUBS; ++i) {
+              const int m0 = tm * BM + sub_row(i);
+              const uint32_t sai = sa + i * (GEMM_BM * BK * 2);
+              if constexpr (!A_MN) {
+                tma_load_2d_pair(sai, &tmA, full, kb * BK, m0);
+              } else {
+#pragma unroll
+                for (int j = 0; j < GEMM_BM / 64; ++j)
+                  tma_load_2d_pair(sai + j * (64 * BK * 2), &tmA, full, m0 + j * 64, kb * BK);
+              }
             }
             if constexpr (!B_MN) {
               tma_load_2d_pair(sb, &tmB, full, kb * BK, n0);  // box of BN/2 rows
             } else {
 #pragma unroll
-              for (int j = 0; j < BN / 128; ++j)
+              for (int j = 0; j < Cfg::B_ROWS / 64; ++j)  // the last chunk may reach past this CTA's half: unused columns
                 tma_load_2d_pair(sb + j * (64 * BK * 2), &tmB, full, n0 + j * 64, kb * BK);
             }
           } else {
           const uint32_t full = smem_u32(&bar_full[stage]);
-          mbar_expect_tx(full, Cfg::A_BYTES + Cfg::B_BYTES);
+          mbar_expect_tx(full, STAGE_TX);
           if constexpr (!A_MN) {
 #pragma unroll
             for (int i = 0; i < SUBS; ++i)
@@ -341,7 +362,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               const uint32_t sai = sa + i * (GEMM_BM * BK * 2);
               if constexpr (!A_MN) adesc = make_smem_desc(sai + k * 32, 16, 1024);
               else                 adesc = make_smem_desc(sai + k * 2048, 64 * BK * 2, 1024);
-              if constexpr (PAIR) tc_mma_bf16_pair(tmem_d, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+              if constexpr (PAIR) tc_mma_bf16_pair(tmem_d + (uint32_t)(i * BN), adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
               else tc_mma_bf16(tmem_d + (uint32_t)(i * BN), adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
             }
           }
@@ -398,7 +419,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
       };
-      prefetch_first(tm * BM + row_off + lane_group * 32 + lane);
+      prefetch_first(tm * BM + sub_row(0) + lane_group * 32 + lane);
       // Residual piece `piece` (counted over the whole kernel) of the current (tile, sub): same validity test as
       // the consuming loop, so every issued piece is consumed.
       uint32_t res_issued = res_uses;
@@ -416,8 +437,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       };
       if constexpr (EPI == EPI_STORE_F32_TMARES) {  // first two pieces of sub-tile 0, while the MMAs still run
-        issue_res(tm * BM + row_off + lane_group * 32, tn * BN);
-        issue_res(tm * BM + row_off + lane_group * 32, tn * BN + CW);
+        issue_res(tm * BM + sub_row(0) + lane_group * 32, tn * BN);
+        issue_res(tm * BM + sub_row(0) + lane_group * 32, tn * BN + CW);
       }
       if (!mbar_wait(smem_u32(&bar_tfull[buf]), tphase, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
         ok = false;
@@ -426,7 +447,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_after();
 #pragma unroll 1
       for (int sub = 0; sub < SUBS; ++sub) {
-      const int m_warp = tm * BM + row_off + sub * GEMM_BM + lane_group * 32;
+      const int m_warp = tm * BM + sub_row(sub) + lane_group * 32;
       const int m = m_warp + lane;
       if (sub > 0) {
         prefetch_first(m);
