@@ -15,6 +15,8 @@ struct NcclId {
 typedef int (*GetUniqueIdFn)(NcclId*);
 typedef int (*CommInitRankFn)(void**, int, NcclId, int);
 typedef int (*AllReduceFn)(const void*, void*, size_t, int, int, void*, cudaStream_t);
+typedef int (*ReduceScatterFn)(const void*, void*, size_t, int, int, void*, cudaStream_t);
+typedef int (*AllGatherFn)(const void*, void*, size_t, int, void*, cudaStream_t);
 typedef int (*CommDestroyFn)(void*);
 typedef const char* (*GetErrorStringFn)(int);
 
@@ -23,6 +25,8 @@ struct NcclApi {
   GetUniqueIdFn get_unique_id = nullptr;
   CommInitRankFn comm_init_rank = nullptr;
   AllReduceFn all_reduce = nullptr;
+  ReduceScatterFn reduce_scatter = nullptr;
+  AllGatherFn all_gather = nullptr;
   CommDestroyFn comm_destroy = nullptr;
   GetErrorStringFn get_error_string = nullptr;
   std::string err;
@@ -44,9 +48,12 @@ NcclApi* nccl() {
     api.get_unique_id = (GetUniqueIdFn)dlsym(api.handle, "ncclGetUniqueId");
     api.comm_init_rank = (CommInitRankFn)dlsym(api.handle, "ncclCommInitRank");
     api.all_reduce = (AllReduceFn)dlsym(api.handle, "ncclAllReduce");
+    api.reduce_scatter = (ReduceScatterFn)dlsym(api.handle, "ncclReduceScatter");
+    api.all_gather = (AllGatherFn)dlsym(api.handle, "ncclAllGather");
     api.comm_destroy = (CommDestroyFn)dlsym(api.handle, "ncclCommDestroy");
     api.get_error_string = (GetErrorStringFn)dlsym(api.handle, "ncclGetErrorString");
-    if (!api.get_unique_id || !api.comm_init_rank || !api.all_reduce || !api.comm_destroy)
+    if (!api.get_unique_id || !api.comm_init_rank || !api.all_reduce || !api.comm_destroy || !api.reduce_scatter ||
+        !api.all_gather)
       api.err = "NCCL symbols missing";
   });
   return &api;
@@ -54,6 +61,8 @@ NcclApi* nccl() {
 
 constexpr int kNcclFloat = 7;  // ncclFloat32
 constexpr int kNcclSum = 0;    // ncclSum
+constexpr int kNcclDouble = 8; // ncclFloat64
+constexpr int kNcclInt8 = 0;   // ncclInt8
 // ~32 MiB buckets: large enough to run at link bandwidth, small enough to pipeline.
 constexpr size_t kBucketElems = 8u << 20;
 
@@ -111,6 +120,40 @@ int DataParallel::all_reduce_sum(float* buf, size_t n, cudaStream_t stream) {
       err_ = std::string("ncclAllReduce: ") + (a->get_error_string ? a->get_error_string(r) : "error");
       return -1;
     }
+  }
+  return 0;
+}
+
+int DataParallel::all_reduce_sum_f64(double* buf, size_t n, cudaStream_t stream) {
+  if (!comm_ || n == 0) return 0;
+  NcclApi* a = nccl();
+  int r = a->all_reduce(buf, buf, n, kNcclDouble, kNcclSum, comm_, stream);
+  if (r != 0) {
+    err_ = std::string("ncclAllReduce: ") + (a->get_error_string ? a->get_error_string(r) : "error");
+    return -1;
+  }
+  return 0;
+}
+
+int DataParallel::reduce_scatter_sum(float* buf, size_t n_per_rank, cudaStream_t stream) {
+  if (!comm_ || n_per_rank == 0) return 0;
+  NcclApi* a = nccl();
+  int r = a->reduce_scatter(buf, buf + (size_t)rank_ * n_per_rank, n_per_rank, kNcclFloat, kNcclSum, comm_, stream);
+  if (r != 0) {
+    err_ = std::string("ncclReduceScatter: ") + (a->get_error_string ? a->get_error_string(r) : "error");
+    return -1;
+  }
+  return 0;
+}
+
+int DataParallel::all_gather_bytes(void* buf, size_t bytes_per_rank, cudaStream_t stream) {
+  if (!comm_ || bytes_per_rank == 0) return 0;
+  NcclApi* a = nccl();
+  int r = a->all_gather(static_cast<char*>(buf) + (size_t)rank_ * bytes_per_rank, buf, bytes_per_rank, kNcclInt8, comm_,
+                        stream);
+  if (r != 0) {
+    err_ = std::string("ncclAllGather: ") + (a->get_error_string ? a->get_error_string(r) : "error");
+    return -1;
   }
   return 0;
 }

@@ -18,6 +18,14 @@ class DataParallel {
   bool active() const { return comm_ != nullptr; }
   // In-place sum over ranks, issued in buckets on `stream`.
   int all_reduce_sum(float* buf, size_t n, cudaStream_t stream);
+  // Sum of n doubles over ranks, in place (the squared gradient norm of a sharded optimizer).
+  int all_reduce_sum_f64(double* buf, size_t n, cudaStream_t stream);
+  // In-place reduce-scatter: buf holds world * n_per_rank floats; afterwards rank r's slice
+  // [r * n_per_rank, (r + 1) * n_per_rank) holds the sum over ranks (the other slices are unspecified).
+  int reduce_scatter_sum(float* buf, size_t n_per_rank, cudaStream_t stream);
+  // In-place all-gather: rank r contributes bytes [r * bytes_per_rank, (r + 1) * bytes_per_rank) of buf.
+  int all_gather_bytes(void* buf, size_t bytes_per_rank, cudaStream_t stream);
+  int rank() const { return rank_; }
   void shutdown();
   const char* last_error() const { return err_.c_str(); }
   int world() const { return world_; }

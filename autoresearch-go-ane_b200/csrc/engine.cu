@@ -304,6 +304,25 @@ class EngineT final : public EngineBase {
   DataParallel dp_;
   cudaStream_t comm_stream_ = nullptr;   // gradient all-reduce, overlapped with backward
   cudaEvent_t ev_bucket_ = nullptr, ev_comm_done_ = nullptr;
+  // Sharded optimizer (world_size > 1): the layer matrices' gradients are reduce-scattered per bucket of
+  // bucket_layers_ layers, each rank updates its slice of every bucket (fp32 weights and Adam moments of the
+  // other slices are not touched), and the updated fp32 weights are all-gathered bucket by bucket on the
+  // communication stream while the next pass already runs; a layer waits for its bucket.  Embedding, norm
+  // weights and scalars stay replicated (all-reduce + full update): the embedding is read in fp32.
+  bool shard_opt_ = false;
+  int bucket_layers_ = 1;
+  std::vector<cudaEvent_t> ev_gather_;    // per bucket: weights (and bf16 copies) complete on this rank
+  cudaEvent_t ev_opt_done_ = nullptr, ev_norm_in_ = nullptr, ev_norm_out_ = nullptr;
+  bool gather_pending_ = false;
+  bool moments_current_ = true;           // the non-owned slices of the Adam moments match their owners'
+  int n_buckets() const { return (L_ + bucket_layers_ - 1) / bucket_layers_; }
+  size_t bucket_lo(int b) const { return s_qkv_[b * bucket_layers_].off; }
+  size_t bucket_hi(int b) const { return (b + 1) * bucket_layers_ < L_ ? s_qkv_[(b + 1) * bucket_layers_].off : r_mat1_; }
+  size_t bucket_slice(int b) const { return (bucket_hi(b) - bucket_lo(b)) / (size_t)o_.world_size; }
+  void wait_bucket(int b) { if (gather_pending_) cudaStreamWaitEvent(stream_, ev_gather_[b], 0); }
+  void wait_all_buckets() { if (gather_pending_) cudaStreamWaitEvent(stream_, ev_gather_.back(), 0); }
+  int reduce_bucket(int b);
+  int gather_moments();
   bool overlap_reduce_ = false;           // this micro-step is the last before the optimizer update
   size_t reduced_lo_ = 0;                 // G_[reduced_lo_, r_mat1_) has already been handed to the all-reduce
   std::vector<void*> allocs_;
@@ -318,6 +337,7 @@ class EngineT final : public EngineBase {
 template <typename T>
 void EngineT<T>::destroy() {
   if (stream_) cudaStreamSynchronize(stream_);
+  if (comm_stream_) cudaStreamSynchronize(comm_stream_);  // weight gathers of the last update may still run
   dp_.shutdown();
   for (void* p : allocs_) cudaFree(p);
   allocs_.clear();
@@ -355,9 +375,19 @@ void EngineT<T>::destroy() {
       e = nullptr;
     }
   if (comm_stream_) {
+    cudaStreamSynchronize(comm_stream_);
     cudaStreamDestroy(comm_stream_);
     comm_stream_ = nullptr;
   }
+  for (cudaEvent_t* ev : {&ev_opt_done_, &ev_norm_in_, &ev_norm_out_})
+    if (*ev) {
+      cudaEventDestroy(*ev);
+      *ev = nullptr;
+    }
+  for (auto& ev : ev_gather_)
+    if (ev) cudaEventDestroy(ev);
+  ev_gather_.clear();
+  gather_pending_ = false;
   if (stream_) {
     cudaStreamDestroy(stream_);
     stream_ = nullptr;
@@ -634,6 +664,17 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
       return rc;
     if ((rc = cuda_check(cudaEventCreateWithFlags(&ev_bucket_, cudaEventDisableTiming), "event")) != 0) return rc;
     if ((rc = cuda_check(cudaEventCreateWithFlags(&ev_comm_done_, cudaEventDisableTiming), "event")) != 0) return rc;
+    const char* e = getenv("ANE_B200_DP_LAYERS_PER_BUCKET");  // layers per gradient bucket (default 1)
+    bucket_layers_ = e && atoi(e) > 0 ? atoi(e) : 1;
+    const char* se = getenv("ANE_B200_DP_SHARD_OPTIMIZER");   // 0: replicated update on every rank
+    shard_opt_ = !(se && se[0] == '0');
+    for (int b = 0; b < n_buckets(); ++b)  // slices must keep 16-byte alignment
+      if ((bucket_hi(b) - bucket_lo(b)) % ((size_t)o_.world_size * 4) != 0) shard_opt_ = false;
+    for (cudaEvent_t* ev : {&ev_opt_done_, &ev_norm_in_, &ev_norm_out_})
+      if ((rc = cuda_check(cudaEventCreateWithFlags(ev, cudaEventDisableTiming), "event")) != 0) return rc;
+    ev_gather_.assign(n_buckets(), nullptr);
+    for (auto& ev : ev_gather_)
+      if ((rc = cuda_check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "event")) != 0) return rc;
   }
   if ((rc = cuda_check(cudaStreamSynchronize(stream_), "open sync")) != 0) return rc;
   t_open_ns_ = now_ns();
@@ -644,6 +685,7 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
 template <typename T>
 int EngineT<T>::refresh_shadow() {
   if constexpr (!kIsF32) {
+    wait_all_buckets();
     count_launch();
     cast_f32_to_bf16(P_, Sh_, shadow_n_, stream_);
   }
@@ -691,6 +733,7 @@ int EngineT<T>::forward(const uint16_t* d_tok, int B, int Tl, int pos0) {
     const float* w_ffn = isN_ ? nullptr : P_ + s_rms_ffn_[l].off;
     const float* rl = isN_ ? P_ + s_resid_.off + l : d_one_;
     const float* xl = isN_ ? P_ + s_x0l_.off + l : nullptr;
+    if (l % bucket_layers_ == 0) wait_bucket(l / bucket_layers_);
     count_launch();
     rmsnorm_forward<T>(xs_[l], w_att, a.xn, a.rstd1, M, D_, stream_);
     // llama arch, bf16, head_dim 64: the rotation of q and k happens on the fp32 accumulators in the epilogue
@@ -1063,21 +1106,14 @@ int EngineT<T>::backward_layers(int B) {
     }
     if (post_fix) cast_to_t(dprev, dcur_t_[cur ^ 1], MD);
     (void)dprev_t;
-    // ANE_B200_DP_LAYERS_PER_BUCKET groups that many layers into one all-reduce (default 1).
-    static const int layers_per_bucket = [] {
-      const char* e = getenv("ANE_B200_DP_LAYERS_PER_BUCKET");
-      const int v = e ? atoi(e) : 1;
-      return v > 0 ? v : 1;
-    }();
-    if (overlap_reduce_ && l % layers_per_bucket == 0) {
-      // The matrix gradients of layers l.. are final: hand them to the all-reduce on the communication
-      // stream while the layers below are still being differentiated.
-      const size_t lo = s_qkv_[l].off, hi = reduced_lo_;
+    if (overlap_reduce_ && l % bucket_layers_ == 0) {
+      // The matrix gradients of this bucket's layers are final: hand them to the reduction on the
+      // communication stream while the layers below are still being differentiated.
       cudaEventRecord(ev_bucket_, stream_);
       cudaStreamWaitEvent(comm_stream_, ev_bucket_, 0);
       if (dws != stream_) cudaStreamWaitEvent(comm_stream_, ev_dw_done_[l], 0);
-      if (dp_.all_reduce_sum(G_ + lo, hi - lo, comm_stream_) != 0) return fail(ANE_ERR_NCCL, dp_.last_error());
-      reduced_lo_ = lo;
+      if ((rc = reduce_bucket(l / bucket_layers_)) != 0) return rc;
+      reduced_lo_ = s_qkv_[l].off;
     }
     cur ^= 1;
   }
@@ -1119,6 +1155,42 @@ int EngineT<T>::backward_layers(int B) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// Gradient exchange of one bucket of layers on the communication stream: all-reduce, or (sharded optimizer)
+// reduce-scatter, after which the slices this rank does not own are cleared so that later micro-steps
+// accumulate onto zeros (the update clears the owned slice).
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+int EngineT<T>::reduce_bucket(int b) {
+  const size_t lo = bucket_lo(b), hi = bucket_hi(b);
+  if (!shard_opt_) {
+    if (dp_.all_reduce_sum(G_ + lo, hi - lo, comm_stream_) != 0) return fail(ANE_ERR_NCCL, dp_.last_error());
+    return 0;
+  }
+  const size_t sl = bucket_slice(b), mine = lo + (size_t)o_.rank * sl;
+  if (dp_.reduce_scatter_sum(G_ + lo, sl, comm_stream_) != 0) return fail(ANE_ERR_NCCL, dp_.last_error());
+  if (mine > lo) cudaMemsetAsync(G_ + lo, 0, (mine - lo) * sizeof(float), comm_stream_);
+  if (mine + sl < hi) cudaMemsetAsync(G_ + mine + sl, 0, (hi - mine - sl) * sizeof(float), comm_stream_);
+  return 0;
+}
+
+// Brings the Adam moments of every slice to every rank (collective; after it the moments are current until the
+// next update).
+template <typename T>
+int EngineT<T>::gather_moments() {
+  if (!dp_.active() || !shard_opt_ || moments_current_) return 0;
+  cudaEventRecord(ev_bucket_, stream_);
+  cudaStreamWaitEvent(comm_stream_, ev_bucket_, 0);
+  for (int b = 0; b < n_buckets(); ++b)
+    for (float* base : {Mo_, Vo_})
+      if (dp_.all_gather_bytes(base + bucket_lo(b), bucket_slice(b) * sizeof(float), comm_stream_) != 0)
+        return fail(ANE_ERR_NCCL, dp_.last_error());
+  cudaEventRecord(ev_comm_done_, comm_stream_);
+  cudaStreamWaitEvent(stream_, ev_comm_done_, 0);
+  moments_current_ = true;
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
 // Optimizer update (ane/engine.go:646-682).
 // ------------------------------------------------------------------------------------------------
 template <typename T>
@@ -1126,21 +1198,22 @@ int EngineT<T>::do_flush() {
   if (pending_seqs_ == 0) return 0;
   int rc;
   uint32_t global_pending = pending_seqs_ * (uint32_t)o_.world_size;
+  const bool shard = dp_.active() && shard_opt_;
   if (dp_.active()) {
-    if (overlap_reduce_) {
-      // matrices were reduced bucket by bucket during backward; the rest (embedding, norms, ...) follows
-      cudaEventRecord(ev_bucket_, stream_);
-      cudaStreamWaitEvent(comm_stream_, ev_bucket_, 0);
-      if (reduced_lo_ > r_mat0_ && dp_.all_reduce_sum(G_ + r_mat0_, reduced_lo_ - r_mat0_, comm_stream_) != 0)
-        return fail(ANE_ERR_NCCL, dp_.last_error());
-      if (dp_.all_reduce_sum(G_ + r_mat1_, n_params_ - r_mat1_, comm_stream_) != 0)
-        return fail(ANE_ERR_NCCL, dp_.last_error());
-      cudaEventRecord(ev_comm_done_, comm_stream_);
-      cudaStreamWaitEvent(stream_, ev_comm_done_, 0);
-      overlap_reduce_ = false;
-    } else if ((rc = dp_.all_reduce_sum(G_, n_params_, stream_)) != 0) {
+    // matrices not yet reduced during backward (all of them when the update was not foreseen), bucket by
+    // bucket from the top; then the rest (embedding, norms, ...)
+    if (!overlap_reduce_) reduced_lo_ = r_mat1_;
+    cudaEventRecord(ev_bucket_, stream_);
+    cudaStreamWaitEvent(comm_stream_, ev_bucket_, 0);
+    if (dw_overlap_) cudaStreamWaitEvent(comm_stream_, ev_dw_done_[0], 0);
+    for (int b = n_buckets() - 1; b >= 0; --b)
+      if (bucket_lo(b) < reduced_lo_ && (rc = reduce_bucket(b)) != 0) return rc;
+    reduced_lo_ = r_mat0_;
+    if (dp_.all_reduce_sum(G_ + r_mat1_, n_params_ - r_mat1_, comm_stream_) != 0)
       return fail(ANE_ERR_NCCL, dp_.last_error());
-    }
+    cudaEventRecord(ev_comm_done_, comm_stream_);
+    cudaStreamWaitEvent(stream_, ev_comm_done_, 0);
+    overlap_reduce_ = false;
   }
   cudaEventRecord(ev_adam0_, stream_);
   float pre_scale = (float)(1.0 / (double)global_pending);
@@ -1148,8 +1221,22 @@ int EngineT<T>::do_flush() {
   cudaMemsetAsync(d_acc_, 0, sizeof(double) * 2, stream_);
   if (o_.grad_clip > 0) {
     // layer tensors + embedding (+ value embeddings and gates); the llama arch clips over every parameter.
-    count_launch(2);
-    sumsq_accumulate(G_ + r_mat0_, r_mat1_ - r_mat0_, pre_scale, d_acc_, stream_);
+    if (shard) {
+      // this rank's slices of the matrices, summed over ranks; the replicated groups are added afterwards
+      for (int b = 0; b < n_buckets(); ++b) {
+        count_launch();
+        sumsq_accumulate(G_ + bucket_lo(b) + (size_t)o_.rank * bucket_slice(b), bucket_slice(b), pre_scale, d_acc_, stream_);
+      }
+      cudaEventRecord(ev_norm_in_, stream_);
+      cudaStreamWaitEvent(comm_stream_, ev_norm_in_, 0);
+      if (dp_.all_reduce_sum_f64(d_acc_, 1, comm_stream_) != 0) return fail(ANE_ERR_NCCL, dp_.last_error());
+      cudaEventRecord(ev_norm_out_, comm_stream_);
+      cudaStreamWaitEvent(stream_, ev_norm_out_, 0);
+    } else {
+      count_launch();
+      sumsq_accumulate(G_ + r_mat0_, r_mat1_ - r_mat0_, pre_scale, d_acc_, stream_);
+    }
+    count_launch();
     sumsq_accumulate(G_ + s_embed_.off, r_veg1_ - s_embed_.off, pre_scale, d_acc_, stream_);
     if (!isN_) {
       count_launch();
@@ -1177,7 +1264,12 @@ int EngineT<T>::do_flush() {
     count_launch();
     adam_update(P_ + off, G_ + off, Mo_ + off, Vo_ + off, (shadow && !kIsF32) ? Sh_ + off : nullptr, n, h, gs, stream_);
   };
-  run(r_mat0_, r_mat1_ - r_mat0_, hyper(lr_, b1, b2, o_.weight_decay), clip_s, true);
+  if (shard) {
+    for (int b = 0; b < n_buckets(); ++b)
+      run(bucket_lo(b) + (size_t)o_.rank * bucket_slice(b), bucket_slice(b), hyper(lr_, b1, b2, o_.weight_decay), clip_s, true);
+  } else {
+    run(r_mat0_, r_mat1_ - r_mat0_, hyper(lr_, b1, b2, o_.weight_decay), clip_s, true);
+  }
   if (isN_) run(s_smear_gate_.off, s_embed_.off - s_smear_gate_.off, hyper(lr_, b1, b2, o_.weight_decay), pre_s, true);
   run(s_embed_.off, r_ve0_ - s_embed_.off, hyper(embed_lr_, b1, b2, 0.f), clip_s, true);
   run(r_ve0_, r_ve1_ - r_ve0_, hyper(embed_lr_, b1, b2, 0.f), clip_s, false);
@@ -1188,6 +1280,22 @@ int EngineT<T>::do_flush() {
     run(r_lam0_, r_lam1_ - r_lam0_, hyper(lambda_lr_, o_.lambda_beta1, o_.lambda_beta2, 0.f), pre_s, false);
   }
   cudaEventRecord(ev_adam1_, stream_);
+  if (shard) {
+    // every rank's updated slices -> everyone, in the order the next pass reads them
+    cudaEventRecord(ev_opt_done_, stream_);
+    cudaStreamWaitEvent(comm_stream_, ev_opt_done_, 0);
+    for (int b = 0; b < n_buckets(); ++b) {
+      if (dp_.all_gather_bytes(P_ + bucket_lo(b), bucket_slice(b) * sizeof(float), comm_stream_) != 0)
+        return fail(ANE_ERR_NCCL, dp_.last_error());
+      if constexpr (!kIsF32) {
+        count_launch();
+        cast_f32_to_bf16(P_ + bucket_lo(b), Sh_ + bucket_lo(b), bucket_hi(b) - bucket_lo(b), comm_stream_);
+      }
+      cudaEventRecord(ev_gather_[b], comm_stream_);
+    }
+    gather_pending_ = true;
+    moments_current_ = false;
+  }
   pending_seqs_ = 0;
   micro_steps_ = 0;
   st_.pending_steps = 0;
@@ -1199,6 +1307,7 @@ template <typename T>
 int EngineT<T>::flush(double* refresh_ms) {
   int rc = do_flush();
   if (rc != 0) return rc;
+  wait_all_buckets();
   if ((rc = cuda_check(cudaStreamSynchronize(stream_), "flush sync")) != 0) return rc;
   if (refresh_ms) *refresh_ms = 0.0;
   return 0;
@@ -1508,6 +1617,7 @@ int EngineT<T>::import_tensor(uint32_t id, uint32_t layer, uint32_t which, const
   if (n != s.n) return fail(ANE_ERR_ARG, "storiesane import: element count mismatch");
   float* base = which == 0 ? P_ : which == 1 ? G_ : which == 2 ? Mo_ : Vo_;
   int rc;
+  wait_all_buckets();
   if (!isN_ && (id == ANE_T_W1 || id == ANE_T_W3)) {
     // W1 and W3 share the fused W13 matrix in blocks of 32 rows: [W1 rows 0..31 | W3 rows 0..31 | W1 rows 32..63 | ...]
     const size_t blk = (size_t)32 * D_ * sizeof(float);
@@ -1538,6 +1648,10 @@ int EngineT<T>::export_tensor(uint32_t id, uint32_t layer, uint32_t which, float
   if (n == 0) return 0;
   const float* base = which == 0 ? P_ : which == 1 ? G_ : which == 2 ? Mo_ : Vo_;
   int rc;
+  wait_all_buckets();
+  // Adam moments of the layer matrices live on the rank that owns the slice: reading them is a collective
+  // call (every rank must export), which brings all slices up to date once per update.
+  if (which >= 2 && s.off >= r_mat0_ && s.off < r_mat1_ && (rc = gather_moments()) != 0) return rc;
   if (!isN_ && (id == ANE_T_W1 || id == ANE_T_W3)) {  // de-interleave the 32-row blocks (see import_tensor)
     const size_t blk = (size_t)32 * D_ * sizeof(float);
     const float* src = base + s_w13_[layer].off + (id == ANE_T_W3 ? (size_t)32 * D_ : 0);
@@ -1684,6 +1798,7 @@ int EngineT<T>::timer_begin() {
 template <typename T>
 int EngineT<T>::timer_end(float* ms) {
   if (!ev_t0_) return fail(ANE_ERR_STATE, "storiesane timer: end without begin");
+  wait_all_buckets();
   int rc = cuda_check(cudaEventRecord(ev_t1_, stream_), "timer end");
   if (rc) return rc;
   if ((rc = cuda_check(cudaEventSynchronize(ev_t1_), "timer sync")) != 0) return rc;
