@@ -222,6 +222,8 @@ enum {
 int64_t ane_tensor_size(ane_engine* e, uint32_t tensor_id, uint32_t layer); /* elements; 0 if absent; <0 error */
 int32_t ane_import_tensor(ane_engine* e, uint32_t tensor_id, uint32_t layer, uint32_t which, const float* buf,
                           uint64_t n);
+/* With world_size > 1 the Adam moments (which 2, 3) of the layer matrices are kept by the rank that owns each
+ * slice: exporting them is a collective call (every rank must make it); weights and gradients export locally. */
 int32_t ane_export_tensor(ane_engine* e, uint32_t tensor_id, uint32_t layer, uint32_t which, float* buf, uint64_t n);
 
 /* Activation taps of the last step, reference layout [n_seq][channels][seq] (ane/train_full.go:12-37). */
