@@ -258,10 +258,11 @@ def run_ours(args):
                 "frac": round(achieved / tf_sust, 4), "traffic": None, "peak_source": f"bf16_tflops_sustained ({src})",
                 "kernel": "gemm_tc_kernel (tcgen05 GEMM, all shapes of one step)", "gemm_launches_per_step": gemm_launches,
                 "gemm_ms_per_step": round(gemm_ms, 3),
-                # DRAM traffic of two captured launches (ncu --set full, profiles/gemm_tc_kernel_*.md);
+                # DRAM traffic of three captured launches (ncu --set full, profiles/gemm_tc_kernel_*.md);
                 # the aggregate over all 150 launches of a step was not captured, hence traffic = null.
-                "traffic_cases": {"classifier_fwd_8192x32000x768": {"dram_bytes": 532471552, "algorithmic_bytes": 586022912},
-                                  "w2_dx_8192x768x4096": {"dram_bytes": 121922048, "algorithmic_bytes": 98566144}},
+                "traffic_cases": {"classifier_fwd_8192x32000x768": {"dram_bytes": 532205568, "algorithmic_bytes": 586022912},
+                                  "w2_dx_8192x768x4096": {"dram_bytes": 78061312, "algorithmic_bytes": 98566144},
+                                  "qkv_fwd_8192x2304x768": {"dram_bytes": 16279296, "algorithmic_bytes": 53870592}},
                 "step_frac_of_burst_peak": round(flops_per_token * tokens_per_step / world / (ms_per_step * 1e-3) / 1e12 / tf_burst, 4)}
 
     # ---- EvalLogits latency (the second half of the headline metric): one 256-token window per call,
