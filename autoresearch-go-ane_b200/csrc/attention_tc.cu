@@ -465,25 +465,27 @@ bool ensure_attrs() {
 
 bool attention_tc_supported(int hd) { return hd == HD; }
 
-void attention_forward_tc(const bf16* qkv, bf16* out, float* lse, int B, int seq, int H, int KV, float scale,
+void attention_forward_tc(const bf16* qkv, bf16* out, bf16* out_lo, float* lse, int B, int seq, int H, int KV, float scale,
                           int* d_status, cudaStream_t s) {
   if (B <= 0 || seq <= 0 || !ensure_attrs()) return;
   static const bool legacy = getenv("ANE_B200_ATT_LEGACY") != nullptr;
   if (!legacy && attention_tcgen05_supported(HD, seq) &&
-      attention_forward_tcgen05(qkv, out, lse, B, seq, H, KV, scale, d_status, s) == 0)
+      attention_forward_tcgen05(qkv, out, out_lo, lse, B, seq, H, KV, scale, d_status, s) == 0)
     return;
+  // the mma.sync kernels keep no rounding remainder of O: an all-zero one leaves the backward's delta as it was
+  if (out_lo) cudaMemsetAsync(out_lo, 0, sizeof(bf16) * (size_t)B * seq * H * HD, s);
   dim3 grid((seq + BR - 1) / BR, B * H);
   attention_fwd_tc_kernel<<<grid, ATT_THREADS, kFwdSmem, s>>>(qkv, out, lse, seq, H, KV, scale);
 }
 
-void attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* d_out, const float* lse, float* delta,
+void attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* out_lo, const bf16* d_out, const float* lse, float* delta,
                            bf16* dqkv, const float* cosb, const float* sinb, int B, int seq, int H, int KV,
                            float scale, int* d_status, cudaStream_t s) {
   if (B <= 0 || seq <= 0 || !ensure_attrs()) return;
   // ANE_B200_ATT_LEGACY=1 keeps the mma.sync kernels (A/B measurements).
   static const bool legacy = getenv("ANE_B200_ATT_LEGACY") != nullptr;
   if (!legacy && attention_tcgen05_supported(HD, seq) &&
-      attention_backward_tcgen05(qkv, out, d_out, lse, delta, dqkv, cosb, sinb, B, seq, H, KV, scale, d_status, s) == 0)
+      attention_backward_tcgen05(qkv, out, out_lo, d_out, lse, delta, dqkv, cosb, sinb, B, seq, H, KV, scale, d_status, s) == 0)
     return;
   const long long warps = (long long)B * seq * H;
   attention_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>(d_out, out, delta, B, seq, H);

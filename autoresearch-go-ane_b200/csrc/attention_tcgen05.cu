@@ -46,6 +46,7 @@ struct Attn5Params {
   int T, H, KV;
   float scale;
   int* status;
+  int o_lo;            // dQ: tm_o_lo holds bf16(O - bf16(O)) from the forward; delta = rowsum(dO * (O + O_lo))
 };
 
 // Instruction descriptor: bf16 x bf16 -> fp32, M = 128, N = 64; operand majors selectable.
@@ -83,7 +84,8 @@ template <int MODE>
 __global__ void __launch_bounds__(A5_THREADS, 2)
 attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_constant__ CUtensorMap tm_qkv_x,
                  const __grid_constant__ CUtensorMap tm_do_r, const __grid_constant__ CUtensorMap tm_do_x,
-                 const __grid_constant__ CUtensorMap tm_o_r, const __grid_constant__ CUtensorMap tm_dqkv,
+                 const __grid_constant__ CUtensorMap tm_o_r, const __grid_constant__ CUtensorMap tm_o_lo,
+                 const __grid_constant__ CUtensorMap tm_dqkv,
                  const __grid_constant__ CUtensorMap tm_cos, const __grid_constant__ CUtensorMap tm_sin, Attn5Params p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[2];
@@ -161,7 +163,7 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
     pdl_wait();  // everything read below was written by earlier kernels
     // The first loads leave before the CTA-wide set-up barrier: their latency overlaps the TMEM allocation.
     const uint32_t rbar = smem_u32(&bar_r);
-    mbar_expect_tx(rbar, (MODE == A5_DKV ? 2 : 3) * kTileR);
+    mbar_expect_tx(rbar, (MODE == A5_DKV ? 2 : (p.o_lo ? 4 : 3)) * kTileR);
     if constexpr (MODE == A5_DKV) {
       tma_load_2d(sR1, &tm_qkv_r, rbar, (H + kvh) * 64, row0 + rt * 128);
       tma_load_2d(sR2, &tm_qkv_r, rbar, (H + KV + kvh) * 64, row0 + rt * 128);
@@ -170,6 +172,7 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
       tma_load_2d(sR1, &tm_qkv_r, rbar, h * 64, row0 + rt * 128);
       tma_load_2d(sR2, &tm_do_r, rbar, h * 64, row0 + rt * 128);
       tma_load_2d(sDS, &tm_o_r, rbar, h * 64, row0 + rt * 128);
+      if (p.o_lo) tma_load_2d(sP, &tm_o_lo, rbar, h * 64, row0 + rt * 128);  // P' is not an operand of dQ: its tile is free
     }
     issue_x(0);
     issue_x(1);  // n_it >= 2 always
@@ -261,7 +264,7 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
       // delta for these 128 queries, from the dO and O tiles in shared memory; the dK/dV kernel that
       // follows in the stream reads it from global memory.
       ok = mbar_wait(smem_u32(&bar_r), 0, status, DEV_MBAR_TIMEOUT_EPILOGUE);
-      float part = 0.f;
+      float part = 0.f, part_lo = 0.f;
       if (ok) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -275,8 +278,18 @@ attn5_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
             const float2 af = __bfloat1622float2(a2[e]), cf = __bfloat1622float2(c2[e]);
             part += af.x * cf.x + af.y * cf.y;
           }
+          if (p.o_lo) {
+            const uint4 d = *reinterpret_cast<const uint4*>(pP + off);
+            const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 af = __bfloat1622float2(a2[e]), df = __bfloat1622float2(d2[e]);
+              part_lo += af.x * df.x + af.y * df.y;
+            }
+          }
         }
       }
+      part += part_lo;
       xd[half][r] = part;
       named_bar_sync(1, A5_COMPUTE);  // also: every read of O is done before dS' is written over it
       del_r = part + xd[half ^ 1][r];
@@ -445,11 +458,13 @@ struct Attn5FwdParams {
   int T, H, KV;
   float scale;
   int* status;
+  int write_lo;  // also store out_lo = bf16(O - bf16(O)) through tm_out_lo (for the backward's delta)
 };
 
 __global__ void __launch_bounds__(A5_THREADS, 2)
 attn5_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_constant__ CUtensorMap tm_qkv_x,
-                 const __grid_constant__ CUtensorMap tm_out, Attn5FwdParams p) {
+                 const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ CUtensorMap tm_out_lo,
+                 Attn5FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[2];
   __shared__ __align__(8) uint64_t bar_empty[2];
@@ -651,12 +666,22 @@ attn5_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv_r, const __grid_cons
       uint8_t* pO = smem_al + (sP - smem_base);
 #pragma unroll
       for (int q = 0; q < 4; ++q) st_chunk(pO, r, half * 4 + q, o + 8 * q);
+      if (p.write_lo) {
+        // What bf16 rounding took away from O, as a second bf16 tile in the other P buffer (its last reader,
+        // the final P V product, has been folded above).  The backward forms delta = rowsum(dO * O) from
+        // O + O_lo: with O alone, delta's rounding error is the largest error of dQ and dK.
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[e] -= __bfloat162float(__float2bfloat16_rn(o[e]));
+#pragma unroll
+        for (int q = 0; q < 4; ++q) st_chunk(pO + kTileR, r, half * 4 + q, o + 8 * q);
+      }
       fence_proxy_async_smem();
       if (half == 0) p.lse[((size_t)b * H + h) * T + rpos] = m_run / kLog2e + logf(l_run);
     }
     named_bar_sync(1, A5_COMPUTE);
     if (ok && threadIdx.x == 64) {
       tma_store_2d(&tm_out, sP, h * 64, row0 + rt * 128);
+      if (p.write_lo) tma_store_2d(&tm_out_lo, sP + kTileR, h * 64, row0 + rt * 128);
       tma_store_commit();
       tma_store_wait_read<0>();
     }
@@ -1040,7 +1065,7 @@ attn5_bwd_split_kernel(const __grid_constant__ CUtensorMap tm_hi_r, const __grid
 constexpr size_t kSplitSmem = 3 * kTileR + 6 * kTileX + 2 * kTileR + 1024;
 
 constexpr size_t kDkvSmem5 = 2 * kTileR + 4 * kTileX + 2 * kTileR + 1024;
-constexpr size_t kDqSmem5 = 2 * kTileR + 4 * kTileX + 1 * kTileR + 1024;
+constexpr size_t kDqSmem5 = 2 * kTileR + 4 * kTileX + 2 * kTileR + 1024;  // dS' tile + the O_lo tile for delta
 
 bool g_attr5_done = false;
 bool ensure_attrs5() {
@@ -1065,22 +1090,26 @@ bool ensure_attrs5() {
 
 bool attention_tcgen05_supported(int hd, int seq) { return hd == 64 && seq > 0 && seq % 128 == 0; }
 
-int attention_forward_tcgen05(const bf16* qkv, bf16* out, float* lse, int B, int seq, int H, int KV, float scale,
-                              int* d_status, cudaStream_t s) {
+int attention_forward_tcgen05(const bf16* qkv, bf16* out, bf16* out_lo, float* lse, int B, int seq, int H, int KV,
+                              float scale, int* d_status, cudaStream_t s) {
   if (B <= 0) return 0;
   if (!attention_tcgen05_supported(64, seq) || H % KV != 0 || !ensure_attrs5()) return -1;
   const uint64_t M = (uint64_t)B * seq;
   const uint64_t ld = (uint64_t)(H + 2 * KV) * 64;
-  CUtensorMap tm_qkv_r, tm_qkv_x, tm_out;
+  CUtensorMap tm_qkv_r, tm_qkv_x, tm_out, tm_out_lo;
   if (!make_tmap_2d(&tm_qkv_r, qkv, ld, M, ld, 64, 128, false) || !make_tmap_2d(&tm_qkv_x, qkv, ld, M, ld, 64, 64, false) ||
-      !make_tmap_2d(&tm_out, out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 128, false))
+      !make_tmap_2d(&tm_out, out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 128, false) ||
+      !make_tmap_2d(&tm_out_lo, out_lo ? out_lo : out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 128, false))
     return -2;
-  Attn5FwdParams p{out, lse, seq, H, KV, scale, d_status};
+  Attn5FwdParams p{out, lse, seq, H, KV, scale, d_status, out_lo ? 1 : 0};
   dim3 grid(B * H, seq / 128);
-  return launch_pdl(attn5_fwd_kernel, grid, dim3(A5_THREADS), kFwdSmem5, s, tm_qkv_r, tm_qkv_x, tm_out, p) == cudaSuccess ? 0 : -4;
+  return launch_pdl(attn5_fwd_kernel, grid, dim3(A5_THREADS), kFwdSmem5, s, tm_qkv_r, tm_qkv_x, tm_out, tm_out_lo, p) ==
+                 cudaSuccess
+             ? 0
+             : -4;
 }
 
-int attention_backward_tcgen05(const bf16* qkv, const bf16* out, const bf16* d_out, const float* lse, float* delta,
+int attention_backward_tcgen05(const bf16* qkv, const bf16* out, const bf16* out_lo, const bf16* d_out, const float* lse, float* delta,
                                bf16* dqkv,
                                const float* cosb, const float* sinb, int B, int seq, int H, int KV, float scale,
                                int* d_status, cudaStream_t s) {
@@ -1088,11 +1117,12 @@ int attention_backward_tcgen05(const bf16* qkv, const bf16* out, const bf16* d_o
   if (!attention_tcgen05_supported(64, seq) || H % KV != 0 || !ensure_attrs5()) return -1;
   const uint64_t M = (uint64_t)B * seq;
   const uint64_t ld = (uint64_t)(H + 2 * KV) * 64;
-  CUtensorMap tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_o_r, tm_dqkv, tm_cos, tm_sin;
+  CUtensorMap tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_o_r, tm_o_lo, tm_dqkv, tm_cos, tm_sin;
   if (!make_tmap_2d(&tm_qkv_r, qkv, ld, M, ld, 64, 128, false) || !make_tmap_2d(&tm_qkv_x, qkv, ld, M, ld, 64, 64, false) ||
       !make_tmap_2d(&tm_do_r, d_out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 128, false) ||
       !make_tmap_2d(&tm_do_x, d_out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 64, false) ||
       !make_tmap_2d(&tm_o_r, out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 128, false) ||
+      !make_tmap_2d(&tm_o_lo, out_lo ? out_lo : out, (uint64_t)H * 64, M, (uint64_t)H * 64, 64, 128, false) ||
       !make_tmap_2d(&tm_dqkv, dqkv, ld, M, ld, 64, 128, false))
     return -2;
   if (cosb != nullptr && sinb != nullptr) {  // [seq, 32] fp32 tables, one 128-byte row per position
@@ -1103,15 +1133,15 @@ int attention_backward_tcgen05(const bf16* qkv, const bf16* out, const bf16* d_o
     cosb = sinb = nullptr;
     tm_cos = tm_sin = tm_dqkv;  // never dereferenced
   }
-  Attn5Params p{lse, delta, dqkv, cosb, sinb, seq, H, KV, scale, d_status};
+  Attn5Params p{lse, delta, dqkv, cosb, sinb, seq, H, KV, scale, d_status, out_lo ? 1 : 0};
   // dQ first: it also produces delta, which the dK/dV kernel consumes.
   dim3 gq(B * H, seq / 128);
   if (launch_pdl(attn5_bwd_kernel<A5_DQ>, gq, dim3(A5_THREADS), kDqSmem5, s, tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_o_r,
-                 tm_dqkv, tm_cos, tm_sin, p) != cudaSuccess)
+                 tm_o_lo, tm_dqkv, tm_cos, tm_sin, p) != cudaSuccess)
     return -4;
   dim3 gk(B * KV, seq / 128);
   if (launch_pdl(attn5_bwd_kernel<A5_DKV>, gk, dim3(A5_THREADS), kDkvSmem5, s, tm_qkv_r, tm_qkv_x, tm_do_r, tm_do_x, tm_o_r,
-                 tm_dqkv, tm_cos, tm_sin, p) != cudaSuccess)
+                 tm_o_lo, tm_dqkv, tm_cos, tm_sin, p) != cudaSuccess)
     return -4;
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -270,6 +270,99 @@ template void rope_qknorm_backward<float, float>(float*, const float*, const flo
 template void rope_qknorm_backward<float, bf16>(float*, const float*, const float*, const float*, int, int, int, int,
                                                 int, bool, bool, bool, bf16*, bool, cudaStream_t);
 
+// Head size 64, fp32 pre-norm q|k: the same backward with one (even, odd) pair per lane, so a head is one
+// 8-byte (fp32) or 4-byte (bf16) access per lane, and four heads per warp whose loads are all issued
+// before the first reduction.  The incoming gradient may be bf16 (the tensor-core attention backward
+// writes bf16), which removes the conversion pass in front of this kernel; the fp32 result is written
+// only when out_f32 is given (it may be the fp32 input itself), the GEMM operand copy when out_t is.
+template <typename TI>
+__device__ __forceinline__ float2 load_pair(const TI* p);
+template <>
+__device__ __forceinline__ float2 load_pair<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <>
+__device__ __forceinline__ float2 load_pair<bf16>(const bf16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+template <typename TO>
+__device__ __forceinline__ void store_pair(TO* p, float e, float o);
+template <>
+__device__ __forceinline__ void store_pair<float>(float* p, float e, float o) { *reinterpret_cast<float2*>(p) = make_float2(e, o); }
+template <>
+__device__ __forceinline__ void store_pair<bf16>(bf16* p, float e, float o) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(e, o);
+}
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+rope_qknorm_backward_hd64_kernel(const TI* din, float* out_f32, const float* __restrict__ qk_pre,
+                                 const float* __restrict__ cosb, const float* __restrict__ sinb, int M, int seq, int H,
+                                 int KV, int qk_norm, int reference_coeff, int skip_rope, TO* __restrict__ out_t) {
+  constexpr int HD = 64, G = 4;
+  const int heads = H + KV, slots = H + 2 * KV;
+  const int groups = (slots + G - 1) / G;
+  const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)M * groups) return;
+  const int m = (int)(wid / groups), h0 = (int)(wid - (long long)m * groups) * G;
+  const int t = m % seq;
+  const size_t row = (size_t)m * slots * HD;
+  float2 g[G], x[G];
+#pragma unroll
+  for (int q = 0; q < G; ++q) {
+    const int head = h0 + q;
+    g[q] = head < slots ? load_pair<TI>(din + row + (size_t)head * HD + 2 * lane) : make_float2(0.f, 0.f);
+    x[q] = (qk_norm && head < heads) ? load_pair<float>(qk_pre + (size_t)m * heads * HD + (size_t)head * HD + 2 * lane)
+                                     : make_float2(0.f, 0.f);
+  }
+  float c = 1.f, s = 0.f;
+  if (!skip_rope) {
+    c = cosb[t * (HD / 2) + lane];
+    s = sinb[t * (HD / 2) + lane];
+  }
+#pragma unroll
+  for (int q = 0; q < G; ++q) {
+    const int head = h0 + q;
+    if (head >= slots) break;
+    float e = g[q].x, o = g[q].y;
+    if (head < heads) {
+      if (qk_norm) {
+        const float ss = warp_sum(x[q].x * x[q].x + x[q].y * x[q].y);
+        const float dot = warp_sum(e * x[q].x + o * x[q].y);
+        const float qs = 1.2f;
+        const float r = 1.0f / sqrtf(ss / (float)HD + 1e-5f);
+        float coeff = dot * r * r * r / (float)HD * qs;
+        if (reference_coeff) coeff *= qs;
+        e = e * r * qs - coeff * x[q].x;
+        o = o * r * qs - coeff * x[q].y;
+      }
+      const float e2 = e * c + o * s, o2 = o * c - e * s;
+      e = e2;
+      o = o2;
+    }
+    const size_t off = row + (size_t)head * HD + 2 * lane;
+    // v heads pass through unchanged: nothing to write when the fp32 output is the input itself
+    if (out_f32 && (head < heads || (const void*)out_f32 != (const void*)din)) store_pair<float>(out_f32 + off, e, o);
+    if (out_t) store_pair<TO>(out_t + off, e, o);
+  }
+}
+
+template <typename TI, typename TO>
+void rope_qknorm_backward_hd64(const TI* din, float* out_f32, const float* qk_pre, const float* cosb, const float* sinb,
+                               int M, int seq, int H, int KV, bool qk_norm, bool reference_coeff, bool skip_rope, TO* out_t,
+                               cudaStream_t s) {
+  const long long warps = (long long)M * ((H + 2 * KV + 3) / 4);
+  if (warps <= 0) return;
+  const int wpb = 8;
+  rope_qknorm_backward_hd64_kernel<TI, TO><<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, s>>>(
+      din, out_f32, qk_pre, cosb, sinb, M, seq, H, KV, qk_norm, reference_coeff, skip_rope, out_t);
+}
+template void rope_qknorm_backward_hd64<float, float>(const float*, float*, const float*, const float*, const float*, int,
+                                                      int, int, int, bool, bool, bool, float*, cudaStream_t);
+template void rope_qknorm_backward_hd64<float, bf16>(const float*, float*, const float*, const float*, const float*, int, int,
+                                                     int, int, bool, bool, bool, bf16*, cudaStream_t);
+template void rope_qknorm_backward_hd64<bf16, bf16>(const bf16*, float*, const float*, const float*, const float*, int, int,
+                                                    int, int, bool, bool, bool, bf16*, cudaStream_t);
+
 // ------------------------------------------------------------------------------------------
 // FFN activations
 // ------------------------------------------------------------------------------------------

@@ -61,6 +61,7 @@ struct Act {  // saved activations of one layer (ane/train_full.go:12-37)
   void* qkv = nullptr;    // packed q|k|v: fp32 when the engine keeps attention operands in fp32, else T
   void* qkpre = nullptr;  // rotated pre-norm q|k (reference architecture), same type as qkv
   T* att = nullptr;
+  T* att_lo = nullptr;    // bf16 engines on the tensor-core attention: what rounding att to bf16 dropped (for delta)
   T* x2n = nullptr;
   T* h13 = nullptr;
   T* gate = nullptr;
@@ -500,6 +501,9 @@ int EngineT<T>::alloc_buffers() {
   for (int l = 0; l < L_; ++l) {
     Act<T>& a = acts_[l];
     A(a.x2, MD); A(a.xn, MD); A(a.att, (size_t)M_ * QD_); A(a.x2n, MD);
+    // ANE_B200_ATT_NO_LO=1 leaves the remainder out (delta from the bf16 output alone; for comparisons)
+    if (!kIsF32 && !qkv_f32_ && attention_tc_supported(hd_) && getenv("ANE_B200_ATT_NO_LO") == nullptr)
+      A(a.att_lo, (size_t)M_ * QD_);
     {
       uint8_t* raw = nullptr;
       A(raw, (size_t)M_ * QKVD_ * (qkv_f32_ ? 4 : sizeof(T)));
@@ -780,14 +784,14 @@ int EngineT<T>::forward(const uint16_t* d_tok, int B, int Tl, int pos0) {
         if (att_split_ && Tl == S_) {  // scaled scores are not amplified: the bf16 hi part suffices in the forward
           count_launch();
           cast_f32_to_bf16((const float*)a.qkv, qkvh_, (uint64_t)M * QKVD_, stream_);
-          done = attention_forward_tcgen05(qkvh_, a.att, a.lse, B, Tl, H_, KV_, att_scale, d_status_, stream_) == 0;
+          done = attention_forward_tcgen05(qkvh_, a.att, nullptr, a.lse, B, Tl, H_, KV_, att_scale, d_status_, stream_) == 0;
         }
       }
       if (!done)
         attention_forward_simt<float, T>((const float*)a.qkv, a.att, a.lse, B, Tl, H_, KV_, hd_, att_scale, stream_);
     } else if constexpr (!kIsF32) {
       if (att_tc_)
-        attention_forward_tc((const bf16*)a.qkv, a.att, a.lse, B, Tl, H_, KV_, att_scale, d_status_, stream_);
+        attention_forward_tc((const bf16*)a.qkv, a.att, (bf16*)a.att_lo, a.lse, B, Tl, H_, KV_, att_scale, d_status_, stream_);
       else
         attention_forward_simt<T, T>((const T*)a.qkv, a.att, a.lse, B, Tl, H_, KV_, hd_, att_scale, stream_);
     }
@@ -1012,6 +1016,7 @@ int EngineT<T>::backward_layers(int B) {
     }
     T* dqkv = tview(dqkv_f32, dqkv_[pb]);
     bool dqkv_ready = false;  // true once dqkv holds the final GEMM operand
+    bool dq_is_bf16 = false;  // attention gradient left in dqkv_raw_ (bf16) instead of dqkv_f32
     if (qkv_f32_) {
       bool done = false;
       if constexpr (!kIsF32) {
@@ -1020,8 +1025,8 @@ int EngineT<T>::backward_layers(int B) {
           split_f32_to_bf16x2((const float*)a.qkv, qkvh_, qkvl_, (uint64_t)M * QKVD_, stream_);
           done = attention_backward_tcgen05_split(qkvh_, qkvl_, datt_, att_lse_b_, att_delta_, dqkv_raw_, B, S_, H_, KV_,
                                                   att_scale_bwd, d_status_, stream_) == 0;
-          if (done)
-            to_f32_kernel<bf16><<<ew_grid((uint64_t)M * QKVD_), 256, 0, stream_>>>(dqkv_raw_, dqkv_f32, (uint64_t)M * QKVD_);
+          // head size 64 (the only one these kernels take): the next kernel reads the bf16 gradient directly
+          dq_is_bf16 = done;
         }
       }
       if (!done) {
@@ -1033,7 +1038,7 @@ int EngineT<T>::backward_layers(int B) {
       if (att_tc_) {
         // Tensor-core path: the kernels undo the rotation and emit bf16 operands directly.
         count_launch(3);
-        attention_backward_tc((const bf16*)a.qkv, a.att, datt_, a.lse, att_delta_, dqkv_[pb], rope_cos_, rope_sin_, B, S_,
+        attention_backward_tc((const bf16*)a.qkv, a.att, (const bf16*)a.att_lo, datt_, a.lse, att_delta_, dqkv_[pb], rope_cos_, rope_sin_, B, S_,
                               H_, KV_, att_scale_bwd, d_status_, stream_);
         dqkv_ready = true;
         if (o_.debug_taps) {
@@ -1051,8 +1056,22 @@ int EngineT<T>::backward_layers(int B) {
       // The fp32 result is kept when something still reads it (value-embedding backward, taps).
       const bool keep_f32 = kIsF32 || is_ve_layer(l) || o_.debug_taps;
       count_launch();
-      rope_qknorm_backward<float, T>(dqkv_f32, (const float*)a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_,
-                                     quirks_, quirks_, tcopy_arg(dqkv_[pb]), keep_f32, stream_);
+      bool fast = false;
+      if constexpr (!kIsF32) {
+        if (dq_is_bf16) {
+          rope_qknorm_backward_hd64<bf16, T>(dqkv_raw_, keep_f32 ? dqkv_f32 : nullptr, (const float*)a.qkpre, rope_cos_,
+                                             rope_sin_, M, S_, H_, KV_, isN_, quirks_, quirks_, tcopy_arg(dqkv_[pb]), stream_);
+          fast = true;
+        }
+      }
+      if (!fast && hd_ == 64) {
+        rope_qknorm_backward_hd64<float, T>(dqkv_f32, keep_f32 ? dqkv_f32 : nullptr, (const float*)a.qkpre, rope_cos_,
+                                            rope_sin_, M, S_, H_, KV_, isN_, quirks_, quirks_, tcopy_arg(dqkv_[pb]), stream_);
+        fast = true;
+      }
+      if (!fast)
+        rope_qknorm_backward<float, T>(dqkv_f32, (const float*)a.qkpre, rope_cos_, rope_sin_, M, S_, H_, KV_, hd_, isN_,
+                                       quirks_, quirks_, tcopy_arg(dqkv_[pb]), keep_f32, stream_);
       if (o_.debug_taps)
         cudaMemcpyAsync(a.t_dqkv, dqkv_f32, sizeof(float) * (size_t)M * QKVD_, cudaMemcpyDeviceToDevice, stream_);
     }

@@ -52,6 +52,12 @@ template <typename T, typename TO>
 void rope_qknorm_backward(T* dqkv, const T* qk_pre, const float* cosb, const float* sinb, int M, int seq, int H,
                           int KV, int hd, bool qk_norm, bool reference_coeff, bool skip_rope, TO* out_t,
                           bool write_back, cudaStream_t s);
+// Head size 64 with fp32 pre-norm q|k; the incoming gradient may be bf16, the fp32 output is optional and may
+// be the input itself (elementwise.cu).
+template <typename TI, typename TO>
+void rope_qknorm_backward_hd64(const TI* din, float* out_f32, const float* qk_pre, const float* cosb, const float* sinb,
+                               int M, int seq, int H, int KV, bool qk_norm, bool reference_coeff, bool skip_rope, TO* out_t,
+                               cudaStream_t s);
 void build_rope_tables(float* cosb, float* sinb, int seq, int hd, double theta, cudaStream_t s);
 
 // FFN activations.  relu2: g = max(h,0)^2 (ane/common.go:146).  swiglu: g = silu(h1)*h3 with h13 = [M, 2*Hd].
@@ -90,15 +96,18 @@ void attention_decode_simt(const T* qkv, const T* kcache, const T* vcache, T* ou
 
 // Tensor-core causal attention (bf16 operands, head_dim 64 only; see attention_tc.cu).
 bool attention_tc_supported(int hd);
-void attention_forward_tc(const bf16* qkv, bf16* out, float* lse, int B, int seq, int H, int KV, float scale,
+// `out_lo` (optional, [M, H*64] like `out`) receives bf16(O - bf16(O)): given to the backward as well, it makes
+// delta = rowsum(dO * O) as accurate as an fp32 O would (with bf16 O alone that rounding is the largest
+// error of dQ and dK).  Kernels that do not produce it clear it.
+void attention_forward_tc(const bf16* qkv, bf16* out, bf16* out_lo, float* lse, int B, int seq, int H, int KV, float scale,
                           int* d_status, cudaStream_t s);
-int attention_forward_tcgen05(const bf16* qkv, bf16* out, float* lse, int B, int seq, int H, int KV, float scale,
-                              int* d_status, cudaStream_t s);
+int attention_forward_tcgen05(const bf16* qkv, bf16* out, bf16* out_lo, float* lse, int B, int seq, int H, int KV,
+                              float scale, int* d_status, cudaStream_t s);
 // Writes every element of dq|dk|dv (bf16, packed like qkv); with cos/sin tables the rotation of q and k
 // is undone in the epilogue (pass nullptr to skip).  `delta` is scratch [B*H*seq].
 // With head_dim 64 and seq % 128 == 0 the tcgen05 kernels (attention_tcgen05.cu) run, else mma.sync ones;
 // `d_status` is the device status word their bounded waits report through.
-void attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* d_out, const float* lse, float* delta,
+void attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* out_lo, const bf16* d_out, const float* lse, float* delta,
                            bf16* dqkv, const float* cosb, const float* sinb, int B, int seq, int H, int KV,
                            float scale, int* d_status, cudaStream_t s);
 bool attention_tcgen05_supported(int hd, int seq);
@@ -108,7 +117,7 @@ int attention_backward_tcgen05_split(const bf16* qkv_hi, const bf16* qkv_lo, con
                                      bf16* dqkv, int B, int seq, int H, int KV, float scale, int* d_status,
                                      cudaStream_t s);
 // `delta` is scratch [B*H*seq] (rowsum(dO * O), produced by the dQ kernel).  Returns 0 or a negative error code.
-int attention_backward_tcgen05(const bf16* qkv, const bf16* out, const bf16* d_out, const float* lse, float* delta,
+int attention_backward_tcgen05(const bf16* qkv, const bf16* out, const bf16* out_lo, const bf16* d_out, const float* lse, float* delta,
                                bf16* dqkv,
                                const float* cosb, const float* sinb, int B, int seq, int H, int KV, float scale,
                                int* d_status, cudaStream_t s);

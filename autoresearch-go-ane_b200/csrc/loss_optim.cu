@@ -1,4 +1,5 @@
 // Cross-entropy over logit rows, gradient-norm reduction and the fused AdamW update.
+#include <cstdlib>
 #include "common.cuh"
 #include "kernels.h"
 
@@ -226,10 +227,177 @@ cross_entropy_rows_bf16_kernel(const bf16* __restrict__ logits, const uint16_t* 
   }
 }
 
+// Register-resident form for rows of up to threads x slots x 8 = 32768 logits: the block reads its
+// row once, 16 bytes per load with every load of a thread in flight together, and keeps it packed in
+// registers (two blocks per SM hold two 64 KB rows: 512 threads x 8 pieces or 256 threads x 16 pieces).  Three sweeps over the registers:
+// packed bf16 maxima, sum of exponentials, gradient.  Per logit that is about ten instructions and two
+// MUFU operations, against ~29 issued instructions of the streaming kernel above, which is bound by
+// instruction issue and not by memory.  The target's one-hot term is patched into the single 16-byte
+// piece that holds it, outside the per-element work.
+
+__device__ __forceinline__ float ex2_fast(float x) {  // one MUFU.EX2, denormal results flushed to zero
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));  // volatile: keeps the sweeps in source order (register pressure)
+  return y;
+}
+__device__ __forceinline__ float bf16_lo_f(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi_f(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&t);
+}
+__device__ __forceinline__ uint32_t bf16x2_max(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+template <bool SOFTCAP, int kCERegThreads, int kCERegSlots>
+__global__ void __launch_bounds__(kCERegThreads, 2)
+cross_entropy_rows_bf16_reg_kernel(const bf16* __restrict__ logits, const uint16_t* __restrict__ targets,
+                                   const float* __restrict__ inv_valid, const float* __restrict__ tgt_logit,
+                                   bf16* __restrict__ dlogits, float* __restrict__ loss_rows, int rows, int row0,
+                                   int seq, int V, float grad_scale) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  if (r >= rows) return;
+  const int grow = row0 + r;
+  const uint4* x8 = reinterpret_cast<const uint4*>(logits + (size_t)r * V);
+  uint4* d8 = dlogits ? reinterpret_cast<uint4*>(dlogits + (size_t)r * V) : nullptr;
+  const int tgt = targets[grow];
+  const int V8 = V >> 3;
+  const int tid = threadIdx.x;
+  __shared__ float s_m[kCERegThreads / 32], s_l[kCERegThreads / 32];
+  if (tgt >= V) {  // invalid target: zero gradient row, not counted (cpu.go:253-258)
+    if (d8)
+      for (int i = tid; i < V8; i += kCERegThreads) d8[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (tid == 0 && loss_rows) loss_rows[grow] = 0.f;
+    return;
+  }
+  constexpr uint32_t kNegInf2 = 0xff80ff80u;  // two bf16 -inf: contributes nothing to maximum or sum
+  uint4 q[kCERegSlots];
+#pragma unroll
+  for (int j = 0; j < kCERegSlots; ++j) {
+    const int i = tid + j * kCERegThreads;
+    q[j] = i < V8 ? x8[i] : make_uint4(kNegInf2, kNegInf2, kNegInf2, kNegInf2);
+  }
+  // sweep 1: row maximum of the raw logits (the soft cap is monotonic, so it is applied to the maximum)
+  uint32_t mx = kNegInf2;
+#pragma unroll
+  for (int j = 0; j < kCERegSlots; ++j)
+    mx = bf16x2_max(mx, bf16x2_max(bf16x2_max(q[j].x, q[j].y), bf16x2_max(q[j].z, q[j].w)));
+  float m = fmaxf(bf16_lo_f(mx), bf16_hi_f(mx));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  const int lane = tid & 31, warp = tid >> 5;
+  if (lane == 0) s_m[warp] = m;
+  __syncthreads();
+  m = s_m[lane & (kCERegThreads / 32 - 1)];
+#pragma unroll
+  for (int o = kCERegThreads / 64; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  const float bm = SOFTCAP ? 15.0f * fast_tanh(m * (1.0f / 15.0f)) : m;
+  constexpr float kLog2e = 1.4426950408889634f;
+  const float mb = bm * kLog2e;
+  // sweep 2: sum of exp(z - max)
+  float l = 0.f;
+#pragma unroll
+  for (int j = 0; j < kCERegSlots; ++j) {
+    const uint32_t w[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float a = bf16_lo_f(w[k]), b = bf16_hi_f(w[k]);
+      if (SOFTCAP) {
+        a = 15.0f * fast_tanh(a * (1.0f / 15.0f));
+        b = 15.0f * fast_tanh(b * (1.0f / 15.0f));
+      }
+      l += ex2_fast(fmaf(a, kLog2e, -mb)) + ex2_fast(fmaf(b, kLog2e, -mb));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+  if (lane == 0) s_l[warp] = l;
+  __syncthreads();
+  l = s_l[lane & (kCERegThreads / 32 - 1)];
+#pragma unroll
+  for (int o = kCERegThreads / 64; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+  if (tid == 0 && loss_rows) {
+    float zt = tgt_logit[grow];
+    if (SOFTCAP) zt = softcap_f(zt);
+    loss_rows[grow] = -logf(fmaxf(expf(zt - bm) / l, 1e-10f));
+  }
+  if (!d8) return;
+  // sweep 3: gradient gs * (softmax - onehot) [* d softcap], written in the logits' own format
+  const float gs = grad_scale * inv_valid[grow / seq];
+  const float sc = gs / l;
+#pragma unroll
+  for (int j = 0; j < kCERegSlots; ++j) {
+    const int i = tid + j * kCERegThreads;
+    const uint32_t w[4] = {q[j].x, q[j].y, q[j].z, q[j].w};
+    float o[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float a = bf16_lo_f(w[k]), b = bf16_hi_f(w[k]);
+      if (SOFTCAP) {
+        const float ta = fast_tanh(a * (1.0f / 15.0f)), tb = fast_tanh(b * (1.0f / 15.0f));
+        o[2 * k] = ex2_fast(fmaf(15.0f * ta, kLog2e, -mb)) * sc * (1.f - ta * ta);
+        o[2 * k + 1] = ex2_fast(fmaf(15.0f * tb, kLog2e, -mb)) * sc * (1.f - tb * tb);
+      } else {
+        o[2 * k] = ex2_fast(fmaf(a, kLog2e, -mb)) * sc;
+        o[2 * k + 1] = ex2_fast(fmaf(b, kLog2e, -mb)) * sc;
+      }
+    }
+    if (i < V8)
+      d8[i] = make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]), pack_bf16x2(o[4], o[5]), pack_bf16x2(o[6], o[7]));
+  }
+  // The target's one-hot term: the thread that stored the piece holding the target rewrites that one
+  // element afterwards (same thread, same address: program order), which keeps the sweep free of it.
+  if (tid == ((tgt >> 3) & (kCERegThreads - 1))) {
+    float z = __bfloat162float(logits[(size_t)r * V + tgt]), dcap = 1.f;
+    if (SOFTCAP) {
+      const float th = fast_tanh(z * (1.0f / 15.0f));
+      z = 15.0f * th;
+      dcap = 1.f - th * th;
+    }
+    dlogits[(size_t)r * V + tgt] = __float2bfloat16_rn((ex2_fast(fmaf(z, kLog2e, -mb)) * sc - gs) * dcap);
+  }
+}
+
+// Set ANE_B200_CE_STREAMING=1 to keep every row on the streaming kernel (for comparisons).
+static bool ce_force_streaming() {
+  static const bool v = [] {
+    const char* e = getenv("ANE_B200_CE_STREAMING");
+    return e && e[0] == '1';
+  }();
+  return v;
+}
+
+// ANE_B200_CE_REG_THREADS=256 selects 256 threads x 16 pieces for the register-resident kernel (default 512 x 8).
+static int ce_reg_threads() {
+  static const int v = [] {
+    const char* e = getenv("ANE_B200_CE_REG_THREADS");
+    return (e && atoi(e) == 256) ? 256 : 512;
+  }();
+  return v;
+}
+
 void cross_entropy_rows_bf16(const bf16* logits, const uint16_t* targets, const float* inv_valid, const float* tgt_logit,
                              bf16* dlogits, float* loss_rows, int rows, int row0, int seq, int V, bool softcap,
                              float grad_scale, cudaStream_t s) {
   if (rows <= 0) return;
+  if ((V >> 3) <= 4096 && !ce_force_streaming()) {
+    auto go = [&](auto kernel, int threads) {
+      launch_pdl(kernel, dim3(rows), dim3(threads), 0, s, logits, targets, inv_valid, tgt_logit, dlogits, loss_rows, rows,
+                 row0, seq, V, grad_scale);
+    };
+    if (ce_reg_threads() == 256) {
+      if (softcap) go(cross_entropy_rows_bf16_reg_kernel<true, 256, 16>, 256);
+      else go(cross_entropy_rows_bf16_reg_kernel<false, 256, 16>, 256);
+    } else {
+      if (softcap) go(cross_entropy_rows_bf16_reg_kernel<true, 512, 8>, 512);
+      else go(cross_entropy_rows_bf16_reg_kernel<false, 512, 8>, 512);
+    }
+    return;
+  }
   static bool attr_done = false;
   if (!attr_done) {
     if (cudaFuncSetAttribute(cross_entropy_rows_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
