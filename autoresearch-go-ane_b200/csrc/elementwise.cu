@@ -292,6 +292,61 @@ __device__ __forceinline__ void store_pair<bf16>(bf16* p, float e, float o) {
   *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(e, o);
 }
 
+// Forward counterpart for fp32 q|k|v with head size 64: rotation and QK-norm of four heads per warp (one pair
+// per lane), fp32 results in place, the pre-norm copy for the backward, and in the same pass the bf16 copy of
+// all of q|k|v that the tensor-core attention reads (otherwise a separate conversion pass over the tensor).
+__global__ void __launch_bounds__(256)
+rope_qknorm_forward_hd64_kernel(float* qkv, float* __restrict__ qk_pre, const float* __restrict__ cosb,
+                                const float* __restrict__ sinb, int M, int seq, int H, int KV, int qk_norm, int pos0,
+                                bf16* __restrict__ hi_out) {
+  constexpr int HD = 64, G = 4;
+  const int heads = H + KV, slots = H + 2 * KV;
+  const int groups = (slots + G - 1) / G;
+  const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)M * groups) return;
+  const int m = (int)(wid / groups), h0 = (int)(wid - (long long)m * groups) * G;
+  const int t = pos0 + m % seq;
+  const size_t row = (size_t)m * slots * HD;
+  float2 v[G];
+#pragma unroll
+  for (int q = 0; q < G; ++q) {
+    const int head = h0 + q;
+    v[q] = head < slots ? *reinterpret_cast<const float2*>(qkv + row + (size_t)head * HD + 2 * lane) : make_float2(0.f, 0.f);
+  }
+  const float c = cosb[t * (HD / 2) + lane], s = sinb[t * (HD / 2) + lane];
+#pragma unroll
+  for (int q = 0; q < G; ++q) {
+    const int head = h0 + q;
+    if (head >= slots) break;
+    float e = v[q].x, o = v[q].y;
+    const size_t off = row + (size_t)head * HD + 2 * lane;
+    if (head < heads) {
+      const float e2 = e * c - o * s, o2 = o * c + e * s;
+      e = e2;
+      o = o2;
+      if (qk_norm) {
+        const float ss = warp_sum(e * e + o * o);
+        const float scale = 1.2f / sqrtf(ss / (float)HD + 1e-5f);
+        if (qk_pre) store_pair<float>(qk_pre + (size_t)m * heads * HD + (size_t)head * HD + 2 * lane, e, o);
+        e *= scale;
+        o *= scale;
+      }
+      store_pair<float>(qkv + off, e, o);
+    }
+    if (hi_out) store_pair<bf16>(hi_out + off, e, o);
+  }
+}
+
+void rope_qknorm_forward_hd64(float* qkv, float* qk_pre, const float* cosb, const float* sinb, int M, int seq, int H, int KV,
+                              bool qk_norm, int pos0, bf16* hi_out, cudaStream_t s) {
+  const long long warps = (long long)M * ((H + 2 * KV + 3) / 4);
+  if (warps <= 0) return;
+  const int wpb = 8;
+  rope_qknorm_forward_hd64_kernel<<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, 0, s>>>(qkv, qk_pre, cosb, sinb, M, seq, H,
+                                                                                         KV, qk_norm, pos0, hi_out);
+}
+
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 rope_qknorm_backward_hd64_kernel(const TI* din, float* out_f32, const float* __restrict__ qk_pre,
@@ -640,36 +695,47 @@ template void ve_forward<float>(float*, const float*, const uint16_t*, const flo
 template void ve_forward<bf16>(bf16*, const float*, const uint16_t*, const float*, const float*, float*, int, int, int,
                                int, int, int, cudaStream_t);
 
+// Blocks stride over the (token, head) pairs and keep the gate-weight gradient (H x 12 sums that every pair
+// adds to) in shared memory, flushed once per block: the global atomics on those few addresses were the
+// bulk of this kernel's time.
 template <typename T>
 __global__ void ve_backward_kernel(const T* __restrict__ dqkv, const float* __restrict__ x,
                                    const uint16_t* __restrict__ tok, const float* __restrict__ ve_embed,
                                    const float* __restrict__ ve_gate, const float* __restrict__ gate_act,
                                    float* __restrict__ g_ve_embed, float* __restrict__ g_ve_gate,
                                    float* __restrict__ d_prev, int M, int D, int H, int KV, int hd, int vocab) {
-  const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  extern __shared__ float s_gate[];  // [H][kVEGateChannels]
+  for (int i = threadIdx.x; i < H * kVEGateChannels; i += blockDim.x) s_gate[i] = 0.f;
+  __syncthreads();
   const int lane = threadIdx.x & 31;
-  if (wid >= (long long)M * H) return;
-  const int m = (int)(wid / H), h = (int)(wid - (long long)m * H);
-  const int t = tok[m];
-  if (t >= vocab) return;
-  const float act = gate_act[(size_t)m * H + h];
-  const float gate = 3.0f * act;
-  const int ld = (H + 2 * KV) * hd;
-  const T* dv = dqkv + (size_t)m * ld + (size_t)(H + KV) * hd + (size_t)h * hd;
-  const float* ve = ve_embed + (size_t)t * D + (size_t)h * hd;
-  float* gve = g_ve_embed + (size_t)t * D + (size_t)h * hd;
-  float d_gate = 0.f;
-  for (int d = lane; d < hd; d += 32) {
-    const float g = to_f<T>(dv[d]);
-    atomicAdd(gve + d, g * gate);
-    d_gate += g * ve[d];
+  const long long total = (long long)M * H;
+  const long long step = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); wid < total; wid += step) {
+    const int m = (int)(wid / H), h = (int)(wid - (long long)m * H);
+    const int t = tok[m];
+    if (t >= vocab) continue;
+    const float act = gate_act[(size_t)m * H + h];
+    const float gate = 3.0f * act;
+    const int ld = (H + 2 * KV) * hd;
+    const T* dv = dqkv + (size_t)m * ld + (size_t)(H + KV) * hd + (size_t)h * hd;
+    const float* ve = ve_embed + (size_t)t * D + (size_t)h * hd;
+    float* gve = g_ve_embed + (size_t)t * D + (size_t)h * hd;
+    float d_gate = 0.f;
+    for (int d = lane; d < hd; d += 32) {
+      const float g = to_f<T>(dv[d]);
+      atomicAdd(gve + d, g * gate);
+      d_gate += g * ve[d];
+    }
+    d_gate = warp_sum(d_gate);
+    const float d_gate_pre = d_gate * 3.0f * act * (1.f - act);
+    if (lane < kVEGateChannels) {
+      atomicAdd(&s_gate[h * kVEGateChannels + lane], d_gate_pre * x[(size_t)m * D + lane]);
+      atomicAdd(d_prev + (size_t)m * D + lane, d_gate_pre * ve_gate[h * kVEGateChannels + lane]);
+    }
   }
-  d_gate = warp_sum(d_gate);
-  const float d_gate_pre = d_gate * 3.0f * act * (1.f - act);
-  if (lane < kVEGateChannels) {
-    atomicAdd(g_ve_gate + h * kVEGateChannels + lane, d_gate_pre * x[(size_t)m * D + lane]);
-    atomicAdd(d_prev + (size_t)m * D + lane, d_gate_pre * ve_gate[h * kVEGateChannels + lane]);
-  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < H * kVEGateChannels; i += blockDim.x)
+    if (s_gate[i] != 0.f) atomicAdd(g_ve_gate + i, s_gate[i]);
 }
 template <typename T>
 void ve_backward(const T* dqkv, const float* x, const uint16_t* tok, const float* ve_embed, const float* ve_gate,
@@ -677,9 +743,10 @@ void ve_backward(const T* dqkv, const float* x, const uint16_t* tok, const float
                  int KV, int hd, int vocab, cudaStream_t s) {
   const long long warps = (long long)M * H;
   if (warps <= 0) return;
-  ve_backward_kernel<T><<<(unsigned)((warps + 7) / 8), 256, 0, s>>>(dqkv, x, tok, ve_embed, ve_gate, gate_act,
-                                                                     g_ve_embed, g_ve_gate, d_prev, M, D, H, KV, hd,
-                                                                     vocab);
+  long long blocks = (warps + 7) / 8;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  ve_backward_kernel<T><<<(unsigned)blocks, 256, sizeof(float) * H * kVEGateChannels, s>>>(
+      dqkv, x, tok, ve_embed, ve_gate, gate_act, g_ve_embed, g_ve_gate, d_prev, M, D, H, KV, hd, vocab);
 }
 template void ve_backward<float>(const float*, const float*, const uint16_t*, const float*, const float*,
                                  const float*, float*, float*, float*, int, int, int, int, int, int, cudaStream_t);

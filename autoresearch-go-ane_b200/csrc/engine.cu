@@ -759,14 +759,28 @@ int EngineT<T>::forward(const uint16_t* d_tok, int B, int Tl, int pos0) {
       count_launch();
       if ((rc = gemm(g)) != 0) return rc;
     }
+    // bf16 engine with fp32 q|k|v on the split-precision tensor-core attention: the rotation kernel also writes the
+    // bf16 copy that the attention forward reads.  The value embedding only touches v and does not read q or k,
+    // so it goes first and its result is part of that copy.
+    bool hi_ready = false;
+    bool fuse_hi = false;
+    if constexpr (!kIsF32) fuse_hi = !fused_rope && qkv_f32_ && att_split_ && Tl == S_ && !decoding_ && hd_ == 64;
+    if (fuse_hi && is_ve_layer(l)) {
+      count_launch();
+      ve_forward<float>((float*)a.qkv, xs_[l], d_tok, P_ + s_ve_embed_[l].off, P_ + s_ve_gate_[l].off, a.ve_act, M, D_,
+                        H_, KV_, hd_, V_, stream_);
+    }
     if (!fused_rope) {
       count_launch();
-      if (qkv_f32_)
+      if (fuse_hi) {
+        rope_qknorm_forward_hd64((float*)a.qkv, (float*)a.qkpre, rope_cos_, rope_sin_, M, Tl, H_, KV_, isN_, pos0, qkvh_, stream_);
+        hi_ready = true;
+      } else if (qkv_f32_)
         rope_qknorm_forward<float>((float*)a.qkv, (float*)a.qkpre, rope_cos_, rope_sin_, M, Tl, H_, KV_, hd_, isN_, pos0, stream_);
       else
         rope_qknorm_forward<T>((T*)a.qkv, (T*)a.qkpre, rope_cos_, rope_sin_, M, Tl, H_, KV_, hd_, isN_, pos0, stream_);
     }
-    if (is_ve_layer(l)) {  // reference architecture only, so qkv is fp32 here
+    if (!fuse_hi && is_ve_layer(l)) {  // reference architecture only, so qkv is fp32 here
       count_launch();
       ve_forward<float>((float*)a.qkv, xs_[l], d_tok, P_ + s_ve_embed_[l].off, P_ + s_ve_gate_[l].off, a.ve_act, M, D_,
                         H_, KV_, hd_, V_, stream_);
@@ -782,8 +796,10 @@ int EngineT<T>::forward(const uint16_t* d_tok, int B, int Tl, int pos0) {
       bool done = false;
       if constexpr (!kIsF32) {
         if (att_split_ && Tl == S_) {  // scaled scores are not amplified: the bf16 hi part suffices in the forward
-          count_launch();
-          cast_f32_to_bf16((const float*)a.qkv, qkvh_, (uint64_t)M * QKVD_, stream_);
+          if (!hi_ready) {
+            count_launch();
+            cast_f32_to_bf16((const float*)a.qkv, qkvh_, (uint64_t)M * QKVD_, stream_);
+          }
           done = attention_forward_tcgen05(qkvh_, a.att, nullptr, a.lse, B, Tl, H_, KV_, att_scale, d_status_, stream_) == 0;
         }
       }

@@ -52,6 +52,10 @@ template <typename T, typename TO>
 void rope_qknorm_backward(T* dqkv, const T* qk_pre, const float* cosb, const float* sinb, int M, int seq, int H,
                           int KV, int hd, bool qk_norm, bool reference_coeff, bool skip_rope, TO* out_t,
                           bool write_back, cudaStream_t s);
+// Head size 64, fp32 q|k|v: rotation (+ QK-norm) in place, and with `hi_out` the bf16 copy of all of q|k|v in the
+// same pass (elementwise.cu).
+void rope_qknorm_forward_hd64(float* qkv, float* qk_pre, const float* cosb, const float* sinb, int M, int seq, int H, int KV,
+                              bool qk_norm, int pos0, bf16* hi_out, cudaStream_t s);
 // Head size 64 with fp32 pre-norm q|k; the incoming gradient may be bf16, the fp32 output is optional and may
 // be the input itself (elementwise.cu).
 template <typename TI, typename TO>

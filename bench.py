@@ -81,12 +81,16 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks, power and throttle reasons with nvidia-smi (every 20 ms).  The process is started
+    before the warm-up steps, so that its start-up time is not taken from the timed region; mark() / window()
+    bracket the timed regions, and only samples that arrived inside a window are reported."""
 
     def __init__(self, device: int):
         self.device = device
         self.proc = None
         self.lines: list[str] = []
+        self.windows: list[tuple[int, int]] = []
+        self._mark = 0
 
     def start(self):
         q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
@@ -94,7 +98,7 @@ class ClockSampler:
              "clocks_event_reasons.sw_power_cap")
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -104,6 +108,12 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def mark(self):
+        self._mark = len(self.lines)
+
+    def window(self):
+        self.windows.append((self._mark, len(self.lines)))
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -112,22 +122,26 @@ class ClockSampler:
             self.proc.wait(timeout=2)
         except Exception:
             pass
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        picked = [ln for a, b in self.windows for ln in self.lines[a:b]]
+        for ln in picked:
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 7:
                 continue
             try:
                 sm.append(float(parts[0]))
                 mx.append(float(parts[1]))
+                pw.append(float(parts[2]))
             except ValueError:
                 continue
             for nm, v in zip(names, parts[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(nm)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_min_mhz": min(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "power_w": float(np.median(pw)) if pw else None,
+                "reasons": sorted(reasons), "samples": len(sm),
+                "window": "timed regions of the device-resident and end-to-end legs"}
 
 
 def init_weights(engine, ane, seed, cfg):
@@ -206,12 +220,13 @@ def run_ours(args):
     tokens_per_step = MICRO_BATCH * T * world
 
     # ---- device-resident leg ("value")
-    for _ in range(args.warmup):
-        r = e.step()
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        r = e.step()
+    barrier()
+    sampler.mark()
     launches0 = e.launch_count()
     e.timer_begin()
     t0 = time.perf_counter()
@@ -220,9 +235,9 @@ def run_ours(args):
         last = e.step()
     ms = e.timer_end()
     wall_ms = (time.perf_counter() - t0) * 1e3
+    sampler.window()
     barrier()
     launches = e.launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
     ms = max_over_ranks(ms)
     ms_per_step = ms / args.steps
     value = tokens_per_step / (ms_per_step * 1e-3)
@@ -237,11 +252,14 @@ def run_ours(args):
         batches.append((inp, tgt))
     e.step_tokens(*batches[-1])
     barrier()
+    sampler.mark()
     t0 = time.perf_counter()
     for s in range(args.steps):
         e.step_tokens(*batches[s])
     ane._ffi.lib.ane_dev_sync()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
+    sampler.window()
+    clocks = sampler.stop() if rank == 0 else None
     barrier()
     e2e_value = tokens_per_step * args.steps / e2e_s
     h2d = 2 * MICRO_BATCH * T * 2
