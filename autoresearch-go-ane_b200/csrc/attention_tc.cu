@@ -151,8 +151,8 @@ __device__ __forceinline__ void store_grad_bf16(bf16* base, int ld, int row_lo, 
 // Forward: grid (query tiles of 128, B*H); 8 warps x 16 query rows; key/value tiles of 64 streamed.
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(ATT_THREADS)
-attention_fwd_tc_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, float* __restrict__ lse, int T, int H,
-                        int KV, float scale) {
+attention_fwd_tc_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, bf16* __restrict__ out_lo,
+                        float* __restrict__ lse, int T, int H, int KV, float scale) {
   extern __shared__ __align__(16) uint8_t att_smem[];
   bf16* Qs = reinterpret_cast<bf16*>(att_smem);   // [BR][LDS]
   bf16* Ks = Qs + BR * LDS;                       // [2][KT][LDS]
@@ -242,9 +242,14 @@ attention_fwd_tc_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, fl
       const float inv = 1.0f / l_i[r];
       bf16* op = out + (row0 + row) * (size_t)(H * HD) + (size_t)h * HD;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
-        *reinterpret_cast<__nv_bfloat162*>(op + nt * 8 + 2 * t4) =
-            __floats2bfloat162_rn(o[nt][2 * r] * inv, o[nt][2 * r + 1] * inv);
+      for (int nt = 0; nt < 8; ++nt) {
+        const float ox = o[nt][2 * r] * inv, oy = o[nt][2 * r + 1] * inv;
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(ox, oy);
+        *reinterpret_cast<__nv_bfloat162*>(op + nt * 8 + 2 * t4) = hi;
+        if (out_lo)  // what the rounding dropped, for the backward's delta
+          *reinterpret_cast<__nv_bfloat162*>(out_lo + (op - out) + nt * 8 + 2 * t4) =
+              __floats2bfloat162_rn(ox - __bfloat162float(hi.x), oy - __bfloat162float(hi.y));
+      }
       if (t4 == 0) lse[((size_t)b * H + h) * T + row] = m_i[r] / kLog2e + logf(l_i[r]);
     }
   }
@@ -252,7 +257,7 @@ attention_fwd_tc_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, fl
 
 // delta[b,h,t] = sum_d dO * O  (one warp per (token, head))
 __global__ void attention_delta_kernel(const bf16* __restrict__ d_out, const bf16* __restrict__ out,
-                                       float* __restrict__ delta, int B, int T, int H) {
+                                       const bf16* __restrict__ out_lo, float* __restrict__ delta, int B, int T, int H) {
   const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (wid >= (long long)B * T * H) return;
@@ -263,6 +268,10 @@ __global__ void attention_delta_kernel(const bf16* __restrict__ d_out, const bf1
   const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(d_out + off);
   const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(out + off);
   float v = __bfloat162float(a.x) * __bfloat162float(c.x) + __bfloat162float(a.y) * __bfloat162float(c.y);
+  if (out_lo) {
+    const __nv_bfloat162 d = *reinterpret_cast<const __nv_bfloat162*>(out_lo + off);
+    v += __bfloat162float(a.x) * __bfloat162float(d.x) + __bfloat162float(a.y) * __bfloat162float(d.y);
+  }
   v = warp_sum(v);
   if (lane == 0) delta[((size_t)b * H + h) * T + t] = v;
 }
@@ -472,10 +481,8 @@ void attention_forward_tc(const bf16* qkv, bf16* out, bf16* out_lo, float* lse, 
   if (!legacy && attention_tcgen05_supported(HD, seq) &&
       attention_forward_tcgen05(qkv, out, out_lo, lse, B, seq, H, KV, scale, d_status, s) == 0)
     return;
-  // the mma.sync kernels keep no rounding remainder of O: an all-zero one leaves the backward's delta as it was
-  if (out_lo) cudaMemsetAsync(out_lo, 0, sizeof(bf16) * (size_t)B * seq * H * HD, s);
   dim3 grid((seq + BR - 1) / BR, B * H);
-  attention_fwd_tc_kernel<<<grid, ATT_THREADS, kFwdSmem, s>>>(qkv, out, lse, seq, H, KV, scale);
+  attention_fwd_tc_kernel<<<grid, ATT_THREADS, kFwdSmem, s>>>(qkv, out, out_lo, lse, seq, H, KV, scale);
 }
 
 void attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* out_lo, const bf16* d_out, const float* lse, float* delta,
@@ -488,7 +495,7 @@ void attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* out_lo,
       attention_backward_tcgen05(qkv, out, out_lo, d_out, lse, delta, dqkv, cosb, sinb, B, seq, H, KV, scale, d_status, s) == 0)
     return;
   const long long warps = (long long)B * seq * H;
-  attention_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>(d_out, out, delta, B, seq, H);
+  attention_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>(d_out, out, out_lo, delta, B, seq, H);
   dim3 gq((seq + BR - 1) / BR, B * H);
   attention_bwd_dq_tc_kernel<<<gq, ATT_THREADS, kDqSmem, s>>>(qkv, d_out, lse, delta, dqkv, cosb, sinb, seq, H, KV,
                                                                scale);

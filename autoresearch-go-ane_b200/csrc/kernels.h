@@ -102,7 +102,7 @@ void attention_decode_simt(const T* qkv, const T* kcache, const T* vcache, T* ou
 bool attention_tc_supported(int hd);
 // `out_lo` (optional, [M, H*64] like `out`) receives bf16(O - bf16(O)): given to the backward as well, it makes
 // delta = rowsum(dO * O) as accurate as an fp32 O would (with bf16 O alone that rounding is the largest
-// error of dQ and dK).  Kernels that do not produce it clear it.
+// error of dQ).
 void attention_forward_tc(const bf16* qkv, bf16* out, bf16* out_lo, float* lse, int B, int seq, int H, int KV, float scale,
                           int* d_status, cudaStream_t s);
 int attention_forward_tcgen05(const bf16* qkv, bf16* out, bf16* out_lo, float* lse, int B, int seq, int H, int KV,

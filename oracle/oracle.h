@@ -10,7 +10,8 @@
  * PARITY UNPINNED: the reference ships no golden vectors, known-answer tests or
  * fixtures for this path and cannot be built here (no Go toolchain), so this
  * restatement is pinned only by line-by-line traceability to the cited Go
- * sources plus self-consistency checks (finite differences, invariants).
+ * sources plus self-consistency checks (finite differences, invariants) and an
+ * independent fp64 torch-autograd statement of both networks (tests/test_oracle.py).
  */
 #ifndef ANE_ORACLE_H_
 #define ANE_ORACLE_H_

@@ -131,6 +131,155 @@ def test_exact_gradients_llama_arch_gqa():
     _directional_fd(O.ARCH_L)
 
 
+def test_llama_arch_matches_torch_autograd_fp64():
+    """An independent statement of the llama-style network in torch (fp64, autograd): weighted RMSNorm
+    (eps 1e-5), rotation of interleaved pairs, causal GQA attention, SwiGLU, tied classifier, mean
+    cross-entropy over the valid targets.  Loss and every parameter gradient of the oracle must agree
+    with it; one target lies outside the vocabulary."""
+    import torch
+
+    D, Hd, H, KV, L, V, T = 32, 48, 4, 2, 3, 64, 12
+    hd = D // H
+    m = O.Model(dim=D, hidden=Hd, heads=H, kv_heads=KV, layers=L, vocab=V, seq=T, arch=O.ARCH_L, quirks=0,
+                loss_scale=1.0, accum_steps=1000, grad_clip=0.0)
+    O.init_weights(m, 1, std=0.3)
+    for tid, layer, a in m.tensors():
+        if tid in (O.T_RMS_ATT, O.T_RMS_FFN, O.T_RMS_FINAL):
+            a[:] = 1 + 0.2 * np.random.default_rng(layer + tid).standard_normal(a.size)
+    toks = O.zipf_tokens(T + 1, V, 3)
+    inp, tgt = toks[:T].copy(), toks[1:T + 1].copy()
+    tgt[4] = 65535
+    loss = m.accumulate(inp, tgt)
+    P = {(tid, layer): torch.tensor(a.astype(np.float64), requires_grad=True) for tid, layer, a in m.tensors(O.W)}
+    theta = float(m.cfg.rope_theta)
+
+    def rms(x, w):
+        return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-5) * w
+
+    def rope(x, nh):
+        x = x.view(T, nh, hd // 2, 2)
+        pos = torch.arange(T, dtype=torch.float64)[:, None]
+        i = torch.arange(hd // 2, dtype=torch.float64)[None, :]
+        ang = pos / theta ** (2 * i / hd)
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        e, o = x[..., 0], x[..., 1]
+        return torch.stack([e * c - o * s, o * c + e * s], -1).view(T, nh * hd)
+
+    emb = P[(O.T_EMBED, 0)].view(V, D)
+    x = emb[torch.tensor(inp.astype(np.int64))]
+    causal = torch.tril(torch.ones(T, T, dtype=torch.bool))
+    for l in range(L):
+        xn = rms(x, P[(O.T_RMS_ATT, l)])
+        q = rope(xn @ P[(O.T_WQ, l)].view(H * hd, D).T, H)
+        k = rope(xn @ P[(O.T_WK, l)].view(KV * hd, D).T, KV)
+        v = xn @ P[(O.T_WV, l)].view(KV * hd, D).T
+        outs = []
+        for h in range(H):
+            g = h // (H // KV)
+            sc = q[:, h * hd:(h + 1) * hd] @ k[:, g * hd:(g + 1) * hd].T / np.sqrt(hd)
+            outs.append(torch.softmax(sc.masked_fill(~causal, float("-inf")), -1) @ v[:, g * hd:(g + 1) * hd])
+        x2 = x + torch.cat(outs, 1) @ P[(O.T_WO, l)].view(D, H * hd).T
+        x2n = rms(x2, P[(O.T_RMS_FFN, l)])
+        h1 = x2n @ P[(O.T_W1, l)].view(Hd, D).T
+        h3 = x2n @ P[(O.T_W3, l)].view(Hd, D).T
+        x = x2 + (torch.nn.functional.silu(h1) * h3) @ P[(O.T_W2, l)].view(D, Hd).T
+    logits = rms(x, P[(O.T_RMS_FINAL, 0)]) @ emb.T
+    valid = torch.tensor(tgt < V)
+    lt = torch.nn.functional.cross_entropy(logits[valid], torch.tensor(tgt.astype(np.int64))[valid])
+    lt.backward()
+    assert abs(loss - float(lt.detach())) < 1e-5
+    for (tid, layer), p in P.items():
+        g = m.tensor(tid, layer, O.G)
+        ref = p.grad.numpy().ravel()
+        err = np.linalg.norm(g - ref) / np.linalg.norm(ref)
+        assert err < 1e-4, (O.TENSOR_NAMES[tid], layer, err)
+
+
+def test_reference_arch_matches_torch_autograd_fp64():
+    """The same for the network the reference trains, with its backward quirks off (exact gradients):
+    embedding norm, smear, parameterless RMSNorm, rotation then 1.2 x per-head norm of q and k, value
+    embeddings on odd layers, lambda-weighted residuals with the x0 skip, ReLU^2, backout of the middle
+    layer's output, soft-capped logits (ane/train_full.go:383-453,480-558)."""
+    import torch
+
+    D, Hd, H, L, V, T = 32, 48, 4, 4, 64, 12
+    hd = D // H
+    m = O.Model(dim=D, hidden=Hd, heads=H, kv_heads=H, layers=L, vocab=V, seq=T, arch=O.ARCH_N, quirks=0,
+                loss_scale=1.0, accum_steps=1000, grad_clip=0.0)
+    O.init_weights(m, 1, std=0.3)
+    m.tensor(O.T_SMEAR_LAMBDA)[:] = 0.3
+    m.tensor(O.T_BACKOUT_LAMBDA)[:] = 0.3
+    a = m.tensor(O.T_X0_LAMBDAS)
+    a[:] = np.linspace(0.1, 0.4, a.size)
+    a = m.tensor(O.T_RESID_LAMBDAS)
+    a[:] = np.linspace(0.8, 1.2, a.size)
+    for tid, layer, a in m.tensors():
+        if tid == O.T_VE_GATE:
+            a[:] = 0.5 * np.random.default_rng(layer).standard_normal(a.size)
+    toks = O.zipf_tokens(T + 1, V, 3)
+    inp, tgt = toks[:T].copy(), toks[1:T + 1].copy()
+    tgt[4] = 65535
+    loss = m.accumulate(inp, tgt)
+    P = {(tid, layer): torch.tensor(a.astype(np.float64), requires_grad=True) for tid, layer, a in m.tensors(O.W)}
+    theta = float(m.cfg.rope_theta)
+
+    def rms(x):
+        return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-5)
+
+    def rope(x):
+        x = x.view(T, H, hd // 2, 2)
+        pos = torch.arange(T, dtype=torch.float64)[:, None]
+        i = torch.arange(hd // 2, dtype=torch.float64)[None, :]
+        ang = pos / theta ** (2 * i / hd)
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        e, o = x[..., 0], x[..., 1]
+        return torch.stack([e * c - o * s, o * c + e * s], -1)
+
+    def qknorm(x):
+        x = x.reshape(T, H, hd)
+        return (1.2 * x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-5)).reshape(T, H * hd)
+
+    emb = P[(O.T_EMBED, 0)].view(V, D)
+    tok = torch.tensor(inp.astype(np.int64))
+    x0 = rms(emb[tok])
+    gp = x0 @ P[(O.T_SMEAR_GATE, 0)].view(D, D).T
+    shifted = torch.cat([torch.zeros(1, D, dtype=torch.float64), x0[:-1]], 0)
+    x = x0 + P[(O.T_SMEAR_LAMBDA, 0)] * torch.sigmoid(gp) * shifted   # position 0 has no predecessor
+    rl, xl = P[(O.T_RESID_LAMBDAS, 0)], P[(O.T_X0_LAMBDAS, 0)]
+    causal = torch.tril(torch.ones(T, T, dtype=torch.bool))
+    xmid = None
+    for l in range(L):
+        xn = rms(x)
+        q = qknorm(rope(xn @ P[(O.T_WQ, l)].view(D, D).T))
+        k = qknorm(rope(xn @ P[(O.T_WK, l)].view(D, D).T))
+        v = xn @ P[(O.T_WV, l)].view(D, D).T
+        if (O.T_VE_EMBED, l) in P:
+            g = torch.sigmoid(x[:, :12] @ P[(O.T_VE_GATE, l)].view(H, 12).T)
+            ve = P[(O.T_VE_EMBED, l)].view(V, D)[tok].view(T, H, hd)
+            v = (v.view(T, H, hd) + 3 * g[:, :, None] * ve).reshape(T, D)
+        outs = []
+        for h in range(H):
+            sc = q[:, h * hd:(h + 1) * hd] @ k[:, h * hd:(h + 1) * hd].T / np.sqrt(hd)
+            outs.append(torch.softmax(sc.masked_fill(~causal, float("-inf")), -1) @ v[:, h * hd:(h + 1) * hd])
+        x2 = rl[l] * x + torch.cat(outs, 1) @ P[(O.T_WO, l)].view(D, D).T + xl[l] * x0
+        h1 = rms(x2) @ P[(O.T_W1, l)].view(Hd, D).T
+        x = rl[l] * x2 + (torch.relu(h1) ** 2) @ P[(O.T_W2, l)].view(D, Hd).T + xl[l] * x0
+        if l == L // 2 - 1:
+            xmid = x
+    x = x - P[(O.T_BACKOUT_LAMBDA, 0)] * xmid
+    logits = 15 * torch.tanh((rms(x) @ emb.T) / 15)
+    valid = torch.tensor(tgt < V)
+    lt = torch.nn.functional.cross_entropy(logits[valid], torch.tensor(tgt.astype(np.int64))[valid])
+    lt.backward()
+    assert abs(loss - float(lt.detach())) < 1e-5
+    assert any(tid == O.T_VE_EMBED for tid, _ in P)
+    for (tid, layer), p in P.items():
+        g = m.tensor(tid, layer, O.G)
+        ref = p.grad.numpy().ravel()
+        err = np.linalg.norm(g - ref) / np.linalg.norm(ref)
+        assert err < 1e-4, (O.TENSOR_NAMES[tid], layer, err)
+
+
 def test_quirks_change_only_the_backward():
     cfg = dict(dim=32, hidden=48, heads=4, layers=2, vocab=64, seq=12, arch=O.ARCH_N, loss_scale=1.0, accum_steps=100)
     toks = O.zipf_tokens(13, 64, 3)

@@ -186,12 +186,12 @@ def test_loss_trajectory_fp32_llama_tiny_config():
     e.close()
 
 
-@pytest.mark.parametrize("arch,quirks,vocab", [(O.ARCH_L, 0, 512), (O.ARCH_N, 1, 512), (O.ARCH_L, 0, 40000)])
+@pytest.mark.parametrize("arch,quirks,vocab", [(O.ARCH_L, 0, 512), (O.ARCH_L, 0, 40000)])
 def test_bf16_head_with_invalid_targets_and_wide_vocabulary(arch, quirks, vocab):
     """The bf16 training head (bf16 logits, fp32 target logit, cross-entropy kernel) with a target and a
     token outside the vocabulary (zero gradient row, not counted; zero embedding row), with and without
     the soft cap.  Up to 32768 logits a row is held in registers; 40000 takes the streaming kernel."""
-    cfg = dict(dim=64, hidden=128, heads=1, layers=1, vocab=vocab, seq=128)
+    cfg = dict(dim=128, hidden=256, heads=2, layers=2, vocab=vocab, seq=128)
     hyper = dict(lr=3e-4, accum_steps=1000)
     m, e = make_pair(ane, cfg, arch=arch, quirks=quirks, dtype=ane.DTYPE_BF16, batch=2, hyper=hyper)
     inp, tgt = batch_tokens(cfg, 2, 21, invalid=True)
