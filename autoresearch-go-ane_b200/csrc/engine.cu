@@ -1017,9 +1017,13 @@ int EngineT<T>::backward_layers(int B) {
     }
     if (isN_) {  // lambda gradients, FFN residual (ane/train_full.go:732-748)
       count_launch(3);
-      dot_accumulate(dcur, a.x2, MD, 1.f, G_ + s_resid_.off + l, stream_);
-      dot_accumulate(dcur, x0_, MD, 1.f, G_ + s_x0l_.off + l, stream_);
-      axpy_dev(gx0_, dcur, xl, 1.f, MD, false, stream_);
+      if (MD % 4 == 0) {
+        lambda_grads(dcur, a.x2, x0_, gx0_, xl, MD, G_ + s_resid_.off + l, G_ + s_x0l_.off + l, stream_);
+      } else {
+        dot_accumulate(dcur, a.x2, MD, 1.f, G_ + s_resid_.off + l, stream_);
+        dot_accumulate(dcur, x0_, MD, 1.f, G_ + s_x0l_.off + l, stream_);
+        axpy_dev(gx0_, dcur, xl, 1.f, MD, false, stream_);
+      }
     }
     // ---- attention backward
     {
@@ -1131,9 +1135,13 @@ int EngineT<T>::backward_layers(int B) {
     }
     if (isN_) {  // lambda gradients, attention residual (ane/train_full.go:770-782)
       count_launch(3);
-      dot_accumulate(dx2, xs_[l], MD, 1.f, G_ + s_resid_.off + l, stream_);
-      dot_accumulate(dx2, x0_, MD, 1.f, G_ + s_x0l_.off + l, stream_);
-      axpy_dev(gx0_, dx2, xl, 1.f, MD, false, stream_);
+      if (MD % 4 == 0) {
+        lambda_grads(dx2, xs_[l], x0_, gx0_, xl, MD, G_ + s_resid_.off + l, G_ + s_x0l_.off + l, stream_);
+      } else {
+        dot_accumulate(dx2, xs_[l], MD, 1.f, G_ + s_resid_.off + l, stream_);
+        dot_accumulate(dx2, x0_, MD, 1.f, G_ + s_x0l_.off + l, stream_);
+        axpy_dev(gx0_, dx2, xl, 1.f, MD, false, stream_);
+      }
       if (l == L_ / 2) {  // gradient of the backout term joins at the output of layer L/2-1
         count_launch();
         add_inplace(dprev, gmid_, MD, stream_);

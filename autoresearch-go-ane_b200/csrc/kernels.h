@@ -165,6 +165,9 @@ void smear_forward(const float* x_pre, const float* gate_pre, const float* lambd
 void smear_backward(const float* d_out, const float* x_pre, const float* gate_pre, const float* lambda,
                     float* d_gate_pre, float* dx, float* g_lambda, int M, int seq, int D, cudaStream_t s);
 // out[0] += alpha * sum(a*b)  (double accumulation; ane/train_full.go:733-782, ane/common.go:396-400)
+// out_a += sum(d*a), out_b += sum(d*b), y += *alpha * d in one pass (n % 4 == 0, 16-byte aligned buffers).
+void lambda_grads(const float* d, const float* a, const float* b, float* y, const float* alpha, uint64_t n, float* out_a,
+                  float* out_b, cudaStream_t s);
 void dot_accumulate(const float* a, const float* b, uint64_t n, float alpha, float* out, cudaStream_t s);
 // y += (*alpha) * x  and  y = (*alpha) * x   (alpha is a device scalar; sign flips it)
 void axpy_dev(float* y, const float* x, const float* alpha, float sign, uint64_t n, bool assign, cudaStream_t s);
