@@ -831,14 +831,21 @@ int EngineT<T>::forward(const uint16_t* d_tok, int B, int Tl, int pos0) {
       // 32-row blocks, so every 64-column piece of h13 holds matching h1 and h3 columns).
       static const bool no_fuse_gate = getenv("ANE_B200_NO_FUSE_SWIGLU") != nullptr;  // A/B measurements
       const bool fused_gate = !kIsF32 && !isN_ && !no_fuse_gate && Hd_ % 64 == 0;
+      // reference arch, bf16: gate = max(h1, 0)^2 from the same epilogue
+      static const bool no_fuse_relu2 = getenv("ANE_B200_NO_FUSE_RELU2") != nullptr;  // A/B measurements
+      const bool fused_relu2 = !kIsF32 && isN_ && !no_fuse_relu2 && Hd_ % 8 == 0;
       if (fused_gate) {
         g.out = GEMM_OUT_BF16_SWIGLU;
+        g.aux = a.gate;
+        g.ldaux = Hd_;
+      } else if (fused_relu2) {
+        g.out = GEMM_OUT_BF16_RELU2;
         g.aux = a.gate;
         g.ldaux = Hd_;
       }
       count_launch();
       if ((rc = gemm(g)) != 0) return rc;
-      if (!fused_gate) {
+      if (!fused_gate && !fused_relu2) {
         count_launch();
         if (isN_) relu2_forward<T>(a.h13, a.gate, (uint64_t)M * Hd_, stream_);
         else swiglu_forward<T>(a.h13, a.gate, M, Hd_, stream_);

@@ -225,6 +225,17 @@ static int dispatch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
       return -2;
     }
   }
+  if (d.out == GEMM_OUT_BF16_RELU2) {
+    if constexpr (!A_MN && !B_MN) {
+      CUtensorMap td;  // gate [M, N], same pieces as C
+      if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 64, 32, false) || !make_tmap(&td, d.aux, d.N, d.M, d.ldaux, 64, 32, false))
+        return -2;
+      return launch_tc<BN, MT, A_MN, B_MN, EPI_STORE_BF16_RELU2>(ta, tb, tc, td, epi, d, 1, d_status, stream);
+    } else {
+      g_gemm_err = "the ReLU^2 epilogue takes K-major operands only";
+      return -2;
+    }
+  }
   if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 32, 32, true)) return -2;
   if (d.out == GEMM_OUT_F32) {
     // One residual, K-major operands and room for the residual buffers: let TMA fetch the residual pieces.
@@ -394,6 +405,10 @@ int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream) {
   if (d.out == GEMM_OUT_BF16_SWIGLU && (d.aux == nullptr || d.N % 128 != 0 || d.ldaux % 8 != 0 ||
                                         (reinterpret_cast<uintptr_t>(d.aux) & 15) != 0)) {
     g_gemm_err = "SwiGLU epilogue: N must be a multiple of 128 and the gate buffer 16-byte aligned with ldaux % 8 == 0";
+    return -2;
+  }
+  if (d.out == GEMM_OUT_BF16_RELU2 && (d.aux == nullptr || d.ldaux % 8 != 0 || (reinterpret_cast<uintptr_t>(d.aux) & 15) != 0)) {
+    g_gemm_err = "ReLU^2 epilogue: the gate buffer must be 16-byte aligned with ldaux % 8 == 0";
     return -2;
   }
   if (d.out == GEMM_OUT_BF16_ROPE &&

@@ -30,6 +30,9 @@ enum GemmOut : int {
   // that one element in fp32 into tgt_out[tgt_row0 + row]: classifier logits for the cross-entropy, which
   // then reads bf16 logits but takes the target logit at full precision.  K-major operands only.
   GEMM_OUT_BF16_TGT = 5,
+  // store bf16 (h) and also gate = max(h, 0)^2, taken from the fp32 accumulators, into `aux` [M, N] (bf16, row
+  // pitch ldaux): the reference architecture's FFN activation (ane/common.go:146).  K-major operands only.
+  GEMM_OUT_BF16_RELU2 = 6,
 };
 
 struct GemmDesc {
@@ -46,7 +49,7 @@ struct GemmDesc {
   const float* res2 = nullptr;
   const float* s2 = nullptr;
   int ldres = 0;
-  void* aux = nullptr;  // GEMM_OUT_BF16_SWIGLU: gate output
+  void* aux = nullptr;  // GEMM_OUT_BF16_SWIGLU, GEMM_OUT_BF16_RELU2: gate output
   int ldaux = 0;
   const float* rope_cos = nullptr;  // GEMM_OUT_BF16_ROPE
   const float* rope_sin = nullptr;

@@ -106,6 +106,8 @@ enum EpiKind : int {
   EPI_STORE_F32_TMARES = 5,
   // EPI_STORE_BF16 that also writes the accumulator of each row's target column in fp32.
   EPI_STORE_BF16_TGT = 6,
+  // EPI_STORE_BF16 plus gate = max(h, 0)^2 of every 64-column piece, staged as one more piece (tmD: gate [M, N]).
+  EPI_STORE_BF16_RELU2 = 7,
 };
 struct EpiParams {
   float alpha;
@@ -114,7 +116,7 @@ struct EpiParams {
   const float* res2;
   const float* s2;
   int ldres;
-  bf16* aux;   // EPI_STORE_BF16_SWIGLU: gate [M, N/2]
+  bf16* aux;   // EPI_STORE_BF16_SWIGLU: gate [M, N/2]; EPI_STORE_BF16_RELU2: gate [M, N]
   int ldaux;
   const float* rope_cos;  // EPI_STORE_BF16_ROPE: [positions, 32]
   const float* rope_sin;
@@ -381,7 +383,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, 32*lane_group+32)
     // Columns per staged piece: 128 bytes of output per row.
     constexpr bool kBf16Out = (EPI == EPI_STORE_BF16 || EPI == EPI_STORE_BF16_SWIGLU || EPI == EPI_STORE_BF16_ROPE ||
-                               EPI == EPI_STORE_BF16_TGT);
+                               EPI == EPI_STORE_BF16_TGT || EPI == EPI_STORE_BF16_RELU2);
     constexpr int CW = kBf16Out ? 64 : 32;
     constexpr int SBUF = Cfg::SBUF;
     const uint32_t stage_base = smem_stage0 + (uint32_t)(warp - 2) * (uint32_t)(SBUF * 4096);
@@ -563,6 +565,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               __syncwarp();
               row_ptr = stage_ptr + sbuf * 4096 + lane * 128;
             }
+          }
+          if constexpr (EPI == EPI_STORE_BF16_RELU2) {
+            // gate piece first (this buffer), then the h piece takes the next buffer of the rotation
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              float g[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float h = fmaxf(epi.alpha * acc[8 * q + e], 0.f);
+                g[e] = h * h;
+              }
+              *reinterpret_cast<uint4*>(row_ptr + ((q ^ (lane & 7)) << 4)) =
+                  make_uint4(pack2_bf16(g[0], g[1]), pack2_bf16(g[2], g[3]), pack2_bf16(g[4], g[5]), pack2_bf16(g[6], g[7]));
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmD, stage_base + (uint32_t)sbuf * 4096u, n0, m_warp);
+              tma_store_commit();
+              tma_store_wait_read<SBUF - 1>();  // the next buffer in the rotation is free again
+            }
+            sbuf = (sbuf + 1) % SBUF;
+            __syncwarp();
+            row_ptr = stage_ptr + sbuf * 4096 + lane * 128;
           }
 #pragma unroll
           for (int q = 0; q < 8; ++q) {  // 8 chunks of 8 bf16
