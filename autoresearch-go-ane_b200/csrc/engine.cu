@@ -17,7 +17,9 @@
 #include <string.h>
 
 #include <algorithm>
+#include <atomic>
 #include <chrono>
+#include <thread>
 
 #include "common.cuh"
 #include "dp.h"
@@ -282,7 +284,7 @@ class EngineT final : public EngineBase {
   T* dlogits2_ = nullptr;                  // second chunk buffer: the classifier dW GEMM of chunk c runs on the
   cudaEvent_t ev_cls_ce_[2] = {nullptr, nullptr};  // side stream while chunk c+1 is computed
   cudaEvent_t ev_cls_dw_[2] = {nullptr, nullptr};
-  cudaEvent_t ev_logits_[8] = {};          // EvalLogits: one per downloaded piece
+  cudaEvent_t ev_logits_[16] = {};          // EvalLogits: one per downloaded piece
   float *rope_cos_ = nullptr, *rope_sin_ = nullptr;
   double* d_acc_ = nullptr;
   float *d_scales_ = nullptr, *d_norm_ = nullptr;
@@ -1479,9 +1481,11 @@ int EngineT<T>::eval_logits(const uint16_t* tokens, uint32_t n_seq, float* out, 
         softcap_inplace(logits_, per_seq, stream_);
       }
       // device -> pinned staging (full PCIe rate) -> caller's buffer, in pieces: the host copies piece i
-      // out of the staging buffer while pieces i+1.. are still crossing PCIe
-      constexpr int kPieces = 8;
+      // out of the staging buffer while pieces i+1.. are still crossing PCIe.  One core copies ~10 GB/s, a
+      // fifth of the PCIe rate, so the pieces are dealt to a few threads (ANE_B200_EVAL_COPY_THREADS, default 4).
+      constexpr int kPieces = 16;
       const uint64_t piece = (per_seq + kPieces - 1) / kPieces;
+      int n_pieces = 0;
       for (int pi = 0; pi < kPieces; ++pi) {
         const uint64_t off = (uint64_t)pi * piece;
         if (off >= per_seq) break;
@@ -1490,14 +1494,35 @@ int EngineT<T>::eval_logits(const uint16_t* tokens, uint32_t n_seq, float* out, 
                                              stream_), "logits download")) != 0)
           return rc;
         cudaEventRecord(ev_logits_[pi], stream_);
+        ++n_pieces;
       }
-      for (int pi = 0; pi < kPieces; ++pi) {
-        const uint64_t off = (uint64_t)pi * piece;
-        if (off >= per_seq) break;
-        const uint64_t n = std::min(piece, per_seq - off);
-        if ((rc = cuda_check(cudaEventSynchronize(ev_logits_[pi]), "logits sync")) != 0) return rc;
-        memcpy(out + (size_t)(s0 + b) * per_seq + off, h_logits_ + off, sizeof(float) * n);
-      }
+      static const int copy_threads = [] {
+        const char* e = getenv("ANE_B200_EVAL_COPY_THREADS");
+        const int v = e ? atoi(e) : 4;
+        return v < 1 ? 1 : (v > 8 ? 8 : v);
+      }();
+      float* dst = out + (size_t)(s0 + b) * per_seq;
+      std::atomic<int> copy_err{0};
+      auto copy_share = [&](int t) {  // pieces t, t + threads, ...: every thread's last piece is a late one
+        if (t > 0 && cudaSetDevice(o_.device) != cudaSuccess) {
+          copy_err.store(1);
+          return;
+        }
+        for (int pi = t; pi < n_pieces; pi += copy_threads) {
+          const uint64_t off = (uint64_t)pi * piece;
+          const uint64_t n = std::min(piece, per_seq - off);
+          if (cudaEventSynchronize(ev_logits_[pi]) != cudaSuccess) {
+            copy_err.store(1);
+            return;
+          }
+          memcpy(dst + off, h_logits_ + off, sizeof(float) * n);
+        }
+      };
+      std::vector<std::thread> helpers;
+      for (int t = 1; t < copy_threads && t < n_pieces; ++t) helpers.emplace_back(copy_share, t);
+      copy_share(0);
+      for (auto& h : helpers) h.join();
+      if (copy_err.load() != 0) return cuda_check(cudaErrorUnknown, "logits sync");
     }
   }
   return check_device_status(nullptr);
