@@ -1502,13 +1502,15 @@ int EngineT<T>::eval_logits(const uint16_t* tokens, uint32_t n_seq, float* out, 
         return v < 1 ? 1 : (v > 8 ? 8 : v);
       }();
       float* dst = out + (size_t)(s0 + b) * per_seq;
+      // small outputs (under 1 MiB) are not worth a thread start
+      const int use_threads = per_seq * sizeof(float) < (1u << 20) ? 1 : copy_threads;
       std::atomic<int> copy_err{0};
       auto copy_share = [&](int t) {  // pieces t, t + threads, ...: every thread's last piece is a late one
         if (t > 0 && cudaSetDevice(o_.device) != cudaSuccess) {
           copy_err.store(1);
           return;
         }
-        for (int pi = t; pi < n_pieces; pi += copy_threads) {
+        for (int pi = t; pi < n_pieces; pi += use_threads) {
           const uint64_t off = (uint64_t)pi * piece;
           const uint64_t n = std::min(piece, per_seq - off);
           if (cudaEventSynchronize(ev_logits_[pi]) != cudaSuccess) {
@@ -1519,7 +1521,7 @@ int EngineT<T>::eval_logits(const uint16_t* tokens, uint32_t n_seq, float* out, 
         }
       };
       std::vector<std::thread> helpers;
-      for (int t = 1; t < copy_threads && t < n_pieces; ++t) helpers.emplace_back(copy_share, t);
+      for (int t = 1; t < use_threads && t < n_pieces; ++t) helpers.emplace_back(copy_share, t);
       copy_share(0);
       for (auto& h : helpers) h.join();
       if (copy_err.load() != 0) return cuda_check(cudaErrorUnknown, "logits sync");

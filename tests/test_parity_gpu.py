@@ -53,7 +53,12 @@ def tap_errors(m, e, cfg, batch, taps):
     return worst
 
 
-@pytest.mark.parametrize("arch,quirks,extra", [(O.ARCH_L, 0, {"kv_heads": 2}), (O.ARCH_N, 1, {}), (O.ARCH_N, 0, {})])
+# head size 64 in fp32 mode takes the head-64 forms of the rotation / QK-norm backward
+HD64 = {"dim": 128, "heads": 2, "layers": 2}
+
+
+@pytest.mark.parametrize("arch,quirks,extra", [(O.ARCH_L, 0, {"kv_heads": 2}), (O.ARCH_N, 1, {}), (O.ARCH_N, 0, {}),
+                                               (O.ARCH_L, 0, dict(HD64, kv_heads=1)), (O.ARCH_N, 1, HD64)])
 def test_fp32_step_matches_oracle(arch, quirks, extra):
     cfg = dict(TINY, **extra)
     hyper = dict(lr=1e-3, adam_beta1=0.9, adam_beta2=0.95, weight_decay=0.1, grad_clip=1.0, accum_steps=1000)
