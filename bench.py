@@ -101,6 +101,11 @@ class ClockSampler:
                 ["nvidia-smi", f"--id={self.device}", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
+            # nvidia-smi needs 0.1-0.3 s before its first line: wait for it here, outside every timed region, so that
+            # even a short timed region (ten steps are 80 ms) holds samples
+            t0 = time.perf_counter()
+            while not self.lines and time.perf_counter() - t0 < 3.0:
+                time.sleep(0.01)
         except Exception:
             self.proc = None
 
@@ -125,6 +130,10 @@ class ClockSampler:
         sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         picked = [ln for a, b in self.windows for ln in self.lines[a:b]]
+        window = "timed region of the device-resident leg, one sample per 20 ms"
+        if not picked:  # region shorter than one sampling period: fall back to everything since the warm-up began
+            picked = list(self.lines)
+            window = "warm-up and timed region of the device-resident leg (no sample fell inside the timed region alone)"
         for ln in picked:
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 7:
@@ -141,7 +150,7 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_min_mhz": min(sm) if sm else None,
                 "sm_max_mhz": max(mx) if mx else None, "power_w": float(np.median(pw)) if pw else None,
                 "reasons": sorted(reasons), "samples": len(sm),
-                "window": "timed region of the device-resident leg, one sample per 20 ms"}
+                "window": window}
 
 
 def init_weights(engine, ane, seed, cfg):
