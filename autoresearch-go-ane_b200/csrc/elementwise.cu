@@ -347,6 +347,46 @@ void rope_qknorm_forward_hd64(float* qkv, float* qk_pre, const float* cosb, cons
                                                                                          KV, qk_norm, pos0, hi_out);
 }
 
+// Eight values of a row as fp32, from 16 bytes of bf16 or 32 bytes of fp32, and back.
+template <typename TI>
+__device__ __forceinline__ void load8(const TI* p, float* v);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float* v) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<bf16>(const bf16* p, float* v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 f = __bfloat1622float2(h[k]);
+    v[2 * k] = f.x;
+    v[2 * k + 1] = f.y;
+  }
+}
+template <typename TO>
+__device__ __forceinline__ void store8(TO* p, const float* v);
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float* v) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void store8<bf16>(bf16* p, const float* v) {
+  uint4 u;
+  __nv_bfloat162 t;
+  t = __floats2bfloat162_rn(v[0], v[1]); u.x = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2bfloat162_rn(v[2], v[3]); u.y = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2bfloat162_rn(v[4], v[5]); u.z = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2bfloat162_rn(v[6], v[7]); u.w = *reinterpret_cast<uint32_t*>(&t);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// A warp takes four consecutive heads of one token; eight lanes share a head, each with eight consecutive
+// elements (four rotation pairs), so the two per-head sums of the QK-norm backward are three-step
+// reductions over eight lanes and every access is 16 or 32 bytes wide.
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 rope_qknorm_backward_hd64_kernel(const TI* din, float* out_f32, const float* __restrict__ qk_pre,
@@ -358,47 +398,53 @@ rope_qknorm_backward_hd64_kernel(const TI* din, float* out_f32, const float* __r
   const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (wid >= (long long)M * groups) return;
-  const int m = (int)(wid / groups), h0 = (int)(wid - (long long)m * groups) * G;
+  const int m = (int)(wid / groups);
+  const int head = (int)(wid - (long long)m * groups) * G + (lane >> 3);
+  const int part = lane & 7;  // elements [8 * part, 8 * part + 8) of the head
   const int t = m % seq;
-  const size_t row = (size_t)m * slots * HD;
-  float2 g[G], x[G];
+  const bool live = head < slots, qk = head < heads;
+  const size_t off = (size_t)m * slots * HD + (size_t)head * HD + 8 * part;
+  float g[8], x[8];
 #pragma unroll
-  for (int q = 0; q < G; ++q) {
-    const int head = h0 + q;
-    g[q] = head < slots ? load_pair<TI>(din + row + (size_t)head * HD + 2 * lane) : make_float2(0.f, 0.f);
-    x[q] = (qk_norm && head < heads) ? load_pair<float>(qk_pre + (size_t)m * heads * HD + (size_t)head * HD + 2 * lane)
-                                     : make_float2(0.f, 0.f);
-  }
-  float c = 1.f, s = 0.f;
-  if (!skip_rope) {
-    c = cosb[t * (HD / 2) + lane];
-    s = sinb[t * (HD / 2) + lane];
-  }
+  for (int k = 0; k < 8; ++k) g[k] = x[k] = 0.f;
+  if (live) load8<TI>(din + off, g);
+  if (qk && qk_norm) load8<float>(qk_pre + (size_t)m * heads * HD + (size_t)head * HD + 8 * part, x);
+  if (qk_norm) {  // warp-uniform: lanes of v heads and of missing heads add zeros
+    float ss = 0.f, dot = 0.f;
 #pragma unroll
-  for (int q = 0; q < G; ++q) {
-    const int head = h0 + q;
-    if (head >= slots) break;
-    float e = g[q].x, o = g[q].y;
-    if (head < heads) {
-      if (qk_norm) {
-        const float ss = warp_sum(x[q].x * x[q].x + x[q].y * x[q].y);
-        const float dot = warp_sum(e * x[q].x + o * x[q].y);
-        const float qs = 1.2f;
-        const float r = 1.0f / sqrtf(ss / (float)HD + 1e-5f);
-        float coeff = dot * r * r * r / (float)HD * qs;
-        if (reference_coeff) coeff *= qs;
-        e = e * r * qs - coeff * x[q].x;
-        o = o * r * qs - coeff * x[q].y;
-      }
-      const float e2 = e * c + o * s, o2 = o * c - e * s;
-      e = e2;
-      o = o2;
+    for (int k = 0; k < 8; ++k) {
+      ss += x[k] * x[k];
+      dot += g[k] * x[k];
     }
-    const size_t off = row + (size_t)head * HD + 2 * lane;
-    // v heads pass through unchanged: nothing to write when the fp32 output is the input itself
-    if (out_f32 && (head < heads || (const void*)out_f32 != (const void*)din)) store_pair<float>(out_f32 + off, e, o);
-    if (out_t) store_pair<TO>(out_t + off, e, o);
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+      ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    }
+    if (qk) {
+      const float qs = 1.2f;
+      const float r = 1.0f / sqrtf(ss / (float)HD + 1e-5f);
+      float coeff = dot * r * r * r / (float)HD * qs;
+      if (reference_coeff) coeff *= qs;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) g[k] = g[k] * r * qs - coeff * x[k];
+    }
   }
+  if (!live) return;
+  if (qk && !skip_rope) {
+    const float4 c4 = *reinterpret_cast<const float4*>(cosb + t * (HD / 2) + 4 * part);
+    const float4 s4 = *reinterpret_cast<const float4*>(sinb + t * (HD / 2) + 4 * part);
+    const float c[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const float e = g[2 * p], o = g[2 * p + 1];
+      g[2 * p] = e * c[p] + o * sn[p];
+      g[2 * p + 1] = o * c[p] - e * sn[p];
+    }
+  }
+  // v heads pass through unchanged: nothing to write when the fp32 output is the input itself
+  if (out_f32 && (qk || (const void*)out_f32 != (const void*)din)) store8<float>(out_f32 + off, g);
+  if (out_t) store8<TO>(out_t + off, g);
 }
 
 template <typename TI, typename TO>
