@@ -104,6 +104,7 @@ SIGNATURES = {
     "ane_get_lr": (c_float, [c_void_p]),
     "ane_get_state": (c_int32, [c_void_p, POINTER(State)]),
     "ane_set_state": (c_int32, [c_void_p, POINTER(State)]),
+    "ane_reseed": (c_int32, [c_void_p, c_int64]),
     "ane_tensor_size": (c_int64, [c_void_p, c_uint32, c_uint32]),
     "ane_import_tensor": (c_int32, [c_void_p, c_uint32, c_uint32, c_uint32, POINTER(c_float), c_uint64]),
     "ane_export_tensor": (c_int32, [c_void_p, c_uint32, c_uint32, c_uint32, POINTER(c_float), c_uint64]),

@@ -178,10 +178,71 @@ def _read_into(f, n: int) -> np.ndarray:
     return a
 
 
+def load_weights_and_moments(engine, path: str) -> TrainMeta:
+    """stories.LoadCheckpoint as ane.Open uses it on a ModelPath that is not a llama2.c file
+    (ane/engine.go:252): weights and Adam moments only; counters, learning rate and trailer stay untouched."""
+    engine._alive("open")
+    d = dims_of(engine)
+    with open(path, "rb") as f:
+        ver, meta = unpack_header(f.read(HEADER_BYTES), d)
+        if (ver == CKPT_VERSION_V5) != (d.arch == ARCH_REFERENCE):
+            raise ValueError("checkpoint config mismatch")
+        for t, l, which in sections(d):
+            n = engine.tensor_size(t, l)
+            if n > 0:
+                engine.import_tensor(t, l, _read_into(f, n), which)
+    return meta
+
+
+def random_init(engine, seed: int) -> None:
+    """Fresh weights with the distributions of stories.RandomInit (ane/stories/weights.go:165-210) for the
+    reference architecture: Wq/Wk/Wv/W1/value embeddings uniform in +-sqrt(3/dim), Wo and W2 zero, value-embedding
+    gates uniform in [0, 0.02), embedding standard normal, residual lambdas 1, x0 lambdas 0.1, smear gate
+    uniform in +-1/sqrt(dim), smear and backout lambdas 0.01.  Go's math/rand stream is not
+    restated, so the values are statistically, not bitwise, those of the reference for the same seed.  The
+    llama-style architecture gets N(0, 0.02) matrices and unit norm weights."""
+    engine._alive("random init")
+    d = dims_of(engine)
+    rng = np.random.default_rng(seed)
+    hd = d.dim // d.heads
+    kvd = (engine.opts.n_kv_heads or d.heads) * hd
+    if d.arch == ARCH_REFERENCE:
+        s = float(np.sqrt(3.0) / np.sqrt(d.dim))
+        uni = lambda n, a: (a * (2.0 * rng.random(n, dtype=np.float32) - 1.0)).astype(np.float32)  # noqa: E731
+        for l in range(d.layers):
+            engine.import_tensor(E.T_WQ, l, uni(d.dim * d.dim, s))
+            engine.import_tensor(E.T_WK, l, uni(kvd * d.dim, s))
+            engine.import_tensor(E.T_WV, l, uni(kvd * d.dim, s))
+            engine.import_tensor(E.T_WO, l, np.zeros(d.dim * d.dim, np.float32))
+            engine.import_tensor(E.T_W1, l, uni(d.hidden * d.dim, s))
+            engine.import_tensor(E.T_W2, l, np.zeros(d.dim * d.hidden, np.float32))
+            if is_ve_layer(l, d):
+                engine.import_tensor(E.T_VE_EMBED, l, uni(d.vocab * d.dim, s))
+                engine.import_tensor(E.T_VE_GATE, l, (0.02 * rng.random(d.heads * 12, dtype=np.float32)))
+        engine.import_tensor(E.T_EMBED, 0, rng.standard_normal(d.vocab * d.dim, dtype=np.float32))
+        engine.import_tensor(E.T_RESID_LAMBDAS, 0, np.ones(d.layers, np.float32))
+        engine.import_tensor(E.T_X0_LAMBDAS, 0, np.full(d.layers, 0.1, np.float32))
+        engine.import_tensor(E.T_SMEAR_GATE, 0, uni(d.dim * d.dim, float(1.0 / np.sqrt(d.dim))))
+        engine.import_tensor(E.T_SMEAR_LAMBDA, 0, np.full(1, 0.01, np.float32))
+        engine.import_tensor(E.T_BACKOUT_LAMBDA, 0, np.full(1, 0.01, np.float32))
+        return
+    nrm = lambda n: (0.02 * rng.standard_normal(n, dtype=np.float32)).astype(np.float32)  # noqa: E731
+    for l in range(d.layers):
+        engine.import_tensor(E.T_WQ, l, nrm(d.dim * d.dim))
+        engine.import_tensor(E.T_WK, l, nrm(kvd * d.dim))
+        engine.import_tensor(E.T_WV, l, nrm(kvd * d.dim))
+        engine.import_tensor(E.T_WO, l, nrm(d.dim * d.dim))
+        engine.import_tensor(E.T_W1, l, nrm(d.hidden * d.dim))
+        engine.import_tensor(E.T_W3, l, nrm(d.hidden * d.dim))
+        engine.import_tensor(E.T_W2, l, nrm(d.dim * d.hidden))
+    engine.import_tensor(E.T_EMBED, 0, nrm(d.vocab * d.dim))
+
+
 def load_checkpoint(engine, path: str) -> TrainMeta:
     """Engine.LoadCheckpoint (ane/engine.go:534-565): weights, Adam moments, lr and counters from the file;
     pending gradients are cleared and then restored from a version-2 trailer when one follows; a missing
-    trailer or a foreign magic is not an error (ane/engine.go:726-735)."""
+    trailer or a foreign magic is not an error (ane/engine.go:726-735).  The window sampler restarts from
+    drand48Seed(seed + meta.step) and the wall clock continues from the stored total (ane/engine.go:559-560)."""
     engine._alive("load checkpoint")
     d = dims_of(engine)
     with open(path, "rb") as f:
@@ -211,6 +272,7 @@ def load_checkpoint(engine, path: str) -> TrainMeta:
                 engine.import_tensor(t, l, _read_into(f, n) if grads is not None else np.zeros(n, np.float32), which)
     engine.set_lr(meta.lr)
     engine.load_state(st)
+    engine.reseed((engine.opts.seed or 42) + meta.step)
     return meta
 
 

@@ -28,7 +28,10 @@ class EngineError(RuntimeError):
 
 @dataclass
 class Options:
-    """ane.Options (ane/engine.go:14-40) plus the runtime model dimensions."""
+    """ane.Options (ane/engine.go:14-40) plus the runtime model dimensions.  `model_path` is the
+    reference's ModelPath: a llama2.c model file or a checkpoint, loaded by open() (ane/engine.go:250-257);
+    left empty, the engine starts from zero weights and the caller imports tensors (tests do)."""
+    model_path: str = ""
     tokens: np.ndarray | None = None
     seq: int = 0
     accum_steps: int = 0
@@ -133,7 +136,23 @@ class Engine:
         rc = lib.ane_open(byref(o), tok_ptr, n_tok, dp, byref(h))
         if rc != 0:
             raise EngineError(rc, lib.ane_last_error(None).decode())
-        return Engine(h, opts)
+        eng = Engine(h, opts)
+        if opts.model_path:
+            # ane/engine.go:250-257: a llama2.c model file first, else a training checkpoint (weights and
+            # optimizer state only: Open does not restore counters, the trailer or the learning rate)
+            from . import checkpoint
+            try:
+                try:
+                    checkpoint.load_pretrained(eng, opts.model_path)
+                except (ValueError, OSError) as first:
+                    try:
+                        checkpoint.load_weights_and_moments(eng, opts.model_path)
+                    except (ValueError, OSError):
+                        raise EngineError(-1, f"storiesane open: load model: {first}") from first
+            except Exception:
+                eng.close()
+                raise
+        return eng
 
     def _check(self, rc: int):
         if rc != 0:
@@ -264,6 +283,11 @@ class Engine:
                   "pending_steps"):
             setattr(s, k, getattr(st, k))
         self._check(lib.ane_set_state(self._h, byref(s)))
+
+    def reseed(self, seed: int):
+        """Restart the window sampler from drand48Seed(seed) (ane/engine.go:559, :873)."""
+        self._alive("reseed")
+        self._check(lib.ane_reseed(self._h, int(seed)))
 
     # -- tensors and taps
     def tensor_size(self, tid: int, layer: int = 0) -> int:

@@ -26,6 +26,7 @@ EVAL_SEQ_LEN = 256          # harness.go:37
 AVG_BYTES_PER_TOKEN = 3.7   # harness.go:43
 WARMUP_FRACTION = 0.05      # experiment.go:41
 WARMUP_STEPS = 3            # program.md:31: the budget excludes the first three steps
+LR_FLOOR_FRACTION = 1e-3    # SetLR rejects lr <= 0 (ane/engine.go:370-372): the ramp starts at peak/1000
 
 
 def load_tokens(path: str) -> np.ndarray:
@@ -46,9 +47,34 @@ def eval_windows(tokens: np.ndarray, eval_tokens: int = EVAL_TOKENS, seq: int = 
     return np.stack([val[p:p + seq] for p in starts]) if len(starts) else np.zeros((0, seq), np.uint16)
 
 
-def eval_loss(engine, tokens: np.ndarray, eval_tokens: int = EVAL_TOKENS) -> float:
-    """Mean next-token cross-entropy in nats over the validation windows (harness.go:46-89)."""
+def _eval_loss_reference_indexing(engine, windows: np.ndarray) -> float:
+    """harness.go:58-84 as written: EvalLogits returns [vocab][seq] (logits[v*seq+t]) but the loop slices it as
+    logits[t*vocab:(t+1)*vocab], and the running maximum starts at the smallest positive float64
+    (math.SmallestNonzeroFloat64), so a row of negative values keeps that start value.  Reproduces the reference's
+    val_loss / val_bpb for regression comparisons with numbers from its own harness."""
+    total, positions = 0.0, 0
+    seq, vocab = engine.seq, engine.vocab
+    tiny = np.float64(5e-324)
+    for w in windows:
+        flat = engine.eval_logits(w, layout=0).reshape(-1).astype(np.float64)
+        rows = flat.reshape(seq, vocab)[:seq - 1]          # the reference's slicing of the flat buffer
+        targets = w[1:seq].astype(np.int64)
+        mx = np.maximum(rows.max(axis=1), tiny)
+        lse = mx + np.log(np.exp(rows - mx[:, None]).sum(axis=1))
+        total += float((lse - rows[np.arange(seq - 1), targets]).sum())
+        positions += seq - 1
+    if positions == 0:
+        raise ValueError("eval: no positions evaluated")
+    return total / positions
+
+
+def eval_loss(engine, tokens: np.ndarray, eval_tokens: int = EVAL_TOKENS, reference_indexing: bool = False) -> float:
+    """Mean next-token cross-entropy in nats over the validation windows (harness.go:46-89).
+    reference_indexing=True walks the downloaded logits exactly like the reference's loop does (see
+    _eval_loss_reference_indexing); the default scores position t with the logits of position t on the device."""
     windows = eval_windows(np.asarray(tokens, dtype=np.uint16), eval_tokens, engine.seq)
+    if reference_indexing:
+        return _eval_loss_reference_indexing(engine, windows)
     total, positions = 0.0, 0
     batch = max(1, engine.opts.batch)
     for i in range(0, len(windows), batch):
@@ -89,13 +115,16 @@ def train(engine, budget_s: float | None = None, max_steps: int | None = None, p
           clock=time.perf_counter) -> TrainLog:
     """Runs Step() until the wall-clock budget (or step count) is used up.  Progress for the schedule is
     elapsed / budget when a budget is given, else step / max_steps.  The first WARMUP_STEPS steps run at the
-    schedule's progress 0 value and are not counted against the budget or in the throughput."""
+    start of the ramp and are not counted against the budget or in the throughput.  The schedule is 0 at
+    progress 0 and SetLR refuses lr <= 0 (ane/engine.go:370-372), so values below peak_lr * LR_FLOOR_FRACTION
+    are raised to that floor."""
     if budget_s is None and max_steps is None:
         raise ValueError("train: give a time budget or a step count")
     log = TrainLog()
     tokens_per_step = engine.opts.batch * engine.seq * max(1, engine.opts.world_size)
+    floor = peak_lr * LR_FLOOR_FRACTION
     for _ in range(WARMUP_STEPS):
-        engine.set_lr(lr_schedule(0.0, peak_lr))
+        engine.set_lr(max(lr_schedule(0.0, peak_lr), floor))
         engine.step()
     t0 = clock()
     while True:
@@ -108,7 +137,7 @@ def train(engine, budget_s: float | None = None, max_steps: int | None = None, p
             progress = log.steps / max_steps
         if max_steps is not None and log.steps >= max_steps:
             break
-        lr = lr_schedule(progress, peak_lr)
+        lr = max(lr_schedule(progress, peak_lr), floor)
         engine.set_lr(lr)
         r = engine.step()
         log.steps += 1

@@ -147,6 +147,7 @@ class EngineT final : public EngineBase {
   float get_lr() override { return lr_; }
   int get_state(ane_state* s) override;
   int set_state(const ane_state* s) override;
+  int reseed(int64_t seed) override;
   int64_t tensor_size(uint32_t id, uint32_t layer) override;
   int import_tensor(uint32_t id, uint32_t layer, uint32_t which, const float* buf, uint64_t n) override;
   int export_tensor(uint32_t id, uint32_t layer, uint32_t which, float* buf, uint64_t n) override;
@@ -1557,7 +1558,6 @@ int EngineT<T>::eval_loss(const uint16_t* tokens, uint32_t n_seq, double* loss_s
       cross_entropy_rows<T>(logits_, d_tgt_, d_one_ - 0, (T*)nullptr, loss_rows_, rows, r0, M + 1, V_, isN_, 0.f, stream_);
     }
     std::vector<float> rows_host(M);
-    std::vector<uint16_t> tg(M);
     if ((rc = cuda_check(cudaMemcpyAsync(rows_host.data(), loss_rows_, sizeof(float) * M, cudaMemcpyDeviceToHost, stream_),
                          "loss rows")) != 0)
       return rc;
@@ -1674,6 +1674,13 @@ int EngineT<T>::set_state(const ane_state* s) {  // ane/engine.go:506-512
   st_ = *s;
   micro_steps_ = s->pending_steps;
   pending_seqs_ = s->pending_steps * (uint32_t)B_;
+  // the wall clock continues from the restored total (ane/engine.go:560: start = now - CumWall)
+  t_open_ns_ = now_ns() - (int64_t)(s->cum_wall_ms * 1e6);
+  return 0;
+}
+template <typename T>
+int EngineT<T>::reseed(int64_t seed) {  // drand48Seed, ane/engine.go:873
+  rng_ = (((uint64_t)seed & 0xffffffffull) << 16) | 0x330Eull;
   return 0;
 }
 

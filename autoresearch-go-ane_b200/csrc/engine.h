@@ -25,6 +25,7 @@ class EngineBase {
   virtual float get_lr() = 0;
   virtual int get_state(ane_state* s) = 0;
   virtual int set_state(const ane_state* s) = 0;
+  virtual int reseed(int64_t seed) = 0;
   virtual int64_t tensor_size(uint32_t id, uint32_t layer) = 0;
   virtual int import_tensor(uint32_t id, uint32_t layer, uint32_t which, const float* buf, uint64_t n) = 0;
   virtual int export_tensor(uint32_t id, uint32_t layer, uint32_t which, float* buf, uint64_t n) = 0;

@@ -152,6 +152,10 @@ int32_t ane_set_state(ane_engine* e, const ane_state* in) {
   ENGINE_OR_FAIL(e, "load state");
   return e->impl->set_state(in);
 }
+int32_t ane_reseed(ane_engine* e, int64_t seed) {
+  ENGINE_OR_FAIL(e, "reseed");
+  return e->impl->reseed(seed);
+}
 int64_t ane_tensor_size(ane_engine* e, uint32_t tensor_id, uint32_t layer) {
   if (!e || !e->impl) return -1;
   return e->impl->tensor_size(tensor_id, layer);

@@ -17,7 +17,11 @@
 using namespace ane;
 
 static thread_local std::string g_ops_err;
-static int* g_ops_status = nullptr;  // device status word shared by the op entry points
+// One device status word and one timer event pair per device: a kernel launched on device d must be handed
+// device-d memory, and events belong to the device that was current when they were made.
+static constexpr int kMaxDevices = 64;
+static int* g_ops_status_dev[kMaxDevices] = {nullptr};
+static cudaEvent_t g_ev0_dev[kMaxDevices] = {nullptr}, g_ev1_dev[kMaxDevices] = {nullptr};
 
 static int set_err(int code, const std::string& msg) {
   g_ops_err = msg;
@@ -32,10 +36,26 @@ static int cuda_fail(cudaError_t e, const char* what) {
     if (_e != cudaSuccess) return cuda_fail(_e, #call); \
   } while (0)
 
-static int ensure_status() {
-  if (g_ops_status) return 0;
-  CK(cudaMalloc(&g_ops_status, sizeof(int)));
-  CK(cudaMemset(g_ops_status, 0, sizeof(int)));
+static int current_device(int* dev) {
+  CK(cudaGetDevice(dev));
+  if (*dev < 0 || *dev >= kMaxDevices) return set_err(ANE_ERR_ARG, "device ordinal out of range");
+  return 0;
+}
+// The status word of the current device (allocated on first use there).
+static int ensure_status(int** out) {
+  int dev = 0;
+  if (int rc = current_device(&dev)) return rc;
+  if (!g_ops_status_dev[dev]) {
+    int* p = nullptr;
+    CK(cudaMalloc(&p, sizeof(int)));
+    cudaError_t e = cudaMemset(p, 0, sizeof(int));
+    if (e != cudaSuccess) {
+      cudaFree(p);
+      return cuda_fail(e, "cudaMemset");
+    }
+    g_ops_status_dev[dev] = p;
+  }
+  *out = g_ops_status_dev[dev];
   return 0;
 }
 
@@ -87,30 +107,34 @@ int32_t ane_dev_sync(void) {
 // Reads and clears the device status word the op kernels report into
 // (0 = ok; 101..103 = a bounded pipeline wait gave up).
 int32_t ane_ops_device_status(int32_t* out_status) {
-  if (ensure_status()) return ANE_ERR_CUDA;
+  int* status = nullptr;
+  if (ensure_status(&status)) return ANE_ERR_CUDA;
   int v = 0;
-  CK(cudaMemcpy(&v, g_ops_status, sizeof(int), cudaMemcpyDeviceToHost));
-  CK(cudaMemset(g_ops_status, 0, sizeof(int)));
+  CK(cudaMemcpy(&v, status, sizeof(int), cudaMemcpyDeviceToHost));
+  CK(cudaMemset(status, 0, sizeof(int)));
   if (out_status) *out_status = v;
   return 0;
 }
 
 // Times `fn`-style regions: begin/end record CUDA events on the default stream.
-static cudaEvent_t g_ev0 = nullptr, g_ev1 = nullptr;
 int32_t ane_timer_begin(void) {
-  if (!g_ev0) {
-    CK(cudaEventCreate(&g_ev0));
-    CK(cudaEventCreate(&g_ev1));
+  int dev = 0;
+  if (int rc = current_device(&dev)) return rc;
+  if (!g_ev0_dev[dev]) {
+    CK(cudaEventCreate(&g_ev0_dev[dev]));
+    CK(cudaEventCreate(&g_ev1_dev[dev]));
   }
-  CK(cudaEventRecord(g_ev0, 0));
+  CK(cudaEventRecord(g_ev0_dev[dev], 0));
   return 0;
 }
 int32_t ane_timer_end(float* out_ms) {
-  if (!g_ev0) return set_err(ANE_ERR_ARG, "ane_timer_end without ane_timer_begin");
-  CK(cudaEventRecord(g_ev1, 0));
-  CK(cudaEventSynchronize(g_ev1));
+  int dev = 0;
+  if (int rc = current_device(&dev)) return rc;
+  if (!g_ev0_dev[dev] || !g_ev1_dev[dev]) return set_err(ANE_ERR_ARG, "ane_timer_end without ane_timer_begin on this device");
+  CK(cudaEventRecord(g_ev1_dev[dev], 0));
+  CK(cudaEventSynchronize(g_ev1_dev[dev]));
   float ms = 0.f;
-  CK(cudaEventElapsedTime(&ms, g_ev0, g_ev1));
+  CK(cudaEventElapsedTime(&ms, g_ev0_dev[dev], g_ev1_dev[dev]));
   if (out_ms) *out_ms = ms;
   return 0;
 }
@@ -133,12 +157,16 @@ int32_t ane_op_sumsq(const float* d_g, uint64_t n, float pre_scale, double* d_ou
   if (!d_g || !d_out) return set_err(ANE_ERR_ARG, "ane_op_sumsq: null pointer");
   double* acc = nullptr;
   CK(cudaMalloc(&acc, sizeof(double)));
-  CK(cudaMemsetAsync(acc, 0, sizeof(double), 0));
-  sumsq_accumulate(d_g, n, pre_scale, acc, 0);
-  CK(cudaGetLastError());
-  CK(cudaMemcpyAsync(d_out, acc, sizeof(double), cudaMemcpyDeviceToDevice, 0));
-  CK(cudaStreamSynchronize(0));
-  CK(cudaFree(acc));
+  cudaError_t e = cudaMemsetAsync(acc, 0, sizeof(double), 0);
+  if (e == cudaSuccess) {
+    sumsq_accumulate(d_g, n, pre_scale, acc, 0);
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaMemcpyAsync(d_out, acc, sizeof(double), cudaMemcpyDeviceToDevice, 0);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(0);
+  const cudaError_t ef = cudaFree(acc);  // the accumulator is released on every path
+  if (e != cudaSuccess) return cuda_fail(e, "ane_op_sumsq");
+  if (ef != cudaSuccess) return cuda_fail(ef, "cudaFree");
   return 0;
 }
 
@@ -158,7 +186,8 @@ int32_t ane_op_gemm(const ane_gemm_args* a) {
   if (a->m < 0 || a->n < 0 || a->k < 0 || a->lda <= 0 || a->ldb <= 0 || a->ldc <= 0)
     return set_err(ANE_ERR_ARG, "ane_op_gemm: bad dimensions");
   if ((a->d_res1 || a->d_res2) && a->ldres <= 0) return set_err(ANE_ERR_ARG, "ane_op_gemm: ldres missing");
-  if (ensure_status()) return ANE_ERR_CUDA;
+  int* status = nullptr;
+  if (ensure_status(&status)) return ANE_ERR_CUDA;
   GemmDesc d;
   d.A = a->d_a; d.B = a->d_b; d.C = a->d_c;
   d.M = a->m; d.N = a->n; d.K = a->k;
@@ -169,7 +198,7 @@ int32_t ane_op_gemm(const ane_gemm_args* a) {
   d.res1 = a->d_res1; d.s1 = a->d_s1; d.res2 = a->d_res2; d.s2 = a->d_s2;
   d.ldres = a->ldres;
   d.split_k = a->split_k;
-  int rc = (a->dtype == ANE_DTYPE_F32) ? gemm_f32(d, 0) : gemm_bf16(d, g_ops_status, 0);
+  int rc = (a->dtype == ANE_DTYPE_F32) ? gemm_f32(d, 0) : gemm_bf16(d, status, 0);
   if (rc != 0) return set_err(ANE_ERR_KERNEL, gemm_last_error());
   return 0;
 }

@@ -7,6 +7,11 @@
 // This file cannot be compiled in the build container (no Go toolchain); it is kept
 // deliberately plain: fixed-layout structs, integer and pointer arguments only, no callbacks,
 // no Go pointer retained by C after a call returns.
+//
+// The stories package of the reference (model files, checkpoints, RandomInit) stays as it is and is
+// imported here: Open reads Options.ModelPath with stories.LoadPretrained / stories.LoadCheckpoint and
+// hands every tensor to the device with ImportTensor; SaveCheckpoint / LoadCheckpoint (checkpoint.go)
+// go through stories.SaveCheckpoint / stories.LoadCheckpoint and the engine's own "SANE" trailer.
 package ane
 
 import (
@@ -19,6 +24,8 @@ import (
 	"unsafe"
 
 	"github.com/ebitengine/purego"
+
+	"github.com/tmc/autoresearch-go-ane/ane/stories"
 )
 
 // Options mirrors ane.Options of the reference (ane/engine.go:14-40) and adds the runtime model
@@ -55,6 +62,9 @@ type Options struct {
 	FP32                                       bool
 	Device, Rank, WorldSize                    int
 	DPID                                       []byte // 128-byte bootstrap id when WorldSize > 1
+	// NoModel lets a host that imports every tensor itself (ImportTensor) open an engine without a model
+	// file; the reference has no such mode and rejects an empty ModelPath, which stays the default here.
+	NoModel bool
 }
 
 // State mirrors ane.State (ane/engine.go:43-52).
@@ -139,6 +149,7 @@ var (
 	cExport     func(e uintptr, id, layer, which uint32, buf *float32, n uint64) int32
 	cTensorSize func(e uintptr, id, layer uint32) int64
 	cDecode     func(e uintptr, prompts *uint16, nSeq, promptLen, nNew uint32, temperature float32, uniforms *float64, out *uint16) int32
+	cReseed     func(e uintptr, seed int64) int32
 )
 
 func load() error {
@@ -167,6 +178,7 @@ func load() error {
 		purego.RegisterLibFunc(&cExport, lib, "ane_export_tensor")
 		purego.RegisterLibFunc(&cTensorSize, lib, "ane_tensor_size")
 		purego.RegisterLibFunc(&cDecode, lib, "ane_decode_sample")
+		purego.RegisterLibFunc(&cReseed, lib, "ane_reseed")
 	})
 	return loadErr
 }
@@ -184,18 +196,35 @@ func cString(p *byte) string {
 
 // Engine holds only the opaque handle and cached scalars; all state lives on the device.
 type Engine struct {
-	h     uintptr
-	seq   int
-	vocab int
+	h      uintptr
+	seq    int
+	vocab  int
+	seed   int64 // Options.Seed after defaults: LoadCheckpoint reseeds the sampler with seed + meta.Step
+	layers int
+	stock  bool // the reference's fixed model (stories.* sizes, reference architecture): checkpoints apply
 }
 
 func (e *Engine) err(op string, rc int32) error {
 	return fmt.Errorf("storiesane %s: %s (status %d)", op, cString(cLastError(e.h)), rc)
 }
 
-// Open mirrors ane.Open (ane/engine.go:184).  Weights are imported separately with ImportTensor
-// (the stories package keeps reading llama2.c files and V2-V5 checkpoints in Go).
+// stockModel reports whether the options describe the model the stories package is compiled for
+// (ane/stories/config.go:3-18) in the reference architecture: only then can its files be loaded.
+func stockModel(o Options) bool {
+	is := func(v, want int) bool { return v == 0 || v == want }
+	return o.Arch == 0 && is(o.Dim, stories.Dim) && is(o.Hidden, stories.Hidden) && is(o.Layers, stories.NLayers) &&
+		is(o.Heads, stories.Heads) && is(o.KVHeads, stories.Heads) && is(o.Vocab, stories.Vocab)
+}
+
+// Open mirrors ane.Open (ane/engine.go:184-355): ModelPath is required and is read as a llama2.c model
+// file, else as a training checkpoint (weights and optimizer state), exactly like ane/engine.go:250-257.
 func Open(opts Options) (*Engine, error) {
+	if opts.ModelPath == "" && !opts.NoModel {
+		return nil, fmt.Errorf("storiesane open: model path is empty") // ane/engine.go:185-187
+	}
+	if opts.ModelPath != "" && !stockModel(opts) {
+		return nil, fmt.Errorf("storiesane open: model files describe the %d-dim reference model; use NoModel and ImportTensor for other shapes", stories.Dim)
+	}
 	if err := load(); err != nil {
 		return nil, err
 	}
@@ -240,9 +269,40 @@ func Open(opts Options) (*Engine, error) {
 	}
 	vocab := opts.Vocab
 	if vocab <= 0 {
-		vocab = 32000
+		vocab = stories.Vocab
 	}
-	return &Engine{h: h, seq: seq, vocab: vocab}, nil
+	layers := opts.Layers
+	if layers <= 0 {
+		layers = stories.NLayers
+	}
+	seed := opts.Seed
+	if seed == 0 {
+		seed = 42 // ane/engine.go:200-202
+	}
+	e := &Engine{h: h, seq: seq, vocab: vocab, seed: seed, layers: layers, stock: stockModel(opts)}
+	if opts.ModelPath != "" {
+		// ane/engine.go:248-257: pretrained file first, checkpoint second; the first error is the one reported
+		mw := stories.NewModelWeights(stories.Vocab)
+		var opt *stories.OptimState
+		if len(opts.Tokens) > 0 {
+			opt = stories.NewOptimState(stories.Vocab)
+		}
+		loaded, _, err := stories.LoadPretrained(opts.ModelPath)
+		if err != nil {
+			if _, ckptErr := stories.LoadCheckpoint(opts.ModelPath, mw, opt); ckptErr != nil {
+				e.Close()
+				return nil, fmt.Errorf("storiesane open: load model: %w", err)
+			}
+		} else {
+			*mw = *loaded
+			opt = nil // a model file carries no optimizer state: the device moments stay zero
+		}
+		if err := e.pushModel(mw, opt); err != nil {
+			e.Close()
+			return nil, err
+		}
+	}
+	return e, nil
 }
 
 // Close mirrors (*Engine).Close (ane/engine.go:567).

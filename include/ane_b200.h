@@ -62,7 +62,9 @@ int32_t ane_op_sumsq(const float* d_g, uint64_t n, float pre_scale, double* d_ou
  * library, so n is limited to 2^28 elements (larger n returns ANE_ERR_ARG).  For hosts that own all
  * device memory themselves or must not trigger an allocation in a latency-critical loop.  No
  * counterpart in the reference.  The first call on a device resolves the array's address (do it
- * before any stream capture); calls share the array, so overlapping calls race. */
+ * before any stream capture); calls share the array, so overlapping calls race.  Unlike ane_op_sumsq,
+ * which waits for the device, this call only queues its two kernels on the default stream and returns:
+ * *d_out is ready once that stream has caught up (ane_dev_sync, or any later work on the same stream). */
 int32_t ane_op_sumsq_noalloc(const float* d_g, uint64_t n, float pre_scale, double* d_out);
 const char* ane_op_sumsq_noalloc_last_error(void);
 
@@ -208,7 +210,13 @@ int32_t ane_decode_sample(ane_engine* e, const uint16_t* prompts, uint32_t n_seq
 int32_t ane_set_lr(ane_engine* e, float lr);   /* ane/engine.go:366 */
 float ane_get_lr(ane_engine* e);               /* ane/engine.go:358 */
 int32_t ane_get_state(ane_engine* e, ane_state* out);       /* ane/engine.go:498 */
-int32_t ane_set_state(ane_engine* e, const ane_state* in);  /* ane/engine.go:506 */
+/* LoadState (ane/engine.go:506).  The engine's wall clock continues from in->cum_wall_ms
+ * (ane/engine.go:560: start = now - CumWall). */
+int32_t ane_set_state(ane_engine* e, const ane_state* in);
+/* Restarts the window sampler from drand48Seed(seed) (ane/engine.go:873): what LoadCheckpoint does with
+ * seed + meta.Step after a resume (ane/engine.go:559), so that the resumed run does not replay the
+ * windows of the run that wrote the file. */
+int32_t ane_reseed(ane_engine* e, int64_t seed);
 
 /* Weights / gradients / optimizer moments by tensor id, as row-major fp32 in the reference's
  * shapes (ane/stories/weights.go:13-42), so a host can read and write checkpoints

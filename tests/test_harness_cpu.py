@@ -100,8 +100,13 @@ class FakeEngine:
         return self._lr
 
     def set_lr(self, lr):
+        if lr <= 0:  # ane/engine.go:370-372, mirrored by the library
+            raise E.EngineError(-1, "storiesane set lr: lr must be > 0")
         self._lr = float(np.float32(lr))
         self.lrs.append(lr)
+
+    def reseed(self, seed):
+        self.seed_now = seed
 
     def state(self):
         return self._st
@@ -128,7 +133,7 @@ def test_train_loop_spends_the_budget_after_three_warmup_steps():
     log = H.train(e, budget_s=10.0, peak_lr=1e-3, clock=clock)
     assert e.steps == log.steps + H.WARMUP_STEPS
     assert 35 <= log.steps <= 40 and log.tokens == log.steps * 2 * 16
-    assert e.lrs[:3] == [0.0, 0.0, 0.0]                                   # warm-up steps sit at progress 0
+    assert e.lrs[:3] == [pytest.approx(1e-6)] * 3        # warm-up steps: the ramp's floor (SetLR refuses zero)
     assert max(log.lrs) <= 1e-3 and log.lrs[-1] < 0.2e-3 and log.lrs[0] == pytest.approx(0.5e-3)  # 0.25 s of 10 s
     assert log.losses == [10.0 / (i + 4) for i in range(log.steps)]
     by_steps = H.train(FakeEngine(), max_steps=20, peak_lr=1e-3)
@@ -250,6 +255,86 @@ def test_llama2c_model_file_import(tmp_path, arch):
         f.write(struct.pack("<i", D + 1))
     with pytest.raises(ValueError, match="config mismatch"):
         C.load_pretrained(e, path)
+
+
+def test_load_checkpoint_restarts_the_sampler_at_seed_plus_step(tmp_path):
+    src = FakeEngine()
+    src.opts.seed = 7
+    path = str(tmp_path / "c.bin")
+    C.save_checkpoint(src, path, C.TrainMeta(step=11))
+    dst = FakeEngine()
+    dst.opts.seed = 7
+    C.load_checkpoint(dst, path)
+    assert dst.seed_now == 7 + 11                         # ane/engine.go:559: drand48Seed(seed + meta.Step)
+    dst.opts.seed = 0
+    C.load_checkpoint(dst, path)
+    assert dst.seed_now == 42 + 11                        # Open's default seed (ane/engine.go:200-202)
+
+
+def test_open_style_load_takes_weights_and_moments_only(tmp_path):
+    src = FakeEngine()
+    src._st = E.State(token_pos=99, cum_steps=6, adam_t=3, pending_steps=1)
+    path = str(tmp_path / "c.bin")
+    C.save_checkpoint(src, path, C.TrainMeta(step=6))
+    dst = FakeEngine()
+    grads_before = {k: v.copy() for k, v in dst.t.items() if k[2] == E.G}
+    C.load_weights_and_moments(dst, path)                 # what ane.Open does with a checkpoint path
+    for k, a in src.t.items():
+        if k[2] != E.G:
+            np.testing.assert_array_equal(dst.t[k], a, err_msg=str(k))
+    for k, a in grads_before.items():
+        np.testing.assert_array_equal(dst.t[k], a)
+    assert dst.state().token_pos == 0 and dst.state().adam_t == 0 and dst.lrs == []
+
+
+def test_random_init_follows_the_distributions_of_the_reference():
+    e = FakeEngine(layers=4, vocab=400, dim=32, hidden=48, heads=2)
+    C.random_init(e, 3)
+    s = math.sqrt(3.0) / math.sqrt(32)
+    wq = e.t[(E.T_WQ, 1, 0)]
+    assert abs(wq).max() <= s and abs(wq).max() > 0.9 * s and abs(float(wq.mean())) < 0.05 * s
+    assert not e.t[(E.T_WO, 0, 0)].any() and not e.t[(E.T_W2, 3, 0)].any()     # output projections start at zero
+    emb = e.t[(E.T_EMBED, 0, 0)]
+    assert 0.95 < float(emb.std()) < 1.05
+    np.testing.assert_array_equal(e.t[(E.T_RESID_LAMBDAS, 0, 0)], np.ones(4, np.float32))
+    np.testing.assert_array_equal(e.t[(E.T_X0_LAMBDAS, 0, 0)], np.full(4, 0.1, np.float32))
+    assert e.t[(E.T_SMEAR_LAMBDA, 0, 0)][0] == np.float32(0.01) and e.t[(E.T_BACKOUT_LAMBDA, 0, 0)][0] == np.float32(0.01)
+    gate = e.t[(E.T_VE_GATE, 3, 0)]
+    assert gate.min() >= 0 and gate.max() < 0.02
+    again = FakeEngine(layers=4, vocab=400, dim=32, hidden=48, heads=2)
+    C.random_init(again, 3)
+    np.testing.assert_array_equal(again.t[(E.T_WQ, 1, 0)], wq)                   # seeded
+    lm = FakeEngine(arch=E.ARCH_LLAMA, layers=2, vocab=400, dim=32, hidden=48, heads=2)
+    C.random_init(lm, 1)
+    assert 0.018 < float(lm.t[(E.T_W3, 1, 0)].std()) < 0.022
+
+
+def test_eval_loss_with_the_reference_indexing():
+    """harness.go:58-84 slices the [vocab][seq] logits as [seq][vocab]; the switch reproduces that walk."""
+    seq, vocab = 16, 50
+
+    class LogitsEngine:
+        def __init__(self):
+            self.seq, self.vocab = seq, vocab
+            self.opts = E.Options(seq=seq, vocab=vocab, batch=1)
+
+        def eval_logits(self, w, layout=0):
+            rng = np.random.default_rng(int(w[0]))
+            return rng.standard_normal((1, vocab, seq)).astype(np.float32)
+
+    tokens = (np.arange(200) % vocab).astype(np.uint16)
+    got = H.eval_loss(LogitsEngine(), tokens, eval_tokens=100, reference_indexing=True)
+    total, n = 0.0, 0
+    for w in H.eval_windows(tokens, 100, seq):
+        flat = LogitsEngine().eval_logits(w).reshape(-1).astype(np.float64)
+        for t in range(seq - 1):                                                  # the reference's loop, literally
+            row = flat[t * vocab:(t + 1) * vocab]
+            mx = 5e-324
+            for v in row:
+                mx = max(mx, v)
+            total += math.log(sum(math.exp(v - mx) for v in row)) - (row[int(w[t + 1])] - mx)
+            n += 1
+    assert got == pytest.approx(total / n, rel=1e-12)
 
 
 # ------------------------------------------------------------------ sampleFromLogits
