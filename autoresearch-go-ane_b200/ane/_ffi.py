@@ -16,7 +16,7 @@ if not os.path.exists(LIB_PATH):
     )
 lib = ctypes.CDLL(LIB_PATH)
 
-DTYPE_BF16, DTYPE_F32 = 0, 1
+DTYPE_BF16, DTYPE_F32, DTYPE_BF16X3 = 0, 1, 2
 ARCH_REFERENCE, ARCH_LLAMA = 0, 1
 
 
@@ -60,7 +60,7 @@ class GemmArgs(ctypes.Structure):
         ("m", c_int32), ("n", c_int32), ("k", c_int32), ("lda", c_int32), ("ldb", c_int32), ("ldc", c_int32),
         ("a_mn", c_int32), ("b_mn", c_int32), ("out_mode", c_int32), ("alpha", c_float),
         ("d_res1", c_void_p), ("d_s1", c_void_p), ("d_res2", c_void_p), ("d_s2", c_void_p), ("ldres", c_int32),
-        ("split_k", c_int32),
+        ("split_k", c_int32), ("d_aux", c_void_p), ("ldaux", c_int32), ("pad_", c_int32),
     ]
 
 

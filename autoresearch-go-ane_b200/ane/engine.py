@@ -11,7 +11,7 @@ from dataclasses import dataclass, field
 import numpy as np
 
 from . import _ffi
-from ._ffi import ARCH_LLAMA, ARCH_REFERENCE, DTYPE_BF16, DTYPE_F32, lib
+from ._ffi import ARCH_LLAMA, ARCH_REFERENCE, DTYPE_BF16, DTYPE_BF16X3, DTYPE_F32, lib
 
 # tensor ids (include/ane_b200.h)
 T_EMBED, T_WQ, T_WK, T_WV, T_WO, T_W1, T_W2, T_W3 = range(8)

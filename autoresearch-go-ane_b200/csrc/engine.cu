@@ -192,7 +192,7 @@ class EngineT final : public EngineBase {
       cudaEventCreate(&e1);
       cudaEventRecord(e0, st);
     }
-    if constexpr (kIsF32) rc = gemm_f32(d, st);
+    if constexpr (kIsF32) rc = x3_ ? gemm_bf16x3(d, &split_, d_status_, st) : gemm_f32(d, st);
     else rc = gemm_bf16(d, d_status_, st);
     if (profiling_) {
       cudaEventRecord(e1, st);
@@ -238,6 +238,8 @@ class EngineT final : public EngineBase {
   // (ane/train_full.go:268-269), which amplifies operand rounding; its q/k/v stay in fp32.
   bool qkv_f32_ = false;
   bool att_tc_ = false;  // tensor-core attention kernels (bf16 operands, head_dim 64)
+  bool x3_ = false;      // fp32 engine whose GEMMs run as three bf16 tensor-core products (ANE_DTYPE_BF16X3)
+  SplitScratch split_;   // its operand halves (one stream at a time: no side stream in this mode)
   bool decoding_ = false;  // forward() runs one KV-cached decode step
   std::vector<T*> kcache_, vcache_;  // [B, S_, KV*hd] per layer, allocated by the first decode
   int32_t* d_argmax_ = nullptr;
@@ -343,6 +345,7 @@ void EngineT<T>::destroy() {
   if (stream_) cudaStreamSynchronize(stream_);
   if (comm_stream_) cudaStreamSynchronize(comm_stream_);  // weight gathers of the last update may still run
   dp_.shutdown();
+  split_.release();
   for (void* p : allocs_) cudaFree(p);
   allocs_.clear();
   if (h_in_) cudaFreeHost(h_in_);
@@ -624,6 +627,8 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
   {
     const char* env = getenv("ANE_B200_DW_OVERLAP");
     dw_overlap_ = !(env && env[0] == '0');
+    x3_ = kIsF32 && o_.compute_dtype == ANE_DTYPE_BF16X3;
+    if (x3_) dw_overlap_ = false;  // the split scratch serves one stream
   }
   layout_params();
   if ((rc = alloc_buffers()) != 0) return rc;
@@ -985,12 +990,23 @@ int EngineT<T>::backward_layers(int B) {
       g.A = dcur_t; g.B = wop(s_w2_[l].off); g.C = dgate_;
       g.M = M; g.N = Hd_; g.K = D_; g.lda = D_; g.ldb = Hd_; g.ldc = Hd_; g.b_mn = true;
       g.out = kIsF32 ? GEMM_OUT_F32 : GEMM_OUT_BF16;
+      // llama arch, bf16: the SwiGLU backward runs on the accumulators in the epilogue (d h13 written directly,
+      // d gate never stored)
+      static const bool no_fuse_dswiglu = getenv("ANE_B200_NO_FUSE_DSWIGLU") != nullptr;  // A/B measurements
+      const bool fused_dswiglu = !kIsF32 && !isN_ && !no_fuse_dswiglu && Hd_ % 32 == 0;
+      if (fused_dswiglu) {
+        g.out = GEMM_OUT_DSWIGLU;
+        g.C = dh13; g.ldc = N13_;
+        g.aux = a.h13; g.ldaux = N13_;
+      }
       count_launch();
       if ((rc = gemm(g)) != 0) return rc;
+      if (!fused_dswiglu) {
+        count_launch();
+        if (isN_) relu2_backward<T>(dgate_, a.h13, dh13, (uint64_t)M * Hd_, stream_);
+        else swiglu_backward<T>(dgate_, a.h13, dh13, M, Hd_, stream_);
+      }
     }
-    count_launch();
-    if (isN_) relu2_backward<T>(dgate_, a.h13, dh13, (uint64_t)M * Hd_, stream_);
-    else swiglu_backward<T>(dgate_, a.h13, dh13, M, Hd_, stream_);
     if (o_.debug_taps) {
       count_launch();
       to_f32_kernel<T><<<ew_grid((uint64_t)M * N13_), 256, 0, stream_>>>(dh13, a.t_dh13, (uint64_t)M * N13_);
@@ -1895,7 +1911,7 @@ int EngineT<T>::timer_end(float* ms) {
 }  // namespace
 
 EngineBase* create_engine(int compute_dtype) {
-  if (compute_dtype == ANE_DTYPE_F32) return new EngineT<float>();
+  if (compute_dtype == ANE_DTYPE_F32 || compute_dtype == ANE_DTYPE_BF16X3) return new EngineT<float>();
   return new EngineT<bf16>();
 }
 

@@ -118,8 +118,9 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
                      const EpiParams& epi,
                      const GemmDesc& d, int split_k, int* d_status, cudaStream_t stream) {
   auto kern = gemm_tc_kernel<BN, MT, A_MN, B_MN, EPI>;
-  constexpr uint32_t smem_bytes = GemmCfg<BN, MT>::smem_bytes(EPI == EPI_STORE_F32_TMARES);
-  static_assert(smem_bytes <= GEMM_SMEM_LIMIT && GemmCfg<BN, MT>::stages(EPI == EPI_STORE_F32_TMARES) >= 3, "pipeline does not fit");
+  constexpr bool tma_res = (EPI == EPI_STORE_F32_TMARES || EPI == EPI_DSWIGLU);
+  constexpr uint32_t smem_bytes = GemmCfg<BN, MT>::smem_bytes(tma_res, EPI == EPI_DSWIGLU);
+  static_assert(smem_bytes <= GEMM_SMEM_LIMIT && GemmCfg<BN, MT>::stages(tma_res, EPI == EPI_DSWIGLU) >= 3, "pipeline does not fit");
   static bool attr_set = false;  // per template instantiation
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
@@ -233,6 +234,18 @@ static int dispatch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
       return launch_tc<BN, MT, A_MN, B_MN, EPI_STORE_BF16_RELU2>(ta, tb, tc, td, epi, d, 1, d_status, stream);
     } else {
       g_gemm_err = "the ReLU^2 epilogue takes K-major operands only";
+      return -2;
+    }
+  }
+  if (d.out == GEMM_OUT_DSWIGLU) {
+    if constexpr (!A_MN && B_MN && BN == 256 && (MT == 1 || MT == GEMM_MT_PAIR)) {
+      CUtensorMap td;  // h13 in, d h13 out: [M, 2N] bf16, pieces of 32 rows x 64 columns
+      if (!make_tmap(&tc, d.C, 2 * (uint64_t)d.N, d.M, d.ldc, 64, 32, false) ||
+          !make_tmap(&td, d.aux, 2 * (uint64_t)d.N, d.M, d.ldaux, 64, 32, false))
+        return -2;
+      return launch_tc<BN, MT, A_MN, B_MN, EPI_DSWIGLU>(ta, tb, tc, td, epi, d, 1, d_status, stream);
+    } else {
+      g_gemm_err = "the SwiGLU-backward epilogue takes the dX form (A K-major, B MN-major) on 256-column tiles";
       return -2;
     }
   }
@@ -417,6 +430,21 @@ int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream) {
     g_gemm_err = "rotary epilogue: needs 16-byte aligned cos/sin tables, rope_seq > 0, rope_cols % 64 == 0 and alpha == 1";
     return -2;
   }
+  if (d.out == GEMM_OUT_DSWIGLU) {
+    if (d.aux == nullptr || d.a_mn || !d.b_mn || d.N % 32 != 0 || d.ldaux % 8 != 0 || d.ldc % 8 != 0 ||
+        (reinterpret_cast<uintptr_t>(d.aux) & 15) != 0) {
+      g_gemm_err = "SwiGLU-backward epilogue: dX form only, N % 32 == 0, h13 and d h13 16-byte aligned with pitches % 8 == 0";
+      return -2;
+    }
+    // 256-column tiles: CTA pairs when they fill their waves (the step's shape), else one CTA per tile
+    const int pairs = gemm_num_sms() / 2;
+    const long tiles = (long)((d.M + 255) / 256) * ((d.N + 255) / 256);
+    const long waves = (tiles + pairs - 1) / pairs;
+    const double eff = (double)tiles / (double)(waves * pairs);
+    static const bool no_pair = [] { const char* e = getenv("ANE_B200_GEMM_PAIR"); return e && atoi(e) == 0; }();
+    if (!no_pair && d.M >= 256 && eff >= 0.8) return dispatch_layout<256, GEMM_MT_PAIR>(d, 1, d_status, stream);
+    return dispatch_layout<256, 1>(d, 1, d_status, stream);
+  }
   GemmPlan p = plan_gemm(d, gemm_num_sms());
   if (d.out == GEMM_OUT_BF16_SWIGLU && p.bn == 192) p.bn = 256;  // gate rows pair up two 64-column pieces
   // CTA-pair tiles (256 x 256 per two SMs, half of the B tile per CTA): measured faster than both single-CTA
@@ -464,6 +492,89 @@ int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream) {
   if (p.bn == 256) return dispatch_layout<256, 1>(d, p.sched, d_status, stream);
   if (p.bn == 192) return dispatch_layout<192, 1>(d, p.sched, d_status, stream);
   return dispatch_layout<128, 1>(d, p.sched, d_status, stream);
+}
+
+// ------------------------------------------------------------------------------------------
+// Split-precision GEMM: fp32 operands as bf16 (hi, lo) pairs, three tensor-core products.
+// ------------------------------------------------------------------------------------------
+// src [rows, cols] fp32 with row pitch ld  ->  hi, lo [rows, ldo] bf16 (ldo >= cols, a multiple of 8)
+__global__ void split_rows_kernel(const float* __restrict__ src, bf16* __restrict__ hi, bf16* __restrict__ lo, int rows,
+                                  int cols, long long ld, int ldo) {
+  const long long total = (long long)rows * cols;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
+    const float x = src[(size_t)r * ld + c];
+    const bf16 h = __float2bfloat16_rn(x);
+    hi[(size_t)r * ldo + c] = h;
+    lo[(size_t)r * ldo + c] = __float2bfloat16_rn(x - __bfloat162float(h));
+  }
+}
+
+void SplitScratch::release() {
+  for (int i = 0; i < 4; ++i) {
+    if (buf[i]) cudaFree(buf[i]);
+    buf[i] = nullptr;
+    cap[i] = 0;
+  }
+}
+
+int gemm_bf16x3(const GemmDesc& d, SplitScratch* sc, int* d_status, cudaStream_t stream) {
+  if (d.M <= 0 || d.N <= 0 || d.K <= 0) return 0;
+  if (d.out != GEMM_OUT_F32 && d.out != GEMM_OUT_ACCUM) {
+    g_gemm_err = "split-precision GEMM writes fp32 (store or accumulate) only";
+    return -2;
+  }
+  // stored shapes of the operands
+  const int a_rows = d.a_mn ? d.K : d.M, a_cols = d.a_mn ? d.M : d.K;
+  const int b_rows = d.b_mn ? d.K : d.N, b_cols = d.b_mn ? d.N : d.K;
+  const int lda = (a_cols + 7) / 8 * 8, ldb = (b_cols + 7) / 8 * 8;
+  const size_t need[4] = {(size_t)a_rows * lda * 2, (size_t)a_rows * lda * 2, (size_t)b_rows * ldb * 2, (size_t)b_rows * ldb * 2};
+  for (int i = 0; i < 4; ++i) {
+    if (sc->cap[i] >= need[i]) continue;
+    // the previous, smaller buffer may still be read by GEMMs in flight on this stream
+    if (sc->buf[i]) {
+      cudaStreamSynchronize(stream);
+      cudaFree(sc->buf[i]);
+      sc->buf[i] = nullptr;
+      sc->cap[i] = 0;
+    }
+    const size_t bytes = need[i] + need[i] / 4 + 256;
+    if (cudaMalloc(&sc->buf[i], bytes) != cudaSuccess) {
+      g_gemm_err = "split-precision GEMM: out of memory for the operand halves";
+      return -3;
+    }
+    sc->cap[i] = bytes;
+  }
+  bf16* ah = reinterpret_cast<bf16*>(sc->buf[0]);
+  bf16* al = reinterpret_cast<bf16*>(sc->buf[1]);
+  bf16* bh = reinterpret_cast<bf16*>(sc->buf[2]);
+  bf16* bl = reinterpret_cast<bf16*>(sc->buf[3]);
+  auto grid = [](long long n) {
+    long long g = (n + 255) / 256;
+    return (unsigned)(g > 148LL * 16 ? 148LL * 16 : (g < 1 ? 1 : g));
+  };
+  split_rows_kernel<<<grid((long long)a_rows * a_cols), 256, 0, stream>>>(reinterpret_cast<const float*>(d.A), ah, al, a_rows,
+                                                                          a_cols, d.lda, lda);
+  split_rows_kernel<<<grid((long long)b_rows * b_cols), 256, 0, stream>>>(reinterpret_cast<const float*>(d.B), bh, bl, b_rows,
+                                                                          b_cols, d.ldb, ldb);
+  if (cudaGetLastError() != cudaSuccess) {
+    g_gemm_err = "split-precision GEMM: operand split launch failed";
+    return -4;
+  }
+  GemmDesc g = d;  // the large term keeps the output kind (store with residuals, or accumulate)
+  g.A = ah; g.B = bh; g.lda = lda; g.ldb = ldb;
+  int rc = gemm_bf16(g, d_status, stream);
+  if (rc != 0) return rc;
+  GemmDesc c = g;  // the two cross terms accumulate on top
+  c.out = GEMM_OUT_ACCUM;
+  c.res1 = c.res2 = nullptr;
+  c.s1 = c.s2 = nullptr;
+  c.split_k = 0;
+  c.B = bl;
+  if ((rc = gemm_bf16(c, d_status, stream)) != 0) return rc;
+  c.A = al;
+  c.B = bh;
+  return gemm_bf16(c, d_status, stream);
 }
 
 // ------------------------------------------------------------------------------------------

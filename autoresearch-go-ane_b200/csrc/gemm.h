@@ -33,6 +33,11 @@ enum GemmOut : int {
   // store bf16 (h) and also gate = max(h, 0)^2, taken from the fp32 accumulators, into `aux` [M, N] (bf16, row
   // pitch ldaux): the reference architecture's FFN activation (ane/common.go:146).  K-major operands only.
   GEMM_OUT_BF16_RELU2 = 6,
+  // SwiGLU backward fused into the product d gate = A*B [M, N]: with `aux` = h13 [M, 2N] (bf16, h1 | h3 interleaved
+  // in blocks of 32 columns, row pitch ldaux) the kernel writes C = d h13 [M, 2N] in the same layout (row pitch ldc),
+  //   d h1 = d gate * h3 * silu'(h1),  d h3 = d gate * silu(h1),
+  // from the fp32 accumulators; d gate itself is not stored.  A K-major, B MN-major (the dX form), N % 32 == 0.
+  GEMM_OUT_DSWIGLU = 7,
 };
 
 struct GemmDesc {
@@ -64,6 +69,18 @@ struct GemmDesc {
 int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream);
 // fp32 operands, SIMT FMA (the fp32 parity mode).
 int gemm_f32(const GemmDesc& d, cudaStream_t stream);
+
+// fp32 operands at split precision on the tensor cores: A and B are each cut into a bf16 (hi, lo) pair
+// (hi = bf16(x), lo = bf16(x - hi): together ~16 significand bits) and the product is formed as the three
+// bf16 GEMMs Ah*Bh + Ah*Bl + Al*Bh accumulated in fp32 (the dropped Al*Bl term is ~2^-18 relative).  Output
+// kinds GEMM_OUT_F32 (with residuals) and GEMM_OUT_ACCUM.  The scratch holds the four operand halves and
+// grows on demand; one scratch serves one stream at a time.
+struct SplitScratch {
+  void* buf[4] = {nullptr, nullptr, nullptr, nullptr};  // A hi, A lo, B hi, B lo
+  size_t cap[4] = {0, 0, 0, 0};                         // bytes
+  void release();
+};
+int gemm_bf16x3(const GemmDesc& d, SplitScratch* scratch, int* d_status, cudaStream_t stream);
 
 int gemm_num_sms();
 // 2-D tensor map over a row-major [outer, inner] buffer (row pitch ld elements) of bf16 (or fp32) with a

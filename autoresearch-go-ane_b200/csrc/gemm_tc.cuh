@@ -58,13 +58,14 @@ struct GemmCfg {
   static constexpr uint32_t STAGING_BYTES = 4 * SBUF * 4096;  // 4 epilogue warps x SBUF buffers x (32 rows x 128 B)
   // Pipeline depth.  Single-CTA kernels take what fits beside the staging buffers and use the TMA-fed residual
   // epilogue only if its buffers still fit; pair kernels give up stages for them instead.
-  __host__ __device__ static constexpr int stages(bool tma_res) {
-    const uint32_t avail = GEMM_SMEM_LIMIT - 1024u - STAGING_BYTES - ((PAIR && tma_res) ? GEMM_TMARES_BYTES : 0u);
+  // `room`: also a single-CTA kernel gives up stages for the TMA-fed input pieces (an epilogue that cannot do without them)
+  __host__ __device__ static constexpr int stages(bool tma_res, bool room = false) {
+    const uint32_t avail = GEMM_SMEM_LIMIT - 1024u - STAGING_BYTES - (((PAIR || room) && tma_res) ? GEMM_TMARES_BYTES : 0u);
     const int n = (int)(avail / (A_BYTES + B_BYTES));
     return n > 6 ? 6 : n;
   }
-  __host__ __device__ static constexpr uint32_t smem_bytes(bool tma_res) {  // +1024: alignment
-    return stages(tma_res) * (A_BYTES + B_BYTES) + STAGING_BYTES + 1024 + (tma_res ? GEMM_TMARES_BYTES : 0u);
+  __host__ __device__ static constexpr uint32_t smem_bytes(bool tma_res, bool room = false) {  // +1024: alignment
+    return stages(tma_res, room) * (A_BYTES + B_BYTES) + STAGING_BYTES + 1024 + (tma_res ? GEMM_TMARES_BYTES : 0u);
   }
   static constexpr int ACC_COLS = SUBS * BN;                     // one accumulator set
   static constexpr int NBUF = (2 * ACC_COLS <= 512) ? 2 : 1;     // TMEM accumulator sets
@@ -108,6 +109,11 @@ enum EpiKind : int {
   EPI_STORE_BF16_TGT = 6,
   // EPI_STORE_BF16 plus gate = max(h, 0)^2 of every 64-column piece, staged as one more piece (tmD: gate [M, N]).
   EPI_STORE_BF16_RELU2 = 7,
+  // SwiGLU backward on the accumulators: acc = d gate [M, N]; tmD = h13 [M, 2N] (bf16, h1 | h3 interleaved in blocks
+  // of 32 columns), tmC = d h13 [M, 2N] in the same layout.  A piece is 32 accumulator columns: its h1 | h3 columns
+  // are one 64-column bf16 piece of h13, fetched by TMA like the residual pieces of EPI_STORE_F32_TMARES, and its
+  // d h1 | d h3 columns one 64-column piece of the output.  d gate itself is never written.
+  EPI_DSWIGLU = 8,
 };
 struct EpiParams {
   float alpha;
@@ -187,7 +193,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD, EpiParams epi, int M,
                int N, int K, int split_k, int* status) {
   using Cfg = GemmCfg<BN, MT>;
-  constexpr int STAGES = Cfg::stages(EPI == EPI_STORE_F32_TMARES);
+  constexpr bool kTmaRes = (EPI == EPI_STORE_F32_TMARES || EPI == EPI_DSWIGLU);  // an input piece per output piece, by TMA
+  constexpr int STAGES = Cfg::stages(kTmaRes, EPI == EPI_DSWIGLU);
   constexpr int BM = Cfg::BM_TILE, BK = GEMM_BK;
   constexpr int NBUF = Cfg::NBUF;
   constexpr bool PAIR = Cfg::PAIR;
@@ -227,7 +234,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
-    if constexpr (EPI == EPI_STORE_F32_TMARES) {
+    if constexpr (kTmaRes) {
       for (int w = 0; w < 4; ++w)
         for (int b = 0; b < 2; ++b) mbar_init(smem_u32(&bar_res[w][b]), 1);
       tma_prefetch_desc(&tmD);
@@ -426,19 +433,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       // the consuming loop, so every issued piece is consumed.
       uint32_t res_issued = res_uses;
       auto issue_res = [&](int m_w, int n0r) {
-        if constexpr (EPI == EPI_STORE_F32_TMARES) {
+        if constexpr (kTmaRes) {
           if (n0r < N && n0r < (tn + 1) * BN && m_w < M) {
             if (lane == 0) {
               const uint32_t b = res_issued & 1u;
               const uint32_t bar = smem_u32(&bar_res[warp - 2][b]);
               mbar_expect_tx(bar, 4096);
-              tma_load_2d(res_base + b * 4096u, &tmD, bar, n0r, m_w);
+              tma_load_2d(res_base + b * 4096u, &tmD, bar, EPI == EPI_DSWIGLU ? 2 * n0r : n0r, m_w);
             }
             ++res_issued;
           }
         }
       };
-      if constexpr (EPI == EPI_STORE_F32_TMARES) {  // first two pieces of sub-tile 0, while the MMAs still run
+      if constexpr (kTmaRes) {  // first two pieces of sub-tile 0, while the MMAs still run
         issue_res(tm * BM + sub_row(0) + lane_group * 32, tn * BN);
         issue_res(tm * BM + sub_row(0) + lane_group * 32, tn * BN + CW);
       }
@@ -453,7 +460,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int m = m_warp + lane;
       if (sub > 0) {
         prefetch_first(m);
-        if constexpr (EPI == EPI_STORE_F32_TMARES) {
+        if constexpr (kTmaRes) {
           issue_res(m_warp, tn * BN);
           issue_res(m_warp, tn * BN + CW);
         }
@@ -507,7 +514,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) tma_store_wait_read<SBUF - 1>();
         __syncwarp();
         uint8_t* row_ptr = stage_ptr + sbuf * 4096 + lane * 128;
-        if constexpr (kBf16Out) {
+        if constexpr (EPI == EPI_DSWIGLU) {
+          const uint32_t b = res_uses & 1u;
+          if (!mbar_wait(smem_u32(&bar_res[warp - 2][b]), (res_uses >> 1) & 1u, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
+            ok = false;
+            break;
+          }
+          // this row's 64 bf16 of h13: 16-byte chunks 0-3 = h1 of the piece's 32 gate columns, 4-7 = h3
+          const uint8_t* hrow = res_ptr + b * 4096u + lane * 128;
+          uint4 hraw[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) hraw[q] = *reinterpret_cast<const uint4*>(hrow + ((q ^ (lane & 7)) << 4));
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const __nv_bfloat162* h1p = reinterpret_cast<const __nv_bfloat162*>(&hraw[q]);
+            const __nv_bfloat162* h3p = reinterpret_cast<const __nv_bfloat162*>(&hraw[q + 4]);
+            uint32_t o1[4], o3[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 x = __bfloat1622float2(h1p[e]), h = __bfloat1622float2(h3p[e]);
+              const float dg0 = epi.alpha * acc[8 * q + 2 * e], dg1 = epi.alpha * acc[8 * q + 2 * e + 1];
+              // sigmoid by one ex2 and one fast reciprocal; d silu = s (1 + x (1 - s))
+              const float s0 = __fdividef(1.f, 1.f + exp2f(-1.4426950408889634f * x.x));
+              const float s1 = __fdividef(1.f, 1.f + exp2f(-1.4426950408889634f * x.y));
+              o1[e] = pack2_bf16(dg0 * h.x * s0 * (1.f + x.x * (1.f - s0)), dg1 * h.y * s1 * (1.f + x.y * (1.f - s1)));
+              o3[e] = pack2_bf16(dg0 * x.x * s0, dg1 * x.y * s1);
+            }
+            *reinterpret_cast<uint4*>(row_ptr + ((q ^ (lane & 7)) << 4)) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+            *reinterpret_cast<uint4*>(row_ptr + (((q + 4) ^ (lane & 7)) << 4)) = make_uint4(o3[0], o3[1], o3[2], o3[3]);
+          }
+        } else if constexpr (kBf16Out) {
           if constexpr (EPI == EPI_STORE_BF16_TGT) {
             const int t = tgt_col - n0;
             if (t >= 0 && t < CW) {  // one piece per row at most
@@ -656,13 +692,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if constexpr (EPI == EPI_STORE_F32_TMARES) {  // this residual buffer is free: fetch the piece after next
+        if constexpr (kTmaRes) {  // this residual buffer is free: fetch the piece after next
           ++res_uses;
           issue_res(m_warp, n0 + 2 * CW);
         }
         if (lane == 0) {
           const uint32_t src = stage_base + (uint32_t)sbuf * 4096u;
           if constexpr (EPI == EPI_REDUCE_F32) tma_reduce_add_2d(&tmC, src, n0, m_warp);
+          else if constexpr (EPI == EPI_DSWIGLU) tma_store_2d(&tmC, src, 2 * n0, m_warp);
           else tma_store_2d(&tmC, src, n0, m_warp);
           tma_store_commit();
         }

@@ -198,7 +198,17 @@ int32_t ane_op_gemm(const ane_gemm_args* a) {
   d.res1 = a->d_res1; d.s1 = a->d_s1; d.res2 = a->d_res2; d.s2 = a->d_s2;
   d.ldres = a->ldres;
   d.split_k = a->split_k;
-  int rc = (a->dtype == ANE_DTYPE_F32) ? gemm_f32(d, 0) : gemm_bf16(d, status, 0);
+  d.aux = const_cast<void*>(a->d_aux);
+  d.ldaux = a->ldaux;
+  int rc;
+  if (a->dtype == ANE_DTYPE_BF16X3) {
+    SplitScratch sc;  // operand halves for this call only
+    rc = gemm_bf16x3(d, &sc, status, 0);
+    cudaStreamSynchronize(0);
+    sc.release();
+  } else {
+    rc = (a->dtype == ANE_DTYPE_F32) ? gemm_f32(d, 0) : gemm_bf16(d, status, 0);
+  }
   if (rc != 0) return set_err(ANE_ERR_KERNEL, gemm_last_error());
   return 0;
 }

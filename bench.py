@@ -9,9 +9,14 @@ bf16 GEMM operands, fp32 master weights and optimizer).  Synthetic data: seeded 
 stream and N(0, 0.02) weights stand in for TinyStories and the stories110M checkpoint.
 
 `value` is tokens/s with the token stream resident in HBM (Engine.Step samples windows on the
-device); `e2e` is the same metric through ane_step_tokens with host batches copied H2D and the
-loss read back every step.  `--impl reference` times the CPU restatement of the reference's Go
-step (the reference itself cannot be built here) on the host cores.
+device): the timed region of exactly `--steps` steps is repeated (`--repeats`, default 5) and the median
+repeat is reported, with the spread beside it.  `e2e` is the same metric through ane_step_tokens with host
+batches copied H2D and the loss read back every step.  `c4` is the fixed-global-batch form of the
+data-parallel configuration: 256 sequences per optimizer update, gradient accumulation 256 / (32 N) on
+N GPUs.  At one GPU the line also carries `extras`: batch-64 evaluation, the GQA seq-1024 step and its
+KV-cached decode, and the reference architecture's step, each with its fraction of the step roofline.
+`--impl reference` times the CPU restatement of the reference's Go step (the reference itself cannot be
+built here) on the host cores.
 """
 from __future__ import annotations
 
@@ -22,6 +27,7 @@ import subprocess
 import sys
 import threading
 import time
+import zlib
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -63,6 +69,10 @@ def train_flops_per_token(cfg, arch):
 
 TRAIN_FLOPS_PER_TOKEN = train_flops_per_token(WORKLOAD, "llama")
 
+# DRAM bytes (read + write) of all gemm_tc_kernel launches of one 110M step, from an ncu capture of this
+# command; bench.py cannot run ncu itself, so the figure is tagged with the commit it was taken at.
+GEMM_TRAFFIC = {"dram_bytes_per_step": None, "source": "not captured for this build"}
+
 
 def zipf_tokens(n, vocab, seed, s=1.1):
     rng = np.random.Generator(np.random.PCG64(seed))
@@ -81,9 +91,10 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks, power and throttle reasons with nvidia-smi (every 20 ms).  The process is started
-    before the warm-up steps, so that its start-up time is not taken from the timed region; mark() / window()
-    bracket the timed region, and only samples that arrived inside it are reported."""
+    """Samples SM clocks, power and throttle reasons with nvidia-smi (every 50 ms) through both timed legs
+    (device-resident and end-to-end), so that neither leg pays for polling that the other does not.  The
+    process is started before the warm-up steps; mark() / window() bracket each timed region, and only
+    samples that arrived inside one are reported."""
 
     def __init__(self, device: int):
         self.device = device
@@ -98,7 +109,7 @@ class ClockSampler:
              "clocks_event_reasons.sw_power_cap")
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "20"],
+                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
             # nvidia-smi needs 0.1-0.3 s before its first line: wait for it here, outside every timed region, so that
@@ -130,10 +141,10 @@ class ClockSampler:
         sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         picked = [ln for a, b in self.windows for ln in self.lines[a:b]]
-        window = "timed region of the device-resident leg, one sample per 20 ms"
-        if not picked:  # region shorter than one sampling period: fall back to everything since the warm-up began
+        window = "timed regions of the device-resident and end-to-end legs, one sample per 50 ms"
+        if not picked:  # regions shorter than one sampling period: fall back to everything since the warm-up began
             picked = list(self.lines)
-            window = "warm-up and timed region of the device-resident leg (no sample fell inside the timed region alone)"
+            window = "warm-up and timed regions (no sample fell inside a timed region alone)"
         for ln in picked:
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 7:
@@ -176,6 +187,26 @@ def init_weights(engine, ane, seed, cfg):
             engine.import_tensor(tid, 0, np.full(n, val, dtype=np.float32))
 
 
+def fwd_flops_per_token(cfg, arch):
+    """Forward-only FLOPs per token (evaluation, prefill): 2*N_mm + causal attention 2*L*T*D."""
+    D, Hd, L, H, KV, V, T = (cfg[k] for k in ("dim", "hidden", "n_layers", "n_heads", "n_kv_heads", "vocab", "seq"))
+    hd = D // H
+    n_mm = L * (2 * D * D + 2 * D * KV * hd + (3 if arch == "llama" else 2) * D * Hd) + V * D
+    return 2 * n_mm + 2 * L * T * D
+
+
+def open_engine(ane, wl, batch, tokens, *, accum=1, rank=0, world=1, local_rank=0, dp_id=None, ce_chunk=0):
+    is_ref_arch = wl["arch"] == "reference"
+    opts = ane.Options(tokens=tokens, batch=batch, arch=ane.ARCH_REFERENCE if is_ref_arch else ane.ARCH_LLAMA,
+                       quirks=1 if is_ref_arch else 0, compute_dtype=ane.DTYPE_BF16,
+                       accum_steps=accum, lr=3e-4, adam_beta1=0.9, adam_beta2=0.95, weight_decay=0.1, grad_clip=1.0,
+                       seed=42, device=local_rank, rank=rank, world_size=world, dp_id=dp_id, ce_chunk_rows=ce_chunk,
+                       **wl["cfg"])
+    e = ane.open(opts)
+    init_weights(e, ane, seed=1234, cfg=wl["cfg"])
+    return e
+
+
 def run_ours(args):
     import ane
 
@@ -183,7 +214,6 @@ def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     dist = None
-    dp_id = None
     if world > 1:
         import torch
         import torch.distributed as dist_mod
@@ -191,9 +221,13 @@ def run_ours(args):
         dist = dist_mod
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
+
+    def new_dp_id():
+        if dist is None:
+            return None
         obj = [ane.dp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(obj, src=0)
-        dp_id = obj[0]
+        return obj[0]
 
     def barrier():
         if dist is not None:
@@ -210,50 +244,54 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def timed_steps(engine, n):
+        """Exactly n steps between a barrier + synchronize on both sides; device time, max over ranks."""
+        barrier()
+        engine.timer_begin()
+        last = None
+        for _ in range(n):
+            last = engine.step()
+        ms = engine.timer_end()
+        barrier()
+        return max_over_ranks(ms), last
+
     wl = WORKLOADS[args.workload]
     WORKLOAD, MICRO_BATCH = wl["cfg"], wl["batch"]
     if args.batch > 0:  # another micro-batch than the workload's own (the workload name then says so)
         wl = dict(wl, name=wl["name"].replace(f"micro-batch {MICRO_BATCH} per GPU", f"micro-batch {args.batch} per GPU"))
         MICRO_BATCH = args.batch
-    is_ref_arch = wl["arch"] == "reference"
     flops_per_token = train_flops_per_token(WORKLOAD, wl["arch"])
+    hbm, tf_burst, tf_sust, src = measured_peaks()
     tokens = zipf_tokens(N_STREAM_TOKENS, WORKLOAD["vocab"], seed=0)
-    opts = ane.Options(tokens=tokens, batch=MICRO_BATCH, arch=ane.ARCH_REFERENCE if is_ref_arch else ane.ARCH_LLAMA,
-                       quirks=1 if is_ref_arch else 0, compute_dtype=ane.DTYPE_BF16,
-                       accum_steps=1, lr=3e-4, adam_beta1=0.9, adam_beta2=0.95, weight_decay=0.1, grad_clip=1.0,
-                       seed=42, device=local_rank, rank=rank, world_size=world, dp_id=dp_id, ce_chunk_rows=args.ce_chunk,
-                       **WORKLOAD)
-    e = ane.open(opts)
-    init_weights(e, ane, seed=1234, cfg=WORKLOAD)
+    e = open_engine(ane, wl, MICRO_BATCH, tokens, rank=rank, world=world, local_rank=local_rank, dp_id=new_dp_id(),
+                    ce_chunk=args.ce_chunk)
     T = WORKLOAD["seq"]
     tokens_per_step = MICRO_BATCH * T * world
 
-    # ---- device-resident leg ("value")
+    # ---- device-resident leg ("value"): `repeats` timed regions of exactly `steps` steps, median reported
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     for _ in range(args.warmup):
-        r = e.step()
-    barrier()
-    sampler.mark()
+        e.step()
     launches0 = e.launch_count()
-    e.timer_begin()
+    region_ms, last = [], None
     t0 = time.perf_counter()
-    last = None
-    for _ in range(args.steps):
-        last = e.step()
-    ms = e.timer_end()
-    wall_ms = (time.perf_counter() - t0) * 1e3
-    sampler.window()
-    # stopped here: polling nvidia-smi during the end-to-end leg costs that leg a few percent of host time
-    clocks = sampler.stop() if rank == 0 else None
-    barrier()
-    launches = e.launch_count() - launches0
-    ms = max_over_ranks(ms)
+    for _ in range(max(1, args.repeats)):
+        sampler.mark()
+        ms, last = timed_steps(e, args.steps)
+        sampler.window()
+        region_ms.append(ms)
+    wall_ms = (time.perf_counter() - t0) * 1e3 / max(1, args.repeats)
+    launches = (e.launch_count() - launches0) // max(1, args.repeats)
+    ms = float(np.median(region_ms))
     ms_per_step = ms / args.steps
     value = tokens_per_step / (ms_per_step * 1e-3)
+    repeats = {"n": len(region_ms), "ms_per_step_median": round(ms_per_step, 4),
+               "ms_per_step_min": round(min(region_ms) / args.steps, 4),
+               "ms_per_step_max": round(max(region_ms) / args.steps, 4)}
 
-    # ---- end-to-end leg: host batches in, loss out, every step
+    # ---- end-to-end leg: host batches in, loss out, every step (clock sampling continues)
     rng = np.random.default_rng(7 + rank)
     pos = rng.integers(0, tokens.size - T - 1, size=(args.steps + 1, MICRO_BATCH))
     batches = []
@@ -262,34 +300,57 @@ def run_ours(args):
         tgt = np.stack([tokens[p + 1:p + 1 + T] for p in pos[s]])
         batches.append((inp, tgt))
     e.step_tokens(*batches[-1])
+    e2e_runs = []
+    for _ in range(max(1, args.repeats)):
+        barrier()
+        sampler.mark()
+        t0 = time.perf_counter()
+        for s in range(args.steps):
+            e.step_tokens(*batches[s])
+        ane._ffi.lib.ane_dev_sync()
+        e2e_runs.append(max_over_ranks(time.perf_counter() - t0))
+        sampler.window()
     barrier()
-    t0 = time.perf_counter()
-    for s in range(args.steps):
-        e.step_tokens(*batches[s])
-    ane._ffi.lib.ane_dev_sync()
-    e2e_s = max_over_ranks(time.perf_counter() - t0)
-    barrier()
-    e2e_value = tokens_per_step * args.steps / e2e_s
+    clocks = sampler.stop() if rank == 0 else None
+    e2e_value = tokens_per_step * args.steps / float(np.median(e2e_runs))
     h2d = 2 * MICRO_BATCH * T * 2
     d2h = 8
+
+    # ---- replicas must stay identical under data parallelism: checksums of two weight tensors per rank
+    dp_check = None
+    if dist is not None:
+        import torch
+        sums = [zlib.crc32(e.export_tensor(ane.T_WQ, 1).tobytes()), zlib.crc32(e.export_tensor(ane.T_EMBED, 0).tobytes())]
+        mine = torch.tensor(sums + [0], dtype=torch.int64, device="cuda")
+        loss_t = torch.tensor([float(last.loss)], dtype=torch.float64, device="cuda")
+        all_sums = [torch.zeros_like(mine) for _ in range(world)]
+        all_loss = [torch.zeros_like(loss_t) for _ in range(world)]
+        dist.all_gather(all_sums, mine)
+        dist.all_gather(all_loss, loss_t)
+        same = all(bool(torch.equal(t, all_sums[0])) for t in all_sums)
+        losses = [float(t.item()) for t in all_loss]
+        dp_check = {"replicas_identical": same, "tensors": ["wq[1]", "embed"], "checksum": "crc32 of the fp32 bytes",
+                    "loss_spread": round(max(losses) - min(losses), 5),
+                    "note": "ranks train on different windows, so their last losses differ; weights must not"}
 
     # ---- dominant-kernel roofline: every GEMM launch timed with CUDA events over one profiled step
     e.profile_gemm(True)
     e.step()
     gemm_ms, gemm_flops, gemm_launches = e.profile_read()
     e.profile_gemm(False)
-    hbm, tf_burst, tf_sust, src = measured_peaks()
     achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
-    roofline = {"bound": "tensor", "achieved": round(achieved, 1), "peak": tf_sust, "unit": "TFLOP/s",
-                "frac": round(achieved / tf_sust, 4), "traffic": None, "peak_source": f"bf16_tflops_sustained ({src})",
+    step_tflops = flops_per_token * tokens_per_step / world / (ms_per_step * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": round(achieved, 1), "peak": tf_burst, "unit": "TFLOP/s",
+                "frac": round(achieved / tf_burst, 4), "traffic": GEMM_TRAFFIC["dram_bytes_per_step"],
+                "traffic_source": GEMM_TRAFFIC["source"],
+                "peak_source": f"bf16_tflops burst ({src}); a step is 8 ms of mixed kernels, not the seconds-long GEMM loop "
+                               "of the sustained figure",
+                "frac_of_sustained_peak": round(achieved / tf_sust, 4),
                 "kernel": "gemm_tc_kernel (tcgen05 GEMM, all shapes of one step)", "gemm_launches_per_step": gemm_launches,
                 "gemm_ms_per_step": round(gemm_ms, 3),
-                # DRAM traffic of three captured launches (ncu --set full, profiles/gemm_tc_kernel_*.md);
-                # the aggregate over all 150 launches of a step was not captured, hence traffic = null.
-                "traffic_cases": {"classifier_fwd_8192x32000x768": {"dram_bytes": 532205568, "algorithmic_bytes": 586022912},
-                                  "w2_dx_8192x768x4096": {"dram_bytes": 78061312, "algorithmic_bytes": 98566144},
-                                  "qkv_fwd_8192x2304x768": {"dram_bytes": 16279296, "algorithmic_bytes": 53870592}},
-                "step_frac_of_burst_peak": round(flops_per_token * tokens_per_step / world / (ms_per_step * 1e-3) / 1e12 / tf_burst, 4)}
+                "algorithmic_flops_per_step": gemm_flops,
+                "step_tflops": round(step_tflops, 1),
+                "step_frac_of_burst_peak": round(step_tflops / tf_burst, 4)}
 
     # ---- EvalLogits latency (the second half of the headline metric): one 256-token window per call,
     # full 32000 x 256 fp32 logits returned to the host in the reference's [vocab][seq] order.
@@ -316,18 +377,21 @@ def run_ours(args):
                    "d2h_bytes_per_op": WORKLOAD["vocab"] * T * 4,
                    "note": "host-visible latency of one EvalLogits call (batch 1); EvalLoss keeps logits on the device"}
 
-    # ---- optional extra legs (one GPU): batched evaluation and KV-cached greedy decoding
+    # ---- extra legs (one GPU): the other configurations, each with its fraction of the step roofline
     extras = None
-    if args.extras and world == 1:
+    if args.extras and world == 1 and args.workload == "110m":
         extras = {}
         nb = 64
         batch_tokens = np.ascontiguousarray(tokens[:nb * T])
+        fwd_fl = fwd_flops_per_token(WORKLOAD, wl["arch"]) * nb * T
         e.eval_loss(batch_tokens)
         t0 = time.perf_counter()
         for _ in range(5):
             e.eval_loss(batch_tokens)
         dt = (time.perf_counter() - t0) / 5
-        extras["eval_loss_batch64"] = {"ms_per_op": round(dt * 1e3, 3), "tok_per_s": round(nb * T / dt, 1)}
+        extras["eval_loss_batch64"] = {"ms_per_op": round(dt * 1e3, 3), "tok_per_s": round(nb * T / dt, 1),
+                                       "frac_of_burst_peak": round(fwd_fl / dt / 1e12 / tf_burst, 4),
+                                       "note": "64 windows of 256 tokens, fused device loss, host-visible"}
         e.eval_logits(batch_tokens, layout=1)
         t0 = time.perf_counter()
         for _ in range(3):
@@ -335,26 +399,66 @@ def run_ours(args):
         dt = (time.perf_counter() - t0) / 3
         extras["eval_logits_batch64"] = {"ms_per_op": round(dt * 1e3, 3), "tok_per_s": round(nb * T / dt, 1),
                                          "d2h_bytes_per_op": nb * T * WORKLOAD["vocab"] * 4,
-                                         "note": "host-visible, fp32 logits for 64 x seq tokens copied to the host"}
-        if T >= 768:  # prompt 512 + 256 generated tokens must fit the KV cache (= seq)
-            # decoding runs 32 sequences at once, whatever the training micro-batch: a second engine
-            e.close()
-            e = ane.open(ane.Options(tokens=tokens, batch=32, arch=ane.ARCH_LLAMA, quirks=0, compute_dtype=ane.DTYPE_BF16,
-                                     accum_steps=1, seed=42, device=local_rank, **WORKLOAD))
-            init_weights(e, ane, seed=1234, cfg=WORKLOAD)
-            prompts = np.ascontiguousarray(tokens[:32 * 512].reshape(32, 512))
-            e.decode_greedy(prompts[:, :64], 4)
-            t0 = time.perf_counter()
-            e.decode_greedy(prompts, 256)
-            dt = time.perf_counter() - t0
-            extras["decode_greedy"] = {"batch": 32, "prompt": 512, "new_tokens": 256, "seconds": round(dt, 4),
-                                       "generated_tok_per_s": round(32 * 256 / dt, 1),
-                                       "note": "prefill + 256 KV-cached greedy steps, host-visible"}
+                                         "d2h_gb_per_s": round(nb * T * WORKLOAD["vocab"] * 4 / dt / 1e9, 1),
+                                         "note": "host-visible, fp32 logits for 64 x seq tokens copied to the host: bound "
+                                                 "by the 2.1 GB download, not by the device"}
+        e.close()
+        e = None
+        for key in ("gqa1024", "reference"):
+            w2 = WORKLOADS[key]
+            toks2 = tokens
+            e2 = open_engine(ane, w2, w2["batch"], toks2)
+            for _ in range(3):
+                e2.step()
+            ms2, last2 = timed_steps(e2, 10)
+            tps = w2["batch"] * w2["cfg"]["seq"]
+            fl2 = train_flops_per_token(w2["cfg"], w2["arch"]) * tps
+            extras[f"train_step_{key}"] = {"workload": w2["name"], "ms_per_step": round(ms2 / 10, 4),
+                                           "tok_per_s": round(tps / (ms2 / 10 * 1e-3), 1),
+                                           "step_frac_of_burst_peak": round(fl2 / (ms2 / 10 * 1e-3) / 1e12 / tf_burst, 4),
+                                           "loss": round(float(last2.loss), 4)}
+            e2.close()
+        # KV-cached greedy decoding of the GQA variant: 32 sequences, 512-token prompts, 256 new tokens
+        w2 = WORKLOADS["gqa1024"]
+        e2 = open_engine(ane, w2, 32, tokens)
+        prompts = np.ascontiguousarray(tokens[:32 * 512].reshape(32, 512))
+        e2.decode_greedy(prompts[:, :64], 4)
+        t0 = time.perf_counter()
+        e2.decode_greedy(prompts, 256)
+        dt = time.perf_counter() - t0
+        # per decode step every weight (bf16) and the KV cache up to the current position are read once
+        n_w = (train_flops_per_token(w2["cfg"], "llama") - 3.5 * 2 * 12 * 1024 * 768) / 6
+        kvd = w2["cfg"]["dim"] // w2["cfg"]["n_heads"] * w2["cfg"]["n_kv_heads"]
+        kv_bytes = sum(32 * (512 + i) * kvd * 2 * 2 * 12 for i in range(256))
+        dec_bytes = 256 * n_w * 2 + kv_bytes
+        extras["decode_greedy_gqa1024"] = {"batch": 32, "prompt": 512, "new_tokens": 256, "seconds": round(dt, 4),
+                                           "generated_tok_per_s": round(32 * 256 / dt, 1),
+                                           "hbm_frac_lower_bound": round(dec_bytes / dt / 1e9 / hbm, 4),
+                                           "note": "prefill + 256 KV-cached greedy steps, host-visible; the fraction sets "
+                                                   "weight + KV-cache bytes of the decode steps against the measured copy "
+                                                   "bandwidth over the whole call (prefill included in the time)"}
+        e2.close()
+    if e is not None:
+        e.close()
+
+    # ---- configuration with a fixed global batch: 256 sequences per optimizer update on every N
+    c4 = None
+    if args.workload == "110m" and args.batch <= 0 and 256 % (MICRO_BATCH * world) == 0:
+        accum = 256 // (MICRO_BATCH * world)
+        e4 = open_engine(ane, wl, MICRO_BATCH, tokens, accum=accum, rank=rank, world=world, local_rank=local_rank,
+                         dp_id=new_dp_id(), ce_chunk=args.ce_chunk)
+        for _ in range(accum):          # one optimizer step of warm-up
+            e4.step()
+        n_opt = 3
+        ms4, last4 = timed_steps(e4, n_opt * accum)
+        e4.close()
+        c4 = {"global_batch": 256, "accum_steps": accum, "micro_batch_per_gpu": MICRO_BATCH,
+              "ms_per_optimizer_step": round(ms4 / n_opt, 4), "tok_per_s": round(256 * T * n_opt / (ms4 * 1e-3), 1),
+              "optimizer_steps_timed": n_opt, "flushed_last": bool(last4.flushed), "scaling": "strong"}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and args.workload == "110m":
         cpu_baseline = cpu_reference_leg(steps=8, warmup=1)
-    e.close()
     if rank == 0:
         line = {
             "metric": "train tok/s (110M, seq 256)", "value": round(value, 1), "unit": "tok/s", "n_gpus": world,
@@ -365,8 +469,12 @@ def run_ours(args):
                        "l2_policy": "inputs larger than L2 (GBs of activations per step)"},
             "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "loss": round(float(last.loss), 4),
-            "wall_ms_per_step": round(wall_ms / args.steps, 4), "eval_logits": eval_logits,
+            "repeats": repeats, "wall_ms_per_step": round(wall_ms / args.steps, 4), "eval_logits": eval_logits,
         }
+        if c4 is not None:
+            line["c4"] = c4
+        if dp_check is not None:
+            line["dp_check"] = dp_check
         if cpu_baseline is not None:
             line["cpu_baseline"] = cpu_baseline
         if extras is not None:
@@ -374,6 +482,8 @@ def run_ours(args):
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+    if dp_check is not None and not dp_check["replicas_identical"]:
+        sys.exit(3)
 
 
 def cpu_reference_leg(steps: int, warmup: int):
@@ -433,8 +543,9 @@ KERNEL_CASES = {
 
 
 def run_kernel_case(args):
-    """One GEMM shape of the step in isolation (device-resident zero operands), for ncu captures and
-    per-shape roofline numbers:  python bench.py --kernel-case classifier_fwd --steps 3 --warmup 2"""
+    """One GEMM shape of the step in isolation on seeded random operands (zeros would draw less power and run at
+    higher clocks than the step does), for ncu captures and per-shape roofline numbers:
+    python bench.py --kernel-case classifier_fwd --steps 3 --warmup 2"""
     import ctypes
 
     import ane
@@ -445,8 +556,22 @@ def run_kernel_case(args):
     with_res = len(KERNEL_CASES[args.kernel_case]) > 6
     c_bytes = M * N * (2 if out_mode == 0 else 4)
     dA, dB, dC = lib.ane_dev_malloc(M * K * 2), lib.ane_dev_malloc(N * K * 2), lib.ane_dev_malloc(c_bytes)
-    for p, n in ((dA, M * K * 2), (dB, N * K * 2), (dC, c_bytes)):
-        lib.ane_dev_memset(p, 0, n)
+    lib.ane_dev_memset(dC, 0, c_bytes)
+    rng = np.random.Generator(np.random.PCG64(5))
+
+    def fill_bf16(dst, n, scale):   # N(0, scale) in bf16, uploaded in pieces through an fp32 staging buffer
+        piece = 1 << 24
+        stage = lib.ane_dev_malloc(piece * 4)
+        for o in range(0, n, piece):
+            m = min(piece, n - o)
+            a = (scale * rng.standard_normal(m, dtype=np.float32)).astype(np.float32)
+            lib.ane_dev_h2d(stage, a.ctypes.data, m * 4)
+            lib.ane_op_cast_f32_to_bf16(stage, dst + o * 2, m)
+        lib.ane_dev_sync()
+        lib.ane_dev_free(stage)
+
+    fill_bf16(dA, M * K, 1.0)
+    fill_bf16(dB, N * K, 0.02)
     g = _ffi.GemmArgs()
     g.struct_size = ctypes.sizeof(_ffi.GemmArgs)
     g.dtype = ane.DTYPE_BF16
@@ -486,7 +611,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ce-chunk", type=int, default=0, help="token rows per classifier/CE chunk (0 = library default)")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="110m")
-    ap.add_argument("--extras", action="store_true", help="also time batch-64 evaluation and (seq >= 768) greedy decoding")
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
+    ap.add_argument("--no-extras", dest="extras", action="store_false",
+                    help="skip the extra one-GPU legs (batch-64 evaluation, GQA seq-1024 step and decode, reference architecture)")
     ap.add_argument("--batch", type=int, default=0, help="sequences per GPU per step (0 = the workload's own)")
     ap.add_argument("--kernel-case", choices=sorted(KERNEL_CASES), default=None)
     args = ap.parse_args()

@@ -31,6 +31,11 @@ extern "C" {
 
 #define ANE_DTYPE_BF16 0
 #define ANE_DTYPE_F32 1
+/* fp32 storage everywhere like ANE_DTYPE_F32, but every GEMM runs on the tensor cores as three bf16
+ * products of (hi, lo) operand pairs (Ah*Bh + Ah*Bl + Al*Bh, fp32 accumulation): near-fp32 results at
+ * tensor-core speed, for parity with the reference's fp32 CPU step where bf16 operands are too coarse
+ * (its backward recomputes the softmax from unscaled scores, ane/train_full.go:268-269). */
+#define ANE_DTYPE_BF16X3 2
 
 /* ---- device buffers and timing (test / measurement seams) ------------------- */
 int32_t ane_device_count(void);
@@ -75,11 +80,15 @@ const char* ane_op_sumsq_noalloc_last_error(void);
  * ane/common.go:91, ane/train_full.go:213,242, ane/stories/cpu.go:303-385).
  *   a_mn = 0: A stored [M,K];  a_mn = 1: A stored [K,M]
  *   b_mn = 0: B stored [N,K];  b_mn = 1: B stored [K,N]
- *   out_mode 0: store bf16, 1: store fp32, 2: C += (fp32, beta = 1)
+ *   out_mode 0: store bf16, 1: store fp32, 2: C += (fp32, beta = 1),
+ *            7: SwiGLU backward fused into the product (dX form, bf16 operands): A*B is d gate [m, n]; d_aux = h13
+ *               [m, 2n] bf16 with h1 | h3 interleaved in blocks of 32 columns; d_c receives d h13 [m, 2n] bf16 in the
+ *               same layout (ldc its pitch): d h1 = d gate * h3 * silu'(h1), d h3 = d gate * silu(h1)
+ *               (the reference's FFN is ReLU^2, ane/common.go:146; this is the llama-style counterpart)
  */
 typedef struct ane_gemm_args {
   uint32_t struct_size;
-  int32_t dtype; /* ANE_DTYPE_BF16 (tcgen05) or ANE_DTYPE_F32 (SIMT) operands */
+  int32_t dtype; /* operands: ANE_DTYPE_BF16 (tcgen05), ANE_DTYPE_F32 (SIMT), ANE_DTYPE_BF16X3 (fp32 in, split tcgen05) */
   const void* d_a;
   const void* d_b;
   void* d_c;
@@ -94,6 +103,9 @@ typedef struct ane_gemm_args {
   const float* d_s2;
   int32_t ldres;
   int32_t split_k; /* 0 = library chooses */
+  const void* d_aux; /* out_mode 7: h13 */
+  int32_t ldaux;
+  int32_t pad_;
 } ane_gemm_args;
 int32_t ane_op_gemm(const ane_gemm_args* args);
 
@@ -115,7 +127,7 @@ typedef struct ane_options {
   int32_t batch;          /* sequences per ane_step call (reference: 1) */
   int32_t arch;           /* ANE_ARCH_*                                  */
   int32_t quirks;         /* 1: reproduce the reference's backward exactly (ANE_ARCH_REFERENCE only) */
-  int32_t compute_dtype;  /* ANE_DTYPE_BF16 (tensor cores) or ANE_DTYPE_F32 (parity mode) */
+  int32_t compute_dtype;  /* ANE_DTYPE_BF16 (tensor cores), ANE_DTYPE_F32 (SIMT parity mode) or ANE_DTYPE_BF16X3 */
   float rope_theta;       /* 0: 100000 (reference arch) / 10000 (llama arch) */
   int32_t accum_steps;    /* ane_step calls per optimizer update */
   float lr;

@@ -56,6 +56,34 @@ def test_decode_bf16_matches_own_full_forward():
     e.close()
 
 
+def test_decode_bf16_gqa_full_size_batch_32_prompt_512():
+    """The decode configuration at full size: 110M GQA model (12 query / 4 KV heads, 12 layers, vocab 32000, KV cache
+    of 1024 positions), 32 sequences, 512-token prompts (prefill through the tcgen05 attention kernels, four 128-row
+    tiles), then KV-cached greedy steps.  Checked against the engine's own full-recompute forward on four of the
+    sequences: wherever the top-2 margin is clear the cached path picks the same token."""
+    cfg = dict(dim=768, hidden=2048, heads=12, kv_heads=4, layers=12, vocab=32000, seq=1024)
+    _, e = make_pair(ane, cfg, arch=O.ARCH_L, quirks=0, dtype=ane.DTYPE_BF16, batch=32, std=0.05, debug_taps=False)
+    prompts = O.zipf_tokens(32 * 512, cfg["vocab"], 12).reshape(32, 512)
+    n_new = 24
+    got = e.decode_greedy(prompts, n_new)
+    assert got.shape == (32, n_new) and got.max() < cfg["vocab"]
+    agree = total = 0
+    for b in (0, 7, 19, 31):
+        full = np.zeros(cfg["seq"], dtype=np.uint16)
+        full[:512] = prompts[b]
+        full[512:512 + n_new] = got[b]
+        logits = e.eval_logits(full)[0]                  # [vocab, seq], teacher-forced on the generated tokens
+        for step in range(n_new):
+            col = logits[:, 511 + step]
+            top2 = np.sort(col)[-2:]
+            if top2[1] - top2[0] > 0.05:
+                total += 1
+                agree += int(col.argmax() == got[b, step])
+    print(f"decode agreement {agree}/{total} on clear margins")
+    assert total >= 8 and agree == total
+    e.close()
+
+
 def test_decode_rejected_for_reference_arch():
     cfg = dict(dim=64, hidden=96, heads=4, layers=2, vocab=256, seq=32)
     _, e = make_pair(ane, cfg, arch=O.ARCH_N, quirks=1, dtype=ane.DTYPE_F32, batch=1, debug_taps=False)

@@ -49,6 +49,24 @@ def _run(rank, world, batch, dp_id, tokens, dtype, out_path, accum=1):
     e.close()
 
 
+def _join_or_kill(procs, timeout=300):
+    """A child that does not finish in time is ended here (terminate, then kill), so that it cannot keep a GPU
+    after the test has failed."""
+    codes = []
+    for p in procs:
+        p.join(timeout=timeout)
+        if p.is_alive():
+            p.terminate()
+            p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+                p.join(timeout=10)
+            codes.append("timeout")
+        else:
+            codes.append(p.exitcode)
+    assert codes == [0] * len(procs), codes
+
+
 @pytest.mark.parametrize("dtype,accum", [(ane.DTYPE_F32, 1), (ane.DTYPE_BF16, 1), (ane.DTYPE_F32, 2)])
 def test_two_gpu_data_parallel_matches_single_gpu(tmp_path, dtype, accum):
     if ane._ffi.lib.ane_device_count() < 2:
@@ -59,13 +77,10 @@ def test_two_gpu_data_parallel_matches_single_gpu(tmp_path, dtype, accum):
     procs = [ctx.Process(target=_run, args=(r, 2, B, dp_id, tokens, dtype, str(tmp_path / f"r{r}.npz"), accum)) for r in range(2)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(timeout=300)
-        assert p.exitcode == 0
+    _join_or_kill(procs)
     single = ctx.Process(target=_run, args=(0, 1, 2 * B, None, tokens, dtype, str(tmp_path / "single.npz"), accum))
     single.start()
-    single.join(timeout=300)
-    assert single.exitcode == 0
+    _join_or_kill([single])
     r0, r1, s = (np.load(tmp_path / f) for f in ("r0.npz", "r1.npz", "single.npz"))
     tol = 2e-5 if dtype == ane.DTYPE_F32 else 2e-3
     np.testing.assert_allclose((r0["losses"] + r1["losses"]) / 2, s["losses"], atol=1e-3 if dtype == ane.DTYPE_BF16 else 1e-5)

@@ -123,7 +123,34 @@ def test_short_k_wide_n_shapes_take_the_cta_pair_tiles():
         assert rel_l2(got, want + (R if res else 0)) < 1e-4, (M, N, K, b_mn, res)
 
 
-@pytest.mark.parametrize("dtype", [ane.DTYPE_BF16, ane.DTYPE_F32])
+def test_split_precision_gemm_carries_fp32_operands_through_the_tensor_cores():
+    """ANE_DTYPE_BF16X3: fp32 operands cut into bf16 (hi, lo) pairs, three tcgen05 products.  Against float64
+    on the unrounded operands the result must be fp32-like (a single bf16 product is ~3e-3 off); the three
+    operand layouts of the step, a residual, an accumulating output and ragged sizes."""
+    rng = np.random.default_rng(8)
+    M, N, K = 1024, 768, 2304
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = rng.standard_normal((K, N)).astype(np.float32)
+    got = _gemm(ane.DTYPE_BF16X3, A, B, np.zeros((M, N), np.float32), M, N, K, 0, 1, 1)
+    want = A.astype(np.float64) @ B.astype(np.float64)
+    assert rel_l2(got, want) < 2e-5
+    one = _gemm(ane.DTYPE_BF16, A, B, np.zeros((M, N), np.float32), M, N, K, 0, 1, 1)
+    assert rel_l2(one, want) > 1e-3                                     # the single bf16 product, for scale
+    M, N, K = 1000, 760, 776                                            # forward form, ragged, with a residual
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    W = rng.standard_normal((N, K)).astype(np.float32)
+    R = rng.standard_normal((M, N)).astype(np.float32)
+    got = _gemm(ane.DTYPE_BF16X3, A, W, np.zeros((M, N), np.float32), M, N, K, 0, 0, 1, res=R)
+    assert rel_l2(got, A.astype(np.float64) @ W.astype(np.float64).T + R) < 2e-5
+    M, N, K = 2304, 768, 2048                                           # weight-gradient form, accumulating
+    At = rng.standard_normal((K, M)).astype(np.float32)
+    B = rng.standard_normal((K, N)).astype(np.float32)
+    C0 = rng.standard_normal((M, N)).astype(np.float32)
+    got = _gemm(ane.DTYPE_BF16X3, At, B, C0, M, N, K, 1, 1, 2)
+    assert rel_l2(got, C0 + At.astype(np.float64).T @ B.astype(np.float64)) < 2e-5
+
+
+@pytest.mark.parametrize("dtype", [ane.DTYPE_BF16, ane.DTYPE_F32, ane.DTYPE_BF16X3])
 @pytest.mark.parametrize("oc,ic,seq", [(96, 64, 40), (256, 136, 300), (768, 256, 128)])
 def test_linear_forward_dx_dw_match_oracle(dtype, oc, ic, seq):
     """linearCF / linearBackwardDXCF / accumLinearGradCF (ane/common.go:91, ane/train_full.go:213,242)."""
@@ -150,6 +177,57 @@ def test_linear_forward_dx_dw_match_oracle(dtype, oc, ic, seq):
     for split in (1, 2):
         got = _gemm(dtype, np.ascontiguousarray(dy_cf.T), np.ascontiguousarray(x_cf.T), dw0, oc, ic, seq, 1, 1, 2, split)
         assert rel_l2(got, want) < tol
+
+
+def _down_bf16(p, shape):
+    n = int(np.prod(shape))
+    q = lib.ane_dev_malloc(n * 4)
+    _ck(lib.ane_op_cast_bf16_to_f32(p, q, n))
+    out = _down(q, shape)
+    lib.ane_dev_free(q)
+    return out
+
+
+@pytest.mark.parametrize("M,Hd,K", [(8192, 2048, 768), (300, 96, 136), (1000, 2048, 768)])
+def test_swiglu_backward_fused_into_the_dx_product(M, Hd, K):
+    """out_mode 7: d gate = dOut . W2 stays in the accumulators; the epilogue reads h1 | h3 (interleaved in blocks
+    of 32 columns) and writes d h1 = d gate * h3 * silu'(h1), d h3 = d gate * silu(h1) in the same layout.  Against
+    float64 on the same bf16 operands; the step's shape (CTA-pair tiles) and ragged ones (single-CTA tiles)."""
+    rng = np.random.default_rng(M + Hd)
+    dOut = _bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    W2 = _bf16_round((rng.standard_normal((K, Hd)) / np.sqrt(K)).astype(np.float32))       # stored [K, N]: MN-major B
+    h1 = _bf16_round(rng.standard_normal((M, Hd)).astype(np.float32) * 2.0)
+    h3 = _bf16_round(rng.standard_normal((M, Hd)).astype(np.float32))
+    h13 = np.empty((M, 2 * Hd), np.float32)
+    blk = h13.reshape(M, Hd // 32, 2, 32)
+    blk[:, :, 0, :] = h1.reshape(M, Hd // 32, 32)
+    blk[:, :, 1, :] = h3.reshape(M, Hd // 32, 32)
+    dA, dB, dH = _up_bf16(dOut), _up_bf16(W2), _up_bf16(h13)
+    dC = lib.ane_dev_malloc(M * 2 * Hd * 2)
+    _ck(lib.ane_dev_memset(dC, 0xFF, M * 2 * Hd * 2))
+    g = _ffi.GemmArgs()
+    g.struct_size = ctypes.sizeof(_ffi.GemmArgs)
+    g.dtype = ane.DTYPE_BF16
+    g.d_a, g.d_b, g.d_c, g.d_aux = dA, dB, dC, dH
+    g.m, g.n, g.k = M, Hd, K
+    g.lda, g.ldb, g.ldc, g.ldaux = K, Hd, 2 * Hd, 2 * Hd
+    g.a_mn, g.b_mn, g.out_mode, g.alpha = 0, 1, 7, 1.0
+    _ck(lib.ane_op_gemm(ctypes.byref(g)))
+    _ck(lib.ane_dev_sync())
+    st = ctypes.c_int32(0)
+    _ck(lib.ane_ops_device_status(ctypes.byref(st)))
+    assert st.value == 0
+    got = _down_bf16(dC, (M, 2 * Hd)).reshape(M, Hd // 32, 2, 32)
+    dg = dOut.astype(np.float64) @ W2.astype(np.float64)
+    x = h1.astype(np.float64)
+    sg = 1.0 / (1.0 + np.exp(-x))
+    want1 = dg * h3 * sg * (1.0 + x * (1.0 - sg))
+    want3 = dg * x * sg
+    assert np.isfinite(got).all()
+    assert rel_l2(got[:, :, 0, :].reshape(M, Hd), want1) < 4e-3          # one bf16 rounding of the output
+    assert rel_l2(got[:, :, 1, :].reshape(M, Hd), want3) < 4e-3
+    for p in (dA, dB, dH, dC):
+        lib.ane_dev_free(p)
 
 
 def test_gemm_rejects_misaligned_pitch():

@@ -20,12 +20,40 @@ MID = dict(dim=256, hidden=512, heads=4, layers=4, vocab=4096, seq=128)
 FWD_TAPS = [O.TAP_X, O.TAP_XNORM, O.TAP_Q, O.TAP_K, O.TAP_V, O.TAP_ATT, O.TAP_X2, O.TAP_X2NORM, O.TAP_H1, O.TAP_GATE]
 BWD_TAPS = [O.TAP_DOUT, O.TAP_DH1, O.TAP_DX2, O.TAP_DQ, O.TAP_DK, O.TAP_DV]
 F32_TOL = 1e-4
-BF16_TOL = 1e-2
-# Per-tensor weight gradients in bf16: 12 layers of bf16 operand rounding put the llama arch at
-# 1-2e-2.  With the reference's backward quirks the softmax is recomputed from unscaled scores
-# (ane/train_full.go:268-269), which amplifies any upstream rounding about tenfold.
-BF16_GRAD_TOL = {0: 6e-2, 1: 2e-2}
-LOSS_TOL = 1e-3
+BF16_TOL = 1e-2     # per-layer activations and per-tensor gradients, rel-L2 against the fp32 oracle
+LOSS_TOL = 1e-3     # nats
+
+# What exceeds the stated tolerance, by name.  Every GEMM product of two bf16-rounded operands carries a relative
+# error of ~1.6e-3 (2^-9 / sqrt(3) per operand); the residual stream sums two such branch outputs per layer, the
+# backward chain does the same in the other direction, and a weight gradient multiplies the two.  After 12
+# layers that is ~0.8e-2 on activations and 1.0-2.0e-2 on weight gradients: a property of bf16 operands, which
+# the split-precision mode (ANE_DTYPE_BF16X3, tested below against the unwidened tolerance) removes.
+# Entries: tensor kind -> (bound, cause).  A tensor above BF16_TOL whose kind is not listed, or above its
+# bound, fails the test; so does a count of tensors above BF16_TOL larger than the recorded one.
+CAUSE_DEPTH = "12 layers of bf16 operand rounding in the forward and backward chains (measured 1.0-1.3e-2)"
+CAUSE_QK = ("dS = P * (dP - delta) cancels the common part of v, so dq / dk are ~3x as sensitive to the bf16 rounding "
+            "of v and dO as the other gradients (measured <= 2.0e-2)")
+CAUSE_QUIRK = ("the reference's backward recomputes the softmax from unscaled scores (ane/train_full.go:268-269): |s| up "
+               "to 1.44 * head_dim, so bf16 rounding upstream of q and k is amplified ~10x in dq / dk and in everything "
+               "below them")
+EXC_LLAMA_12L = {"wq": (2.2e-2, CAUSE_QK), "wk": (2.2e-2, CAUSE_QK), "w1": (1.5e-2, CAUSE_DEPTH), "w2": (1.5e-2, CAUSE_DEPTH),
+                 "w3": (1.5e-2, CAUSE_DEPTH), "rms_ffn": (1.5e-2, CAUSE_DEPTH), "rms_att": (1.2e-2, CAUSE_DEPTH),
+                 "wo": (1.2e-2, CAUSE_DEPTH), "wv": (1.2e-2, CAUSE_DEPTH)}
+EXC_LLAMA_SHALLOW = {"wq": (1.5e-2, CAUSE_QK), "wk": (1.5e-2, CAUSE_QK), "rms_att": (1.2e-2, "one bf16 product per element, "
+                     "few rows to average over at this size"), "rms_ffn": (1.2e-2, "as rms_att"),
+                     "w1": (1.1e-2, CAUSE_DEPTH), "w3": (1.1e-2, CAUSE_DEPTH)}
+EXC_REFERENCE = {k: (6e-2, CAUSE_QUIRK) for k in ("wq", "wk", "wv", "wo", "w1", "w2", "embed", "smear_gate", "smear_lambda",
+                                                  "backout_lambda", "ve_embed", "ve_gate", "resid_lambdas", "x0_lambdas")}
+
+
+def check_grads(rep, exceptions, max_over):
+    """rep: (kind, layer, err, norm) per tensor.  Returns the offenders above BF16_TOL for the message."""
+    over = [(k, l, round(err, 5)) for k, l, err, nrm in rep if nrm > 0 and err > BF16_TOL]
+    for k, l, err in over:
+        assert k in exceptions, f"{k}[{l}] = {err} exceeds {BF16_TOL} and has no entry in the exception table"
+        assert err <= exceptions[k][0], f"{k}[{l}] = {err} exceeds its recorded bound {exceptions[k][0]} ({exceptions[k][1]})"
+    assert len(over) <= max_over, f"{len(over)} tensors above {BF16_TOL}, {max_over} recorded: {sorted(over, key=lambda x: -x[2])[:8]}"
+    return over
 
 
 def batch_tokens(cfg, batch, seed, invalid=True):
@@ -104,8 +132,62 @@ def test_bf16_step_matches_oracle(arch, quirks, extra):
     errs = tap_errors(m, e, cfg, 2, FWD_TAPS)
     assert max(errs.values()) < BF16_TOL, max(errs.items(), key=lambda kv: kv[1])
     rep = []
+    compare_grads(m, e, rep)
+    if arch == O.ARCH_L:     # 4 layers: two tensors sit at the tolerance (wq / wk of layer 1: 1.03e-2, 1.02e-2)
+        check_grads(rep, EXC_LLAMA_SHALLOW, 4)
+    else:                    # wq / wk of all four layers at 2.3-2.8e-2, wv / value embeddings / w1 at 1.0-1.3e-2
+        check_grads(rep, EXC_REFERENCE, 16)
+    e.close()
+
+
+@pytest.mark.parametrize("arch,quirks,extra", [(O.ARCH_L, 0, {"kv_heads": 2}), (O.ARCH_N, 1, {})])
+def test_split_precision_step_meets_the_stated_tolerance(arch, quirks, extra):
+    """ANE_DTYPE_BF16X3 (fp32 storage, every GEMM as three bf16 tensor-core products of hi / lo operand pairs):
+    the same step as test_bf16_step_matches_oracle with nothing widened -- activations, attention gradients,
+    every parameter gradient within 1e-2 (they come in near the fp32 engine's 1e-6), loss within 1e-3."""
+    cfg = dict(MID, **extra)
+    hyper = dict(lr=3e-4, adam_beta1=0.9, adam_beta2=0.95, weight_decay=0.1, grad_clip=1.0, accum_steps=1000)
+    m, e = make_pair(ane, cfg, arch=arch, quirks=quirks, dtype=ane.DTYPE_BF16X3, batch=2, hyper=hyper)
+    inp, tgt = batch_tokens(cfg, 2, 5)
+    losses = oracle_batch_accumulate(m, inp, tgt, cfg["seq"])
+    r = e.step_tokens(inp, tgt)
+    assert r.device_status == 0
+    assert abs(r.loss - float(np.mean(losses))) < 1e-4
+    errs = tap_errors(m, e, cfg, 2, FWD_TAPS + BWD_TAPS)
+    print("worst taps", sorted(errs.items(), key=lambda kv: -kv[1])[:3])
+    assert max(errs.values()) < 1e-3, max(errs.items(), key=lambda kv: kv[1])
+    rep = []
     worst = compare_grads(m, e, rep)
-    assert worst < BF16_GRAD_TOL[arch], sorted(rep, key=lambda x: -x[2])[:5]
+    print("worst gradients", sorted(rep, key=lambda x: -x[2])[:3])
+    assert worst < 1e-3, sorted(rep, key=lambda x: -x[2])[:5]
+    e.close()
+
+
+def test_split_precision_reference_network_full_size_two_steps():
+    """The reference's own network at its own size and hyperparameters (see
+    test_bf16_reference_network_full_size_two_steps), backward quirks on, in the split-precision mode: every
+    parameter gradient within 1e-2 and the loss within 1e-3 nats before and after an optimizer step -- the
+    stated tolerance on the tensor-core path, where plain bf16 operands give up to 5e-2."""
+    cfg = dict(dim=768, hidden=2048, heads=12, layers=12, vocab=32000, seq=256)
+    hyper = dict(lr=3e-4, adam_beta1=0.8, adam_beta2=0.95, adam_eps=1e-10, weight_decay=0.0, grad_clip=1.0,
+                 loss_scale=256.0, accum_steps=1000)
+    m, e = make_pair(ane, cfg, arch=O.ARCH_N, quirks=1, dtype=ane.DTYPE_BF16X3, batch=2, hyper=hyper)
+    for step in range(2):
+        inp, tgt = batch_tokens(cfg, 2, 50 + step, invalid=False)
+        losses = oracle_batch_accumulate(m, inp, tgt, cfg["seq"])
+        r = e.step_tokens(inp, tgt)
+        assert r.device_status == 0
+        print(f"step {step}: loss gpu {r.loss:.5f} oracle {float(np.mean(losses)):.5f}")
+        assert abs(r.loss - float(np.mean(losses))) < LOSS_TOL, (step, r.loss, losses)
+        if step == 0:
+            errs = tap_errors(m, e, cfg, 2, FWD_TAPS)
+            assert max(errs.values()) < BF16_TOL, max(errs.items(), key=lambda kv: kv[1])
+            rep = []
+            worst = compare_grads(m, e, rep)
+            print("worst gradients", sorted(rep, key=lambda x: -x[2])[:6])
+            assert worst < BF16_TOL, sorted(rep, key=lambda x: -x[2])[:5]
+        m.flush()
+        e.flush()
     e.close()
 
 
@@ -126,21 +208,84 @@ def test_bf16_110m_configuration_three_steps():
         # every weight by about lr in the direction of its gradient's sign and the loss falls by a nat per step;
         # entries whose gradient is below the bf16 noise take the other sign, and the ~0.1 % of the gradient's
         # L1 mass they hold shows up as ~2e-3 nats.
-        tol = LOSS_TOL if step == 0 else 5e-3
+        tol = LOSS_TOL if step == 0 else LOSS_TOL_AFTER_UPDATE
         print(f"step {step}: loss gpu {r.loss:.5f} oracle {float(np.mean(losses)):.5f}")
         assert abs(r.loss - float(np.mean(losses))) < tol, (step, r.loss, losses)
         if step == 0:
             errs = tap_errors(m, e, cfg, 2, FWD_TAPS)
-            # gate = silu(h1) * h3 multiplies two bf16-rounded factors: sqrt(2) x the error of either (1.27e-2 at
-            # layer 9, where the residual stream itself carries 0.85e-2)
+            # exception: gate = silu(h1) * h3 multiplies two bf16-rounded factors, sqrt(2) x the error of either
+            # (1.0-1.27e-2 in layers 2-11, where the residual stream itself carries up to 0.85e-2); nothing else
             plain = {k: v for k, v in errs.items() if k[0] != O.TAP_GATE}
             assert max(plain.values()) < BF16_TOL, max(plain.items(), key=lambda kv: kv[1])
-            assert max(errs.values()) < 1.5e-2, max(errs.items(), key=lambda kv: kv[1])
+            assert max(errs.values()) < 1.4e-2, max(errs.items(), key=lambda kv: kv[1])
             rep = []
-            assert compare_grads(m, e, rep) < BF16_GRAD_TOL[O.ARCH_L], sorted(rep, key=lambda x: -x[2])[:5]
+            compare_grads(m, e, rep)
+            # measured: 69 of the 111 tensors between 1.0e-2 and 2.0e-2 (wq / wk 1.3-2.0e-2, w1 / w2 / w3 / rms_ffn
+            # 1.1-1.3e-2, one rms_att, wq / wk of layer 0 at 1.1e-2); embedding, wo, wv, rms_final within 1e-2
+            over = check_grads(rep, EXC_LLAMA_12L, 80)
+            print(f"{len(over)} of {len(rep)} gradient tensors above {BF16_TOL}")
         m.flush()
         e.flush()
     assert e.state().adam_t == 3 and m.adam_t == 3
+    e.close()
+
+
+# After an AdamW update the two sides no longer hold the same weights: the first steps move every weight by about
+# lr along its gradient's sign, so entries whose gradient is below the bf16 noise go the other way, and the loss
+# falls a nat per step while that difference rides along.  Measured over 20 steps at full size: |diff| <= 2.4e-3,
+# no trend (it changes sign); 8.8e-4 before the first update.
+LOSS_TOL_AFTER_UPDATE = 3e-3
+
+
+def test_loss_trajectory_20_steps_bf16_llama_full_size():
+    """20 optimizer steps of the benchmark's model (dim 768, 12 layers, vocab 32000, seq 256; two sequences per
+    step, AdamW lr 3e-4, betas 0.9 / 0.95, weight decay 0.1, clip 1.0) in bf16 against the fp32 oracle."""
+    cfg = dict(dim=768, hidden=2048, heads=12, layers=12, vocab=32000, seq=256)
+    hyper = dict(lr=3e-4, adam_beta1=0.9, adam_beta2=0.95, weight_decay=0.1, grad_clip=1.0, accum_steps=1)
+    m, e = make_pair(ane, cfg, arch=O.ARCH_L, quirks=0, dtype=ane.DTYPE_BF16, batch=2, hyper=hyper, debug_taps=False)
+    diffs = []
+    for step in range(20):
+        inp, tgt = batch_tokens(cfg, 2, 40 + step, invalid=False)
+        losses = oracle_batch_accumulate(m, inp, tgt, cfg["seq"])
+        m.flush()
+        r = e.step_tokens(inp, tgt)
+        assert r.device_status == 0 and r.flushed
+        diffs.append(r.loss - float(np.mean(losses)))
+        assert abs(diffs[-1]) < (LOSS_TOL if step == 0 else LOSS_TOL_AFTER_UPDATE), (step, diffs)
+    print("loss differences", [f"{d:+.1e}" for d in diffs])
+    assert abs(float(np.mean(diffs))) < LOSS_TOL          # no drift: the mean difference stays inside the tolerance
+    assert e.state().adam_t == 20 and m.adam_t == 20
+    assert r.loss < 7.0                                   # and the model did train (10.56 at the start)
+    e.close()
+
+
+def test_bf16_gqa_seq_1024_one_step_full_size():
+    """The GQA long-context configuration at full size (12 query / 4 KV heads of 64, seq 1024 = eight 128-row
+    tiles of the tcgen05 attention kernels, 12 layers, vocab 32000), two sequences, bf16 against the oracle:
+    loss, forward taps, attention gradients and every parameter gradient."""
+    cfg = dict(dim=768, hidden=2048, heads=12, kv_heads=4, layers=12, vocab=32000, seq=1024)
+    hyper = dict(lr=3e-4, adam_beta1=0.9, adam_beta2=0.95, weight_decay=0.1, grad_clip=1.0, accum_steps=1000)
+    m, e = make_pair(ane, cfg, arch=O.ARCH_L, quirks=0, dtype=ane.DTYPE_BF16, batch=2, hyper=hyper)
+    inp, tgt = batch_tokens(cfg, 2, 60, invalid=False)
+    losses = oracle_batch_accumulate(m, inp, tgt, cfg["seq"])
+    r = e.step_tokens(inp, tgt)
+    assert r.device_status == 0
+    assert abs(r.loss - float(np.mean(losses))) < LOSS_TOL
+    errs = tap_errors(m, e, cfg, 2, FWD_TAPS)
+    # exceptions: with 1024 rows per sequence the residual stream itself reaches 1.0e-2 at layers 9-11, so the taps
+    # computed from it sit at 1.0-1.16e-2 there (k of layer 11 the largest) and k of layer 6 at 1.02e-2; the gate
+    # product (see the 110M test) at 1.0-1.5e-2 from layer 2 on.  Layers 0-5: everything but the gate within 1e-2.
+    first = {k: v for k, v in errs.items() if k[1] < 6 and k[0] != O.TAP_GATE}
+    assert max(first.values()) < BF16_TOL, max(first.items(), key=lambda kv: kv[1])
+    plain = {k: v for k, v in errs.items() if k[0] != O.TAP_GATE}
+    assert max(plain.values()) < 1.25e-2, max(plain.items(), key=lambda kv: kv[1])
+    assert max(errs.values()) < 1.6e-2, max(errs.items(), key=lambda kv: kv[1])
+    errs = tap_errors(m, e, cfg, 2, [O.TAP_DQ, O.TAP_DK, O.TAP_DV])
+    assert max(errs.values()) < 2.2e-2, sorted(errs.items(), key=lambda kv: -kv[1])[:4]      # CAUSE_QK
+    rep = []
+    compare_grads(m, e, rep)
+    over = check_grads(rep, dict(EXC_LLAMA_12L, embed=(1.1e-2, CAUSE_DEPTH), rms_final=(1.1e-2, CAUSE_DEPTH)), 90)
+    print(f"{len(over)} of {len(rep)} gradient tensors above {BF16_TOL}")
     e.close()
 
 
@@ -159,7 +304,7 @@ def test_bf16_reference_network_full_size_two_steps():
         losses = oracle_batch_accumulate(m, inp, tgt, cfg["seq"])
         r = e.step_tokens(inp, tgt)
         assert r.device_status == 0
-        tol = LOSS_TOL if step == 0 else 5e-3  # see test_bf16_110m_configuration_three_steps
+        tol = LOSS_TOL  # measured 0.9e-4, 7.3e-4
         print(f"step {step}: loss gpu {r.loss:.5f} oracle {float(np.mean(losses)):.5f}")
         assert abs(r.loss - float(np.mean(losses))) < tol, (step, r.loss, losses)
         if step == 0:
@@ -167,9 +312,11 @@ def test_bf16_reference_network_full_size_two_steps():
             print("worst forward taps", sorted(errs.items(), key=lambda kv: -kv[1])[:3])
             assert max(errs.values()) < BF16_TOL, max(errs.items(), key=lambda kv: kv[1])
             rep = []
-            worst = compare_grads(m, e, rep)
+            compare_grads(m, e, rep)
             print("worst gradients", sorted(rep, key=lambda x: -x[2])[:6])
-            assert worst < BF16_GRAD_TOL[O.ARCH_N], sorted(rep, key=lambda x: -x[2])[:5]
+            # plain bf16 operands: up to 5.0e-2 (wq / wk of layers 0-2), falling with depth to ~1e-2 at layer 11;
+            # the split-precision mode brings all of them inside 1e-2 (test_split_precision_reference_network_*)
+            check_grads(rep, EXC_REFERENCE, len(rep))
         m.flush()
         e.flush()
     assert e.state().adam_t == 2 and m.adam_t == 2
@@ -194,9 +341,10 @@ def test_bf16_attention_multi_tile_sequences(kv_heads, seq):
     # the product taps (gate = silu(h1)*h3) then sit slightly above 1e-2
     assert max(errs.values()) < 1.5e-2, max(errs.items(), key=lambda kv: kv[1])
     errs = tap_errors(m, e, cfg, 2, [O.TAP_DQ, O.TAP_DK, O.TAP_DV])
-    assert max(errs.values()) < 2e-2, sorted(errs.items(), key=lambda kv: -kv[1])[:4]
+    assert max(errs.values()) < 1.7e-2, sorted(errs.items(), key=lambda kv: -kv[1])[:4]      # CAUSE_QK: 1.2-1.6e-2
     rep = []
-    assert compare_grads(m, e, rep) < 2e-2, sorted(rep, key=lambda x: -x[2])[:5]
+    compare_grads(m, e, rep)
+    check_grads(rep, EXC_LLAMA_SHALLOW, 9)
     e.close()
 
 
@@ -216,9 +364,10 @@ def test_bf16_reference_arch_split_precision_attention_two_tiles():
     errs = tap_errors(m, e, cfg, 2, FWD_TAPS)
     assert max(errs.values()) < BF16_TOL, max(errs.items(), key=lambda kv: kv[1])
     errs = tap_errors(m, e, cfg, 2, [O.TAP_DQ, O.TAP_DK, O.TAP_DV])
-    assert max(errs.values()) < BF16_GRAD_TOL[O.ARCH_N], sorted(errs.items(), key=lambda kv: -kv[1])[:4]
+    assert max(errs.values()) < 3.2e-2, sorted(errs.items(), key=lambda kv: -kv[1])[:4]      # CAUSE_QUIRK: 2.4-2.9e-2
     rep = []
-    assert compare_grads(m, e, rep) < BF16_GRAD_TOL[O.ARCH_N], sorted(rep, key=lambda x: -x[2])[:5]
+    compare_grads(m, e, rep)
+    check_grads(rep, EXC_REFERENCE, 4)                                                        # wq / wk of both layers
     e.close()
 
 
@@ -241,13 +390,13 @@ def test_loss_trajectory_20_steps_bf16_reference_arch():
 
 
 def test_loss_trajectory_fp32_llama_tiny_config():
-    """The tiny CPU-runnable configuration (dim 288, 6 layers, 6 heads of 48, hidden 768, vocab 32000,
-    seq 256, batch 8 shrunk to 2 for test time), fp32 on both sides."""
+    """The tiny CPU-runnable configuration as stated (dim 288, 6 layers, 6 heads of 48, hidden 768, vocab 32000,
+    seq 256, batch 8, AdamW lr 3e-4 / 0.9 / 0.95 / weight decay 0.1), fp32 on both sides, 20 optimizer steps."""
     cfg = dict(dim=288, hidden=768, heads=6, layers=6, vocab=32000, seq=256)
     hyper = dict(lr=3e-4, adam_beta1=0.9, adam_beta2=0.95, weight_decay=0.1, accum_steps=1)
-    m, e = make_pair(ane, cfg, arch=O.ARCH_L, quirks=0, dtype=ane.DTYPE_F32, batch=2, hyper=hyper, debug_taps=False)
-    for step in range(2):
-        inp, tgt = batch_tokens(cfg, 2, 100 + step, invalid=False)
+    m, e = make_pair(ane, cfg, arch=O.ARCH_L, quirks=0, dtype=ane.DTYPE_F32, batch=8, hyper=hyper, debug_taps=False)
+    for step in range(20):
+        inp, tgt = batch_tokens(cfg, 8, 100 + step, invalid=False)
         losses = oracle_batch_accumulate(m, inp, tgt, cfg["seq"])
         m.flush()
         r = e.step_tokens(inp, tgt)
@@ -258,8 +407,13 @@ def test_loss_trajectory_fp32_llama_tiny_config():
     e.close()
 
 
-@pytest.mark.parametrize("arch,quirks,vocab,bad_token", [(O.ARCH_L, 0, 512, True), (O.ARCH_N, 1, 512, False),
-                                                         (O.ARCH_L, 0, 40000, True)])
+@pytest.mark.parametrize("arch,quirks,vocab,bad_token", [
+    (O.ARCH_L, 0, 512, True), (O.ARCH_N, 1, 512, False), (O.ARCH_L, 0, 40000, True),
+    pytest.param(O.ARCH_N, 1, 512, True, marks=pytest.mark.xfail(strict=True, reason=(
+        "reference architecture with a token outside the vocabulary in bf16: wv / w1 / wo of layer 0 come in at "
+        "7.4e-2 (bound 6e-2); that position's residual has norm ~0.005, the parameterless norms scale its gradient "
+        "~200-fold, and the one row then carries the weight gradient, so bf16 rounding no longer averages over rows"))),
+])
 def test_bf16_head_with_invalid_targets_and_wide_vocabulary(arch, quirks, vocab, bad_token):
     """The bf16 training head (bf16 logits, fp32 target logit, cross-entropy kernel) with a target outside
     the vocabulary (zero gradient row, not counted), with and without the soft cap, and in the llama cases a
@@ -280,7 +434,26 @@ def test_bf16_head_with_invalid_targets_and_wide_vocabulary(arch, quirks, vocab,
     assert r.device_status == 0
     assert abs(r.loss - float(np.mean(losses))) < LOSS_TOL
     rep = []
-    assert compare_grads(m, e, rep) < BF16_GRAD_TOL[arch], sorted(rep, key=lambda x: -x[2])[:5]
+    compare_grads(m, e, rep)
+    if arch == O.ARCH_L:
+        check_grads(rep, {}, 0)                      # two layers: everything within 1e-2
+    else:
+        check_grads(rep, EXC_REFERENCE, 6)           # wq / wk of both layers 2.1-2.5e-2, x0 lambdas 1.2e-2
+    e.close()
+
+
+def test_split_precision_head_with_a_token_outside_the_vocabulary_reference_arch():
+    """The case that plain bf16 fails (xfail above) in the split-precision mode: inside the stated tolerance."""
+    cfg = dict(dim=128, hidden=256, heads=2, layers=2, vocab=512, seq=128)
+    m, e = make_pair(ane, cfg, arch=O.ARCH_N, quirks=1, dtype=ane.DTYPE_BF16X3, batch=2, hyper=dict(lr=3e-4, accum_steps=1000))
+    inp, tgt = batch_tokens(cfg, 2, 21, invalid=False)
+    tgt[1, 3] = 65535
+    inp[0, 5] = 65535
+    losses = oracle_batch_accumulate(m, inp, tgt, cfg["seq"])
+    r = e.step_tokens(inp, tgt)
+    assert r.device_status == 0 and abs(r.loss - float(np.mean(losses))) < 1e-4
+    rep = []
+    assert compare_grads(m, e, rep) < BF16_TOL, sorted(rep, key=lambda x: -x[2])[:5]
     e.close()
 
 
