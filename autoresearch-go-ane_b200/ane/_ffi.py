@@ -32,7 +32,8 @@ class Options(ctypes.Structure):
         ("embed_lr_mult", c_float), ("scalar_lr_mult", c_float), ("lambda_lr_mult", c_float),
         ("lambda_beta1", c_float), ("lambda_beta2", c_float),
         ("use_ane", c_int32), ("hybrid_backward", c_int32), ("device", c_int32), ("rank", c_int32),
-        ("world_size", c_int32), ("debug_taps", c_int32), ("ce_chunk_rows", c_int32), ("reserved", c_int32 * 6),
+        ("world_size", c_int32), ("debug_taps", c_int32), ("ce_chunk_rows", c_int32), ("ce_chunk_cols", c_int32),
+        ("reserved", c_int32 * 5),
     ]
 
 

@@ -68,6 +68,7 @@ class Options:
     dp_id: bytes | None = None
     debug_taps: bool = False
     ce_chunk_rows: int = 0
+    ce_chunk_cols: int = 0
 
 
 @dataclass
@@ -120,7 +121,7 @@ class Engine:
         for name in ("dim", "hidden", "n_layers", "n_heads", "n_kv_heads", "vocab", "seq", "batch", "arch", "quirks",
                      "compute_dtype", "rope_theta", "accum_steps", "lr", "seed", "adam_beta1", "adam_beta2", "adam_eps",
                      "weight_decay", "grad_clip", "loss_scale", "embed_lr_mult", "scalar_lr_mult", "lambda_lr_mult",
-                     "lambda_beta1", "lambda_beta2", "device", "rank", "world_size", "ce_chunk_rows"):
+                     "lambda_beta1", "lambda_beta2", "device", "rank", "world_size", "ce_chunk_rows", "ce_chunk_cols"):
             setattr(o, name, getattr(opts, name))
         o.use_ane = int(opts.use_ane)
         o.hybrid_backward = int(opts.hybrid_backward)

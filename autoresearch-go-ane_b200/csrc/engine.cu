@@ -198,7 +198,8 @@ class EngineT final : public EngineBase {
       cudaEventRecord(e1, st);
       prof_events_.push_back({e0, e1});
       prof_shapes_.push_back({d.M, d.N, d.K, (d.a_mn ? 1 : 0) | (d.b_mn ? 2 : 0) | (d.out << 2) | (d.res1 ? 16 : 0)});
-      prof_flops_ += 2.0 * (double)d.M * (double)d.N * (double)d.K;
+      // the recomputed classifier product of the logit-free head is time spent, not algorithmic work
+      if (d.out != GEMM_OUT_CE_GRAD) prof_flops_ += 2.0 * (double)d.M * (double)d.N * (double)d.K;
     }
     if (rc != 0) return fail(ANE_ERR_KERNEL, gemm_last_error());
     return 0;
@@ -283,6 +284,14 @@ class EngineT final : public EngineBase {
   bool dw_overlap_ = true;
   float *rstdf_ = nullptr, *logits_ = nullptr, *loss_rows_ = nullptr, *inv_valid_ = nullptr, *d_loss_ = nullptr;
   float* tgt_logit_ = nullptr;             // fp32 logit of every row's target (bf16-logits cross-entropy)
+  // Classifier head that keeps no logits (bf16 engines): statistics of pass 1 per 256-column tile and row, the
+  // rows' log2-sum-exp and gradient coefficients, and the gradient block [M, head_cols_] that pass 2 writes and
+  // the dX / dEmbed products read while it is still in L2.
+  bool head_fused_ = false;
+  int head_cols_ = 0;
+  float *ce_stats_ = nullptr, *ce_lse2_ = nullptr, *ce_coef_ = nullptr;
+  bf16* dl_block_ = nullptr;
+  int fused_head(int B);
   T* dlogits_ = nullptr;
   T* dlogits2_ = nullptr;                  // second chunk buffer: the classifier dW GEMM of chunk c runs on the
   cudaEvent_t ev_cls_ce_[2] = {nullptr, nullptr};  // side stream while chunk c+1 is computed
@@ -543,7 +552,13 @@ int EngineT<T>::alloc_buffers() {
     A(qkvh_, (size_t)M_ * QKVD_); A(qkvl_, (size_t)M_ * QKVD_); A(dqkv_raw_, (size_t)M_ * QKVD_);
     A(att_lse_b_, (size_t)B_ * H_ * S_);
   }
-  A(logits_, (size_t)ce_rows_ * V_); A(dlogits_, (size_t)ce_rows_ * V_); A(dlogits2_, (size_t)ce_rows_ * V_);
+  A(logits_, (size_t)ce_rows_ * V_);
+  if (head_fused_) {
+    A(ce_stats_, (size_t)2 * ((V_ + 255) / 256) * M_); A(ce_lse2_, M_); A(ce_coef_, M_);
+    A(dl_block_, (size_t)M_ * head_cols_);
+  } else {
+    A(dlogits_, (size_t)ce_rows_ * V_); A(dlogits2_, (size_t)ce_rows_ * V_);
+  }
   A(loss_rows_, M_); A(inv_valid_, B_); A(d_loss_, 4); A(tgt_logit_, M_);
   A(rope_cos_, (size_t)S_ * (hd_ / 2)); A(rope_sin_, (size_t)S_ * (hd_ / 2));
   A(d_acc_, 2); A(d_scales_, 4); A(d_norm_, 2); A(d_status_, 1);
@@ -604,7 +619,18 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
   N13_ = isN_ ? Hd_ : 2 * Hd_;
   att_tc_ = !qkv_f32_ && attention_tc_supported(hd_);
   att_split_ = !kIsF32 && qkv_f32_ && attention_tcgen05_supported(hd_, S_) && getenv("ANE_B200_ATT_SIMT") == nullptr;
-  ce_rows_ = o_.ce_chunk_rows > 0 ? o_.ce_chunk_rows : 8192;  // 8192 x 32000 bf16 logits = 524 MB per chunk
+  // bf16 engines: the training head keeps no logits (two passes over the classifier product, the gradient formed
+  // per block of vocabulary columns).  ANE_B200_HEAD_UNFUSED=1 keeps the chunked logits -> cross-entropy form.
+  head_fused_ = !kIsF32 && getenv("ANE_B200_HEAD_UNFUSED") == nullptr;
+  if (head_fused_) {
+    // gradient block [M, cols] in bf16: sized to stay in L2 between its producer and its two consumers (<= 64 MB)
+    int cols = o_.ce_chunk_cols > 0 ? o_.ce_chunk_cols : (int)std::min<size_t>(65536, ((size_t)64 << 20) / ((size_t)2 * B_ * S_));
+    cols = std::max(256, cols / 256 * 256);
+    head_cols_ = std::min(cols, (V_ + 255) / 256 * 256);
+  }
+  // rows per logits chunk where logits still exist: the unfused head (8192 x 32000 bf16 = 524 MB) and the
+  // evaluation paths (fp32 logits, 1024 rows at a time when the training head keeps none)
+  ce_rows_ = o_.ce_chunk_rows > 0 ? o_.ce_chunk_rows : (head_fused_ ? 1024 : 8192);
   if (ce_rows_ > M_) ce_rows_ = M_;
   ce_rows_ = std::max(ce_rows_, std::min(M_, S_));  // eval logits uses one sequence per chunk
   lr_ = o_.lr;
@@ -890,6 +916,16 @@ int EngineT<T>::head_and_backward(int B) {
   int rc;
   count_launch();
   count_valid_targets(d_tgt_, inv_valid_, B, S_, V_, stream_);
+  if (head_fused_) {
+    if ((rc = fused_head(B)) != 0) return rc;
+    count_launch();
+    reduce_loss(loss_rows_, inv_valid_, d_loss_, B, S_, stream_);
+    const float* w_fin = isN_ ? nullptr : P_ + s_rms_final_.off;
+    count_launch();
+    rmsnorm_backward<T>(dy_, xs_[L_], w_fin, rstdf_, nullptr, nullptr, dcur_[0], tcopy_arg(dcur_t_[0]),
+                        isN_ ? nullptr : G_ + s_rms_final_.off, M, D_, stream_);
+    return backward_layers(B);
+  }
   // The dEmbed GEMM of a chunk runs on the side stream (it only feeds the optimizer); the two dlogits
   // buffers alternate so that the next chunk's cross-entropy does not overwrite its operand.
   cudaStream_t dws = (dw_overlap_ && !profiling_) ? dw_stream_ : stream_;
@@ -943,6 +979,60 @@ int EngineT<T>::head_and_backward(int B) {
   rmsnorm_backward<T>(dy_, xs_[L_], w_final, rstdf_, nullptr, nullptr, dcur_[0], tcopy_arg(dcur_t_[0]),
                       isN_ ? nullptr : G_ + s_rms_final_.off, M, D_, stream_);
   return backward_layers(B);
+}
+
+// ------------------------------------------------------------------------------------------------
+// The same head without logits in memory (bf16 engines).  Pass 1: the classifier product with an epilogue
+// that keeps, per row and 256-column tile, only the maximum and the sum of exponentials, plus the row's
+// target logit; a small kernel merges them into the row's log-sum-exp, loss and gradient coefficient.
+// Pass 2, per block of vocabulary columns: the product again, its epilogue writing
+// coef * (softmax - onehot) in bf16 into a block that stays in L2, then dy (+)= block * Embed[block] and
+// gEmbed[block] += block^T * xn.  One more product than the stored-logits form in exchange for ~2 GB less
+// HBM traffic per step and no [tokens, vocab] buffer.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+int EngineT<T>::fused_head(int B) {
+  if constexpr (kIsF32) {
+    return fail(ANE_ERR_STATE, "storiesane step: the logit-free head runs on bf16 engines");
+  } else {
+    const int M = B * S_;
+    int rc;
+    GemmDesc g;
+    g.A = xnf_; g.B = wop(s_embed_.off); g.C = nullptr;
+    g.M = M; g.N = V_; g.K = D_; g.lda = D_; g.ldb = D_; g.ldc = V_;
+    g.out = GEMM_OUT_CE_STATS;
+    g.tgt = d_tgt_; g.tgt_out = tgt_logit_; g.tgt_row0 = 0;
+    g.ce_stats = ce_stats_; g.ce_rows = M; g.ce_softcap = isN_;
+    count_launch();
+    if ((rc = gemm(g)) != 0) return rc;
+    count_launch();
+    ce_merge_stats(ce_stats_, (V_ + 255) / 256, M, tgt_logit_, d_tgt_, inv_valid_, S_, V_, isN_, o_.loss_scale, ce_lse2_,
+                   ce_coef_, loss_rows_, stream_);
+    for (int v0 = 0; v0 < V_; v0 += head_cols_) {
+      const int nc = std::min(head_cols_, V_ - v0);
+      GemmDesc p2 = g;  // logits of columns [v0, v0 + nc) again, turned into their gradient
+      p2.B = wop(s_embed_.off + (size_t)v0 * D_); p2.C = dl_block_;
+      p2.N = nc; p2.ldc = head_cols_;
+      p2.out = GEMM_OUT_CE_GRAD;
+      p2.tgt_out = nullptr; p2.ce_stats = nullptr;
+      p2.ce_lse2 = ce_lse2_; p2.ce_coef = ce_coef_; p2.ce_col0 = v0;
+      count_launch();
+      if ((rc = gemm(p2)) != 0) return rc;
+      GemmDesc gx;  // dy (+)= block * Embed[v0 : v0 + nc]   (ane/stories/cpu.go:333-360)
+      gx.A = dl_block_; gx.B = wop(s_embed_.off + (size_t)v0 * D_); gx.C = dy_;
+      gx.M = M; gx.N = D_; gx.K = nc; gx.lda = head_cols_; gx.ldb = D_; gx.ldc = D_; gx.b_mn = true; gx.out = GEMM_OUT_F32;
+      if (v0 > 0) { gx.res1 = dy_; gx.s1 = d_one_; gx.ldres = D_; }  // in place: every piece is read before it is written
+      count_launch();
+      if ((rc = gemm(gx)) != 0) return rc;
+      GemmDesc gw;  // gEmbed[v0 : v0 + nc] += block^T * xn   (ane/stories/cpu.go:366-385)
+      gw.A = dl_block_; gw.B = xnf_; gw.C = G_ + s_embed_.off + (size_t)v0 * D_;
+      gw.M = nc; gw.N = D_; gw.K = M; gw.lda = head_cols_; gw.ldb = D_; gw.ldc = D_; gw.a_mn = true; gw.b_mn = true;
+      gw.out = GEMM_OUT_ACCUM;
+      count_launch();
+      if ((rc = gemm(gw)) != 0) return rc;
+    }
+    return 0;
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1563,7 +1653,24 @@ int EngineT<T>::eval_loss(const uint16_t* tokens, uint32_t n_seq, double* loss_s
     shift_targets_kernel<<<(M + 255) / 256, 256, 0, stream_>>>(d_in_, d_tgt_, nb, S_);
     if ((rc = forward(d_in_, nb, S_, 0)) != 0) return rc;
     cudaMemsetAsync(loss_rows_, 0, sizeof(float) * M, stream_);
-    for (int r0 = 0; r0 < M; r0 += ce_rows_) {
+    bool fused_done = false;
+    if constexpr (!kIsF32) {
+      if (head_fused_) {  // pass 1 of the logit-free head is all the loss needs: statistics, target logits, merge
+        GemmDesc g;
+        g.A = xnf_; g.B = wop(s_embed_.off); g.C = nullptr;
+        g.M = M; g.N = V_; g.K = D_; g.lda = D_; g.ldb = D_; g.ldc = V_;
+        g.out = GEMM_OUT_CE_STATS;
+        g.tgt = d_tgt_; g.tgt_out = tgt_logit_; g.tgt_row0 = 0;
+        g.ce_stats = ce_stats_; g.ce_rows = M; g.ce_softcap = isN_;
+        count_launch();
+        if ((rc = gemm(g)) != 0) return rc;
+        count_launch();
+        ce_merge_stats(ce_stats_, (V_ + 255) / 256, M, tgt_logit_, d_tgt_, nullptr, S_, V_, isN_, 0.f, ce_lse2_, ce_coef_,
+                       loss_rows_, stream_);
+        fused_done = true;
+      }
+    }
+    for (int r0 = 0; r0 < M && !fused_done; r0 += ce_rows_) {
       const int rows = std::min(ce_rows_, M - r0);
       GemmDesc g;
       g.A = xnf_ + (size_t)r0 * D_; g.B = wop(s_embed_.off); g.C = logits_;

@@ -186,7 +186,8 @@ template <int BN, int MT, bool A_MN, bool B_MN>
 static int dispatch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const GemmDesc& d, int split_k,
                         int* d_status, cudaStream_t stream) {
   EpiParams epi{d.alpha, d.res1, d.s1, d.res2, d.s2, d.ldres, reinterpret_cast<bf16*>(d.aux), d.ldaux,
-                d.rope_cos, d.rope_sin, d.rope_seq, d.rope_pos0, d.rope_cols, d.tgt, d.tgt_out, d.tgt_row0};
+                d.rope_cos, d.rope_sin, d.rope_seq, d.rope_pos0, d.rope_cols, d.tgt, d.tgt_out, d.tgt_row0,
+                d.ce_stats, d.ce_lse2, d.ce_coef, d.ce_rows, d.ce_col0, d.ce_softcap ? 1 : 0};
   CUtensorMap tc;
   if (d.out == GEMM_OUT_BF16) {
     if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 64, 32, false)) return -2;
@@ -234,6 +235,17 @@ static int dispatch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
       return launch_tc<BN, MT, A_MN, B_MN, EPI_STORE_BF16_RELU2>(ta, tb, tc, td, epi, d, 1, d_status, stream);
     } else {
       g_gemm_err = "the ReLU^2 epilogue takes K-major operands only";
+      return -2;
+    }
+  }
+  if (d.out == GEMM_OUT_CE_STATS || d.out == GEMM_OUT_CE_GRAD) {
+    if constexpr (!A_MN && !B_MN && BN == 256 && (MT == 1 || MT == GEMM_MT_PAIR)) {
+      if (d.out == GEMM_OUT_CE_STATS)  // no output tensor: the A map stands in for the unused descriptors
+        return launch_tc<BN, MT, A_MN, B_MN, EPI_CE_STATS>(ta, tb, ta, ta, epi, d, 1, d_status, stream);
+      if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 64, 32, false)) return -2;
+      return launch_tc<BN, MT, A_MN, B_MN, EPI_CE_GRAD>(ta, tb, tc, tc, epi, d, 1, d_status, stream);
+    } else {
+      g_gemm_err = "the classifier-head epilogues take K-major operands on 256-column tiles";
       return -2;
     }
   }
@@ -437,6 +449,21 @@ int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream) {
       return -2;
     }
     // 256-column tiles: CTA pairs when they fill their waves (the step's shape), else one CTA per tile
+    const int pairs = gemm_num_sms() / 2;
+    const long tiles = (long)((d.M + 255) / 256) * ((d.N + 255) / 256);
+    const long waves = (tiles + pairs - 1) / pairs;
+    const double eff = (double)tiles / (double)(waves * pairs);
+    static const bool no_pair = [] { const char* e = getenv("ANE_B200_GEMM_PAIR"); return e && atoi(e) == 0; }();
+    if (!no_pair && d.M >= 256 && eff >= 0.8) return dispatch_layout<256, GEMM_MT_PAIR>(d, 1, d_status, stream);
+    return dispatch_layout<256, 1>(d, 1, d_status, stream);
+  }
+  if (d.out == GEMM_OUT_CE_STATS || d.out == GEMM_OUT_CE_GRAD) {
+    const bool stats = d.out == GEMM_OUT_CE_STATS;
+    if (d.a_mn || d.b_mn || d.tgt == nullptr || (stats && (d.ce_stats == nullptr || d.tgt_out == nullptr || d.ce_rows < d.M)) ||
+        (!stats && (d.ce_lse2 == nullptr || d.ce_coef == nullptr || d.C == nullptr))) {
+      g_gemm_err = "classifier-head epilogue: K-major operands, targets and the statistics / per-row buffers are required";
+      return -2;
+    }
     const int pairs = gemm_num_sms() / 2;
     const long tiles = (long)((d.M + 255) / 256) * ((d.N + 255) / 256);
     const long waves = (tiles + pairs - 1) / pairs;

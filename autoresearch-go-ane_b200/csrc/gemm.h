@@ -38,6 +38,14 @@ enum GemmOut : int {
   //   d h1 = d gate * h3 * silu'(h1),  d h3 = d gate * silu(h1),
   // from the fp32 accumulators; d gate itself is not stored.  A K-major, B MN-major (the dX form), N % 32 == 0.
   GEMM_OUT_DSWIGLU = 7,
+  // Classifier head that keeps no logits (both K-major operands, 256-column tiles).
+  // CE_STATS: nothing is stored but, per row and 256-column tile, the maximum and the sum of exponentials of the
+  //   (optionally soft-capped) logits in the log2 domain -> ce_stats[tile][row] (float2, ce_rows rows per tile), and
+  //   the row's target logit -> tgt_out (like GEMM_OUT_BF16_TGT).
+  // CE_GRAD: the product is recomputed for the vocabulary columns [ce_col0, ce_col0 + N) and
+  //   C(bf16)[row, col] = ce_coef[row] * (2^(z log2e - ce_lse2[row]) - [col is the row's target]) (* d softcap).
+  GEMM_OUT_CE_STATS = 8,
+  GEMM_OUT_CE_GRAD = 9,
 };
 
 struct GemmDesc {
@@ -62,6 +70,11 @@ struct GemmDesc {
   const uint16_t* tgt = nullptr;  // GEMM_OUT_BF16_TGT
   float* tgt_out = nullptr;
   int tgt_row0 = 0;
+  float* ce_stats = nullptr;       // GEMM_OUT_CE_STATS
+  const float* ce_lse2 = nullptr;  // GEMM_OUT_CE_GRAD
+  const float* ce_coef = nullptr;
+  int ce_rows = 0, ce_col0 = 0;
+  bool ce_softcap = false;
   int split_k = 0;  // 0 => choose
 };
 

@@ -114,7 +114,24 @@ enum EpiKind : int {
   // are one 64-column bf16 piece of h13, fetched by TMA like the residual pieces of EPI_STORE_F32_TMARES, and its
   // d h1 | d h3 columns one 64-column piece of the output.  d gate itself is never written.
   EPI_DSWIGLU = 8,
+  // Classifier head without logits in memory, pass 1: acc = logits tile.  Every row's maximum and sum of
+  // exponentials over the tile's columns (log2 domain, after the optional soft cap) go to ce_stats[tile_n][row];
+  // the row's target logit, if its column falls into the tile, to tgt_out (fp32, before the soft cap).  Nothing
+  // else is stored.
+  EPI_CE_STATS = 9,
+  // Pass 2 (logits recomputed for a block of vocabulary columns): C(bf16) = coef[row] * (softmax - onehot)
+  // [* d softcap] with the row's log2-sum-exp from pass 1; the gradient of the loss with respect to the logits.
+  EPI_CE_GRAD = 10,
 };
+__device__ __forceinline__ float epi_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// tanh by one ex2 and one fast reciprocal: 1 - 2 / (1 + 2^(2 u log2 e))
+__device__ __forceinline__ float epi_tanh(float u) {
+  return 1.f - __fdividef(2.f, 1.f + epi_ex2(2.885390081777927f * u));
+}
 struct EpiParams {
   float alpha;
   const float* res1;  // optional fp32 [M, ldres]
@@ -127,9 +144,15 @@ struct EpiParams {
   const float* rope_cos;  // EPI_STORE_BF16_ROPE: [positions, 32]
   const float* rope_sin;
   int rope_seq, rope_pos0, rope_cols;
-  const uint16_t* tgt;  // EPI_STORE_BF16_TGT
+  const uint16_t* tgt;  // EPI_STORE_BF16_TGT, EPI_CE_STATS, EPI_CE_GRAD
   float* tgt_out;
   int tgt_row0;
+  float* ce_stats;       // EPI_CE_STATS: [tiles_n][ce_rows] pairs (max, sum of 2^(z - max)), z in the log2 domain
+  const float* ce_lse2;  // EPI_CE_GRAD: per row log2-sum-exp
+  const float* ce_coef;  // EPI_CE_GRAD: per row gradient coefficient (0: row without a target)
+  int ce_rows;           // row count of the statistics buffer
+  int ce_col0;           // vocabulary column of this product's column 0
+  int ce_softcap;        // z = 15 tanh(logit / 15) (ane/common.go:272-287)
 };
 
 // Work scheduler shared by the three warp roles (each role walks the same sequence).
@@ -390,7 +413,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, 32*lane_group+32)
     // Columns per staged piece: 128 bytes of output per row.
     constexpr bool kBf16Out = (EPI == EPI_STORE_BF16 || EPI == EPI_STORE_BF16_SWIGLU || EPI == EPI_STORE_BF16_ROPE ||
-                               EPI == EPI_STORE_BF16_TGT || EPI == EPI_STORE_BF16_RELU2);
+                               EPI == EPI_STORE_BF16_TGT || EPI == EPI_STORE_BF16_RELU2 || EPI == EPI_CE_STATS ||
+                               EPI == EPI_CE_GRAD);
     constexpr int CW = kBf16Out ? 64 : 32;
     constexpr int SBUF = Cfg::SBUF;
     const uint32_t stage_base = smem_stage0 + (uint32_t)(warp - 2) * (uint32_t)(SBUF * 4096);
@@ -466,8 +490,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       }
       int tgt_col = -1;        // EPI_STORE_BF16_TGT: this row's target column
-      if constexpr (EPI == EPI_STORE_BF16_TGT) {
+      if constexpr (EPI == EPI_STORE_BF16_TGT || EPI == EPI_CE_STATS || EPI == EPI_CE_GRAD) {
         if (m < M) tgt_col = (int)epi.tgt[epi.tgt_row0 + m];
+      }
+      float ce_m = -INFINITY, ce_s = 0.f;  // EPI_CE_STATS: this row's running maximum / sum over the tile's pieces
+      float ce_l = 0.f, ce_c = 0.f;        // EPI_CE_GRAD: this row's log2-sum-exp and coefficient
+      if constexpr (EPI == EPI_CE_GRAD) {
+        if (m < M) {
+          ce_l = epi.ce_lse2[m];
+          ce_c = epi.ce_coef[m];
+        }
       }
       uint32_t gate_even[16];  // EPI_STORE_BF16_SWIGLU: the even piece's half of a gate row
       float4 rc4[8], rs4[8];   // EPI_STORE_BF16_ROPE: cos / sin of this thread's token, 32 pairs
@@ -509,12 +541,97 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
         tmem_ld_wait();
+        if constexpr (EPI == EPI_CE_STATS) {
+          constexpr float kL2e = 1.4426950408889634f;
+          const int t = tgt_col - epi.ce_col0 - n0;
+          if (t >= 0 && t < CW) {  // one piece per row at most
+            float v = 0.f;
+#pragma unroll
+            for (int e = 0; e < CW; ++e) v = (e == t) ? acc[e] : v;
+            epi.tgt_out[epi.tgt_row0 + m] = epi.alpha * v;
+          }
+          const int nvalid = N - n0;  // columns past the matrix hold zeros: they must not count
+          // Four independent chains for the maximum and for the sum: one warp per scheduler has only its own
+          // instruction-level parallelism to hide the latency of the adds and of the exponentials.
+          float pm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          float ps[4] = {0.f, 0.f, 0.f, 0.f};
+          if (!epi.ce_softcap && nvalid >= CW) {  // the common case: 2^(acc * a2 - max) straight from the accumulators
+            const float a2 = epi.alpha * kL2e;    // alpha > 0: the maximum of the raw values is the maximum of the scaled ones
+#pragma unroll
+            for (int e = 0; e < CW; e += 4) {
+              pm[0] = fmaxf(pm[0], acc[e]); pm[1] = fmaxf(pm[1], acc[e + 1]);
+              pm[2] = fmaxf(pm[2], acc[e + 2]); pm[3] = fmaxf(pm[3], acc[e + 3]);
+            }
+            const float mn = fmaxf(ce_m, a2 * fmaxf(fmaxf(pm[0], pm[1]), fmaxf(pm[2], pm[3])));
+#pragma unroll
+            for (int e = 0; e < CW; e += 4) {
+              ps[0] += epi_ex2(fmaf(acc[e], a2, -mn)); ps[1] += epi_ex2(fmaf(acc[e + 1], a2, -mn));
+              ps[2] += epi_ex2(fmaf(acc[e + 2], a2, -mn)); ps[3] += epi_ex2(fmaf(acc[e + 3], a2, -mn));
+            }
+            ce_s = ce_s * epi_ex2(ce_m - mn) + ((ps[0] + ps[1]) + (ps[2] + ps[3]));
+            ce_m = mn;
+          } else {
+#pragma unroll
+            for (int e = 0; e < CW; ++e) {
+              float v = epi.alpha * acc[e];
+              if (epi.ce_softcap) v = 15.f * epi_tanh(v * (1.f / 15.f));
+              v = (e < nvalid) ? v * kL2e : -INFINITY;
+              acc[e] = v;
+              pm[e & 3] = fmaxf(pm[e & 3], v);
+            }
+            const float mn = fmaxf(ce_m, fmaxf(fmaxf(pm[0], pm[1]), fmaxf(pm[2], pm[3])));
+#pragma unroll
+            for (int e = 0; e < CW; ++e) ps[e & 3] += epi_ex2(acc[e] - mn);
+            ce_s = ce_s * epi_ex2(ce_m - mn) + ((ps[0] + ps[1]) + (ps[2] + ps[3]));
+            ce_m = mn;
+          }
+          continue;  // nothing is staged or stored
+        }
         // The piece staged SBUF iterations ago must have been read by its TMA store before its
         // buffer is rewritten.
         if (lane == 0) tma_store_wait_read<SBUF - 1>();
         __syncwarp();
         uint8_t* row_ptr = stage_ptr + sbuf * 4096 + lane * 128;
-        if constexpr (EPI == EPI_DSWIGLU) {
+        if constexpr (EPI == EPI_CE_GRAD) {
+          constexpr float kL2e = 1.4426950408889634f;
+          const int t = tgt_col - epi.ce_col0 - n0;
+          // The one-hot term touches one element of one piece per row: it is taken out of the sweep.  A row whose
+          // target falls into this piece first fetches that raw value, then corrects the element after the sweep.
+          float corr = 0.f;
+          const bool has_t = t >= 0 && t < CW;
+          if (has_t) {
+            float v = 0.f;
+#pragma unroll
+            for (int e = 0; e < CW; ++e) v = (e == t) ? acc[e] : v;
+            v *= epi.alpha;
+            float dcap = 1.f;
+            if (epi.ce_softcap) {
+              const float th = epi_tanh(v * (1.f / 15.f));
+              dcap = 1.f - th * th;
+            }
+            corr = ce_c * dcap;
+          }
+          if (!epi.ce_softcap) {
+            const float a2 = epi.alpha * kL2e;
+#pragma unroll
+            for (int e = 0; e < CW; ++e) acc[e] = ce_c * epi_ex2(fmaf(acc[e], a2, -ce_l));
+          } else {
+#pragma unroll
+            for (int e = 0; e < CW; ++e) {
+              const float th = epi_tanh(epi.alpha * acc[e] * (1.f / 15.f));
+              acc[e] = ce_c * epi_ex2(fmaf(15.f * th, kL2e, -ce_l)) * (1.f - th * th);
+            }
+          }
+          if (has_t) {
+#pragma unroll
+            for (int e = 0; e < CW; ++e) acc[e] = (e == t) ? acc[e] - corr : acc[e];
+          }
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<uint4*>(row_ptr + ((q ^ (lane & 7)) << 4)) =
+                make_uint4(pack2_bf16(acc[8 * q], acc[8 * q + 1]), pack2_bf16(acc[8 * q + 2], acc[8 * q + 3]),
+                           pack2_bf16(acc[8 * q + 4], acc[8 * q + 5]), pack2_bf16(acc[8 * q + 6], acc[8 * q + 7]));
+        } else if constexpr (EPI == EPI_DSWIGLU) {
           const uint32_t b = res_uses & 1u;
           if (!mbar_wait(smem_u32(&bar_res[warp - 2][b]), (res_uses >> 1) & 1u, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
             ok = false;
@@ -704,6 +821,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tma_store_commit();
         }
         sbuf = (sbuf + 1) % SBUF;
+      }
+      if constexpr (EPI == EPI_CE_STATS) {
+        if (m < M && m_warp < M && tn * BN < N)
+          reinterpret_cast<float2*>(epi.ce_stats)[(size_t)tn * epi.ce_rows + m] = make_float2(ce_m, ce_s);
       }
       }  // sub
       tc_fence_before();

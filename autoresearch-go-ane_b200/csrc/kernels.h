@@ -139,6 +139,11 @@ void cross_entropy_rows(const float* logits, const uint16_t* targets, const floa
 void cross_entropy_rows_bf16(const bf16* logits, const uint16_t* targets, const float* inv_valid, const float* tgt_logit,
                              bf16* dlogits, float* loss_rows, int rows, int row0, int seq, int V, bool softcap,
                              float grad_scale, cudaStream_t s);
+// Between the two passes of the classifier head that keeps no logits: per-tile (max, sum) pairs [n_tiles][rows]
+// (log2 domain) -> lse2[row], coef[row] = grad_scale * inv_valid[row / seq] (0 without a target) and loss_rows[row].
+void ce_merge_stats(const float* stats, int n_tiles, int rows, const float* tgt_logit, const uint16_t* targets,
+                    const float* inv_valid, int seq, int V, bool softcap, float grad_scale, float* lse2, float* coef,
+                    float* loss_rows, cudaStream_t s);
 void softcap_inplace(float* logits, uint64_t n, cudaStream_t s);
 // inv_valid[b] = 1/count(targets[b,:] < V) (0 when none); ane/stories/cpu.go:276-279.
 void count_valid_targets(const uint16_t* targets, float* inv_valid, int B, int seq, int V, cudaStream_t s);

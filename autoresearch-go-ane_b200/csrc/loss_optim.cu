@@ -429,6 +429,49 @@ template void cross_entropy_rows<float>(const float*, const uint16_t*, const flo
 template void cross_entropy_rows<bf16>(const float*, const uint16_t*, const float*, bf16*, float*, int, int, int, int,
                                        bool, float, cudaStream_t);
 
+// Classifier head without logits in memory, between its two passes: the per-tile (maximum, sum) pairs of a row
+// (log2 domain) combine to the row's log2-sum-exp; the loss of the row follows from its target logit
+// (ane/stories/cpu.go:212-292: -log(max(p[target], 1e-10)); rows whose target lies outside the vocabulary
+// count nothing and get a zero gradient row), and coef = grad_scale * inv_valid[sequence] is what pass 2
+// multiplies (softmax - onehot) by.  One thread per row; stats is [n_tiles][rows].
+__global__ void ce_merge_stats_kernel(const float2* __restrict__ stats, int n_tiles, int rows, const float* __restrict__ tgt_logit,
+                                      const uint16_t* __restrict__ targets, const float* __restrict__ inv_valid, int seq, int V,
+                                      int softcap, float grad_scale, float* __restrict__ lse2, float* __restrict__ coef,
+                                      float* __restrict__ loss_rows) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  float m = -INFINITY, s = 0.f;
+  for (int t = 0; t < n_tiles; ++t) {
+    const float2 v = stats[(size_t)t * rows + r];
+    const float mn = fmaxf(m, v.x);
+    s = s * exp2f(m - mn) + v.y * exp2f(v.x - mn);
+    m = mn;
+  }
+  const float l2 = m + log2f(s);
+  lse2[r] = l2;
+  const int tgt = targets[r];
+  if (tgt >= V) {
+    coef[r] = 0.f;
+    if (loss_rows) loss_rows[r] = 0.f;
+    return;
+  }
+  coef[r] = inv_valid ? grad_scale * inv_valid[r / seq] : 0.f;
+  if (loss_rows) {
+    float zt = tgt_logit[r];
+    if (softcap) zt = softcap_f(zt);
+    loss_rows[r] = -logf(fmaxf(exp2f(zt * 1.4426950408889634f - l2), 1e-10f));
+  }
+}
+void ce_merge_stats(const float* stats, int n_tiles, int rows, const float* tgt_logit, const uint16_t* targets,
+                    const float* inv_valid, int seq, int V, bool softcap, float grad_scale, float* lse2, float* coef,
+                    float* loss_rows, cudaStream_t s) {
+  if (rows <= 0) return;
+  launch_pdl(ce_merge_stats_kernel, dim3((rows + 127) / 128), dim3(128), 0, s, reinterpret_cast<const float2*>(stats), n_tiles,
+             rows, tgt_logit, targets, inv_valid, seq, V, softcap ? 1 : 0, grad_scale, lse2, coef, loss_rows);
+}
+
 __global__ void softcap_inplace_kernel(float* __restrict__ logits, uint64_t n) {
   uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;

@@ -109,8 +109,8 @@ type cOptions struct {
 	embedLRMult, scalarLRMult, lambdaLRMult          float32
 	lambdaBeta1, lambdaBeta2                         float32
 	useANE, hybridBackward, device, rank, worldSize  int32
-	debugTaps, ceChunkRows                           int32
-	reserved                                         [6]int32
+	debugTaps, ceChunkRows, ceChunkCols              int32
+	reserved                                         [5]int32
 }
 
 type cStepResult struct {

@@ -195,12 +195,12 @@ def fwd_flops_per_token(cfg, arch):
     return 2 * n_mm + 2 * L * T * D
 
 
-def open_engine(ane, wl, batch, tokens, *, accum=1, rank=0, world=1, local_rank=0, dp_id=None, ce_chunk=0):
+def open_engine(ane, wl, batch, tokens, *, accum=1, rank=0, world=1, local_rank=0, dp_id=None, ce_chunk=0, ce_cols=0):
     is_ref_arch = wl["arch"] == "reference"
     opts = ane.Options(tokens=tokens, batch=batch, arch=ane.ARCH_REFERENCE if is_ref_arch else ane.ARCH_LLAMA,
                        quirks=1 if is_ref_arch else 0, compute_dtype=ane.DTYPE_BF16,
                        accum_steps=accum, lr=3e-4, adam_beta1=0.9, adam_beta2=0.95, weight_decay=0.1, grad_clip=1.0,
-                       seed=42, device=local_rank, rank=rank, world_size=world, dp_id=dp_id, ce_chunk_rows=ce_chunk,
+                       seed=42, device=local_rank, rank=rank, world_size=world, dp_id=dp_id, ce_chunk_rows=ce_chunk, ce_chunk_cols=ce_cols,
                        **wl["cfg"])
     e = ane.open(opts)
     init_weights(e, ane, seed=1234, cfg=wl["cfg"])
@@ -264,7 +264,7 @@ def run_ours(args):
     hbm, tf_burst, tf_sust, src = measured_peaks()
     tokens = zipf_tokens(N_STREAM_TOKENS, WORKLOAD["vocab"], seed=0)
     e = open_engine(ane, wl, MICRO_BATCH, tokens, rank=rank, world=world, local_rank=local_rank, dp_id=new_dp_id(),
-                    ce_chunk=args.ce_chunk)
+                    ce_chunk=args.ce_chunk, ce_cols=args.ce_cols)
     T = WORKLOAD["seq"]
     tokens_per_step = MICRO_BATCH * T * world
 
@@ -446,7 +446,7 @@ def run_ours(args):
     if args.workload == "110m" and args.batch <= 0 and 256 % (MICRO_BATCH * world) == 0:
         accum = 256 // (MICRO_BATCH * world)
         e4 = open_engine(ane, wl, MICRO_BATCH, tokens, accum=accum, rank=rank, world=world, local_rank=local_rank,
-                         dp_id=new_dp_id(), ce_chunk=args.ce_chunk)
+                         dp_id=new_dp_id(), ce_chunk=args.ce_chunk, ce_cols=args.ce_cols)
         for _ in range(accum):          # one optimizer step of warm-up
             e4.step()
         n_opt = 3
@@ -610,6 +610,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ce-chunk", type=int, default=0, help="token rows per classifier/CE chunk (0 = library default)")
+    ap.add_argument("--ce-cols", type=int, default=0,
+                    help="vocabulary columns per gradient block of the logit-free head (0 = library default)")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="110m")
     ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
     ap.add_argument("--no-extras", dest="extras", action="store_false",

@@ -139,8 +139,9 @@ typedef struct ane_options {
   int32_t device;          /* CUDA device ordinal */
   int32_t rank, world_size;/* data-parallel rank / size (world_size <= 1: single GPU) */
   int32_t debug_taps;      /* 1: keep per-layer gradient taps for ane_get_tap */
-  int32_t ce_chunk_rows;   /* token rows per classifier/cross-entropy chunk (0: library chooses) */
-  int32_t reserved[6];
+  int32_t ce_chunk_rows;   /* token rows per logits chunk where logits exist (evaluation; fp32 heads) (0: library chooses) */
+  int32_t ce_chunk_cols;   /* vocabulary columns per gradient block of the logit-free training head (0: library chooses) */
+  int32_t reserved[5];
 } ane_options;
 
 /* Mirrors ane.StepResult (ane/engine.go:55-69); durations in nanoseconds. */
