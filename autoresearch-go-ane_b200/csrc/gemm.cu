@@ -119,8 +119,11 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
                      const GemmDesc& d, int split_k, int* d_status, cudaStream_t stream) {
   auto kern = gemm_tc_kernel<BN, MT, A_MN, B_MN, EPI>;
   constexpr bool tma_res = (EPI == EPI_STORE_F32_TMARES || EPI == EPI_DSWIGLU);
-  constexpr uint32_t smem_bytes = GemmCfg<BN, MT>::smem_bytes(tma_res, EPI == EPI_DSWIGLU);
-  static_assert(smem_bytes <= GEMM_SMEM_LIMIT && GemmCfg<BN, MT>::stages(tma_res, EPI == EPI_DSWIGLU) >= 3, "pipeline does not fit");
+  constexpr int depth = GemmCfg<BN, MT>::res_depth(EPI);
+  constexpr int ew = GemmCfg<BN, MT>::epi_warps(EPI);
+  constexpr int threads = 64 + 32 * ew;
+  constexpr uint32_t smem_bytes = GemmCfg<BN, MT>::smem_bytes(tma_res, EPI == EPI_DSWIGLU, depth, ew);
+  static_assert(smem_bytes <= GEMM_SMEM_LIMIT && GemmCfg<BN, MT>::stages(tma_res, EPI == EPI_DSWIGLU, depth, ew) >= 3, "pipeline does not fit");
   static bool attr_set = false;  // per template instantiation
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
@@ -138,7 +141,7 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     if (max_pairs == 0) {
       cudaLaunchConfig_t q = {};
       q.gridDim = dim3(2 * 74);
-      q.blockDim = dim3(GEMM_THREADS);
+      q.blockDim = dim3(threads);
       q.dynamicSmemBytes = smem_bytes;
       cudaLaunchAttribute at[1];
       at[0].id = cudaLaunchAttributeClusterDimension;
@@ -154,7 +157,7 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     }
     const int work = base_tiles * (split_k > 0 ? split_k : 1);
     const int pairs = work < max_pairs ? work : max_pairs;
-    cudaError_t e = launch_pdl_cluster(kern, dim3(2 * (pairs < 1 ? 1 : pairs)), dim3(GEMM_THREADS), smem_bytes, stream, 2u,
+    cudaError_t e = launch_pdl_cluster(kern, dim3(2 * (pairs < 1 ? 1 : pairs)), dim3(threads), smem_bytes, stream, 2u,
                                        ta, tb, tc, td, epi, d.M, d.N, d.K, split_k > 0 ? split_k : 1, d_status);
     if (e != cudaSuccess) {
       g_gemm_err = std::string("gemm_tc pair launch: ") + cudaGetErrorString(e);
@@ -173,7 +176,7 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     grid = (int)g;
   }
   if (grid < 1) grid = 1;
-  cudaError_t e = launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), smem_bytes, stream, ta, tb, tc, td, epi, d.M, d.N,
+  cudaError_t e = launch_pdl(kern, dim3(grid), dim3(threads), smem_bytes, stream, ta, tb, tc, td, epi, d.M, d.N,
                              d.K, split_k, d_status);
   if (e != cudaSuccess) {
     g_gemm_err = std::string("gemm_tc launch: ") + cudaGetErrorString(e);

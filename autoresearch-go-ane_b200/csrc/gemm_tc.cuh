@@ -28,7 +28,10 @@ namespace ane {
 
 static constexpr int GEMM_BM = 128;
 static constexpr int GEMM_BK = 64;
-static constexpr int GEMM_THREADS = 192;
+static constexpr int GEMM_THREADS = 192;  // TMA warp, MMA warp, four epilogue warps (kernels with eight: 320)
+#ifndef ANE_B200_GEMM_EW8
+#define ANE_B200_GEMM_EW8 0  // 1: the SwiGLU epilogues of the 256-column CTA-pair kernels run on eight epilogue warps
+#endif
 
 // MT = number of 128-row A sub-tiles per output tile.  MT = 2 (256 x BN tiles) shares every B tile between
 // two MMAs, so the shared-memory fill per FLOP drops by a third; its MT*BN accumulator columns leave no
@@ -56,17 +59,33 @@ struct GemmCfg {
   // measured no faster than two and cost a pipeline stage).
   static constexpr int SBUF = 2;
   static constexpr uint32_t STAGING_BYTES = 4 * SBUF * 4096;  // 4 epilogue warps x SBUF buffers x (32 rows x 128 B)
+  // Epilogue warps.  The epilogues that do arithmetic per element and move more than one piece per 64 accumulator
+  // columns (SwiGLU forward: h13 + gate; SwiGLU backward: h13 in, d h13 out) take longer than the 12-k-block main
+  // loop of their products with four warps (one per scheduler, ~750 cycles of fixed cost per piece).  With eight,
+  // two warps share each TMEM lane group and split the tile's columns (256-column CTA-pair tiles only).  Measured
+  // with ANE_B200_GEMM_EW8=1: the two warps of a scheduler then share its exponential unit and the pipeline drops
+  // to three stages, W2-dX 51 -> 46 us, W1|W3 forward 51 -> 56 us, the step unchanged; hence off by default.
+  __host__ __device__ static constexpr int epi_warps(int epi_kind) {
+    return (ANE_B200_GEMM_EW8 && PAIR && SUBS == 1 && BN == 256 && (epi_kind == 3 || epi_kind == 8)) ? 8 : 4;
+  }
+  __host__ __device__ static constexpr uint32_t staging_bytes(int ew) { return (uint32_t)ew * SBUF * 4096; }
   // Pipeline depth.  Single-CTA kernels take what fits beside the staging buffers and use the TMA-fed residual
   // epilogue only if its buffers still fit; pair kernels give up stages for them instead.
   // `room`: also a single-CTA kernel gives up stages for the TMA-fed input pieces (an epilogue that cannot do without them)
-  __host__ __device__ static constexpr int stages(bool tma_res, bool room = false) {
-    const uint32_t avail = GEMM_SMEM_LIMIT - 1024u - STAGING_BYTES - (((PAIR || room) && tma_res) ? GEMM_TMARES_BYTES : 0u);
+  // `depth`: input pieces each epilogue warp keeps in flight; `ew`: epilogue warps
+  __host__ __device__ static constexpr int stages(bool tma_res, bool room = false, int depth = 2, int ew = 4) {
+    const uint32_t res = (uint32_t)(ew * depth) * 4096u;
+    const uint32_t avail = GEMM_SMEM_LIMIT - 1024u - staging_bytes(ew) - (((PAIR || room) && tma_res) ? res : 0u);
     const int n = (int)(avail / (A_BYTES + B_BYTES));
     return n > 6 ? 6 : n;
   }
-  __host__ __device__ static constexpr uint32_t smem_bytes(bool tma_res, bool room = false) {  // +1024: alignment
-    return stages(tma_res, room) * (A_BYTES + B_BYTES) + STAGING_BYTES + 1024 + (tma_res ? GEMM_TMARES_BYTES : 0u);
+  __host__ __device__ static constexpr uint32_t smem_bytes(bool tma_res, bool room = false, int depth = 2, int ew = 4) {  // +1024: alignment
+    return stages(tma_res, room, depth, ew) * (A_BYTES + B_BYTES) + staging_bytes(ew) + 1024 +
+           (tma_res ? (uint32_t)(ew * depth) * 4096u : 0u);
   }
+  // Input pieces (residual, h13) each epilogue warp keeps in flight.  Four instead of two measured no faster for the
+  // SwiGLU backward (its pieces arrive in time; the epilogue is bound by its arithmetic), so two everywhere.
+  __host__ __device__ static constexpr int res_depth(int) { return 2; }
   static constexpr int ACC_COLS = SUBS * BN;                     // one accumulator set
   static constexpr int NBUF = (2 * ACC_COLS <= 512) ? 2 : 1;     // TMEM accumulator sets
   static constexpr uint32_t TMEM_COLS = (NBUF * ACC_COLS <= 256) ? 256 : 512;
@@ -211,13 +230,15 @@ struct GemmSched {
 };
 
 template <int BN, int MT, bool A_MN, bool B_MN, int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(64 + 32 * GemmCfg<BN, MT>::epi_warps(EPI), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD, EpiParams epi, int M,
                int N, int K, int split_k, int* status) {
   using Cfg = GemmCfg<BN, MT>;
   constexpr bool kTmaRes = (EPI == EPI_STORE_F32_TMARES || EPI == EPI_DSWIGLU);  // an input piece per output piece, by TMA
-  constexpr int STAGES = Cfg::stages(kTmaRes, EPI == EPI_DSWIGLU);
+  constexpr int RD = Cfg::res_depth(EPI);  // input pieces in flight per epilogue warp
+  constexpr int EW = Cfg::epi_warps(EPI);  // epilogue warps: 4, or 8 (two per TMEM lane group, half of the columns each)
+  constexpr int STAGES = Cfg::stages(kTmaRes, EPI == EPI_DSWIGLU, RD, EW);
   constexpr int BM = Cfg::BM_TILE, BK = GEMM_BK;
   constexpr int NBUF = Cfg::NBUF;
   constexpr bool PAIR = Cfg::PAIR;
@@ -232,7 +253,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __shared__ __align__(8) uint64_t bar_tfull[NBUF];
   __shared__ __align__(8) uint64_t bar_tempty[NBUF];
   __shared__ uint32_t tmem_slot;
-  __shared__ __align__(8) uint64_t bar_res[4][2];  // EPI_STORE_F32_TMARES: residual piece landed
+  __shared__ __align__(8) uint64_t bar_res[8][4];  // TMA-fed input pieces (residual, h13): piece landed
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smem_a0 = smem_base;
@@ -258,13 +279,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       mbar_init(smem_u32(&bar_empty[s]), 1);
     }
     if constexpr (kTmaRes) {
-      for (int w = 0; w < 4; ++w)
-        for (int b = 0; b < 2; ++b) mbar_init(smem_u32(&bar_res[w][b]), 1);
+      for (int w = 0; w < EW; ++w)
+        for (int b = 0; b < RD; ++b) mbar_init(smem_u32(&bar_res[w][b]), 1);
       tma_prefetch_desc(&tmD);
     }
     for (int b = 0; b < NBUF; ++b) {
       mbar_init(smem_u32(&bar_tfull[b]), 1);
-      mbar_init(smem_u32(&bar_tempty[b]), PAIR ? 8 : 4);  // the epilogue warps of both CTAs
+      mbar_init(smem_u32(&bar_tempty[b]), (PAIR ? 2 : 1) * EW);  // the epilogue warps of both CTAs
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
@@ -428,9 +449,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (epi.res2) a2 = epi.s2 ? *epi.s2 : 1.f;
     }
     // EPI_STORE_F32_TMARES: this warp's two residual buffers, behind the store staging of all four warps
-    const uint32_t res_base = smem_stage0 + Cfg::STAGING_BYTES + (uint32_t)(warp - 2) * 8192u;
+    const uint32_t res_base = smem_stage0 + Cfg::staging_bytes(EW) + (uint32_t)(warp - 2) * (uint32_t)(RD * 4096);
+    // with eight warps, warps 2-5 take the first half of the tile's columns and warps 6-9 the second
+    constexpr int CSPAN = BN / (EW / 4);
+    const int c_begin = ((warp - 2) >> 2) * CSPAN, c_end = c_begin + CSPAN;
     const uint8_t* res_ptr = smem_raw + (res_base - smem_u32(smem_raw));
-    uint32_t res_uses = 0;  // pieces consumed so far (buffer = uses & 1, phase = (uses >> 1) & 1)
+    uint32_t res_uses = 0;  // pieces consumed so far (buffer = uses % RD, phase = (uses / RD) & 1)
     GemmSched sched;
     sched.init(M, N, K, BM, BN, split_k, sched_id, sched_n);
     int tm, tn, kb0, kb1;
@@ -444,8 +468,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       auto prefetch_first = [&](int m) {
         if constexpr (EPI == EPI_STORE_F32) {
           pre_ok = false;
-          if (epi.res1 && m < M && tn * BN + 32 <= N) {
-            const float4* rp = reinterpret_cast<const float4*>(epi.res1 + (size_t)m * epi.ldres + tn * BN);
+          if (epi.res1 && m < M && tn * BN + c_begin + 32 <= N) {
+            const float4* rp = reinterpret_cast<const float4*>(epi.res1 + (size_t)m * epi.ldres + tn * BN + c_begin);
 #pragma unroll
             for (int q = 0; q < 8; ++q) pre[q] = rp[q];
             pre_ok = true;
@@ -458,9 +482,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t res_issued = res_uses;
       auto issue_res = [&](int m_w, int n0r) {
         if constexpr (kTmaRes) {
-          if (n0r < N && n0r < (tn + 1) * BN && m_w < M) {
+          if (n0r < N && n0r < tn * BN + c_end && m_w < M) {
             if (lane == 0) {
-              const uint32_t b = res_issued & 1u;
+              const uint32_t b = res_issued % (uint32_t)RD;
               const uint32_t bar = smem_u32(&bar_res[warp - 2][b]);
               mbar_expect_tx(bar, 4096);
               tma_load_2d(res_base + b * 4096u, &tmD, bar, EPI == EPI_DSWIGLU ? 2 * n0r : n0r, m_w);
@@ -470,8 +494,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       };
       if constexpr (kTmaRes) {  // first two pieces of sub-tile 0, while the MMAs still run
-        issue_res(tm * BM + sub_row(0) + lane_group * 32, tn * BN);
-        issue_res(tm * BM + sub_row(0) + lane_group * 32, tn * BN + CW);
+#pragma unroll
+        for (int k = 0; k < RD; ++k) issue_res(tm * BM + sub_row(0) + lane_group * 32, tn * BN + c_begin + k * CW);
       }
       if (!mbar_wait(smem_u32(&bar_tfull[buf]), tphase, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
         ok = false;
@@ -485,8 +509,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (sub > 0) {
         prefetch_first(m);
         if constexpr (kTmaRes) {
-          issue_res(m_warp, tn * BN);
-          issue_res(m_warp, tn * BN + CW);
+#pragma unroll
+          for (int k = 0; k < RD; ++k) issue_res(m_warp, tn * BN + c_begin + k * CW);
         }
       }
       int tgt_col = -1;        // EPI_STORE_BF16_TGT: this row's target column
@@ -518,7 +542,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) +
                              (uint32_t)(buf * Cfg::ACC_COLS + sub * BN);
 #pragma unroll 1
-      for (int c = 0; c < BN; c += CW) {
+      for (int c = c_begin; c < c_end; c += CW) {
         const int n0 = tn * BN + c;
         if (n0 >= N || m_warp >= M) break;  // warp-uniform
         float acc[CW];
@@ -533,7 +557,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int q = 0; q < 8; ++q) cur[q] = pre[q];
           pre_ok = false;
           const int nn = n0 + CW;
-          if (epi.res1 && m < M && c + CW < BN && nn + 32 <= N) {
+          if (epi.res1 && m < M && c + CW < c_end && nn + 32 <= N) {
             const float4* rp = reinterpret_cast<const float4*>(epi.res1 + (size_t)m * epi.ldres + nn);
 #pragma unroll
             for (int q = 0; q < 8; ++q) pre[q] = rp[q];
@@ -632,8 +656,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 make_uint4(pack2_bf16(acc[8 * q], acc[8 * q + 1]), pack2_bf16(acc[8 * q + 2], acc[8 * q + 3]),
                            pack2_bf16(acc[8 * q + 4], acc[8 * q + 5]), pack2_bf16(acc[8 * q + 6], acc[8 * q + 7]));
         } else if constexpr (EPI == EPI_DSWIGLU) {
-          const uint32_t b = res_uses & 1u;
-          if (!mbar_wait(smem_u32(&bar_res[warp - 2][b]), (res_uses >> 1) & 1u, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
+          const uint32_t b = res_uses % (uint32_t)RD;
+          if (!mbar_wait(smem_u32(&bar_res[warp - 2][b]), (res_uses / (uint32_t)RD) & 1u, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
             ok = false;
             break;
           }
@@ -760,8 +784,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint8_t* res_row = nullptr;
           float4 rres[8];  // the residual piece, read before any staging store (the compiler cannot tell the two apart)
           if constexpr (EPI == EPI_STORE_F32_TMARES) {
-            const uint32_t b = res_uses & 1u;
-            if (!mbar_wait(smem_u32(&bar_res[warp - 2][b]), (res_uses >> 1) & 1u, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
+            const uint32_t b = res_uses % (uint32_t)RD;
+            if (!mbar_wait(smem_u32(&bar_res[warp - 2][b]), (res_uses / (uint32_t)RD) & 1u, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
               ok = false;
               break;
             }
@@ -811,7 +835,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         __syncwarp();
         if constexpr (kTmaRes) {  // this residual buffer is free: fetch the piece after next
           ++res_uses;
-          issue_res(m_warp, n0 + 2 * CW);
+          issue_res(m_warp, n0 + RD * CW);
         }
         if (lane == 0) {
           const uint32_t src = stage_base + (uint32_t)sbuf * 4096u;

@@ -539,6 +539,8 @@ KERNEL_CASES = {
     "wo_fwd": (8192, 768, 768, 0, 0, 1, 1),          # fp32 out + fp32 residual (x2 = x + att . Wo^T)
     "w2_fwd": (8192, 768, 2048, 0, 0, 1, 1),
     "wo_dx": (8192, 768, 768, 0, 1, 0),
+    "w2_dx_plain": (8192, 2048, 768, 0, 1, 0),       # d gate = dOut . W2, bf16 out (the SwiGLU backward then a kernel of its own)
+    "w2_dx_dswiglu": (8192, 2048, 768, 0, 1, 7),     # the same product with the SwiGLU backward in its epilogue
 }
 
 
@@ -555,6 +557,8 @@ def run_kernel_case(args):
     M, N, K, a_mn, b_mn, out_mode = KERNEL_CASES[args.kernel_case][:6]
     with_res = len(KERNEL_CASES[args.kernel_case]) > 6
     c_bytes = M * N * (2 if out_mode == 0 else 4)
+    if out_mode == 7:
+        c_bytes = M * 2 * N * 2   # d h13 [M, 2N] bf16
     dA, dB, dC = lib.ane_dev_malloc(M * K * 2), lib.ane_dev_malloc(N * K * 2), lib.ane_dev_malloc(c_bytes)
     lib.ane_dev_memset(dC, 0, c_bytes)
     rng = np.random.Generator(np.random.PCG64(5))
@@ -579,8 +583,12 @@ def run_kernel_case(args):
     g.m, g.n, g.k = M, N, K
     g.lda = M if a_mn else K
     g.ldb = N if b_mn else K
-    g.ldc = N
+    g.ldc = 2 * N if out_mode == 7 else N
     g.a_mn, g.b_mn, g.out_mode, g.alpha = a_mn, b_mn, out_mode, 1.0
+    if out_mode == 7:
+        dH = lib.ane_dev_malloc(M * 2 * N * 2)
+        fill_bf16(dH, M * 2 * N, 1.0)
+        g.d_aux, g.ldaux = dH, 2 * N
     if with_res:
         dR = lib.ane_dev_malloc(c_bytes)
         lib.ane_dev_memset(dR, 0, c_bytes)
@@ -596,7 +604,7 @@ def run_kernel_case(args):
     per = ms.value / args.steps
     _, tf_burst, _, src = measured_peaks()
     tflops = 2.0 * M * N * K / (per * 1e-3) / 1e12
-    alg_bytes = (M * K + N * K) * 2 + c_bytes * (2 if (out_mode == 2 or with_res) else 1)
+    alg_bytes = (M * K + N * K) * 2 + c_bytes * (2 if (out_mode in (2, 7) or with_res) else 1)
     print(json.dumps({"kernel_case": args.kernel_case, "shape": [M, N, K], "us_per_launch": round(per * 1e3, 2),
                       "achieved_tflops": round(tflops, 1), "frac_of_burst_peak": round(tflops / tf_burst, 4),
                       "peak_source": src, "algorithmic_bytes": alg_bytes}), flush=True)
