@@ -204,6 +204,30 @@ class EngineT final : public EngineBase {
     if (rc != 0) return fail(ANE_ERR_KERNEL, gemm_last_error());
     return 0;
   }
+  // The weight-gradient products of layer `l` as one grouped launch (bf16 engines).
+  int gemm_group(const GemmDesc* ds, int n, int l, cudaStream_t st) {
+    if constexpr (kIsF32) {
+      return fail(ANE_ERR_STATE, "storiesane step: grouped products run on bf16 engines");
+    } else {
+      cudaEvent_t e0 = nullptr, e1 = nullptr;
+      if (profiling_) {
+        cudaEventCreate(&e0);
+        cudaEventCreate(&e1);
+        cudaEventRecord(e0, st);
+      }
+      bool built = group_built_[l] != 0;
+      const int rc = gemm_bf16_grouped(ds, n, d_groups_ + (size_t)l * gemm_group_slot_bytes(), &built, d_status_, st);
+      group_built_[l] = built ? 1 : 0;
+      if (profiling_) {
+        cudaEventRecord(e1, st);
+        prof_events_.push_back({e0, e1});
+        prof_shapes_.push_back({0, 0, ds[0].K, 3 | (GEMM_OUT_ACCUM << 2)});
+        for (int p = 0; p < n; ++p) prof_flops_ += 2.0 * (double)ds[p].M * (double)ds[p].N * (double)ds[p].K;
+      }
+      if (rc != 0) return fail(ANE_ERR_KERNEL, gemm_last_error());
+      return 0;
+    }
+  }
   // T-typed view of an fp32 buffer: in fp32 mode the buffer itself, else a separately written copy.
   T* tview(float* f32buf, T* tbuf) const {
     if constexpr (kIsF32) return f32buf;
@@ -287,6 +311,14 @@ class EngineT final : public EngineBase {
   // Classifier head that keeps no logits (bf16 engines): statistics of pass 1 per 256-column tile and row, the
   // rows' log2-sum-exp and gradient coefficients, and the gradient block [M, head_cols_] that pass 2 writes and
   // the dX / dEmbed products read while it is still in L2.
+  // bf16 engines with ANE_B200_GROUP_DW=1: the four weight-gradient products of a layer leave as one grouped
+  // stream-K launch on the side stream once the layer's main chain is done (one start-up and about one exposed
+  // epilogue per CTA instead of four of each).  One descriptor slot per layer, filled at its first use.  Off by
+  // default: the products' own time falls (6.79 -> 6.52 ms per step summed) but the step gets slower (8.83 ->
+  // 8.97 ms), because one persistent launch holds every SM for ~95 us while the main chain waits for SMs.
+  bool group_dw_ = false;
+  uint8_t* d_groups_ = nullptr;
+  std::vector<char> group_built_;
   bool head_fused_ = false;
   int head_cols_ = 0;
   float *ce_stats_ = nullptr, *ce_lse2_ = nullptr, *ce_coef_ = nullptr;
@@ -563,6 +595,10 @@ int EngineT<T>::alloc_buffers() {
   A(rope_cos_, (size_t)S_ * (hd_ / 2)); A(rope_sin_, (size_t)S_ * (hd_ / 2));
   A(d_acc_, 2); A(d_scales_, 4); A(d_norm_, 2); A(d_status_, 1);
   A(d_in_, M_); A(d_tgt_, M_); A(d_pos_, B_);
+  if (group_dw_) {
+    A(d_groups_, (size_t)L_ * gemm_group_slot_bytes());
+    group_built_.assign(L_, 0);
+  }
   tap_tmp_n_ = std::max((size_t)M_ * std::max({QKVD_, N13_, D_}), (size_t)V_ * S_);
   A(tap_tmp_, tap_tmp_n_);
 #undef A
@@ -638,10 +674,16 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
 
   int rc;
   if ((rc = cuda_check(cudaSetDevice(o_.device), "cudaSetDevice")) != 0) return rc;
-  if ((rc = cuda_check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate")) != 0) return rc;
+  // ANE_B200_STREAM_PRIO=1: the main chain's stream above the weight-gradient stream, so that freed SMs go to the
+  // critical path first (measurement switch)
+  int prio_lo = 0, prio_hi = 0;
+  cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi);
+  const char* spe = getenv("ANE_B200_STREAM_PRIO");
+  const bool stream_prio = spe && spe[0] == '1';
+  if ((rc = cuda_check(cudaStreamCreateWithPriority(&stream_, cudaStreamNonBlocking, stream_prio ? prio_hi : 0), "cudaStreamCreate")) != 0) return rc;
   for (cudaEvent_t* e : {&ev0_, &ev1_, &ev_adam0_, &ev_adam1_})
     if ((rc = cuda_check(cudaEventCreate(e), "cudaEventCreate")) != 0) return rc;
-  if ((rc = cuda_check(cudaStreamCreateWithFlags(&dw_stream_, cudaStreamNonBlocking), "cudaStreamCreate")) != 0) return rc;
+  if ((rc = cuda_check(cudaStreamCreateWithPriority(&dw_stream_, cudaStreamNonBlocking, stream_prio ? prio_lo : 0), "cudaStreamCreate")) != 0) return rc;
   if ((rc = cuda_check(cudaEventCreateWithFlags(&ev_dw_in_, cudaEventDisableTiming), "cudaEventCreate")) != 0) return rc;
   for (cudaEvent_t* e : {&ev_cls_ce_[0], &ev_cls_ce_[1], &ev_cls_dw_[0], &ev_cls_dw_[1]})
     if ((rc = cuda_check(cudaEventCreateWithFlags(e, cudaEventDisableTiming), "cudaEventCreate")) != 0) return rc;
@@ -654,6 +696,10 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
     const char* env = getenv("ANE_B200_DW_OVERLAP");
     dw_overlap_ = !(env && env[0] == '0');
     x3_ = kIsF32 && o_.compute_dtype == ANE_DTYPE_BF16X3;
+    {
+      const char* ge = getenv("ANE_B200_GROUP_DW");
+      group_dw_ = !kIsF32 && ge && ge[0] == '1';
+    }
     if (x3_) dw_overlap_ = false;  // the split scratch serves one stream
   }
   layout_params();
@@ -1113,23 +1159,27 @@ int EngineT<T>::backward_layers(int B) {
     rmsnorm_backward<T>(dxn_, a.x2, w_ffn, a.rstd2, dcur, rl, dx2, tcopy_arg(dx2_t_[pb]),
                         isN_ ? nullptr : G_ + s_rms_ffn_[l].off, M, D_, stream_);
     if (o_.debug_taps) cudaMemcpyAsync(a.t_dx2, dx2, sizeof(float) * MD, cudaMemcpyDeviceToDevice, stream_);
+    GemmDesc dw[4];  // this layer's weight-gradient products: dW2, dW13, dWo, dWqkv
+    const bool grouped = group_dw_ && M == M_;
     {
-      GemmDesc g;  // dW2 += dOut^T * gate
+      GemmDesc& g = dw[0];  // dW2 += dOut^T * gate
       g.A = dcur_t; g.B = a.gate; g.C = G_ + s_w2_[l].off;
       g.M = D_; g.N = Hd_; g.K = M; g.lda = D_; g.ldb = Hd_; g.ldc = Hd_; g.a_mn = true; g.b_mn = true;
       g.out = GEMM_OUT_ACCUM;
-      if (dws != stream_) {  // operands (dOut copy, gate, dh13, x2n) are ready at this point of the main stream
-        cudaEventRecord(ev_dw_in_, stream_);
-        cudaStreamWaitEvent(dws, ev_dw_in_, 0);
-      }
-      count_launch();
-      if ((rc = gemm(g, dws)) != 0) return rc;
-      GemmDesc g2;  // dW13 += dh13^T * x2n
+      GemmDesc& g2 = dw[1];  // dW13 += dh13^T * x2n
       g2.A = dh13; g2.B = a.x2n; g2.C = G_ + s_w13_[l].off;
       g2.M = N13_; g2.N = D_; g2.K = M; g2.lda = N13_; g2.ldb = D_; g2.ldc = D_; g2.a_mn = true; g2.b_mn = true;
       g2.out = GEMM_OUT_ACCUM;
-      count_launch();
-      if ((rc = gemm(g2, dws)) != 0) return rc;
+      if (!grouped) {
+        if (dws != stream_) {  // operands (dOut copy, gate, dh13, x2n) are ready at this point of the main stream
+          cudaEventRecord(ev_dw_in_, stream_);
+          cudaStreamWaitEvent(dws, ev_dw_in_, 0);
+        }
+        count_launch();
+        if ((rc = gemm(g, dws)) != 0) return rc;
+        count_launch();
+        if ((rc = gemm(g2, dws)) != 0) return rc;
+      }
     }
     if (isN_) {  // lambda gradients, FFN residual (ane/train_full.go:732-748)
       count_launch(3);
@@ -1231,22 +1281,27 @@ int EngineT<T>::backward_layers(int B) {
                          G_ + s_ve_embed_[l].off, G_ + s_ve_gate_[l].off, dprev, M, D_, H_, KV_, hd_, V_, stream_);
     }
     {
-      GemmDesc g;  // dWo += dx2^T * att
+      GemmDesc& g = dw[2];  // dWo += dx2^T * att
       g.A = dx2_t; g.B = a.att; g.C = G_ + s_wo_[l].off;
       g.M = D_; g.N = QD_; g.K = M; g.lda = D_; g.ldb = QD_; g.ldc = QD_; g.a_mn = true; g.b_mn = true;
       g.out = GEMM_OUT_ACCUM;
+      GemmDesc& g2 = dw[3];  // dWqkv += dqkv^T * xn
+      g2.A = dqkv; g2.B = a.xn; g2.C = G_ + s_qkv_[l].off;
+      g2.M = QKVD_; g2.N = D_; g2.K = M; g2.lda = QKVD_; g2.ldb = D_; g2.ldc = D_; g2.a_mn = true; g2.b_mn = true;
+      g2.out = GEMM_OUT_ACCUM;
       if (dws != stream_) {
         cudaEventRecord(ev_dw_in_, stream_);
         cudaStreamWaitEvent(dws, ev_dw_in_, 0);
       }
-      count_launch();
-      if ((rc = gemm(g, dws)) != 0) return rc;
-      GemmDesc g2;  // dWqkv += dqkv^T * xn
-      g2.A = dqkv; g2.B = a.xn; g2.C = G_ + s_qkv_[l].off;
-      g2.M = QKVD_; g2.N = D_; g2.K = M; g2.lda = QKVD_; g2.ldb = D_; g2.ldc = D_; g2.a_mn = true; g2.b_mn = true;
-      g2.out = GEMM_OUT_ACCUM;
-      count_launch();
-      if ((rc = gemm(g2, dws)) != 0) return rc;
+      if (grouped) {
+        count_launch();
+        if ((rc = gemm_group(dw, 4, l, dws)) != 0) return rc;
+      } else {
+        count_launch();
+        if ((rc = gemm(g, dws)) != 0) return rc;
+        count_launch();
+        if ((rc = gemm(g2, dws)) != 0) return rc;
+      }
       if (dws != stream_) cudaEventRecord(ev_dw_done_[l], dws);
     }
     if (isN_) {  // lambda gradients, attention residual (ane/train_full.go:770-782)

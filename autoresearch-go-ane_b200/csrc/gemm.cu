@@ -158,7 +158,8 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     const int work = base_tiles * (split_k > 0 ? split_k : 1);
     const int pairs = work < max_pairs ? work : max_pairs;
     cudaError_t e = launch_pdl_cluster(kern, dim3(2 * (pairs < 1 ? 1 : pairs)), dim3(threads), smem_bytes, stream, 2u,
-                                       ta, tb, tc, td, epi, d.M, d.N, d.K, split_k > 0 ? split_k : 1, d_status);
+                                       ta, tb, tc, td, epi, d.M, d.N, d.K, split_k > 0 ? split_k : 1, d_status,
+                                       (const GemmGroup*)nullptr);
     if (e != cudaSuccess) {
       g_gemm_err = std::string("gemm_tc pair launch: ") + cudaGetErrorString(e);
       return -4;
@@ -177,7 +178,7 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
   }
   if (grid < 1) grid = 1;
   cudaError_t e = launch_pdl(kern, dim3(grid), dim3(threads), smem_bytes, stream, ta, tb, tc, td, epi, d.M, d.N,
-                             d.K, split_k, d_status);
+                             d.K, split_k, d_status, (const GemmGroup*)nullptr);
   if (e != cudaSuccess) {
     g_gemm_err = std::string("gemm_tc launch: ") + cudaGetErrorString(e);
     return -4;
@@ -523,6 +524,83 @@ int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream) {
   if (p.bn == 192) return dispatch_layout<192, 1>(d, p.sched, d_status, stream);
   return dispatch_layout<128, 1>(d, p.sched, d_status, stream);
 }
+
+// ------------------------------------------------------------------------------------------
+// Grouped accumulating products: C_p += A_p^T B_p for up to four problems with one contraction length, both
+// operands stored [K, .] (the weight gradients of a layer), one stream-K launch over the concatenated tiles
+// of 256 x 256.  `slot` is device memory for the group's descriptors; it is filled on the first call for a
+// given slot (`*built`) and reused afterwards -- the operands of a layer never move.
+// ------------------------------------------------------------------------------------------
+int gemm_bf16_grouped(const GemmDesc* ds, int n, void* slot, bool* built, int* d_status, cudaStream_t stream) {
+  if (n < 1 || n > 4 || slot == nullptr || built == nullptr) {
+    g_gemm_err = "grouped GEMM: one to four problems and a descriptor slot are required";
+    return -2;
+  }
+  constexpr int BN = 256, MT = 2;
+  constexpr int BM_TILE = GemmCfg<BN, MT>::BM_TILE;
+  int K = ds[0].K;
+  long tiles = 0;
+  for (int p = 0; p < n; ++p) {
+    const GemmDesc& d = ds[p];
+    if (!d.a_mn || !d.b_mn || d.out != GEMM_OUT_ACCUM || d.K != K || d.alpha != 1.f || d.M <= 0 || d.N <= 0) {
+      g_gemm_err = "grouped GEMM: every problem must be C += A^T B with MN-major operands, alpha 1 and the same K";
+      return -2;
+    }
+    tiles += (long)((d.M + BM_TILE - 1) / BM_TILE) * ((d.N + BN - 1) / BN);
+  }
+  if (!*built) {
+    GemmGroup g;
+    memset(&g, 0, sizeof g);
+    g.n = n;
+    int t0 = 0;
+    for (int p = 0; p < n; ++p) {
+      const GemmDesc& d = ds[p];
+      if (!make_tmap(&g.a[p], d.A, d.M, d.K, d.lda, 64, GEMM_BK) || !make_tmap(&g.b[p], d.B, d.N, d.K, d.ldb, 64, GEMM_BK) ||
+          !make_tmap(&g.c[p], d.C, d.N, d.M, d.ldc, 32, 32, true))
+        return -2;
+      g.M[p] = d.M;
+      g.N[p] = d.N;
+      g.tile0[p] = t0;
+      t0 += ((d.M + BM_TILE - 1) / BM_TILE) * ((d.N + BN - 1) / BN);
+    }
+    g.tile0[n] = t0;
+    // synchronous copy: the descriptors must be in place before the launch below and the source is on the stack
+    if (cudaMemcpy(slot, &g, sizeof g, cudaMemcpyHostToDevice) != cudaSuccess) {
+      g_gemm_err = "grouped GEMM: descriptor upload failed";
+      return -3;
+    }
+    *built = true;
+  }
+  auto kern = gemm_tc_kernel<BN, MT, true, true, EPI_REDUCE_F32>;
+  constexpr uint32_t smem_bytes = GemmCfg<BN, MT>::smem_bytes(false);
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes) != cudaSuccess) {
+      g_gemm_err = "grouped GEMM: cudaFuncSetAttribute failed";
+      return -3;
+    }
+    attr_set = true;
+  }
+  const long long units = (long long)tiles * ((K + GEMM_BK - 1) / GEMM_BK);
+  long long grid = units / 8;
+  if (grid > gemm_num_sms()) grid = gemm_num_sms();
+  if (grid < 1) grid = 1;
+  CUtensorMap ta, tb, tc;  // the kernel's own map parameters are not used by a grouped launch; any valid maps do
+  const GemmDesc& d0 = ds[0];
+  if (!make_tmap(&ta, d0.A, d0.M, d0.K, d0.lda, 64, GEMM_BK) || !make_tmap(&tb, d0.B, d0.N, d0.K, d0.ldb, 64, GEMM_BK) ||
+      !make_tmap(&tc, d0.C, d0.N, d0.M, d0.ldc, 32, 32, true))
+    return -2;
+  EpiParams epi{};
+  epi.alpha = 1.f;
+  cudaError_t e = launch_pdl(kern, dim3((unsigned)grid), dim3(GEMM_THREADS), smem_bytes, stream, ta, tb, tc, tc, epi, d0.M, d0.N,
+                             K, 0, d_status, reinterpret_cast<const GemmGroup*>(slot));
+  if (e != cudaSuccess) {
+    g_gemm_err = std::string("grouped GEMM launch: ") + cudaGetErrorString(e);
+    return -4;
+  }
+  return 0;
+}
+size_t gemm_group_slot_bytes() { return sizeof(GemmGroup); }
 
 // ------------------------------------------------------------------------------------------
 // Split-precision GEMM: fp32 operands as bf16 (hi, lo) pairs, three tensor-core products.

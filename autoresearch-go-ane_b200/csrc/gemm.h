@@ -95,6 +95,12 @@ struct SplitScratch {
 };
 int gemm_bf16x3(const GemmDesc& d, SplitScratch* scratch, int* d_status, cudaStream_t stream);
 
+// Up to four accumulating products C_p += A_p^T B_p (both operands stored [K, .], the same K: the weight gradients of
+// one layer) in one stream-K launch.  `slot` = gemm_group_slot_bytes() of device memory (64-byte aligned) that keeps
+// the group's descriptors; `*built` says whether it already holds them (the operands of a slot must not change).
+int gemm_bf16_grouped(const GemmDesc* ds, int n, void* slot, bool* built, int* d_status, cudaStream_t stream);
+size_t gemm_group_slot_bytes();
+
 int gemm_num_sms();
 // 2-D tensor map over a row-major [outer, inner] buffer (row pitch ld elements) of bf16 (or fp32) with a
 // 128B-swizzled [box_outer, box_inner] box; cached per (device, arguments).  False + gemm_last_error() on failure.

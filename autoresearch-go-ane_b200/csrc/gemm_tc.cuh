@@ -174,6 +174,17 @@ struct EpiParams {
   int ce_softcap;        // z = 15 tanh(logit / 15) (ane/common.go:272-287)
 };
 
+// Several accumulating products with one contraction length, run by one launch (the four weight gradients of a
+// layer: dW = dY^T X with K = tokens for all of them).  Lives in device memory; the tile lists of the problems
+// are concatenated and dealt out stream-K, so the launch pays one start-up and each CTA about one exposed
+// epilogue where four launches paid four of each.
+struct alignas(64) GemmGroup {
+  CUtensorMap a[4], b[4], c[4];
+  int M[4], N[4];
+  int tile0[5];  // first tile of each problem in the concatenated list; tile0[n] = all tiles
+  int n;
+};
+
 // Work scheduler shared by the three warp roles (each role walks the same sequence).
 //   split_k > 0 : classic persistent schedule, work item = (k split, tile), stride gridDim.x.
 //   split_k == 0: stream-K.  The tiles x k-blocks units are dealt out in equal contiguous ranges, one per
@@ -183,12 +194,18 @@ struct GemmSched {
   int tiles_m, tiles, kblocks, split_k, kb_per_split, total_work, w;
   long long u, u1;
   int bid, nblk;  // this CTA's (or CTA pair's) index and the number of them
-  __device__ __forceinline__ void init(int M, int N, int K, int BM_TILE, int BN, int split, int bid_, int nblk_) {
+  const GemmGroup* grp;  // grouped launch: tiles index the concatenated list
+  int bm_tile, prob;     // prob = problem of the segment returned last
+  __device__ __forceinline__ void init(int M, int N, int K, int BM_TILE, int BN, int split, int bid_, int nblk_,
+                                       const GemmGroup* g = nullptr) {
     bid = bid_;
     nblk = nblk_;
+    grp = g;
+    bm_tile = BM_TILE;
+    prob = 0;
     tiles_m = (M + BM_TILE - 1) / BM_TILE;
     const int tiles_n = (N + BN - 1) / BN;
-    tiles = tiles_m * tiles_n;
+    tiles = g ? g->tile0[g->n] : tiles_m * tiles_n;
     kblocks = (K + GEMM_BK - 1) / GEMM_BK;
     split_k = split;
     if (split_k > 0) {
@@ -211,8 +228,7 @@ struct GemmSched {
         kb0 = split * kb_per_split;
         kb1 = min(kb0 + kb_per_split, kblocks);
         if (kb1 <= kb0) continue;
-        tn = rem / tiles_m;
-        tm = rem - tn * tiles_m;
+        place(rem, tm, tn);
         return true;
       }
       return false;
@@ -223,18 +239,34 @@ struct GemmSched {
     const long long left = u1 - u;
     kb1 = (left < (long long)(kblocks - kb0)) ? kb0 + (int)left : kblocks;
     u += kb1 - kb0;
-    tn = tile / tiles_m;
-    tm = tile - tn * tiles_m;
+    place(tile, tm, tn);
     return true;
+  }
+  // tile index -> (tm, tn), and for a grouped launch the problem it belongs to
+  __device__ __forceinline__ void place(int tile, int& tm, int& tn) {
+    int tmn = tiles_m;
+    if (grp) {
+      int p = 0;
+      while (p + 1 < grp->n && tile >= grp->tile0[p + 1]) ++p;
+      prob = p;
+      tile -= grp->tile0[p];
+      tmn = (grp->M[p] + bm_tile - 1) / bm_tile;
+    }
+    tn = tile / tmn;
+    tm = tile - tn * tmn;
   }
 };
 
 template <int BN, int MT, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(64 + 32 * GemmCfg<BN, MT>::epi_warps(EPI), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD, EpiParams epi, int M,
-               int N, int K, int split_k, int* status) {
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD, EpiParams epi, int M0,
+               int N0, int K, int split_k, int* status, const GemmGroup* group) {
   using Cfg = GemmCfg<BN, MT>;
+  // grouped launches exist for the accumulating weight-gradient form on single-CTA tiles only
+  constexpr bool kGroup = A_MN && B_MN && EPI == EPI_REDUCE_F32 && MT < GEMM_MT_PAIR;
+  const GemmGroup* grp = kGroup ? group : nullptr;
+  int M = M0, N = N0;  // the epilogue of a grouped launch sets them per tile
   constexpr bool kTmaRes = (EPI == EPI_STORE_F32_TMARES || EPI == EPI_DSWIGLU);  // an input piece per output piece, by TMA
   constexpr int RD = Cfg::res_depth(EPI);  // input pieces in flight per epilogue warp
   constexpr int EW = Cfg::epi_warps(EPI);  // epilogue warps: 4, or 8 (two per TMEM lane group, half of the columns each)
@@ -316,9 +348,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t phase = 0;
       bool ok = true;
       GemmSched sched;
-      sched.init(M, N, K, BM, BN, split_k, sched_id, sched_n);
+      sched.init(M, N, K, BM, BN, split_k, sched_id, sched_n, grp);
       int tm, tn, kb0, kb1;
       while (ok && sched.next(tm, tn, kb0, kb1)) {
+        const CUtensorMap* pA = grp ? &grp->a[sched.prob] : &tmA;
+        const CUtensorMap* pB = grp ? &grp->b[sched.prob] : &tmB;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, status, DEV_MBAR_TIMEOUT_PRODUCER)) {
             ok = false;
@@ -356,18 +390,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if constexpr (!A_MN) {
 #pragma unroll
             for (int i = 0; i < SUBS; ++i)
-              tma_load_2d(sa + i * (GEMM_BM * BK * 2), &tmA, full, kb * BK, tm * BM + i * GEMM_BM);
+              tma_load_2d(sa + i * (GEMM_BM * BK * 2), pA, full, kb * BK, tm * BM + i * GEMM_BM);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
-              tma_load_2d(sa + j * (64 * BK * 2), &tmA, full, tm * BM + j * 64, kb * BK);
+              tma_load_2d(sa + j * (64 * BK * 2), pA, full, tm * BM + j * 64, kb * BK);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(sb, &tmB, full, kb * BK, tn * BN);
+            tma_load_2d(sb, pB, full, kb * BK, tn * BN);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * (64 * BK * 2), &tmB, full, tn * BN + j * 64, kb * BK);
+              tma_load_2d(sb + j * (64 * BK * 2), pB, full, tn * BN + j * 64, kb * BK);
           }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -385,7 +419,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int local = 0;
       bool ok = true;
       GemmSched sched;
-      sched.init(M, N, K, BM, BN, split_k, sched_id, sched_n);
+      sched.init(M, N, K, BM, BN, split_k, sched_id, sched_n, grp);
       int tm, tn, kb0, kb1;
       while (ok && sched.next(tm, tn, kb0, kb1)) {
         const int buf = local % NBUF;
@@ -456,9 +490,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint8_t* res_ptr = smem_raw + (res_base - smem_u32(smem_raw));
     uint32_t res_uses = 0;  // pieces consumed so far (buffer = uses % RD, phase = (uses / RD) & 1)
     GemmSched sched;
-    sched.init(M, N, K, BM, BN, split_k, sched_id, sched_n);
+    sched.init(M, N, K, BM, BN, split_k, sched_id, sched_n, grp);
     int tm, tn, kb0, kb1;
     while (ok && sched.next(tm, tn, kb0, kb1)) {
+      const CUtensorMap* pC = &tmC;
+      if (grp) {  // this tile's problem: its output map and bounds
+        pC = &grp->c[sched.prob];
+        M = grp->M[sched.prob];
+        N = grp->N[sched.prob];
+      }
       const int buf = local % NBUF;
       const uint32_t tphase = (uint32_t)(local / NBUF) & 1u;
       // Residual rows are fetched one 32-column piece ahead (the first piece while the MMAs of this
@@ -839,7 +879,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         if (lane == 0) {
           const uint32_t src = stage_base + (uint32_t)sbuf * 4096u;
-          if constexpr (EPI == EPI_REDUCE_F32) tma_reduce_add_2d(&tmC, src, n0, m_warp);
+          if constexpr (EPI == EPI_REDUCE_F32) tma_reduce_add_2d(pC, src, n0, m_warp);
           else if constexpr (EPI == EPI_DSWIGLU) tma_store_2d(&tmC, src, 2 * n0, m_warp);
           else tma_store_2d(&tmC, src, n0, m_warp);
           tma_store_commit();

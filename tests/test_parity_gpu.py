@@ -480,6 +480,31 @@ def test_logit_free_head_in_blocks_of_vocabulary_columns(arch, quirks, vocab, co
     e.close()
 
 
+def test_grouped_weight_gradient_launch_matches_the_separate_launches(monkeypatch):
+    """ANE_B200_GROUP_DW=1: the four weight-gradient products of a layer as one grouped stream-K launch (descriptors
+    in device memory, tiles of the four problems concatenated).  Same gradients as the separate launches up to the
+    order of the fp32 reduce-adds, ragged tile edges included (dim 320, hidden 704)."""
+    cfg = dict(dim=320, hidden=704, heads=5, kv_heads=5, layers=3, vocab=1024, seq=128)
+    hyper = dict(lr=3e-4, accum_steps=1000)
+    inp, tgt = batch_tokens(cfg, 2, 31, invalid=False)
+    grads = []
+    for flag in ("0", "1"):
+        monkeypatch.setenv("ANE_B200_GROUP_DW", flag)
+        m, e = make_pair(ane, cfg, arch=O.ARCH_L, quirks=0, dtype=ane.DTYPE_BF16, batch=2, hyper=hyper, debug_taps=False)
+        r = e.step_tokens(inp, tgt)
+        assert r.device_status == 0
+        grads.append({(t, l): e.export_tensor(t, l, ane.G) for t in (ane.T_WQ, ane.T_WO, ane.T_W1, ane.T_W3, ane.T_W2)
+                      for l in range(cfg["layers"])})
+        if flag == "1":
+            oracle_batch_accumulate(m, inp, tgt, cfg["seq"])
+            rep = []
+            compare_grads(m, e, rep)
+            check_grads(rep, EXC_LLAMA_SHALLOW, 6)
+        e.close()
+    for k in grads[0]:
+        assert rel_l2(grads[1][k], grads[0][k]) < 1e-5, k
+
+
 def test_split_precision_head_with_a_token_outside_the_vocabulary_reference_arch():
     """The case that plain bf16 fails (xfail above) in the split-precision mode: inside the stated tolerance."""
     cfg = dict(dim=128, hidden=256, heads=2, layers=2, vocab=512, seq=128)
