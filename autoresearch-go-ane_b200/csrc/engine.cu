@@ -669,6 +669,7 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
   ce_rows_ = o_.ce_chunk_rows > 0 ? o_.ce_chunk_rows : (head_fused_ ? 1024 : 8192);
   if (ce_rows_ > M_) ce_rows_ = M_;
   ce_rows_ = std::max(ce_rows_, std::min(M_, S_));  // eval logits uses one sequence per chunk
+  ce_rows_ = std::max(ce_rows_, std::min(M_, B_));  // decoding: one row of logits per sequence
   lr_ = o_.lr;
   set_lr(lr_);
 
