@@ -485,15 +485,17 @@ void attention_forward_tc(const bf16* qkv, bf16* out, bf16* out_lo, float* lse, 
   attention_fwd_tc_kernel<<<grid, ATT_THREADS, kFwdSmem, s>>>(qkv, out, out_lo, lse, seq, H, KV, scale);
 }
 
-void attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* out_lo, const bf16* d_out, const float* lse, float* delta,
-                           bf16* dqkv, const float* cosb, const float* sinb, int B, int seq, int H, int KV,
-                           float scale, int* d_status, cudaStream_t s) {
-  if (B <= 0 || seq <= 0 || !ensure_attrs()) return;
+int attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* out_lo, const bf16* d_out, const float* lse, float* delta,
+                          bf16* dqkv, const float* cosb, const float* sinb, const float* rope_chunks, int B, int seq, int H,
+                          int KV, float scale, int* d_status, cudaStream_t s) {
+  if (B <= 0 || seq <= 0 || !ensure_attrs()) return 0;
   // ANE_B200_ATT_LEGACY=1 keeps the mma.sync kernels (A/B measurements).
   static const bool legacy = getenv("ANE_B200_ATT_LEGACY") != nullptr;
-  if (!legacy && attention_tcgen05_supported(HD, seq) &&
-      attention_backward_tcgen05(qkv, out, out_lo, d_out, lse, delta, dqkv, cosb, sinb, B, seq, H, KV, scale, d_status, s) == 0)
-    return;
+  if (!legacy && attention_tcgen05_supported(HD, seq)) {
+    const int n = attention_backward_tcgen05(qkv, out, out_lo, d_out, lse, delta, dqkv, cosb, sinb, rope_chunks, B, seq, H, KV, scale,
+                                             d_status, s);
+    if (n > 0) return n;
+  }
   const long long warps = (long long)B * seq * H;
   attention_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>(d_out, out, out_lo, delta, B, seq, H);
   dim3 gq((seq + BR - 1) / BR, B * H);
@@ -502,6 +504,7 @@ void attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* out_lo,
   dim3 gk((seq + BR - 1) / BR, B * KV);
   attention_bwd_dkv_tc_kernel<<<gk, ATT_THREADS, kDkvSmem, s>>>(qkv, d_out, lse, delta, dqkv, cosb, sinb, seq, H, KV,
                                                                  scale);
+  return 3;
 }
 
 }  // namespace ane

@@ -330,6 +330,7 @@ class EngineT final : public EngineBase {
   cudaEvent_t ev_cls_dw_[2] = {nullptr, nullptr};
   cudaEvent_t ev_logits_[16] = {};          // EvalLogits: one per downloaded piece
   float *rope_cos_ = nullptr, *rope_sin_ = nullptr;
+  float* rope_chunks_ = nullptr;  // the same tables by 16-byte chunk, for the one-CTA-per-head attention backward
   double* d_acc_ = nullptr;
   float *d_scales_ = nullptr, *d_norm_ = nullptr;
   int* d_status_ = nullptr;
@@ -593,6 +594,7 @@ int EngineT<T>::alloc_buffers() {
   }
   A(loss_rows_, M_); A(inv_valid_, B_); A(d_loss_, 4); A(tgt_logit_, M_);
   A(rope_cos_, (size_t)S_ * (hd_ / 2)); A(rope_sin_, (size_t)S_ * (hd_ / 2));
+  if (hd_ == 64) A(rope_chunks_, (size_t)S_ * 64);
   A(d_acc_, 2); A(d_scales_, 4); A(d_norm_, 2); A(d_status_, 1);
   A(d_in_, M_); A(d_tgt_, M_); A(d_pos_, B_);
   if (group_dw_) {
@@ -731,6 +733,7 @@ int EngineT<T>::open(const ane_options& opts, const uint16_t* tokens, uint64_t n
   }
   count_launch();
   build_rope_tables(rope_cos_, rope_sin_, S_, hd_, (double)o_.rope_theta, stream_);
+  if (rope_chunks_ != nullptr) attention_rope_chunk_tables(rope_cos_, rope_sin_, rope_chunks_, S_, stream_);
   if ((rc = refresh_shadow()) != 0) return rc;
   if (n_tokens > 0 && tokens) {
     n_tokens_ = n_tokens;
@@ -1224,9 +1227,8 @@ int EngineT<T>::backward_layers(int B) {
     } else if constexpr (!kIsF32) {
       if (att_tc_) {
         // Tensor-core path: the kernels undo the rotation and emit bf16 operands directly.
-        count_launch(3);
-        attention_backward_tc((const bf16*)a.qkv, a.att, (const bf16*)a.att_lo, datt_, a.lse, att_delta_, dqkv_[pb], rope_cos_, rope_sin_, B, S_,
-                              H_, KV_, att_scale_bwd, d_status_, stream_);
+        count_launch(attention_backward_tc((const bf16*)a.qkv, a.att, (const bf16*)a.att_lo, datt_, a.lse, att_delta_, dqkv_[pb], rope_cos_, rope_sin_, rope_chunks_, B, S_,
+                                           H_, KV_, att_scale_bwd, d_status_, stream_));
         dqkv_ready = true;
         if (o_.debug_taps) {
           count_launch();

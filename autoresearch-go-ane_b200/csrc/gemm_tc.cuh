@@ -151,6 +151,14 @@ __device__ __forceinline__ float epi_ex2(float x) {
 __device__ __forceinline__ float epi_tanh(float u) {
   return 1.f - __fdividef(2.f, 1.f + epi_ex2(2.885390081777927f * u));
 }
+// sigmoid(x) = 0.5 + 0.5 tanh(x / 2) on the hardware tanh (relative error ~2^-11, below the bf16 rounding of
+// everything it feeds): one special-function instruction where ex2 + reciprocal take two, and the SwiGLU
+// epilogues are bound by that unit (16 results per clock per SM).
+__device__ __forceinline__ float epi_sigmoid(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  return fmaf(0.5f, t, 0.5f);
+}
 struct EpiParams {
   float alpha;
   const float* res1;  // optional fp32 [M, ldres]
@@ -715,9 +723,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int e = 0; e < 4; ++e) {
               const float2 x = __bfloat1622float2(h1p[e]), h = __bfloat1622float2(h3p[e]);
               const float dg0 = epi.alpha * acc[8 * q + 2 * e], dg1 = epi.alpha * acc[8 * q + 2 * e + 1];
-              // sigmoid by one ex2 and one fast reciprocal; d silu = s (1 + x (1 - s))
-              const float s0 = __fdividef(1.f, 1.f + exp2f(-1.4426950408889634f * x.x));
-              const float s1 = __fdividef(1.f, 1.f + exp2f(-1.4426950408889634f * x.y));
+              // d silu = s (1 + x (1 - s)) with s = sigmoid(x)
+              const float s0 = epi_sigmoid(x.x), s1 = epi_sigmoid(x.y);
               o1[e] = pack2_bf16(dg0 * h.x * s0 * (1.f + x.x * (1.f - s0)), dg1 * h.y * s1 * (1.f + x.y * (1.f - s1)));
               o3[e] = pack2_bf16(dg0 * x.x * s0, dg1 * x.y * s1);
             }
@@ -753,12 +760,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t gcur[16];
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
-              // silu(x) * h = x * h / (1 + 2^(-x log2 e)): one ex2 and one fast reciprocal per element (the
-              // epilogue has four warps per SM, so instruction count matters here)
+              // silu(x) * h = x * h * sigmoid(x) (the epilogue has four warps per SM, so instruction count
+              // matters here)
               const float x0 = epi.alpha * acc[2 * e], x1 = epi.alpha * acc[2 * e + 1];
               const float h0 = epi.alpha * acc[32 + 2 * e], h1 = epi.alpha * acc[32 + 2 * e + 1];
-              const float d0 = 1.f + exp2f(-1.4426950408889634f * x0), d1 = 1.f + exp2f(-1.4426950408889634f * x1);
-              gcur[e] = pack2_bf16(__fdividef(x0 * h0, d0), __fdividef(x1 * h1, d1));
+              gcur[e] = pack2_bf16(x0 * h0 * epi_sigmoid(x0), x1 * h1 * epi_sigmoid(x1));
             }
             if (((c / CW) & 1) == 0) {
 #pragma unroll

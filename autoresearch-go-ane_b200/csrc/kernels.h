@@ -111,20 +111,24 @@ int attention_forward_tcgen05(const bf16* qkv, bf16* out, bf16* out_lo, float* l
 // is undone in the epilogue (pass nullptr to skip).  `delta` is scratch [B*H*seq].
 // With head_dim 64 and seq % 128 == 0 the tcgen05 kernels (attention_tcgen05.cu) run, else mma.sync ones;
 // `d_status` is the device status word their bounded waits report through.
-void attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* out_lo, const bf16* d_out, const float* lse, float* delta,
-                           bf16* dqkv, const float* cosb, const float* sinb, int B, int seq, int H, int KV,
-                           float scale, int* d_status, cudaStream_t s);
+// Returns the number of kernels it launched.
+// `rope_chunks` (optional): the tables as attention_rope_chunk_tables() lays them out, for the seq-256 backward.
+int attention_backward_tc(const bf16* qkv, const bf16* out, const bf16* out_lo, const bf16* d_out, const float* lse, float* delta,
+                          bf16* dqkv, const float* cosb, const float* sinb, const float* rope_chunks, int B, int seq, int H,
+                          int KV, float scale, int* d_status, cudaStream_t s);
+void attention_rope_chunk_tables(const float* cosb, const float* sinb, float* out, int seq, cudaStream_t s);
 bool attention_tcgen05_supported(int hd, int seq);
 // Backward for q|k|v kept in fp32 and given as bf16 (hi, lo) pairs: scores at split precision, own row
 // statistics for the backward's `scale` (lse, delta: scratch [B*H*seq]), dq|dk|dv out as bf16, no rotation.
 int attention_backward_tcgen05_split(const bf16* qkv_hi, const bf16* qkv_lo, const bf16* d_out, float* lse, float* delta,
                                      bf16* dqkv, int B, int seq, int H, int KV, float scale, int* d_status,
                                      cudaStream_t s);
-// `delta` is scratch [B*H*seq] (rowsum(dO * O), produced by the dQ kernel).  Returns 0 or a negative error code.
+// `delta` is scratch [B*H*seq] (rowsum(dO * O), produced by the dQ kernel, or by the one-CTA-per-head kernel that
+// sequences of 256 without grouped heads take).  Returns the number of kernels launched or a negative error code.
 int attention_backward_tcgen05(const bf16* qkv, const bf16* out, const bf16* out_lo, const bf16* d_out, const float* lse, float* delta,
                                bf16* dqkv,
-                               const float* cosb, const float* sinb, int B, int seq, int H, int KV, float scale,
-                               int* d_status, cudaStream_t s);
+                               const float* cosb, const float* sinb, const float* rope_chunks, int B, int seq, int H, int KV,
+                               float scale, int* d_status, cudaStream_t s);
 
 // Cross-entropy over token-major logits [rows, V] (fp32), ane/stories/cpu.go:212-292 with the
 // soft cap of ane/common.go:272-287 folded in:

@@ -542,6 +542,7 @@ KERNEL_CASES = {
     "wo_fwd": (8192, 768, 768, 0, 0, 1, 1),          # fp32 out + fp32 residual (x2 = x + att . Wo^T)
     "w2_fwd": (8192, 768, 2048, 0, 0, 1, 1),
     "wo_dx": (8192, 768, 768, 0, 1, 0),
+    "w13_fwd_swiglu": (8192, 4096, 768, 0, 0, 3),    # h1|h3 interleaved in bf16 plus gate = silu(h1) * h3 [M, N/2]
     "w2_dx_plain": (8192, 2048, 768, 0, 1, 0),       # d gate = dOut . W2, bf16 out (the SwiGLU backward then a kernel of its own)
     "w2_dx_dswiglu": (8192, 2048, 768, 0, 1, 7),     # the same product with the SwiGLU backward in its epilogue
 }
@@ -592,6 +593,10 @@ def run_kernel_case(args):
         dH = lib.ane_dev_malloc(M * 2 * N * 2)
         fill_bf16(dH, M * 2 * N, 1.0)
         g.d_aux, g.ldaux = dH, 2 * N
+    if out_mode == 3:
+        dH = lib.ane_dev_malloc(M * N)
+        lib.ane_dev_memset(dH, 0, M * N)
+        g.d_aux, g.ldaux = dH, N // 2
     if with_res:
         dR = lib.ane_dev_malloc(c_bytes)
         lib.ane_dev_memset(dR, 0, c_bytes)
@@ -607,7 +612,7 @@ def run_kernel_case(args):
     per = ms.value / args.steps
     _, tf_burst, _, src = measured_peaks()
     tflops = 2.0 * M * N * K / (per * 1e-3) / 1e12
-    alg_bytes = (M * K + N * K) * 2 + c_bytes * (2 if (out_mode in (2, 7) or with_res) else 1)
+    alg_bytes = (M * K + N * K) * 2 + c_bytes * (2 if (out_mode in (2, 7) or with_res) else 1) + (M * N if out_mode == 3 else 0)
     print(json.dumps({"kernel_case": args.kernel_case, "shape": [M, N, K], "us_per_launch": round(per * 1e3, 2),
                       "achieved_tflops": round(tflops, 1), "frac_of_burst_peak": round(tflops / tf_burst, 4),
                       "peak_source": src, "algorithmic_bytes": alg_bytes}), flush=True)
