@@ -1463,6 +1463,16 @@ attn5_bwd_head_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_c
         if (lane == 0) mbar_arrive(smem_u32(staged));
       };
 
+      // The rotation chunks a drain reads are asked into L1 one phase ahead (no registers held meanwhile).
+      auto prefetch_rope = [&](int t) {
+        if (!rope) return;
+        const float4* c4 = p.rope + (size_t)(half * 4) * T + (t * 128 + r);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          asm volatile("prefetch.global.L1 [%0];" ::"l"(c4 + q * T));
+          asm volatile("prefetch.global.L1 [%0];" ::"l"(c4 + (8 + q) * T));
+        }
+      };
       float sv[64];
       probs(0, true, c, sv);
       finish(0, c, sv, true);
@@ -1478,12 +1488,14 @@ attn5_bwd_head_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_c
       if (half == 0) p.delta[stat0 + 128 + r] = del_r[1];
       finish(1, c + 1, sv, false);
       // The third block's probabilities are formed while the second block's MMAs retire.
+      prefetch_rope(0);
       probs(1, true, c + 2, sv);
       ok = ok && mbar_wait(smem_u32(&bar_acc1), kp, status, DEV_MBAR_TIMEOUT_EPILOGUE);
       tc_fence_after();
       // the spare tiles: the previous head's last stores have read them (store groups complete in order)
       if (k > 0) ok = ok && mbar_wait(smem_u32(&bar_stfree), 1u, status, DEV_MBAR_TIMEOUT_EPILOGUE);
       drain(0, tDQ0, &bar_kvdr, &bar_stage0);
+      prefetch_rope(1);
       finish(1, c + 2, sv, false);
       if (u + (int)gridDim.x < n_units) load_lse(u + gridDim.x, lse_n);
       ok = ok && mbar_wait(smem_u32(&bar_acc2), kp, status, DEV_MBAR_TIMEOUT_EPILOGUE);
