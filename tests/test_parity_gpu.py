@@ -357,6 +357,31 @@ def test_bf16_attention_multi_tile_sequences(kv_heads, seq):
     e.close()
 
 
+@pytest.mark.parametrize("heads,batch", [(4, 2), (4, 80)])
+def test_bf16_attention_backward_one_cta_per_head(heads, batch):
+    """seq 256 without grouped heads takes the backward that gives every (sequence, head) one CTA: three
+    128 x 128 blocks per head, dQ / dK / dV and delta in one pass.  Eight units on an idle device, and 320
+    units, which a 148-SM device walks in three rounds (the persistent loop's hand-over from one head to
+    the next: operand tiles refilled while the previous head drains, accumulators reused).  Attention
+    gradients after the inverse rotation are compared tap by tap for the last sequence (a third-round unit
+    in the large case), weight gradients over all sequences."""
+    cfg = dict(dim=64 * heads, hidden=256, heads=heads, kv_heads=heads, layers=2, vocab=512, seq=256)
+    hyper = dict(lr=3e-4, accum_steps=1000)
+    m, e = make_pair(ane, cfg, arch=O.ARCH_L, quirks=0, dtype=ane.DTYPE_BF16, batch=batch, hyper=hyper, std=0.05)
+    inp, tgt = batch_tokens(cfg, batch, 17, invalid=False)
+    losses = oracle_batch_accumulate(m, inp, tgt, cfg["seq"])
+    r = e.step_tokens(inp, tgt)
+    assert r.device_status == 0
+    assert abs(r.loss - float(np.mean(losses))) < LOSS_TOL
+    errs = tap_errors(m, e, cfg, batch, [O.TAP_DQ, O.TAP_DK, O.TAP_DV])
+    assert max(errs.values()) < 1.7e-2, sorted(errs.items(), key=lambda kv: -kv[1])[:4]      # CAUSE_QK: 1.05-1.15e-2 here
+    assert max(v for (tid, _), v in errs.items() if tid == O.TAP_DV) < 1e-2
+    rep = []
+    compare_grads(m, e, rep)
+    check_grads(rep, EXC_LLAMA_SHALLOW, 9)
+    e.close()
+
+
 def test_bf16_reference_arch_split_precision_attention_two_tiles():
     """Reference architecture in bf16 with head_dim 64 and seq 256: q|k|v stay fp32 and attention runs on
     the split-precision tcgen05 kernels (statistics pass, dQ, dK/dV with hi/lo score products) over two
