@@ -65,8 +65,8 @@ def batch_tokens(cfg, batch, seed, invalid=True):
     inp = np.stack([toks[b * (seq + 1):b * (seq + 1) + seq] for b in range(batch)])
     tgt = np.stack([toks[b * (seq + 1) + 1:b * (seq + 1) + seq + 1] for b in range(batch)])
     if invalid and batch > 1:
-        tgt[1, 3] = 65535      # target outside the vocabulary: zero gradient row, not counted
-        inp[0, 5] = 65535      # token outside the vocabulary: zero embedding row
+        tgt[1, min(3, seq - 1)] = 65535      # target outside the vocabulary: zero gradient row, not counted
+        inp[0, min(5, seq - 1)] = 65535      # token outside the vocabulary: zero embedding row
     return inp, tgt
 
 
@@ -117,6 +117,38 @@ def test_fp32_step_matches_oracle(arch, quirks, extra):
         assert compare_grads(m, e, rep, which) < 2e-4, rep
     lo = m.eval_logits(np.ascontiguousarray(inp[1]))
     lg = e.eval_logits(inp[1])[0]  # reference layout [vocab][seq]
+    assert rel_l2(lg, lo) < F32_TOL
+    np.testing.assert_array_equal(lg.argmax(0), lo.argmax(0))
+    e.close()
+
+
+@pytest.mark.parametrize("arch,quirks", [(O.ARCH_L, 0), (O.ARCH_N, 1)])
+@pytest.mark.parametrize("seq", [1, 7])
+def test_fp32_shortest_sequences(arch, quirks, seq):
+    """One-token and seven-token windows with a 96-entry vocabulary: every row count below a warp, a
+    causal mask that is a single diagonal entry (seq 1), rotation at position 0 only, and a vocabulary
+    smaller than one GEMM tile.  Forward and backward taps, gradients, the update and the evaluation
+    logits against the oracle in fp32."""
+    cfg = dict(dim=64, hidden=96, heads=4, layers=2, vocab=96, seq=seq)
+    hyper = dict(lr=1e-3, adam_beta1=0.9, adam_beta2=0.95, weight_decay=0.1, grad_clip=1.0, accum_steps=1000)
+    m, e = make_pair(ane, cfg, arch=arch, quirks=quirks, dtype=ane.DTYPE_F32, batch=3, hyper=hyper, std=0.1,
+                     perturb_scalars=True)
+    inp, tgt = batch_tokens(cfg, 3, 23)
+    losses = oracle_batch_accumulate(m, inp, tgt, seq)
+    r = e.step_tokens(inp, tgt)
+    assert r.device_status == 0
+    assert abs(r.loss - float(np.mean(losses))) < 1e-5
+    errs = tap_errors(m, e, cfg, 3, FWD_TAPS + BWD_TAPS)
+    assert max(errs.values()) < F32_TOL, max(errs.items(), key=lambda kv: kv[1])
+    rep = []
+    assert compare_grads(m, e, rep) < F32_TOL, rep
+    m.flush()
+    e.flush()
+    rep = []
+    assert compare_grads(m, e, rep, O.W) < 2e-4, rep
+    lo = m.eval_logits(np.ascontiguousarray(inp[2]))
+    lg = e.eval_logits(inp[2])[0]
+    assert lg.shape == (96, seq)
     assert rel_l2(lg, lo) < F32_TOL
     np.testing.assert_array_equal(lg.argmax(0), lo.argmax(0))
     e.close()
