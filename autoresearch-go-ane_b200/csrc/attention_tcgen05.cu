@@ -1003,11 +1003,13 @@ constexpr size_t kFwdPersistSmem = kTileR + 6 * kTileX + 2 * kTileR + 1024;
 // forms them twice, and the five accumulators (dQ_0, dQ_1, dK_j, dV_j next to S and dP: all 512
 // columns of tensor memory) never leave the SM.  The next block's S is issued as soon as the row
 // threads have copied the current one to registers, its dP likewise, so the row threads run back to back.
-// Finished accumulators are staged in the operand tiles that are dead by then (dQ_0 / dK_0 / dV_0 in Q0 /
-// K0 / V0 after the second block, the others after the third) and sent out by the producer thread, which
-// then fetches the NEXT head's tiles into them, each as soon as it is free.  delta is rowsum(P dP) for the
-// first query tile (its one block holds whole rows) and rowsum(dO (O + O_lo)) for the second, from O tiles
-// parked in the staging tiles while those are idle.
+// Finished accumulators (dQ_0, dK_0, dV_0 after the second block, the others after the third) are staged in
+// two spare tiles and in V0 / K1 / V1, dead by then, and sent out by the producer thread.  The same thread
+// fetches the NEXT head's tiles, each group as soon as its tiles are free: Q0 and dO0 when the first block's
+// MMAs have retired, K0 after the second block's, V0 when the store of dV_0 has read it, Q1 and dO1 after the
+// third block's, K1 and V1 after their stores - so a head's first block finds its operands waiting.  delta is
+// rowsum(P dP) for the first query tile (its one block holds whole rows) and rowsum(dO (O + O_lo)) for the
+// second, from O tiles parked in the spare tiles while those are idle.
 // ------------------------------------------------------------------------------------------------
 __host__ __device__ constexpr uint32_t a5_idesc_n(bool a_mn, bool b_mn, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
@@ -1017,8 +1019,8 @@ __host__ __device__ constexpr uint32_t a5_idesc_n(bool a_mn, bool b_mn, int n) {
 struct Attn5HeadParams {
   const float* lse;    // [B, H, T] natural-log sum-exp of the scaled scores
   float* delta;        // [B, H, T] rowsum(dO * O), written for inspection
-  const bf16* o;       // [M, H*64] attention output
-  const bf16* o_lo;    // bf16(O - bf16(O)) or nullptr
+  const bf16* o;       // [M, H*64] attention output (read through its tensor map)
+  const bf16* o_lo;    // bf16(O - bf16(O)) or nullptr: whether the second tensor map is read as well
   bf16* dqkv;          // [M, 3*H*64] dq | dk | dv
   const float4* rope;  // rotation tables by 16-byte chunk: [cos chunk 0..7 | sin chunk 0..7][T] (see
                        // attention_rope_chunk_tables), or nullptr for no rotation
