@@ -1134,14 +1134,20 @@ int EngineT<T>::backward_layers(int B) {
       // d gate never stored)
       static const bool no_fuse_dswiglu = getenv("ANE_B200_NO_FUSE_DSWIGLU") != nullptr;  // A/B measurements
       const bool fused_dswiglu = !kIsF32 && !isN_ && !no_fuse_dswiglu && Hd_ % 32 == 0;
+      // reference arch, bf16: likewise the ReLU^2 backward, d h = d gate * 2 max(h, 0)
+      const bool fused_drelu2 = !kIsF32 && isN_ && !no_fuse_dswiglu && Hd_ % 64 == 0;
       if (fused_dswiglu) {
         g.out = GEMM_OUT_DSWIGLU;
+        g.C = dh13; g.ldc = N13_;
+        g.aux = a.h13; g.ldaux = N13_;
+      } else if (fused_drelu2) {
+        g.out = GEMM_OUT_DRELU2;
         g.C = dh13; g.ldc = N13_;
         g.aux = a.h13; g.ldaux = N13_;
       }
       count_launch();
       if ((rc = gemm(g)) != 0) return rc;
-      if (!fused_dswiglu) {
+      if (!fused_dswiglu && !fused_drelu2) {
         count_launch();
         if (isN_) relu2_backward<T>(dgate_, a.h13, dh13, (uint64_t)M * Hd_, stream_);
         else swiglu_backward<T>(dgate_, a.h13, dh13, M, Hd_, stream_);

@@ -118,12 +118,12 @@ static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
                      const EpiParams& epi,
                      const GemmDesc& d, int split_k, int* d_status, cudaStream_t stream) {
   auto kern = gemm_tc_kernel<BN, MT, A_MN, B_MN, EPI>;
-  constexpr bool tma_res = (EPI == EPI_STORE_F32_TMARES || EPI == EPI_DSWIGLU);
+  constexpr bool tma_res = (EPI == EPI_STORE_F32_TMARES || EPI == EPI_DSWIGLU || EPI == EPI_DRELU2);
   constexpr int depth = GemmCfg<BN, MT>::res_depth(EPI);
   constexpr int ew = GemmCfg<BN, MT>::epi_warps(EPI);
   constexpr int threads = 64 + 32 * ew;
-  constexpr uint32_t smem_bytes = GemmCfg<BN, MT>::smem_bytes(tma_res, EPI == EPI_DSWIGLU, depth, ew);
-  static_assert(smem_bytes <= GEMM_SMEM_LIMIT && GemmCfg<BN, MT>::stages(tma_res, EPI == EPI_DSWIGLU, depth, ew) >= 3, "pipeline does not fit");
+  constexpr uint32_t smem_bytes = GemmCfg<BN, MT>::smem_bytes(tma_res, EPI == EPI_DSWIGLU || EPI == EPI_DRELU2, depth, ew);
+  static_assert(smem_bytes <= GEMM_SMEM_LIMIT && GemmCfg<BN, MT>::stages(tma_res, EPI == EPI_DSWIGLU || EPI == EPI_DRELU2, depth, ew) >= 3, "pipeline does not fit");
   static bool attr_set = false;  // per template instantiation
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
@@ -262,6 +262,17 @@ static int dispatch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
       return launch_tc<BN, MT, A_MN, B_MN, EPI_DSWIGLU>(ta, tb, tc, td, epi, d, 1, d_status, stream);
     } else {
       g_gemm_err = "the SwiGLU-backward epilogue takes the dX form (A K-major, B MN-major) on 256-column tiles";
+      return -2;
+    }
+  }
+  if (d.out == GEMM_OUT_DRELU2) {
+    if constexpr (!A_MN && B_MN && BN == 256 && (MT == 1 || MT == GEMM_MT_PAIR)) {
+      CUtensorMap td;  // h in, d h out: [M, N] bf16, pieces of 32 rows x 64 columns
+      if (!make_tmap(&tc, d.C, d.N, d.M, d.ldc, 64, 32, false) || !make_tmap(&td, d.aux, d.N, d.M, d.ldaux, 64, 32, false))
+        return -2;
+      return launch_tc<BN, MT, A_MN, B_MN, EPI_DRELU2>(ta, tb, tc, td, epi, d, 1, d_status, stream);
+    } else {
+      g_gemm_err = "the ReLU^2-backward epilogue takes the dX form (A K-major, B MN-major) on 256-column tiles";
       return -2;
     }
   }
@@ -446,10 +457,11 @@ int gemm_bf16(const GemmDesc& d, int* d_status, cudaStream_t stream) {
     g_gemm_err = "rotary epilogue: needs 16-byte aligned cos/sin tables, rope_seq > 0, rope_cols % 64 == 0 and alpha == 1";
     return -2;
   }
-  if (d.out == GEMM_OUT_DSWIGLU) {
-    if (d.aux == nullptr || d.a_mn || !d.b_mn || d.N % 32 != 0 || d.ldaux % 8 != 0 || d.ldc % 8 != 0 ||
-        (reinterpret_cast<uintptr_t>(d.aux) & 15) != 0) {
-      g_gemm_err = "SwiGLU-backward epilogue: dX form only, N % 32 == 0, h13 and d h13 16-byte aligned with pitches % 8 == 0";
+  if (d.out == GEMM_OUT_DSWIGLU || d.out == GEMM_OUT_DRELU2) {
+    if (d.aux == nullptr || d.a_mn || !d.b_mn || d.N % (d.out == GEMM_OUT_DRELU2 ? 64 : 32) != 0 || d.ldaux % 8 != 0 ||
+        d.ldc % 8 != 0 || (reinterpret_cast<uintptr_t>(d.aux) & 15) != 0) {
+      g_gemm_err = "SwiGLU / ReLU^2 backward epilogue: dX form only, N % 32 == 0 (ReLU^2: % 64), the saved activations and the "
+                   "output 16-byte aligned with pitches % 8 == 0";
       return -2;
     }
     // 256-column tiles: CTA pairs when they fill their waves (the step's shape), else one CTA per tile

@@ -46,6 +46,10 @@ enum GemmOut : int {
   //   C(bf16)[row, col] = ce_coef[row] * (2^(z log2e - ce_lse2[row]) - [col is the row's target]) (* d softcap).
   GEMM_OUT_CE_STATS = 8,
   GEMM_OUT_CE_GRAD = 9,
+  // ReLU^2 backward fused into the product d gate = A*B [M, N]: with `aux` = h [M, N] (bf16, row pitch ldaux) the
+  // kernel writes C = d h = d gate * 2 max(h, 0) (bf16, row pitch ldc) from the fp32 accumulators; d gate itself is
+  // not stored (ane/common.go:146 differentiated).  A K-major, B MN-major (the dX form), N % 64 == 0.
+  GEMM_OUT_DRELU2 = 10,
 };
 
 struct GemmDesc {

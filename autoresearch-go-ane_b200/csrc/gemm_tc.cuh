@@ -141,6 +141,9 @@ enum EpiKind : int {
   // Pass 2 (logits recomputed for a block of vocabulary columns): C(bf16) = coef[row] * (softmax - onehot)
   // [* d softcap] with the row's log2-sum-exp from pass 1; the gradient of the loss with respect to the logits.
   EPI_CE_GRAD = 10,
+  // d h = d gate * 2 max(h, 0) on the accumulators of d gate = A*B, with h [M, N] (bf16) fed by TMA through the D
+  // map, one 32-row x 64-column piece per output piece: the ReLU^2 backward (ane/common.go:146) in the W2-dX epilogue.
+  EPI_DRELU2 = 11,
 };
 __device__ __forceinline__ float epi_ex2(float x) {
   float y;
@@ -275,10 +278,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   constexpr bool kGroup = A_MN && B_MN && EPI == EPI_REDUCE_F32 && MT < GEMM_MT_PAIR;
   const GemmGroup* grp = kGroup ? group : nullptr;
   int M = M0, N = N0;  // the epilogue of a grouped launch sets them per tile
-  constexpr bool kTmaRes = (EPI == EPI_STORE_F32_TMARES || EPI == EPI_DSWIGLU);  // an input piece per output piece, by TMA
+  constexpr bool kTmaRes = (EPI == EPI_STORE_F32_TMARES || EPI == EPI_DSWIGLU || EPI == EPI_DRELU2);  // an input piece per output piece, by TMA
   constexpr int RD = Cfg::res_depth(EPI);  // input pieces in flight per epilogue warp
   constexpr int EW = Cfg::epi_warps(EPI);  // epilogue warps: 4, or 8 (two per TMEM lane group, half of the columns each)
-  constexpr int STAGES = Cfg::stages(kTmaRes, EPI == EPI_DSWIGLU, RD, EW);
+  constexpr int STAGES = Cfg::stages(kTmaRes, EPI == EPI_DSWIGLU || EPI == EPI_DRELU2, RD, EW);
   constexpr int BM = Cfg::BM_TILE, BK = GEMM_BK;
   constexpr int NBUF = Cfg::NBUF;
   constexpr bool PAIR = Cfg::PAIR;
@@ -477,7 +480,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // Columns per staged piece: 128 bytes of output per row.
     constexpr bool kBf16Out = (EPI == EPI_STORE_BF16 || EPI == EPI_STORE_BF16_SWIGLU || EPI == EPI_STORE_BF16_ROPE ||
                                EPI == EPI_STORE_BF16_TGT || EPI == EPI_STORE_BF16_RELU2 || EPI == EPI_CE_STATS ||
-                               EPI == EPI_CE_GRAD);
+                               EPI == EPI_CE_GRAD || EPI == EPI_DRELU2);
     constexpr int CW = kBf16Out ? 64 : 32;
     constexpr int SBUF = Cfg::SBUF;
     const uint32_t stage_base = smem_stage0 + (uint32_t)(warp - 2) * (uint32_t)(SBUF * 4096);
@@ -730,6 +733,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             *reinterpret_cast<uint4*>(row_ptr + ((q ^ (lane & 7)) << 4)) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
             *reinterpret_cast<uint4*>(row_ptr + (((q + 4) ^ (lane & 7)) << 4)) = make_uint4(o3[0], o3[1], o3[2], o3[3]);
+          }
+        } else if constexpr (EPI == EPI_DRELU2) {
+          const uint32_t b = res_uses % (uint32_t)RD;
+          if (!mbar_wait(smem_u32(&bar_res[warp - 2][b]), (res_uses / (uint32_t)RD) & 1u, status, DEV_MBAR_TIMEOUT_EPILOGUE)) {
+            ok = false;
+            break;
+          }
+          const uint8_t* hrow = res_ptr + b * 4096u + lane * 128;  // this row's 64 bf16 of h
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const uint4 hraw = *reinterpret_cast<const uint4*>(hrow + ((q ^ (lane & 7)) << 4));
+            const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&hraw);
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 h = __bfloat1622float2(hp[e]);
+              const float two_a = 2.f * epi.alpha;
+              o[e] = pack2_bf16(two_a * acc[8 * q + 2 * e] * fmaxf(h.x, 0.f), two_a * acc[8 * q + 2 * e + 1] * fmaxf(h.y, 0.f));
+            }
+            *reinterpret_cast<uint4*>(row_ptr + ((q ^ (lane & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
           }
         } else if constexpr (kBf16Out) {
           if constexpr (EPI == EPI_STORE_BF16_TGT) {

@@ -85,6 +85,8 @@ const char* ane_op_sumsq_noalloc_last_error(void);
  *               [m, 2n] bf16 with h1 | h3 interleaved in blocks of 32 columns; d_c receives d h13 [m, 2n] bf16 in the
  *               same layout (ldc its pitch): d h1 = d gate * h3 * silu'(h1), d h3 = d gate * silu(h1)
  *               (the reference's FFN is ReLU^2, ane/common.go:146; this is the llama-style counterpart)
+ *           10: ReLU^2 backward fused into the product (dX form, bf16 operands, n % 64 == 0): A*B is d gate [m, n];
+ *               d_aux = h [m, n] bf16; d_c receives d h = d gate * 2 max(h, 0) in bf16 (ane/common.go:146 differentiated)
  */
 typedef struct ane_gemm_args {
   uint32_t struct_size;
@@ -103,7 +105,7 @@ typedef struct ane_gemm_args {
   const float* d_s2;
   int32_t ldres;
   int32_t split_k; /* 0 = library chooses */
-  const void* d_aux; /* out_mode 7: h13 */
+  const void* d_aux; /* out_mode 7: h13; out_mode 10: h */
   int32_t ldaux;
   int32_t pad_;
 } ane_gemm_args;

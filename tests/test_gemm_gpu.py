@@ -230,6 +230,39 @@ def test_swiglu_backward_fused_into_the_dx_product(M, Hd, K):
         lib.ane_dev_free(p)
 
 
+@pytest.mark.parametrize("M,Hd,K", [(8192, 2048, 768), (320, 192, 128), (100, 64, 72)])
+def test_relu2_backward_fused_into_the_dx_product(M, Hd, K):
+    """out_mode 10: d gate = dOut . W2 stays in the accumulators; the epilogue reads h and writes
+    d h = d gate * 2 max(h, 0) (the reference's ReLU^2 activation, ane/common.go:146, differentiated).  Against
+    float64 on the same bf16 operands; the step's shape (CTA-pair tiles) and ragged ones (single-CTA tiles)."""
+    rng = np.random.default_rng(M + Hd + 1)
+    dOut = _bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    W2 = _bf16_round((rng.standard_normal((K, Hd)) / np.sqrt(K)).astype(np.float32))       # stored [K, N]: MN-major B
+    h = _bf16_round(rng.standard_normal((M, Hd)).astype(np.float32) * 2.0)
+    dA, dB, dH = _up_bf16(dOut), _up_bf16(W2), _up_bf16(h)
+    dC = lib.ane_dev_malloc(M * Hd * 2)
+    _ck(lib.ane_dev_memset(dC, 0xFF, M * Hd * 2))
+    g = _ffi.GemmArgs()
+    g.struct_size = ctypes.sizeof(_ffi.GemmArgs)
+    g.dtype = ane.DTYPE_BF16
+    g.d_a, g.d_b, g.d_c, g.d_aux = dA, dB, dC, dH
+    g.m, g.n, g.k = M, Hd, K
+    g.lda, g.ldb, g.ldc, g.ldaux = K, Hd, Hd, Hd
+    g.a_mn, g.b_mn, g.out_mode, g.alpha = 0, 1, 10, 1.0
+    _ck(lib.ane_op_gemm(ctypes.byref(g)))
+    _ck(lib.ane_dev_sync())
+    st = ctypes.c_int32(0)
+    _ck(lib.ane_ops_device_status(ctypes.byref(st)))
+    assert st.value == 0
+    got = _down_bf16(dC, (M, Hd))
+    want = (dOut.astype(np.float64) @ W2.astype(np.float64)) * 2.0 * np.maximum(h.astype(np.float64), 0.0)
+    assert np.isfinite(got).all()
+    assert rel_l2(got, want) < 4e-3          # one bf16 rounding of the output
+    assert np.all(got[h <= 0] == 0)          # exact zeros where the activation was off
+    for p in (dA, dB, dH, dC):
+        lib.ane_dev_free(p)
+
+
 def test_gemm_rejects_misaligned_pitch():
     A = np.zeros((16, 20), np.float32)  # 20 bf16 = 40 bytes per row: not a 16-byte multiple
     dA, dB, dC = _up_bf16(A), _up_bf16(A), _up(np.zeros((16, 16), np.float32))
