@@ -336,7 +336,7 @@ def run_ours(args):
                     "loss_spread": round(max(losses) - min(losses), 5),
                     "note": "ranks train on different windows, so their last losses differ; weights must not"}
 
-    # ---- dominant-kernel roofline: every GEMM launch timed with CUDA events over one profiled step
+    # ---- dominant-kernel roofline: every GEMM launch timed with CUDA events over a profiled step
     # (three profiled steps, the median taken: one step's sum moves by several per cent with the clocks)
     prof = []
     for _ in range(3):
