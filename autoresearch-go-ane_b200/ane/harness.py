@@ -9,6 +9,8 @@
   train            README.md:17, program.md:31: steps for a fixed wall-clock budget that starts after
                    the first three steps, learning rate set from the schedule before every step.  The
                    reference describes this loop but ships an empty main.go; this is the loop as described.
+  benchmark_step / benchmark_eval_logits / benchmark_eval_loss
+                   bench_test.go:75-158  the three benchmarks with the reference's metric names
 
 The reference's evalLoss slices the [vocab][seq] logits as if they were [seq][vocab] (harness.go:62); the
 device path scores position t with the logits of position t, i.e. the indexing the harness intends.
@@ -147,3 +149,50 @@ def train(engine, budget_s: float | None = None, max_steps: int | None = None, p
     engine.flush()
     log.seconds = clock() - t0
     return log
+
+
+def benchmark_step(engine, n: int = 10, accum_steps: int | None = None) -> dict:
+    """BenchmarkStep (bench_test.go:75-119): three untimed steps, then n steps; metrics taken from the last
+    StepResult as the reference does.  `tok/s` follows the reference's formula, seq * AccumSteps / StepDuration
+    (bench_test.go:92,107-110), although one Step() handles `batch` sequences and no accumulation loop - with
+    the reference's own engine (batch 1) that over-reports by AccumSteps; `tok/s_processed` counts the tokens
+    the step really pushed through.  `ane_ms` is the device time of the step (the reference's ANE evaluation
+    time), `adam_ms` the optimizer's, as ane.StepResult reports them."""
+    for _ in range(3):
+        engine.step()
+    accum = accum_steps if accum_steps is not None else max(1, int(getattr(engine.opts, "accum_steps", 1)))
+    last = None
+    t0 = time.perf_counter()
+    for _ in range(n):
+        last = engine.step()
+    wall = time.perf_counter() - t0
+    out = {"loss": float(last.loss), "step_ms": last.step_duration * 1e3,
+           "ane_ms": last.device_eval_duration * 1e3, "adam_ms": last.adam_duration * 1e3,
+           "ns/op": wall / n * 1e9}
+    if last.step_duration > 0:
+        out["tok/s"] = engine.seq * accum / last.step_duration
+        out["tok/s_processed"] = engine.opts.batch * engine.seq / last.step_duration
+    return out
+
+
+def benchmark_eval_logits(engine, tokens: np.ndarray, n: int = 10, seq: int = EVAL_SEQ_LEN) -> dict:
+    """BenchmarkEvalLogits (bench_test.go:121-139): one window of `seq` tokens per call, logits returned."""
+    window = np.ascontiguousarray(tokens[:seq])
+    engine.eval_logits(window)
+    t0 = time.perf_counter()
+    for _ in range(n):
+        engine.eval_logits(window)
+    dt = (time.perf_counter() - t0) / n
+    return {"ns/op": dt * 1e9, "tok/s": seq / dt}
+
+
+def benchmark_eval_loss(engine, tokens: np.ndarray, n: int = 1, eval_tokens: int = EVAL_TOKENS,
+                        reference_indexing: bool = False) -> dict:
+    """BenchmarkEvalLoss (bench_test.go:141-158): the full validation pass; val_loss in nats, val_bpb = loss /
+    ln 2 / 3.7."""
+    loss = 0.0
+    t0 = time.perf_counter()
+    for _ in range(n):
+        loss = eval_loss(engine, tokens, eval_tokens=eval_tokens, reference_indexing=reference_indexing)
+    dt = (time.perf_counter() - t0) / n
+    return {"val_loss": loss, "val_bpb": val_bpb(loss), "ns/op": dt * 1e9}

@@ -141,6 +141,27 @@ def test_train_loop_spends_the_budget_after_three_warmup_steps():
 
 
 # ------------------------------------------------------------------ ckpt.go / engine.go trailer
+def test_benchmark_step_reports_the_reference_metric_names():
+    """bench_test.go:75-119: three untimed steps, then n; loss / step_ms / ane_ms / adam_ms from the last result
+    and tok/s by the reference's own formula (seq * AccumSteps / StepDuration)."""
+    e = FakeEngine(seq=16, batch=2)
+    real_step = e.step
+
+    def step():
+        r = real_step()
+        r.step_duration, r.device_eval_duration, r.adam_duration = 0.004, 0.003, 0.0005
+        return r
+
+    e.step = step
+    out = H.benchmark_step(e, n=5, accum_steps=8)
+    assert e.steps == 8
+    assert out["loss"] == pytest.approx(10.0 / 8)
+    assert out["step_ms"] == pytest.approx(4.0) and out["ane_ms"] == pytest.approx(3.0) and out["adam_ms"] == pytest.approx(0.5)
+    assert out["tok/s"] == pytest.approx(16 * 8 / 0.004)               # the reference's figure
+    assert out["tok/s_processed"] == pytest.approx(2 * 16 / 0.004)     # tokens the step really handled
+    assert out["ns/op"] > 0
+
+
 def test_header_is_96_bytes_in_the_reference_field_order():
     d = C.Dims(layers=12, vocab=32000, dim=768, hidden=2048, heads=12, seq=256, arch=E.ARCH_REFERENCE)
     meta = C.TrainMeta(step=7, total_steps=100, lr=3e-4, loss=2.5, cum_compile=1.5, cum_train=20.25, cum_wall=30.5,

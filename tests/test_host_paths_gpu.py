@@ -65,6 +65,27 @@ def test_training_driver_and_evaluation_harness_on_an_engine(arch, quirks):
     e.close()
 
 
+def test_benchmarks_with_the_reference_metric_names_on_an_engine():
+    """The three benchmarks of bench_test.go:75-158 through the harness twins on a real engine: metric names,
+    consistency of tok/s with the step's own duration, val_bpb from val_loss."""
+    toks = O.zipf_tokens(4096, CFG["vocab"], 19)
+    hyper = dict(lr=1e-3, accum_steps=2)
+    m, e = make_pair(ane, CFG, arch=O.ARCH_L, quirks=0, dtype=ane.DTYPE_F32, batch=2, hyper=hyper, tokens=toks,
+                     debug_taps=False, std=0.1)
+    b = H.benchmark_step(e, n=4)
+    assert set(b) >= {"loss", "tok/s", "tok/s_processed", "step_ms", "ane_ms", "adam_ms", "ns/op"}
+    assert np.isfinite(b["loss"]) and b["step_ms"] > 0 and 0 < b["ane_ms"] <= b["step_ms"] + 1e-6
+    assert b["tok/s"] == pytest.approx(CFG["seq"] * 2 / (b["step_ms"] * 1e-3))
+    assert b["tok/s_processed"] == pytest.approx(2 * CFG["seq"] / (b["step_ms"] * 1e-3))
+    assert e.state().cum_steps == 7
+    lg = H.benchmark_eval_logits(e, toks, n=3, seq=CFG["seq"])
+    assert lg["ns/op"] > 0 and lg["tok/s"] == pytest.approx(CFG["seq"] / (lg["ns/op"] * 1e-9))
+    ev = H.benchmark_eval_loss(e, toks, eval_tokens=600)
+    assert ev["val_loss"] == pytest.approx(H.eval_loss(e, toks, eval_tokens=600), abs=1e-6)
+    assert ev["val_bpb"] == pytest.approx(ev["val_loss"] / np.log(2.0) / 3.7)
+    e.close()
+
+
 def test_load_checkpoint_reseeds_the_sampler_and_keeps_the_wall_clock(tmp_path):
     toks = O.zipf_tokens(8192, CFG["vocab"], 5)
     hyper = dict(lr=1e-3, accum_steps=1, seed=7)
