@@ -71,6 +71,8 @@ SIGNATURES = {
     "ane_dev_set": (c_int32, [c_int32]),
     "ane_dev_malloc": (c_void_p, [c_uint64]),
     "ane_dev_free": (c_int32, [c_void_p]),
+    "ane_host_malloc": (c_void_p, [c_uint64]),
+    "ane_host_free": (c_int32, [c_void_p]),
     "ane_dev_h2d": (c_int32, [c_void_p, c_void_p, c_uint64]),
     "ane_dev_d2h": (c_int32, [c_void_p, c_void_p, c_uint64]),
     "ane_dev_memset": (c_int32, [c_void_p, c_int32, c_uint64]),

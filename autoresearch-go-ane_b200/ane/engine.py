@@ -5,6 +5,7 @@ Everything is executed by libane_b200.so on the GPU."""
 from __future__ import annotations
 
 import ctypes
+import weakref
 from ctypes import POINTER, byref, c_double, c_float, c_uint8, c_uint16, c_uint64, c_void_p
 from dataclasses import dataclass, field
 
@@ -335,6 +336,21 @@ class Engine:
 
     def launch_count(self) -> int:
         return int(lib.ane_launch_count(self._h))
+
+
+def pinned_empty(shape, dtype=np.float32) -> np.ndarray:
+    """An uninitialised array in page-locked host memory (ane_host_malloc), freed when the array and its views are
+    gone.  Engine.eval_logits(out=...) writes such an array straight from the device, without the staging copy an
+    ordinary array needs."""
+    dt = np.dtype(dtype)
+    count = int(np.prod(shape))
+    nbytes = max(1, count * dt.itemsize)
+    p = lib.ane_host_malloc(nbytes)
+    if not p:
+        raise MemoryError(lib.ane_ops_last_error().decode())
+    buf = (ctypes.c_byte * nbytes).from_address(p)
+    weakref.finalize(buf, lib.ane_host_free, p)
+    return np.frombuffer(buf, dtype=dt, count=count).reshape(shape)
 
 
 def open(opts: Options) -> Engine:  # noqa: A001 - mirrors ane.Open

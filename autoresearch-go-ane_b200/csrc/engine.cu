@@ -1656,6 +1656,19 @@ int EngineT<T>::eval_logits(const uint16_t* tokens, uint32_t n_seq, float* out, 
       // fifth of the PCIe rate (32.8 MB cross in 0.6-0.7 ms), so the pieces are dealt to several threads
       // (ANE_B200_EVAL_COPY_THREADS; default: the host's cores, at most 16) - measured per call with 2 / 4 / 8 /
       // 12 / 16 threads: 2.54 / 2.10 / 1.99 / 1.91 / 1.75 ms, of which 0.83 ms is the forward pass.
+      float* dst = out + (size_t)(s0 + b) * per_seq;
+      {
+        // A page-locked destination (ane_host_malloc, or memory the caller registered) takes the copy directly.
+        cudaPointerAttributes pa;
+        if (cudaPointerGetAttributes(&pa, dst) == cudaSuccess && pa.type == cudaMemoryTypeHost) {
+          if ((rc = cuda_check(cudaMemcpyAsync(dst, logits_, sizeof(float) * per_seq, cudaMemcpyDeviceToHost, stream_),
+                               "logits download")) != 0)
+            return rc;
+          if ((rc = cuda_check(cudaStreamSynchronize(stream_), "logits sync")) != 0) return rc;
+          continue;
+        }
+        cudaGetLastError();  // an ordinary pointer may leave an error code behind on older drivers
+      }
       static const int kPieces = [] {
         const char* e = getenv("ANE_B200_EVAL_PIECES");
         const int v = e ? atoi(e) : 32;
@@ -1679,7 +1692,6 @@ int EngineT<T>::eval_logits(const uint16_t* tokens, uint32_t n_seq, float* out, 
         const int v = e ? atoi(e) : (hw == 0 ? 4 : (int)hw);
         return v < 1 ? 1 : (v > 16 ? 16 : v);
       }();
-      float* dst = out + (size_t)(s0 + b) * per_seq;
       // small outputs (under 1 MiB) are not worth a thread start
       const int use_threads = per_seq * sizeof(float) < (1u << 20) ? 1 : copy_threads;
       std::atomic<int> copy_err{0};

@@ -87,6 +87,19 @@ int32_t ane_dev_free(void* d_ptr) {
   CK(cudaFree(d_ptr));
   return 0;
 }
+void* ane_host_malloc(uint64_t bytes) {
+  void* p = nullptr;
+  cudaError_t e = cudaMallocHost(&p, bytes ? bytes : 1);
+  if (e != cudaSuccess) {
+    cuda_fail(e, "cudaMallocHost");
+    return nullptr;
+  }
+  return p;
+}
+int32_t ane_host_free(void* h_ptr) {
+  CK(cudaFreeHost(h_ptr));
+  return 0;
+}
 int32_t ane_dev_h2d(void* d_dst, const void* h_src, uint64_t bytes) {
   CK(cudaMemcpy(d_dst, h_src, bytes, cudaMemcpyHostToDevice));
   return 0;

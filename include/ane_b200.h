@@ -45,6 +45,11 @@ int32_t ane_dev_free(void* d_ptr);
 int32_t ane_dev_h2d(void* d_dst, const void* h_src, uint64_t bytes);
 int32_t ane_dev_d2h(void* h_dst, const void* d_src, uint64_t bytes);
 int32_t ane_dev_memset(void* d_ptr, int32_t value, uint64_t bytes);
+/* Page-locked host memory.  ane_eval_logits copies into such a buffer straight from the device; into ordinary
+ * (pageable) memory the logits go through the engine's own page-locked staging buffer and a host copy.  The
+ * reference has no counterpart: its EvalLogits returns a fresh Go slice (ane/engine.go:954-1038). */
+void* ane_host_malloc(uint64_t bytes);
+int32_t ane_host_free(void* h_ptr);
 int32_t ane_dev_sync(void);
 int32_t ane_timer_begin(void);
 int32_t ane_timer_end(float* out_ms);

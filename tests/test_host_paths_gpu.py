@@ -86,6 +86,24 @@ def test_benchmarks_with_the_reference_metric_names_on_an_engine():
     e.close()
 
 
+def test_eval_logits_into_page_locked_memory_matches_the_staged_copy():
+    """ane.pinned_empty gives page-locked memory; EvalLogits copies into it straight from the device and must
+    return what the staged path (pageable array) returns, in both layouts and for several windows."""
+    toks = O.zipf_tokens(4096, CFG["vocab"], 23)
+    m, e = make_pair(ane, CFG, arch=O.ARCH_L, quirks=0, dtype=ane.DTYPE_F32, batch=2, hyper=dict(lr=1e-3), tokens=toks,
+                     debug_taps=False, std=0.1)
+    windows = np.ascontiguousarray(toks[:3 * CFG["seq"]])
+    for layout in (0, 1):
+        want = e.eval_logits(windows, layout=layout)
+        out = ane.pinned_empty(want.shape)
+        out[...] = -1.0
+        got = e.eval_logits(windows, layout=layout, out=out)
+        assert got is out
+        np.testing.assert_array_equal(got, want)
+    del out, got
+    e.close()
+
+
 def test_load_checkpoint_reseeds_the_sampler_and_keeps_the_wall_clock(tmp_path):
     toks = O.zipf_tokens(8192, CFG["vocab"], 5)
     hyper = dict(lr=1e-3, accum_steps=1, seed=7)
